@@ -1,0 +1,404 @@
+// C[M,N] = epilogue( A[M,K] * B[N,K]^T ), bf16 operands, fp32 accumulation in TMEM.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer (A and B k-blocks of 64 -> 128-byte-swizzled shared tiles)
+//   warp 1      tcgen05.mma issuer (one lane), owns the TMEM allocation
+//   warps 2..9  epilogue: TMEM -> registers -> fused math -> swizzled staging -> TMA store
+// Two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// Fused epilogues (all optional, all applied on fp32 values):
+//   x = (acc + bias[col]) * scale[col]            (scale before the activation unless scale_post)
+//   Z = x                                         (second output: the pre-activation, MODE_Z)
+//   y = act(x)   act in {none, GELU, SiLU, ReLU, softmax over aligned groups of 64 columns}
+//   y = y + aux | y * GELU'(aux) | y * SiLU'(aux) | y * ReLU'(aux) | softmax-backward(y; aux = p)
+// The auxiliary tile is prefetched by TMA into the same staging buffer the result leaves from.
+// A may be split along K into two tensors (A | A2), which gives K-concatenated GEMMs
+// without materialising the concatenation.
+#pragma once
+#include "common.cuh"
+#include "tmap.cuh"
+
+namespace pnm {
+
+enum { ACT_NONE = 0, ACT_GELU = 1, ACT_SILU = 2, ACT_RELU = 3, ACT_SOFTMAX64 = 4 };
+enum { AUX_NONE = 0, AUX_ADD = 1, AUX_DGELU = 2, AUX_DSOFTMAX = 3, AUX_DSILU = 4, AUX_DRELU = 5 };
+enum { MODE_PLAIN = 0, MODE_Z = 1, MODE_AUX = 2 };
+
+struct GemmArgs {
+  int M, N, K, K1;
+  const float* bias;
+  const float* scale;
+  float* group_out;
+  int act;
+  int aux_mode;
+  int scale_post;
+  int num_m_tiles, num_n_tiles;
+  int* err;
+};
+
+constexpr int kGemmThreads = 320;
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kChunkBytes = 32 * 128;  // 32 rows x 64 bf16
+
+template <int BN, int MODE>
+struct GemmCfg {
+  static constexpr int NBUF = (MODE == MODE_AUX) ? 3 : 2;
+  static constexpr int STAGE_BYTES = kBM * kBK * 2 + BN * kBK * 2;
+  static constexpr int STAGING = 8 * NBUF * kChunkBytes;
+  static constexpr int BUDGET = 232448 - 1024 /*align*/ - 512 /*barriers*/;
+  static constexpr int STAGES_RAW = (BUDGET - STAGING) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
+  static constexpr int SMEM = 1024 + STAGES * STAGE_BYTES + STAGING + 512;
+  static constexpr int TMEM_COLS = 2 * BN;  // 256 or 512: powers of two
+  static_assert(STAGES >= 2, "not enough shared memory for a pipeline");
+};
+
+__device__ __forceinline__ void stage_write_row(uint8_t* buf, int lane, const float* v) {
+  // 64 fp32 -> 64 bf16 = 8 chunks of 16 bytes, chunk j of row r lands at (j ^ (r & 7)).
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint4 u;
+    u.x = pack_bf16x2(v[8 * j + 0], v[8 * j + 1]);
+    u.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+    u.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+    u.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+    *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = u;
+  }
+}
+__device__ __forceinline__ void stage_read_row(const uint8_t* buf, int lane, float* a) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint4 u = *reinterpret_cast<const uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4));
+    float2 f;
+    f = unpack_bf16x2(u.x); a[8 * j + 0] = f.x; a[8 * j + 1] = f.y;
+    f = unpack_bf16x2(u.y); a[8 * j + 2] = f.x; a[8 * j + 3] = f.y;
+    f = unpack_bf16x2(u.z); a[8 * j + 4] = f.x; a[8 * j + 5] = f.y;
+    f = unpack_bf16x2(u.w); a[8 * j + 6] = f.x; a[8 * j + 7] = f.y;
+  }
+}
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
+               const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+               const __grid_constant__ CUtensorMap tmX /* Z (store) or aux (load) */, const GemmArgs g) {
+  using Cfg = GemmCfg<BN, MODE>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int NBUF = Cfg::NBUF;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* staging = base + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + Cfg::STAGING);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint64_t* auxbar = tempty + 2;                      // [8 warps][NBUF]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(auxbar + 8 * 3);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = g.num_m_tiles * g.num_n_tiles;
+  const int num_kb = (g.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 8); }
+    for (int i = 0; i < 8 * 3; ++i) mbar_init(&auxbar[i], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmC);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const int mt = tile / g.num_n_tiles, nt = tile % g.num_n_tiles;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          uint8_t* sa = base + s * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + kBM * kBK * 2;
+          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+          const int k = kb * kBK;
+          if (k < g.K1) tma_load_2d(sa, &tmA, &full[s], k, mt * kBM);
+          else tma_load_2d(sa, &tmA2, &full[s], k - g.K1, mt * kBM);
+          tma_load_2d(sb, &tmB, &full[s], k, nt * BN);
+        }
+      }
+      if (!ok) {
+        // give copies already in flight a bounded chance to land before the CTA leaves
+        for (int s = 0; s < STAGES; ++s)
+          for (int i = 0; i < (1 << 14) && !mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1); ++i) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, false, false);
+      uint32_t it = 0, tc = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++tc) {
+        const int acc = tc & 1;
+        const uint32_t aph = (tc >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], aph ^ 1, abort_flag, g.err, ERR_WAIT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          uint8_t* sa = base + s * Cfg::STAGE_BYTES;
+          const uint64_t ad = make_smem_desc(smem_u32(sa), 16, 1024, 2);
+          const uint64_t bd = make_smem_desc(smem_u32(sa + kBM * kBK * 2), 16, 1024, 2);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)
+            umma_f16(d, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&tfull[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int e = warp - 2, q = warp & 3, h = e >> 2;
+    constexpr int CH = BN / 128;  // 64-column chunks per warp per tile
+    uint8_t* stg = staging + e * NBUF * kChunkBytes;
+    uint64_t* mybar = auxbar + e * 3;
+    uint32_t use = 0, tc = 0;
+    bool ok = true;
+
+    auto item_coords = [&](uint32_t item, int& r0, int& c0) -> bool {
+      const int tile = blockIdx.x + int(item / CH) * gridDim.x;
+      if (tile >= num_tiles) return false;
+      const int mt = tile / g.num_n_tiles, nt = tile % g.num_n_tiles;
+      r0 = mt * kBM + q * 32;
+      c0 = nt * BN + h * (BN / 2) + int(item % CH) * 64;
+      return true;
+    };
+    auto issue_aux = [&](uint32_t item) {
+      int r0, c0;
+      if (!item_coords(item, r0, c0)) return;
+      if (lane == 0) {
+        tma_store_wait_read<NBUF - 2 < 0 ? 0 : NBUF - 2>();
+        const int b = item % NBUF;
+        mbar_expect_tx(&mybar[b], kChunkBytes);
+        tma_load_2d(stg + b * kChunkBytes, &tmX, &mybar[b], c0, r0);
+      }
+    };
+    if (MODE == MODE_AUX) issue_aux(0);
+
+    uint32_t item = 0;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++tc) {
+      const int acc = tc & 1;
+      const uint32_t aph = (tc >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], aph, abort_flag, g.err, ERR_WAIT_TMEM_FULL)) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int ci = 0; ci < CH; ++ci, ++item) {
+        int r0, c0;
+        item_coords(item, r0, c0);
+        if (MODE == MODE_AUX) issue_aux(item + 1);
+        float v[64];
+        const uint32_t taddr = tmem_base + acc * BN + h * (BN / 2) + ci * 64 + (uint32_t(q * 32) << 16);
+        tmem_ld32(taddr, v);
+        tmem_ld32(taddr + 32, v + 32);
+        tmem_ld_wait();
+        if (ci == CH - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty[acc]);
+        }
+        const bool store_ok = (r0 < g.M) && (c0 < g.N);
+        const bool full_cols = (c0 + 64 <= g.N);
+        // ---- x = (acc + bias) * scale
+        if (g.bias) {
+          if (full_cols) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + c0) + j);
+              v[4 * j] += b.x; v[4 * j + 1] += b.y; v[4 * j + 2] += b.z; v[4 * j + 3] += b.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) if (c0 + j < g.N) v[j] += __ldg(g.bias + c0 + j);
+          }
+        }
+        if (g.scale && !g.scale_post) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) if (c0 + j < g.N) v[j] *= __ldg(g.scale + c0 + j);
+        }
+        // ---- second output: pre-activation
+        if (MODE == MODE_Z) {
+          const int b = use % NBUF;
+          if (lane == 0) tma_store_wait_read<NBUF - 1>();
+          __syncwarp();
+          stage_write_row(stg + b * kChunkBytes, lane, v);
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (store_ok) tma_store_2d(stg + b * kChunkBytes, &tmX, c0, r0);
+            tma_store_commit();
+          }
+          ++use;
+        }
+        // ---- activation
+        switch (g.act) {
+          case ACT_GELU:
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = gelu_f(v[j]);
+            break;
+          case ACT_SILU:
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = silu_f(v[j]);
+            break;
+          case ACT_RELU:
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = fmaxf(v[j], 0.f);
+            break;
+          case ACT_SOFTMAX64: {
+            float m = v[0];
+#pragma unroll
+            for (int j = 1; j < 64; ++j) m = fmaxf(m, v[j]);
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < 64; ++j) { v[j] = ex2_fast((v[j] - m) * 1.4426950409f); s += v[j]; }
+            const float inv = __frcp_rn(s);
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] *= inv;
+          } break;
+          default: break;
+        }
+        // ---- auxiliary operand
+        int b = use % NBUF;
+        if (MODE == MODE_AUX) {
+          b = item % NBUF;
+          const uint32_t bph = (item / NBUF) & 1;
+          if (!mbar_wait(&mybar[b], bph, abort_flag, g.err, ERR_WAIT_AUX)) { ok = false; break; }
+          float a[64];
+          stage_read_row(stg + b * kChunkBytes, lane, a);
+          switch (g.aux_mode) {
+            case AUX_ADD:
+#pragma unroll
+              for (int j = 0; j < 64; ++j) v[j] += a[j];
+              break;
+            case AUX_DGELU:
+#pragma unroll
+              for (int j = 0; j < 64; ++j) v[j] *= gelu_grad_f(a[j]);
+              break;
+            case AUX_DSILU:
+#pragma unroll
+              for (int j = 0; j < 64; ++j) v[j] *= silu_grad_f(a[j]);
+              break;
+            case AUX_DRELU:
+#pragma unroll
+              for (int j = 0; j < 64; ++j) v[j] = a[j] > 0.f ? v[j] : 0.f;
+              break;
+            case AUX_DSOFTMAX: {
+              float dot = 0.f;
+#pragma unroll
+              for (int j = 0; j < 64; ++j) dot += v[j] * a[j];
+              float gs = 0.f;
+#pragma unroll
+              for (int j = 0; j < 64; ++j) {
+                v[j] = a[j] * (v[j] - dot);
+                gs += (a[j] > 0.f) ? v[j] * __logf(a[j]) : 0.f;
+              }
+              if (g.group_out) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) gs += __shfl_xor_sync(0xffffffffu, gs, o);
+                if (lane == 0 && c0 < g.N) atomicAdd(g.group_out + (c0 >> 6), gs);
+              }
+            } break;
+            default: break;
+          }
+        } else {
+          if (lane == 0) tma_store_wait_read<NBUF - 1>();
+          __syncwarp();
+        }
+        if (g.scale && g.scale_post) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) if (c0 + j < g.N) v[j] *= __ldg(g.scale + c0 + j);
+        }
+        stage_write_row(stg + b * kChunkBytes, lane, v);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (store_ok) tma_store_2d(stg + b * kChunkBytes, &tmC, c0, r0);
+          tma_store_commit();
+        }
+        ++use;
+      }
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+    __syncwarp();
+  }
+  // ------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------- host
+struct GemmCall {
+  const void* A; int lda;
+  const void* A2; int lda2;
+  const void* B; int ldb;
+  void* C; int ldc;
+  void* Z; int ldz;          // optional second output (pre-activation)
+  const void* AUX; int ldaux; // optional auxiliary input [M,N]
+  int M, N, K, K1;
+  const float* bias; const float* scale; float* group_out;
+  int act, aux_mode, scale_post;
+  int max_ctas;  // 0 = number of SMs
+};
+
+template <int BN, int MODE>
+inline int launch_gemm_tn(const GemmCall& c, int num_sms, int* err_word, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN, MODE>;
+  CUtensorMap tA, tA2, tB, tC, tX;
+  const int K2 = c.K - c.K1;
+  if (make_tmap_2d_b16(&tA, c.A, c.M, c.K1, c.lda, kBM, kBK)) return -10;
+  if (K2 > 0) { if (make_tmap_2d_b16(&tA2, c.A2, c.M, K2, c.lda2, kBM, kBK)) return -11; }
+  else tA2 = tA;
+  if (make_tmap_2d_b16(&tB, c.B, c.N, c.K, c.ldb, BN, kBK)) return -12;
+  if (make_tmap_2d_b16(&tC, c.C, c.M, c.N, c.ldc, 32, 64)) return -13;
+  if (MODE == MODE_Z) { if (make_tmap_2d_b16(&tX, c.Z, c.M, c.N, c.ldz, 32, 64)) return -14; }
+  else if (MODE == MODE_AUX) { if (make_tmap_2d_b16(&tX, c.AUX, c.M, c.N, c.ldaux, 32, 64)) return -15; }
+  else tX = tC;
+  GemmArgs g;
+  g.M = c.M; g.N = c.N; g.K = c.K; g.K1 = c.K1;
+  g.bias = c.bias; g.scale = c.scale; g.group_out = c.group_out;
+  g.act = c.act; g.aux_mode = c.aux_mode; g.scale_post = c.scale_post;
+  g.num_m_tiles = (c.M + kBM - 1) / kBM;
+  g.num_n_tiles = (c.N + BN - 1) / BN;
+  g.err = err_word;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_tn_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
+        cudaSuccess)
+      return -16;
+    attr_set = true;
+  }
+  int tiles = g.num_m_tiles * g.num_n_tiles;
+  int cap = c.max_ctas > 0 ? c.max_ctas : num_sms;
+  int grid = tiles < cap ? tiles : cap;
+  gemm_tn_kernel<BN, MODE><<<grid, kGemmThreads, Cfg::SMEM, stream>>>(tA, tA2, tB, tC, tX, g);
+  return cudaGetLastError() == cudaSuccess ? 0 : -17;
+}
+
+}  // namespace pnm

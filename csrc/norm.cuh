@@ -1,0 +1,250 @@
+// LayerNorm forward / backward over the last dimension, bf16 activations, fp32 statistics
+// and parameters.  One warp per row, 16-byte vector loads, persistent grid-stride loop so
+// that the per-column reductions of the backward (dgamma, dbeta) stay in registers until
+// the CTA writes one partial row to scratch; a second tiny kernel folds the partials.
+#pragma once
+#include "common.cuh"
+
+namespace pnm {
+
+constexpr int kLnWarps = 8;
+constexpr int kLnMaxVec = 4;  // supports C up to 32 lanes * 8 elems * 4 = 1024
+
+// y = (x - mean) * rstd * gamma + beta ; optional second input r: normalises (x + r) and
+// writes the sum to `sum_out` (fused residual add).
+template <int VEC>
+__global__ void __launch_bounds__(kLnWarps * 32)
+layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ r,
+                     const float* __restrict__ gamma, const float* __restrict__ beta, __nv_bfloat16* __restrict__ y,
+                     __nv_bfloat16* __restrict__ sum_out, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                     long long M, int C, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long warp_global = (long long)blockIdx.x * kLnWarps + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * kLnWarps;
+  float gam[VEC][8], bet[VEC][8];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) {
+    const int c = (v * 32 + lane) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      gam[v][j] = (c + j < C) ? gamma[c + j] : 0.f;
+      bet[v][j] = (c + j < C && beta) ? beta[c + j] : 0.f;
+    }
+  }
+  for (long long row = warp_global; row < M; row += nwarps) {
+    float val[VEC][8];
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const int c = (v * 32 + lane) * 8;
+      if (c < C) {
+        uint4 u = *reinterpret_cast<const uint4*>(x + row * C + c);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        uint32_t rw[4] = {0, 0, 0, 0};
+        if (r) {
+          uint4 ur = *reinterpret_cast<const uint4*>(r + row * C + c);
+          rw[0] = ur.x; rw[1] = ur.y; rw[2] = ur.z; rw[3] = ur.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = unpack_bf16x2(w[j]);
+          if (r) { float2 fr = unpack_bf16x2(rw[j]); f.x += fr.x; f.y += fr.y; }
+          val[v][2 * j] = f.x; val[v][2 * j + 1] = f.y;
+          s += f.x + f.y;
+        }
+        if (r && sum_out) {
+          uint4 o;
+          o.x = pack_bf16x2(val[v][0], val[v][1]); o.y = pack_bf16x2(val[v][2], val[v][3]);
+          o.z = pack_bf16x2(val[v][4], val[v][5]); o.w = pack_bf16x2(val[v][6], val[v][7]);
+          *reinterpret_cast<uint4*>(sum_out + row * C + c) = o;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) val[v][j] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float mean = s / C;
+    float sq = 0.f;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const int c = (v * 32 + lane) * 8;
+      if (c < C) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float d = val[v][j] - mean; sq += d * d; }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float rstd = rsqrtf(sq / C + eps);
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const int c = (v * 32 + lane) * 8;
+      if (c < C) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (val[v][j] - mean) * rstd * gam[v][j] + bet[v][j];
+        uint4 u;
+        u.x = pack_bf16x2(o[0], o[1]); u.y = pack_bf16x2(o[2], o[3]);
+        u.z = pack_bf16x2(o[4], o[5]); u.w = pack_bf16x2(o[6], o[7]);
+        *reinterpret_cast<uint4*>(y + row * C + c) = u;
+      }
+    }
+  }
+}
+
+// dx = rstd * (g*dy - mean_c(g*dy) - xhat * mean_c(g*dy*xhat)) (+ dres) ; partial dgamma/dbeta
+// rows go to scratch[blockIdx.x][2][C].
+template <int VEC>
+__global__ void __launch_bounds__(kLnWarps * 32)
+layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                     const float* __restrict__ gamma, const float* __restrict__ mean_in,
+                     const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
+                     __nv_bfloat16* __restrict__ dx, float* __restrict__ scratch, long long M, int C) {
+  __shared__ float red[kLnWarps][2][32 * 8 + 8];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const long long warp_global = (long long)blockIdx.x * kLnWarps + wib;
+  const long long nwarps = (long long)gridDim.x * kLnWarps;
+  float gam[VEC][8], dg[VEC][8], db[VEC][8];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) {
+    const int c = (v * 32 + lane) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      gam[v][j] = (c + j < C) ? gamma[c + j] : 0.f;
+      dg[v][j] = 0.f; db[v][j] = 0.f;
+    }
+  }
+  for (long long row = warp_global; row < M; row += nwarps) {
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[VEC][8], gy[VEC][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const int c = (v * 32 + lane) * 8;
+      if (c < C) {
+        uint4 ux = *reinterpret_cast<const uint4*>(x + row * C + c);
+        uint4 ud = *reinterpret_cast<const uint4*>(dy + row * C + c);
+        const uint32_t wx[4] = {ux.x, ux.y, ux.z, ux.w}, wd[4] = {ud.x, ud.y, ud.z, ud.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 fx = unpack_bf16x2(wx[j]), fd = unpack_bf16x2(wd[j]);
+          const float h0 = (fx.x - mean) * rstd, h1 = (fx.y - mean) * rstd;
+          xh[v][2 * j] = h0; xh[v][2 * j + 1] = h1;
+          dg[v][2 * j] += fd.x * h0; dg[v][2 * j + 1] += fd.y * h1;
+          db[v][2 * j] += fd.x; db[v][2 * j + 1] += fd.y;
+          const float g0 = fd.x * gam[v][2 * j], g1 = fd.y * gam[v][2 * j + 1];
+          gy[v][2 * j] = g0; gy[v][2 * j + 1] = g1;
+          s1 += g0 + g1; s2 += g0 * h0 + g1 * h1;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { xh[v][j] = 0.f; gy[v][j] = 0.f; }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+      s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    const float m1 = s1 / C, m2 = s2 / C;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const int c = (v * 32 + lane) * 8;
+      if (c < C) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (gy[v][j] - m1 - xh[v][j] * m2);
+        if (dres) {
+          uint4 ur = *reinterpret_cast<const uint4*>(dres + row * C + c);
+          const uint32_t wr[4] = {ur.x, ur.y, ur.z, ur.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(wr[j]); o[2 * j] += f.x; o[2 * j + 1] += f.y; }
+        }
+        uint4 u;
+        u.x = pack_bf16x2(o[0], o[1]); u.y = pack_bf16x2(o[2], o[3]);
+        u.z = pack_bf16x2(o[4], o[5]); u.w = pack_bf16x2(o[6], o[7]);
+        *reinterpret_cast<uint4*>(dx + row * C + c) = u;
+      }
+    }
+  }
+  // fold the warps of this CTA, one vector slot at a time, then write the CTA partial
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { red[wib][0][lane * 8 + j] = dg[v][j]; red[wib][1][lane * 8 + j] = db[v][j]; }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * 256; i += kLnWarps * 32) {
+      const int which = i / 256, col = i % 256;
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < kLnWarps; ++w) s += red[w][which][col];
+      const int c = v * 256 + col;
+      if (c < C) scratch[((size_t)blockIdx.x * 2 + which) * C + c] = s;
+    }
+    __syncthreads();
+  }
+}
+
+// dgamma[c] = sum_b scratch[b][0][c], dbeta[c] = sum_b scratch[b][1][c]
+__global__ void layernorm_bwd_finalize_kernel(const float* __restrict__ scratch, int nblocks, int C,
+                                              float* __restrict__ dgamma, float* __restrict__ dbeta) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 2 * C) return;
+  const int which = i / C, c = i % C;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += scratch[((size_t)b * 2 + which) * C + c];
+  if (which == 0) { if (dgamma) dgamma[c] = s; }
+  else { if (dbeta) dbeta[c] = s; }
+}
+
+inline int ln_vec_for(int C) { return (C + 255) / 256; }
+
+inline int launch_layernorm_fwd(const void* x, const void* r, const float* gamma, const float* beta, void* y,
+                                void* sum_out, float* mean, float* rstd, long long M, int C, float eps, int num_sms,
+                                cudaStream_t st) {
+  if (C % 8 || C > 1024) return -30;
+  long long want = (M + kLnWarps - 1) / kLnWarps;
+  int grid = (int)(want < (long long)num_sms * 8 ? want : (long long)num_sms * 8);
+  if (grid < 1) grid = 1;
+  auto X = (const __nv_bfloat16*)x; auto R = (const __nv_bfloat16*)r; auto Y = (__nv_bfloat16*)y; auto S = (__nv_bfloat16*)sum_out;
+  switch (ln_vec_for(C)) {
+    case 1: layernorm_fwd_kernel<1><<<grid, kLnWarps * 32, 0, st>>>(X, R, gamma, beta, Y, S, mean, rstd, M, C, eps); break;
+    case 2: layernorm_fwd_kernel<2><<<grid, kLnWarps * 32, 0, st>>>(X, R, gamma, beta, Y, S, mean, rstd, M, C, eps); break;
+    case 3: layernorm_fwd_kernel<3><<<grid, kLnWarps * 32, 0, st>>>(X, R, gamma, beta, Y, S, mean, rstd, M, C, eps); break;
+    default: layernorm_fwd_kernel<4><<<grid, kLnWarps * 32, 0, st>>>(X, R, gamma, beta, Y, S, mean, rstd, M, C, eps); break;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -31;
+}
+
+// Number of CTAs the backward uses (= rows of scratch needed: grid * 2 * C floats).
+inline int layernorm_bwd_grid(long long M, int num_sms) {
+  long long want = (M + kLnWarps - 1) / kLnWarps;
+  int grid = (int)(want < (long long)num_sms * 2 ? want : (long long)num_sms * 2);
+  return grid < 1 ? 1 : grid;
+}
+
+inline int launch_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean,
+                                const float* rstd, const void* dres, void* dx, float* dgamma, float* dbeta,
+                                float* scratch, long long M, int C, int num_sms, cudaStream_t st) {
+  if (C % 8 || C > 1024) return -32;
+  const int grid = layernorm_bwd_grid(M, num_sms);
+  auto DY = (const __nv_bfloat16*)dy; auto X = (const __nv_bfloat16*)x; auto DR = (const __nv_bfloat16*)dres; auto DX = (__nv_bfloat16*)dx;
+  switch (ln_vec_for(C)) {
+    case 1: layernorm_bwd_kernel<1><<<grid, kLnWarps * 32, 0, st>>>(DY, X, gamma, mean, rstd, DR, DX, scratch, M, C); break;
+    case 2: layernorm_bwd_kernel<2><<<grid, kLnWarps * 32, 0, st>>>(DY, X, gamma, mean, rstd, DR, DX, scratch, M, C); break;
+    case 3: layernorm_bwd_kernel<3><<<grid, kLnWarps * 32, 0, st>>>(DY, X, gamma, mean, rstd, DR, DX, scratch, M, C); break;
+    default: layernorm_bwd_kernel<4><<<grid, kLnWarps * 32, 0, st>>>(DY, X, gamma, mean, rstd, DR, DX, scratch, M, C); break;
+  }
+  if (cudaGetLastError() != cudaSuccess) return -33;
+  const int threads = 256;
+  layernorm_bwd_finalize_kernel<<<(2 * C + threads - 1) / threads, threads, 0, st>>>(scratch, grid, C, dgamma, dbeta);
+  return cudaGetLastError() == cudaSuccess ? 0 : -34;
+}
+
+}  // namespace pnm

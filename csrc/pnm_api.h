@@ -1,0 +1,34 @@
+// C ABI of the sm_100a kernel library (libpnm_b200.so).  All pointers are device pointers
+// unless stated otherwise; `stream` is a cudaStream_t.  Every function returns 0 on success
+// and a negative code when an argument is rejected or a launch fails.  Device-side
+// time-outs of bounded waits are reported through pnm_get_error().
+#pragma once
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int pnm_version();
+int pnm_num_sms();
+int pnm_get_error();    // synchronising read of the device error word (0 = none)
+int pnm_reset_error();
+
+// C[M,N] = epilogue(A[M,K] * B[N,K]^T); bf16 in/out, fp32 accumulate.  See gemm_tn.cuh.
+int pnm_gemm_tn(const void* A, int lda, const void* A2, int lda2, const void* B, int ldb, void* C, int ldc, void* Z,
+                int ldz, const void* AUX, int ldaux, int M, int N, int K, int K1, const float* bias,
+                const float* scale, float* group_out, int act, int aux_mode, int scale_post, int bn, int max_ctas,
+                void* stream);
+
+// out[Na,Nb] (fp32) += A[M,Na]^T * B[M,Nb];  colsum[Na] += column sums of A (optional).
+int pnm_gemm_nt(const void* A, int lda, const void* B, int ldb, float* out, int ldo, float* colsum, int M, int Na,
+                int Nb, int max_ctas, void* stream);
+
+int pnm_layernorm_fwd(const void* x, const void* r, const float* gamma, const float* beta, void* y, void* sum_out,
+                      float* mean, float* rstd, long long M, int C, float eps, void* stream);
+long long pnm_layernorm_bwd_scratch_floats(long long M, int C);
+int pnm_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
+                      const void* dres, void* dx, float* dgamma, float* dbeta, float* scratch, long long M, int C,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,104 @@
+// Single translation unit of the sm_100a kernel library.  Exposes a plain C ABI (raw device
+// pointers + a CUDA stream) that the Python layer binds with ctypes; no dependency on the
+// PyTorch headers, so the whole library rebuilds in seconds.
+#include "common.cuh"
+#include "tmap.cuh"
+#include "gemm_tn.cuh"
+#include "gemm_nt.cuh"
+#include "norm.cuh"
+#include "pnm_api.h"
+
+__device__ int pnm_error_word = 0;
+
+namespace {
+int g_num_sms = 0;
+int* g_err_ptr = nullptr;
+
+int ensure_init() {
+  if (g_num_sms > 0 && g_err_ptr) return 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  if (cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&g_err_ptr), pnm_error_word) != cudaSuccess) return -1;
+  return 0;
+}
+}  // namespace
+
+extern "C" {
+
+int pnm_version() { return 100; }
+
+int pnm_num_sms() { return ensure_init() ? -1 : g_num_sms; }
+
+int pnm_get_error() {
+  if (ensure_init()) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, g_err_ptr, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return v;
+}
+
+int pnm_reset_error() {
+  if (ensure_init()) return -1;
+  return cudaMemset(g_err_ptr, 0, sizeof(int)) == cudaSuccess ? 0 : -1;
+}
+
+int pnm_gemm_tn(const void* A, int lda, const void* A2, int lda2, const void* B, int ldb, void* C, int ldc, void* Z,
+                int ldz, const void* AUX, int ldaux, int M, int N, int K, int K1, const float* bias,
+                const float* scale, float* group_out, int act, int aux_mode, int scale_post, int bn, int max_ctas,
+                void* stream) {
+  if (ensure_init()) return -1;
+  if (M <= 0 || N <= 0 || K <= 0) return -2;
+  if ((N % 8) || (K % 8) || (lda % 8) || (ldb % 8) || (ldc % 8)) return -3;
+  if (K1 <= 0 || K1 > K) K1 = K;
+  if (K1 < K && ((K1 % 64) || !A2 || (lda2 % 8))) return -4;
+  if (Z && AUX) return -5;
+  if ((aux_mode != 0) != (AUX != nullptr)) return -6;
+  if (act == pnm::ACT_SOFTMAX64 && (N % 64)) return -7;
+  pnm::GemmCall c;
+  c.A = A; c.lda = lda; c.A2 = A2; c.lda2 = lda2; c.B = B; c.ldb = ldb; c.C = C; c.ldc = ldc;
+  c.Z = Z; c.ldz = ldz; c.AUX = AUX; c.ldaux = ldaux;
+  c.M = M; c.N = N; c.K = K; c.K1 = K1;
+  c.bias = bias; c.scale = scale; c.group_out = group_out;
+  c.act = act; c.aux_mode = aux_mode; c.scale_post = scale_post; c.max_ctas = max_ctas;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (AUX) return pnm::launch_gemm_tn<128, pnm::MODE_AUX>(c, g_num_sms, g_err_ptr, st);
+  if (Z) return pnm::launch_gemm_tn<128, pnm::MODE_Z>(c, g_num_sms, g_err_ptr, st);
+  if (bn == 0) bn = (N > 128) ? 256 : 128;
+  if (bn == 256) return pnm::launch_gemm_tn<256, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+  return pnm::launch_gemm_tn<128, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+}
+
+int pnm_gemm_nt(const void* A, int lda, const void* B, int ldb, float* out, int ldo, float* colsum, int M, int Na,
+                int Nb, int max_ctas, void* stream) {
+  if (ensure_init()) return -1;
+  if (M <= 0 || Na <= 0 || Nb <= 0) return -2;
+  if ((Na % 8) || (Nb % 8) || (lda % 8) || (ldb % 8)) return -3;
+  pnm::NtCall c;
+  c.A = A; c.lda = lda; c.B = B; c.ldb = ldb; c.out = out; c.ldo = ldo; c.colsum = colsum;
+  c.M = M; c.Na = Na; c.Nb = Nb; c.max_ctas = max_ctas;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (Nb > 128) return pnm::launch_gemm_nt<256>(c, g_num_sms, g_err_ptr, st);
+  return pnm::launch_gemm_nt<128>(c, g_num_sms, g_err_ptr, st);
+}
+
+int pnm_layernorm_fwd(const void* x, const void* r, const float* gamma, const float* beta, void* y, void* sum_out,
+                      float* mean, float* rstd, long long M, int C, float eps, void* stream) {
+  if (ensure_init()) return -1;
+  return pnm::launch_layernorm_fwd(x, r, gamma, beta, y, sum_out, mean, rstd, M, C, eps, g_num_sms,
+                                   reinterpret_cast<cudaStream_t>(stream));
+}
+
+long long pnm_layernorm_bwd_scratch_floats(long long M, int C) {
+  if (ensure_init()) return -1;
+  return (long long)pnm::layernorm_bwd_grid(M, g_num_sms) * 2 * C;
+}
+
+int pnm_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
+                      const void* dres, void* dx, float* dgamma, float* dbeta, float* scratch, long long M, int C,
+                      void* stream) {
+  if (ensure_init()) return -1;
+  return pnm::launch_layernorm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, scratch, M, C, g_num_sms,
+                                   reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,351 @@
+"""tcgen05 GEMM primitives and the autograd functions built on them.
+
+``gemm_tn``  : ``C = epilogue(A @ B.T)``  — forward / data-gradient GEMMs (``csrc/gemm_tn.cuh``)
+``gemm_nt``  : ``out += A.T @ B``         — weight gradients and token reductions (``csrc/gemm_nt.cuh``)
+``mlp_chain``: ``Linear → act → … → Linear (+ residual)`` as one autograd node whose
+backward fuses ``act'(z)`` into the data-gradient GEMM epilogue and obtains the bias
+gradient from the same pass as the weight gradient.
+
+These replace cuBLAS ``F.linear`` + separate activation kernels of the reference
+(``physicsnemo/nn/module/mlp_layers.py:171-173``, ``mesh_graph_mlp.py:120-206``).
+Every function has a plain PyTorch path (CPU, fp32, or when the library is not loaded)
+that doubles as the numerical oracle in the tests.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+ACT_NONE, ACT_GELU, ACT_SILU, ACT_RELU, ACT_SOFTMAX64 = 0, 1, 2, 3, 4
+AUX_NONE, AUX_ADD, AUX_DGELU, AUX_DSOFTMAX, AUX_DSILU, AUX_DRELU = 0, 1, 2, 3, 4, 5
+_DACT = {ACT_GELU: AUX_DGELU, ACT_SILU: AUX_DSILU, ACT_RELU: AUX_DRELU}
+
+launch_count = 0  # number of library kernels launched by this process (bench bookkeeping)
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str):
+    if code != 0:
+        raise RuntimeError(f"{what} failed with code {code}")
+
+
+def _rowmajor2d(t: torch.Tensor) -> torch.Tensor:
+    """2-D view whose last dim is contiguous and whose row stride is a multiple of 8."""
+    assert t.dim() == 2
+    if t.stride(1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t
+
+
+def gemm_tn(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    bias: Optional[torch.Tensor] = None,
+    scale: Optional[torch.Tensor] = None,
+    act: int = ACT_NONE,
+    aux: Optional[torch.Tensor] = None,
+    aux_mode: int = AUX_NONE,
+    a2: Optional[torch.Tensor] = None,
+    z_out: bool = False,
+    out: Optional[torch.Tensor] = None,
+    group_out: Optional[torch.Tensor] = None,
+    scale_post: bool = False,
+    bn: int = 0,
+    max_ctas: int = 0,
+):
+    """``epilogue([a | a2] @ b.T)`` on tcgen05; bf16 operands, fp32 accumulation, bf16 result.
+
+    a: [M, K1], a2: [M, K - K1] (optional), b: [N, K]; bias / scale: fp32 [N];
+    aux: bf16 [M, N] consumed according to ``aux_mode``; ``z_out`` also returns the
+    pre-activation.  Returns ``out`` or ``(out, z)``.
+    """
+    global launch_count
+    lib = _lib.load(required=True)
+    a = _rowmajor2d(a)
+    b = _rowmajor2d(b)
+    M, K1 = a.shape
+    N, K = b.shape
+    if a2 is not None:
+        a2 = _rowmajor2d(a2)
+        assert a2.shape[0] == M and K1 + a2.shape[1] == K
+    else:
+        assert K1 == K, f"A has K={K1} but B has K={K}"
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    z = torch.empty((M, N), dtype=torch.bfloat16, device=a.device) if z_out else None
+    if aux is not None:
+        aux = _rowmajor2d(aux)
+        assert aux.shape == (M, N) and aux.dtype == torch.bfloat16
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous()
+    if scale is not None:
+        assert scale.dtype == torch.float32 and scale.numel() == N and scale.is_contiguous()
+    code = lib.pnm_gemm_tn(
+        _ptr(a), a.stride(0), _ptr(a2), 0 if a2 is None else a2.stride(0), _ptr(b), b.stride(0),
+        _ptr(out), out.stride(0), _ptr(z), 0 if z is None else z.stride(0),
+        _ptr(aux), 0 if aux is None else aux.stride(0),
+        M, N, K, K1, _ptr(bias), _ptr(scale), _ptr(group_out), act, aux_mode, int(scale_post), bn, max_ctas,
+        _stream(),
+    )
+    _check(code, "pnm_gemm_tn")
+    launch_count += 1
+    return (out, z) if z_out else out
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, *, colsum: bool = False, out: Optional[torch.Tensor] = None,
+            colsum_out: Optional[torch.Tensor] = None, max_ctas: int = 0):
+    """``a.T @ b`` in fp32 (a: [M, Na], b: [M, Nb], bf16), optionally the column sums of ``a``.
+
+    ``out`` / ``colsum_out`` accumulate when given (they must hold valid fp32 data).
+    """
+    global launch_count
+    lib = _lib.load(required=True)
+    a = _rowmajor2d(a)
+    b = _rowmajor2d(b)
+    M, Na = a.shape
+    Nb = b.shape[1]
+    assert b.shape[0] == M
+    if out is None:
+        out = torch.zeros((Na, Nb), dtype=torch.float32, device=a.device)
+    cs = None
+    if colsum or colsum_out is not None:
+        cs = colsum_out if colsum_out is not None else torch.zeros((Na,), dtype=torch.float32, device=a.device)
+    code = lib.pnm_gemm_nt(_ptr(a), a.stride(0), _ptr(b), b.stride(0), _ptr(out), out.stride(0), _ptr(cs),
+                           M, Na, Nb, max_ctas, _stream())
+    _check(code, "pnm_gemm_nt")
+    launch_count += 1
+    return (out, cs) if cs is not None else out
+
+
+# ------------------------------------------------------------------ oracles
+def act_torch(x: torch.Tensor, act: int) -> torch.Tensor:
+    if act == ACT_GELU:
+        return F.gelu(x)
+    if act == ACT_SILU:
+        return F.silu(x)
+    if act == ACT_RELU:
+        return F.relu(x)
+    if act == ACT_SOFTMAX64:
+        shp = x.shape
+        return torch.softmax(x.reshape(*shp[:-1], shp[-1] // 64, 64), dim=-1).reshape(shp)
+    return x
+
+
+def gemm_tn_reference(a, b, *, bias=None, scale=None, act=ACT_NONE, aux=None, aux_mode=AUX_NONE, a2=None,
+                      scale_post=False):
+    """fp32 PyTorch statement of what ``gemm_tn`` computes (used by the tests)."""
+    af = a.float() if a2 is None else torch.cat([a.float(), a2.float()], dim=1)
+    x = af @ b.float().t()
+    if bias is not None:
+        x = x + bias
+    if scale is not None and not scale_post:
+        x = x * scale
+    z = x
+    y = act_torch(x, act)
+    if aux_mode == AUX_ADD:
+        y = y + aux.float()
+    elif aux_mode in (AUX_DGELU, AUX_DSILU, AUX_DRELU):
+        t = aux.float().detach().requires_grad_(True)
+        with torch.enable_grad():
+            f = act_torch(t, {AUX_DGELU: ACT_GELU, AUX_DSILU: ACT_SILU, AUX_DRELU: ACT_RELU}[aux_mode])
+            (g,) = torch.autograd.grad(f.sum(), t)
+        y = y * g
+    elif aux_mode == AUX_DSOFTMAX:
+        p = aux.float()
+        shp = y.shape
+        y4, p4 = y.reshape(shp[0], -1, 64), p.reshape(shp[0], -1, 64)
+        y = (p4 * (y4 - (y4 * p4).sum(-1, keepdim=True))).reshape(shp)
+    if scale is not None and scale_post:
+        y = y * scale
+    return y, z
+
+
+# ----------------------------------------------------------------- dispatch
+def fused_path_enabled(x: torch.Tensor) -> bool:
+    """True when ``x`` should take the sm_100a kernels (CUDA + bf16 compute)."""
+    if not isinstance(x, torch.Tensor) or not x.is_cuda:
+        return False
+    if type(x) is not torch.Tensor and type(x).__name__ != "Parameter":
+        return False  # tensor subclasses (ShardTensor) dispatch through their own handlers
+    if torch.is_autocast_enabled("cuda"):
+        dt = torch.get_autocast_dtype("cuda")
+    else:
+        dt = x.dtype
+    if dt != torch.bfloat16:
+        return False
+    _lib.load(required=True)  # a CUDA box without the library is an error, not a fallback
+    return True
+
+
+_wcache: dict = {}
+
+
+def _bf16_weight(w: torch.Tensor, transpose: bool = False) -> torch.Tensor:
+    """bf16 (optionally transposed) copy of a parameter, cached until the parameter changes."""
+    if w.dtype == torch.bfloat16 and not transpose:
+        return w.detach()
+    key = (id(w), transpose)
+    ver = (w._version, w.data_ptr(), tuple(w.shape))
+    hit = _wcache.get(key)
+    if hit is not None and hit[0] == ver:
+        return hit[1]
+    src = w.detach()
+    val = (src.t() if transpose else src).to(torch.bfloat16).contiguous()
+    if len(_wcache) > 4096:
+        _wcache.clear()
+    _wcache[key] = (ver, val)
+    return val
+
+
+def _pad_cols(t: torch.Tensor, mult: int = 8) -> torch.Tensor:
+    k = t.shape[-1]
+    pad = (-k) % mult
+    return F.pad(t, (0, pad)) if pad else t
+
+
+class _MlpChainFn(torch.autograd.Function):
+    """``h_i = act_i(h_{i-1} W_i^T + b_i)``, last layer optionally ``+ residual``."""
+
+    @staticmethod
+    def forward(ctx, x2d, residual, acts, n_layers, need_z, *params):
+        weights = params[:n_layers]
+        biases = params[n_layers:]
+        acts = list(acts)
+        h = x2d
+        hs, zs = [x2d], []
+        for i in range(n_layers):
+            w = _bf16_weight(weights[i])
+            if w.shape[1] != h.shape[1]:  # K padded to a multiple of 8
+                w = _pad_cols(w)
+            n_true = w.shape[0]
+            if n_true % 8:
+                w = F.pad(w, (0, 0, 0, (-n_true) % 8))
+            b = biases[i]
+            if b is not None:
+                b = b.detach().float().contiguous()
+                if b.numel() != w.shape[0]:
+                    b = F.pad(b, (0, w.shape[0] - b.numel()))
+            last = i == n_layers - 1
+            use_res = last and residual is not None
+            if acts[i] != ACT_NONE and need_z:
+                h, z = gemm_tn(h, w, bias=b, act=acts[i], z_out=True)
+                zs.append(z)
+            else:
+                h = gemm_tn(h, w, bias=b, act=acts[i], aux=residual if use_res else None,
+                            aux_mode=AUX_ADD if use_res else AUX_NONE)
+                zs.append(None)
+            if last and acts[i] != ACT_NONE and use_res:
+                h = h + residual
+            if n_true != h.shape[1]:
+                h = h[:, :n_true]
+            hs.append(h)
+        ctx.acts, ctx.n_layers = acts, n_layers
+        ctx.has_res = residual is not None
+        ctx.save_for_backward(*hs[:-1], *[z for z in zs if z is not None], *weights)
+        ctx.z_mask = [z is not None for z in zs]
+        ctx.bias_mask = [b is not None for b in biases]
+        return hs[-1]
+
+    @staticmethod
+    def backward(ctx, dy):
+        n = ctx.n_layers
+        saved = ctx.saved_tensors
+        hs = list(saved[:n])
+        nz = sum(ctx.z_mask)
+        zlist = list(saved[n:n + nz])
+        weights = saved[n + nz:]
+        zs, zi = [], 0
+        for m in ctx.z_mask:
+            zs.append(zlist[zi] if m else None)
+            zi += int(m)
+        acts = ctx.acts
+        dres = dy if ctx.has_res else None
+        g = dy.contiguous()
+        if acts[n - 1] != ACT_NONE:
+            # activation on the output layer: no upstream GEMM to fuse into
+            z = zs[n - 1].float().requires_grad_(True)
+            with torch.enable_grad():
+                f = act_torch(z, acts[n - 1])
+            g = torch.autograd.grad(f, z, g.float())[0].to(torch.bfloat16)
+        dws, dbs = [None] * n, [None] * n
+        dx = None
+        for i in range(n - 1, -1, -1):
+            w = weights[i]
+            n_true, k_true = w.shape
+            gi = g
+            if gi.shape[1] % 8:
+                gi = _pad_cols(gi)
+            hin = hs[i]
+            need_b = ctx.bias_mask[i] and ctx.needs_input_grad[5 + n + i]
+            if ctx.needs_input_grad[5 + i] or need_b:
+                res = gemm_nt(gi, hin, colsum=need_b)
+                dw, db = (res if need_b else (res, None))
+                dws[i] = dw[:n_true, :k_true].to(w.dtype) if (dw.shape != w.shape or w.dtype != dw.dtype) else dw
+                if db is not None:
+                    dbs[i] = db[:n_true]
+            if i > 0 or ctx.needs_input_grad[0]:
+                wt = _bf16_weight(w, transpose=True)  # [K, N]
+                if wt.shape[1] % 8:
+                    wt = _pad_cols(wt)
+                if wt.shape[0] % 8:
+                    wt = F.pad(wt, (0, 0, 0, (-wt.shape[0]) % 8))
+                if i > 0 and zs[i - 1] is not None:
+                    g = gemm_tn(gi, wt, aux=zs[i - 1] if zs[i - 1].shape[1] == wt.shape[0] else _pad_cols(zs[i - 1]),
+                                aux_mode=_DACT[acts[i - 1]])
+                else:
+                    g = gemm_tn(gi, wt)
+                if g.shape[1] != hin.shape[1]:
+                    g = g[:, :hin.shape[1]]
+                if i == 0:
+                    dx = g
+        return (dx, dres, None, None, None, *dws, *dbs)
+
+
+def mlp_chain(x: torch.Tensor, weights: Sequence[torch.Tensor], biases: Sequence[Optional[torch.Tensor]],
+              acts: Sequence[int], residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Apply ``len(weights)`` linear layers with activations ``acts`` (codes) between them.
+
+    ``x``: [..., K]; returns [..., N_last] (+ ``residual`` when given).  CUDA bf16 inputs run on
+    the tcgen05 kernels, anything else through PyTorch.
+    """
+    if not fused_path_enabled(x):
+        h = x
+        for w, b, a in zip(weights, biases, acts):
+            h = act_torch(F.linear(h, w, b), a)
+        return h if residual is None else h + residual
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    if x2.dtype != torch.bfloat16:
+        x2 = x2.to(torch.bfloat16)
+    if x2.shape[1] % 8:
+        x2 = _pad_cols(x2)
+    r2 = None
+    if residual is not None:
+        r2 = residual.reshape(-1, residual.shape[-1])
+        if r2.dtype != torch.bfloat16:
+            r2 = r2.to(torch.bfloat16)
+    n = len(weights)
+    need_z = torch.is_grad_enabled() and (
+        x.requires_grad or any(w.requires_grad for w in weights) or (residual is not None and residual.requires_grad)
+    )
+    y = _MlpChainFn.apply(x2, r2, tuple(acts), n, need_z, *weights, *biases)
+    return y.reshape(*shp[:-1], y.shape[-1])
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, act: int = ACT_NONE,
+           residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``act(x @ weight.T + bias) (+ residual)`` — single-layer ``mlp_chain``."""
+    return mlp_chain(x, [weight], [bias], [act], residual)

@@ -1,0 +1,67 @@
+"""LayerNorm on the sm_100a kernels (``csrc/norm.cuh``) with a PyTorch oracle path.
+
+Replaces ``torch.nn.LayerNorm`` / ``te.LayerNorm`` calls of the reference
+(``physicsnemo/nn/module/layer_norm.py``, ``models/transolver/transolver.py:207-209``):
+bf16 activations, fp32 statistics and parameters, optional fused residual add
+(``y = LN(x + r)`` also returning ``x + r``).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from . import gemm as _g
+
+
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x2d, gamma, beta, eps):
+        lib = _lib.load(required=True)
+        M, C = x2d.shape
+        y = torch.empty_like(x2d)
+        mean = torch.empty((M,), dtype=torch.float32, device=x2d.device)
+        rstd = torch.empty((M,), dtype=torch.float32, device=x2d.device)
+        g32 = gamma.detach().float().contiguous()
+        b32 = beta.detach().float().contiguous() if beta is not None else None
+        code = lib.pnm_layernorm_fwd(x2d.data_ptr(), None, g32.data_ptr(), None if b32 is None else b32.data_ptr(),
+                                     y.data_ptr(), None, mean.data_ptr(), rstd.data_ptr(), M, C, float(eps),
+                                     _g._stream())
+        _g._check(code, "pnm_layernorm_fwd")
+        _g.launch_count += 1
+        ctx.save_for_backward(x2d, g32, mean, rstd)
+        ctx.has_beta = beta is not None
+        ctx.param_dtype = gamma.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib.load(required=True)
+        x2d, g32, mean, rstd = ctx.saved_tensors
+        M, C = x2d.shape
+        dy = dy.contiguous()
+        dx = torch.empty_like(x2d)
+        dgamma = torch.empty((C,), dtype=torch.float32, device=x2d.device)
+        dbeta = torch.empty((C,), dtype=torch.float32, device=x2d.device)
+        nfl = lib.pnm_layernorm_bwd_scratch_floats(M, C)
+        scratch = torch.empty((nfl,), dtype=torch.float32, device=x2d.device)
+        code = lib.pnm_layernorm_bwd(dy.data_ptr(), x2d.data_ptr(), g32.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                                     None, dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), scratch.data_ptr(),
+                                     M, C, _g._stream())
+        _g._check(code, "pnm_layernorm_bwd")
+        _g.launch_count += 2
+        return dx, dgamma.to(ctx.param_dtype), (dbeta.to(ctx.param_dtype) if ctx.has_beta else None), None
+
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float = 1e-5) -> torch.Tensor:
+    """LayerNorm over the last dimension."""
+    C = x.shape[-1]
+    if not _g.fused_path_enabled(x) or C % 8 or C > 1024:
+        return F.layer_norm(x, (C,), weight, bias, eps)
+    x2 = x.reshape(-1, C)
+    if x2.dtype != torch.bfloat16:
+        x2 = x2.to(torch.bfloat16)
+    x2 = x2.contiguous()
+    return _LayerNormFn.apply(x2, weight, bias, eps).reshape(x.shape)

@@ -1,0 +1,127 @@
+"""Numerics of the tcgen05 GEMM family against fp32 PyTorch statements of the same ops."""
+import pytest
+import torch
+
+from physicsnemo_b200 import ops
+from physicsnemo_b200.ops import gemm as G
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _close(out, ref, tol=2e-2):
+    out, ref = out.float(), ref.float()
+    err = (out - ref).abs().max().item()
+    denom = ref.abs().max().item() + 1e-6
+    assert err <= tol * max(1.0, denom), f"max abs err {err} (ref max {denom})"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (300, 256, 256), (1000, 64, 128), (257, 264, 72), (20000, 512, 256)])
+@pytest.mark.parametrize("bn", [0, 128])
+def test_gemm_tn_plain(M, N, K, bn):
+    a, b = _rand(M, K), _rand(N, K, scale=0.1)
+    bias = torch.randn(N, device="cuda")
+    out = ops.gemm_tn(a, b, bias=bias, bn=bn)
+    ref, _ = ops.gemm_tn_reference(a, b, bias=bias)
+    _close(out, ref)
+    assert ops.device_error() == 0
+
+
+@pytest.mark.parametrize("act", [G.ACT_GELU, G.ACT_SILU, G.ACT_RELU, G.ACT_SOFTMAX64])
+def test_gemm_tn_activation_and_z(act):
+    M, N, K = 777, 256, 128
+    a, b = _rand(M, K), _rand(N, K, scale=0.2)
+    bias = torch.randn(N, device="cuda")
+    scale = torch.rand(N, device="cuda") + 0.5
+    out, z = ops.gemm_tn(a, b, bias=bias, scale=scale, act=act, z_out=True)
+    ref, zref = ops.gemm_tn_reference(a, b, bias=bias, scale=scale, act=act)
+    _close(z, zref)
+    _close(out, ref)
+    out2 = ops.gemm_tn(a, b, bias=bias, scale=scale, act=act)
+    _close(out2, ref)
+
+
+@pytest.mark.parametrize("aux_mode", [G.AUX_ADD, G.AUX_DGELU, G.AUX_DSILU, G.AUX_DRELU, G.AUX_DSOFTMAX])
+def test_gemm_tn_aux(aux_mode):
+    M, N, K = 1500, 384, 192
+    a, b = _rand(M, K), _rand(N, K, scale=0.2)
+    if aux_mode == G.AUX_DSOFTMAX:
+        aux = torch.softmax(torch.randn(M, N // 64, 64, device="cuda"), -1).reshape(M, N).to(torch.bfloat16)
+    else:
+        aux = _rand(M, N)
+    scale = torch.rand(N, device="cuda") + 0.5
+    grp = torch.zeros(N // 64, device="cuda") if aux_mode == G.AUX_DSOFTMAX else None
+    out = ops.gemm_tn(a, b, aux=aux, aux_mode=aux_mode, scale=scale, scale_post=True, group_out=grp)
+    ref, _ = ops.gemm_tn_reference(a, b, aux=aux, aux_mode=aux_mode, scale=scale, scale_post=True)
+    _close(out, ref, tol=3e-2)
+    if grp is not None:
+        y = (a.float() @ b.float().t()).reshape(M, -1, 64)
+        p = aux.float().reshape(M, -1, 64)
+        ds = p * (y - (y * p).sum(-1, keepdim=True))
+        gref = (ds * torch.log(p.clamp_min(1e-30)) * (p > 0)).sum((0, 2))
+        _close(grp, gref, tol=5e-2)
+    assert ops.device_error() == 0
+
+
+def test_gemm_tn_k_concat():
+    M, N, K1, K2 = 900, 256, 128, 192
+    a, a2, b = _rand(M, K1), _rand(M, K2), _rand(N, K1 + K2, scale=0.1)
+    out = ops.gemm_tn(a, b, a2=a2)
+    ref, _ = ops.gemm_tn_reference(a, b, a2=a2)
+    _close(out, ref)
+
+
+@pytest.mark.parametrize("M,Na,Nb", [(64, 128, 128), (5000, 256, 256), (4097, 512, 256), (1000, 64, 32), (30000, 1024, 256)])
+def test_gemm_nt(M, Na, Nb):
+    a, b = _rand(M, Na, scale=0.3), _rand(M, Nb, scale=0.3)
+    out, cs = ops.gemm_nt(a, b, colsum=True)
+    ref = a.float().t() @ b.float()
+    _close(out, ref, tol=1e-2)
+    _close(cs, a.float().sum(0), tol=1e-2)
+    assert ops.device_error() == 0
+
+
+@pytest.mark.parametrize("C", [128, 256, 768])
+def test_layernorm(C):
+    M = 3001
+    x = _rand(M, C).requires_grad_(True)
+    w = (torch.rand(C, device="cuda") + 0.5).requires_grad_(True)
+    b = torch.randn(C, device="cuda").requires_grad_(True)
+    y = ops.layer_norm(x, w, b)
+    dy = _rand(M, C)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_(True)
+    wr, br = w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    yr = torch.nn.functional.layer_norm(xr, (C,), wr, br)
+    yr.backward(dy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad, tol=3e-2)
+    _close(w.grad, wr.grad, tol=2e-2)
+    _close(b.grad, br.grad, tol=2e-2)
+
+
+def test_mlp_chain_matches_torch():
+    M = 2050
+    x = _rand(M, 6).requires_grad_(True)
+    res = _rand(M, 256).requires_grad_(True)
+    ws = [torch.randn(512, 6, device="cuda") * 0.3, torch.randn(256, 512, device="cuda") * 0.05]
+    bs = [torch.randn(512, device="cuda") * 0.1, torch.randn(256, device="cuda") * 0.1]
+    for t in ws + bs:
+        t.requires_grad_(True)
+    y = ops.mlp_chain(x, ws, bs, [G.ACT_GELU, G.ACT_NONE], residual=res)
+    dy = _rand(M, 256)
+    y.backward(dy)
+    got = [x.grad, res.grad] + [t.grad for t in ws + bs]
+    xr = x.detach().float().requires_grad_(True)
+    rr = res.detach().float().requires_grad_(True)
+    wr = [t.detach().clone().requires_grad_(True) for t in ws]
+    br = [t.detach().clone().requires_grad_(True) for t in bs]
+    h = torch.nn.functional.gelu(xr @ wr[0].t() + br[0]) @ wr[1].t() + br[1] + rr
+    h.backward(dy.float())
+    _close(y, h, tol=3e-2)
+    for g, r in zip(got, [xr.grad, rr.grad] + [t.grad for t in wr + br]):
+        _close(g, r, tol=4e-2)
+    assert ops.device_error() == 0
