@@ -1,0 +1,111 @@
+"""Embedding layers for diffusion / transformer models.
+
+Parity: ``physicsnemo/nn/module/embedding_layers.py`` — ``FourierEmbedding`` (``:29``),
+``PositionalEmbedding`` (``:67-152``: ``freqs`` buffer, ``cos_sin`` / ``np_sin_cos``
+ordering, optional learnable MLP), ``SinusoidalTimestepEmbedding``, ``OneHotEmbedding``.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+
+class FourierEmbedding(nn.Module):
+    """Random Fourier features of a scalar (noise level) input."""
+
+    def __init__(self, num_channels: int, scale: int = 16, amp_mode: bool = False):
+        super().__init__()
+        self.register_buffer("freqs", torch.randn(num_channels // 2) * scale)
+        self.amp_mode = amp_mode
+
+    def forward(self, x):
+        freqs = self.freqs
+        if not self.amp_mode and x.dtype != freqs.dtype:
+            freqs = freqs.to(x.dtype)
+        x = x.ger(2 * np.pi * freqs)
+        return torch.cat([x.cos(), x.sin()], dim=1)
+
+
+class PositionalEmbedding(nn.Module):
+    """Sinusoidal embedding ``[cos(x f), sin(x f)]`` with ``f_i = max_positions^(-i/(C/2))``."""
+
+    def __init__(self, num_channels: int, max_positions: int = 10000, endpoint: bool = False,
+                 amp_mode: bool = False, learnable: bool = False, freq_embed_dim: int | None = None,
+                 mlp_hidden_dim: int | None = None, embed_fn: str = "cos_sin"):
+        super().__init__()
+        self.num_channels = num_channels
+        self.max_positions = max_positions
+        self.endpoint = endpoint
+        self.amp_mode = amp_mode
+        self.learnable = learnable
+        self.embed_fn = embed_fn
+        if embed_fn not in ("cos_sin", "np_sin_cos"):
+            raise ValueError(f"embed_fn must be 'cos_sin' or 'np_sin_cos', got {embed_fn}")
+        if learnable:
+            self.freq_embed_dim = freq_embed_dim or num_channels
+            self.mlp_hidden_dim = mlp_hidden_dim or 2 * num_channels
+            self.mlp = nn.Sequential(
+                nn.Linear(self.freq_embed_dim, self.mlp_hidden_dim, bias=True), nn.SiLU(),
+                nn.Linear(self.mlp_hidden_dim, num_channels, bias=True),
+            )
+            n = self.freq_embed_dim // 2
+        else:
+            n = num_channels // 2
+        freqs = torch.arange(start=0, end=n, dtype=torch.float32)
+        freqs = freqs / (n - (1 if endpoint else 0))
+        freqs = (1 / max_positions) ** freqs
+        self.register_buffer("freqs", freqs, persistent=True)
+        self._register_load_state_dict_pre_hook(self._fill_missing_freqs, with_module=False)
+
+    def _fill_missing_freqs(self, state_dict, prefix, *args):
+        # checkpoints written before ``freqs`` became a persistent buffer lack the key
+        key = prefix + "freqs"
+        if key not in state_dict:
+            state_dict[key] = self.freqs.detach().clone()
+
+    def forward(self, x):
+        freqs = self.freqs
+        if not self.amp_mode and x.dtype != freqs.dtype:
+            freqs = freqs.to(x.dtype)
+        x = x.ger(freqs)
+        if self.embed_fn == "cos_sin":
+            x = torch.cat([x.cos(), x.sin()], dim=1)
+        else:
+            x = torch.cat([x.sin(), x.cos()], dim=1)
+        if self.learnable:
+            x = self.mlp(x)
+        return x
+
+
+class SinusoidalTimestepEmbedding(nn.Module):
+    """Transformer-style timestep embedding (sin half then cos half)."""
+
+    def __init__(self, num_channels: int, max_period: int = 10000):
+        super().__init__()
+        self.num_channels, self.max_period = num_channels, max_period
+
+    def forward(self, t):
+        half = self.num_channels // 2
+        freqs = torch.exp(-math.log(self.max_period) * torch.arange(half, device=t.device, dtype=torch.float32) / half)
+        args = t.float()[:, None] * freqs[None]
+        emb = torch.cat([torch.sin(args), torch.cos(args)], dim=-1)
+        if self.num_channels % 2:
+            emb = torch.cat([emb, torch.zeros_like(emb[:, :1])], dim=-1)
+        return emb
+
+
+class OneHotEmbedding(nn.Module):
+    """Soft one-hot embedding of ``t`` in [0, 1] over ``num_channels`` bins."""
+
+    def __init__(self, num_channels: int):
+        super().__init__()
+        self.num_channels = num_channels
+        ind = torch.arange(num_channels).view(1, -1)
+        self.register_buffer("indices", ind)
+
+    def forward(self, t):
+        ind = t * (self.num_channels - 1)
+        return torch.clamp(1 - torch.abs(ind - self.indices), min=0)
