@@ -192,7 +192,7 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
 }
 
 // dgamma[c] = sum_b scratch[b][0][c], dbeta[c] = sum_b scratch[b][1][c]
-__global__ void layernorm_bwd_finalize_kernel(const float* __restrict__ scratch, int nblocks, int C,
+static __global__ void layernorm_bwd_finalize_kernel(const float* __restrict__ scratch, int nblocks, int C,
                                               float* __restrict__ dgamma, float* __restrict__ dbeta) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= 2 * C) return;

@@ -53,7 +53,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         return _LIB_PATH
     _LIB_DIR.mkdir(parents=True, exist_ok=True)
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc, *NVCC_FLAGS, "-o", str(_LIB_PATH), str(_SRC_DIR / "pnm_lib.cu")]
+    cmd = [nvcc, *NVCC_FLAGS, "-o", str(_LIB_PATH), *[str(p) for p in sorted(_SRC_DIR.glob("*.cu"))]]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
