@@ -1,0 +1,96 @@
+"""Kernel micro-benchmarks: CUDA-event timing and roofline fractions of the library kernels.
+
+``python -m physicsnemo_b200.ops.microbench <kernel> [--m ROWS] [--iters N]`` with ``<kernel>``
+one of ``gemm_tn``, ``gemm_tn_gelu_z``, ``gemm_tn_softmax``, ``gemm_tn_aux``, ``gemm_nt``,
+``layernorm``, ``all``.  Inputs are larger than the 126 MB L2 at the default size; the small
+sizes (``--m 262144``) are meant for profiler captures.  Denominators come from
+``MEASURED_PEAKS.json`` at the repository root when present (measured copy bandwidth and
+cuBLAS bf16 throughput), else from the fallback 6.65 TB/s / 1.59 PFLOP/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import gemm as G
+from .norm import layer_norm
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def _time(fn, iters, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        flush.add_(1.0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+def _r(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def cases(M):
+    bias256, bias512, bias1024 = (torch.randn(n, device="cuda") for n in (256, 512, 1024))
+    a256, a1024 = _r(M, 256), _r(M, 1024, scale=0.3)
+    w256, w512, w1024, wk1024 = _r(256, 256, scale=0.05), _r(512, 256, scale=0.05), _r(1024, 256, scale=0.05), _r(256, 1024, scale=0.03)
+    aux = _r(M, 256)
+    p512 = _r(M, 512, scale=0.1)
+    out = {}
+    out["gemm_tn"] = (lambda: G.gemm_tn(a256, w256, bias=bias256), 2.0 * M * 256 * 256, M * 256 * 2 * 2)
+    out["gemm_tn_k1024"] = (lambda: G.gemm_tn(a1024, wk1024, bias=bias256), 2.0 * M * 256 * 1024, M * (1024 + 256) * 2)
+    out["gemm_tn_gelu_z"] = (lambda: G.gemm_tn(a256, w1024, bias=bias1024, act=G.ACT_GELU, z_out=True),
+                             2.0 * M * 1024 * 256, M * (256 + 2 * 1024) * 2)
+    out["gemm_tn_softmax"] = (lambda: G.gemm_tn(a256, w512, bias=bias512, act=G.ACT_SOFTMAX64),
+                              2.0 * M * 512 * 256, M * (256 + 512) * 2)
+    out["gemm_tn_aux"] = (lambda: G.gemm_tn(a256, w256, bias=bias256, aux=aux, aux_mode=G.AUX_ADD),
+                          2.0 * M * 256 * 256, M * 256 * 2 * 3)
+    out["gemm_nt"] = (lambda: G.gemm_nt(p512, a256, colsum=True), 2.0 * M * 512 * 256, M * (512 + 256) * 2)
+    g, b = torch.ones(256, device="cuda"), torch.zeros(256, device="cuda")
+    out["layernorm"] = (lambda: layer_norm(a256, g, b), 0.0, M * 256 * 2 * 2)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel")
+    ap.add_argument("--m", type=int, default=1_000_000)
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    hbm, tflops, src = _peaks()
+    flush = torch.empty(256 * 1024 * 1024 // 4, device="cuda")
+    table = cases(args.m)
+    names = list(table) if args.kernel == "all" else [args.kernel]
+    for name in names:
+        fn, flops, nbytes = table[name]
+        ms = _time(fn, args.iters, flush)
+        t_roof = max(flops / (tflops * 1e12), nbytes / (hbm * 1e9)) * 1e3
+        print(json.dumps({"kernel": name, "M": args.m, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+                          "gbs": round(nbytes / ms / 1e6, 1), "roofline_ms": round(t_roof, 4),
+                          "frac_of_roofline": round(t_roof / ms, 3), "peaks": src}))
+    from . import device_error
+
+    assert device_error() == 0
+
+
+if __name__ == "__main__":
+    main()
