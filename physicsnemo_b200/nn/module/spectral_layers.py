@@ -1,0 +1,210 @@
+"""Spectral (Fourier) convolutions for FNO, 1-D to 4-D.
+
+Parity: ``physicsnemo/nn/module/spectral_layers.py`` — ``SpectralConv1d/2d/3d/4d``
+(``:27/106/203/349``): real FFT over the trailing spatial dims, multiplication of the retained
+low-frequency corners by complex weights ``weights{k}`` stored as real tensors
+``[in, out, m1, …, 2]``, zero elsewhere, inverse FFT.  Corner order of the weights follows
+the reference so state dicts interchange.  Helpers for PINO derivatives (``:640-863``).
+
+One generic implementation serves all ranks: the corner products are written straight into
+a zero spectrum (one allocation) instead of padding each product to full size and summing.
+"""
+from __future__ import annotations
+
+import itertools
+from typing import List
+
+import torch
+import torch.nn as nn
+from torch import Tensor
+
+# sign pattern (True = high-frequency / negative side) of each weight over the leading dims
+_CORNERS = {
+    1: [()],
+    2: [(False,), (True,)],
+    3: [(False, False), (True, False), (False, True), (True, True)],
+    4: [(False, False, False), (True, False, False), (False, True, False), (False, False, True),
+        (True, True, False), (True, False, True), (False, True, True), (True, True, True)],
+}
+_LETTERS = "xyzt"
+
+
+class _SpectralConvNd(nn.Module):
+    ndim = 0
+
+    def __init__(self, in_channels: int, out_channels: int, *modes: int):
+        super().__init__()
+        assert len(modes) == self.ndim
+        self.in_channels, self.out_channels = in_channels, out_channels
+        for i, m in enumerate(modes):
+            setattr(self, f"modes{i + 1}", m)
+        self.modes = tuple(modes)
+        self.scale = 1 / (in_channels * out_channels)
+        for k in range(len(_CORNERS[self.ndim])):
+            self.register_parameter(f"weights{k + 1}", nn.Parameter(torch.empty(in_channels, out_channels, *modes, 2)))
+        self.reset_parameters()
+        sub = _LETTERS[: self.ndim]
+        self._eq = f"bi{sub},io{sub}->bo{sub}"
+
+    def reset_parameters(self):
+        for k in range(len(_CORNERS[self.ndim])):
+            w = getattr(self, f"weights{k + 1}")
+            w.data = self.scale * torch.rand(w.data.shape)
+
+    def _mul(self, inp: Tensor, weights: Tensor) -> Tensor:
+        return torch.einsum(self._eq, inp, torch.view_as_complex(weights))
+
+    def forward(self, x: Tensor) -> Tensor:
+        nd = self.ndim
+        dims = tuple(range(-nd, 0))
+        spatial = x.shape[-nd:]
+        x_ft = torch.fft.rfftn(x.float() if x.dtype in (torch.bfloat16, torch.float16) else x, dim=dims)
+        out_ft = torch.zeros(x.shape[0], self.out_channels, *x_ft.shape[2:], dtype=x_ft.dtype, device=x.device)
+        last = slice(0, self.modes[-1])
+        parts = []
+        for k, signs in enumerate(_CORNERS[nd]):
+            idx = [slice(None), slice(None)]
+            for d, hi in enumerate(signs):
+                idx.append(slice(-self.modes[d], None) if hi else slice(0, self.modes[d]))
+            idx.append(last)
+            idx = tuple(idx)
+            parts.append((idx, self._mul(x_ft[idx], getattr(self, f"weights{k + 1}"))))
+        # functional scatter keeps autograd simple: out = zeros.index_put for each corner
+        for idx, val in parts:
+            out_ft = _slice_add(out_ft, idx, val)
+        y = torch.fft.irfftn(out_ft, s=spatial, dim=dims)
+        return y.to(x.dtype) if y.dtype != x.dtype and x.dtype in (torch.bfloat16, torch.float16) else y
+
+
+class _SliceAdd(torch.autograd.Function):
+    """``out[idx] += val`` as a differentiable, allocation-free (in-place on a fresh buffer) op."""
+
+    @staticmethod
+    def forward(ctx, out, idx, val):
+        ctx.idx = idx
+        ctx.mark_dirty(out)
+        out[idx] += val
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None, g[ctx.idx]
+
+
+def _slice_add(out, idx, val):
+    return _SliceAdd.apply(out, idx, val)
+
+
+class SpectralConv1d(_SpectralConvNd):
+    ndim = 1
+
+    def __init__(self, in_channels: int, out_channels: int, modes1: int):
+        super().__init__(in_channels, out_channels, modes1)
+
+    def compl_mul1d(self, input, weights):
+        return self._mul(input, weights)
+
+
+class SpectralConv2d(_SpectralConvNd):
+    ndim = 2
+
+    def __init__(self, in_channels: int, out_channels: int, modes1: int, modes2: int):
+        super().__init__(in_channels, out_channels, modes1, modes2)
+
+    def compl_mul2d(self, input, weights):
+        return self._mul(input, weights)
+
+
+class SpectralConv3d(_SpectralConvNd):
+    ndim = 3
+
+    def __init__(self, in_channels: int, out_channels: int, modes1: int, modes2: int, modes3: int):
+        super().__init__(in_channels, out_channels, modes1, modes2, modes3)
+
+    def compl_mul3d(self, input, weights):
+        return self._mul(input, weights)
+
+
+class SpectralConv4d(_SpectralConvNd):
+    ndim = 4
+
+    def __init__(self, in_channels: int, out_channels: int, modes1: int, modes2: int, modes3: int, modes4: int):
+        super().__init__(in_channels, out_channels, modes1, modes2, modes3, modes4)
+
+    def compl_mul4d(self, input, weights):
+        return self._mul(input, weights)
+
+
+# ==========================================================================
+# PINO helpers: exact derivatives of periodic fields through the FFT
+# ==========================================================================
+def fourier_derivatives(x: Tensor, ell: List[float]):
+    """First and second derivatives of ``x`` (B, C, *S) on a periodic box of lengths ``ell``.
+
+    Returns ``(wx, wxx)``: concatenations over the spatial dims (along channels) of
+    ``d/dx_k`` and ``d²/dx_k²``.
+    """
+    nd = x.dim() - 2
+    if len(ell) != nd:
+        raise ValueError("input tensor and domain lengths must have the same dimensionality")
+    dims = list(range(2, 2 + nd))
+    x_h = torch.fft.fftn(x, dim=dims)
+    wx, wxx = [], []
+    for k in range(nd):
+        n = x.shape[2 + k]
+        freq = torch.fft.fftfreq(n, d=1.0 / n).to(x.device) * (2 * torch.pi / ell[k])
+        shape = [1] * x.dim()
+        shape[2 + k] = n
+        kk = freq.reshape(shape)
+        wx.append(torch.fft.ifftn(1j * kk * x_h, dim=dims).real)
+        wxx.append(torch.fft.ifftn(-(kk ** 2) * x_h, dim=dims).real)
+    return torch.cat(wx, dim=1), torch.cat(wxx, dim=1)
+
+
+@torch.jit.ignore
+def calc_latent_derivatives(x: Tensor, domain_length: List[int] = 2):
+    """Fourier derivatives of a latent field after periodic extension by reflection-free padding."""
+    dim = x.dim() - 2
+    if isinstance(domain_length, (int, float)):
+        domain_length = [domain_length] * dim
+    padd = [(i - 1) // 2 for i in list(x.shape[2:])]
+    domain_length = [float(domain_length[i] * (2 * p + x.shape[2 + i]) / x.shape[2 + i]) for i, p in enumerate(padd)]
+    pad = []
+    for p in reversed(padd):
+        pad += [p, p]
+    x_p = torch.nn.functional.pad(x, pad, mode="replicate")
+    dx, ddx = fourier_derivatives(x_p, domain_length)
+    sl = (slice(None), slice(None)) + tuple(slice(p, -p if p > 0 else None) for p in padd)
+    dxs = [t[sl] for t in dx.split(x.shape[1], dim=1)]
+    ddxs = [t[sl] for t in ddx.split(x.shape[1], dim=1)]
+    return dxs, ddxs
+
+
+def first_order_pino_grads(u: Tensor, ux: List[Tensor], weights_1: Tensor, weights_2: Tensor, bias_1: Tensor):
+    """Chain rule through a two-layer point-wise decoder: ``d y / d x_k`` from latent derivatives."""
+    dim = len(ux)
+    dim_str = "xyz"[:dim]
+    # first layer pre-activation and its tanh derivative
+    hidden = torch.einsum(f"mi,bi{dim_str}->bm{dim_str}", weights_1, u) + bias_1.reshape(1, -1, *([1] * dim))
+    dsig = 1 - torch.tanh(hidden) ** 2
+    out = []
+    for k in range(dim):
+        dh = torch.einsum(f"mi,bi{dim_str}->bm{dim_str}", weights_1, ux[k])
+        out.append(torch.einsum(f"om,bm{dim_str}->bo{dim_str}", weights_2, dsig * dh))
+    return out
+
+
+def second_order_pino_grads(u: Tensor, ux: Tensor, uxx: Tensor, weights_1: Tensor, weights_2: Tensor, bias_1: Tensor):
+    """Second derivatives through the same two-layer tanh decoder."""
+    dim = len(ux)
+    dim_str = "xyz"[:dim]
+    hidden = torch.einsum(f"mi,bi{dim_str}->bm{dim_str}", weights_1, u) + bias_1.reshape(1, -1, *([1] * dim))
+    t = torch.tanh(hidden)
+    dsig = 1 - t ** 2
+    ddsig = -2 * t * dsig
+    out = []
+    for k in range(dim):
+        dh = torch.einsum(f"mi,bi{dim_str}->bm{dim_str}", weights_1, ux[k])
+        ddh = torch.einsum(f"mi,bi{dim_str}->bm{dim_str}", weights_1, uxx[k])
+        out.append(torch.einsum(f"om,bm{dim_str}->bo{dim_str}", weights_2, ddsig * dh * dh + dsig * ddh))
+    return out
