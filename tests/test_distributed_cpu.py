@@ -1,0 +1,96 @@
+"""Distributed primitives on CPU (gloo) ranks against single-process oracles."""
+import torch
+import torch.distributed as dist
+
+from tests.dist_utils import run_ranks
+
+
+def _collectives(rank, world):
+    from physicsnemo_b200.distributed import (DistributedManager, all_gather_v, gather_v, indexed_all_to_all_v,
+                                              scatter_v, fused_all_reduce)
+    from physicsnemo_b200.distributed.utils import compute_split_shapes
+
+    m = DistributedManager()
+    assert m.rank == rank and m.world_size == world
+    torch.manual_seed(0)
+    sizes = [3 + r for r in range(world)]
+    full = torch.randn(sum(sizes), 4)
+    chunks = list(full.split(sizes))
+    # all_gather_v fwd + bwd
+    x = chunks[rank].clone().requires_grad_(True)
+    y = all_gather_v(x, sizes)
+    assert torch.allclose(y, full)
+    w = torch.arange(y.numel(), dtype=torch.float32).reshape(y.shape)
+    (y * w).sum().backward()
+    assert torch.allclose(x.grad, world * w.split(sizes)[rank])
+    # gather_v / scatter_v
+    g = gather_v(chunks[rank], sizes, dst=0)
+    if rank == 0:
+        assert torch.allclose(g, full)
+    s = scatter_v(full if rank == 1 % world else torch.empty(0, 4), sizes, src=1 % world)
+    assert torch.allclose(s, chunks[rank])
+    # indexed all-to-all-v: rank i sends rows idx[i][j] to rank j
+    gen = torch.Generator().manual_seed(1)
+    idx_all = [[torch.randint(0, sizes[i], (2 + (i + j) % 3,), generator=gen) for j in range(world)] for i in range(world)]
+    send_sizes = [[len(idx_all[i][j]) for j in range(world)] for i in range(world)]
+    x = chunks[rank].clone().requires_grad_(True)
+    out = indexed_all_to_all_v(x, idx_all[rank], send_sizes)
+    ref = torch.cat([chunks[i][idx_all[i][rank]] for i in range(world)])
+    assert torch.allclose(out, ref)
+    out.sum().backward()
+    gref = torch.zeros_like(chunks[rank])
+    for j in range(world):
+        gref.index_add_(0, idx_all[rank][j], torch.ones(len(idx_all[rank][j]), 4))
+    assert torch.allclose(x.grad, gref)
+    # fused all reduce keeps structure
+    bundle = {"b": torch.ones(3) * (rank + 1), "a": [torch.ones(2, 2), torch.tensor(float(rank))]}
+    red = fused_all_reduce(bundle)
+    tot = sum(range(1, world + 1))
+    assert torch.allclose(red["b"], torch.ones(3) * tot) and torch.allclose(red["a"][0], torch.ones(2, 2) * world)
+    assert compute_split_shapes(10, 4) == [3, 3, 3, 1] and compute_split_shapes(9, 4) == [2, 2, 2, 3]
+
+
+def test_collectives_two_ranks():
+    run_ranks(_collectives, world=2)
+
+
+def test_collectives_three_ranks():
+    run_ranks(_collectives, world=3)
+
+
+def _dist_fft(rank, world):
+    from physicsnemo_b200.distributed import DistributedManager
+    from physicsnemo_b200.distributed.fft import DistributedIRFFT2, DistributedRFFT2
+
+    m = DistributedManager()
+    m.initialize_mesh((world,), ("spatial_parallel",))
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 8, 12, dtype=torch.float64)
+    ref = torch.fft.rfft2(x, dim=(-2, -1), norm="ortho")
+    xl = x.chunk(world, dim=-1)[rank].clone().requires_grad_(True)
+    y = DistributedRFFT2.apply(xl, (None, None), (-2, -1), "ortho")
+    assert torch.allclose(y, ref.chunk(world, dim=-2)[rank], atol=1e-10)
+    back = DistributedIRFFT2.apply(y, (x.shape[-2], x.shape[-1]), (-2, -1), "ortho")
+    assert torch.allclose(back, x.chunk(world, dim=-1)[rank], atol=1e-10)
+    (y.real.sum() + y.imag.sum()).backward()
+    xr = x.clone().requires_grad_(True)
+    yr = torch.fft.rfft2(xr, dim=(-2, -1), norm="ortho")
+    (yr.real.sum() + yr.imag.sum()).backward()
+    assert torch.allclose(xl.grad, xr.grad.chunk(world, dim=-1)[rank], atol=1e-10)
+
+
+def test_distributed_fft_two_ranks():
+    run_ranks(_dist_fft, world=2)
+
+
+def test_process_group_config_tree():
+    from physicsnemo_b200.distributed import ProcessGroupConfig, ProcessGroupNode
+
+    cfg = ProcessGroupConfig(ProcessGroupNode("world"))
+    cfg.add_node(ProcessGroupNode("model_parallel"), parent="world")
+    cfg.add_node(ProcessGroupNode("data_parallel"), parent="world")
+    cfg.add_node(ProcessGroupNode("spatial_parallel"), parent="model_parallel")
+    cfg.add_node(ProcessGroupNode("channel_parallel"), parent="model_parallel")
+    assert sorted(cfg.leaf_groups()) == ["channel_parallel", "data_parallel", "spatial_parallel"]
+    cfg.set_leaf_group_sizes({"spatial_parallel": 2, "channel_parallel": 2, "data_parallel": 4})
+    assert cfg.get_node("model_parallel").size == 4 and cfg.get_node("world").size == 16
