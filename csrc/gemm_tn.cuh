@@ -12,7 +12,7 @@
 //   y = act(x)   act in {none, GELU, SiLU, ReLU, softmax over aligned groups of 64 columns}
 //   y = y + aux | y * GELU'(aux) | y * SiLU'(aux) | y * ReLU'(aux) | softmax-backward(y; aux = p)
 // The auxiliary tile is prefetched by TMA into the same staging buffer the result leaves from.
-// A may be split along K into two tensors (A | A2), which gives K-concatenated GEMMs
+// A may be split along K into up to three tensors (A | A2 | A3), which gives K-concatenated GEMMs
 // without materialising the concatenation.
 #pragma once
 #include "common.cuh"
@@ -25,7 +25,7 @@ enum { AUX_NONE = 0, AUX_ADD = 1, AUX_DGELU = 2, AUX_DSOFTMAX = 3, AUX_DSILU = 4
 enum { MODE_PLAIN = 0, MODE_Z = 1, MODE_AUX = 2 };
 
 struct GemmArgs {
-  int M, N, K, K1;
+  int M, N, K, K1, K2;
   const float* bias;
   const float* scale;
   float* group_out;
@@ -81,7 +81,7 @@ __device__ __forceinline__ void stage_read_row(const uint8_t* buf, int lane, flo
 template <int BN, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
-               const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+               const __grid_constant__ CUtensorMap tmA3, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
                const __grid_constant__ CUtensorMap tmX /* Z (store) or aux (load) */, const GemmArgs g) {
   using Cfg = GemmCfg<BN, MODE>;
   constexpr int STAGES = Cfg::STAGES;
@@ -132,7 +132,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
           const int k = kb * kBK;
           if (k < g.K1) tma_load_2d(sa, &tmA, &full[s], k, mt * kBM);
-          else tma_load_2d(sa, &tmA2, &full[s], k - g.K1, mt * kBM);
+          else if (k < g.K2) tma_load_2d(sa, &tmA2, &full[s], k - g.K1, mt * kBM);
+          else tma_load_2d(sa, &tmA3, &full[s], k - g.K2, mt * kBM);
           tma_load_2d(sb, &tmB, &full[s], k, nt * BN);
         }
       }
@@ -357,11 +358,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 struct GemmCall {
   const void* A; int lda;
   const void* A2; int lda2;
+  const void* A3; int lda3;
   const void* B; int ldb;
   void* C; int ldc;
   void* Z; int ldz;          // optional second output (pre-activation)
   const void* AUX; int ldaux; // optional auxiliary input [M,N]
-  int M, N, K, K1;
+  int M, N, K, K1, K2;
   const float* bias; const float* scale; float* group_out;
   int act, aux_mode, scale_post;
   int max_ctas;  // 0 = number of SMs
@@ -370,18 +372,19 @@ struct GemmCall {
 template <int BN, int MODE>
 inline int launch_gemm_tn(const GemmCall& c, int num_sms, int* err_word, cudaStream_t stream) {
   using Cfg = GemmCfg<BN, MODE>;
-  CUtensorMap tA, tA2, tB, tC, tX;
-  const int K2 = c.K - c.K1;
+  CUtensorMap tA, tA2, tA3, tB, tC, tX;
   if (make_tmap_2d_b16(&tA, c.A, c.M, c.K1, c.lda, kBM, kBK)) return -10;
-  if (K2 > 0) { if (make_tmap_2d_b16(&tA2, c.A2, c.M, K2, c.lda2, kBM, kBK)) return -11; }
+  if (c.K2 > c.K1) { if (make_tmap_2d_b16(&tA2, c.A2, c.M, c.K2 - c.K1, c.lda2, kBM, kBK)) return -11; }
   else tA2 = tA;
+  if (c.K > c.K2) { if (make_tmap_2d_b16(&tA3, c.A3, c.M, c.K - c.K2, c.lda3, kBM, kBK)) return -18; }
+  else tA3 = tA;
   if (make_tmap_2d_b16(&tB, c.B, c.N, c.K, c.ldb, BN, kBK)) return -12;
   if (make_tmap_2d_b16(&tC, c.C, c.M, c.N, c.ldc, 32, 64)) return -13;
   if (MODE == MODE_Z) { if (make_tmap_2d_b16(&tX, c.Z, c.M, c.N, c.ldz, 32, 64)) return -14; }
   else if (MODE == MODE_AUX) { if (make_tmap_2d_b16(&tX, c.AUX, c.M, c.N, c.ldaux, 32, 64)) return -15; }
   else tX = tC;
   GemmArgs g;
-  g.M = c.M; g.N = c.N; g.K = c.K; g.K1 = c.K1;
+  g.M = c.M; g.N = c.N; g.K = c.K; g.K1 = c.K1; g.K2 = c.K2;
   g.bias = c.bias; g.scale = c.scale; g.group_out = c.group_out;
   g.act = c.act; g.aux_mode = c.aux_mode; g.scale_post = c.scale_post;
   g.num_m_tiles = (c.M + kBM - 1) / kBM;
@@ -397,7 +400,7 @@ inline int launch_gemm_tn(const GemmCall& c, int num_sms, int* err_word, cudaStr
   int tiles = g.num_m_tiles * g.num_n_tiles;
   int cap = c.max_ctas > 0 ? c.max_ctas : num_sms;
   int grid = tiles < cap ? tiles : cap;
-  gemm_tn_kernel<BN, MODE><<<grid, kGemmThreads, Cfg::SMEM, stream>>>(tA, tA2, tB, tC, tX, g);
+  gemm_tn_kernel<BN, MODE><<<grid, kGemmThreads, Cfg::SMEM, stream>>>(tA, tA2, tA3, tB, tC, tX, g);
   return cudaGetLastError() == cudaSuccess ? 0 : -17;
 }
 

@@ -10,14 +10,14 @@ namespace pnm {
 constexpr int kLnWarps = 8;
 constexpr int kLnMaxVec = 4;  // supports C up to 32 lanes * 8 elems * 4 = 1024
 
-// y = (x - mean) * rstd * gamma + beta ; optional second input r: normalises (x + r) and
-// writes the sum to `sum_out` (fused residual add).
+// y = (x - mean) * rstd * gamma + beta (+ post); optional second input r: normalises (x + r)
+// and writes the sum to `sum_out` (fused residual add before the normalisation).
 template <int VEC>
 __global__ void __launch_bounds__(kLnWarps * 32)
 layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ r,
                      const float* __restrict__ gamma, const float* __restrict__ beta, __nv_bfloat16* __restrict__ y,
                      __nv_bfloat16* __restrict__ sum_out, float* __restrict__ mean_out, float* __restrict__ rstd_out,
-                     long long M, int C, float eps) {
+                     const __nv_bfloat16* __restrict__ post, long long M, int C, float eps) {
   const int lane = threadIdx.x & 31;
   const long long warp_global = (long long)blockIdx.x * kLnWarps + (threadIdx.x >> 5);
   const long long nwarps = (long long)gridDim.x * kLnWarps;
@@ -89,6 +89,14 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
         float o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = (val[v][j] - mean) * rstd * gam[v][j] + bet[v][j];
+        if (post) {  // y = LN(x) + post  (residual added after the normalisation)
+          const uint4 up = *reinterpret_cast<const uint4*>(post + row * C + c);
+          float2 f;
+          f = unpack_bf16x2(up.x); o[0] += f.x; o[1] += f.y;
+          f = unpack_bf16x2(up.y); o[2] += f.x; o[3] += f.y;
+          f = unpack_bf16x2(up.z); o[4] += f.x; o[5] += f.y;
+          f = unpack_bf16x2(up.w); o[6] += f.x; o[7] += f.y;
+        }
         uint4 u;
         u.x = pack_bf16x2(o[0], o[1]); u.y = pack_bf16x2(o[2], o[3]);
         u.z = pack_bf16x2(o[4], o[5]); u.w = pack_bf16x2(o[6], o[7]);
@@ -206,18 +214,18 @@ static __global__ void layernorm_bwd_finalize_kernel(const float* __restrict__ s
 inline int ln_vec_for(int C) { return (C + 255) / 256; }
 
 inline int launch_layernorm_fwd(const void* x, const void* r, const float* gamma, const float* beta, void* y,
-                                void* sum_out, float* mean, float* rstd, long long M, int C, float eps, int num_sms,
-                                cudaStream_t st) {
+                                void* sum_out, float* mean, float* rstd, const void* post, long long M, int C,
+                                float eps, int num_sms, cudaStream_t st) {
   if (C % 8 || C > 1024) return -30;
   long long want = (M + kLnWarps - 1) / kLnWarps;
   int grid = (int)(want < (long long)num_sms * 8 ? want : (long long)num_sms * 8);
   if (grid < 1) grid = 1;
-  auto X = (const __nv_bfloat16*)x; auto R = (const __nv_bfloat16*)r; auto Y = (__nv_bfloat16*)y; auto S = (__nv_bfloat16*)sum_out;
+  auto X = (const __nv_bfloat16*)x; auto R = (const __nv_bfloat16*)r; auto Y = (__nv_bfloat16*)y; auto S = (__nv_bfloat16*)sum_out; auto P = (const __nv_bfloat16*)post;
   switch (ln_vec_for(C)) {
-    case 1: layernorm_fwd_kernel<1><<<grid, kLnWarps * 32, 0, st>>>(X, R, gamma, beta, Y, S, mean, rstd, M, C, eps); break;
-    case 2: layernorm_fwd_kernel<2><<<grid, kLnWarps * 32, 0, st>>>(X, R, gamma, beta, Y, S, mean, rstd, M, C, eps); break;
-    case 3: layernorm_fwd_kernel<3><<<grid, kLnWarps * 32, 0, st>>>(X, R, gamma, beta, Y, S, mean, rstd, M, C, eps); break;
-    default: layernorm_fwd_kernel<4><<<grid, kLnWarps * 32, 0, st>>>(X, R, gamma, beta, Y, S, mean, rstd, M, C, eps); break;
+    case 1: layernorm_fwd_kernel<1><<<grid, kLnWarps * 32, 0, st>>>(X, R, gamma, beta, Y, S, mean, rstd, P, M, C, eps); break;
+    case 2: layernorm_fwd_kernel<2><<<grid, kLnWarps * 32, 0, st>>>(X, R, gamma, beta, Y, S, mean, rstd, P, M, C, eps); break;
+    case 3: layernorm_fwd_kernel<3><<<grid, kLnWarps * 32, 0, st>>>(X, R, gamma, beta, Y, S, mean, rstd, P, M, C, eps); break;
+    default: layernorm_fwd_kernel<4><<<grid, kLnWarps * 32, 0, st>>>(X, R, gamma, beta, Y, S, mean, rstd, P, M, C, eps); break;
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -31;
 }

@@ -13,8 +13,8 @@ int pnm_get_error();    // synchronising read of the device error word (0 = none
 int pnm_reset_error();
 
 // C[M,N] = epilogue(A[M,K] * B[N,K]^T); bf16 in/out, fp32 accumulate.  See gemm_tn.cuh.
-int pnm_gemm_tn(const void* A, int lda, const void* A2, int lda2, const void* B, int ldb, void* C, int ldc, void* Z,
-                int ldz, const void* AUX, int ldaux, int M, int N, int K, int K1, const float* bias,
+int pnm_gemm_tn(const void* A, int lda, const void* A2, int lda2, const void* A3, int lda3, const void* B, int ldb, void* C, int ldc, void* Z,
+                int ldz, const void* AUX, int ldaux, int M, int N, int K, int K1, int K2, const float* bias,
                 const float* scale, float* group_out, int act, int aux_mode, int scale_post, int bn, int max_ctas,
                 void* stream);
 
@@ -22,12 +22,20 @@ int pnm_gemm_tn(const void* A, int lda, const void* A2, int lda2, const void* B,
 int pnm_gemm_nt(const void* A, int lda, const void* B, int ldb, float* out, int ldo, float* colsum, int M, int Na,
                 int Nb, int max_ctas, void* stream);
 
+// y = LN(x [+ r]) [+ post]; bf16 rows of C channels (C % 8 == 0, C <= 1024), fp32 gamma / beta / statistics.
 int pnm_layernorm_fwd(const void* x, const void* r, const float* gamma, const float* beta, void* y, void* sum_out,
-                      float* mean, float* rstd, long long M, int C, float eps, void* stream);
+                      float* mean, float* rstd, const void* post, long long M, int C, float eps, void* stream);
 long long pnm_layernorm_bwd_scratch_floats(long long M, int C);
 int pnm_layernorm_bwd(const void* dy, const void* x, const float* gamma, const float* mean, const float* rstd,
                       const void* dres, void* dx, float* dgamma, float* dbeta, float* scratch, long long M, int C,
                       void* stream);
+
+// out[e,:] = in[idx[e],:] (* scale[idx[e]]); bf16 rows, int32 indices (idx may be null = identity).
+int pnm_gather_rows(const void* in, int ldi, const int* idx, const float* scale, void* out, int ldo, long long E,
+                    int C, void* stream);
+// out[n,:] (+)= sum over k in [offsets[n], offsets[n+1]) of in[perm[k],:]; mode 1 divides by the count.
+int pnm_segment_sum(const void* in, int ldi, const int* perm, const int* offsets, void* out, int ldo, long long N,
+                    int C, int accumulate, int mode, void* stream);
 
 #ifdef __cplusplus
 }

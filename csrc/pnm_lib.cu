@@ -6,6 +6,7 @@
 #include "gemm_tn.cuh"
 #include "gemm_nt.cuh"
 #include "norm.cuh"
+#include "graph.cuh"
 #include "pnm_api.h"
 
 __device__ int pnm_error_word = 0;
@@ -42,22 +43,24 @@ int pnm_reset_error() {
   return cudaMemset(g_err_ptr, 0, sizeof(int)) == cudaSuccess ? 0 : -1;
 }
 
-int pnm_gemm_tn(const void* A, int lda, const void* A2, int lda2, const void* B, int ldb, void* C, int ldc, void* Z,
-                int ldz, const void* AUX, int ldaux, int M, int N, int K, int K1, const float* bias,
+int pnm_gemm_tn(const void* A, int lda, const void* A2, int lda2, const void* A3, int lda3, const void* B, int ldb, void* C, int ldc, void* Z,
+                int ldz, const void* AUX, int ldaux, int M, int N, int K, int K1, int K2, const float* bias,
                 const float* scale, float* group_out, int act, int aux_mode, int scale_post, int bn, int max_ctas,
                 void* stream) {
   if (ensure_init()) return -1;
   if (M <= 0 || N <= 0 || K <= 0) return -2;
   if ((N % 8) || (K % 8) || (lda % 8) || (ldb % 8) || (ldc % 8)) return -3;
   if (K1 <= 0 || K1 > K) K1 = K;
+  if (K2 < K1 || K2 > K) K2 = K;
   if (K1 < K && ((K1 % 64) || !A2 || (lda2 % 8))) return -4;
+  if (K2 < K && ((K2 % 64) || !A3 || (lda3 % 8))) return -4;
   if (Z && AUX) return -5;
   if ((aux_mode != 0) != (AUX != nullptr)) return -6;
   if (act == pnm::ACT_SOFTMAX64 && (N % 64)) return -7;
   pnm::GemmCall c;
-  c.A = A; c.lda = lda; c.A2 = A2; c.lda2 = lda2; c.B = B; c.ldb = ldb; c.C = C; c.ldc = ldc;
+  c.A = A; c.lda = lda; c.A2 = A2; c.lda2 = lda2; c.A3 = A3; c.lda3 = lda3; c.B = B; c.ldb = ldb; c.C = C; c.ldc = ldc;
   c.Z = Z; c.ldz = ldz; c.AUX = AUX; c.ldaux = ldaux;
-  c.M = M; c.N = N; c.K = K; c.K1 = K1;
+  c.M = M; c.N = N; c.K = K; c.K1 = K1; c.K2 = K2;
   c.bias = bias; c.scale = scale; c.group_out = group_out;
   c.act = act; c.aux_mode = aux_mode; c.scale_post = scale_post; c.max_ctas = max_ctas;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -82,9 +85,9 @@ int pnm_gemm_nt(const void* A, int lda, const void* B, int ldb, float* out, int 
 }
 
 int pnm_layernorm_fwd(const void* x, const void* r, const float* gamma, const float* beta, void* y, void* sum_out,
-                      float* mean, float* rstd, long long M, int C, float eps, void* stream) {
+                      float* mean, float* rstd, const void* post, long long M, int C, float eps, void* stream) {
   if (ensure_init()) return -1;
-  return pnm::launch_layernorm_fwd(x, r, gamma, beta, y, sum_out, mean, rstd, M, C, eps, g_num_sms,
+  return pnm::launch_layernorm_fwd(x, r, gamma, beta, y, sum_out, mean, rstd, post, M, C, eps, g_num_sms,
                                    reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -99,6 +102,19 @@ int pnm_layernorm_bwd(const void* dy, const void* x, const float* gamma, const f
   if (ensure_init()) return -1;
   return pnm::launch_layernorm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, scratch, M, C, g_num_sms,
                                    reinterpret_cast<cudaStream_t>(stream));
+}
+
+int pnm_gather_rows(const void* in, int ldi, const int* idx, const float* scale, void* out, int ldo, long long E,
+                    int C, void* stream) {
+  if (ensure_init()) return -1;
+  return pnm::launch_gather_rows(in, ldi, idx, scale, out, ldo, E, C, g_num_sms, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int pnm_segment_sum(const void* in, int ldi, const int* perm, const int* offsets, void* out, int ldo, long long N,
+                    int C, int accumulate, int mode, void* stream) {
+  if (ensure_init()) return -1;
+  return pnm::launch_segment_sum(in, ldi, perm, offsets, out, ldo, N, C, accumulate, mode, g_num_sms,
+                                 reinterpret_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

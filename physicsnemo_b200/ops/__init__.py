@@ -6,6 +6,7 @@ from .gemm import (
     fused_path_enabled, gemm_nt, gemm_tn, gemm_tn_reference, linear, mlp_chain,
 )
 from .norm import layer_norm
+from .graph import SegmentIndex, gather_rows, segment_reduce
 
 
 def library_available() -> bool:

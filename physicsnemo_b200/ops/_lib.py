@@ -73,10 +73,12 @@ def _declare(lib):
         "pnm_num_sms": ([], i32),
         "pnm_get_error": ([], i32),
         "pnm_reset_error": ([], i32),
-        "pnm_gemm_tn": ([vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, vp,
+        "pnm_gemm_tn": ([vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp,
                          i32, i32, i32, i32, i32, vp], i32),
         "pnm_gemm_nt": ([vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, vp], i32),
-        "pnm_layernorm_fwd": ([vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp], i32),
+        "pnm_layernorm_fwd": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp], i32),
+        "pnm_gather_rows": ([vp, i32, vp, vp, vp, i32, i64, i32, vp], i32),
+        "pnm_segment_sum": ([vp, i32, vp, vp, vp, i32, i64, i32, i32, i32, vp], i32),
         "pnm_layernorm_bwd_scratch_floats": ([i64, i32], i64),
         "pnm_layernorm_bwd": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, vp], i32),
     }

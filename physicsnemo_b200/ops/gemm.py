@@ -58,6 +58,7 @@ def gemm_tn(
     aux: Optional[torch.Tensor] = None,
     aux_mode: int = AUX_NONE,
     a2: Optional[torch.Tensor] = None,
+    a3: Optional[torch.Tensor] = None,
     z_out: bool = False,
     out: Optional[torch.Tensor] = None,
     group_out: Optional[torch.Tensor] = None,
@@ -67,7 +68,7 @@ def gemm_tn(
 ):
     """``epilogue([a | a2] @ b.T)`` on tcgen05; bf16 operands, fp32 accumulation, bf16 result.
 
-    a: [M, K1], a2: [M, K - K1] (optional), b: [N, K]; bias / scale: fp32 [N];
+    a: [M, K1], a2 / a3: further column blocks of A (optional, K-concatenated), b: [N, K]; bias / scale: fp32 [N];
     aux: bf16 [M, N] consumed according to ``aux_mode``; ``z_out`` also returns the
     pre-activation.  Returns ``out`` or ``(out, z)``.
     """
@@ -77,9 +78,15 @@ def gemm_tn(
     b = _rowmajor2d(b)
     M, K1 = a.shape
     N, K = b.shape
+    K2 = K
     if a2 is not None:
         a2 = _rowmajor2d(a2)
-        assert a2.shape[0] == M and K1 + a2.shape[1] == K
+        K2 = K1 + a2.shape[1]
+        if a3 is not None:
+            a3 = _rowmajor2d(a3)
+            assert a3.shape[0] == M and K2 + a3.shape[1] == K
+        else:
+            assert a2.shape[0] == M and K2 == K
     else:
         assert K1 == K, f"A has K={K1} but B has K={K}"
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
@@ -94,10 +101,11 @@ def gemm_tn(
     if scale is not None:
         assert scale.dtype == torch.float32 and scale.numel() == N and scale.is_contiguous()
     code = lib.pnm_gemm_tn(
-        _ptr(a), a.stride(0), _ptr(a2), 0 if a2 is None else a2.stride(0), _ptr(b), b.stride(0),
+        _ptr(a), a.stride(0), _ptr(a2), 0 if a2 is None else a2.stride(0), _ptr(a3), 0 if a3 is None else a3.stride(0),
+        _ptr(b), b.stride(0),
         _ptr(out), out.stride(0), _ptr(z), 0 if z is None else z.stride(0),
         _ptr(aux), 0 if aux is None else aux.stride(0),
-        M, N, K, K1, _ptr(bias), _ptr(scale), _ptr(group_out), act, aux_mode, int(scale_post), bn, max_ctas,
+        M, N, K, K1, K2, _ptr(bias), _ptr(scale), _ptr(group_out), act, aux_mode, int(scale_post), bn, max_ctas,
         _stream(),
     )
     _check(code, "pnm_gemm_tn")
@@ -145,9 +153,9 @@ def act_torch(x: torch.Tensor, act: int) -> torch.Tensor:
 
 
 def gemm_tn_reference(a, b, *, bias=None, scale=None, act=ACT_NONE, aux=None, aux_mode=AUX_NONE, a2=None,
-                      scale_post=False):
+                      a3=None, scale_post=False):
     """fp32 PyTorch statement of what ``gemm_tn`` computes (used by the tests)."""
-    af = a.float() if a2 is None else torch.cat([a.float(), a2.float()], dim=1)
+    af = torch.cat([t.float() for t in (a, a2, a3) if t is not None], dim=1)
     x = af @ b.float().t()
     if bias is not None:
         x = x + bias
@@ -217,18 +225,23 @@ def _pad_cols(t: torch.Tensor, mult: int = 8) -> torch.Tensor:
 
 
 class _MlpChainFn(torch.autograd.Function):
-    """``h_i = act_i(h_{i-1} W_i^T + b_i)``, last layer optionally ``+ residual``."""
+    """``h_i = act_i(h_{i-1} W_i^T + b_i)``, last layer optionally ``+ residual``.
+
+    The input of the first layer may be given as up to three column blocks (K-concatenated
+    inside the GEMM, no materialised concatenation)."""
 
     @staticmethod
-    def forward(ctx, x2d, residual, acts, n_layers, need_z, *params):
-        weights = params[:n_layers]
-        biases = params[n_layers:]
+    def forward(ctx, residual, acts, n_layers, need_z, n_src, *rest):
+        srcs = list(rest[:n_src])
+        weights = rest[n_src:n_src + n_layers]
+        biases = rest[n_src + n_layers:]
         acts = list(acts)
-        h = x2d
-        hs, zs = [x2d], []
+        hs, zs = [], []
+        h = None
         for i in range(n_layers):
             w = _bf16_weight(weights[i])
-            if w.shape[1] != h.shape[1]:  # K padded to a multiple of 8
+            k_in = sum(t.shape[1] for t in srcs) if i == 0 else h.shape[1]
+            if w.shape[1] != k_in:  # K padded to a multiple of 8
                 w = _pad_cols(w)
             n_true = w.shape[0]
             if n_true % 8:
@@ -239,34 +252,45 @@ class _MlpChainFn(torch.autograd.Function):
                 if b.numel() != w.shape[0]:
                     b = F.pad(b, (0, w.shape[0] - b.numel()))
             last = i == n_layers - 1
-            use_res = last and residual is not None
+            use_res = last and residual is not None and acts[i] == ACT_NONE
+            a_kw = {}
+            if i == 0:
+                a = srcs[0]
+                if n_src > 1:
+                    a_kw["a2"] = srcs[1]
+                if n_src > 2:
+                    a_kw["a3"] = srcs[2]
+            else:
+                a = h
             if acts[i] != ACT_NONE and need_z:
-                h, z = gemm_tn(h, w, bias=b, act=acts[i], z_out=True)
+                h, z = gemm_tn(a, w, bias=b, act=acts[i], z_out=True, **a_kw)
                 zs.append(z)
             else:
-                h = gemm_tn(h, w, bias=b, act=acts[i], aux=residual if use_res else None,
-                            aux_mode=AUX_ADD if use_res else AUX_NONE)
+                h = gemm_tn(a, w, bias=b, act=acts[i], aux=residual if use_res else None,
+                            aux_mode=AUX_ADD if use_res else AUX_NONE, **a_kw)
                 zs.append(None)
-            if last and acts[i] != ACT_NONE and use_res:
+            if last and residual is not None and not use_res:
                 h = h + residual
             if n_true != h.shape[1]:
                 h = h[:, :n_true]
             hs.append(h)
-        ctx.acts, ctx.n_layers = acts, n_layers
+        ctx.acts, ctx.n_layers, ctx.n_src = acts, n_layers, n_src
         ctx.has_res = residual is not None
-        ctx.save_for_backward(*hs[:-1], *[z for z in zs if z is not None], *weights)
+        ctx.src_widths = [t.shape[1] for t in srcs]
+        ctx.save_for_backward(*srcs, *hs[:-1], *[z for z in zs if z is not None], *weights)
         ctx.z_mask = [z is not None for z in zs]
         ctx.bias_mask = [b is not None for b in biases]
         return hs[-1]
 
     @staticmethod
     def backward(ctx, dy):
-        n = ctx.n_layers
+        n, ns = ctx.n_layers, ctx.n_src
         saved = ctx.saved_tensors
-        hs = list(saved[:n])
+        srcs = list(saved[:ns])
+        hs = [None] + list(saved[ns:ns + n - 1])  # hs[i] = input of layer i (i >= 1)
         nz = sum(ctx.z_mask)
-        zlist = list(saved[n:n + nz])
-        weights = saved[n + nz:]
+        zlist = list(saved[ns + n - 1:ns + n - 1 + nz])
+        weights = saved[ns + n - 1 + nz:]
         zs, zi = [], 0
         for m in ctx.z_mask:
             zs.append(zlist[zi] if m else None)
@@ -276,62 +300,89 @@ class _MlpChainFn(torch.autograd.Function):
         g = dy.contiguous()
         if acts[n - 1] != ACT_NONE:
             # activation on the output layer: no upstream GEMM to fuse into
-            z = zs[n - 1].float().requires_grad_(True)
+            z = zs[n - 1][:, :g.shape[1]].float().requires_grad_(True)
             with torch.enable_grad():
                 f = act_torch(z, acts[n - 1])
             g = torch.autograd.grad(f, z, g.float())[0].to(torch.bfloat16)
+        base = 5 + ns  # index of the first weight among the forward inputs
         dws, dbs = [None] * n, [None] * n
-        dx = None
+        dsrc = [None] * ns
         for i in range(n - 1, -1, -1):
             w = weights[i]
             n_true, k_true = w.shape
             gi = g
             if gi.shape[1] % 8:
                 gi = _pad_cols(gi)
-            hin = hs[i]
-            need_b = ctx.bias_mask[i] and ctx.needs_input_grad[5 + n + i]
-            if ctx.needs_input_grad[5 + i] or need_b:
-                res = gemm_nt(gi, hin, colsum=need_b)
-                dw, db = (res if need_b else (res, None))
-                dws[i] = dw[:n_true, :k_true].to(w.dtype) if (dw.shape != w.shape or w.dtype != dw.dtype) else dw
+            need_b = ctx.bias_mask[i] and ctx.needs_input_grad[base + n + i]
+            if ctx.needs_input_grad[base + i] or need_b:
+                if i == 0 and ns > 1:
+                    # weight gradient per column block of the K-concatenated input
+                    parts, db = [], None
+                    for j, t in enumerate(srcs):
+                        res = gemm_nt(gi, t, colsum=need_b and j == 0)
+                        if need_b and j == 0:
+                            res, db = res
+                        parts.append(res[:n_true])
+                    dw = torch.cat(parts, dim=1)[:, :k_true]
+                else:
+                    hin = srcs[0] if i == 0 else hs[i]
+                    res = gemm_nt(gi, hin, colsum=need_b)
+                    dw, db = (res if need_b else (res, None))
+                    dw = dw[:n_true, :k_true]
+                dws[i] = dw if dw.dtype == w.dtype else dw.to(w.dtype)
                 if db is not None:
                     dbs[i] = db[:n_true]
-            if i > 0 or ctx.needs_input_grad[0]:
+            need_dx = i > 0 or any(ctx.needs_input_grad[5 + j] for j in range(ns))
+            if need_dx:
                 wt = _bf16_weight(w, transpose=True)  # [K, N]
                 if wt.shape[1] % 8:
                     wt = _pad_cols(wt)
                 if wt.shape[0] % 8:
                     wt = F.pad(wt, (0, 0, 0, (-wt.shape[0]) % 8))
                 if i > 0 and zs[i - 1] is not None:
-                    g = gemm_tn(gi, wt, aux=zs[i - 1] if zs[i - 1].shape[1] == wt.shape[0] else _pad_cols(zs[i - 1]),
+                    zprev = zs[i - 1]
+                    g = gemm_tn(gi, wt, aux=zprev if zprev.shape[1] == wt.shape[0] else _pad_cols(zprev),
                                 aux_mode=_DACT[acts[i - 1]])
                 else:
                     g = gemm_tn(gi, wt)
-                if g.shape[1] != hin.shape[1]:
-                    g = g[:, :hin.shape[1]]
                 if i == 0:
-                    dx = g
-        return (dx, dres, None, None, None, *dws, *dbs)
+                    off = 0
+                    for j, wdt in enumerate(ctx.src_widths):
+                        if ctx.needs_input_grad[5 + j]:
+                            dsrc[j] = g[:, off:off + wdt]
+                        off += wdt
+                elif g.shape[1] != hs[i].shape[1]:
+                    g = g[:, :hs[i].shape[1]]
+        return (dres, None, None, None, None, *dsrc, *dws, *dbs)
 
 
-def mlp_chain(x: torch.Tensor, weights: Sequence[torch.Tensor], biases: Sequence[Optional[torch.Tensor]],
+def mlp_chain(x, weights: Sequence[torch.Tensor], biases: Sequence[Optional[torch.Tensor]],
               acts: Sequence[int], residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Apply ``len(weights)`` linear layers with activations ``acts`` (codes) between them.
 
-    ``x``: [..., K]; returns [..., N_last] (+ ``residual`` when given).  CUDA bf16 inputs run on
-    the tcgen05 kernels, anything else through PyTorch.
+    ``x``: [..., K] or a list / tuple of up to three tensors [..., K_j] that are treated as
+    the column blocks of one input (every block but the last a multiple of 64 wide);
+    returns [..., N_last] (+ ``residual`` when given).  CUDA bf16 inputs run on the tcgen05
+    kernels, anything else through PyTorch.
     """
-    if not fused_path_enabled(x):
-        h = x
+    xs = list(x) if isinstance(x, (list, tuple)) else [x]
+    if not fused_path_enabled(xs[0]):
+        h = xs[0] if len(xs) == 1 else torch.cat(xs, dim=-1)
         for w, b, a in zip(weights, biases, acts):
             h = act_torch(F.linear(h, w, b), a)
         return h if residual is None else h + residual
-    shp = x.shape
-    x2 = x.reshape(-1, shp[-1])
-    if x2.dtype != torch.bfloat16:
-        x2 = x2.to(torch.bfloat16)
-    if x2.shape[1] % 8:
-        x2 = _pad_cols(x2)
+    shp = xs[0].shape
+    multi_ok = len(xs) <= 3 and all(t.shape[-1] % 64 == 0 for t in xs[:-1])
+    if len(xs) > 1 and not multi_ok:
+        xs = [torch.cat(xs, dim=-1)]
+    x2s = []
+    for t in xs:
+        t2 = t.reshape(-1, t.shape[-1])
+        if t2.dtype != torch.bfloat16:
+            t2 = t2.to(torch.bfloat16)
+        x2s.append(t2)
+    if x2s[-1].shape[1] % 8:
+        x2s[-1] = _pad_cols(x2s[-1])
     r2 = None
     if residual is not None:
         r2 = residual.reshape(-1, residual.shape[-1])
@@ -339,9 +390,10 @@ def mlp_chain(x: torch.Tensor, weights: Sequence[torch.Tensor], biases: Sequence
             r2 = r2.to(torch.bfloat16)
     n = len(weights)
     need_z = torch.is_grad_enabled() and (
-        x.requires_grad or any(w.requires_grad for w in weights) or (residual is not None and residual.requires_grad)
+        any(t.requires_grad for t in xs) or any(w.requires_grad for w in weights)
+        or (residual is not None and residual.requires_grad)
     )
-    y = _MlpChainFn.apply(x2, r2, tuple(acts), n, need_z, *weights, *biases)
+    y = _MlpChainFn.apply(r2, tuple(acts), n, need_z, len(x2s), *x2s, *weights, *biases)
     return y.reshape(*shp[:-1], y.shape[-1])
 
 

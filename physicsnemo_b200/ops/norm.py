@@ -18,7 +18,7 @@ from . import gemm as _g
 
 class _LayerNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x2d, gamma, beta, eps):
+    def forward(ctx, x2d, gamma, beta, eps, post=None):
         lib = _lib.load(required=True)
         M, C = x2d.shape
         y = torch.empty_like(x2d)
@@ -27,12 +27,14 @@ class _LayerNormFn(torch.autograd.Function):
         g32 = gamma.detach().float().contiguous()
         b32 = beta.detach().float().contiguous() if beta is not None else None
         code = lib.pnm_layernorm_fwd(x2d.data_ptr(), None, g32.data_ptr(), None if b32 is None else b32.data_ptr(),
-                                     y.data_ptr(), None, mean.data_ptr(), rstd.data_ptr(), M, C, float(eps),
+                                     y.data_ptr(), None, mean.data_ptr(), rstd.data_ptr(),
+                                     None if post is None else post.data_ptr(), M, C, float(eps),
                                      _g._stream())
         _g._check(code, "pnm_layernorm_fwd")
         _g.launch_count += 1
         ctx.save_for_backward(x2d, g32, mean, rstd)
         ctx.has_beta = beta is not None
+        ctx.has_post = post is not None
         ctx.param_dtype = gamma.dtype
         return y
 
@@ -52,16 +54,25 @@ class _LayerNormFn(torch.autograd.Function):
                                      M, C, _g._stream())
         _g._check(code, "pnm_layernorm_bwd")
         _g.launch_count += 2
-        return dx, dgamma.to(ctx.param_dtype), (dbeta.to(ctx.param_dtype) if ctx.has_beta else None), None
+        return (dx, dgamma.to(ctx.param_dtype), (dbeta.to(ctx.param_dtype) if ctx.has_beta else None), None,
+                dy if ctx.has_post else None)
 
 
-def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float = 1e-5) -> torch.Tensor:
-    """LayerNorm over the last dimension."""
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float = 1e-5,
+               post: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LayerNorm over the last dimension; ``post`` (same shape) is added to the result."""
     C = x.shape[-1]
     if not _g.fused_path_enabled(x) or C % 8 or C > 1024:
-        return F.layer_norm(x, (C,), weight, bias, eps)
+        y = F.layer_norm(x, (C,), weight, bias, eps)
+        return y if post is None else y + post
     x2 = x.reshape(-1, C)
     if x2.dtype != torch.bfloat16:
         x2 = x2.to(torch.bfloat16)
     x2 = x2.contiguous()
-    return _LayerNormFn.apply(x2, weight, bias, eps).reshape(x.shape)
+    p2 = None
+    if post is not None:
+        p2 = post.reshape(-1, C)
+        if p2.dtype != torch.bfloat16:
+            p2 = p2.to(torch.bfloat16)
+        p2 = p2.contiguous()
+    return _LayerNormFn.apply(x2, weight, bias, eps, p2).reshape(x.shape)

@@ -1,0 +1,104 @@
+"""CPU checks of the model zoo: parameter counts of the five headline configurations,
+checkpoint round trips, and agreement of structure with the published layouts."""
+import warnings
+
+import pytest
+import torch
+
+import physicsnemo_b200 as pn
+from physicsnemo_b200.models.afno import AFNO
+from physicsnemo_b200.models.diffusion_unets import SongUNet
+from physicsnemo_b200.models.fno import FNO
+from physicsnemo_b200.models.meshgraphnet import MeshGraphNet
+from physicsnemo_b200.models.transolver import Transolver
+from physicsnemo_b200.nn.module.gnn_layers.graph_types import Graph
+
+
+def test_headline_parameter_counts():
+    fno = FNO(in_channels=1, out_channels=1, decoder_layers=1, decoder_layer_size=128, dimension=2,
+              latent_channels=32, num_fno_layers=4, num_fno_modes=12, padding=8, activation_fn="gelu")
+    assert (fno.num_parameters(), len(fno.state_dict())) == (2_368_481, 24)
+    mgn = MeshGraphNet(6, 3, 3, processor_size=15, mlp_activation_fn="silu", hidden_dim_processor=128)
+    assert (mgn.num_parameters(), len(mgn.state_dict())) == (2_332_419, 262)
+    tr = Transolver(functional_dim=3, out_dim=4, embedding_dim=3, n_layers=8, n_hidden=256, n_head=8, slice_num=64,
+                    mlp_ratio=4, use_te=False)
+    assert (tr.num_parameters(), len(tr.state_dict())) == (5_969_732, 152)
+    with torch.device("meta"):
+        unet = SongUNet(img_resolution=1024, in_channels=16, out_channels=4, model_channels=128,
+                        channel_mult=[1, 2, 2, 4], num_blocks=2, attn_resolutions=[64])
+        afno = AFNO(inp_shape=[720, 1440], in_channels=73, out_channels=73, patch_size=[8, 8], embed_dim=768,
+                    depth=12, num_blocks=8, sparsity_threshold=0.01)
+    assert (sum(p.numel() for p in unet.parameters()), len(unet.state_dict())) == (73_761_156, 349)
+    assert (sum(p.numel() for p in afno.parameters()), len(afno.state_dict())) == (79_900_416, 148)
+
+
+@pytest.mark.parametrize("legacy", [False, True])
+def test_checkpoint_round_trip(tmp_path, legacy):
+    model = FNO(in_channels=2, out_channels=1, dimension=2, latent_channels=8, num_fno_layers=2, num_fno_modes=3,
+                padding=2, decoder_layer_size=8)
+    path = tmp_path / "fno.mdlus"
+    model.save(str(path), legacy_format=legacy)
+    loaded = pn.Module.from_checkpoint(str(path))
+    assert type(loaded) is FNO
+    x = torch.randn(2, 2, 12, 12)
+    assert torch.equal(model(x), loaded(x))
+    other = FNO(in_channels=2, out_channels=1, dimension=2, latent_channels=8, num_fno_layers=2, num_fno_modes=3,
+                padding=2, decoder_layer_size=8)
+    other.load(str(path))
+    assert torch.equal(model(x), other(x))
+
+
+def test_nested_modules_and_overrides(tmp_path):
+    class Inner(pn.Module):
+        _overridable_args = {"scale"}
+
+        def __init__(self, width, scale=1.0):
+            super().__init__(meta=pn.ModelMetaData())
+            self.lin = torch.nn.Linear(width, width)
+            self.scale = scale
+
+    class Outer(pn.Module):
+        def __init__(self, inner, depth=1):
+            super().__init__()
+            self.inner, self.depth = inner, depth
+
+    import sys
+    mod = sys.modules[__name__]
+    mod.Inner, mod.Outer = Inner, Outer
+    Inner.__qualname__, Outer.__qualname__ = "Inner", "Outer"
+    m = Outer(Inner(4, scale=2.0), depth=3)
+    p = tmp_path / "o.mdlus"
+    m.save(str(p))
+    r = pn.Module.from_checkpoint(str(p), override_args={"inner.scale": 5.0})
+    assert r.depth == 3 and r.inner.scale == 5.0 and torch.equal(r.inner.lin.weight, m.inner.lin.weight)
+    with pytest.raises(ValueError):
+        pn.Module.from_checkpoint(str(p), override_args={"depth": 2})
+
+
+def test_from_torch_and_registry():
+    from physicsnemo_b200.core import ModelRegistry
+
+    class Net(torch.nn.Module):
+        def __init__(self, n):
+            super().__init__()
+            self.l = torch.nn.Linear(n, n)
+
+        def forward(self, x):
+            return self.l(x)
+
+    Wrapped = pn.Module.from_torch(Net, meta=pn.ModelMetaData(), name="WrappedNetForTest", register=True)
+    m = Wrapped(3)
+    assert isinstance(m, pn.Module) and m(torch.randn(2, 3)).shape == (2, 3)
+    assert ModelRegistry().factory("WrappedNetForTest") is Wrapped
+
+
+def test_small_forward_backward_all_models():
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        g = Graph(torch.randint(0, 30, (2, 90)), 30)
+        MeshGraphNet(4, 3, 2, processor_size=2)(torch.randn(30, 4), torch.randn(90, 3), g).sum().backward()
+        AFNO([16, 16], 2, 2, patch_size=[4, 4], embed_dim=16, depth=1, num_blocks=4)(torch.randn(1, 2, 16, 16)).sum().backward()
+        SongUNet(16, 3, 2, model_channels=8, channel_mult=[1, 2], num_blocks=1, attn_resolutions=[8])(
+            torch.randn(1, 3, 16, 16), torch.rand(1)).sum().backward()
+        Transolver(2, 1, structured_shape=(8, 8), unified_pos=True, n_hidden=16, n_head=2, slice_num=4, use_te=False)(
+            torch.randn(1, 8, 8, 2)).sum().backward()
