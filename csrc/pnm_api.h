@@ -37,6 +37,13 @@ int pnm_gather_rows(const void* in, int ldi, const int* idx, const float* scale,
 int pnm_segment_sum(const void* in, int ldi, const int* perm, const int* offsets, void* out, int ldo, long long N,
                     int C, int accumulate, int mode, void* stream);
 
+// In-kernel all-reduce (sum, fp32) over peer-mapped symmetric buffers; see peer.cuh for the layout.
+int pnm_peer_allreduce(const float* in, float* out, long long n, float scale, int two_shot, const void* const* bases,
+                       int rank, int world, unsigned int epoch, long long capacity_floats, double budget_s,
+                       void* stream);
+int pnm_peer_flag_bytes();
+int pnm_peer_wait_probe(const void* flag, unsigned int expect, double budget_s, int* status_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

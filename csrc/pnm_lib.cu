@@ -7,6 +7,7 @@
 #include "gemm_nt.cuh"
 #include "norm.cuh"
 #include "graph.cuh"
+#include "peer.cuh"
 #include "pnm_api.h"
 
 __device__ int pnm_error_word = 0;
@@ -115,6 +116,29 @@ int pnm_segment_sum(const void* in, int ldi, const int* perm, const int* offsets
   if (ensure_init()) return -1;
   return pnm::launch_segment_sum(in, ldi, perm, offsets, out, ldo, N, C, accumulate, mode, g_num_sms,
                                  reinterpret_cast<cudaStream_t>(stream));
+}
+
+// bases: host array of `world` peer-mapped pointers to the symmetric buffers (this rank's own included).
+int pnm_peer_allreduce(const float* in, float* out, long long n, float scale, int two_shot, const void* const* bases,
+                       int rank, int world, unsigned int epoch, long long capacity_floats, double budget_s,
+                       void* stream) {
+  if (ensure_init()) return -1;
+  pnm::PeerArgs p;
+  if (world > pnm::kPeerMaxRanks) return -50;
+  for (int r = 0; r < world; ++r) p.base[r] = reinterpret_cast<uint8_t*>(const_cast<void*>(bases[r]));
+  p.rank = rank; p.world = world; p.epoch = epoch; p.capacity = capacity_floats;
+  p.budget_ns = (unsigned long long)(budget_s * 1e9);
+  return pnm::launch_peer_allreduce(in, out, n, scale, two_shot, p, g_err_ptr, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int pnm_peer_flag_bytes() { return pnm::kFlagBytes; }
+
+// Launch a wait on `flag` that gives up after budget_s seconds; *status_out = 1 if satisfied, 0 if it timed out.
+int pnm_peer_wait_probe(const void* flag, unsigned int expect, double budget_s, int* status_out, void* stream) {
+  if (ensure_init()) return -1;
+  pnm::peer_wait_probe_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint32_t*>(flag), expect, (unsigned long long)(budget_s * 1e9), g_err_ptr, status_out);
+  return cudaGetLastError() == cudaSuccess ? 0 : -52;
 }
 
 }  // extern "C"

@@ -88,9 +88,15 @@ class _PhysAttnFn(torch.autograd.Function):
         dev = xn.device
         # out = w @ Wcomb.T + bo (+res)
         dWcomb, dbo = G.gemm_nt(dout, w, colsum=True)                         # (C, H*S), (C,)
+        share = 1.0
         if ctx.reduce_fn is not None:
+            # the slice tokens are global quantities: their gradient needs the global dWcomb.
             packed = ctx.reduce_fn(torch.cat([dWcomb.reshape(-1), dbo]))
             dWcomb, dbo = packed[: dWcomb.numel()].reshape(dWcomb.shape), packed[dWcomb.numel():]
+            # parameter gradients derived from reduced quantities are already global and equal on
+            # every rank; they are handed out as 1/world shares so that the model-wide gradient
+            # sum over the shards restores them.
+            share = 1.0 / float(getattr(ctx.reduce_fn, "world", None) or getattr(getattr(ctx.reduce_fn, "__self__", None), "world", 1))
         pWo, pWqkv = p[8], p[7]
         d_tok, d_norm, dWo, dWqkv = torch.autograd.grad(Wcomb, [tok_leaf, norm_leaf, pWo, pWqkv], dWcomb,
                                                          retain_graph=False)
@@ -105,12 +111,6 @@ class _PhysAttnFn(torch.autograd.Function):
         dWc, dbc = G.gemm_nt(dlogit, xn, colsum=True)                         # (H*S, C), (H*S,)
         dWfx, dbfx = G.gemm_nt(dfx, xn, colsum=True)                          # (H*D, C), (H*D,)
         d_inv_t = (grp / inv_t.detach().reshape(H, S)[:, 0]).repeat_interleave(S) / S
-        if ctx.reduce_fn is not None:
-            sizes = [dWc.numel(), dbc.numel(), dWfx.numel(), dbfx.numel(), d_inv_t.numel()]
-            packed = ctx.reduce_fn(torch.cat([dWc.reshape(-1), dbc, dWfx.reshape(-1), dbfx, d_inv_t]))
-            parts = packed.split(sizes)
-            dWc, dbc, dWfx, dbfx, d_inv_t = (parts[0].reshape(dWc.shape), parts[1], parts[2].reshape(dWfx.shape),
-                                             parts[3], parts[4])
         pWx, pbx, pWs, pbs, ptemp = p[0], p[1], p[4], p[5], p[6]
         dWx, dbx, dWs, dbs, dtemp = torch.autograd.grad([Wc, bc, inv_t], [pWx, pbx, pWs, pbs, ptemp],
                                                         [dWc, dbc, d_inv_t], allow_unused=True)
@@ -118,6 +118,8 @@ class _PhysAttnFn(torch.autograd.Function):
         Wback = torch.cat([Wc.detach().t(), p[2].detach().t()], dim=1).to(torch.bfloat16).contiguous()  # (C, H*S + H*D)
         dxn = G.gemm_tn(dlogit, Wback, a2=dfx)
         dres = dout if ctx.has_res else None
+        if share != 1.0:
+            dWqkv, dWo, dbo = dWqkv * share, dWo * share, dbo * share
         grads = [dWx, dbx, dWfx, dbfx, dWs, dbs, dtemp, dWqkv, dWo, dbo]
         grads = [None if g is None else g.to(dt) for g, dt in zip(grads, ctx.param_dtypes)]
         ctx.graph = None
@@ -128,8 +130,9 @@ def physics_attention_irregular(mod, x: torch.Tensor, residual: torch.Tensor | N
     """Fused forward of ``PhysicsAttentionIrregularMesh`` ``mod`` on ``x`` (B, N, C), B folded.
 
     ``reduce_fn`` (optional) maps a flat fp32 tensor of partial sums to the sum over all point
-    shards (an all-reduce); it is applied to slice tokens / norms forward and to the small
-    parameter-side gradients backward.
+    shards (an all-reduce); it is applied once forward (slice tokens and norms) and once
+    backward (the gradient of the combined de-slicing matrix, from which the token gradients
+    follow).  All other parameter gradients stay per-shard partial sums.
     """
     B, N, C = x.shape
     outs = []

@@ -36,7 +36,7 @@ class PointParallel:
             try:
                 from .peer import PeerAllReduce
 
-                self._peer = PeerAllReduce(group=group, max_numel=1 << 20)
+                self._peer = PeerAllReduce(group=group, max_numel=1 << 23)
             except Exception:
                 if backend == "peer":
                     raise
