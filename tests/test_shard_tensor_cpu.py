@@ -1,0 +1,166 @@
+"""Domain-parallel oracle: the same module on gathered data (one process) and on sharded
+data (gloo ranks) must agree in outputs, input gradients and parameter gradients."""
+import copy
+
+import torch
+import torch.distributed as dist
+
+from tests.dist_utils import run_ranks
+
+
+def _check(name, a, b, tol=1e-5):
+    err = (a - b).abs().max().item()
+    assert err <= tol * max(1.0, b.abs().max().item()), f"{name}: max err {err}"
+
+
+def _numerical_check(mesh, module, full_inputs, shard_dims, tol=1e-5, sizes=None):
+    """Run ``module`` on full inputs and on ShardTensors; compare forward and all gradients."""
+    from physicsnemo_b200.parallel import Replicate, Shard, ShardTensor, reduce_param_grads
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    ref = copy.deepcopy(module)
+    full = [t.clone().requires_grad_(t.is_floating_point()) for t in full_inputs]
+    out_ref = ref(*full)
+    out_ref.float().mean().backward()
+    shards = []
+    for t, d in zip(full_inputs, shard_dims):
+        if d is None:
+            shards.append(ShardTensor.from_local(t.clone(), mesh, [Replicate()]))
+            continue
+        if sizes is None:
+            pieces = t.tensor_split(world, dim=d)
+        else:
+            pieces = t.split(sizes, dim=d)
+        loc = pieces[rank].clone().requires_grad_(t.is_floating_point())
+        shards.append(ShardTensor.from_local(loc, mesh, [Shard(d)]))
+    out = module(*shards)
+    assert isinstance(out, ShardTensor), type(out)
+    _check("forward", out.full_tensor().detach(), out_ref.detach(), tol)
+    loss = out.float().mean()
+    loss.backward()
+    for (n, p), (_, q) in zip(module.named_parameters(), ref.named_parameters()):
+        assert p.grad is not None, n
+        _check(f"grad {n}", p.grad, q.grad, tol * 10)
+    for s, f, d in zip(shards, full, shard_dims):
+        if d is None or not f.is_floating_point():
+            continue
+        pieces = f.grad.tensor_split(world, dim=d) if sizes is None else f.grad.split(sizes, dim=d)
+        _check("input grad", s.grad.to_local(), pieces[rank], tol * 10)
+
+
+def _conv_norm_pool(rank, world):
+    from physicsnemo_b200.distributed import DistributedManager
+
+    mesh = DistributedManager().initialize_mesh((world,), ("domain",))
+    torch.manual_seed(0)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.c1 = torch.nn.Conv2d(3, 8, 3, padding=1)
+            self.gn = torch.nn.GroupNorm(4, 8)
+            self.c2 = torch.nn.Conv2d(8, 8, 3, padding=1, stride=2)
+            self.c3 = torch.nn.Conv2d(8, 4, 1)
+            self.up = torch.nn.ConvTranspose2d(4, 4, 2, stride=2)
+
+        def forward(self, x):
+            x = torch.nn.functional.silu(self.gn(self.c1(x)))
+            x = self.c2(x)
+            x = torch.nn.functional.avg_pool2d(x, 2)
+            x = self.up(self.c3(x))
+            x = torch.nn.functional.interpolate(x, scale_factor=2, mode="nearest")
+            return torch.nn.functional.pad(x, (1, 1, 2, 2))
+
+    x = torch.randn(2, 3, 16 * world, 12, dtype=torch.float64)
+    _numerical_check(mesh, Net().double(), [x], [2], tol=1e-9)
+    # uneven shards, valid convolution (no padding), bilinear up-sampling
+    class Net2(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.c = torch.nn.Conv2d(2, 3, 5, padding=0)
+
+        def forward(self, x):
+            return torch.nn.functional.interpolate(self.c(x), scale_factor=2, mode="bilinear")
+
+    sizes = [7 + r for r in range(world)]
+    x = torch.randn(1, 2, sum(sizes), 9, dtype=torch.float64)
+    _numerical_check(mesh, Net2().double(), [x], [2], tol=1e-9, sizes=sizes)
+
+
+def test_conv_norm_pool_two_ranks():
+    run_ranks(_conv_norm_pool, world=2)
+
+
+def test_conv_norm_pool_three_ranks():
+    run_ranks(_conv_norm_pool, world=3)
+
+
+def _attention_and_transolver(rank, world):
+    from physicsnemo_b200.distributed import DistributedManager
+    from physicsnemo_b200.models.transolver import Transolver
+    from physicsnemo_b200.parallel import Replicate, Shard, ShardTensor
+
+    mesh = DistributedManager().initialize_mesh((world,), ("domain",))
+    torch.manual_seed(0)
+
+    class Attn(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.qkv = torch.nn.Linear(16, 48)
+
+        def forward(self, x):
+            B, N, _ = x.shape
+            q, k, v = self.qkv(x).reshape(B, N, 3, 2, 8).permute(2, 0, 3, 1, 4).unbind(0)
+            o = torch.nn.functional.scaled_dot_product_attention(q, k, v)
+            return o.transpose(1, 2).reshape(B, N, 16)
+
+    x = torch.randn(2, 6 * world + 1, 16, dtype=torch.float64)
+    sizes = [6] * (world - 1) + [7]
+    _numerical_check(mesh, Attn().double(), [x], [1], tol=1e-9, sizes=sizes)
+    model = Transolver(functional_dim=2, out_dim=3, embedding_dim=3, n_layers=2, n_hidden=32, n_head=4, slice_num=8,
+                       use_te=False).double()
+    fx = torch.randn(1, 10 * world, 2, dtype=torch.float64)
+    emb = torch.randn(1, 10 * world, 3, dtype=torch.float64)
+
+    class Wrap(torch.nn.Module):
+        def __init__(self, m):
+            super().__init__()
+            self.m = m
+
+        def forward(self, fx, emb):
+            return self.m(fx, embedding=emb)
+
+    _numerical_check(mesh, Wrap(model), [fx, emb], [1, 1], tol=1e-8)
+
+
+def test_ring_attention_and_transolver_two_ranks():
+    run_ranks(_attention_and_transolver, world=2)
+
+
+def _redistribute_and_scatter(rank, world):
+    from physicsnemo_b200.distributed import DistributedManager
+    from physicsnemo_b200.parallel import Partial, Replicate, Shard, ShardTensor, scatter_tensor, sync_module_over_mesh
+
+    mesh = DistributedManager().initialize_mesh((world,), ("domain",))
+    torch.manual_seed(0)
+    full = torch.randn(5, 7, 4)
+    st = scatter_tensor(full if rank == 0 else None, 0, mesh, (Shard(1),))
+    assert tuple(st.shape) == (5, 7, 4)
+    assert torch.equal(st.full_tensor(), full)
+    moved = st.redistribute(placements=[Shard(0)])
+    assert torch.equal(moved.full_tensor(), full) and moved.placements[0] == Shard(0)
+    part = ShardTensor.from_local(torch.ones(3) * (rank + 1), mesh, [Partial("sum")])
+    assert torch.equal(part.full_tensor(), torch.ones(3) * sum(range(1, world + 1)))
+    s = st.sum(dim=1)
+    assert isinstance(s.placements[0], Partial) and torch.allclose(s.full_tensor(), full.sum(1), atol=1e-5)
+    assert abs(st.mean().item() - full.mean().item()) < 1e-6
+    assert torch.allclose(st.amax(dim=1).full_tensor(), full.amax(1))
+    lin = torch.nn.Linear(4, 4)
+    sync_module_over_mesh(lin, mesh, verify=True)
+    w = lin.weight.detach().clone()
+    dist.broadcast(w, src=0)
+    assert torch.equal(w, lin.weight)
+
+
+def test_redistribute_scatter_sync_three_ranks():
+    run_ranks(_redistribute_and_scatter, world=3)
