@@ -96,8 +96,11 @@ class TransolverBlock(nn.Module):
             self.ln_mlp2 = nn.Sequential(LayerNorm(hidden_dim), nn.Linear(hidden_dim, out_dim))
 
     def forward(self, fx: torch.Tensor) -> torch.Tensor:
-        fx = self.Attn(self.ln_1(fx), residual=fx)
-        fx = self.ln_mlp1[1](self.ln_mlp1[0](fx), residual=fx)
+        ln1, ln2 = self.ln_1, self.ln_mlp1[0]
+        xn, skip = ops.layer_norm(fx, ln1.weight, ln1.bias, ln1.eps, return_residual=True)
+        fx = self.Attn(xn, residual=skip)
+        xn, skip = ops.layer_norm(fx, ln2.weight, ln2.bias, ln2.eps, return_residual=True)
+        fx = self.ln_mlp1[1](xn, residual=skip)
         if self.last_layer:
             h = self.ln_mlp2[0](fx)
             lin = self.ln_mlp2[1]

@@ -18,7 +18,7 @@ from . import gemm as _g
 
 class _LayerNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x2d, gamma, beta, eps, post=None):
+    def forward(ctx, x2d, gamma, beta, eps, post=None, alias_out=False):
         lib = _lib.load(required=True)
         M, C = x2d.shape
         y = torch.empty_like(x2d)
@@ -36,12 +36,17 @@ class _LayerNormFn(torch.autograd.Function):
         ctx.has_beta = beta is not None
         ctx.has_post = post is not None
         ctx.param_dtype = gamma.dtype
+        ctx.alias_out = alias_out
+        if alias_out:
+            return y, x2d.view_as(x2d)
         return y
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dalias=None):
         lib = _lib.load(required=True)
         x2d, g32, mean, rstd = ctx.saved_tensors
+        if dalias is not None:
+            dalias = dalias.contiguous()
         M, C = x2d.shape
         dy = dy.contiguous()
         dx = torch.empty_like(x2d)
@@ -50,21 +55,27 @@ class _LayerNormFn(torch.autograd.Function):
         nfl = lib.pnm_layernorm_bwd_scratch_floats(M, C)
         scratch = torch.empty((nfl,), dtype=torch.float32, device=x2d.device)
         code = lib.pnm_layernorm_bwd(dy.data_ptr(), x2d.data_ptr(), g32.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
-                                     None, dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(), scratch.data_ptr(),
-                                     M, C, _g._stream())
+                                     None if dalias is None else dalias.data_ptr(), dx.data_ptr(), dgamma.data_ptr(),
+                                     dbeta.data_ptr(), scratch.data_ptr(), M, C, _g._stream())
         _g._check(code, "pnm_layernorm_bwd")
         _g.launch_count += 2
         return (dx, dgamma.to(ctx.param_dtype), (dbeta.to(ctx.param_dtype) if ctx.has_beta else None), None,
-                dy if ctx.has_post else None)
+                dy if ctx.has_post else None, None)
 
 
 def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float = 1e-5,
-               post: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """LayerNorm over the last dimension; ``post`` (same shape) is added to the result."""
+               post: Optional[torch.Tensor] = None, return_residual: bool = False):
+    """LayerNorm over the last dimension; ``post`` (same shape) is added to the result.
+
+    ``return_residual=True`` returns ``(LN(x), x')`` where ``x'`` is ``x`` itself, routed through the
+    same autograd node: a pre-norm residual block that consumes ``x'`` as its skip connection gets the
+    sum of the two gradient paths from the LayerNorm backward kernel instead of a separate add.
+    """
     C = x.shape[-1]
     if not _g.fused_path_enabled(x) or C % 8 or C > 1024:
         y = F.layer_norm(x, (C,), weight, bias, eps)
-        return y if post is None else y + post
+        y = y if post is None else y + post
+        return (y, x) if return_residual else y
     x2 = x.reshape(-1, C)
     if x2.dtype != torch.bfloat16:
         x2 = x2.to(torch.bfloat16)
@@ -75,4 +86,7 @@ def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
         if p2.dtype != torch.bfloat16:
             p2 = p2.to(torch.bfloat16)
         p2 = p2.contiguous()
+    if return_residual:
+        y, alias = _LayerNormFn.apply(x2, weight, bias, eps, p2, True)
+        return y.reshape(x.shape), alias.reshape(x.shape)
     return _LayerNormFn.apply(x2, weight, bias, eps, p2).reshape(x.shape)
