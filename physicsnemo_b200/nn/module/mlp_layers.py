@@ -67,19 +67,29 @@ class Mlp(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if not (self._fusable and ops.fused_path_enabled(x)):
             return self.layers(x)
+        # maximal runs of Linear(+activation) go through one fused chain, so that the activation
+        # derivative is applied inside the next layer's input-gradient GEMM
         mods = list(self.layers)
         i = 0
+        ws, bs, acts = [], [], []
+
+        def flush(h):
+            if ws:
+                h = ops.mlp_chain(h, list(ws), list(bs), list(acts))
+                ws.clear(), bs.clear(), acts.clear()
+            return h
+
         while i < len(mods):
             m = mods[i]
             if isinstance(m, nn.Linear):
                 code = 0
-                if i + 1 < len(mods):
+                if i + 1 < len(mods) and not isinstance(mods[i + 1], (nn.Dropout, nn.Linear)):
                     c = activation_code(mods[i + 1])
-                    if c is not None and c != 0 and not isinstance(mods[i + 1], nn.Dropout):
+                    if c:
                         code = c
-                x = ops.linear(x, m.weight, m.bias, act=code)
+                ws.append(m.weight), bs.append(m.bias), acts.append(code)
                 i += 2 if code else 1
             else:
-                x = m(x)
+                x = m(flush(x))
                 i += 1
-        return x
+        return flush(x)

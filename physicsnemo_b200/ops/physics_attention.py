@@ -137,12 +137,13 @@ def physics_attention_irregular(mod, x: torch.Tensor, residual: torch.Tensor | N
     B, N, C = x.shape
     outs = []
     for b in range(B):  # slice tokens are per sample; B is 1 in the point-cloud recipes
-        xb = x[b]
+        # a view when B == 1: the backward of a select would zero-fill and copy the whole gradient
+        xb = x.reshape(N, C) if B == 1 else x[b]
         if xb.dtype != torch.bfloat16:
             xb = xb.to(torch.bfloat16)
         rb = None
         if residual is not None:
-            rb = residual[b]
+            rb = residual.reshape(N, C) if B == 1 else residual[b]
             if rb.dtype != torch.bfloat16:
                 rb = rb.to(torch.bfloat16)
             rb = rb.contiguous()
