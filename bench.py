@@ -132,12 +132,13 @@ def run_ours(args, rank, world, dev):
     import physicsnemo_b200  # noqa: F401
     from physicsnemo_b200 import ops
     from physicsnemo_b200.models.transolver import Transolver
+    from physicsnemo_b200.optim import FusedAdam
     from physicsnemo_b200.parallel.point_parallel import PointParallel
 
     torch.manual_seed(1234)
     model = Transolver(**CFG).to(dev)
     pp = PointParallel(model) if world > 1 else None
-    opt = torch.optim.Adam(model.parameters(), lr=1e-3, fused=True)
+    opt = FusedAdam(model.parameters(), lr=1e-3)
     n_local = N_POINTS // world
     xyz, nrm, tgt = make_ellipsoid_cloud(N_POINTS, seed=0)
     sl = slice(rank * n_local, (rank + 1) * n_local if rank < world - 1 else N_POINTS)

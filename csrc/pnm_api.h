@@ -44,6 +44,12 @@ int pnm_peer_allreduce(const float* in, float* out, long long n, float scale, in
 int pnm_peer_flag_bytes();
 int pnm_peer_wait_probe(const void* flag, unsigned int expect, double budget_s, int* status_out, void* stream);
 
+// Multi-tensor Adam / AdamW over a device table of tensors (layout in optim.cu); fp32 parameters and moments.
+int pnm_opt_chunk();
+int pnm_adam_multi(const void* entries, const void* blocks, int n_blocks, float lr, float b1, float b2, float eps,
+                   float wd, float step_size, float inv_bc2_sqrt, int decoupled, float grad_scale, void* stream);
+int pnm_grad_sqnorm_multi(const void* entries, const void* blocks, int n_blocks, float* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
