@@ -50,6 +50,19 @@ int pnm_adam_multi(const void* entries, const void* blocks, int n_blocks, float 
                    float wd, float step_size, float inv_bc2_sqrt, int decoupled, float grad_scale, void* stream);
 int pnm_grad_sqnorm_multi(const void* entries, const void* blocks, int n_blocks, float* out, void* stream);
 
+// Periodic stencil programs (layout in stencil.cu): gradients, divergence, curl, Laplacians and their transposes.
+int pnm_stencil_max_terms();
+int pnm_stencil_program_bytes();
+int pnm_stencil_apply(const void* in, void* out, const void* tables, const void* prog_host, int dtype, void* stream);
+
+// Mesh gradient reconstruction (mesh_grad.cu). backward != 0 runs the transposed pass for the values
+// (vals = upstream gradient [n, D, C], out = dvals [n, C], zero-initialised by the caller).
+int pnm_mesh_lsq_gradient(const float* pts, const float* vals, const long long* offs, const long long* nbr, float* out,
+                          long long n, int D, int C, float weight_power, float eps, int min_neighbors, int backward,
+                          void* stream);
+int pnm_mesh_green_gauss(const float* a, const long long* idx, const float* vals, float* out, long long n_cells, int D,
+                         int C, int mode, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
