@@ -63,6 +63,24 @@ int pnm_mesh_lsq_gradient(const float* pts, const float* vals, const long long* 
 int pnm_mesh_green_gauss(const float* a, const long long* idx, const float* vals, float* out, long long n_cells, int D,
                          int C, int mode, void* stream);
 
+// Grid <-> point interpolation (interp.cu): gather (scatter == 0) or atomic scatter of point values onto the grid.
+int pnm_interp(const float* pts, const float* src, float* dst, const float* grid_desc, const int* n, int dims, int type,
+               long long npts, int C, int scatter, void* stream);
+
+// Neighbour queries (neighbors.cu). Points are pre-sorted by cell of a uniform grid; `order` maps sorted -> original.
+int pnm_radius_count(const float* pts_sorted, const int* cell_start, const int* cell_end, const float* queries,
+                     int* counts, const float* lo, float cell, const int* n, int nq, float radius, void* stream);
+int pnm_radius_fill(const float* pts_sorted, const int* order, const int* cell_start, const int* cell_end,
+                    const float* queries, const long long* offsets, long long* pairs, long long total, const float* lo,
+                    float cell, const int* n, int nq, float radius, void* stream);
+int pnm_radius_topk(const float* pts_sorted, const int* order, const int* cell_start, const int* cell_end,
+                    const float* queries, long long* idx, float* d2, const float* lo, float cell, const int* n, int nq,
+                    int K, float radius, void* stream);
+int pnm_knn_max_k();
+int pnm_knn(const float* pts, const float* queries, long long* idx, float* dist, int np, int nq, int D, int K, void* stream);
+// Farthest point sampling, one CTA per cloud; scratch: [B, N] floats; out: [B, S] int64, column 0 preset to the first sample.
+int pnm_fps(const float* pts, float* scratch, long long* out, int B, int N, int S, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
