@@ -68,3 +68,58 @@ class UNetAttention(torch.nn.Module):
         attn = torch.nn.functional.scaled_dot_product_attention(q, k, v, scale=1 / math.sqrt(k.shape[-1]))
         attn = attn.transpose(-1, -2)
         return self.proj(attn.reshape(*x.shape)) + x
+
+
+class _EarthAttention(torch.nn.Module):
+    """Window attention with the earth-specific position bias of Pangu-Weather.
+
+    Parity: ``physicsnemo/nn/module/attention_layers.py:181-394`` (``EarthAttention3D`` / ``EarthAttention2D``).
+    Input ``[B·n_lon, n_windows, N, C]``; the bias table holds one entry per (absolute pressure / latitude pair,
+    relative longitude) and per *type of window* (pressure–latitude window position).  Bias and the
+    shifted-window mask are folded into one additive mask of a single fused scaled-dot-product call.
+    """
+
+    _ndim = 3
+
+    def __init__(self, dim, input_resolution, window_size, num_heads, qkv_bias=True, qk_scale=None, attn_drop=0.0,
+                 proj_drop=0.0):
+        super().__init__()
+        from .utils import get_earth_position_index
+
+        self.dim, self.window_size, self.num_heads = dim, window_size, num_heads
+        self.scale = qk_scale or (dim // num_heads) ** -0.5
+        *abs_w, w_lon = window_size
+        self.type_of_windows, table = 1, 2 * w_lon - 1
+        for n, w in zip(input_resolution, abs_w):
+            self.type_of_windows *= n // w
+            table *= w * w
+        self.earth_position_bias_table = torch.nn.Parameter(torch.zeros(table, self.type_of_windows, num_heads))
+        self.register_buffer("earth_position_index", get_earth_position_index(window_size, ndim=self._ndim))
+        self.qkv = torch.nn.Linear(dim, dim * 3, bias=qkv_bias)
+        self.attn_drop = torch.nn.Dropout(attn_drop)
+        self.proj = torch.nn.Linear(dim, dim)
+        self.proj_drop = torch.nn.Dropout(proj_drop)
+        torch.nn.init.trunc_normal_(self.earth_position_bias_table, std=0.02)
+        self.softmax = torch.nn.Softmax(dim=-1)
+
+    def forward(self, x: torch.Tensor, mask=None):
+        B_, nW, N, C = x.shape
+        H = self.num_heads
+        q, k, v = self.qkv(x).reshape(B_, nW, N, 3, H, C // H).permute(3, 0, 4, 1, 2, 5)      # [B_, H, nW, N, d]
+        bias = self.earth_position_bias_table[self.earth_position_index.view(-1)].view(N, N, self.type_of_windows, H)
+        bias = bias.permute(3, 2, 0, 1).unsqueeze(0)                                           # [1, H, nW, N, N]
+        if mask is not None:
+            n_lon = mask.shape[0]
+            bias = (bias.unsqueeze(1) + mask[None, :, None]).expand(B_ // n_lon, -1, -1, -1, -1, -1).reshape(B_, H, nW, N, N)
+        out = torch.nn.functional.scaled_dot_product_attention(
+            q, k, v, attn_mask=bias.to(q.dtype), dropout_p=self.attn_drop.p if self.training else 0.0, scale=self.scale)
+        out = out.permute(0, 2, 3, 1, 4).reshape(B_, nW, N, C)
+        return self.proj_drop(self.proj(out))
+
+
+class EarthAttention3D(_EarthAttention):
+    _ndim = 3
+
+
+class EarthAttention2D(_EarthAttention):
+    _ndim = 2
