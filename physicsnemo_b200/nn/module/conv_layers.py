@@ -95,16 +95,18 @@ class CubeEmbedding(nn.Module):
 
 
 class ConvBlock(nn.Module):
-    """Up / down / same-resolution conv followed by ``num_residuals`` pre-activation residual units."""
+    """Up (``upsample=1``) / down (``-1``) / same-resolution (``0``) conv followed by ``num_residuals`` conv-GroupNorm-SiLU units with one skip."""
 
     def __init__(self, in_chans, out_chans, num_groups, num_residuals=2, upsample=0):
         super().__init__()
         if upsample == 1:
             self.conv = nn.ConvTranspose2d(in_chans, out_chans, kernel_size=2, stride=2)
-        elif upsample == 0:
+        elif upsample == -1:
             self.conv = nn.Conv2d(in_chans, out_chans, kernel_size=(3, 3), stride=2, padding=1)
-        elif upsample == 2:
-            self.conv = nn.Conv2d(in_chans, out_chans, kernel_size=3, stride=1, padding=1)
+        elif upsample == 0:
+            self.conv = nn.Conv2d(in_chans, out_chans, kernel_size=(3, 3), stride=1, padding=1)
+        else:
+            raise ValueError("upsample must be 1 (transpose conv x2), -1 (stride-2 conv) or 0 (same resolution)")
         blk = []
         for _ in range(num_residuals):
             blk += [nn.Conv2d(out_chans, out_chans, kernel_size=3, stride=1, padding=1),

@@ -226,7 +226,7 @@ class _SwinBlock(nn.Module):
                 for wsl in (slice(0, -self.ws[1]), slice(-self.ws[1], -self.shift[1] or None), slice(-self.shift[1] or W, None)):
                     lab[:, hs, wsl, :] = cnt
                     cnt += 1
-            win = self._part(lab).view(-1, self.ws[0] * self.ws[1])
+            win = self._part(lab).reshape(-1, self.ws[0] * self.ws[1])
             diff = win[:, None, :] - win[:, :, None]
             mask = torch.where(diff != 0, torch.full_like(diff, -100.0), torch.zeros_like(diff))
         self.register_buffer("attn_mask", mask, persistent=False)
@@ -242,7 +242,7 @@ class _SwinBlock(nn.Module):
         y = self.norm1(x)
         if any(self.shift):
             y = torch.roll(y, shifts=(-self.shift[0], -self.shift[1]), dims=(1, 2))
-        win = self._part(y).view(-1, wh * ww, C)
+        win = self._part(y).reshape(-1, wh * ww, C)
         win = self.attn(win, self.attn_mask).view(B, H // wh, W // ww, wh, ww, C).permute(0, 1, 3, 2, 4, 5).reshape(B, H, W, C)
         if any(self.shift):
             win = torch.roll(win, shifts=self.shift, dims=(1, 2))
