@@ -10,6 +10,8 @@ from __future__ import annotations
 
 from typing import List
 
+import math
+
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
@@ -125,130 +127,151 @@ def _convnd(dimension, transposed=False):
     return table[dimension][1 if transposed else 0]
 
 
-class ConvLayer(nn.Module):
-    """N-d convolution with "same"-style exact padding for strided inputs + optional activation."""
+def _get_same_padding(x: int, k: int, s: int) -> int:
+    """Total zero padding that makes a stride-``s`` kernel-``k`` convolution cover ``ceil(x / s)`` outputs."""
+    return max(s * math.ceil(x / s) - s - x + k, 0)
 
-    def __init__(self, in_channels: int, out_channels: int, kernel_size: int, dimension: int, stride: int = 1,
-                 activation_fn: nn.Module = nn.Identity()):
+
+def _same_pads(sizes, k, s):
+    """``F.pad`` argument (innermost axis first) for "same" padding of the trailing spatial ``sizes``."""
+    out = []
+    for n in reversed(sizes):
+        p = _get_same_padding(n, k, s)
+        out += [p // 2, p - p // 2]
+    return out
+
+
+class ConvLayer(nn.Module):
+    """N-d convolution with TensorFlow-style "same" padding (output ``ceil(n / stride)``) and optional activation.
+
+    Parity: ``physicsnemo/nn/module/conv_layers.py`` ``ConvLayer`` (argument order ``in, out, dimension, kernel, stride``).
+    """
+
+    def __init__(self, in_channels: int, out_channels: int, dimension: int, kernel_size: int, stride: int = 1,
+                 activation_fn: nn.Module = nn.Identity()) -> None:
         super().__init__()
         self.in_channels, self.out_channels, self.kernel_size = in_channels, out_channels, kernel_size
         self.stride, self.dimension, self.activation_fn = stride, dimension, activation_fn
         self.conv = _convnd(dimension)(in_channels, out_channels, kernel_size, stride, bias=True)
-        self.reset_parameters()
+        self._reset_parameters()
 
-    def exec_activation_fn(self, x):
+    def _exec_activation_fn(self, x):
         return self.activation_fn(x)
 
-    def reset_parameters(self):
+    def _reset_parameters(self) -> None:
         nn.init.constant_(self.conv.bias, 0)
         nn.init.xavier_uniform_(self.conv.weight)
 
     def forward(self, x):
-        input_length = len(x.size()) - 2
-        if input_length != self.dimension:
-            raise ValueError("Input dimension not compatible")
-        pads = []
-        for i in range(1, input_length + 1):
-            iw = x.size(-i)
-            pad = max((-(-iw // self.stride) - 1) * self.stride + (self.kernel_size - 1) + 1 - iw, 0)
-            pads += [pad // 2, pad - pad // 2]
-        x = F.pad(x, pads, mode="constant", value=0.0)
-        x = self.conv(x)
-        if self.activation_fn is not nn.Identity():
-            x = self.exec_activation_fn(x)
+        if x.ndim - 2 != self.dimension:
+            raise ValueError(f"Expected {self.dimension}D input tensor (excluding batch and channel dims), "
+                             f"got {x.ndim - 2}D tensor with shape {tuple(x.shape)}")
+        x = self.conv(F.pad(x, _same_pads(x.shape[2:], self.kernel_size, self.stride)))
+        if not isinstance(self.activation_fn, nn.Identity):
+            x = self._exec_activation_fn(x)
         return x
 
 
 class TransposeConvLayer(nn.Module):
-    """N-d transposed convolution cropped to ``stride ×`` the input size + optional activation."""
+    """N-d transposed convolution whose output is cropped by the "same" padding of the input size."""
 
-    def __init__(self, in_channels: int, out_channels: int, kernel_size: int, dimension: int, stride: int = 1,
-                 activation_fn=nn.Identity()):
+    def __init__(self, in_channels: int, out_channels: int, dimension: int, kernel_size: int, stride: int = 1,
+                 activation_fn=nn.Identity()) -> None:
         super().__init__()
         self.in_channels, self.out_channels, self.kernel_size = in_channels, out_channels, kernel_size
         self.stride, self.dimension, self.activation_fn = stride, dimension, activation_fn
         self.trans_conv = _convnd(dimension, True)(in_channels, out_channels, kernel_size, stride, bias=True)
-        self.reset_parameters()
+        self._reset_parameters()
 
-    def exec_activation_fn(self, x):
+    def _exec_activation_fn(self, x):
         return self.activation_fn(x)
 
-    def reset_parameters(self):
+    def _reset_parameters(self) -> None:
         nn.init.constant_(self.trans_conv.bias, 0)
         nn.init.xavier_uniform_(self.trans_conv.weight)
 
     def forward(self, x):
-        orig = x.size()
-        input_length = len(orig) - 2
-        if input_length != self.dimension:
-            raise ValueError("Input dimension not compatible")
+        if x.ndim - 2 != self.dimension:
+            raise ValueError(f"Expected {self.dimension}D input tensor (excluding batch and channel dims), "
+                             f"got {x.ndim - 2}D tensor with shape {tuple(x.shape)}")
+        sizes = x.shape[2:]
         x = self.trans_conv(x)
         sl = [slice(None), slice(None)]
-        for i in range(input_length):
-            pad = x.size(2 + i) - orig[2 + i] * self.stride
-            lo = pad // 2
-            sl.append(slice(lo, x.size(2 + i) - (pad - lo)))
+        for a, n in enumerate(sizes):
+            p = _get_same_padding(n, self.kernel_size, self.stride)
+            sl.append(slice(p // 2, x.size(2 + a) - (p - p // 2)))
         x = x[tuple(sl)]
-        if self.activation_fn is not nn.Identity():
-            x = self.exec_activation_fn(x)
+        if not isinstance(self.activation_fn, nn.Identity):
+            x = self._exec_activation_fn(x)
         return x
 
 
 class ConvGRULayer(nn.Module):
     """Convolutional GRU cell: ``forward(x, hidden) -> next hidden``."""
 
-    def __init__(self, in_features: int, hidden_size: int, dimension: int, activation_fn: nn.Module = nn.ReLU()):
+    def __init__(self, in_features: int, hidden_size: int, dimension: int, activation_fn: nn.Module = nn.ReLU()) -> None:
         super().__init__()
         self.in_features, self.hidden_size, self.activation_fn = in_features, hidden_size, activation_fn
-        self.conv_1 = ConvLayer(in_features + hidden_size, 2 * hidden_size, 3, dimension=dimension)
-        self.conv_2 = ConvLayer(in_features + hidden_size, hidden_size, 3, dimension=dimension)
+        self.conv_1 = ConvLayer(in_features + hidden_size, 2 * hidden_size, dimension, kernel_size=3, stride=1)
+        self.conv_2 = ConvLayer(in_features + hidden_size, hidden_size, dimension, kernel_size=3, stride=1)
 
-    def exec_activation_fn(self, x):
+    def _exec_activation_fn(self, x):
         return self.activation_fn(x)
 
     def forward(self, x, hidden):
-        concat = torch.cat((x, hidden), dim=1)
-        conv_concat = self.conv_1(concat)
-        conv_r, conv_z = torch.split(conv_concat, self.hidden_size, 1)
-        reset_gate = torch.special.expit(conv_r)
-        update_gate = torch.special.expit(conv_z)
-        concat = torch.cat((x, torch.mul(hidden, reset_gate)), dim=1)
-        n = self.exec_activation_fn(self.conv_2(concat))
-        return torch.mul((1 - update_gate), n) + torch.mul(update_gate, hidden)
+        if not torch.compiler.is_compiling():
+            if x.shape[1] != self.in_features:
+                raise ValueError(f"Expected input with {self.in_features} features, got {x.shape[1]} features in tensor with shape {tuple(x.shape)}")
+            if hidden.shape[1] != self.hidden_size:
+                raise ValueError(f"Expected hidden state with {self.hidden_size} features, got {hidden.shape[1]} features in tensor with shape {tuple(hidden.shape)}")
+            if x.shape[0] != hidden.shape[0] or x.shape[2:] != hidden.shape[2:]:
+                raise ValueError("Input and hidden state must have matching batch size and spatial dims. "
+                                 f"Got input shape {tuple(x.shape)} and hidden shape {tuple(hidden.shape)}")
+        r, z = torch.split(self.conv_1(torch.cat((x, hidden), dim=1)), self.hidden_size, 1)
+        r, z = torch.sigmoid(r), torch.sigmoid(z)
+        n = self._exec_activation_fn(self.conv_2(torch.cat((x, hidden * r), dim=1)))
+        return (1 - z) * n + z * hidden
 
 
 class ConvResidualBlock(nn.Module):
-    """Two-conv residual block with optional gating, layer norm and strided skip projection."""
+    """Pre-activation two-conv residual block; optional GLU-style gating and parameter-free layer norm.  A stride-2
+    block uses a 4-wide first kernel; its skip path is a "same"-padded 2×2 average pool, and extra output
+    channels are zero-padded in front (no skip parameters)."""
 
     def __init__(self, in_channels: int, out_channels: int, dimension: int, stride: int = 1, gated: bool = False,
                  layer_normalization: bool = False, begin_activation_fn: bool = True,
-                 activation_fn: nn.Module = nn.ReLU()):
+                 activation_fn: nn.Module = nn.ReLU()) -> None:
         super().__init__()
         self.in_channels, self.out_channels, self.stride, self.dimension = in_channels, out_channels, stride, dimension
         self.gated, self.layer_normalization = gated, layer_normalization
         self.begin_activation_fn, self.activation_fn = begin_activation_fn, activation_fn
-        self.conv_1 = ConvLayer(in_channels, out_channels, 3, dimension, stride)
-        self.conv_2 = ConvLayer(out_channels, 2 * out_channels if gated else out_channels, 3, dimension, 1)
-        if stride > 1 or in_channels != out_channels:
-            self.skip = ConvLayer(in_channels, out_channels, 1, dimension, stride)
-        else:
-            self.skip = None
+        if stride not in (1, 2):
+            raise ValueError("stride > 2 is not supported")
+        self.conv_1 = ConvLayer(in_channels, out_channels, dimension, kernel_size=3 if stride == 1 else 4, stride=stride)
+        self.conv_2 = ConvLayer(out_channels, 2 * out_channels if gated else out_channels, dimension, kernel_size=3, stride=1)
 
-    def exec_activation_fn(self, x):
+    def _exec_activation_fn(self, x):
         return self.activation_fn(x)
 
     def _ln(self, x):
         return F.layer_norm(x, x.size()[1:]) if self.layer_normalization else x
 
     def forward(self, x):
-        orig = x
+        if not torch.compiler.is_compiling() and x.ndim - 2 != self.dimension:
+            raise ValueError(f"Expected {self.dimension}D input tensor (excluding batch and channel dims), "
+                             f"got {x.ndim - 2}D tensor with shape {tuple(x.shape)}")
+        skip = x
         if self.begin_activation_fn:
-            x = self.exec_activation_fn(self._ln(x))
-        x = self.conv_1(x)
-        x = self.exec_activation_fn(self._ln(x))
+            x = self._exec_activation_fn(self._ln(x))
+        x = self._exec_activation_fn(self._ln(self.conv_1(x)))
         x = self.conv_2(x)
         if self.gated:
-            x_1, x_2 = torch.split(x, x.size(1) // 2, 1)
-            x = x_1 * torch.special.expit(x_2)
-        skip = self.skip(orig) if self.skip is not None else orig
+            a, b = torch.split(x, x.size(1) // 2, 1)
+            x = a * torch.sigmoid(b)
+        if skip.size(-1) > x.size(-1):
+            pads = tuple(_get_same_padding(n, 2, 2) // 2 for n in skip.shape[2:])
+            pool = (F.avg_pool1d, F.avg_pool2d, F.avg_pool3d)[self.dimension - 1]
+            skip = pool(skip, 2, 2, padding=pads, count_include_pad=False)
+        if self.out_channels > skip.size(1):
+            skip = F.pad(skip, (0, 0) * (skip.ndim - 2) + (self.out_channels - self.in_channels, 0))
         return skip + x
