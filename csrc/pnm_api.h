@@ -81,6 +81,13 @@ int pnm_knn(const float* pts, const float* queries, long long* idx, float* dist,
 // Farthest point sampling, one CTA per cloud; scratch: [B, N] floats; out: [B, S] int64, column 0 preset to the first sample.
 int pnm_fps(const float* pts, float* scratch, long long* out, int B, int N, int S, void* stream);
 
+// PDE data generators (pde_darcy.cu, pde_kh.cu): each solve / simulation is one cooperative launch.
+int pnm_darcy_permeability(const float* fourier, float* perm, int B, int res, int nf, float kmin, float kmax, void* stream);
+int pnm_darcy_solve(float* u0, float* u1, const float* perm, unsigned int* residual, int B, int res, int levels,
+                    int max_iterations, int check_every, float threshold, void* stream);
+int pnm_kh_simulate(float* cons, float* faces, const float* w, float* snap_rho, float* snap_vel, float* snap_p, int B, int N,
+                    int nfreq, int snapshots, int steps_per_snapshot, float gamma, float dx, float dt, float sigma, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
