@@ -88,6 +88,15 @@ int pnm_darcy_solve(float* u0, float* u1, const float* perm, unsigned int* resid
 int pnm_kh_simulate(float* cons, float* faces, const float* w, float* snap_rho, float* snap_vel, float* snap_p, int B, int N,
                     int nfreq, int snapshots, int steps_per_snapshot, float gamma, float dx, float dt, float sigma, void* stream);
 
+// Triangle-mesh queries over an implicit BVH (bvh.cu): bounds [2L-1, 2, 3], order [L] (triangle per leaf, -1 = padding),
+// tris [F, 3, 3]. Misses: NaN distance / point and face -1 (closest), inf distance and face -1 (ray cast).
+int pnm_bvh_closest(const float* bounds, const int* order, const float* tris, const float* queries, float* out_dist,
+                    float* out_point, long long* out_face, int n_leaves, long long nq, float max_dist, void* stream);
+int pnm_bvh_raycast(const float* bounds, const int* order, const float* tris, const float* origins, const float* dirs,
+                    float* out_t, long long* out_face, float* out_uv, int n_leaves, long long nr, float max_distance,
+                    void* stream);
+int pnm_winding_number(const float* tris, const float* queries, float* out, long long n_tris, long long nq, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

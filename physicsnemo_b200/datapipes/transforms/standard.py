@@ -388,7 +388,7 @@ class ComputeSDF(Transform):
         verts, faces = _need(data, self.mesh_coords_key), _need(data, self.mesh_faces_key)
         upd = {}
         for i, k in enumerate(self.input_keys):
-            sdf, closest = signed_distance_field(verts, faces, _need(data, k), use_sign_winding_number=self.use_winding_number)
+            sdf, closest, _ = signed_distance_field(verts, faces, _need(data, k), use_sign_winding_number=self.use_winding_number)
             suffix = "" if len(self.input_keys) == 1 else f"_{k}"
             upd[self.output_key + suffix] = sdf.reshape(-1, 1)
             if self.closest_points_key:

@@ -1,0 +1,9 @@
+"""Simplicial meshes with tensor data: geometry, topology, calculus, generation, spatial queries, IO."""
+from . import io, operations, primitives, spatial
+from .domain_mesh import DomainMesh
+from .fields import RankSpecDict, flatten_rank_spec, rank_counts, ranks_from_tensordict, validate_data_contains_ranks
+from .mesh import MESH_FIELD_ASSOCIATIONS, Adjacency, Mesh, MeshFieldAssociation
+
+__all__ = ["Mesh", "DomainMesh", "Adjacency", "MeshFieldAssociation", "MESH_FIELD_ASSOCIATIONS", "RankSpecDict",
+           "flatten_rank_spec", "rank_counts", "ranks_from_tensordict", "validate_data_contains_ranks", "primitives",
+           "operations", "spatial", "io"]

@@ -1,0 +1,133 @@
+"""Mesh geometry / topology / calculus / generators / IO (CPU) and the BVH kernels against all-pairs search (GPU)."""
+import math
+
+import pytest
+import torch
+
+from physicsnemo_b200.mesh import DomainMesh, Mesh, io, operations as O, primitives as P, spatial as S
+from physicsnemo_b200.nn.functional.geometry import ray_mesh_intersect, signed_distance_field
+
+
+def test_geometry_and_topology():
+    s = P.icosphere(3)
+    assert s.n_manifold_dims == 2 and s.codimension == 1
+    assert abs(float(s.cell_areas.sum()) - 4 * math.pi) < 0.1
+    assert (s.cell_normals * s.cell_centroids).sum(-1).min() > 0.9               # outward
+    assert (s.point_normals * s.points).sum(-1).min() > 0.99
+    rep = O.validate(s)
+    assert rep["is_watertight"] and rep["euler_characteristic"] == 2 and rep["n_boundary_facets"] == 0
+    assert O.validate(P.torus())["euler_characteristic"] == 0
+    assert abs(float(O.enclosed_volume(s)) - 4 / 3 * math.pi) < 0.05
+    assert abs(float(O.enclosed_volume(P.cube_surface(3))) - 1.0) < 1e-5
+    g = P.unit_square(4)
+    assert g.get_boundary_mesh().n_cells == 16 and g.to_edge_graph().n_cells == 16 * 2 + 16 + 8
+    nb = g.facet_neighbors()
+    assert (nb >= 0).sum() == 2 * (g.to_edge_graph().n_cells - 16)
+    c2c = g.get_cell_to_cells_adjacency()
+    assert int(c2c.counts().max()) == 3 and c2c.n_sources == g.n_cells
+    p2p = g.get_point_to_points_adjacency()
+    assert int(p2p.counts().min()) >= 2
+    assert g.to_dual_graph().n_points == g.n_cells
+    b = P.box_volume(2, 3, 2)
+    assert abs(float(b.cell_areas.sum()) - 1.0) < 1e-6 and (torch.linalg.det(b.points[b.cells[:, 1:]] - b.points[b.cells[:, :1]]) > 0).all()
+    assert O.validate(b.get_boundary_mesh())["is_watertight"]
+    with pytest.raises(ValueError):
+        b.cell_normals
+    with pytest.raises(ValueError):
+        Mesh(torch.zeros(3, 2), torch.tensor([[0, 1, 5]]))
+
+
+def test_data_and_editing():
+    g = P.unit_square(6)
+    g = g.with_data(point_data={"f": g.points[:, 0] ** 2 + 3 * g.points[:, 1], "v": g.points.clone()}, cell_data={"c": g.cell_centroids[:, 0]})
+    grad = g.gradient("f")
+    interior = ((g.points > 0.01) & (g.points < 0.99)).all(-1)
+    assert torch.allclose(grad[interior, 0], 2 * g.points[interior, 0], atol=1e-4) and torch.allclose(grad[interior, 1], torch.full_like(grad[interior, 1], 3.0), atol=1e-4)
+    assert torch.allclose(g.laplacian("f")[interior], torch.full((int(interior.sum()),), 2.0), atol=1e-3)
+    assert torch.allclose(g.divergence("v")[interior], torch.full((int(interior.sum()),), 2.0), atol=1e-4)
+    assert g.curl("v")[interior].abs().max() < 1e-4
+    assert torch.allclose(g.point_data_to_cell_data().cell_data["f"], g.point_data["f"][g.cells].mean(1))
+    p = g.cell_data_to_point_data().point_data["c"]
+    assert p.shape == (g.n_points,) and 0 <= p.min() and p.max() <= 1
+    half = g.slice_points(torch.nonzero(g.points[:, 0] <= 0.5).squeeze(1))
+    assert half.n_points == 4 * 7 and half.n_cells == 3 * 6 * 2 and half.point_data["f"].shape[0] == half.n_points
+    merged = Mesh.merge([g, g.translate([1.0, 0.0])])
+    assert merged.n_points == 2 * g.n_points
+    welded = merged.clean(tolerance=1e-6)
+    assert welded.n_points == 2 * g.n_points - 7 and welded.n_cells == merged.n_cells
+    sub = g.subdivide(1)
+    assert sub.n_cells == 4 * g.n_cells and abs(float(sub.cell_areas.sum()) - 1.0) < 1e-6 and "f" in sub.point_data
+    assert P.single_tetrahedron().subdivide(2).n_cells == 64
+    pts, cell = g.sample_points(500, generator=torch.Generator().manual_seed(0))
+    assert pts.shape == (500, 2) and pts.min() >= 0 and pts.max() <= 1
+    smooth = O.laplacian_smooth(P.perturb(g, 0.02, generator=torch.Generator().manual_seed(0)), iterations=20)
+    assert smooth.quality_metrics["shape_quality"].min() > P.perturb(g, 0.02, generator=torch.Generator().manual_seed(0)).quality_metrics["shape_quality"].min()
+    r = g.rotate(math.pi / 2)
+    assert torch.allclose(r.points[:, 0], -g.points[:, 1], atol=1e-6)
+    assert g.pad_to_next_power(2.0).n_points == 64
+    dec = O.cluster_decimate(P.icosphere(3), 0.5)
+    assert 0 < dec.n_points < 642
+    flipped = Mesh(g.points, torch.cat([g.cells[:10].flip(1), g.cells[10:]]))
+    fixed = O.orient_consistently(flipped)
+    n = torch.linalg.det(fixed.points[fixed.cells[:, 1:]] - fixed.points[fixed.cells[:, :1]])
+    assert (n > 0).all() or (n < 0).all()
+
+
+def test_curvature_and_domain(tmp_path):
+    s = P.icosphere(3, radius=2.0)
+    K, H = s.gaussian_curvature_vertices, s.mean_curvature_vertices
+    assert abs(float(K.mean()) - 0.25) < 0.01 and abs(float(H.mean()) - 0.5) < 0.01
+    assert abs(float((K * O.vertex_areas(s)).sum()) - 4 * math.pi) < 1e-3          # Gauss-Bonnet
+    d = DomainMesh.from_interior(P.box_volume(2, 2, 2))
+    d2 = d.split_boundary("boundary", lambda c: c[:, 0] < 1e-6, ("inlet", "walls"))
+    assert set(d2.boundary_names) == {"inlet", "walls"} and d2.boundaries["inlet"].n_cells == 8
+    for name, writer, reader in (("m.obj", io.write_obj, io.read_obj), ("m.stl", io.write_stl, io.read_stl)):
+        writer(s, tmp_path / name)
+        back = reader(tmp_path / name)
+        assert back.n_cells == s.n_cells and abs(float(back.cell_areas.sum() - s.cell_areas.sum())) < 1e-3
+    s.save(tmp_path / "m.pt")
+    assert Mesh.load(tmp_path / "m.pt").n_points == s.n_points
+
+
+def test_sdf_and_rays_torch():
+    s = P.icosphere(3)
+    q = torch.randn(200, 3) * 0.8
+    for wn in (False, True):
+        sdf, cp, face = signed_distance_field(s.points, s.cells, q, use_sign_winding_number=wn)
+        assert (sdf - (q.norm(dim=-1) - 1)).abs().max() < 0.02 and face.min() >= 0
+        assert ((cp - q).norm(dim=-1) - sdf.abs()).abs().max() < 1e-5
+    far = signed_distance_field(s.points, s.cells, torch.tensor([[10.0, 0, 0]]), max_dist=1.0)
+    assert torch.isnan(far[0]).all() and int(far[2]) == -1
+    o = torch.tensor([[0.0, 0, -3], [3.0, 0, -3], [0.2, 0.1, -3]])
+    d = torch.tensor([[0.0, 0, 2], [0, 0, 1.0], [0, 0, 1.0]])
+    hit, t, pt, face, n = ray_mesh_intersect(s.points, s.cells, o, d)
+    assert hit.tolist() == [True, False, True] and abs(float(t[0]) - 2.0) < 0.01 and torch.isinf(t[1]) and int(face[1]) == -1
+    assert (n[0] * torch.tensor([0.0, 0, -1])).sum() > 0.99 and pt[1].abs().sum() == 0
+    bvh = S.BVH(s.points, s.cells)
+    assert bvh.n_leaves == 2048 and bvh.bounds.shape == (4095, 2, 3)
+    assert torch.allclose(bvh.bounds[0, 0], s.points.amin(0)) and torch.allclose(bvh.bounds[0, 1], s.points.amax(0))
+
+
+@pytest.mark.gpu
+def test_bvh_kernels_match_all_pairs():
+    dev = "cuda"
+    m = P.lumpy_sphere(4, generator=torch.Generator().manual_seed(0)).to(dev)
+    q = (torch.rand(20000, 3, device=dev) - 0.5) * 3
+    for wn in (False, True):
+        a = signed_distance_field(m.points, m.cells, q, use_sign_winding_number=wn, implementation="cuda")
+        b = signed_distance_field(m.points, m.cells, q, use_sign_winding_number=wn, implementation="torch")
+        assert (a[0] - b[0]).abs().max() < 1e-4 and (a[1] - b[1]).abs().max() < 1e-3
+        assert (a[2] != b[2]).float().mean() < 0.02                               # ties on shared edges / vertices
+    near = signed_distance_field(m.points, m.cells, q, max_dist=0.05, implementation="cuda")
+    assert torch.isnan(near[0]).any() and (near[0][~torch.isnan(near[0])].abs() <= 0.05 + 1e-6).all()
+    o = torch.cat([(torch.rand(5000, 2, device=dev) - 0.5) * 3, torch.full((5000, 1), -3.0, device=dev)], 1)
+    d = torch.tensor([0.0, 0, 1], device=dev).expand(5000, 3) + 0.1 * torch.randn(5000, 3, device=dev)
+    ha = ray_mesh_intersect(m.points, m.cells, o, d, implementation="cuda")
+    hb = ray_mesh_intersect(m.points, m.cells, o, d, implementation="torch")
+    agree = ha[0] == hb[0]
+    assert agree.float().mean() > 0.999
+    both = ha[0] & hb[0]
+    assert (ha[1][both] - hb[1][both]).abs().max() < 1e-3 and (ha[2][both] - hb[2][both]).abs().max() < 1e-3
+    out = ray_mesh_intersect(m.points, m.cells, o, d, return_bvh=True)
+    again = ray_mesh_intersect(m.points, m.cells, o, d, bvh=out[-1])
+    assert torch.equal(out[3], again[3])
