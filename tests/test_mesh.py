@@ -117,7 +117,13 @@ def test_bvh_kernels_match_all_pairs():
         a = signed_distance_field(m.points, m.cells, q, use_sign_winding_number=wn, implementation="cuda")
         b = signed_distance_field(m.points, m.cells, q, use_sign_winding_number=wn, implementation="torch")
         assert (a[0] - b[0]).abs().max() < 1e-4 and (a[1] - b[1]).abs().max() < 1e-3
-        assert (a[2] != b[2]).float().mean() < 0.02                               # ties on shared edges / vertices
+        # closest points on shared edges / vertices belong to several faces: check the reported face holds the point
+        tri = m.points[m.cells[a[2]]]
+        nrm = torch.linalg.cross(tri[:, 1] - tri[:, 0], tri[:, 2] - tri[:, 0])
+        nrm = nrm / nrm.norm(dim=-1, keepdim=True)
+        assert ((a[1] - tri[:, 0]) * nrm).sum(-1).abs().max() < 1e-4
+        lo, hi = tri.amin(1) - 1e-4, tri.amax(1) + 1e-4
+        assert ((a[1] >= lo) & (a[1] <= hi)).all()
     near = signed_distance_field(m.points, m.cells, q, max_dist=0.05, implementation="cuda")
     assert torch.isnan(near[0]).any() and (near[0][~torch.isnan(near[0])].abs() <= 0.05 + 1e-6).all()
     o = torch.cat([(torch.rand(5000, 2, device=dev) - 0.5) * 3, torch.full((5000, 1), -3.0, device=dev)], 1)
