@@ -13,6 +13,8 @@ from itertools import combinations, product
 
 import torch
 
+from ._stencil import normalize_derivative_orders, validate_mixed
+
 from ....core.function_spec import FunctionSpec
 
 
@@ -86,6 +88,26 @@ def _fd_derivatives(stencil_values, spacing=1.0, order=1, return_mixed_derivs=Fa
     return res.squeeze(-1) if stencil_values.ndim == 2 else res
 
 
+def _by_orders(kernel, name, x, scale, derivative_orders, include_mixed, order, return_mixed_derivs, ndim):
+    """First-derivative rows, then second-derivative rows (then mixed ones), as ``derivative_orders`` asks.
+
+    ``order`` / ``return_mixed_derivs`` are the single-order spelling of the same request.
+    """
+    if order is not None:
+        derivative_orders = order
+    if return_mixed_derivs is not None:
+        include_mixed = return_mixed_derivs
+    orders = normalize_derivative_orders(derivative_orders, name)
+    if ndim is not None:
+        validate_mixed(orders, include_mixed, ndim, name)
+    out = []
+    if 1 in orders:
+        out.append(kernel(x, scale, 1, False))
+    if 2 in orders:
+        out.append(kernel(x, scale, 2, bool(include_mixed)))
+    return out[0] if len(out) == 1 else torch.cat(out, dim=0)
+
+
 class MeshlessFDStencilPoints(FunctionSpec):
     @FunctionSpec.register(name="torch", rank=0, baseline=True)
     def torch_forward(points, spacing=1.0, include_center=True):
@@ -94,8 +116,11 @@ class MeshlessFDStencilPoints(FunctionSpec):
 
 class MeshlessFDDerivatives(FunctionSpec):
     @FunctionSpec.register(name="torch", rank=0, baseline=True)
-    def torch_forward(stencil_values, spacing=1.0, order=1, return_mixed_derivs=False):
-        return _fd_derivatives(stencil_values, spacing, order, return_mixed_derivs)
+    def torch_forward(stencil_values, spacing=1.0, derivative_orders=1, include_mixed=False, order=None,
+                      return_mixed_derivs=None):
+        return _by_orders(_fd_derivatives, "meshless_fd_derivatives", stencil_values, spacing, derivative_orders,
+                          include_mixed, order, return_mixed_derivs,
+                          {3: 1, 9: 2, 27: 3}.get(stencil_values.shape[1]) if stencil_values.ndim >= 2 else None)
 
 
 def _spectral(field, lengths=1.0, order=1, return_mixed_derivs=False):
@@ -131,8 +156,10 @@ def _spectral(field, lengths=1.0, order=1, return_mixed_derivs=False):
 
 class SpectralGridGradient(FunctionSpec):
     @FunctionSpec.register(name="torch", rank=0, baseline=True)
-    def torch_forward(field, lengths=1.0, order=1, return_mixed_derivs=False):
-        return _spectral(field, lengths, order, return_mixed_derivs)
+    def torch_forward(field, lengths=1.0, derivative_orders=1, include_mixed=False, order=None,
+                      return_mixed_derivs=None):
+        return _by_orders(_spectral, "spectral_grid_gradient", field, lengths, derivative_orders, include_mixed, order,
+                          return_mixed_derivs, field.ndim)
 
 
 meshless_fd_stencil_points = MeshlessFDStencilPoints.make_function("meshless_fd_stencil_points")
