@@ -97,6 +97,34 @@ int pnm_bvh_raycast(const float* bounds, const int* order, const float* tris, co
                     void* stream);
 int pnm_winding_number(const float* tris, const float* queries, float* out, long long n_tris, long long nq, void* stream);
 
+// Headless renderers (render.cu). camera = {eye, forward, right, up} as 12 floats; bounds = {min xyz, max xyz};
+// RGBA volumes / colour fields are channels-last float4; outputs rgba [H*W*4], depth [H*W] (3.4e38 = nothing hit),
+// normal [H*W*3].  The splatting renderers need winners [H*W] pre-filled with empty_key.
+int pnm_volume_render(const float* vol, const float* camera, const float* bounds, int W, int H, float step, int max_steps,
+                      float tan_half, float aspect, float opacity_stop, float depth_thr, int nx, int ny, int nz, float* rgba,
+                      float* depth, void* stream);
+int pnm_isosurface_render(const float* field, const float* color_field, const float* camera, const float* bounds,
+                          const float* uniform_color, const float* light, int W, int H, float threshold, float step,
+                          int max_steps, float tan_half, float aspect, float ambient, int has_color_field, int nx, int ny,
+                          int nz, float* rgba, float* depth, float* normal, void* stream);
+int pnm_mesh_raycast_render(const float* bvh_bounds, const int* order, const float* tris, const int* indices, int n_leaves,
+                            const float* colors, const float* camera, const float* uniform_color, const float* light, int W,
+                            int H, float tan_half, float aspect, float max_distance, float ambient, int color_mode,
+                            float* rgba, float* depth, float* normal, void* stream);
+int pnm_point_cloud_render(const float* points, const float* colors, const float* camera, const float* uniform_color, int W,
+                           int H, float tan_half, float aspect, float z_near, float z_far, int point_size, long long n,
+                           float depth_scale, long long empty_key, int has_colors, long long* winners, float* rgba,
+                           float* depth, void* stream);
+int pnm_wireframe_render(const float* edges, const float* camera, const float* uniform_color, int W, int H, float tan_half,
+                         float aspect, float z_near, float z_far, int thickness, long long n, float depth_scale,
+                         long long empty_key, long long* winners, float* rgba, float* depth, void* stream);
+int pnm_line_integral_convolution(const float* vec, const float* seed, float step, int num_steps, float contrast, int nx,
+                                  int ny, int nz, float* out, void* stream);
+int pnm_scalar_field_to_rgba(const float* field, long long n, float vmin, float vmax, float max_opacity,
+                             float opacity_threshold, unsigned char* out, void* stream);
+int pnm_vector_field_to_rgba(const float* vec, const float* lic, long long n, float vmin, float vmax, float max_opacity,
+                             float lic_threshold, unsigned char* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
