@@ -1,0 +1,102 @@
+// Elementwise kernels that have no producer to fuse into.
+//
+// pnm_silu_derivative: out = silu^(k)(x) [* g], k = 0..4, one pass, 16-byte vectors.  The k-th derivative is evaluated
+// in closed form from s = sigmoid(x):  s' = s(1-s), s'' = s'(1-2s), s''' = s''(1-2s) - 2 s'^2,
+// s'''' = s'''(1-2s) - 6 s' s'', and silu^(k) = k s^(k-1) + x s^(k).  Used for higher-order derivatives of
+// physics-informed networks, where autograd would otherwise build a chain of ~10 elementwise launches per order.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "pnm_api.h"
+
+namespace pnm {
+
+template <int K>
+__device__ __forceinline__ float silu_d(float x) {
+  const float s = 1.f / (1.f + __expf(-x));
+  if (K == 0) return x * s;
+  const float d1 = s * (1.f - s);
+  if (K == 1) return s + x * d1;
+  const float t = 1.f - 2.f * s;
+  const float d2 = d1 * t;
+  if (K == 2) return 2.f * d1 + x * d2;
+  const float d3 = d2 * t - 2.f * d1 * d1;
+  if (K == 3) return 3.f * d2 + x * d3;
+  const float d4 = d3 * t - 6.f * d1 * d2;
+  return 4.f * d3 + x * d4;
+}
+
+template <typename T> struct EVec;
+template <> struct EVec<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 u = *reinterpret_cast<const float4*>(p); f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* f) { *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]); }
+  static __device__ __forceinline__ float get(const float* p) { return *p; }
+  static __device__ __forceinline__ void put(float* p, float v) { *p = v; }
+};
+template <> struct EVec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 v = __bfloat1622float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* f) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+  static __device__ __forceinline__ float get(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void put(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
+};
+
+template <typename T, int K>
+__global__ void __launch_bounds__(256) silu_derivative_kernel(const T* __restrict__ x, const T* __restrict__ g, T* __restrict__ out,
+                                                               long long n) {
+  constexpr int V = EVec<T>::N;
+  const long long nvec = n / V, stride = (long long)gridDim.x * blockDim.x;
+  float f[V], m[V];
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += stride) {
+    EVec<T>::load(x + v * V, f);
+    if (g) EVec<T>::load(g + v * V, m);
+#pragma unroll
+    for (int i = 0; i < V; ++i) f[i] = silu_d<K>(f[i]) * (g ? m[i] : 1.f);
+    EVec<T>::store(out + v * V, f);
+  }
+  // ragged tail (n not a multiple of the vector width)
+  for (long long i = nvec * V + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride)
+    EVec<T>::put(out + i, silu_d<K>(EVec<T>::get(x + i)) * (g ? EVec<T>::get(g + i) : 1.f));
+}
+
+template <typename T>
+int launch_silu(const void* x, const void* g, void* out, long long n, int order, cudaStream_t st) {
+  const T* xi = static_cast<const T*>(x);
+  const T* gi = static_cast<const T*>(g);
+  T* o = static_cast<T*>(out);
+  const long long nvec = n / EVec<T>::N + 1;
+  const unsigned grid = (unsigned)min((long long)148 * 16, (nvec + 255) / 256);
+  switch (order) {
+    case 0: silu_derivative_kernel<T, 0><<<grid, 256, 0, st>>>(xi, gi, o, n); break;
+    case 1: silu_derivative_kernel<T, 1><<<grid, 256, 0, st>>>(xi, gi, o, n); break;
+    case 2: silu_derivative_kernel<T, 2><<<grid, 256, 0, st>>>(xi, gi, o, n); break;
+    case 3: silu_derivative_kernel<T, 3><<<grid, 256, 0, st>>>(xi, gi, o, n); break;
+    case 4: silu_derivative_kernel<T, 4><<<grid, 256, 0, st>>>(xi, gi, o, n); break;
+    default: return -1;
+  }
+  return (int)cudaGetLastError();
+}
+
+}  // namespace pnm
+
+extern "C" int pnm_silu_derivative(const void* x, const void* g, void* out, long long n, int order, int dtype, void* stream) {
+  if (n <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(g)) & 15) return -2;
+  cudaStream_t st = (cudaStream_t)stream;
+  return dtype == 0 ? pnm::launch_silu<__nv_bfloat16>(x, g, out, n, order, st) : pnm::launch_silu<float>(x, g, out, n, order, st);
+}

@@ -1,0 +1,449 @@
+// GroupNorm with an optional fused SiLU, forward and backward, for (B, C, *spatial) tensors in either memory format:
+// layout 0 = channels-first (spatial contiguous), layout 1 = channels-last (channels contiguous).  bf16 or fp32 I/O,
+// fp32 statistics.  The spatial extent is split into S slices so that small batches still fill the GPU:
+//
+//   forward   1) slice partials (sum, sum of squares) per (b, slice, group)
+//             2) mean / rstd from the S partials, y = act((x - mean) * rstd * gamma + beta)
+//   backward  1) slice partials per (b, slice, channel): sum of dz * xhat and of dz, dz = dy * act'(z)
+//             2) per-batch channel sums, per-group sums A = sum gamma dz, B = sum gamma dz xhat, dgamma / dbeta
+//             3) dx = rstd * (gamma dz - A/n - xhat B/n)
+//
+// Every access is a 16-byte vector of 8 (bf16) or 4 (fp32) elements.  In the channels-last kernels a thread owns a
+// fixed vector of channels and walks down the pixels, so gamma / beta / scale / shift live in registers.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "pnm_api.h"
+
+namespace pnm {
+
+template <typename T> struct Vec;
+template <> struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 v = __bfloat1622float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* f) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <> struct Vec<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 u = *reinterpret_cast<const float4*>(p);
+    f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* f) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+};
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + __expf(-z)); }
+__device__ __forceinline__ float silu_grad(float z) {
+  const float s = 1.f / (1.f + __expf(-z));
+  return s * (1.f + z * (1.f - s));
+}
+
+__device__ __forceinline__ float2 block_sum2(float a, float b) {
+  __shared__ float2 red[32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o); }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = make_float2(a, b);
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float2 v = l < nw ? red[l] : make_float2(0.f, 0.f);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { v.x += __shfl_xor_sync(0xffffffffu, v.x, o); v.y += __shfl_xor_sync(0xffffffffu, v.y, o); }
+  return v;
+}
+
+struct GNShape { int B, C, G, cpg, S; long long HW; };
+
+// ---------------- channels-first ----------------------------------------------------------------------------------
+// grid (S, B*C): one channel slice per CTA; partial[b][s][c] = (sum x, sum x^2)
+template <typename T>
+__global__ void __launch_bounds__(256) gn_stats_cf(const T* __restrict__ x, float2* __restrict__ partial, GNShape sh) {
+  constexpr int V = Vec<T>::N;
+  const int s = blockIdx.x, bc = blockIdx.y, b = bc / sh.C, c = bc % sh.C;
+  const long long nvec = sh.HW / V, per = (nvec + sh.S - 1) / sh.S, v0 = s * per, v1 = min(nvec, v0 + per);
+  const T* base = x + (long long)bc * sh.HW;
+  float a = 0.f, q = 0.f, f[V];
+  for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+    Vec<T>::load(base + v * V, f);
+#pragma unroll
+    for (int i = 0; i < V; ++i) { a += f[i]; q += f[i] * f[i]; }
+  }
+  const float2 r = block_sum2(a, q);
+  if (threadIdx.x == 0) partial[((long long)b * sh.S + s) * sh.C + c] = r;
+}
+
+// mean / rstd of group g of batch b from the channel partials (call with all threads; result valid in all threads)
+__device__ __forceinline__ float2 group_moments(const float2* __restrict__ partial, const GNShape& sh, int b, int g, float eps) {
+  float a = 0.f, q = 0.f;
+  const int n = sh.S * sh.cpg;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float2 p = partial[((long long)b * sh.S + i / sh.cpg) * sh.C + g * sh.cpg + i % sh.cpg];
+    a += p.x; q += p.y;
+  }
+  const float2 r = block_sum2(a, q);
+  const float cnt = (float)sh.cpg * (float)sh.HW;
+  const float mean = r.x / cnt;
+  return make_float2(mean, rsqrtf(fmaxf(r.y / cnt - mean * mean, 0.f) + eps));
+}
+
+template <typename T, bool kSilu>
+__global__ void __launch_bounds__(256) gn_apply_cf(const T* __restrict__ x, const float2* __restrict__ partial,
+                                                    const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                    T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                    GNShape sh, float eps) {
+  constexpr int V = Vec<T>::N;
+  const int s = blockIdx.x, bc = blockIdx.y, b = bc / sh.C, c = bc % sh.C, g = c / sh.cpg;
+  const float2 m = group_moments(partial, sh, b, g, eps);
+  if (s == 0 && c % sh.cpg == 0 && threadIdx.x == 0) { mean_out[b * sh.G + g] = m.x; rstd_out[b * sh.G + g] = m.y; }
+  const float scale = m.y * gamma[c], shift = beta[c] - m.x * scale;
+  const long long nvec = sh.HW / V, per = (nvec + sh.S - 1) / sh.S, v0 = s * per, v1 = min(nvec, v0 + per);
+  const T* xi = x + (long long)bc * sh.HW;
+  T* yo = y + (long long)bc * sh.HW;
+  float f[V];
+  for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+    Vec<T>::load(xi + v * V, f);
+#pragma unroll
+    for (int i = 0; i < V; ++i) { const float z = f[i] * scale + shift; f[i] = kSilu ? silu_f(z) : z; }
+    Vec<T>::store(yo + v * V, f);
+  }
+}
+
+// backward partials: pc[b][s][c] = (sum dz xhat, sum dz)
+template <typename T, bool kSilu>
+__global__ void __launch_bounds__(256) gn_bwd_stats_cf(const T* __restrict__ x, const T* __restrict__ dy,
+                                                        const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                        const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                        float2* __restrict__ pc, GNShape sh) {
+  constexpr int V = Vec<T>::N;
+  const int s = blockIdx.x, bc = blockIdx.y, b = bc / sh.C, c = bc % sh.C, g = c / sh.cpg;
+  const float mu = mean[b * sh.G + g], rs = rstd[b * sh.G + g], ga = gamma[c], be = beta[c];
+  const long long nvec = sh.HW / V, per = (nvec + sh.S - 1) / sh.S, v0 = s * per, v1 = min(nvec, v0 + per);
+  const T* xi = x + (long long)bc * sh.HW;
+  const T* di = dy + (long long)bc * sh.HW;
+  float a = 0.f, d = 0.f, f[V], e[V];
+  for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+    Vec<T>::load(xi + v * V, f);
+    Vec<T>::load(di + v * V, e);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const float xh = (f[i] - mu) * rs;
+      const float dz = kSilu ? e[i] * silu_grad(xh * ga + be) : e[i];
+      a += dz * xh; d += dz;
+    }
+  }
+  const float2 r = block_sum2(a, d);
+  if (threadIdx.x == 0) pc[((long long)b * sh.S + s) * sh.C + c] = r;
+}
+
+template <typename T, bool kSilu>
+__global__ void __launch_bounds__(256) gn_bwd_apply_cf(const T* __restrict__ x, const T* __restrict__ dy,
+                                                        const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                        const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                        const float2* __restrict__ group_ab, T* __restrict__ dx, GNShape sh) {
+  constexpr int V = Vec<T>::N;
+  const int s = blockIdx.x, bc = blockIdx.y, b = bc / sh.C, c = bc % sh.C, g = c / sh.cpg;
+  const float mu = mean[b * sh.G + g], rs = rstd[b * sh.G + g], ga = gamma[c], be = beta[c];
+  const float inv_n = 1.f / ((float)sh.cpg * (float)sh.HW);
+  const float2 ab = group_ab[b * sh.G + g];
+  const float A = ab.x * inv_n, Bq = ab.y * inv_n;
+  const long long nvec = sh.HW / V, per = (nvec + sh.S - 1) / sh.S, v0 = s * per, v1 = min(nvec, v0 + per);
+  const T* xi = x + (long long)bc * sh.HW;
+  const T* di = dy + (long long)bc * sh.HW;
+  T* o = dx + (long long)bc * sh.HW;
+  float f[V], e[V];
+  for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+    Vec<T>::load(xi + v * V, f);
+    Vec<T>::load(di + v * V, e);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const float xh = (f[i] - mu) * rs;
+      const float dz = kSilu ? e[i] * silu_grad(xh * ga + be) : e[i];
+      f[i] = rs * (ga * dz - A - xh * Bq);
+    }
+    Vec<T>::store(o + v * V, f);
+  }
+}
+
+// ---------------- channels-last -----------------------------------------------------------------------------------
+// grid (S, B); a thread owns channels [c0, c0 + V) and every (blockDim / tpp)-th pixel of the slice
+struct CLThread { int c0, lane_pix, ppi; bool active; long long p0, p1; };
+
+template <int V>
+__device__ __forceinline__ CLThread cl_thread(const GNShape& sh, int s) {
+  CLThread t;
+  const int tpp = sh.C / V;
+  t.ppi = blockDim.x / tpp;
+  t.active = (int)threadIdx.x < t.ppi * tpp;
+  t.c0 = ((int)threadIdx.x % tpp) * V;
+  t.lane_pix = (int)threadIdx.x / tpp;
+  const long long per = (sh.HW + sh.S - 1) / sh.S;
+  t.p0 = s * per;
+  t.p1 = min(sh.HW, t.p0 + per);
+  return t;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) gn_stats_cl(const T* __restrict__ x, float2* __restrict__ partial, GNShape sh) {
+  constexpr int V = Vec<T>::N;
+  extern __shared__ float smem[];                        // [C][2]
+  const int s = blockIdx.x, b = blockIdx.y;
+  for (int i = threadIdx.x; i < 2 * sh.C; i += blockDim.x) smem[i] = 0.f;
+  __syncthreads();
+  const CLThread t = cl_thread<V>(sh, s);
+  float a[V], q[V], f[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) a[i] = q[i] = 0.f;
+  if (t.active) {
+    const T* base = x + (long long)b * sh.HW * sh.C + t.c0;
+    for (long long p = t.p0 + t.lane_pix; p < t.p1; p += t.ppi) {
+      Vec<T>::load(base + p * sh.C, f);
+#pragma unroll
+      for (int i = 0; i < V; ++i) { a[i] += f[i]; q[i] += f[i] * f[i]; }
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i) { atomicAdd(&smem[2 * (t.c0 + i)], a[i]); atomicAdd(&smem[2 * (t.c0 + i) + 1], q[i]); }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < sh.C; c += blockDim.x)
+    partial[((long long)b * sh.S + s) * sh.C + c] = make_float2(smem[2 * c], smem[2 * c + 1]);
+}
+
+// fills smem mom[g] = (mean, rstd) for all groups of batch b
+__device__ __forceinline__ void all_group_moments(const float2* __restrict__ partial, const GNShape& sh, int b, float eps,
+                                                  float2* mom) {
+  for (int g = threadIdx.x; g < sh.G; g += blockDim.x) {
+    float a = 0.f, q = 0.f;
+    for (int s = 0; s < sh.S; ++s)
+      for (int k = 0; k < sh.cpg; ++k) {
+        const float2 p = partial[((long long)b * sh.S + s) * sh.C + g * sh.cpg + k];
+        a += p.x; q += p.y;
+      }
+    const float cnt = (float)sh.cpg * (float)sh.HW;
+    const float mean = a / cnt;
+    mom[g] = make_float2(mean, rsqrtf(fmaxf(q / cnt - mean * mean, 0.f) + eps));
+  }
+  __syncthreads();
+}
+
+template <typename T, bool kSilu>
+__global__ void __launch_bounds__(256) gn_apply_cl(const T* __restrict__ x, const float2* __restrict__ partial,
+                                                    const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                    T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                    GNShape sh, float eps) {
+  constexpr int V = Vec<T>::N;
+  extern __shared__ float smem[];
+  float2* mom = reinterpret_cast<float2*>(smem);         // [G]
+  const int s = blockIdx.x, b = blockIdx.y;
+  all_group_moments(partial, sh, b, eps, mom);
+  if (s == 0)
+    for (int g = threadIdx.x; g < sh.G; g += blockDim.x) { mean_out[b * sh.G + g] = mom[g].x; rstd_out[b * sh.G + g] = mom[g].y; }
+  const CLThread t = cl_thread<V>(sh, s);
+  if (!t.active) return;
+  float scale[V], shift[V], f[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    const int c = t.c0 + i;
+    const float2 m = mom[c / sh.cpg];
+    scale[i] = m.y * gamma[c];
+    shift[i] = beta[c] - m.x * scale[i];
+  }
+  const long long off = (long long)b * sh.HW * sh.C + t.c0;
+  for (long long p = t.p0 + t.lane_pix; p < t.p1; p += t.ppi) {
+    Vec<T>::load(x + off + p * sh.C, f);
+#pragma unroll
+    for (int i = 0; i < V; ++i) { const float z = f[i] * scale[i] + shift[i]; f[i] = kSilu ? silu_f(z) : z; }
+    Vec<T>::store(y + off + p * sh.C, f);
+  }
+}
+
+template <typename T, bool kSilu>
+__global__ void __launch_bounds__(256) gn_bwd_stats_cl(const T* __restrict__ x, const T* __restrict__ dy,
+                                                        const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                        const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                        float2* __restrict__ pc, GNShape sh) {
+  constexpr int V = Vec<T>::N;
+  extern __shared__ float smem[];                        // [C][2]
+  const int s = blockIdx.x, b = blockIdx.y;
+  for (int i = threadIdx.x; i < 2 * sh.C; i += blockDim.x) smem[i] = 0.f;
+  __syncthreads();
+  const CLThread t = cl_thread<V>(sh, s);
+  if (t.active) {
+    float mu[V], rs[V], ga[V], be[V], a[V], d[V], f[V], e[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int c = t.c0 + i, g = c / sh.cpg;
+      mu[i] = mean[b * sh.G + g]; rs[i] = rstd[b * sh.G + g]; ga[i] = gamma[c]; be[i] = beta[c];
+      a[i] = d[i] = 0.f;
+    }
+    const long long off = (long long)b * sh.HW * sh.C + t.c0;
+    for (long long p = t.p0 + t.lane_pix; p < t.p1; p += t.ppi) {
+      Vec<T>::load(x + off + p * sh.C, f);
+      Vec<T>::load(dy + off + p * sh.C, e);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float xh = (f[i] - mu[i]) * rs[i];
+        const float dz = kSilu ? e[i] * silu_grad(xh * ga[i] + be[i]) : e[i];
+        a[i] += dz * xh; d[i] += dz;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i) { atomicAdd(&smem[2 * (t.c0 + i)], a[i]); atomicAdd(&smem[2 * (t.c0 + i) + 1], d[i]); }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < sh.C; c += blockDim.x)
+    pc[((long long)b * sh.S + s) * sh.C + c] = make_float2(smem[2 * c], smem[2 * c + 1]);
+}
+
+template <typename T, bool kSilu>
+__global__ void __launch_bounds__(256) gn_bwd_apply_cl(const T* __restrict__ x, const T* __restrict__ dy,
+                                                        const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                        const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                        const float2* __restrict__ group_ab, T* __restrict__ dx, GNShape sh) {
+  constexpr int V = Vec<T>::N;
+  const int s = blockIdx.x, b = blockIdx.y;
+  const CLThread t = cl_thread<V>(sh, s);
+  if (!t.active) return;
+  const float inv_n = 1.f / ((float)sh.cpg * (float)sh.HW);
+  float mu[V], rs[V], ga[V], be[V], A[V], Bq[V], f[V], e[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    const int c = t.c0 + i, g = c / sh.cpg;
+    mu[i] = mean[b * sh.G + g]; rs[i] = rstd[b * sh.G + g]; ga[i] = gamma[c]; be[i] = beta[c];
+    const float2 ab = group_ab[b * sh.G + g];
+    A[i] = ab.x * inv_n; Bq[i] = ab.y * inv_n;
+  }
+  const long long off = (long long)b * sh.HW * sh.C + t.c0;
+  for (long long p = t.p0 + t.lane_pix; p < t.p1; p += t.ppi) {
+    Vec<T>::load(x + off + p * sh.C, f);
+    Vec<T>::load(dy + off + p * sh.C, e);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const float xh = (f[i] - mu[i]) * rs[i];
+      const float dz = kSilu ? e[i] * silu_grad(xh * ga[i] + be[i]) : e[i];
+      f[i] = rs[i] * (ga[i] * dz - A[i] - xh * Bq[i]);
+    }
+    Vec<T>::store(dx + off + p * sh.C, f);
+  }
+}
+
+// per batch item: channel sums over slices, group sums A = sum gamma * dbeta_c, B = sum gamma * dgamma_c, and the
+// parameter gradients accumulated over the batch with atomics (dgamma / dbeta zeroed by the caller).  grid (B)
+__global__ void __launch_bounds__(256) gn_bwd_reduce(const float2* __restrict__ pc, const float* __restrict__ gamma,
+                                                      float2* __restrict__ group_ab, float* __restrict__ dgamma,
+                                                      float* __restrict__ dbeta, GNShape sh) {
+  extern __shared__ float smem[];                        // [G][2]
+  const int b = blockIdx.x;
+  for (int i = threadIdx.x; i < 2 * sh.G; i += blockDim.x) smem[i] = 0.f;
+  __syncthreads();
+  for (int c = threadIdx.x; c < sh.C; c += blockDim.x) {
+    float a = 0.f, d = 0.f;
+    for (int s = 0; s < sh.S; ++s) { const float2 p = pc[((long long)b * sh.S + s) * sh.C + c]; a += p.x; d += p.y; }
+    atomicAdd(&dgamma[c], a);
+    atomicAdd(&dbeta[c], d);
+    const int g = c / sh.cpg;
+    atomicAdd(&smem[2 * g], gamma[c] * d);
+    atomicAdd(&smem[2 * g + 1], gamma[c] * a);
+  }
+  __syncthreads();
+  for (int g = threadIdx.x; g < sh.G; g += blockDim.x) group_ab[b * sh.G + g] = make_float2(smem[2 * g], smem[2 * g + 1]);
+}
+
+template <typename T>
+int gn_forward(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd, float* scratch,
+               GNShape sh, int layout, int act, float eps, cudaStream_t st) {
+  float2* partial = reinterpret_cast<float2*>(scratch);
+  const T* xi = static_cast<const T*>(x);
+  T* yo = static_cast<T*>(y);
+  if (layout == 0) {
+    const dim3 grid(sh.S, sh.B * sh.C);
+    gn_stats_cf<T><<<grid, 256, 0, st>>>(xi, partial, sh);
+    if (act) gn_apply_cf<T, true><<<grid, 256, 0, st>>>(xi, partial, gamma, beta, yo, mean, rstd, sh, eps);
+    else gn_apply_cf<T, false><<<grid, 256, 0, st>>>(xi, partial, gamma, beta, yo, mean, rstd, sh, eps);
+  } else {
+    const dim3 grid(sh.S, sh.B);
+    gn_stats_cl<T><<<grid, 256, 2 * sh.C * sizeof(float), st>>>(xi, partial, sh);
+    if (act) gn_apply_cl<T, true><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, partial, gamma, beta, yo, mean, rstd, sh, eps);
+    else gn_apply_cl<T, false><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, partial, gamma, beta, yo, mean, rstd, sh, eps);
+  }
+  return (int)cudaGetLastError();
+}
+
+template <typename T>
+int gn_backward(const void* x, const void* dy, const float* gamma, const float* beta, const float* mean, const float* rstd,
+                void* dx, float* dgamma, float* dbeta, float* scratch, GNShape sh, int layout, int act, cudaStream_t st) {
+  float2* pc = reinterpret_cast<float2*>(scratch);
+  float2* ab = pc + (long long)sh.B * sh.S * sh.C;
+  const T* xi = static_cast<const T*>(x);
+  const T* di = static_cast<const T*>(dy);
+  T* o = static_cast<T*>(dx);
+  const dim3 grid = layout == 0 ? dim3(sh.S, sh.B * sh.C) : dim3(sh.S, sh.B);
+  const size_t sm = layout == 0 ? 0 : 2 * sh.C * sizeof(float);
+  if (layout == 0) {
+    if (act) gn_bwd_stats_cf<T, true><<<grid, 256, 0, st>>>(xi, di, gamma, beta, mean, rstd, pc, sh);
+    else gn_bwd_stats_cf<T, false><<<grid, 256, 0, st>>>(xi, di, gamma, beta, mean, rstd, pc, sh);
+  } else {
+    if (act) gn_bwd_stats_cl<T, true><<<grid, 256, sm, st>>>(xi, di, gamma, beta, mean, rstd, pc, sh);
+    else gn_bwd_stats_cl<T, false><<<grid, 256, sm, st>>>(xi, di, gamma, beta, mean, rstd, pc, sh);
+  }
+  gn_bwd_reduce<<<sh.B, 256, 2 * sh.G * sizeof(float), st>>>(pc, gamma, ab, dgamma, dbeta, sh);
+  if (layout == 0) {
+    if (act) gn_bwd_apply_cf<T, true><<<grid, 256, 0, st>>>(xi, di, gamma, beta, mean, rstd, ab, o, sh);
+    else gn_bwd_apply_cf<T, false><<<grid, 256, 0, st>>>(xi, di, gamma, beta, mean, rstd, ab, o, sh);
+  } else {
+    if (act) gn_bwd_apply_cl<T, true><<<grid, 256, 0, st>>>(xi, di, gamma, beta, mean, rstd, ab, o, sh);
+    else gn_bwd_apply_cl<T, false><<<grid, 256, 0, st>>>(xi, di, gamma, beta, mean, rstd, ab, o, sh);
+  }
+  return (int)cudaGetLastError();
+}
+
+static bool gn_supported(const GNShape& sh, int layout, int dtype) {
+  const int V = dtype == 0 ? 8 : 4;
+  if (sh.B <= 0 || sh.C <= 0 || sh.G <= 0 || sh.C % sh.G || sh.S <= 0 || sh.HW <= 0) return false;
+  if (layout == 0) return sh.HW % V == 0 && (long long)sh.B * sh.C <= 65535;
+  return sh.C % V == 0 && sh.C / V <= 256 && sh.B <= 65535 && 2 * sh.C * sizeof(float) <= 48 * 1024;
+}
+
+}  // namespace pnm
+
+extern "C" {
+
+// floats of scratch needed by forward / backward for a given slice count
+long long pnm_groupnorm_scratch_floats(int B, int C, int G, int S) { return 2LL * B * S * C + 2LL * B * G; }
+
+// dtype: 0 bf16, 1 fp32.  layout: 0 channels-first, 1 channels-last.  act: 0 none, 1 SiLU.  Returns -1 if the shape is
+// outside what the kernels cover (the caller then uses another path), else the CUDA error code.
+int pnm_groupnorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd, float* scratch,
+                      int B, int C, long long HW, int G, int S, int layout, int dtype, int act, float eps, void* stream) {
+  pnm::GNShape sh{B, C, G, G > 0 ? C / G : 0, S, HW};
+  if (!pnm::gn_supported(sh, layout, dtype)) return -1;
+  cudaStream_t st = (cudaStream_t)stream;
+  return dtype == 0 ? pnm::gn_forward<__nv_bfloat16>(x, gamma, beta, y, mean, rstd, scratch, sh, layout, act, eps, st)
+                    : pnm::gn_forward<float>(x, gamma, beta, y, mean, rstd, scratch, sh, layout, act, eps, st);
+}
+
+int pnm_groupnorm_bwd(const void* x, const void* dy, const float* gamma, const float* beta, const float* mean,
+                      const float* rstd, void* dx, float* dgamma, float* dbeta, float* scratch, int B, int C, long long HW,
+                      int G, int S, int layout, int dtype, int act, void* stream) {
+  pnm::GNShape sh{B, C, G, G > 0 ? C / G : 0, S, HW};
+  if (!pnm::gn_supported(sh, layout, dtype)) return -1;
+  cudaStream_t st = (cudaStream_t)stream;
+  return dtype == 0 ? pnm::gn_backward<__nv_bfloat16>(x, dy, gamma, beta, mean, rstd, dx, dgamma, dbeta, scratch, sh, layout, act, st)
+                    : pnm::gn_backward<float>(x, dy, gamma, beta, mean, rstd, dx, dgamma, dbeta, scratch, sh, layout, act, st);
+}
+
+}  // extern "C"

@@ -125,6 +125,27 @@ int pnm_scalar_field_to_rgba(const float* field, long long n, float vmin, float 
 int pnm_vector_field_to_rgba(const float* vec, const float* lic, long long n, float vmin, float vmax, float max_opacity,
                              float lic_threshold, unsigned char* out, void* stream);
 
+// GroupNorm (+ fused SiLU) forward / backward (groupnorm.cu).  dtype: 0 bf16, 1 fp32; layout: 0 channels-first,
+// 1 channels-last; act: 0 none, 1 SiLU; S = number of spatial slices; scratch holds pnm_groupnorm_scratch_floats floats.
+// Return value -1: shape not covered by these kernels.  dgamma / dbeta must be zeroed by the caller.
+long long pnm_groupnorm_scratch_floats(int B, int C, int G, int S);
+int pnm_groupnorm_fwd(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd, float* scratch,
+                      int B, int C, long long HW, int G, int S, int layout, int dtype, int act, float eps, void* stream);
+int pnm_groupnorm_bwd(const void* x, const void* dy, const float* gamma, const float* beta, const float* mean,
+                      const float* rstd, void* dx, float* dgamma, float* dbeta, float* scratch, int B, int C, long long HW,
+                      int G, int S, int layout, int dtype, int act, void* stream);
+
+// out = silu^(order)(x) * g (g may be null), order 0..4; dtype 0 bf16, 1 fp32; pointers 16-byte aligned (-2 otherwise).
+int pnm_silu_derivative(const void* x, const void* g, void* out, long long n, int order, int dtype, void* stream);
+
+// Neighbourhood attention over [B, L, H, D] tensors, L = prod(shape[0..nd)) (natten.cu).  dtype 0 bf16, 1 fp32.
+// Returns -1 when the geometry is outside the kernels' limits (<= 512 neighbours, D <= 256).
+int pnm_natten_fwd(const void* q, const void* k, const void* v, void* out, int B, int H, int D, int nd, const int* shape,
+                   const int* kernel, const int* dilation, float scale, int dtype, void* stream);
+int pnm_natten_bwd(const void* q, const void* k, const void* v, const void* dout, void* dq, float* dk, float* dv, int B, int H,
+                   int D, int nd, const int* shape, const int* kernel, const int* dilation, float scale, int dtype,
+                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif

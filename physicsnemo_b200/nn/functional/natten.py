@@ -5,7 +5,9 @@ implemented directly.  Semantics follow NATTEN: tensors are ``[B, *spatial, head
 attends to a ``kernel_size`` (per axis) window of keys centred on it, the window being *shifted* (not
 truncated) at the borders so that each query sees exactly ``prod(kernel_size)`` keys; ``dilation`` strides
 the window.  Formulation: the neighbour index table ``[L, K]`` is built once per (shape, kernel, dilation)
-and cached; keys / values are gathered and reduced with a batched softmax.
+and cached; keys / values are gathered and reduced with a batched softmax (CPU path and oracle).
+On CUDA tensors (bf16 / fp32) the warp-per-query kernels of ``csrc/natten.cu`` run instead: no index table and no
+gathered ``[L, K, D]`` copies of the keys and values exist, forward or backward.
 """
 from __future__ import annotations
 
@@ -45,12 +47,89 @@ def _neighbour_table(shape: tuple, kernel: tuple, dilation: tuple, device_str: s
     return flat                                               # [L, K]
 
 
-def _neighborhood_attention(q, k, v, kernel_size, dilation, scale=None, is_causal=False, **kwargs):
+_DT = {torch.bfloat16: 0, torch.float32: 1}
+
+
+def _lib_na():
+    import ctypes
+
+    from ...ops import _lib
+
+    lib = _lib.load(required=True)
+    if not getattr(lib, "_na_declared", False):
+        c = ctypes
+        vp, i, f = c.c_void_p, c.c_int, c.c_float
+        ip = c.POINTER(c.c_int)
+        lib.pnm_natten_fwd.argtypes = [vp, vp, vp, vp, i, i, i, i, ip, ip, ip, f, i, vp]
+        lib.pnm_natten_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, ip, ip, ip, f, i, vp]
+        lib.pnm_natten_fwd.restype = lib.pnm_natten_bwd.restype = i
+        lib._na_declared = True
+    return lib
+
+
+def _cuda_ok(q, kern, dil, shape) -> bool:
+    import math
+
+    if not (q.is_cuda and q.dtype in _DT and q.shape[-1] <= 256 and math.prod(kern) <= 512):
+        return False
+    return all(k <= n and (d == 1 or k <= n // d) for n, k, d in zip(shape, kern, dil))
+
+
+class _NattenFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, shape, kern, dil, scale):
+        import ctypes
+
+        from ...ops import gemm as _g
+
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        B, H, D = q.shape[0], q.shape[-2], q.shape[-1]
+        nd = len(shape)
+        arr = lambda t: (ctypes.c_int * nd)(*t)  # noqa: E731
+        out = torch.empty_like(q)
+        err = _lib_na().pnm_natten_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, H, D, nd, arr(shape),
+                                       arr(kern), arr(dil), float(scale), _DT[q.dtype],
+                                       torch.cuda.current_stream().cuda_stream)
+        if err:
+            raise RuntimeError(f"pnm_natten_fwd failed ({err})")
+        _g.launch_count += 1
+        ctx.save_for_backward(q, k, v)
+        ctx.cfg = (shape, kern, dil, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        import ctypes
+
+        from ...ops import gemm as _g
+
+        q, k, v = ctx.saved_tensors
+        shape, kern, dil, scale = ctx.cfg
+        B, H, D = q.shape[0], q.shape[-2], q.shape[-1]
+        nd = len(shape)
+        arr = lambda t: (ctypes.c_int * nd)(*t)  # noqa: E731
+        dout = dout.contiguous().to(q.dtype)
+        dq = torch.empty_like(q)
+        dkv = torch.zeros(2, *q.shape, dtype=torch.float32, device=q.device)
+        err = _lib_na().pnm_natten_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr(), dq.data_ptr(),
+                                       dkv[0].data_ptr(), dkv[1].data_ptr(), B, H, D, nd, arr(shape), arr(kern), arr(dil),
+                                       float(scale), _DT[q.dtype], torch.cuda.current_stream().cuda_stream)
+        if err:
+            raise RuntimeError(f"pnm_natten_bwd failed ({err})")
+        _g.launch_count += 1
+        return dq, dkv[0].to(q.dtype), dkv[1].to(q.dtype), None, None, None, None
+
+
+def _neighborhood_attention(q, k, v, kernel_size, dilation, scale=None, is_causal=False, implementation=None, **kwargs):
     nd = q.ndim - 3
     if is_causal:
         raise NotImplementedError("causal neighbourhood attention is not supported")
     shape = tuple(q.shape[1:1 + nd])
     kern, dil = _tuple(kernel_size, nd), _tuple(dilation, nd)
+    if implementation != "torch" and _cuda_ok(q, kern, dil, shape):
+        return _NattenFn.apply(q, k, v, shape, kern, dil, q.shape[-1] ** -0.5 if scale is None else float(scale))
+    if implementation == "cuda":
+        raise RuntimeError("neighbourhood attention kernels need CUDA bf16 / fp32 tensors, head_dim <= 256 and <= 512 neighbours")
     table = _neighbour_table(shape, kern, dil, str(q.device))
     B, H, D = q.shape[0], q.shape[-2], q.shape[-1]
     L = table.shape[0]

@@ -4,14 +4,15 @@ Parity: ``physicsnemo/nn/module/group_norm.py`` — ``get_group_norm`` (``:72-14
 (``:144-288``): groups = ``min(num_groups, num_channels // min_channels_per_group)``; training uses
 ``F.group_norm``, evaluation the explicit mean / (unbiased) variance form; activation by name.
 The Apex NHWC kernel of the reference (``use_apex_gn``) is replaced by this package's
-GroupNorm(+SiLU) kernel, selected automatically for CUDA bf16 channels-last inputs, so
-``use_apex_gn=True`` is accepted and maps to the same class.
+GroupNorm(+SiLU) kernels (``ops/group_norm.py``), used for every CUDA bf16 / fp32 input they cover in
+either memory format, so ``use_apex_gn=True`` is accepted and maps to the same class.
 """
 from __future__ import annotations
 
 import torch
 import torch.nn.functional as F
 
+from ...ops import group_norm as _gn
 from .utils.utils import _validate_amp
 
 
@@ -64,6 +65,11 @@ class GroupNorm(torch.nn.Module):
                 weight = weight.to(x.dtype)
             if bias.dtype != x.dtype:
                 bias = bias.to(x.dtype)
+        if x.is_cuda and _gn.supported(x, self.num_groups):
+            # one kernel pair for norm + affine (+ SiLU); same arithmetic in training and evaluation
+            fuse = self.act == "silu"
+            x = _gn.group_norm(x, self.num_groups, self.weight, self.bias, self.eps, silu=fuse)
+            return x if fuse or self.act_fn is None else self.act_fn(x)
         if self.training:
             x = F.group_norm(x, num_groups=self.num_groups, weight=weight, bias=bias, eps=self.eps)
         else:
