@@ -102,3 +102,34 @@ def test_small_forward_backward_all_models():
             torch.randn(1, 3, 16, 16), torch.rand(1)).sum().backward()
         Transolver(2, 1, structured_shape=(8, 8), unified_pos=True, n_hidden=16, n_head=2, slice_num=4, use_te=False)(
             torch.randn(1, 8, 8, 2)).sum().backward()
+
+
+def test_graphcast_small():
+    import numpy as np
+
+    from physicsnemo_b200.models.graphcast import GraphCastNet
+    from physicsnemo_b200.models.graphcast.utils.icosahedral_mesh import (get_hierarchy_of_triangular_meshes_for_sphere,
+                                                                         merge_meshes)
+
+    meshes = get_hierarchy_of_triangular_meshes_for_sphere(3)
+    assert [(m.vertices.shape[0], m.faces.shape[0]) for m in meshes] == [(12, 20), (42, 80), (162, 320), (642, 1280)]
+    assert np.abs(np.linalg.norm(meshes[-1].vertices, axis=1) - 1).max() < 1e-6
+    assert merge_meshes(meshes).faces.shape[0] == 1700
+    f = meshes[1].faces
+    v = meshes[1].vertices
+    assert (np.einsum("fi,fi->f", np.cross(v[f[:, 1]] - v[f[:, 0]], v[f[:, 2]] - v[f[:, 0]]), v[f].mean(1)) > 0).all()
+    kw = dict(mesh_level=2, input_res=(19, 36), input_dim_grid_nodes=5, output_dim_grid_nodes=3, processor_layers=3, hidden_dim=16)
+    net = GraphCastNet(**kw)
+    assert net.mesh_graph.num_nodes == 162 and net.m2g_graph.num_edges == 3 * 19 * 36
+    assert torch.bincount(net.m2g_graph.edge_index[1]).unique().tolist() == [3]
+    x = torch.randn(1, 5, 19, 36)
+    y = net(x)
+    assert y.shape == (1, 3, 19, 36)
+    y.sum().backward()
+    assert all(p.grad is not None for p in net.parameters())
+    net.set_checkpoint_processor(1)
+    assert torch.allclose(net(x), y, atol=1e-5)
+    trick = GraphCastNet(**kw, do_concat_trick=True, processor_type="GraphTransformer", khop_neighbors=2)
+    assert trick(x).shape == (1, 3, 19, 36)
+    with pytest.raises(ValueError):
+        net(torch.randn(2, 5, 19, 36))
