@@ -1,0 +1,3 @@
+"""Import location kept for parity with ``physicsnemo/models/meshgraphnet/hybrid_meshgraphnet.py``."""
+from .variants import *  # noqa: F401,F403
+from .variants import BiStrideMeshGraphNet, HybridMeshGraphNet, HybridMeshGraphNetProcessor, MeshGraphKAN  # noqa: F401

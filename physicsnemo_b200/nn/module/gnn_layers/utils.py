@@ -68,3 +68,8 @@ def aggregate(efeat: Tensor, num_dst: int, graph, aggregation: str = "sum") -> T
 def aggregate_and_concat(efeat: Tensor, nfeat: Tensor, graph, aggregation: str) -> Tensor:
     """``cat(aggregate(efeat → dst nodes), nfeat)``."""
     return torch.cat((aggregate(efeat, nfeat.shape[0], graph, aggregation), nfeat), -1)
+
+
+def aggregate_and_concat_hetero(mesh_efeat: Tensor, world_efeat: Tensor, nfeat: Tensor, graph, aggregation: str) -> Tensor:
+    """``cat(aggregate(cat(mesh, world) edge features → dst nodes), nfeat)``; ``graph`` lists mesh edges first."""
+    return aggregate_and_concat(torch.cat((mesh_efeat, world_efeat), dim=0), nfeat, graph, aggregation)

@@ -133,3 +133,29 @@ def test_graphcast_small():
     assert trick(x).shape == (1, 3, 19, 36)
     with pytest.raises(ValueError):
         net(torch.randn(2, 5, 19, 36))
+
+
+def test_meshgraphnet_variants():
+    from physicsnemo_b200.models.meshgraphnet import BiStrideMeshGraphNet, HybridMeshGraphNet, MeshGraphKAN
+    from physicsnemo_b200.nn.module.gnn_layers.graph_types import Graph
+
+    torch.manual_seed(0)
+    N, E = 30, 90
+    ei = torch.randint(0, N, (2, E))
+    g = Graph(ei, num_nodes=N)
+    g.pos = torch.randn(N, 3)
+    x, e = torch.randn(N, 4), torch.randn(E, 3)
+    small = dict(processor_size=2, hidden_dim_processor=16, hidden_dim_node_encoder=16, hidden_dim_edge_encoder=16,
+                 hidden_dim_node_decoder=16)
+    assert MeshGraphKAN(4, 3, 2, **small)(x, e, g).shape == (N, 2)
+    hyb = HybridMeshGraphNet(4, 3, 2, **small)
+    assert not hasattr(hyb, "edge_encoder") and hyb(x, e[:60], e[60:], g).shape == (N, 2)
+    with pytest.raises(NotImplementedError):
+        HybridMeshGraphNet(4, 3, 2, do_concat_trick=True)
+    bi = BiStrideMeshGraphNet(4, 3, 2, num_mesh_levels=2, **small)
+    ids = [torch.arange(0, N, 2), torch.arange(0, 15, 2)]
+    edges = [ei, torch.randint(0, 15, (2, 40)), torch.randint(0, 8, (2, 20))]
+    out = bi(x, e, g, ms_edges=edges, ms_ids=ids)
+    assert out.shape == (N, 2)
+    out.sum().backward()
+    assert bi.bistride_processor.bottom_gmp.mlp_edge.model[0].weight.grad is not None
