@@ -32,7 +32,14 @@ __device__ __forceinline__ float load_grad(const void* g, long long i, int bf16)
 // Adam / AdamW.  step_size = lr / (1 - b1^t); inv_bc2_sqrt = 1 / sqrt(1 - b2^t).
 __global__ void __launch_bounds__(kOptThreads)
 adam_multi_kernel(const OptEntry* __restrict__ entries, const int2* __restrict__ blocks, float lr, float b1, float b2,
-                  float eps, float wd, float step_size, float inv_bc2_sqrt, int decoupled, float grad_scale) {
+                  float eps, float wd, float step_size, float inv_bc2_sqrt, int decoupled, float grad_scale,
+                  const float* __restrict__ hyper) {
+  if (hyper) {          // {learning rate, step count} kept on the device: the launch can be replayed from a CUDA graph
+    lr = hyper[0];
+    const float t = hyper[1];
+    step_size = lr / (1.f - powf(b1, t));
+    inv_bc2_sqrt = rsqrtf(1.f - powf(b2, t));
+  }
   const int2 blk = blocks[blockIdx.x];
   const OptEntry e = entries[blk.x];
   const long long lo = (long long)blk.y * kOptChunk;
@@ -103,11 +110,12 @@ extern "C" {
 int pnm_opt_chunk() { return pnm::kOptChunk; }
 
 int pnm_adam_multi(const void* entries, const void* blocks, int n_blocks, float lr, float b1, float b2, float eps,
-                   float wd, float step_size, float inv_bc2_sqrt, int decoupled, float grad_scale, void* stream) {
+                   float wd, float step_size, float inv_bc2_sqrt, int decoupled, float grad_scale, void* stream,
+                   const float* hyper) {
   if (n_blocks <= 0) return 0;
   pnm::adam_multi_kernel<<<n_blocks, pnm::kOptThreads, 0, (cudaStream_t)stream>>>(
       reinterpret_cast<const pnm::OptEntry*>(entries), reinterpret_cast<const int2*>(blocks), lr, b1, b2, eps, wd,
-      step_size, inv_bc2_sqrt, decoupled, grad_scale);
+      step_size, inv_bc2_sqrt, decoupled, grad_scale, hyper);
   return (int)cudaGetLastError();
 }
 

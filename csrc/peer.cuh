@@ -23,7 +23,8 @@ constexpr int kFlagBytes = 2 * 2 * kPeerMaxCtas * kPeerMaxRanks * 4;  // 8 KiB
 struct PeerArgs {
   uint8_t* base[kPeerMaxRanks];  // symmetric buffer of every rank (peer-mapped pointers)
   int rank, world;
-  uint32_t epoch;        // call number, starts at 1
+  uint32_t epoch;        // call number, starts at 1 (an offset from *epoch_base when that is set)
+  const uint32_t* epoch_base;  // optional device-resident counter: lets a captured CUDA graph advance epochs on replay
   long long capacity;    // floats per stage
   unsigned long long budget_ns;
 };
@@ -45,11 +46,11 @@ __device__ __forceinline__ float* peer_data(const PeerArgs& p, int owner, int sl
 
 // Tell every rank that this CTA's data of (slot, phase) is visible; then wait for all of them.
 // Called by all threads of the CTA; returns false when a peer did not arrive in time.
-__device__ __forceinline__ bool peer_exchange_flags(const PeerArgs& p, int slot, int phase, int* err, int* sh_ok) {
+__device__ __forceinline__ bool peer_exchange_flags(const PeerArgs& p, uint32_t epoch, int slot, int phase, int* err, int* sh_ok) {
   __syncthreads();
   if (threadIdx.x < p.world) {
     __threadfence_system();
-    st_release_sys(peer_flag(p, threadIdx.x, slot, phase, blockIdx.x, p.rank), p.epoch);
+    st_release_sys(peer_flag(p, threadIdx.x, slot, phase, blockIdx.x, p.rank), epoch);
   }
   if (threadIdx.x == 0) *sh_ok = 1;
   __syncthreads();
@@ -57,7 +58,7 @@ __device__ __forceinline__ bool peer_exchange_flags(const PeerArgs& p, int slot,
     const uint32_t* f = peer_flag(p, p.rank, slot, phase, blockIdx.x, threadIdx.x);
     unsigned long long t0 = 0;
     uint32_t spins = 0;
-    while (int32_t(ld_acquire_sys(f) - p.epoch) < 0) {
+    while (int32_t(ld_acquire_sys(f) - epoch) < 0) {
       if ((++spins & 0xff) == 0) {
         unsigned long long now = globaltimer_ns();
         if (t0 == 0) t0 = now;
@@ -76,7 +77,8 @@ __global__ void __launch_bounds__(512)
 peer_allreduce_kernel(const float* __restrict__ in, float* __restrict__ out, long long n, float scale, int two_shot,
                       PeerArgs p, int* err) {
   __shared__ int sh_ok;
-  const int slot = p.epoch & 1;
+  const uint32_t epoch = p.epoch + (p.epoch_base ? *p.epoch_base : 0u);
+  const int slot = epoch & 1;
   const int nct = gridDim.x;
   float* mineA = peer_data(p, p.rank, slot, 0);
   if (!two_shot) {
@@ -84,7 +86,7 @@ peer_allreduce_kernel(const float* __restrict__ in, float* __restrict__ out, lon
     const long long lo = per * blockIdx.x;
     const long long hi = lo + per < n ? lo + per : n;
     for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) mineA[i] = in[i];
-    if (!peer_exchange_flags(p, slot, 0, err, &sh_ok)) return;
+    if (!peer_exchange_flags(p, epoch, slot, 0, err, &sh_ok)) return;
     for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
       float s = 0.f;
       for (int r = 0; r < p.world; ++r) s += __ldcg(peer_data(p, r, slot, 0) + i);  // fixed order: same bits on every rank
@@ -102,7 +104,7 @@ peer_allreduce_kernel(const float* __restrict__ in, float* __restrict__ out, lon
     for (long long i = clo + threadIdx.x; i < chi; i += blockDim.x)
       if (base + i < n) mineA[base + i] = in[base + i];
   }
-  if (!peer_exchange_flags(p, slot, 0, err, &sh_ok)) return;
+  if (!peer_exchange_flags(p, epoch, slot, 0, err, &sh_ok)) return;
   {
     const long long base = (long long)p.rank * slice;
     float* mineB = peer_data(p, p.rank, slot, 1);
@@ -113,7 +115,7 @@ peer_allreduce_kernel(const float* __restrict__ in, float* __restrict__ out, lon
       mineB[i] = s * scale;
     }
   }
-  if (!peer_exchange_flags(p, slot, 1, err, &sh_ok)) return;
+  if (!peer_exchange_flags(p, epoch, slot, 1, err, &sh_ok)) return;
   for (int s = 0; s < p.world; ++s) {
     const long long base = s * slice;
     const float* src = peer_data(p, s, slot, 1);

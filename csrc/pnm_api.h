@@ -40,14 +40,15 @@ int pnm_segment_sum(const void* in, int ldi, const int* perm, const int* offsets
 // In-kernel all-reduce (sum, fp32) over peer-mapped symmetric buffers; see peer.cuh for the layout.
 int pnm_peer_allreduce(const float* in, float* out, long long n, float scale, int two_shot, const void* const* bases,
                        int rank, int world, unsigned int epoch, long long capacity_floats, double budget_s,
-                       void* stream);
+                       void* stream, const void* epoch_base);  // epoch_base: optional device uint32 added to epoch
 int pnm_peer_flag_bytes();
 int pnm_peer_wait_probe(const void* flag, unsigned int expect, double budget_s, int* status_out, void* stream);
 
 // Multi-tensor Adam / AdamW over a device table of tensors (layout in optim.cu); fp32 parameters and moments.
 int pnm_opt_chunk();
 int pnm_adam_multi(const void* entries, const void* blocks, int n_blocks, float lr, float b1, float b2, float eps,
-                   float wd, float step_size, float inv_bc2_sqrt, int decoupled, float grad_scale, void* stream);
+                   float wd, float step_size, float inv_bc2_sqrt, int decoupled, float grad_scale, void* stream,
+                   const float* hyper);  // hyper: optional device {lr, step}; overrides lr / step_size / inv_bc2_sqrt
 int pnm_grad_sqnorm_multi(const void* entries, const void* blocks, int n_blocks, float* out, void* stream);
 
 // Periodic stencil programs (layout in stencil.cu): gradients, divergence, curl, Laplacians and their transposes.

@@ -121,12 +121,13 @@ int pnm_segment_sum(const void* in, int ldi, const int* perm, const int* offsets
 // bases: host array of `world` peer-mapped pointers to the symmetric buffers (this rank's own included).
 int pnm_peer_allreduce(const float* in, float* out, long long n, float scale, int two_shot, const void* const* bases,
                        int rank, int world, unsigned int epoch, long long capacity_floats, double budget_s,
-                       void* stream) {
+                       void* stream, const void* epoch_base) {
   if (ensure_init()) return -1;
   pnm::PeerArgs p;
   if (world > pnm::kPeerMaxRanks) return -50;
   for (int r = 0; r < world; ++r) p.base[r] = reinterpret_cast<uint8_t*>(const_cast<void*>(bases[r]));
   p.rank = rank; p.world = world; p.epoch = epoch; p.capacity = capacity_floats;
+  p.epoch_base = reinterpret_cast<const uint32_t*>(epoch_base);
   p.budget_ns = (unsigned long long)(budget_s * 1e9);
   return pnm::launch_peer_allreduce(in, out, n, scale, two_shot, p, g_err_ptr, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -26,7 +26,7 @@ def _declare(lib):
         return
     c = ctypes
     lib.pnm_opt_chunk.restype = c.c_int
-    lib.pnm_adam_multi.argtypes = [c.c_void_p, c.c_void_p, c.c_int] + [c.c_float] * 7 + [c.c_int, c.c_float, c.c_void_p]
+    lib.pnm_adam_multi.argtypes = [c.c_void_p, c.c_void_p, c.c_int] + [c.c_float] * 7 + [c.c_int, c.c_float, c.c_void_p, c.c_void_p]
     lib.pnm_adam_multi.restype = c.c_int
     lib.pnm_grad_sqnorm_multi.argtypes = [c.c_void_p, c.c_void_p, c.c_int, c.c_void_p, c.c_void_p]
     lib.pnm_grad_sqnorm_multi.restype = c.c_int
@@ -70,13 +70,18 @@ class FusedAdam(Optimizer):
     """``Adam`` (``adam_w_mode=False``) or ``AdamW`` with the semantics of ``torch.optim``."""
 
     def __init__(self, params: Iterable, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
-                 weight_decay: float = 0.0, adam_w_mode: bool = False, grad_scale: float = 1.0):
+                 weight_decay: float = 0.0, adam_w_mode: bool = False, grad_scale: float = 1.0, capturable: bool = False):
         if lr < 0 or eps < 0 or not 0 <= betas[0] < 1 or not 0 <= betas[1] < 1:
             raise ValueError("invalid Adam hyper-parameters")
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, adam_w_mode=adam_w_mode,
                                       grad_scale=grad_scale))
         self._tables: dict = {}
         self.kernel_launches = 0
+        # capturable: learning rate and step count live in a device tensor per group ({lr, step}); ``step()`` then
+        # contains no host-computed scalar, so it can be captured into a CUDA graph and replayed.  Change the learning
+        # rate of a captured optimizer with ``set_lr`` (writes the device value), not through ``param_groups``.
+        self.capturable = capturable
+        self._hyper: dict = {}
 
     def _state_of(self, p):
         st = self.state[p]
@@ -85,6 +90,20 @@ class FusedAdam(Optimizer):
             st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.preserve_format)
             st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32, memory_format=torch.preserve_format)
         return st
+
+    def _hyper_of(self, gi: int, group, device) -> torch.Tensor:
+        h = self._hyper.get(gi)
+        if h is None:
+            h = self._hyper[gi] = torch.tensor([float(group["lr"]), 0.0], dtype=torch.float32, device=device)
+        return h
+
+    def set_lr(self, lr: float, group: Optional[int] = None) -> None:
+        """Set the learning rate of one group (or all): host value and, if capturable, the device value."""
+        for gi, g in enumerate(self.param_groups):
+            if group is None or gi == group:
+                g["lr"] = lr
+                if gi in self._hyper:
+                    self._hyper[gi][0] = float(lr)
 
     @torch.no_grad()
     def step(self, closure: Optional[Callable] = None):
@@ -130,9 +149,14 @@ class FusedAdam(Optimizer):
                 tab = build_tables(fused, [p.grad for p in fused], [s["exp_avg"] for s in sts],
                                    [s["exp_avg_sq"] for s in sts], lib.pnm_opt_chunk(), self._tables.setdefault(gi, {}))
                 e_ptr, b_ptr = tab.upload()
+                hyper = None
+                if self.capturable:
+                    hyper = self._hyper_of(gi, group, fused[0].device)
+                    hyper[1:2].add_(1.0)                  # device-side step count (captured with the step)
                 err = lib.pnm_adam_multi(e_ptr, b_ptr, tab.n_blocks, lr, b1, b2, group["eps"], group["weight_decay"],
                                          lr / (1 - b1 ** t), 1.0 / math.sqrt(1 - b2 ** t), int(group["adam_w_mode"]),
-                                         group["grad_scale"], torch.cuda.current_stream().cuda_stream)
+                                         group["grad_scale"], torch.cuda.current_stream().cuda_stream,
+                                         hyper.data_ptr() if hyper is not None else None)
                 if err:
                     raise RuntimeError(f"pnm_adam_multi failed with CUDA error {err}")
                 self.kernel_launches += 1

@@ -38,7 +38,8 @@ class PeerRuntime:
         self.lib = _lib.load(required=True)
         self.lib.pnm_peer_allreduce.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_float,
                                                 ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
-                                                ctypes.c_uint, ctypes.c_longlong, ctypes.c_double, ctypes.c_void_p]
+                                                ctypes.c_uint, ctypes.c_longlong, ctypes.c_double, ctypes.c_void_p,
+                                                ctypes.c_void_p]
         self.lib.pnm_peer_allreduce.restype = ctypes.c_int
         self.flag_bytes = self.lib.pnm_peer_flag_bytes()
         self.capacity = int(capacity_floats)
@@ -52,6 +53,10 @@ class PeerRuntime:
         self._bases = (ctypes.c_void_p * self.world)(*ptrs)
         self.epoch = 0
         self.budget_s = 2.0
+        # Call numbers are ``epoch_base (device) + epoch (host offset)``.  The host offset restarts at every
+        # ``step_done()``, which moves it into the device counter with a one-element add on the stream; a CUDA graph
+        # that contains a whole step (its all-reduces and that add) therefore advances the call numbers at each replay.
+        self.epoch_base = torch.zeros(1, dtype=torch.int32, device=self.device)
         dist.barrier(group=self.group)  # zeroed flags are visible before the first kernel
 
     def all_reduce(self, x: torch.Tensor, scale: float = 1.0, out: Optional[torch.Tensor] = None,
@@ -68,10 +73,19 @@ class PeerRuntime:
         self.epoch += 1
         code = self.lib.pnm_peer_allreduce(x.data_ptr(), out.data_ptr(), n, float(scale), int(two_shot), self._bases,
                                            self.rank, self.world, self.epoch, self.capacity, self.budget_s,
-                                           _g._stream())
+                                           _g._stream(), self.epoch_base.data_ptr())
         _g._check(code, "pnm_peer_allreduce")
         _g.launch_count += 1
         return out
+
+    def step_done(self) -> None:
+        """Fold the calls made since the last ``step_done`` into the device-side call counter.
+
+        Must be the last peer operation of a step that is captured into a CUDA graph; harmless otherwise.
+        """
+        if self.epoch:
+            self.epoch_base.add_(self.epoch)
+            self.epoch = 0
 
     def check(self) -> None:
         """Raise ``PeerTimeoutError`` if any bounded wait has run out (synchronises the device)."""
@@ -89,3 +103,6 @@ class PeerAllReduce:
 
     def all_reduce(self, flat: torch.Tensor) -> torch.Tensor:
         return self.rt.all_reduce(flat.contiguous())
+
+    def step_done(self) -> None:
+        self.rt.step_done()

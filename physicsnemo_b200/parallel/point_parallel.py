@@ -74,3 +74,5 @@ class PointParallel:
         else:
             dist.all_reduce(flat, group=self.group)
         torch._foreach_copy_([g.reshape(-1) for g in grads], list(flat.split([g.numel() for g in grads])))
+        if self._peer is not None:
+            self._peer.step_done()      # last peer call of the step: lets a captured step advance its call numbers

@@ -202,3 +202,45 @@ class StaticCaptureEvaluateNoGrad(_StaticCapture):
                          None, label)
         self.eval = True
         self.no_grad = True
+
+
+class GraphedStep:
+    """A whole training step — forward, backward, gradient reduction, optimizer — as one CUDA graph.
+
+    ``step_fn(*inputs)`` is run ``warmup`` times on a side stream, then captured once with the tensors in
+    ``static_inputs`` as its arguments; calling the object copies new inputs into those tensors (from pinned host
+    memory this is an asynchronous copy on the current stream), replays the graph and returns the captured outputs
+    (static tensors, overwritten by the next replay).  One replay costs one launch on the host, so steps whose
+    kernels are shorter than the per-launch host overhead (small shards, many ranks) stop being host-bound.
+
+    Requirements on ``step_fn``: no host synchronisation and no host-computed scalar that changes from step to step
+    (use ``FusedAdam(capturable=True)``; the peer collectives keep their call counter on the device).
+    """
+
+    def __init__(self, step_fn: Callable, static_inputs, warmup: int = 3, pool=None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("GraphedStep needs a CUDA device")
+        self.step_fn = step_fn
+        self.static_inputs = list(static_inputs)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(max(int(warmup), 1)):
+                step_fn(*self.static_inputs)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, pool=pool):
+            self.static_outputs = step_fn(*self.static_inputs)
+        self.replays = 0
+
+    def __call__(self, *inputs):
+        if inputs:
+            if len(inputs) != len(self.static_inputs):
+                raise ValueError(f"expected {len(self.static_inputs)} inputs, got {len(inputs)}")
+            for dst, src in zip(self.static_inputs, inputs):
+                if src is not dst:
+                    dst.copy_(src, non_blocking=True)
+        self.graph.replay()
+        self.replays += 1
+        return self.static_outputs
