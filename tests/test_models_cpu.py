@@ -159,3 +159,48 @@ def test_meshgraphnet_variants():
     assert out.shape == (N, 2)
     out.sum().backward()
     assert bi.bistride_processor.bottom_gmp.mlp_edge.model[0].weight.grad is not None
+
+
+def test_dpot_mesh_reduced_vfgn():
+    from types import SimpleNamespace as NS
+
+    from physicsnemo_b200.models.dpot import DPOTNet, DPOTNet3D
+    from physicsnemo_b200.models.mesh_reduced import Mesh_Reduced, Sequence_Model
+    from physicsnemo_b200.models.vfgn import VFGNLearnedSimulator
+    from physicsnemo_b200.nn.module.gnn_layers.graph_types import Graph
+
+    torch.manual_seed(0)
+    net = DPOTNet(inp_shape=16, patch_size=4, in_channels=2, out_channels=2, in_timesteps=3, out_timesteps=2, num_blocks=2,
+                  embed_dim=16, out_layer_dim=8, depth=2, modes=3, normalize=True)
+    assert net(torch.randn(2, 16, 16, 3, 2)).shape == (2, 16, 16, 2, 2)
+    net3 = DPOTNet3D(inp_shape=8, patch_size=4, in_channels=1, out_channels=2, in_timesteps=2, num_blocks=2, embed_dim=8,
+                     out_layer_dim=4, depth=1, modes=2, temporal_modes=2)
+    assert net3(torch.randn(1, 8, 8, 8, 2, 1)).shape == (1, 8, 8, 8, 1, 2)
+
+    N, E, P = 40, 120, 8
+    pos, piv = torch.rand(N, 2), torch.rand(P, 2)
+    ei = torch.randint(0, N, (2, E))
+    g = Graph(torch.cat([ei, ei + N], 1), num_nodes=2 * N)
+    g.batch = torch.arange(2).repeat_interleave(N)
+    small = dict(processor_size=2, hidden_dim_processor=16, hidden_dim_node_encoder=16, hidden_dim_edge_encoder=16,
+                 hidden_dim_node_decoder=16)
+    mr = Mesh_Reduced(3, 2, 3, output_encode_dim=4, **small)
+    x, e = torch.randn(2 * N, 3), torch.randn(2 * E, 2)
+    z = mr.encode(x, e, g, pos, piv)
+    assert z.shape == (2 * P, 4) and mr.decode(z, e, g, pos, piv).shape == (2 * N, 3)
+    # interpolating a constant field returns the constant
+    const, *_ = mr.knn_interpolate(torch.full((N, 1), 2.5), pos, piv, k=3)
+    assert torch.allclose(const, torch.full((P, 1), 2.5), atol=1e-5)
+    seq = Sequence_Model(4 * P, 3, None, num_heads=4)
+    zz = z.reshape(2, 1, -1)
+    assert seq.sample(zz, 3, torch.randn(2, 1, 3)).shape == (2, 4, 4 * P)
+
+    stats = {k: NS(mean=torch.zeros(3), std=torch.ones(3)) for k in ("velocity", "acceleration")}
+    sim = VFGNLearnedSimulator(num_dimensions=3, num_seq=5, boundaries=torch.zeros(3, 2), normalization_stats=stats)
+    n, m = 12, 30
+    seqp = torch.randn(2 * n, 5, 3)
+    pred, tgt = sim(torch.randn(2 * n, 3), sim.get_random_walk_noise_for_position_sequence(seqp, 1e-3), seqp,
+                    torch.tensor([n, n]), torch.tensor([m, m]), torch.randint(0, n, (2 * m,)), torch.randint(0, n, (2 * m,)),
+                    1, None, torch.randint(0, 3, (2 * n,)))
+    assert pred.shape == tgt.shape == (2 * n, 3)
+    assert "lin_s.weight" in dict(sim._graph_network._decoder_network.mlp.named_parameters())
