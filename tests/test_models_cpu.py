@@ -204,3 +204,20 @@ def test_dpot_mesh_reduced_vfgn():
                     1, None, torch.randint(0, 3, (2 * n,)))
     assert pred.shape == tgt.shape == (2 * n, 3)
     assert "lin_s.weight" in dict(sim._graph_network._decoder_network.mlp.named_parameters())
+
+
+def test_geotransolver_streams_and_context():
+    from physicsnemo_b200.models.geotransolver import GeoTransolver
+
+    torch.manual_seed(0)
+    net = GeoTransolver(functional_dim=(3, 2), out_dim=(2, 1), geometry_dim=3, global_dim=4, n_layers=2, n_hidden=32, n_head=4,
+                        slice_num=8)
+    a, b = net((torch.randn(2, 50, 3), torch.randn(2, 30, 2)), None, torch.randn(2, 3, 4), torch.randn(2, 40, 3))
+    assert a.shape == (2, 50, 2) and b.shape == (2, 30, 1)
+    (a + 0).sum().backward()
+    grid = GeoTransolver(functional_dim=3, out_dim=2, geometry_dim=2, n_layers=1, n_hidden=32, n_head=4, slice_num=8,
+                         structured_shape=(6, 5), attention_type="GALE")
+    out, states = grid(torch.randn(2, 6, 5, 3), geometry=torch.randn(2, 6, 5, 2), return_embedding_states=True)
+    assert out.shape == (2, 6, 5, 2) and states.shape == (2, 4, 8, 8)
+    with pytest.raises(ValueError):
+        GeoTransolver(functional_dim=3, out_dim=2, structured_shape=(4, 4), include_local_features=True)
