@@ -94,3 +94,30 @@ def test_process_group_config_tree():
     assert sorted(cfg.leaf_groups()) == ["channel_parallel", "data_parallel", "spatial_parallel"]
     cfg.set_leaf_group_sizes({"spatial_parallel": 2, "channel_parallel": 2, "data_parallel": 4})
     assert cfg.get_node("model_parallel").size == 4 and cfg.get_node("world").size == 16
+
+
+def _dist_afno(rank, world):
+    import torch
+    import torch.distributed as dist
+
+    from physicsnemo_b200.distributed import DistributedManager
+    from physicsnemo_b200.models.afno.distributed import DistributedAFNO
+
+    DistributedManager.create_process_subgroup("model_parallel", world)
+    torch.manual_seed(0)                       # same seed: identical replicated parameters, identical shards
+    net = DistributedAFNO(inp_shape=(16, 32), in_channels=3, out_channels=2, patch_size=4, embed_dim=16, depth=2, num_blocks=4)
+    assert net._impl.blocks[0].filter.w1.shape[0] == 4 // world and net._impl.pos_embed.shape[1] == 16 // world
+    torch.manual_seed(1)
+    x = torch.randn(2, 3, 16, 32)
+    y = net(x)
+    assert y.shape == (2, 2, 16, 32) and torch.isfinite(y).all()
+    gathered = [torch.empty_like(y) for _ in range(world)]
+    dist.all_gather(gathered, y.detach())
+    for g in gathered:                         # the gathered channels and the broadcast head make every rank agree
+        assert torch.allclose(g, gathered[0], atol=1e-6)
+    y.square().mean().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in net.parameters())
+
+
+def test_distributed_afno_two_ranks():
+    run_ranks(_dist_afno, world=2)
