@@ -103,6 +103,19 @@ __device__ __forceinline__ void tma_store_2d(const void* smem_src, const CUtenso
                ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
 }
+// 4-D tiled load / store (channels, x, y, image): used by the implicit-GEMM convolution, where a tile of output pixels
+// reads its shifted input window straight from the NHWC tensor; coordinates outside the tensor read as zero.
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c, int x, int y, int n) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c), "r"(x), "r"(y), "r"(n)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const void* smem_src, const CUtensorMap* m, int c, int x, int y, int n) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c), "r"(x), "r"(y), "r"(n)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {

@@ -34,7 +34,21 @@ struct GemmArgs {
   int scale_post;
   int num_m_tiles, num_n_tiles;
   int* err;
+  // implicit-GEMM convolution (conv != 0): rows of A are output pixels of an NHWC image, tiled 8 x 16 per M tile;
+  // K runs over (tap, input channel); the A tile of k-block (tap, c0) is the input window shifted by the tap
+  int conv, tiles_x, tiles_y, cin, ksize, pad, img_h;
 };
+
+constexpr int kConvTileH = 8;
+constexpr int kConvTileW = 16;
+
+__device__ __forceinline__ void conv_tile_origin(const GemmArgs& g, int mt, int& n, int& y0, int& x0) {
+  const int per_img = g.tiles_x * g.tiles_y;
+  n = mt / per_img;
+  const int r = mt - n * per_img;
+  y0 = (r / g.tiles_x) * kConvTileH;
+  x0 = (r % g.tiles_x) * kConvTileW;
+}
 
 constexpr int kGemmThreads = 320;
 constexpr int kBM = 128;
@@ -131,7 +145,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint8_t* sb = sa + kBM * kBK * 2;
           mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
           const int k = kb * kBK;
-          if (k < g.K1) tma_load_2d(sa, &tmA, &full[s], k, mt * kBM);
+          if (g.conv) {
+            int n, y0, x0;
+            conv_tile_origin(g, mt, n, y0, x0);
+            const int tap = k / g.cin, c0 = k - tap * g.cin;
+            tma_load_4d(sa, &tmA, &full[s], c0, x0 + tap % g.ksize - g.pad, y0 + tap / g.ksize - g.pad, n);
+          } else if (k < g.K1) tma_load_2d(sa, &tmA, &full[s], k, mt * kBM);
           else if (k < g.K2) tma_load_2d(sa, &tmA2, &full[s], k - g.K1, mt * kBM);
           else tma_load_2d(sa, &tmA3, &full[s], k - g.K2, mt * kBM);
           tma_load_2d(sb, &tmB, &full[s], k, nt * BN);
@@ -336,7 +355,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (store_ok) tma_store_2d(stg + b * kChunkBytes, &tmC, c0, r0);
+          if (g.conv) {
+            // this warp's 32 rows are two image rows of 16 pixels: one 4-D box; the copy engine clips at the image edge
+            int n, y0, x0;
+            conv_tile_origin(g, r0 / kBM, n, y0, x0);
+            const int yy = y0 + 2 * q;
+            if (c0 < g.N && yy < g.img_h) tma_store_4d(stg + b * kChunkBytes, &tmC, c0, x0, yy, n);
+          } else if (store_ok) tma_store_2d(stg + b * kChunkBytes, &tmC, c0, r0);
           tma_store_commit();
         }
         ++use;
@@ -367,19 +392,25 @@ struct GemmCall {
   const float* bias; const float* scale; float* group_out;
   int act, aux_mode, scale_post;
   int max_ctas;  // 0 = number of SMs
+  // convolution: A is an NHWC image [img_n, img_h, img_w, cin], B holds [N, ksize*ksize*cin] (tap-major), C is NHWC
+  int conv = 0, img_n = 0, img_h = 0, img_w = 0, cin = 0, ksize = 0;
 };
 
 template <int BN, int MODE>
 inline int launch_gemm_tn(const GemmCall& c, int num_sms, int* err_word, cudaStream_t stream) {
   using Cfg = GemmCfg<BN, MODE>;
   CUtensorMap tA, tA2, tA3, tB, tC, tX;
-  if (make_tmap_2d_b16(&tA, c.A, c.M, c.K1, c.lda, kBM, kBK)) return -10;
+  if (c.conv) {
+    if (MODE != MODE_PLAIN) return -19;
+    if (make_tmap_nhwc_b16(&tA, c.A, c.img_n, c.img_h, c.img_w, c.cin, kConvTileH, kConvTileW)) return -10;
+  } else if (make_tmap_2d_b16(&tA, c.A, c.M, c.K1, c.lda, kBM, kBK)) return -10;
   if (c.K2 > c.K1) { if (make_tmap_2d_b16(&tA2, c.A2, c.M, c.K2 - c.K1, c.lda2, kBM, kBK)) return -11; }
   else tA2 = tA;
   if (c.K > c.K2) { if (make_tmap_2d_b16(&tA3, c.A3, c.M, c.K - c.K2, c.lda3, kBM, kBK)) return -18; }
   else tA3 = tA;
   if (make_tmap_2d_b16(&tB, c.B, c.N, c.K, c.ldb, BN, kBK)) return -12;
-  if (make_tmap_2d_b16(&tC, c.C, c.M, c.N, c.ldc, 32, 64)) return -13;
+  if (c.conv) { if (make_tmap_nhwc_b16(&tC, c.C, c.img_n, c.img_h, c.img_w, c.N, 2, kConvTileW)) return -13; }
+  else if (make_tmap_2d_b16(&tC, c.C, c.M, c.N, c.ldc, 32, 64)) return -13;
   if (MODE == MODE_Z) { if (make_tmap_2d_b16(&tX, c.Z, c.M, c.N, c.ldz, 32, 64)) return -14; }
   else if (MODE == MODE_AUX) { if (make_tmap_2d_b16(&tX, c.AUX, c.M, c.N, c.ldaux, 32, 64)) return -15; }
   else tX = tC;
@@ -390,6 +421,14 @@ inline int launch_gemm_tn(const GemmCall& c, int num_sms, int* err_word, cudaStr
   g.num_m_tiles = (c.M + kBM - 1) / kBM;
   g.num_n_tiles = (c.N + BN - 1) / BN;
   g.err = err_word;
+  g.conv = c.conv; g.cin = c.cin; g.ksize = c.ksize; g.pad = c.ksize / 2; g.img_h = c.img_h;
+  g.tiles_x = g.tiles_y = 0;
+  if (c.conv) {
+    g.tiles_x = (c.img_w + kConvTileW - 1) / kConvTileW;
+    g.tiles_y = (c.img_h + kConvTileH - 1) / kConvTileH;
+    g.num_m_tiles = c.img_n * g.tiles_x * g.tiles_y;
+    g.M = g.num_m_tiles * kBM;            // every row of a tile is "in range"; the copy engine clips at image edges
+  }
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_tn_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=

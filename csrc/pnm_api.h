@@ -147,6 +147,12 @@ int pnm_natten_bwd(const void* q, const void* k, const void* v, const void* dout
                    int D, int nd, const int* shape, const int* kernel, const int* dilation, float scale, int dtype,
                    void* stream);
 
+// Stride-1 "same" 2-D convolution of a channels-last bf16 image as an implicit GEMM on the tensor cores (gemm_tn.cuh):
+// x [n, h, w, cin], weight [cout, ksize*ksize*cin] (tap-major), y [n, h, w, cout]; bias fp32 [cout] or null;
+// act as in pnm_gemm_tn.  cin % 64 == 0, cout % 8 == 0, odd ksize <= 7.
+int pnm_conv2d_nhwc(const void* x, const void* weight, void* y, int n, int h, int w, int cin, int cout, int ksize,
+                    const float* bias, int act, int bn, int max_ctas, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -72,6 +72,28 @@ int pnm_gemm_tn(const void* A, int lda, const void* A2, int lda2, const void* A3
   return pnm::launch_gemm_tn<128, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
 }
 
+
+// y[n, h, w, :] = act(sum over taps and input channels of x[n, h + dy, w + dx, :] W[:, tap, :] + bias): stride-1 "same"
+// convolution of a channels-last bf16 image on the tensor cores.  weight: [cout, ksize*ksize*cin] bf16, tap-major
+// (tap = ky * ksize + kx).  Requires cin % 64 == 0, cout % 8 == 0, odd ksize.
+int pnm_conv2d_nhwc(const void* x, const void* weight, void* y, int n, int h, int w, int cin, int cout, int ksize,
+                    const float* bias, int act, int bn, int max_ctas, void* stream) {
+  if (ensure_init()) return -1;
+  if (n <= 0 || h <= 0 || w <= 0 || cin <= 0 || cout <= 0) return -2;
+  if ((cin % 64) || (cout % 8) || !(ksize & 1) || ksize < 1 || ksize > 7) return -3;
+  pnm::GemmCall c{};
+  c.A = x; c.lda = cin; c.A2 = nullptr; c.lda2 = 0; c.A3 = nullptr; c.lda3 = 0;
+  c.B = weight; c.ldb = ksize * ksize * cin; c.C = y; c.ldc = cout; c.Z = nullptr; c.ldz = 0; c.AUX = nullptr; c.ldaux = 0;
+  c.M = n * h * w; c.N = cout; c.K = ksize * ksize * cin; c.K1 = c.K; c.K2 = c.K;
+  c.bias = bias; c.scale = nullptr; c.group_out = nullptr; c.act = act; c.aux_mode = 0; c.scale_post = 0;
+  c.max_ctas = max_ctas;
+  c.conv = 1; c.img_n = n; c.img_h = h; c.img_w = w; c.cin = cin; c.ksize = ksize;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 0) bn = (cout > 128) ? 256 : 128;
+  if (bn == 256) return pnm::launch_gemm_tn<256, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+  return pnm::launch_gemm_tn<128, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+}
+
 int pnm_gemm_nt(const void* A, int lda, const void* B, int ldb, float* out, int ldo, float* colsum, int M, int Na,
                 int Nb, int max_ctas, void* stream) {
   if (ensure_init()) return -1;

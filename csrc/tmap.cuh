@@ -47,4 +47,22 @@ inline int make_tmap_2d_b16(CUtensorMap* out, const void* base, uint64_t rows, u
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
+// 4-D channels-last image tensor [N, H, W, C] of 16-bit elements; box = [1, box_h, box_w, 64 channels], 128-byte
+// swizzle: in shared memory the box is box_h * box_w rows of 128 bytes (x fastest), i.e. the layout of a 2-D
+// [rows, 64] tile, so the GEMM's K-major operand descriptors apply unchanged.  Returns 0 on success.
+inline int make_tmap_nhwc_b16(CUtensorMap* out, const void* base, uint64_t N, uint64_t H, uint64_t W, uint64_t C,
+                              uint32_t box_h, uint32_t box_w) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((C * 2) & 15) || C < 64) return -2;
+  cuuint64_t dims[4] = {C, W, H, N};
+  cuuint64_t strides[3] = {C * 2, W * C * 2, H * W * C * 2};
+  cuuint32_t box[4] = {64, box_w, box_h, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
 }  // namespace pnm

@@ -16,9 +16,20 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ...ops import conv as _conv
+
 from .activations import get_activation
 from .utils.utils import _validate_amp
 from .utils.weight_init import _weight_init
+
+
+
+def _tensor_core_conv_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Use the library's implicit-GEMM convolution: CUDA, channels-last, bf16 (or bf16 autocast), shapes it covers."""
+    if not (x.is_cuda and x.dim() == 4 and x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous()):
+        return False
+    bf16 = x.dtype == torch.bfloat16 or (torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16)
+    return bf16 and _conv.supported(x, w)
 
 
 class Conv2d(nn.Module):
@@ -72,6 +83,9 @@ class Conv2d(nn.Module):
             if self.down:
                 x = F.conv2d(x, f.tile([self.in_channels, 1, 1, 1]), groups=self.in_channels, stride=2, padding=f_pad)
             if w is not None:
+                if _tensor_core_conv_ok(x, w):
+                    # channels-last bf16 on a GPU: implicit-GEMM kernel, bias added in its epilogue
+                    return _conv.conv2d_same(x, w, b)
                 x = F.conv2d(x, w, padding=w_pad, bias=fb)
         if b is not None and not self.fused_conv_bias:
             x = x + b.reshape(1, -1, 1, 1)

@@ -2,7 +2,9 @@
 
 ``python -m physicsnemo_b200.ops.microbench <kernel> [--m ROWS] [--iters N]`` with ``<kernel>``
 one of ``gemm_tn``, ``gemm_tn_gelu_z``, ``gemm_tn_softmax``, ``gemm_tn_aux``, ``gemm_nt``,
-``layernorm``, ``all``.  Inputs are larger than the 126 MB L2 at the default size; the small
+``layernorm``, ``all``; ``conv`` (implicit-GEMM 3×3 convolutions at U-Net shapes next to the framework's
+cuDNN call on the same channels-last bf16 tensors) and ``groupnorm`` (GroupNorm+SiLU forward / backward in both
+memory formats next to ``F.group_norm`` + ``F.silu``).  Inputs are larger than the 126 MB L2 at the default size; the small
 sizes (``--m 262144``) are meant for profiler captures.  Denominators come from
 ``MEASURED_PEAKS.json`` at the repository root when present (measured copy bandwidth and
 cuBLAS bf16 throughput), else from the fallback 6.65 TB/s / 1.59 PFLOP/s.
@@ -70,6 +72,47 @@ def cases(M):
     return out
 
 
+def conv_cases():
+    import torch.nn.functional as F
+
+    from . import conv as C
+
+    out = {}
+    for name, (n, c, h, w, co) in {"c128_512": (8, 128, 512, 512, 128), "c256_256": (8, 256, 256, 256, 256),
+                                   "c512_128": (8, 512, 128, 128, 512), "c128_1024x256": (2, 128, 1024, 256, 128)}.items():
+        x = _r(n, c, h, w).contiguous(memory_format=torch.channels_last)
+        wt = _r(co, c, 3, 3, scale=(9 * c) ** -0.5)
+        b = torch.randn(co, device="cuda")
+        flops = 2.0 * n * h * w * 9 * c * co
+        nbytes = (n * h * w * (c + co) + 9 * c * co) * 2
+        out[f"conv3x3_{name}"] = (lambda x=x, wt=wt, b=b: C.conv2d_same(x, wt, b), flops, nbytes)
+        out[f"cudnn3x3_{name}"] = (lambda x=x, wt=wt, b=b: F.conv2d(x, wt, b.to(torch.bfloat16), padding=1), flops, nbytes)
+    return out
+
+
+def groupnorm_cases():
+    import torch.nn.functional as F
+
+    from . import group_norm as GN
+
+    out = {}
+    n, c, h, w, g = 8, 128, 512, 512, 32
+    wgt, bias = torch.rand(c, device="cuda") + 0.5, torch.randn(c, device="cuda")
+    for fmt, tag in ((torch.contiguous_format, "cf"), (torch.channels_last, "cl")):
+        x = _r(n, c, h, w).contiguous(memory_format=fmt)
+        dy = _r(n, c, h, w).contiguous(memory_format=fmt)
+        nbytes = x.numel() * 2 * 3                          # stats pass + normalise pass reads, one write
+        out[f"groupnorm_silu_fwd_{tag}"] = (lambda x=x: GN.group_norm(x, g, wgt, bias, 1e-5, silu=True), 0.0, nbytes)
+        out[f"torch_groupnorm_silu_fwd_{tag}"] = (lambda x=x: F.silu(F.group_norm(x, g, wgt.to(x.dtype), bias.to(x.dtype), 1e-5)), 0.0, nbytes)
+
+        def fwd_bwd(x=x, dy=dy):
+            xr = x.detach().requires_grad_(True)
+            GN.group_norm(xr, g, wgt, bias, 1e-5, silu=True).backward(dy)
+
+        out[f"groupnorm_silu_fwd_bwd_{tag}"] = (fwd_bwd, 0.0, x.numel() * 2 * 8)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel")
@@ -78,8 +121,15 @@ def main():
     args = ap.parse_args()
     hbm, tflops, src = _peaks()
     flush = torch.empty(256 * 1024 * 1024 // 4, device="cuda")
-    table = cases(args.m)
-    names = list(table) if args.kernel == "all" else [args.kernel]
+    if args.kernel == "conv":
+        table = conv_cases()
+        names = list(table)
+    elif args.kernel == "groupnorm":
+        table = groupnorm_cases()
+        names = list(table)
+    else:
+        table = cases(args.m)
+        names = list(table) if args.kernel == "all" else [args.kernel]
     for name in names:
         fn, flops, nbytes = table[name]
         ms = _time(fn, args.iters, flush)

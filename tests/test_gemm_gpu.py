@@ -125,3 +125,29 @@ def test_mlp_chain_matches_torch():
     for g, r in zip(got, [xr.grad, rr.grad] + [t.grad for t in wr + br]):
         _close(g, r, tol=4e-2)
     assert ops.device_error() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(2, 64, 128, 24, 40, 3), (1, 128, 64, 17, 33, 3), (3, 64, 72, 8, 16, 1), (1, 192, 256, 40, 24, 5)])
+def test_conv2d_same_implicit_gemm(shape):
+    from physicsnemo_b200.ops import conv as C
+
+    n, cin, cout, h, w, k = shape
+    torch.manual_seed(0)
+    x = torch.randn(n, cin, h, w, device="cuda").to(memory_format=torch.channels_last).requires_grad_(True)
+    wt = (torch.randn(cout, cin, k, k, device="cuda") / (cin * k * k) ** 0.5).requires_grad_(True)
+    b = torch.randn(cout, device="cuda").requires_grad_(True)
+    assert C.supported(x, wt)
+    y = C.conv2d_same(x, wt, b)
+    assert y.shape == (n, cout, h, w) and y.is_contiguous(memory_format=torch.channels_last)
+    xr, wr, br = (t.detach().clone().requires_grad_(True) for t in (x, wt, b))
+    ref = torch.nn.functional.conv2d(xr, wr, br, padding=k // 2)
+    assert (y.float() - ref).abs().max() < 4e-2
+    dy = torch.randn_like(ref)
+    y.backward(dy.to(y.dtype))
+    ref.backward(dy)
+    assert (x.grad - xr.grad).abs().max() < 6e-2 * max(1.0, float(xr.grad.abs().max()))
+    assert (wt.grad - wr.grad).abs().max() < 3e-2 * float(wr.grad.abs().max())
+    assert (b.grad - br.grad).abs().max() < 2e-2 * float(br.grad.abs().max())
+    fused = C.conv2d_same(x.detach(), wt.detach(), b.detach(), act="silu")
+    assert (fused.float() - torch.nn.functional.silu(ref.detach())).abs().max() < 4e-2
