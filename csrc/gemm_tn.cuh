@@ -37,17 +37,56 @@ struct GemmArgs {
   // implicit-GEMM convolution (conv != 0): rows of A are output pixels of an NHWC image, tiled 8 x 16 per M tile;
   // K runs over (tap, input channel); the A tile of k-block (tap, c0) is the input window shifted by the tap
   int conv, tiles_x, tiles_y, cin, ksize, pad, img_h;
+  // halo != 0 (3 x 3, img_h % 8 == 0): the image is one horizontal slab of a taller image split over ranks.  The row
+  // above / below the slab comes from the neighbour's published boundary row (a peer-mapped buffer read by plain,
+  // non-multicast TMA loads) once its flag carries halo_epoch; tiles that need it are scheduled last.
+  int halo, has_up, has_down, img_n;
+  const uint32_t* flag_up;
+  const uint32_t* flag_down;
+  uint32_t halo_epoch;
 };
 
 constexpr int kConvTileH = 8;
 constexpr int kConvTileW = 16;
 
 __device__ __forceinline__ void conv_tile_origin(const GemmArgs& g, int mt, int& n, int& y0, int& x0) {
+  if (g.halo) {
+    // interior-first order: tile rows 1 .. tiles_y-2 of every image, then row 0 and row tiles_y-1 (the halo users)
+    const int per_row = g.img_n * g.tiles_x;
+    const int o = mt / per_row, r = mt - o * per_row;
+    n = r / g.tiles_x;
+    x0 = (r % g.tiles_x) * kConvTileW;
+    const int ty = g.tiles_y <= 2 ? o : (o < g.tiles_y - 2 ? o + 1 : (o == g.tiles_y - 2 ? 0 : g.tiles_y - 1));
+    y0 = ty * kConvTileH;
+    return;
+  }
   const int per_img = g.tiles_x * g.tiles_y;
   n = mt / per_img;
   const int r = mt - n * per_img;
   y0 = (r / g.tiles_x) * kConvTileH;
   x0 = (r % g.tiles_x) * kConvTileW;
+}
+
+// Bounded wait (one thread) until a flag written by another GPU reaches `epoch`.
+__device__ __forceinline__ bool wait_remote_flag(const uint32_t* flag, uint32_t epoch, volatile int* abort_flag, int* err_word) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+  if (int32_t(v - epoch) >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (int32_t(v - epoch) >= 0) return true;
+    if ((++spins & 0xffu) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+        atomicCAS(err_word, 0, ERR_WAIT_PEER);
+        *abort_flag = 1;
+        __threadfence_block();
+        return false;
+      }
+    }
+  }
 }
 
 constexpr int kGemmThreads = 320;
@@ -135,6 +174,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      bool up_ready = false, down_ready = false;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         const int mt = tile / g.num_n_tiles, nt = tile % g.num_n_tiles;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -149,7 +189,26 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int n, y0, x0;
             conv_tile_origin(g, mt, n, y0, x0);
             const int tap = k / g.cin, c0 = k - tap * g.cin;
-            tma_load_4d(sa, &tmA, &full[s], c0, x0 + tap % g.ksize - g.pad, y0 + tap / g.ksize - g.pad, n);
+            const int xs = x0 + tap % g.ksize - g.pad, ys = y0 + tap / g.ksize - g.pad;
+            if (g.halo && ys < 0 && g.has_up) {
+              // box rows -1 .. 6: row -1 is the upper neighbour's bottom row, rows 0 .. 6 are local
+              if (!up_ready) {
+                if (!wait_remote_flag(g.flag_up, g.halo_epoch, abort_flag, g.err)) { ok = false; break; }
+                up_ready = true;
+              }
+              tma_load_4d(sa, &tmA3, &full[s], c0, xs, 0, n);
+              tma_load_4d(sa + kConvTileW * 128, &tmA2, &full[s], c0, xs, 0, n);
+            } else if (g.halo && ys + kConvTileH > g.img_h && g.has_down) {
+              // box rows H-7 .. H: rows H-7 .. H-1 are local, row H is the lower neighbour's top row
+              if (!down_ready) {
+                if (!wait_remote_flag(g.flag_down, g.halo_epoch, abort_flag, g.err)) { ok = false; break; }
+                down_ready = true;
+              }
+              tma_load_4d(sa, &tmA2, &full[s], c0, xs, ys, n);
+              tma_load_4d(sa + (kConvTileH - 1) * kConvTileW * 128, &tmX, &full[s], c0, xs, 0, n);
+            } else {
+              tma_load_4d(sa, &tmA, &full[s], c0, xs, ys, n);
+            }
           } else if (k < g.K1) tma_load_2d(sa, &tmA, &full[s], k, mt * kBM);
           else if (k < g.K2) tma_load_2d(sa, &tmA2, &full[s], k - g.K1, mt * kBM);
           else tma_load_2d(sa, &tmA3, &full[s], k - g.K2, mt * kBM);
@@ -394,6 +453,11 @@ struct GemmCall {
   int max_ctas;  // 0 = number of SMs
   // convolution: A is an NHWC image [img_n, img_h, img_w, cin], B holds [N, ksize*ksize*cin] (tap-major), C is NHWC
   int conv = 0, img_n = 0, img_h = 0, img_w = 0, cin = 0, ksize = 0;
+  // halo exchange fused into the convolution (see GemmArgs): boundary rows published by the neighbours [img_n, 1, img_w, cin]
+  int halo = 0;
+  const void* up_rows = nullptr; const void* down_rows = nullptr;
+  const uint32_t* flag_up = nullptr; const uint32_t* flag_down = nullptr;
+  uint32_t halo_epoch = 0;
 };
 
 template <int BN, int MODE>
@@ -403,17 +467,24 @@ inline int launch_gemm_tn(const GemmCall& c, int num_sms, int* err_word, cudaStr
   if (c.conv) {
     if (MODE != MODE_PLAIN) return -19;
     if (make_tmap_nhwc_b16(&tA, c.A, c.img_n, c.img_h, c.img_w, c.cin, kConvTileH, kConvTileW)) return -10;
+    if (c.halo) {
+      if (c.ksize != 3 || (c.img_h % kConvTileH)) return -20;
+      if (make_tmap_nhwc_b16(&tA2, c.A, c.img_n, c.img_h, c.img_w, c.cin, kConvTileH - 1, kConvTileW)) return -11;
+      if (c.up_rows && make_tmap_nhwc_b16(&tA3, c.up_rows, c.img_n, 1, c.img_w, c.cin, 1, kConvTileW)) return -18;
+      if (c.down_rows && make_tmap_nhwc_b16(&tX, c.down_rows, c.img_n, 1, c.img_w, c.cin, 1, kConvTileW)) return -15;
+    }
   } else if (make_tmap_2d_b16(&tA, c.A, c.M, c.K1, c.lda, kBM, kBK)) return -10;
+  const bool halo = c.conv && c.halo;
   if (c.K2 > c.K1) { if (make_tmap_2d_b16(&tA2, c.A2, c.M, c.K2 - c.K1, c.lda2, kBM, kBK)) return -11; }
-  else tA2 = tA;
+  else if (!halo) tA2 = tA;
   if (c.K > c.K2) { if (make_tmap_2d_b16(&tA3, c.A3, c.M, c.K - c.K2, c.lda3, kBM, kBK)) return -18; }
-  else tA3 = tA;
+  else if (!(halo && c.up_rows)) tA3 = tA;
   if (make_tmap_2d_b16(&tB, c.B, c.N, c.K, c.ldb, BN, kBK)) return -12;
   if (c.conv) { if (make_tmap_nhwc_b16(&tC, c.C, c.img_n, c.img_h, c.img_w, c.N, 2, kConvTileW)) return -13; }
   else if (make_tmap_2d_b16(&tC, c.C, c.M, c.N, c.ldc, 32, 64)) return -13;
   if (MODE == MODE_Z) { if (make_tmap_2d_b16(&tX, c.Z, c.M, c.N, c.ldz, 32, 64)) return -14; }
   else if (MODE == MODE_AUX) { if (make_tmap_2d_b16(&tX, c.AUX, c.M, c.N, c.ldaux, 32, 64)) return -15; }
-  else tX = tC;
+  else if (!(halo && c.down_rows)) tX = tC;
   GemmArgs g;
   g.M = c.M; g.N = c.N; g.K = c.K; g.K1 = c.K1; g.K2 = c.K2;
   g.bias = c.bias; g.scale = c.scale; g.group_out = c.group_out;
@@ -423,6 +494,8 @@ inline int launch_gemm_tn(const GemmCall& c, int num_sms, int* err_word, cudaStr
   g.err = err_word;
   g.conv = c.conv; g.cin = c.cin; g.ksize = c.ksize; g.pad = c.ksize / 2; g.img_h = c.img_h;
   g.tiles_x = g.tiles_y = 0;
+  g.halo = c.conv ? c.halo : 0; g.has_up = c.up_rows != nullptr; g.has_down = c.down_rows != nullptr; g.img_n = c.img_n;
+  g.flag_up = c.flag_up; g.flag_down = c.flag_down; g.halo_epoch = c.halo_epoch;
   if (c.conv) {
     g.tiles_x = (c.img_w + kConvTileW - 1) / kConvTileW;
     g.tiles_y = (c.img_h + kConvTileH - 1) / kConvTileH;

@@ -153,6 +153,16 @@ int pnm_natten_bwd(const void* q, const void* k, const void* v, const void* dout
 int pnm_conv2d_nhwc(const void* x, const void* weight, void* y, int n, int h, int w, int cin, int cout, int ksize,
                     const float* bias, int act, int bn, int max_ctas, void* stream);
 
+// Halo exchange fused into the 3 x 3 convolution of a height-sharded image (gemm_tn.cuh, conv mode with halo):
+// pnm_halo_publish copies this slab's first / last rows into its mailbox and raises the neighbours' flags;
+// pnm_conv2d_nhwc_halo reads the neighbours' rows (peer-mapped) inside the convolution kernel once their flags carry
+// `epoch`; interior tiles are computed first.  Null row / flag pointers mark the outer edges (zero padding).
+int pnm_halo_publish(const void* x, void* top, void* bottom, int n, int h, int w, int c, void* flag_at_up, void* flag_at_down,
+                     unsigned int epoch, void* counter, void* stream);
+int pnm_conv2d_nhwc_halo(const void* x, const void* weight, void* y, int n, int h, int w, int cin, int cout, const float* bias,
+                         int act, const void* up_rows, const void* down_rows, const void* flag_up, const void* flag_down,
+                         unsigned int epoch, int bn, int max_ctas, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,6 +1,7 @@
 // Single translation unit of the sm_100a kernel library.  Exposes a plain C ABI (raw device
 // pointers + a CUDA stream) that the Python layer binds with ctypes; no dependency on the
 // PyTorch headers, so the whole library rebuilds in seconds.
+#include <algorithm>
 #include "common.cuh"
 #include "tmap.cuh"
 #include "gemm_tn.cuh"
@@ -88,6 +89,69 @@ int pnm_conv2d_nhwc(const void* x, const void* weight, void* y, int n, int h, in
   c.bias = bias; c.scale = nullptr; c.group_out = nullptr; c.act = act; c.aux_mode = 0; c.scale_post = 0;
   c.max_ctas = max_ctas;
   c.conv = 1; c.img_n = n; c.img_h = h; c.img_w = w; c.cin = cin; c.ksize = ksize;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 0) bn = (cout > 128) ? 256 : 128;
+  if (bn == 256) return pnm::launch_gemm_tn<256, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+  return pnm::launch_gemm_tn<128, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+}
+
+namespace pnm {
+// Copies the first and the last image row of every image of x [n, h, w, c] (bf16) into this rank's mailbox, then raises
+// the flags in the neighbours' buffers: the block that finishes last does the two release stores.
+__global__ void __launch_bounds__(256) halo_publish_kernel(const uint4* __restrict__ x, uint4* __restrict__ top, uint4* __restrict__ bottom,
+                                                          int n, int h, long long row_vecs /* w*c/8 */, uint32_t* flag_at_up,
+                                                          uint32_t* flag_at_down, uint32_t epoch, unsigned int* counter) {
+  const long long total = 2LL * n * row_vecs;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int side = (int)(i / (n * row_vecs));
+    const long long r = i - side * n * row_vecs;
+    const long long img = r / row_vecs, v = r - img * row_vecs;
+    const uint4 val = x[(img * h + (side ? h - 1 : 0)) * row_vecs + v];
+    (side ? bottom : top)[img * row_vecs + v] = val;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(counter, 1u) == gridDim.x - 1) {
+      *counter = 0;
+      __threadfence_system();
+      if (flag_at_up) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag_at_up), "r"(epoch) : "memory");
+      if (flag_at_down) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag_at_down), "r"(epoch) : "memory");
+    }
+  }
+}
+}  // namespace pnm
+
+// Publish the boundary rows of a height slab for the neighbours' halo reads.  top / bottom: this rank's mailbox blocks
+// [n, 1, w, c]; flag_at_up / flag_at_down: peer-mapped addresses of the flags the neighbours wait on (null at the edges).
+int pnm_halo_publish(const void* x, void* top, void* bottom, int n, int h, int w, int c, void* flag_at_up, void* flag_at_down,
+                     unsigned int epoch, void* counter, void* stream) {
+  if (ensure_init()) return -1;
+  if (n <= 0 || h <= 0 || ((long long)w * c) % 8) return -2;
+  const long long row_vecs = (long long)w * c / 8, total = 2LL * n * row_vecs;
+  const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, 4 * g_num_sms);
+  pnm::halo_publish_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(top), reinterpret_cast<uint4*>(bottom), n, h, row_vecs,
+      reinterpret_cast<uint32_t*>(flag_at_up), reinterpret_cast<uint32_t*>(flag_at_down), epoch,
+      reinterpret_cast<unsigned int*>(counter));
+  return cudaGetLastError() == cudaSuccess ? 0 : -52;
+}
+
+// pnm_conv2d_nhwc for a height slab: the rows above / below come from the neighbours' published rows (up_rows / down_rows,
+// peer-mapped, null at the outer edges) once flag_up / flag_down (local memory) carry `epoch`.  3 x 3 only, h % 8 == 0.
+int pnm_conv2d_nhwc_halo(const void* x, const void* weight, void* y, int n, int h, int w, int cin, int cout, const float* bias,
+                         int act, const void* up_rows, const void* down_rows, const void* flag_up, const void* flag_down,
+                         unsigned int epoch, int bn, int max_ctas, void* stream) {
+  if (ensure_init()) return -1;
+  if (n <= 0 || h <= 0 || w <= 0 || (cin % 64) || (cout % 8) || (h % 8)) return -3;
+  pnm::GemmCall c{};
+  c.A = x; c.lda = cin; c.B = weight; c.ldb = 9 * cin; c.C = y; c.ldc = cout;
+  c.M = n * h * w; c.N = cout; c.K = 9 * cin; c.K1 = c.K; c.K2 = c.K;
+  c.bias = bias; c.act = act; c.max_ctas = max_ctas;
+  c.conv = 1; c.img_n = n; c.img_h = h; c.img_w = w; c.cin = cin; c.ksize = 3;
+  c.halo = 1; c.up_rows = up_rows; c.down_rows = down_rows;
+  c.flag_up = reinterpret_cast<const uint32_t*>(flag_up); c.flag_down = reinterpret_cast<const uint32_t*>(flag_down);
+  c.halo_epoch = epoch;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (bn == 0) bn = (cout > 128) ? 256 : 128;
   if (bn == 256) return pnm::launch_gemm_tn<256, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);

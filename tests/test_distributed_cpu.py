@@ -121,3 +121,42 @@ def _dist_afno(rank, world):
 
 def test_distributed_afno_two_ranks():
     run_ranks(_dist_afno, world=2)
+
+
+def _dist_graph(rank, world):
+    import torch
+
+    from physicsnemo_b200.nn.module.gnn_layers.distributed_graph import DistributedGraph, partition_graph_nodewise
+
+    torch.manual_seed(0)
+    n, e = 40, 200
+    dst = torch.randint(0, n, (e,)).sort().values
+    src = torch.randint(0, n, (e,))
+    src[0] = n - 1                                           # make sure the largest id occurs
+    offsets = torch.zeros(n + 1, dtype=torch.long)
+    offsets[1:] = torch.bincount(dst, minlength=n).cumsum(0)
+    for decomp in (False, True):
+        gp = partition_graph_nodewise(offsets, src, world, rank, torch.device("cpu"), matrix_decomp=decomp)
+        g = DistributedGraph(offsets, src, world, graph_partition=gp)
+        feats = torch.arange(n, dtype=torch.float32)[:, None] * torch.tensor([[1.0, 10.0]])
+        part = g.get_src_node_features_in_partition(feats).clone().requires_grad_(True)
+        local = g.get_src_node_features_in_local_graph(part)
+        # local graph: edge j of this rank reads row local_indices[j]; it must be the feature of its global source
+        edge_ids = gp.map_partitioned_edge_ids_to_global.long()
+        assert torch.equal(local[gp.local_indices.long()], feats[src[edge_ids]])
+        assert gp.local_offsets[-1] == edge_ids.numel() == gp.num_local_indices
+        # aggregate onto the local destinations and compare with the global aggregation
+        agg = torch.zeros(gp.num_local_dst_nodes, 2).index_add_(
+            0, torch.repeat_interleave(torch.arange(gp.num_local_dst_nodes), gp.local_offsets.diff().long()),
+            local[gp.local_indices.long()])
+        ref = torch.zeros(n, 2).index_add_(0, dst, feats[src])
+        assert torch.allclose(agg, ref[gp.map_partitioned_dst_ids_to_global.long()])
+        assert torch.allclose(g.get_global_dst_node_features(agg), ref)
+        local.sum().backward()                               # gradient of the halo gather = how often a row was sent
+        assert part.grad.shape == part.shape and float(part.grad.sum()) == 2.0 * sum(row[r] for row in [gp.sizes[rank]] for r in range(world))
+        ef = torch.arange(e, dtype=torch.float32)[:, None]
+        assert torch.equal(g.get_global_edge_features(g.get_edge_features_in_partition(ef)), ef)
+
+
+def test_distributed_graph_two_ranks():
+    run_ranks(_dist_graph, world=2)
