@@ -221,3 +221,27 @@ def test_geotransolver_streams_and_context():
     assert out.shape == (2, 6, 5, 2) and states.shape == (2, 4, 8, 8)
     with pytest.raises(ValueError):
         GeoTransolver(functional_dim=3, out_dim=2, structured_shape=(4, 4), include_local_features=True)
+
+
+def test_healpix_padding_table():
+    from physicsnemo_b200.nn.module.hpx import HEALPixAvgPool, HEALPixLayer, HEALPixPadding, padding_index_table
+
+    n, p = 8, 2
+    idx = padding_index_table(n, p)
+    assert idx.shape == (2, 12, n + 2 * p, n + 2 * p) and int(idx.min()) >= 0 and int(idx.max()) < 12 * n * n
+    # the centre of every padded face is the face itself
+    own = torch.arange(12 * n * n).reshape(12, n, n)
+    assert torch.equal(idx[0, :, p:-p, p:-p], own) and torch.equal(idx[1, :, p:-p, p:-p], own)
+    # only the equatorial faces' free corners average two sources
+    differs = (idx[0] != idx[1]).flatten(1).any(1)
+    assert differs.tolist() == [False] * 4 + [True] * 4 + [False] * 4
+    x = torch.randn(24, 3, n, n, requires_grad=True)
+    y = HEALPixPadding(p)(x)
+    assert y.shape == (24, 3, n + 2 * p, n + 2 * p) and torch.equal(y[:, :, p:-p, p:-p], x)
+    # a constant field stays constant under padding (all weights sum to one)
+    assert torch.allclose(HEALPixPadding(3)(torch.full((12, 1, n, n), 2.5)), torch.full((12, 1, n + 6, n + 6), 2.5))
+    y.sum().backward()
+    assert x.grad.min() >= 1.0                                   # every pixel is used at least by its own centre copy
+    conv = HEALPixLayer(torch.nn.Conv2d, in_channels=3, out_channels=5, kernel_size=3)
+    assert conv(x.detach()).shape == (24, 5, n, n)
+    assert HEALPixAvgPool(pooling=2)(x.detach()).shape == (24, 3, n // 2, n // 2)
