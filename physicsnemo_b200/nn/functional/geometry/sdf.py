@@ -120,6 +120,21 @@ def _sdf_cuda(mesh_vertices, mesh_indices, input_points, max_dist: float = 1e8, 
     return dist.reshape(shape[:-1]).to(dt), cp.reshape(shape).to(dt), face.reshape(shape[:-1])
 
 
+def _winding_cuda(vertices, faces, pts):
+    """Generalized winding number of ``pts [N, 3]`` (exact sum of signed solid angles over all faces) on the GPU."""
+    lib = _lib_bvh()
+    tri = vertices.detach().float()[faces].contiguous()
+    pts = pts.detach().float().contiguous()
+    out = torch.empty(pts.shape[0], dtype=torch.float32, device=pts.device)
+    if pts.shape[0]:
+        e = lib.pnm_winding_number(tri.data_ptr(), pts.data_ptr(), out.data_ptr(), tri.shape[0], pts.shape[0],
+                                   torch.cuda.current_stream().cuda_stream)
+        if e:
+            raise RuntimeError(f"pnm_winding_number failed ({e})")
+        _g.launch_count += 1
+    return out
+
+
 class SignedDistanceField(FunctionSpec):
     @FunctionSpec.register(name="cuda", rank=0)
     def cuda_forward(mesh_vertices, mesh_indices, input_points, max_dist=1e8, use_sign_winding_number=False, bvh=None):
