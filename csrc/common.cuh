@@ -103,6 +103,13 @@ __device__ __forceinline__ void tma_store_2d(const void* smem_src, const CUtenso
                ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
 }
+// 3-D tiled load (x, y, z); coordinates outside the tensor read as zero.
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 // 4-D tiled load / store (channels, x, y, image): used by the implicit-GEMM convolution, where a tile of output pixels
 // reads its shifted input window straight from the NHWC tensor; coordinates outside the tensor read as zero.
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c, int x, int y, int n) {

@@ -1,0 +1,336 @@
+// Fused attention forward on the 5th-generation tensor cores: O = softmax(scale * Q K^T [+ causal mask]) V.
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the keys in tiles of 128:
+//
+//   warp 4     TMA producer: Q once, then K and V tiles into two-stage rings (128-byte-swizzled 64-wide blocks)
+//   warp 5     MMA issuer:   S_j = Q K_j^T   -> TMEM columns [0,256), double buffered
+//                            O_j = P_j V_j   -> TMEM columns [256, 256 + 2 D), double buffered (fresh tile, no accumulate)
+//   warps 0-3  softmax:      thread r owns query row r (= TMEM lane r).  It reads S_j twice from TMEM (row maximum, then
+//                            exponentials), writes P_j as bf16 into the swizzled K-major operand layout in shared memory,
+//                            and keeps the running maximum, the running sum and the output row (D fp32 registers); the
+//                            product tile O_{j-1} is folded into the registers while the tensor core works on tile j.
+//
+// S_{j+1} is issued before P_j is waited for, so the QK^T product of the next tile overlaps the softmax of this one.
+// Every reuse of a TMEM or shared-memory buffer is ordered by the p_full / o_full barriers that the loop waits on
+// anyway (see the comments at the waits), which is why there are no separate "empty" barriers for S, P and O.
+//
+// V is consumed either in its natural [keys, D] layout as an MN-major B operand (VT = false) or from a pre-transposed
+// [D, keys] copy as a K-major operand (VT = true).  Rows of K / V beyond the sequence read as zero through TMA and are
+// masked to -inf before the softmax.  All barrier waits are bounded; a wait that runs out records an error code,
+// releases the other waiters of the CTA, and the CTA still frees its TMEM and returns.
+#pragma once
+#include <cuda_bf16.h>
+#include <math.h>
+
+#include "common.cuh"
+#include "tmap.cuh"
+
+namespace pnm {
+
+struct FlashArgs {
+  CUtensorMap tmQ, tmK, tmV;
+  __nv_bfloat16* out;  // [BH, Sq, D]
+  float* lse;          // [BH, Sq] natural-log sum of exponentials, may be null
+  int Sq, Skv, n_qtiles;
+  float scale_log2;    // softmax scale * log2(e)
+  int causal;
+  int* err;
+};
+
+constexpr int kFaThreads = 192;
+constexpr int kFaBarBytes = 256;
+
+template <int D>
+constexpr int flash_smem_bytes() { return 1024 + 5 * (128 * D * 2) + 2 * (128 * 128 * 2) + kFaBarBytes; }
+
+// Bounded wait that never raises the abort flag: used to let copies in flight land before an aborted CTA leaves.
+__device__ __forceinline__ void mbar_drain(uint64_t* bar, uint32_t parity) {
+  const unsigned long long t0 = globaltimer_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (globaltimer_ns() - t0 > kWaitBudgetNs) break;
+  }
+}
+
+template <int D, bool VT>
+__global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_constant__ FlashArgs g) {
+  static_assert(D == 64 || D == 128, "head dimension 64 or 128");
+  constexpr int KB = D / 64;
+  constexpr int TILE = 128 * D * 2;   // bytes of a Q, K or V tile
+  constexpr int PT = 128 * 128 * 2;   // bytes of a P tile
+  constexpr int BLK = 128 * 128;      // bytes of a [128 rows x 64] block
+  extern __shared__ uint8_t fa_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = base;
+  uint8_t* sK = sQ + TILE;
+  uint8_t* sV = sK + 2 * TILE;
+  uint8_t* sP = sV + 2 * TILE;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(sP + 2 * PT);
+  uint64_t* q_full = bar;
+  uint64_t* k_full = bar + 1;
+  uint64_t* k_empty = bar + 3;
+  uint64_t* v_full = bar + 5;
+  uint64_t* v_empty = bar + 7;
+  uint64_t* s_full = bar + 9;
+  uint64_t* p_full = bar + 11;
+  uint64_t* o_full = bar + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x / g.n_qtiles;
+  const int qt = g.n_qtiles - 1 - (blockIdx.x % g.n_qtiles);   // long (late) causal rows first
+  const int q0 = qt * 128;
+  int T = (g.Skv + 127) >> 7;
+  if (g.causal) T = min(T, qt + 1);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 128);
+      mbar_init(&o_full[s], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&g.tmQ);
+    tma_prefetch_desc(&g.tmK);
+    tma_prefetch_desc(&g.tmV);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      mbar_expect_tx(q_full, TILE);
+      for (int kb = 0; kb < KB; ++kb) tma_load_3d(sQ + kb * BLK, &g.tmQ, q_full, kb * 64, q0, bh);
+      int issued = 0;
+      for (int j = 0; j < T; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, g.err, ERR_WAIT_EMPTY)) break;
+        mbar_expect_tx(&k_full[s], TILE);
+        for (int kb = 0; kb < KB; ++kb) tma_load_3d(sK + s * TILE + kb * BLK, &g.tmK, &k_full[s], kb * 64, j * 128, bh);
+        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, g.err, ERR_WAIT_EMPTY)) { issued = -(j + 1); break; }
+        mbar_expect_tx(&v_full[s], TILE);
+        if (VT) {
+          for (int kb = 0; kb < 2; ++kb)
+            tma_load_3d(sV + s * TILE + kb * (D * 128), &g.tmV, &v_full[s], j * 128 + kb * 64, 0, bh);
+        } else {
+          for (int kb = 0; kb < KB; ++kb)
+            tma_load_3d(sV + s * TILE + kb * BLK, &g.tmV, &v_full[s], kb * 64, j * 128, bh);
+        }
+        issued = j + 1;
+      }
+      if (*abort_flag) {
+        // let the copies that were issued land before the CTA's shared memory goes away
+        mbar_drain(q_full, 0);
+        const int nk = issued < 0 ? -issued : issued, nv = issued < 0 ? -issued - 1 : issued;
+        for (int j = max(nk - 2, 0); j < nk; ++j) mbar_drain(&k_full[j & 1], (j >> 1) & 1);
+        for (int j = max(nv - 2, 0); j < nv; ++j) mbar_drain(&v_full[j & 1], (j >> 1) & 1);
+      }
+    }
+  } else if (warp == 5) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, D, false, !VT);
+      bool ok = mbar_wait(q_full, 0, abort_flag, g.err, ERR_WAIT_FULL);
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!mbar_wait(&k_full[s], (j >> 1) & 1, abort_flag, g.err, ERR_WAIT_FULL)) return false;
+        tc_fence_after();
+        const uint32_t d = tmem_base + s * 128;
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+          const uint64_t ad = make_smem_desc(smem_u32(sQ + kb * BLK), 16, 1024, 2);
+          const uint64_t bd = make_smem_desc(smem_u32(sK + s * TILE + kb * BLK), 16, 1024, 2);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_f16(d, ad + 2 * k, bd + 2 * k, idesc_s, (kb | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(&k_empty[s]);
+        umma_commit(&s_full[s]);
+        return true;
+      };
+      if (ok && T > 0) ok = issue_qk(0);
+      for (int j = 0; ok && j < T; ++j) {
+        // S buffer (j+1)&1 was last read by the softmax of tile j-1, which ended before p_full of tile j-1 completed
+        if (j + 1 < T && !issue_qk(j + 1)) { ok = false; break; }
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        // p_full of tile j also means: every thread folded O_{j-2} into its registers, so O buffer s is free
+        if (!mbar_wait(&p_full[s], ph, abort_flag, g.err, ERR_WAIT_AUX)) { ok = false; break; }
+        if (!mbar_wait(&v_full[s], ph, abort_flag, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d = tmem_base + 256 + s * D;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint64_t ad = make_smem_desc(smem_u32(sP + s * PT + (k >> 2) * BLK), 16, 1024, 2) + 2 * (k & 3);
+          uint64_t bd;
+          if (VT) bd = make_smem_desc(smem_u32(sV + s * TILE + (k >> 2) * (D * 128)), 16, 1024, 2) + 2 * (k & 3);
+          else bd = make_smem_desc(smem_u32(sV + s * TILE + k * 2048), BLK, 1024, 2);   // 16 key rows per step
+          umma_f16(d, ad, bd, idesc_o, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&v_empty[s]);
+        umma_commit(&o_full[s]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- softmax rows
+    const int row = threadIdx.x;
+    const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16);
+    const float c = g.scale_log2;
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    float m = -INFINITY, l = 0.f, alpha_pend = 1.f;
+    bool ok = true;
+
+    auto fold = [&](int t, float a) -> bool {
+      const int s = t & 1;
+      // the TMEM loads below are warp-collective: the warp leaves together or not at all
+      if (!__all_sync(0xffffffffu, mbar_wait(&o_full[s], (t >> 1) & 1, abort_flag, g.err, ERR_WAIT_TMEM_FULL))) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int cc = 0; cc < D / 32; ++cc) {
+        float v[32];
+        tmem_ld32(lane_addr + 256 + s * D + cc * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[cc * 32 + i] = fmaf(o[cc * 32 + i], a, v[i]);
+      }
+      return true;
+    };
+
+    for (int j = 0; j < T; ++j) {
+      const int s = j & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, g.err, ERR_WAIT_TMEM_FULL))) { ok = false; break; }
+      tc_fence_after();
+      const bool edge = (j * 128 + 128 > g.Skv) || (g.causal && j * 128 + 127 > q0);
+      int lim = g.Skv - j * 128;
+      if (g.causal) lim = min(lim, q0 + row - j * 128 + 1);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        float v[32];
+        tmem_ld32(lane_addr + s * 128 + cc * 32, v);
+        tmem_ld_wait();
+        if (edge) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (cc * 32 + i >= lim) v[i] = -INFINITY;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+      }
+      const float m_new = fmaxf(m, mx * c);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = ex2_fast(m - m_use);
+      float rs = 0.f;
+      // P buffer s was last read by the product of tile j-2, whose o_full this thread has already waited for
+      uint8_t* prow = sP + s * PT + row * 128;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        float v[32];
+        tmem_ld32(lane_addr + s * 128 + cc * 32, v);
+        tmem_ld_wait();
+        if (edge) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (cc * 32 + i >= lim) v[i] = -INFINITY;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          v[i] = ex2_fast(fmaf(v[i], c, -m_use));
+          rs += v[i];
+        }
+        uint8_t* blk = prow + (cc >> 1) * BLK;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 u;
+          u.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+          u.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+          u.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+          u.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+          const int chunk = (cc & 1) * 4 + q;
+          *reinterpret_cast<uint4*>(blk + ((chunk ^ (row & 7)) << 4)) = u;
+        }
+      }
+      l = fmaf(l, alpha, rs);
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&p_full[s]);
+      if (j > 0 && !fold(j - 1, alpha_pend)) { ok = false; break; }
+      alpha_pend = alpha;
+      m = m_new;
+    }
+    if (ok && T > 0) ok = fold(T - 1, alpha_pend);
+    if (ok && q0 + row < g.Sq) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = g.out + (size_t(bh) * g.Sq + q0 + row) * D;
+#pragma unroll
+      for (int i = 0; i < D; i += 8) {
+        uint4 u;
+        u.x = pack_bf16x2(o[i + 0] * inv, o[i + 1] * inv);
+        u.y = pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv);
+        u.z = pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv);
+        u.w = pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + i) = u;
+      }
+      if (g.lse) g.lse[size_t(bh) * g.Sq + q0 + row] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+struct FlashCall {
+  const void* q; const void* k; const void* v; void* out; float* lse;
+  int BH, Sq, Skv, ldv;   // ldv: row stride of the transposed V copy (elements), unused otherwise
+  float scale;
+  int causal;
+};
+
+template <int D, bool VT>
+int launch_flash_fwd(const FlashCall& c, int* err, cudaStream_t st) {
+  FlashArgs a;
+  if (make_tmap_3d_b16(&a.tmQ, c.q, c.BH, c.Sq, D, D, uint64_t(c.Sq) * D, 128)) return -2;
+  if (make_tmap_3d_b16(&a.tmK, c.k, c.BH, c.Skv, D, D, uint64_t(c.Skv) * D, 128)) return -2;
+  if (VT) {
+    if (make_tmap_3d_b16(&a.tmV, c.v, c.BH, D, c.Skv, c.ldv, uint64_t(c.ldv) * D, D)) return -2;
+  } else {
+    if (make_tmap_3d_b16(&a.tmV, c.v, c.BH, c.Skv, D, D, uint64_t(c.Skv) * D, 128)) return -2;
+  }
+  a.out = reinterpret_cast<__nv_bfloat16*>(c.out);
+  a.lse = c.lse;
+  a.Sq = c.Sq;
+  a.Skv = c.Skv;
+  a.n_qtiles = (c.Sq + 127) / 128;
+  a.scale_log2 = c.scale * 1.4426950408889634f;
+  a.causal = c.causal;
+  a.err = err;
+  constexpr int smem = flash_smem_bytes<D>();
+  auto kern = flash_fwd_kernel<D, VT>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
+  const long long ctas = (long long)a.n_qtiles * c.BH;
+  if (ctas <= 0 || ctas > 0x7fffffffLL) return -1;
+  kern<<<(unsigned)ctas, kFaThreads, smem, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace pnm

@@ -163,6 +163,12 @@ int pnm_conv2d_nhwc_halo(const void* x, const void* weight, void* y, int n, int 
                          int act, const void* up_rows, const void* down_rows, const void* flag_up, const void* flag_down,
                          unsigned int epoch, int bn, int max_ctas, void* stream);
 
+// out[BH,Sq,D] = softmax(scale * q k^T (+ causal mask, top-left aligned)) v for contiguous bf16 q [BH,Sq,D], k [BH,Skv,D] and
+// v [BH,Skv,D] (v_transposed = 0) or v^T [BH,D,ldv] with ldv >= Skv, ldv % 8 == 0 (v_transposed = 1); D in {64, 128};
+// lse [BH,Sq] (fp32, optional) receives the natural-log sum of exponentials of every row.  See flash_attn.cuh.
+int pnm_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int BH, int Sq, int Skv, int D,
+                       int ldv, float scale, int causal, int v_transposed, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

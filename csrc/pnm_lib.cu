@@ -9,6 +9,7 @@
 #include "norm.cuh"
 #include "graph.cuh"
 #include "peer.cuh"
+#include "flash_attn.cuh"
 #include "pnm_api.h"
 
 __device__ int pnm_error_word = 0;
@@ -226,6 +227,18 @@ int pnm_peer_wait_probe(const void* flag, unsigned int expect, double budget_s, 
   pnm::peer_wait_probe_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint32_t*>(flag), expect, (unsigned long long)(budget_s * 1e9), g_err_ptr, status_out);
   return cudaGetLastError() == cudaSuccess ? 0 : -52;
+}
+
+int pnm_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int BH, int Sq, int Skv, int D,
+                       int ldv, float scale, int causal, int v_transposed, void* stream) {
+  if (ensure_init()) return -1;
+  if (!q || !k || !v || !out || BH <= 0 || Sq <= 0 || Skv <= 0 || !(scale > 0.f)) return -1;
+  if (v_transposed && (ldv < Skv || (ldv & 7))) return -1;
+  pnm::FlashCall c{q, k, v, out, lse, BH, Sq, Skv, ldv, scale, causal};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (D == 64) return v_transposed ? pnm::launch_flash_fwd<64, true>(c, g_err_ptr, st) : pnm::launch_flash_fwd<64, false>(c, g_err_ptr, st);
+  if (D == 128) return v_transposed ? pnm::launch_flash_fwd<128, true>(c, g_err_ptr, st) : pnm::launch_flash_fwd<128, false>(c, g_err_ptr, st);
+  return -1;
 }
 
 }  // extern "C"

@@ -47,6 +47,23 @@ inline int make_tmap_2d_b16(CUtensorMap* out, const void* base, uint64_t rows, u
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
+// 3-D tensor [Z, Y, X] of 16-bit elements, X contiguous, `ldy` elements between rows and `ldz` between slabs;
+// box = [1, box_y, 64] with 128-byte swizzle, i.e. box_y rows of 128 bytes in shared memory.  Returns 0 on success.
+inline int make_tmap_3d_b16(CUtensorMap* out, const void* base, uint64_t Z, uint64_t Y, uint64_t X, uint64_t ldy,
+                            uint64_t ldz, uint32_t box_y) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ldy * 2) & 15) || ((ldz * 2) & 15) || box_y > 256) return -2;
+  cuuint64_t dims[3] = {X, Y, Z};
+  cuuint64_t strides[2] = {ldy * 2, ldz * 2};
+  cuuint32_t box[3] = {64, box_y, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
 // 4-D channels-last image tensor [N, H, W, C] of 16-bit elements; box = [1, box_h, box_w, 64 channels], 128-byte
 // swizzle: in shared memory the box is box_h * box_w rows of 128 bytes (x fastest), i.e. the layout of a 2-D
 // [rows, 64] tile, so the GEMM's K-major operand descriptors apply unchanged.  Returns 0 on success.

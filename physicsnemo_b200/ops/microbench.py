@@ -113,6 +113,27 @@ def groupnorm_cases():
     return out
 
 
+def attention_cases(small: bool = False):
+    """Forward attention: SongUNet bottleneck (one head, 16 384 tokens, D=128 stands in for the split 512-wide head),
+    a DiT-like shape (16 heads, D=64) and a causal case; each against ``F.scaled_dot_product_attention``."""
+    import torch.nn.functional as F
+
+    from . import attention as A
+
+    shapes = {"b8_h4_s16384_d128": (8, 4, 16384, 128, False), "b8_h16_s4096_d64": (8, 16, 4096, 64, False),
+              "b4_h16_s8192_d128_causal": (4, 16, 8192, 128, True)}
+    if small:
+        shapes = {"b2_h8_s4096_d128": (2, 8, 4096, 128, False), "b2_h8_s4096_d64": (2, 8, 4096, 64, False)}
+    out = {}
+    for name, (b, h, s, d, causal) in shapes.items():
+        q, k, v = (_r(b, h, s, d) for _ in range(3))
+        flops = 4.0 * b * h * s * s * d * (0.5 if causal else 1.0)
+        nbytes = 4 * b * h * s * d * 2
+        out[f"flash_{name}"] = (lambda q=q, k=k, v=v, c=causal: A.flash_forward(q, k, v, c), flops, nbytes)
+        out[f"torch_sdpa_{name}"] = (lambda q=q, k=k, v=v, c=causal: F.scaled_dot_product_attention(q, k, v, is_causal=c), flops, nbytes)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel")
@@ -126,6 +147,9 @@ def main():
         names = list(table)
     elif args.kernel == "groupnorm":
         table = groupnorm_cases()
+        names = list(table)
+    elif args.kernel in ("attention", "attention_small"):
+        table = attention_cases(small=args.kernel == "attention_small")
         names = list(table)
     else:
         table = cases(args.m)

@@ -76,3 +76,55 @@ def test_neighbourhood_attention_kernels(case):
         assert (out.float() - ref).abs().max() < tol
         for a, b in ((gq, rq), (gk, rk), (gv, rv)):
             assert (a.float() - b).abs().max() < tol * 4 * max(1.0, float(b.abs().max()))
+
+
+# ---- flash attention (tcgen05) ---------------------------------------------------------------------------------------
+def _sdpa_fp32(q, k, v, causal, scale):
+    s = (q.float() @ k.float().transpose(-1, -2)) * scale
+    if causal:
+        mask = torch.ones(q.shape[-2], k.shape[-2], dtype=torch.bool, device=q.device).tril()
+        s = s.masked_fill(~mask, float("-inf"))
+    return torch.softmax(s, dim=-1) @ v.float(), torch.logsumexp(s, dim=-1)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("layout", ["natural", "transposed"])
+@pytest.mark.parametrize("shape", [(2, 3, 256, 256, 64, False), (1, 2, 384, 384, 128, False), (2, 2, 200, 333, 64, False),
+                                   (1, 2, 130, 77, 128, False), (1, 3, 512, 512, 128, True), (2, 1, 300, 300, 64, True),
+                                   (1, 1, 1024, 2048, 128, False)])
+def test_flash_attention_forward(shape, layout):
+    from physicsnemo_b200.ops import attention as A
+    from physicsnemo_b200.ops import device_error
+
+    b, h, sq, skv, d, causal = shape
+    torch.manual_seed(0)
+    q = torch.randn(b, h, sq, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(b, h, skv, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(b, h, skv, d, device="cuda", dtype=torch.bfloat16)
+    scale = 0.7 / d ** 0.5
+    out, lse = A.flash_forward(q, k, v, causal, scale, v_layout=layout)
+    torch.cuda.synchronize()
+    assert device_error() == 0
+    ref, ref_lse = _sdpa_fp32(q, k, v, causal, scale)
+    assert torch.isfinite(out.float()).all()
+    err = (out.float() - ref).abs().max().item()
+    assert err < 2e-2, f"max abs err {err}"
+    assert (lse - ref_lse).abs().max().item() < 2e-3
+
+
+@pytest.mark.gpu
+def test_flash_attention_autograd_and_fallback():
+    from physicsnemo_b200.ops import attention as A
+
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(2, 4, 256, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+    out = A.sdpa(q, k, v, is_causal=True)
+    out.float().square().sum().backward()
+    qr, kr, vr = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    ref = torch.nn.functional.scaled_dot_product_attention(qr, kr, vr, is_causal=True)
+    ref.float().square().sum().backward()
+    assert (out - ref).abs().max().item() < 2e-2
+    for a, b in ((q, qr), (k, kr), (v, vr)):
+        assert (a.grad.float() - b.grad.float()).abs().max().item() < 5e-2 * b.grad.float().abs().max().item() + 1e-3
+    x = torch.randn(2, 4, 64, 32, device="cuda")                                  # fp32, D=32: PyTorch operator
+    assert torch.allclose(A.sdpa(x, x, x), torch.nn.functional.scaled_dot_product_attention(x, x, x))
