@@ -2,17 +2,27 @@
 //
 // One CTA owns 128 query rows of one (batch, head) and walks the keys in tiles of 128:
 //
-//   warp 4     TMA producer: Q once, then K and V tiles into two-stage rings (128-byte-swizzled 64-wide blocks)
-//   warp 5     MMA issuer:   S_j = Q K_j^T   -> TMEM columns [0,256), double buffered
-//                            O_j = P_j V_j   -> TMEM columns [256, 256 + 2 D), double buffered (fresh tile, no accumulate)
-//   warps 0-3  softmax:      thread r owns query row r (= TMEM lane r).  It reads S_j twice from TMEM (row maximum, then
-//                            exponentials), writes P_j as bf16 into the swizzled K-major operand layout in shared memory,
-//                            and keeps the running maximum, the running sum and the output row (D fp32 registers); the
-//                            product tile O_{j-1} is folded into the registers while the tensor core works on tile j.
+//   warp 8     TMA producer: Q once, then K and V tiles into two-stage rings (128-byte-swizzled 64-wide blocks)
+//   warp 9     MMA issuer:   S_j = Q K_j^T   -> TMEM columns [0,256), double buffered
+//                            O  += P_j V_j   -> TMEM columns [256, 256 + D), accumulated across the key tiles
+//   warps 0-7  softmax:      TMEM lane r holds query row r; warps w and w+4 share the 32 rows of lane quadrant w and
+//                            take 64 of the 128 key columns each, so every scheduler has two resident warps to hide the
+//                            TMEM-load, MUFU and shared-memory latencies of the other.  A thread reads its half of S_j
+//                            once, exponentiates against a *reference* maximum, writes its half of P_j as bf16 into the
+//                            swizzled K-major operand layout in shared memory and keeps a partial running sum.  The two
+//                            halves of a row agree on the reference through one bf16 exchange per tile.
 //
-// S_{j+1} is issued before P_j is waited for, so the QK^T product of the next tile overlaps the softmax of this one.
-// Every reuse of a TMEM or shared-memory buffer is ordered by the p_full / o_full barriers that the loop waits on
-// anyway (see the comments at the waits), which is why there are no separate "empty" barriers for S, P and O.
+// Lazy rescaling.  The reference maximum of a row only moves when the row maximum of a tile exceeds it by more than
+// 2^8; bf16 and fp32 share their exponent range, so exponentials up to 2^8 (and, before a redo is forced, 2^64) are
+// exact enough and cannot overflow.  While the reference stays put the accumulator in TMEM needs no correction at
+// all; when it moves, the warp reads its 32 accumulator rows, scales them and writes them back (tcgen05.ld / st)
+// before it releases P_j, i.e. strictly between the products of tiles j-1 and j.  A tile whose maximum exceeds the
+// reference by more than 2^64 (only possible with pathological inputs; always the case for the first tile, whose
+// reference is -inf) is redone against its own maximum while S_j is still in TMEM.
+//
+// S_{j+1} is issued before P_j is waited for, so the QK^T product of the next tile overlaps the softmax of this one,
+// and the product P_j V_j overlaps the softmax of tile j+1.  Every reuse of a TMEM or shared-memory buffer is ordered
+// by the p_full / o_full barriers that the loops wait on anyway (see the comments at the waits).
 //
 // V is consumed either in its natural [keys, D] layout as an MN-major B operand (VT = false) or from a pre-transposed
 // [D, keys] copy as a K-major operand (VT = true).  Rows of K / V beyond the sequence read as zero through TMA and are
@@ -37,8 +47,8 @@ struct FlashArgs {
   int* err;
 };
 
-constexpr int kFaThreads = 192;
-constexpr int kFaBarBytes = 256;
+constexpr int kFaThreads = 320;
+constexpr int kFaBarBytes = 256 + 1024;   // barriers, then the 1 KB exchange area of the row halves
 
 template <int D>
 constexpr int flash_smem_bytes() { return 1024 + 5 * (128 * D * 2) + 2 * (128 * 128 * 2) + kFaBarBytes; }
@@ -73,7 +83,9 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
   uint64_t* s_full = bar + 9;
   uint64_t* p_full = bar + 11;
   uint64_t* o_full = bar + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 16);
+  uint64_t* xbar = bar + 14;   // [4] one per lane quadrant: the two warps of a row group meet here
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 18);
+  uint8_t* xchg = reinterpret_cast<uint8_t*>(bar) + 256;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -92,16 +104,17 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 128);
-      mbar_init(&o_full[s], 1);
+      mbar_init(&p_full[s], 8);   // one arrival per softmax warp
     }
+    mbar_init(o_full, 1);
+    for (int w = 0; w < 4; ++w) mbar_init(&xbar[w], 2);
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     tma_prefetch_desc(&g.tmQ);
     tma_prefetch_desc(&g.tmK);
     tma_prefetch_desc(&g.tmV);
@@ -111,7 +124,7 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       mbar_expect_tx(q_full, TILE);
@@ -142,7 +155,7 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
         for (int j = max(nv - 2, 0); j < nv; ++j) mbar_drain(&v_full[j & 1], (j >> 1) & 1);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
@@ -170,130 +183,161 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
         if (j + 1 < T && !issue_qk(j + 1)) { ok = false; break; }
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        // p_full of tile j also means: every thread folded O_{j-2} into its registers, so O buffer s is free
+        // p_full of tile j also means: the product of tile j-1 has completed (every thread waits for o_full of tile
+        // j-1 before it arrives) and any correction of the accumulator has been written back
         if (!mbar_wait(&p_full[s], ph, abort_flag, g.err, ERR_WAIT_AUX)) { ok = false; break; }
         if (!mbar_wait(&v_full[s], ph, abort_flag, g.err, ERR_WAIT_FULL)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d = tmem_base + 256 + s * D;
+        const uint32_t d = tmem_base + 256;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint64_t ad = make_smem_desc(smem_u32(sP + s * PT + (k >> 2) * BLK), 16, 1024, 2) + 2 * (k & 3);
           uint64_t bd;
           if (VT) bd = make_smem_desc(smem_u32(sV + s * TILE + (k >> 2) * (D * 128)), 16, 1024, 2) + 2 * (k & 3);
           else bd = make_smem_desc(smem_u32(sV + s * TILE + k * 2048), BLK, 1024, 2);   // 16 key rows per step
-          umma_f16(d, ad, bd, idesc_o, k != 0 ? 1u : 0u);
+          umma_f16(d, ad, bd, idesc_o, (j | k) != 0 ? 1u : 0u);
         }
         umma_commit(&v_empty[s]);
-        umma_commit(&o_full[s]);
+        umma_commit(o_full);
       }
     }
   } else {
     // ------------------------------------------------------------- softmax rows
-    const int row = threadIdx.x;
-    const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16);
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (uint32_t(quad * 32) << 16);
     const float c = g.scale_log2;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f, alpha_pend = 1.f;
+    __nv_bfloat16* xmax = reinterpret_cast<__nv_bfloat16*>(xchg);   // [tile parity][half][row]
+    float* xsum = reinterpret_cast<float*>(xchg);                    // [half][row], after the last tile
+    float ref = -INFINITY;    // reference maximum of the previous tile (what the accumulator and l are relative to)
+    float next = -INFINITY;   // reference chosen for the coming tile
+    float l = 0.f;            // this half's part of the row sum
     bool ok = true;
+    constexpr int OC = D / 64;   // 32-column chunks of the accumulator per half
 
-    auto fold = [&](int t, float a) -> bool {
-      const int s = t & 1;
-      // the TMEM loads below are warp-collective: the warp leaves together or not at all
-      if (!__all_sync(0xffffffffu, mbar_wait(&o_full[s], (t >> 1) & 1, abort_flag, g.err, ERR_WAIT_TMEM_FULL))) return false;
-      tc_fence_after();
-#pragma unroll
-      for (int cc = 0; cc < D / 32; ++cc) {
-        float v[32];
-        tmem_ld32(lane_addr + 256 + s * D + cc * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[cc * 32 + i] = fmaf(o[cc * 32 + i], a, v[i]);
-      }
-      return true;
+    // the two warps of a row group meet: publish (done by the caller), one arrival per warp, bounded wait
+    auto meet = [&](int phase) -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&xbar[quad]);
+      return __all_sync(0xffffffffu, mbar_wait(&xbar[quad], phase & 1, abort_flag, g.err, ERR_WAIT_AUX));
     };
 
     for (int j = 0; j < T; ++j) {
       const int s = j & 1;
+      // the TMEM loads below are warp-collective: the warp leaves together or not at all
       if (!__all_sync(0xffffffffu, mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, g.err, ERR_WAIT_TMEM_FULL))) { ok = false; break; }
       tc_fence_after();
       const bool edge = (j * 128 + 128 > g.Skv) || (g.causal && j * 128 + 127 > q0);
       int lim = g.Skv - j * 128;
       if (g.causal) lim = min(lim, q0 + row - j * 128 + 1);
-      float mx = -INFINITY;
+      lim -= half * 64;   // in this half's column numbering
+      float v[64];
+      tmem_ld32(lane_addr + s * 128 + half * 64, v);
+      tmem_ld32(lane_addr + s * 128 + half * 64 + 32, v + 32);
+      tmem_ld_wait();
+      if (edge) {
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        float v[32];
-        tmem_ld32(lane_addr + s * 128 + cc * 32, v);
-        tmem_ld_wait();
-        if (edge) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) if (cc * 32 + i >= lim) v[i] = -INFINITY;
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+        for (int i = 0; i < 64; ++i) if (i >= lim) v[i] = -INFINITY;
       }
-      const float m_new = fmaxf(m, mx * c);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = ex2_fast(m - m_use);
-      float rs = 0.f;
-      // P buffer s was last read by the product of tile j-2, whose o_full this thread has already waited for
-      uint8_t* prow = sP + s * PT + row * 128;
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        float v[32];
-        tmem_ld32(lane_addr + s * 128 + cc * 32, v);
-        tmem_ld_wait();
-        if (edge) {
+      for (int i = 0; i < 64; i += 4) {
+        m0 = fmaxf(m0, v[i]);
+        m1 = fmaxf(m1, v[i + 1]);
+        m2 = fmaxf(m2, v[i + 2]);
+        m3 = fmaxf(m3, v[i + 3]);
+      }
+      // the maximum only serves as a reference, so the halves exchange it rounded up to bf16
+      const __nv_bfloat16 mine = __float2bfloat16_ru(fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * c);
+      xmax[(s * 2 + half) * 128 + row] = mine;
+      if (!meet(j)) { ok = false; break; }
+      const float tile_max = fmaxf(__bfloat162float(mine), __bfloat162float(xmax[(s * 2 + (half ^ 1)) * 128 + row]));
+      // first tile, or a jump of more than 2^64 somewhere in the row group: take the tile's own maximum as reference
+      if (__any_sync(0xffffffffu, tile_max - next > 64.f)) next = fmaxf(next, tile_max);
+      const float use = (next == -INFINITY) ? 0.f : next;
+      const float alpha = ex2_fast(ref - use);   // 0 for the first tile, 1 while the reference stays put
+      float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+      // P buffer s was last read by the product of tile j-2, whose o_full this thread waited for in iteration j-1
+      uint8_t* prow = sP + s * PT + half * BLK + row * 128;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) if (cc * 32 + i >= lim) v[i] = -INFINITY;
-        }
+      for (int q = 0; q < 8; ++q) {
+        float e[8];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          v[i] = ex2_fast(fmaf(v[i], c, -m_use));
-          rs += v[i];
-        }
-        uint8_t* blk = prow + (cc >> 1) * BLK;
+        for (int i = 0; i < 8; ++i) e[i] = ex2_fast(fmaf(v[q * 8 + i], c, -use));
+        rs0 += e[0] + e[4];
+        rs1 += e[1] + e[5];
+        rs2 += e[2] + e[6];
+        rs3 += e[3] + e[7];
+        uint4 u;
+        u.x = pack_bf16x2(e[0], e[1]);
+        u.y = pack_bf16x2(e[2], e[3]);
+        u.z = pack_bf16x2(e[4], e[5]);
+        u.w = pack_bf16x2(e[6], e[7]);
+        *reinterpret_cast<uint4*>(prow + ((q ^ (row & 7)) << 4)) = u;
+      }
+      l = fmaf(l, alpha, (rs0 + rs1) + (rs2 + rs3));
+      if (j > 0) {
+        // product of tile j-1 done: until the arrive below the accumulator is free to touch
+        if (!__all_sync(0xffffffffu, mbar_wait(o_full, (j - 1) & 1, abort_flag, g.err, ERR_WAIT_TMEM_FULL))) { ok = false; break; }
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          tc_fence_after();
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint4 u;
-          u.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-          u.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-          u.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-          u.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-          const int chunk = (cc & 1) * 4 + q;
-          *reinterpret_cast<uint4*>(blk + ((chunk ^ (row & 7)) << 4)) = u;
+          for (int cc = 0; cc < OC; ++cc) {
+            float o[32];
+            const uint32_t at = lane_addr + 256 + half * (D / 2) + cc * 32;
+            tmem_ld32(at, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+            tmem_st32(at, o);
+          }
+          tmem_st_wait();
         }
       }
-      l = fmaf(l, alpha, rs);
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(&p_full[s]);
-      if (j > 0 && !fold(j - 1, alpha_pend)) { ok = false; break; }
-      alpha_pend = alpha;
-      m = m_new;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[s]);
+      ref = use;
+      next = (tile_max - use > 8.f) ? tile_max : use;
     }
-    if (ok && T > 0) ok = fold(T - 1, alpha_pend);
-    if (ok && q0 + row < g.Sq) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = g.out + (size_t(bh) * g.Sq + q0 + row) * D;
+    if (ok && T > 0) ok = __all_sync(0xffffffffu, mbar_wait(o_full, (T - 1) & 1, abort_flag, g.err, ERR_WAIT_TMEM_FULL));
+    if (ok) {
+      // every softmax warp has arrived on p_full of the last tile, i.e. is past its last read of the exchange area
+      xsum[half * 128 + row] = l;
+      ok = meet(T);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float lt = l + xsum[(half ^ 1) * 128 + row];
+      const bool live = q0 + row < g.Sq;
+      const float inv = lt > 0.f ? 1.f / lt : 0.f;
+      __nv_bfloat16* dst = g.out + (size_t(bh) * g.Sq + q0 + row) * D + half * (D / 2);
 #pragma unroll
-      for (int i = 0; i < D; i += 8) {
-        uint4 u;
-        u.x = pack_bf16x2(o[i + 0] * inv, o[i + 1] * inv);
-        u.y = pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv);
-        u.z = pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv);
-        u.w = pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + i) = u;
+      for (int cc = 0; cc < OC; ++cc) {
+        float o[32];
+        tmem_ld32(lane_addr + 256 + half * (D / 2) + cc * 32, o);
+        tmem_ld_wait();
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 u;
+            u.x = pack_bf16x2(o[i + 0] * inv, o[i + 1] * inv);
+            u.y = pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv);
+            u.z = pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv);
+            u.w = pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv);
+            *reinterpret_cast<uint4*>(dst + cc * 32 + i) = u;
+          }
+        }
       }
-      if (g.lse) g.lse[size_t(bh) * g.Sq + q0 + row] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      if (live && half == 0 && g.lse)
+        g.lse[size_t(bh) * g.Sq + q0 + row] = lt > 0.f ? (ref + log2f(lt)) * 0.6931471805599453f : -INFINITY;
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }

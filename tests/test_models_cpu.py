@@ -245,3 +245,81 @@ def test_healpix_padding_table():
     conv = HEALPixLayer(torch.nn.Conv2d, in_channels=3, out_channels=5, kernel_size=3)
     assert conv(x.detach()).shape == (24, 5, n, n)
     assert HEALPixAvgPool(pooling=2)(x.detach()).shape == (24, 3, n // 2, n // 2)
+
+
+# ---- DLWP-HEALPix U-Nets ---------------------------------------------------------------------------------------------
+def _hpx_configs(recurrent: bool, cln: bool = False):
+    P = "physicsnemo.models.dlwp_healpix.layers"
+    act = {"_target_": "torch.nn.LeakyReLU", "negative_slope": 0.1}
+    block = "SymmetricConvNeXtBlock" if cln else "ConvNeXtBlock"
+    conv = {"_target_": f"{P}.healpix_blocks.{block}", "in_channels": 3, "out_channels": 1, "activation": act, "kernel_size": 3,
+            "dilation": 1, "upscale_factor": 2, "_recursive_": True}
+    if cln:
+        conv["conditional_layer_norm"] = {"_target_": f"{P}.normalization.ConditionalLayerNorm", "_partial_": True, "condition_shape": 5,
+                                          "mlp_hidden_dims": [8]}
+    enc = {"_target_": f"{P}.healpix_encoder.UNetEncoder", "conv_block": conv,
+           "down_sampling_block": {"_target_": "physicsnemo.models.dlwp_healpix_layers.healpix_blocks.AvgPool", "pooling": 2},
+           "n_channels": [8, 16], "n_layers": [1, 1], "dilations": [1, 2], "_recursive_": False}
+    dec = {"_target_": f"{P}.UNetDecoder", "conv_block": conv,
+           "up_sampling_block": {"_target_": f"{P}.TransposedConvUpsample", "activation": act, "upsampling": 2},
+           "output_layer": {"_target_": f"{P}.BasicConvBlock", "kernel_size": 1, "dilation": 1, "n_layers": 1},
+           "n_channels": [16, 8], "n_layers": [1, 1], "dilations": [2, 1], "_recursive_": False}
+    if recurrent:
+        dec["recurrent_block"] = {"_target_": f"{P}.ConvGRUBlock", "kernel_size": 1}
+    return enc, dec
+
+
+def test_healpix_unets_forward_backward_and_rollout_shapes():
+    from physicsnemo_b200.models.dlwp_healpix import HEALPixRecUNet, HEALPixUNet
+    from physicsnemo_b200.models.dlwp_healpix.layers import ConvGRUBlock, build
+
+    torch.manual_seed(0)
+    B, F, H = 2, 12, 8
+    enc, dec = _hpx_configs(recurrent=True)
+    rec = HEALPixRecUNet(enc, dec, input_channels=3, output_channels=4, n_constants=2, decoder_input_channels=1, input_time_dim=2,
+                         output_time_dim=4, delta_time="6h", reset_cycle="24h", presteps=1)
+    x = [torch.randn(B, F, 4, 3, H, H), torch.randn(B, F, 6, 1, H, H), torch.randn(F, 2, H, H)]
+    y = rec(x)
+    assert y.shape == (B, F, 4, 4, H, H)                       # 2 integration steps x 2 time levels, 3 prognostic + 1 diagnostic
+    assert rec(x, output_only_last=True).shape == (B, F, 2, 4, H, H)
+    y.square().mean().backward()
+    assert all(p.grad is not None for p in rec.parameters())
+    assert any(isinstance(m, ConvGRUBlock) for m in rec.modules())
+    assert torch.allclose(rec(x), rec(x))                      # hidden state is reset at the start of every call
+    enc, dec = _hpx_configs(recurrent=False)
+    net = HEALPixUNet(enc, dec, input_channels=3, output_channels=3, n_constants=2, decoder_input_channels=1, input_time_dim=2,
+                      output_time_dim=2, residual_prediction=True)
+    xin = [x[0][:, :, :2], x[1][:, :, :2], x[2]]
+    out = net(xin)
+    assert out.shape == (B, F, 2, 3, H, H)
+    with torch.no_grad():                                      # zero network output -> residual prediction returns its input
+        for p in net.decoder.output_layer.parameters():
+            p.zero_()
+    assert torch.allclose(net(xin), xin[0], atol=1e-6)
+    with pytest.raises(ValueError):
+        HEALPixUNet(enc, dec, 3, 3, 2, 1, input_time_dim=2, output_time_dim=3)
+    assert isinstance(build({"_target_": "torch.nn.Linear", "in_features": 3}, out_features=2), torch.nn.Linear)
+
+
+def test_healpix_unet_conditional_layer_norm_and_constraints():
+    from physicsnemo_b200.models.dlwp_healpix import HEALPixUNet
+    from physicsnemo_b200.models.dlwp_healpix.layers import ConditionalLayerNorm, NonnegativeConstraint
+
+    torch.manual_seed(0)
+    B, F, H = 2, 12, 8
+    enc, dec = _hpx_configs(recurrent=False, cln=True)
+    enc["per_level_cln"] = [True, False]
+    net = HEALPixUNet(enc, dec, input_channels=2, output_channels=2, n_constants=1, decoder_input_channels=1, input_time_dim=1,
+                      output_time_dim=1, residual_prediction=False,
+                      constraints={"nonneg": {"_target_": "physicsnemo.models.dlwp_healpix.layers.healpix_constraints.NonnegativeConstraint",
+                                              "variables": ["q"], "channels": ["t", "q"], "scaling": {"q": {"mean": 1.0, "std": 2.0}}}})
+    n_cln_enc = sum(isinstance(m, ConditionalLayerNorm) for m in net.encoder.modules())
+    assert n_cln_enc == 3                                      # only the first encoder level keeps its three CLN layers
+    x = [torch.randn(B, F, 1, 2, H, H), torch.randn(B, F, 1, 1, H, H), torch.randn(F, 1, H, H)]
+    cond = [torch.randn(B, 5)]
+    y = net(x, conditions_cln=cond)
+    assert y.shape == (B, F, 1, 2, H, H)
+    assert float(y[:, :, :, 1].min()) >= -0.5 - 1e-6           # q >= (0 - mean) / std
+    with pytest.raises(ValueError):
+        net(x)                                                 # conditions are required once CLN is enabled
+    assert isinstance(net.constraints[0], NonnegativeConstraint)

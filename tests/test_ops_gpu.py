@@ -128,3 +128,27 @@ def test_flash_attention_autograd_and_fallback():
         assert (a.grad.float() - b.grad.float()).abs().max().item() < 5e-2 * b.grad.float().abs().max().item() + 1e-3
     x = torch.randn(2, 4, 64, 32, device="cuda")                                  # fp32, D=32: PyTorch operator
     assert torch.allclose(A.sdpa(x, x, x), torch.nn.functional.scaled_dot_product_attention(x, x, x))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("d", [64, 128])
+def test_flash_attention_growing_scores_rescale_the_accumulator(d):
+    """Later key tiles carry much larger scores, so the running reference must move (by more than 2^8 and, for the last
+    tile, by more than 2^64) and the TMEM accumulator is corrected in place."""
+    from physicsnemo_b200.ops import attention as A
+    from physicsnemo_b200.ops import device_error
+
+    torch.manual_seed(1)
+    q = torch.randn(1, 2, 256, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(1, 2, 640, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(1, 2, 640, d, device="cuda", dtype=torch.bfloat16)
+    ramp = torch.tensor([0.2, 1.0, 3.0, 3.0, 30.0], device="cuda").repeat_interleave(128)     # per key tile
+    k = (k.float() * ramp[None, None, :, None]).to(torch.bfloat16)
+    scale = 1.0 / d ** 0.5
+    out, lse = A.flash_forward(q, k, v, False, scale)
+    torch.cuda.synchronize()
+    assert device_error() == 0
+    ref, ref_lse = _sdpa_fp32(q, k, v, False, scale)
+    assert torch.isfinite(out.float()).all()
+    assert (out.float() - ref).abs().max().item() < 3e-2
+    assert ((lse - ref_lse).abs() / ref_lse.abs().clamp_min(1.0)).max().item() < 2e-3
