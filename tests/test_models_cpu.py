@@ -323,3 +323,71 @@ def test_healpix_unet_conditional_layer_norm_and_constraints():
     with pytest.raises(ValueError):
         net(x)                                                 # conditions are required once CLN is enabled
     assert isinstance(net.constraints[0], NonnegativeConstraint)
+
+
+# ---- DoMINO ----------------------------------------------------------------------------------------------------------
+def _domino_small_params(**over):
+    import copy
+
+    from physicsnemo_b200.models.domino import DEFAULT_MODEL_PARAMS
+
+    p = copy.deepcopy(DEFAULT_MODEL_PARAMS)
+    p.interp_res = [8, 8, 8]
+    gc, gl = p.geometry_rep.geo_conv, p.geometry_local
+    gc.volume_radii, gc.volume_neighbors_in_radius = [0.5, 1.5], [4, 8]
+    gc.surface_radii, gc.surface_neighbors_in_radius = [0.5, 1.0], [4, 6]
+    gl.volume_radii, gl.volume_neighbors_in_radius = [0.6, 1.2], [4, 8]
+    gl.surface_radii, gl.surface_neighbors_in_radius = [0.6], [5]
+    p.nn_basis_functions.base_layer = p.aggregation_model.base_layer = p.position_encoder.base_neurons = 16
+    p.parameter_model.base_layer = 8
+    p.num_neighbors_volume, p.num_neighbors_surface = 3, 4
+    for k, v in over.items():
+        if k == "processor_type":
+            p.geometry_rep.geo_processor.processor_type = v
+        else:
+            p[k] = v
+    return p
+
+
+def _domino_batch(B=2, N=30, G=8):
+    torch.manual_seed(3)
+    lin = torch.linspace(-1, 1, G)
+    grid = torch.stack(torch.meshgrid(lin, lin, lin, indexing="ij"), -1).unsqueeze(0).expand(B, -1, -1, -1, -1).contiguous()
+    u = lambda *s: torch.rand(*s) * 1.6 - 0.8  # noqa: E731
+    return dict(geometry_coordinates=u(B, 200, 3), surf_grid=grid, sdf_surf_grid=torch.randn(B, G, G, G), grid=grid,
+                sdf_grid=torch.randn(B, G, G, G), global_params_values=torch.rand(B, 2, 1) + 0.5, global_params_reference=torch.ones(B, 2, 1),
+                sdf_nodes=torch.randn(B, N, 1), pos_volume_closest=torch.randn(B, N, 3), pos_volume_center_of_mass=torch.randn(B, N, 3),
+                volume_mesh_centers=u(B, N, 3), pos_surface_center_of_mass=torch.randn(B, N, 3), surface_mesh_centers=u(B, N, 3),
+                surface_mesh_neighbors=u(B, N, 3, 3), surface_normals=torch.randn(B, N, 3), surface_neighbors_normals=torch.randn(B, N, 3, 3),
+                surface_areas=torch.rand(B, N) + 0.1, surface_neighbors_areas=torch.rand(B, N, 3) + 0.1)
+
+
+@pytest.mark.parametrize("over", [dict(), dict(processor_type="conv", encode_parameters=True), dict(combine_volume_surface=True)])
+def test_domino_forward_backward(over):
+    from physicsnemo_b200.models.domino import DoMINO
+
+    torch.manual_seed(0)
+    model = DoMINO(input_features=3, output_features_vol=2, output_features_surf=3, global_features=2, model_parameters=_domino_small_params(**over))
+    data = _domino_batch()
+    vol, surf = model(data)
+    assert vol.shape == (2, 30, 2) and surf.shape == (2, 30, 3)
+    assert torch.isfinite(vol).all() and torch.isfinite(surf).all()
+    (vol.square().mean() + surf.square().mean()).backward()
+    touched = [n for n, p in model.named_parameters() if p.grad is not None and float(p.grad.abs().sum()) > 0]
+    assert any(n.startswith("geo_rep_volume") for n in touched) and any(n.startswith("agg_model_surf") for n in touched)
+
+
+def test_domino_single_branch_and_validation():
+    from physicsnemo_b200.models.domino import Config, DoMINO
+
+    surf_only = DoMINO(input_features=3, output_features_surf=2, model_parameters=dict(_domino_small_params()))   # plain dict accepted
+    data = _domino_batch()
+    vol, surf = surf_only(data)
+    assert vol is None and surf.shape == (2, 30, 2)
+    with pytest.raises(ValueError):
+        surf_only({k: v for k, v in data.items() if k != "surface_normals"})
+    with pytest.raises(ValueError):
+        DoMINO(input_features=3)
+    cfg = Config({"a": {"b": 1}})
+    cfg.c = {"d": 2}
+    assert cfg.a.b == 1 and cfg.c.d == 2 and isinstance(cfg.c, Config)
