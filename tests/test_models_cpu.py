@@ -391,3 +391,47 @@ def test_domino_single_branch_and_validation():
     cfg = Config({"a": {"b": 1}})
     cfg.c = {"d": 2}
     assert cfg.a.b == 1 and cfg.c.d == 2 and isinstance(cfg.c, Config)
+
+
+# ---- FIGConvUNet -----------------------------------------------------------------------------------------------------
+def test_figconvunet_forward_backward_variants():
+    from physicsnemo_b200.models.figconvnet import FIGConvUNet
+
+    torch.manual_seed(0)
+    pairs = [("b_xc_y_z", (2, 12, 12)), ("b_yc_x_z", (12, 2, 12)), ("b_zc_x_y", (12, 12, 2))]
+    net = FIGConvUNet(in_channels=4, out_channels=3, kernel_size=3, hidden_channels=[8, 16, 16], num_levels=2, mlp_channels=[32, 32],
+                      aabb_max=(1, 1, 1), aabb_min=(-1, -1, -1), resolution_memory_format_pairs=pairs, pos_encode_dim=8,
+                      communication_types=["sum", "mul"])
+    v = torch.rand(2, 300, 3) * 2 - 1
+    y, drag = net(v)
+    assert y.shape == (2, 300, 3) and drag.shape == (2, 1)
+    (y.square().mean() + drag.square().mean()).backward()
+    assert all(p.grad is not None for p in net.parameters())
+    perm = torch.randperm(300)
+    y2, drag2 = net(v[:, perm])
+    assert torch.allclose(y2, y[:, perm], atol=1e-4) and torch.allclose(drag2, drag, atol=1e-4)     # point order does not matter
+    net2 = FIGConvUNet(in_channels=4, out_channels=1, kernel_size=3, hidden_channels=[8, 16], num_levels=1, aabb_max=(1, 1, 1),
+                       aabb_min=(-1, -1, -1), resolution_memory_format_pairs=[("b_xc_y_z", (3, 10, 8)), ("b_zc_x_y", (10, 8, 3))],
+                       pos_encode_dim=8, has_input_features=True, to_point_sample_method="interp", neighbor_search_type="knn", knn_k=4,
+                       use_scalar_output=False, reductions=["mean", "max"], pooling_type="attention")
+    y, drag = net2(v, torch.randn(2, 300, 4))
+    assert y.shape == (2, 300, 1) and drag is None
+    with pytest.raises(ValueError):
+        net2(v, torch.randn(2, 300, 5))
+    with pytest.raises(ValueError):
+        net2(v)
+
+
+def test_figconv_factor_grid_helpers():
+    from physicsnemo_b200.models.figconvnet.figconvunet import _fold, _node_positions, _unfold, segment_reduce
+
+    x = torch.randn(2, 3, 4, 5, 6)
+    for axis, depth in ((0, 4), (1, 5), (2, 6)):
+        folded = _fold(x, axis)
+        assert folded.shape[1] == 3 * depth and torch.equal(_unfold(folded, axis, depth), x)
+    pos = _node_positions((4, 5, 6), x.device, x.dtype).unsqueeze(0).expand(2, -1, -1, -1, -1)
+    assert torch.allclose(torch.nn.functional.grid_sample(x, pos, align_corners=True), x, atol=1e-5)   # a grid sampled at its own nodes
+    vals, seg = torch.tensor([[1.0], [3.0], [5.0], [2.0]]), torch.tensor([0, 0, 2, 2])
+    assert segment_reduce(vals, seg, 3, "mean").flatten().tolist() == [2.0, 0.0, 3.5]
+    assert segment_reduce(vals, seg, 3, "max").flatten().tolist() == [3.0, 0.0, 5.0]
+    assert segment_reduce(vals, seg, 3, "var").flatten().tolist() == [1.0, 0.0, 2.25]
