@@ -2,15 +2,12 @@
 //
 // One CTA owns 128 query rows of one (batch, head) and walks the keys in tiles of 128:
 //
-//   warp 8     TMA producer: Q once, then K and V tiles into two-stage rings (128-byte-swizzled 64-wide blocks)
-//   warp 9     MMA issuer:   S_j = Q K_j^T   -> TMEM columns [0,256), double buffered
+//   warp 4     TMA producer: Q once, then K and V tiles into two-stage rings (128-byte-swizzled 64-wide blocks)
+//   warp 5     MMA issuer:   S_j = Q K_j^T   -> TMEM columns [0,256), double buffered
 //                            O  += P_j V_j   -> TMEM columns [256, 256 + D), accumulated across the key tiles
-//   warps 0-7  softmax:      TMEM lane r holds query row r; warps w and w+4 share the 32 rows of lane quadrant w and
-//                            take 64 of the 128 key columns each, so every scheduler has two resident warps to hide the
-//                            TMEM-load, MUFU and shared-memory latencies of the other.  A thread reads its half of S_j
-//                            once, exponentiates against a *reference* maximum, writes its half of P_j as bf16 into the
-//                            swizzled K-major operand layout in shared memory and keeps a partial running sum.  The two
-//                            halves of a row agree on the reference through one bf16 exchange per tile.
+//   warps 0-3  softmax:      thread r owns query row r (= TMEM lane r).  It reads S_j once (all four 32-column loads in
+//                            flight together), exponentiates against a *reference* maximum, writes P_j as bf16 into the
+//                            swizzled K-major operand layout in shared memory and keeps the running sum.
 //
 // Lazy rescaling.  The reference maximum of a row only moves when the row maximum of a tile exceeds it by more than
 // 2^8; bf16 and fp32 share their exponent range, so exponentials up to 2^8 (and, before a redo is forced, 2^64) are
@@ -47,8 +44,8 @@ struct FlashArgs {
   int* err;
 };
 
-constexpr int kFaThreads = 320;
-constexpr int kFaBarBytes = 256 + 1024;   // barriers, then the 1 KB exchange area of the row halves
+constexpr int kFaThreads = 192;
+constexpr int kFaBarBytes = 256;
 
 template <int D>
 constexpr int flash_smem_bytes() { return 1024 + 5 * (128 * D * 2) + 2 * (128 * 128 * 2) + kFaBarBytes; }
@@ -83,9 +80,7 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
   uint64_t* s_full = bar + 9;
   uint64_t* p_full = bar + 11;
   uint64_t* o_full = bar + 13;
-  uint64_t* xbar = bar + 14;   // [4] one per lane quadrant: the two warps of a row group meet here
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 18);
-  uint8_t* xchg = reinterpret_cast<uint8_t*>(bar) + 256;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -104,17 +99,16 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 8);   // one arrival per softmax warp
+      mbar_init(&p_full[s], 4);   // one arrival per softmax warp
     }
     mbar_init(o_full, 1);
-    for (int w = 0; w < 4; ++w) mbar_init(&xbar[w], 2);
     mbar_fence_init();
   }
-  if (warp == 9) {
+  if (warp == 5) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (warp == 8 && lane == 0) {
+  if (warp == 4 && lane == 0) {
     tma_prefetch_desc(&g.tmQ);
     tma_prefetch_desc(&g.tmK);
     tma_prefetch_desc(&g.tmV);
@@ -124,7 +118,7 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == 4) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       mbar_expect_tx(q_full, TILE);
@@ -155,7 +149,7 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
         for (int j = max(nv - 2, 0); j < nv; ++j) mbar_drain(&v_full[j & 1], (j >> 1) & 1);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 5) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
@@ -203,24 +197,13 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
     }
   } else {
     // ------------------------------------------------------------- softmax rows
-    const int quad = warp & 3, half = warp >> 2;
-    const int row = quad * 32 + lane;
-    const uint32_t lane_addr = tmem_base + (uint32_t(quad * 32) << 16);
+    const int row = threadIdx.x;
+    const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16);
     const float c = g.scale_log2;
-    __nv_bfloat16* xmax = reinterpret_cast<__nv_bfloat16*>(xchg);   // [tile parity][half][row]
-    float* xsum = reinterpret_cast<float*>(xchg);                    // [half][row], after the last tile
     float ref = -INFINITY;    // reference maximum of the previous tile (what the accumulator and l are relative to)
     float next = -INFINITY;   // reference chosen for the coming tile
-    float l = 0.f;            // this half's part of the row sum
+    float l = 0.f;
     bool ok = true;
-    constexpr int OC = D / 64;   // 32-column chunks of the accumulator per half
-
-    // the two warps of a row group meet: publish (done by the caller), one arrival per warp, bounded wait
-    auto meet = [&](int phase) -> bool {
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&xbar[quad]);
-      return __all_sync(0xffffffffu, mbar_wait(&xbar[quad], phase & 1, abort_flag, g.err, ERR_WAIT_AUX));
-    };
 
     for (int j = 0; j < T; ++j) {
       const int s = j & 1;
@@ -230,66 +213,70 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
       const bool edge = (j * 128 + 128 > g.Skv) || (g.causal && j * 128 + 127 > q0);
       int lim = g.Skv - j * 128;
       if (g.causal) lim = min(lim, q0 + row - j * 128 + 1);
-      lim -= half * 64;   // in this half's column numbering
-      float v[64];
-      tmem_ld32(lane_addr + s * 128 + half * 64, v);
-      tmem_ld32(lane_addr + s * 128 + half * 64 + 32, v + 32);
+      float v[128];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) tmem_ld32(lane_addr + s * 128 + cc * 32, v + cc * 32);
       tmem_ld_wait();
+      float mx = -INFINITY;
       if (edge) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) if (i >= lim) v[i] = -INFINITY;
+        for (int i = 0; i < 128; ++i) if (i >= lim) v[i] = -INFINITY;
       }
-      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+      {
+        // four independent chains: one warp per scheduler has nothing else to hide a serial chain behind
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 64; i += 4) {
-        m0 = fmaxf(m0, v[i]);
-        m1 = fmaxf(m1, v[i + 1]);
-        m2 = fmaxf(m2, v[i + 2]);
-        m3 = fmaxf(m3, v[i + 3]);
+        for (int i = 0; i < 128; i += 4) {
+          m0 = fmaxf(m0, v[i]);
+          m1 = fmaxf(m1, v[i + 1]);
+          m2 = fmaxf(m2, v[i + 2]);
+          m3 = fmaxf(m3, v[i + 3]);
+        }
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
       }
-      // the maximum only serves as a reference, so the halves exchange it rounded up to bf16
-      const __nv_bfloat16 mine = __float2bfloat16_ru(fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * c);
-      xmax[(s * 2 + half) * 128 + row] = mine;
-      if (!meet(j)) { ok = false; break; }
-      const float tile_max = fmaxf(__bfloat162float(mine), __bfloat162float(xmax[(s * 2 + (half ^ 1)) * 128 + row]));
-      // first tile, or a jump of more than 2^64 somewhere in the row group: take the tile's own maximum as reference
+      const float tile_max = mx * c;
+      // first tile, or a jump of more than 2^64 somewhere in the warp: take the tile's own maximum as reference
       if (__any_sync(0xffffffffu, tile_max - next > 64.f)) next = fmaxf(next, tile_max);
       const float use = (next == -INFINITY) ? 0.f : next;
       const float alpha = ex2_fast(ref - use);   // 0 for the first tile, 1 while the reference stays put
       float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
       // P buffer s was last read by the product of tile j-2, whose o_full this thread waited for in iteration j-1
-      uint8_t* prow = sP + s * PT + half * BLK + row * 128;
+      uint8_t* prow = sP + s * PT + row * 128;
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        float e[8];
+      for (int cc = 0; cc < 4; ++cc) {
+        uint8_t* blk = prow + (cc >> 1) * BLK;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) e[i] = ex2_fast(fmaf(v[q * 8 + i], c, -use));
-        rs0 += e[0] + e[4];
-        rs1 += e[1] + e[5];
-        rs2 += e[2] + e[6];
-        rs3 += e[3] + e[7];
-        uint4 u;
-        u.x = pack_bf16x2(e[0], e[1]);
-        u.y = pack_bf16x2(e[2], e[3]);
-        u.z = pack_bf16x2(e[4], e[5]);
-        u.w = pack_bf16x2(e[6], e[7]);
-        *reinterpret_cast<uint4*>(prow + ((q ^ (row & 7)) << 4)) = u;
+        for (int q = 0; q < 4; ++q) {
+          float e[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) e[i] = ex2_fast(fmaf(v[cc * 32 + q * 8 + i], c, -use));
+          rs0 += e[0] + e[4];
+          rs1 += e[1] + e[5];
+          rs2 += e[2] + e[6];
+          rs3 += e[3] + e[7];
+          uint4 u;
+          u.x = pack_bf16x2(e[0], e[1]);
+          u.y = pack_bf16x2(e[2], e[3]);
+          u.z = pack_bf16x2(e[4], e[5]);
+          u.w = pack_bf16x2(e[6], e[7]);
+          const int chunk = (cc & 1) * 4 + q;
+          *reinterpret_cast<uint4*>(blk + ((chunk ^ (row & 7)) << 4)) = u;
+        }
       }
       l = fmaf(l, alpha, (rs0 + rs1) + (rs2 + rs3));
       if (j > 0) {
-        // product of tile j-1 done: until the arrive below the accumulator is free to touch
+        // product of tile j-1 done: P buffer s^1 and (after the arrive below) the accumulator are free to touch
         if (!__all_sync(0xffffffffu, mbar_wait(o_full, (j - 1) & 1, abort_flag, g.err, ERR_WAIT_TMEM_FULL))) { ok = false; break; }
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
           tc_fence_after();
 #pragma unroll
-          for (int cc = 0; cc < OC; ++cc) {
+          for (int cc = 0; cc < D / 32; ++cc) {
             float o[32];
-            const uint32_t at = lane_addr + 256 + half * (D / 2) + cc * 32;
-            tmem_ld32(at, o);
+            tmem_ld32(lane_addr + 256 + cc * 32, o);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] *= alpha;
-            tmem_st32(at, o);
+            tmem_st32(lane_addr + 256 + cc * 32, o);
           }
           tmem_st_wait();
         }
@@ -303,22 +290,16 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
     }
     if (ok && T > 0) ok = __all_sync(0xffffffffu, mbar_wait(o_full, (T - 1) & 1, abort_flag, g.err, ERR_WAIT_TMEM_FULL));
     if (ok) {
-      // every softmax warp has arrived on p_full of the last tile, i.e. is past its last read of the exchange area
-      xsum[half * 128 + row] = l;
-      ok = meet(T);
-    }
-    if (ok) {
       tc_fence_after();
-      const float lt = l + xsum[(half ^ 1) * 128 + row];
       const bool live = q0 + row < g.Sq;
-      const float inv = lt > 0.f ? 1.f / lt : 0.f;
-      __nv_bfloat16* dst = g.out + (size_t(bh) * g.Sq + q0 + row) * D + half * (D / 2);
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = g.out + (size_t(bh) * g.Sq + q0 + row) * D;
 #pragma unroll
-      for (int cc = 0; cc < OC; ++cc) {
+      for (int cc = 0; cc < D / 32; ++cc) {
         float o[32];
-        tmem_ld32(lane_addr + 256 + half * (D / 2) + cc * 32, o);
+        tmem_ld32(lane_addr + 256 + cc * 32, o);
         tmem_ld_wait();
-        if (live) {
+        if (live && T > 0) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 u;
@@ -330,14 +311,13 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
           }
         }
       }
-      if (live && half == 0 && g.lse)
-        g.lse[size_t(bh) * g.Sq + q0 + row] = lt > 0.f ? (ref + log2f(lt)) * 0.6931471805599453f : -INFINITY;
+      if (live && g.lse) g.lse[size_t(bh) * g.Sq + q0 + row] = l > 0.f ? (ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 5) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
