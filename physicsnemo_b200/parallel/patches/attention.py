@@ -22,9 +22,26 @@ from .. import collectives as C
 from ._common import MissingShardPatch, NO_TF, ShardTensor, is_st, local, register, resolved, wrap
 
 
+def _flash_block_ok(q, k, v) -> bool:
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        return False
+    if not q.is_cuda:
+        return False
+    from ...ops import attention as _fa
+
+    return _fa.supported(q, k, v)
+
+
 def _block(q, k, v, scale, mask=None):
     """Un-normalised attention of one K/V block: (max, sumexp, weighted values), fp32."""
     acc = torch.float32 if q.dtype in (torch.bfloat16, torch.float16) else q.dtype
+    if mask is None and _flash_block_ok(q, k, v):
+        # flash kernel: normalised output + log-sum-exp, i.e. the triple (lse, 1, out); no S matrix in memory.
+        # Only without autograd: the merge differentiates through the log-sum-exp, which the kernel does not.
+        from ...ops import attention as _fa
+
+        out, lse = _fa.flash_forward(q, k, v, False, scale)
+        return lse.unsqueeze(-1), torch.ones_like(lse).unsqueeze(-1), out.to(acc)
     s = torch.matmul(q, k.transpose(-2, -1)).to(acc) * scale
     if mask is not None:
         s = s + mask

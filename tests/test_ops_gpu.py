@@ -152,3 +152,23 @@ def test_flash_attention_growing_scores_rescale_the_accumulator(d):
     assert torch.isfinite(out.float()).all()
     assert (out.float() - ref).abs().max().item() < 3e-2
     assert ((lse - ref_lse).abs() / ref_lse.abs().clamp_min(1.0)).max().item() < 2e-3
+
+
+@pytest.mark.gpu
+def test_ring_attention_blocks_merge_with_flash_kernel():
+    """Two K/V blocks processed by the flash kernel and merged by their log-sum-exp equal attention over the whole sequence."""
+    from physicsnemo_b200.parallel.patches.attention import _block, _merge
+
+    torch.manual_seed(0)
+    q = torch.randn(2, 4, 256, 64, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(2, 4, 512, 64, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(2, 4, 512, 64, device="cuda", dtype=torch.bfloat16)
+    scale = 1 / 8.0
+    with torch.no_grad():
+        acc = None
+        for lo, hi in ((0, 200), (200, 512)):                    # uneven shards, as a ring over ranks would deliver them
+            acc = _merge(acc, _block(q, k[:, :, lo:hi].contiguous(), v[:, :, lo:hi].contiguous(), scale))
+        m, l, o = acc
+        got = o / l
+    ref, _ = _sdpa_fp32(q, k, v, False, scale)
+    assert (got - ref).abs().max().item() < 2e-2
