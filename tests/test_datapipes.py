@@ -122,3 +122,110 @@ def test_pde_kernels_match_tensor_formulation():
     assert (k.seq_rho - r).abs().max() < 1e-4 and (k.seq_vel - v).abs().max() < 1e-4 and (k.seq_p - p).abs().max() < 2e-4
     out = next(iter(k))
     assert out["density"].shape == (2, 2, 1, 64, 64)
+
+
+# ---- domain datapipes --------------------------------------------------------------------------------------------------
+def test_domino_datapipe_feeds_the_model():
+    import copy
+
+    from physicsnemo_b200.datapipes.cae import DoMINODataPipe, compute_scaling_factors
+    from physicsnemo_b200.mesh import primitives
+    from physicsnemo_b200.models.domino import DEFAULT_MODEL_PARAMS, DoMINO
+
+    torch.manual_seed(0)
+    s = primitives.icosphere(3)
+    V, F = s.points.float() * 0.5, s.cells
+    tri = V[F]
+    n = torch.linalg.cross(tri[:, 1] - tri[:, 0], tri[:, 2] - tri[:, 0])
+    centers, areas, normals = tri.mean(1), 0.5 * n.norm(dim=-1), n / n.norm(dim=-1, keepdim=True)
+    vol = torch.rand(3000, 3) * 2 - 1
+    sample = dict(stl_coordinates=V, stl_faces=F.reshape(-1), stl_centers=centers, stl_areas=areas, global_params_values=torch.tensor([[30.0], [1.2]]),
+                  global_params_reference=torch.tensor([[30.0], [1.2]]), surface_mesh_centers=centers, surface_normals=normals, surface_areas=areas,
+                  surface_fields=torch.randn(centers.shape[0], 4) * 3 + 1, volume_mesh_centers=vol, volume_fields=torch.randn(3000, 5))
+    factors = compute_scaling_factors([sample])
+    assert torch.allclose(factors["surface_fields"]["mean"], sample["surface_fields"].mean(0), atol=1e-4)
+    pipe = DoMINODataPipe(model_type="combined", dataset=[sample], device="cpu", bounding_box_dims=[(1, 1, 1), (-1, -1, -1)],
+                          bounding_box_dims_surf=[(0.6, 0.6, 0.6), (-0.6, -0.6, -0.6)], grid_resolution=(8, 8, 8), sampling=True,
+                          surface_points_sample=64, volume_points_sample=80, geom_points_sample=300, num_surface_neighbors=5,
+                          normalize_coordinates=False, deterministic=True, scaling_type="mean_std_scaling",
+                          surface_factors=torch.stack([factors["surface_fields"]["mean"], factors["surface_fields"]["std"]]),
+                          volume_factors=torch.stack([factors["volume_fields"]["mean"], factors["volume_fields"]["std"]]))
+    out = pipe[0]
+    assert out["surface_mesh_neighbors"].shape == (1, 64, 4, 3) and out["sdf_grid"].shape == (1, 8, 8, 8)
+    r = out["volume_mesh_centers"][0].norm(dim=-1)
+    assert (out["sdf_nodes"][0, :, 0] - (r - 0.5)).abs().max() < 5e-3                       # signed distance to the sphere
+    assert torch.allclose(out["pos_volume_closest"][0].norm(dim=-1), out["sdf_nodes"][0, :, 0].abs(), atol=1e-4)
+    _, back = pipe.unscale_model_outputs(surface_fields=out["surface_fields"])
+    assert float(back.std()) == pytest.approx(3.0, rel=0.2)
+    p = copy.deepcopy(DEFAULT_MODEL_PARAMS)
+    p.interp_res = [8, 8, 8]
+    gc, gl = p.geometry_rep.geo_conv, p.geometry_local
+    gc.volume_radii, gc.volume_neighbors_in_radius, gc.surface_radii, gc.surface_neighbors_in_radius = [0.5], [4], [0.5], [4]
+    gl.volume_radii, gl.volume_neighbors_in_radius, gl.surface_radii, gl.surface_neighbors_in_radius = [0.6], [4], [0.6], [4]
+    p.nn_basis_functions.base_layer = p.aggregation_model.base_layer = p.position_encoder.base_neurons = 8
+    p.num_neighbors_volume, p.num_neighbors_surface = 2, 5
+    model = DoMINO(input_features=3, output_features_vol=5, output_features_surf=4, model_parameters=p)
+    vol_pred, surf_pred = model(out)
+    assert vol_pred.shape == out["volume_fields"].shape and surf_pred.shape == out["surface_fields"].shape
+    with pytest.raises(ValueError):
+        pipe.process_data({"stl_coordinates": V})
+
+
+def test_climate_datapipes(tmp_path):
+    from physicsnemo_b200.datapipes.climate import ERA5Datapipe, SyntheticWeatherDataLoader
+
+    loader = SyntheticWeatherDataLoader(channels=[0, 1, 2], num_samples_per_year=12, num_steps=2, device="cpu", grid_size=(8, 16),
+                                        batch_size=4, seed=1)
+    batch = next(iter(loader))[0]
+    assert batch["invar"].shape == (4, 3, 8, 16) and batch["outvar"].shape == (4, 2, 3, 8, 16)
+    assert float(batch["invar"][:, 0].mean()) > float(batch["invar"][:, 2].mean())          # lapse rate: higher channels are colder
+    rng = np.random.default_rng(0)
+    for year in (2000, 2001):
+        np.save(tmp_path / f"{year}.npy", rng.normal(5.0, 2.0, size=(10, 4, 9, 12)).astype(np.float32))
+    stats = tmp_path / "stats"
+    stats.mkdir()
+    np.save(stats / "global_means.npy", np.full((1, 4, 1, 1), 5.0, np.float32))
+    np.save(stats / "global_stds.npy", np.full((1, 4, 1, 1), 2.0, np.float32))
+    pipe = ERA5Datapipe(str(tmp_path), str(stats), channels=[0, 2], batch_size=3, num_steps=2, stride=2, num_history=1, patch_size=4,
+                        shuffle=False, device="cpu")
+    items = list(pipe)
+    assert len(items) == len(pipe) == (2 * (10 - 2 - 4)) // 3
+    b = items[0][0]
+    assert b["invar"].shape == (3, 2, 2, 8, 12) and b["outvar"].shape == (3, 2, 2, 8, 12)
+    raw = np.load(tmp_path / "2000.npy")
+    assert torch.allclose(b["invar"][0, 1], torch.from_numpy((raw[2][[0, 2]][:, :8] - 5.0) / 2.0), atol=1e-6)   # first window starts at t = 2
+    assert torch.allclose(b["invar"][0, 0], torch.from_numpy((raw[0][[0, 2]][:, :8] - 5.0) / 2.0), atol=1e-6)   # history is one stride back
+    assert torch.allclose(b["outvar"][0, 1], torch.from_numpy((raw[6][[0, 2]][:, :8] - 5.0) / 2.0), atol=1e-6)
+    halves = [ERA5Datapipe(str(tmp_path), None, batch_size=1, shuffle=True, seed=3, device="cpu", process_rank=r, world_size=2) for r in (0, 1)]
+    seen = [torch.stack([it[0]["invar"] for it in h]).sum().item() for h in halves]
+    assert len(halves[0]) == len(halves[1]) and seen[0] != seen[1]                           # ranks read disjoint halves
+
+
+def test_mesh_graph_time_series_dataset(tmp_path):
+    from physicsnemo_b200.datapipes.gnn import VortexSheddingDataset, cells_to_edges, load_json, save_json
+
+    rng = np.random.default_rng(0)
+    pos = rng.random((6, 2)).astype(np.float32)
+    cells = np.array([[0, 1, 2], [1, 2, 3], [2, 3, 4], [3, 4, 5]])
+    traj = dict(mesh_pos=pos, cells=cells, node_type=np.array([0, 0, 4, 6, 0, 5]), velocity=rng.normal(size=(5, 6, 2)).astype(np.float32),
+                pressure=rng.normal(size=(5, 6, 1)).astype(np.float32))
+    ei = cells_to_edges(torch.as_tensor(cells))
+    assert ei.shape == (2, 18)                                        # 9 unique edges, both directions
+    np.savez(tmp_path / "traj0.npz", **traj)
+    ds = VortexSheddingDataset.from_npz_dir(tmp_path, split="train", noise_std=0.0)
+    assert len(ds) == 4
+    s = ds[1]
+    assert s["x"].shape == (6, 2 + 7) and s["edge_attr"].shape == (18, 3) and s["y"].shape == (6, 3)
+    dv, p = ds.denormalize(s["y"])
+    assert torch.allclose(dv, torch.as_tensor(traj["velocity"][2] - traj["velocity"][1]), atol=1e-5)
+    assert torch.allclose(p, torch.as_tensor(traj["pressure"][2]), atol=1e-5)
+    save_json(ds.node_stats, tmp_path / "node_stats.json")
+    stats = load_json(tmp_path / "node_stats.json")
+    val = VortexSheddingDataset([traj], split="valid", node_stats=stats, edge_stats=ds.edge_stats)
+    assert torch.allclose(val[1]["y"], s["y"], atol=1e-5)
+    noisy = VortexSheddingDataset([traj], split="train", noise_std=0.1)[0]
+    clean = VortexSheddingDataset([traj], split="train", noise_std=0.0)[0]
+    moved = (noisy["x"][:, :2] - clean["x"][:, :2]).abs().sum(-1) > 0
+    assert moved.tolist() == [True, True, False, False, True, False]  # only normal nodes are perturbed
+    with pytest.raises(ValueError):
+        VortexSheddingDataset([traj], split="test")
