@@ -1,0 +1,99 @@
+"""experimental: LoRA adapters and the variational GP head."""
+import pytest
+import torch
+import torch.nn as nn
+
+
+class _Net(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.embed = nn.Linear(4, 16)
+        self.blocks = nn.ModuleList([nn.Sequential(nn.Linear(16, 16), nn.GELU(), nn.Linear(16, 16)) for _ in range(2)])
+        self.norm = nn.LayerNorm(16)
+        self.head = nn.Linear(16, 3)
+
+    def forward(self, x):
+        x = self.embed(x)
+        for b in self.blocks:
+            x = x + b(x)
+        return self.head(self.norm(x))
+
+
+def test_lora_apply_train_save_load_merge(tmp_path):
+    from physicsnemo_b200.experimental.peft import (LoRAConfig, apply_lora, is_lora_layer, load_adapter, merge_lora, save_adapter,
+                                                    set_adapter_enabled, split_params_for_optimizer)
+
+    torch.manual_seed(0)
+    base = _Net()
+    ref_state = {k: v.clone() for k, v in base.state_dict().items()}
+    x = torch.randn(5, 4)
+    y0 = base(x)
+    res = apply_lora(base, LoRAConfig(rank=4, alpha=8, target_pattern=r"blocks\.\d+\.[02]$", extras_trainable=["norm"]))
+    assert res.n_wrapped == 4 and res.n_trainable == 4 * (16 * 4 + 4 * 16) + 32
+    assert torch.allclose(base(x), y0)                                            # lora_B starts at zero
+    groups = split_params_for_optimizer(base)
+    assert len(groups["lora"]) == 8 and len(groups["extras"]) == 2 and all(not p.requires_grad for p in groups["frozen"])
+    opt = torch.optim.Adam(groups["lora"] + groups["extras"], lr=1e-2)
+    for _ in range(5):
+        opt.zero_grad()
+        (base(x) - 1.0).square().mean().backward()
+        opt.step()
+    y1 = base(x)
+    assert not torch.allclose(y1, y0)
+    assert torch.equal(base.embed.weight, ref_state["embed.weight"])              # the base stays frozen
+    set_adapter_enabled(base, False)
+    assert torch.allclose(_hidden(base, x), _hidden_of_state(ref_state, x), atol=1e-6)   # adapters off: the frozen trunk is unchanged
+    set_adapter_enabled(base, True)
+    save_adapter(base, tmp_path / "adapter.zip")
+    fresh = _Net()
+    fresh.load_state_dict(ref_state)
+    load_adapter(fresh, tmp_path / "adapter.zip")
+    assert torch.allclose(fresh(x), y1, atol=1e-6)
+    merged = merge_lora(fresh)
+    assert not any(is_lora_layer(m) for m in merged.modules()) and torch.allclose(merged(x), y1, atol=1e-5)
+    other = nn.Sequential(nn.Linear(4, 3))
+    with pytest.raises(ValueError):
+        load_adapter(other, tmp_path / "adapter.zip")                             # different architecture
+    with pytest.raises(ValueError):
+        LoRAConfig(rank=4)
+    with pytest.raises(ValueError):
+        apply_lora(base, LoRAConfig(target_modules=["embed"]))                    # not re-entrant
+
+
+def _hidden_of_state(state, x):
+    net = _Net()
+    net.load_state_dict(state)
+    return _hidden(net, x)
+
+
+def _hidden(net, x):
+    h = net.embed(x)
+    for b in net.blocks:
+        h = h + b(h)
+    return h
+
+
+def test_variational_gp_head_fits_a_function():
+    from physicsnemo_b200.experimental.uq import VariationalGPHead
+
+    torch.manual_seed(0)
+    x = torch.linspace(-2, 2, 120).unsqueeze(1)
+    y = torch.sin(2 * x[:, 0]) + 0.05 * torch.randn(120)
+    head = VariationalGPHead(input_dim=1, n_train=120, n_inducing=16, inducing_points=torch.linspace(-2, 2, 16).unsqueeze(1), lengthscale_range=(0.05, 5.0))
+    first = float(head.loss(x, y))
+    opt = torch.optim.Adam(head.parameters(), lr=0.05)
+    for _ in range(250):
+        opt.zero_grad()
+        loss = head.loss(x, y)
+        loss.backward()
+        opt.step()
+    assert float(loss) < first - 0.5
+    pred = head.predict(x)
+    assert pred.mean.dtype == torch.float32 and float((pred.mean - torch.sin(2 * x[:, 0])).abs().mean()) < 0.1
+    inside = ((y > pred.lower) & (y < pred.upper)).float().mean()
+    assert float(inside) > 0.85
+    far = head.predict(torch.tensor([[6.0]]))
+    assert float(far.variance) > 2 * float(pred.variance.mean())                   # uncertainty grows away from the data
+    dist = head(x[:5])
+    assert dist.covariance_matrix.shape == (5, 5) and torch.allclose(dist.covariance_matrix, dist.covariance_matrix.t(), atol=1e-6)
+    assert float(head.gp_layer.kl_divergence()) >= 0
