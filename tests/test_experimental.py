@@ -97,3 +97,40 @@ def test_variational_gp_head_fits_a_function():
     dist = head(x[:5])
     assert dist.covariance_matrix.shape == (5, 5) and torch.allclose(dist.covariance_matrix, dist.covariance_matrix.t(), atol=1e-6)
     assert float(head.gp_layer.kl_divergence()) >= 0
+
+
+def test_ood_guard_bounds_and_knn():
+    from physicsnemo_b200.experimental.guardrails import OODGuard
+
+    torch.manual_seed(0)
+    guard = OODGuard(buffer_size=64, global_dim=2, geometry_embed_dim=8, knn_k=4, sensitivity=1.5)
+    base = torch.randn(8)
+    for _ in range(5):                                                # 80 samples through a 64-slot ring buffer
+        guard.collect(torch.rand(16, 2) * 2 + 1, base + 0.1 * torch.randn(16, 8))
+    assert bool(guard.geo_full) and float(guard.global_min.min()) >= 1.0 and float(guard.global_max.max()) <= 3.0
+    flags = guard.check(torch.tensor([[2.0, 2.0], [5.0, 2.0]]), torch.stack([base + 0.1 * torch.randn(8), -base]))
+    assert flags["global"].tolist() == [False, True] and flags["geometry"].tolist() == [False, True]
+    assert torch.isfinite(guard.knn_threshold)
+    state = guard.state_dict()
+    clone = OODGuard(buffer_size=64, global_dim=2, geometry_embed_dim=8, knn_k=4)
+    clone.load_state_dict(state)
+    assert torch.equal(clone.geo_embeddings, guard.geo_embeddings)
+    with pytest.raises(ValueError):
+        guard.check(geometry_latent=torch.randn(2, 3, 8))
+
+
+def test_torch_gmm_recovers_two_clusters():
+    from physicsnemo_b200.experimental.guardrails import TorchGMM
+
+    torch.manual_seed(0)
+    a = torch.randn(300, 2) * 0.3 + torch.tensor([2.0, 0.0])
+    b = torch.randn(200, 2) * 0.5 + torch.tensor([-2.0, 1.0])
+    gmm = TorchGMM(2, max_iter=200, tol=1e-5).fit(torch.cat([a, b]))
+    order = gmm.means_[:, 0].argsort()
+    assert torch.allclose(gmm.means_[order], torch.tensor([[-2.0, 1.0], [2.0, 0.0]], dtype=gmm.means_.dtype), atol=0.15)
+    assert torch.allclose(gmm.weights_[order], torch.tensor([0.4, 0.6], dtype=gmm.weights_.dtype), atol=0.03)
+    inside, outside = gmm.score_samples(torch.tensor([[2.0, 0.0]])), gmm.score_samples(torch.tensor([[0.0, -6.0]]))
+    assert float(inside) > float(outside) + 10
+    other = TorchGMM(2)
+    other.set_state(gmm.get_state())
+    assert torch.allclose(other.score_samples(a[:5]), gmm.score_samples(a[:5]).cpu())
