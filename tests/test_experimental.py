@@ -134,3 +134,52 @@ def test_torch_gmm_recovers_two_clusters():
     other = TorchGMM(2)
     other.set_state(gmm.get_state())
     assert torch.allclose(other.score_samples(a[:5]), gmm.score_samples(a[:5]).cpu())
+
+
+def test_rope_tables_and_projection():
+    import math
+
+    from physicsnemo_b200.experimental.nn import (apply_rope, build_axial_rope_cos_sin_2d_continuous, spherical_centroid,
+                                                  stereographic_projection)
+
+    torch.manual_seed(0)
+    q, k = torch.randn(2, 5, 8), torch.randn(2, 5, 8)
+    xa, ya = torch.rand(5) * 3, torch.rand(5) * 3
+    cos, sin = build_axial_rope_cos_sin_2d_continuous(xa, ya, 8)
+    shift = torch.tensor(0.7)
+    cos2, sin2 = build_axial_rope_cos_sin_2d_continuous(xa + shift, ya - shift, 8)
+    s1 = apply_rope(q, cos, sin) @ apply_rope(k, cos, sin).transpose(-1, -2)
+    s2 = apply_rope(q, cos2, sin2) @ apply_rope(k, cos2, sin2).transpose(-1, -2)
+    assert torch.allclose(s1, s2, atol=1e-4)                         # scores depend on relative positions only
+    assert torch.allclose(apply_rope(q, cos, sin).norm(dim=-1), q.norm(dim=-1), atol=1e-5)
+    lat = torch.tensor([[0.1, 0.2], [0.15, 0.25]])
+    lon = torch.tensor([[1.0, 1.1], [1.05, 1.2]])
+    lat0, lon0 = spherical_centroid(lat, lon)
+    x, y = stereographic_projection(lat0, lon0, lat0, lon0)
+    assert abs(float(x)) < 1e-6 and abs(float(y)) < 1e-6           # the centre maps to the origin
+    x, y = stereographic_projection(lat, lon, lat0, lon0)
+    assert float(torch.hypot(x, y).max()) < 0.2
+    with pytest.raises(ValueError):
+        build_axial_rope_cos_sin_2d_continuous(xa, ya, 6)
+    assert math.isclose(float(cos[0, 0]), math.cos(float(xa[0])), rel_tol=1e-5)
+
+
+def test_cached_dataset_and_prefetch(tmp_path):
+    from physicsnemo_b200.experimental.utils import CachedPreprocessingDataset, prefetch_map
+
+    calls = []
+
+    class DS(CachedPreprocessingDataset):
+        @staticmethod
+        def preprocess(sample_path):
+            calls.append(sample_path.name)
+            return {"n": torch.tensor(int(sample_path.stem))}
+
+    for i in range(3):
+        (tmp_path / f"{i}.txt").write_text("x")
+    ds = DS([tmp_path / f"{i}.txt" for i in range(3)], cache_dir=tmp_path / "cache")
+    assert [int(ds[i]["n"]) for i in range(3)] == [0, 1, 2] and [int(ds[i]["n"]) for i in range(3)] == [0, 1, 2]
+    assert calls == ["0.txt", "1.txt", "2.txt"]                      # the second pass came from the cache
+    assert list(prefetch_map(range(5), lambda v: v * v)) == [0, 1, 4, 9, 16] and len(prefetch_map(range(5), abs)) == 5
+    with pytest.raises(FileNotFoundError):
+        DS([tmp_path / "missing.txt"])
