@@ -100,3 +100,80 @@ extern "C" int pnm_silu_derivative(const void* x, const void* g, void* out, long
   cudaStream_t st = (cudaStream_t)stream;
   return dtype == 0 ? pnm::launch_silu<__nv_bfloat16>(x, g, out, n, order, st) : pnm::launch_silu<float>(x, g, out, n, order, st);
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// EDM noise conditioning in one launch: sinusoidal embedding of the noise level (sin half first, then cos half: the
+// "swapped" order the U-Net uses), optional additive term (class / augmentation embedding), then two Linear + SiLU
+// layers.  out[b, :] = silu(W1 silu(W0 (emb(noise[b]) + extra[b]) + b0) + b1).
+//
+// One CTA per batch row.  A warp owns one output channel at a time: its lanes stride over the input channels (coalesced
+// reads of one weight row) and reduce by shuffles; the hidden vector lives in shared memory between the two layers.  The
+// weights (fp32 or bf16) are a megabyte or two and stay in L2 across the CTAs.
+namespace pnm {
+
+template <typename T> __device__ __forceinline__ float cond_ld(const T* p);
+template <> __device__ __forceinline__ float cond_ld<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float cond_ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+template <typename T>
+__global__ void __launch_bounds__(512) edm_conditioning_kernel(const float* __restrict__ noise, const float* __restrict__ freqs,
+                                                               const float* __restrict__ extra, const T* __restrict__ w0,
+                                                               const T* __restrict__ b0, const T* __restrict__ w1,
+                                                               const T* __restrict__ b1, float* __restrict__ out, int C, int E) {
+  extern __shared__ float cond_smem[];
+  float* emb = cond_smem;      // [C]
+  float* hid = cond_smem + C;  // [E]
+  const int b = blockIdx.x, half = C / 2;
+  const float sigma = noise[b];
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float a = sigma * freqs[c < half ? c : c - half];
+    float v = c < half ? sinf(a) : cosf(a);
+    if (extra) v += extra[(size_t)b * C + c];
+    emb[c] = v;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int e = warp; e < E; e += nwarps) {
+    const T* row = w0 + (size_t)e * C;
+    float acc = 0.f;
+    for (int c = lane; c < C; c += 32) acc = fmaf(cond_ld(row + c), emb[c], acc);
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+      const float z = acc + (b0 ? cond_ld(b0 + e) : 0.f);
+      hid[e] = z / (1.f + __expf(-z));
+    }
+  }
+  __syncthreads();
+  for (int e = warp; e < E; e += nwarps) {
+    const T* row = w1 + (size_t)e * E;
+    float acc = 0.f;
+    for (int c = lane; c < E; c += 32) acc = fmaf(cond_ld(row + c), hid[c], acc);
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+      const float z = acc + (b1 ? cond_ld(b1 + e) : 0.f);
+      out[(size_t)b * E + e] = z / (1.f + __expf(-z));
+    }
+  }
+}
+
+}  // namespace pnm
+
+extern "C" int pnm_edm_conditioning(const float* noise, const float* freqs, const float* extra, const void* w0, const void* b0,
+                                    const void* w1, const void* b1, float* out, int B, int C, int E, int weight_dtype,
+                                    void* stream) {
+  if (!noise || !freqs || !w0 || !w1 || !out || B <= 0 || C <= 0 || (C & 1) || E <= 0) return -1;
+  const size_t smem = size_t(C + E) * sizeof(float);
+  if (smem > 48 * 1024) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (weight_dtype == 1) {
+    pnm::edm_conditioning_kernel<float><<<B, 512, smem, st>>>(noise, freqs, extra, (const float*)w0, (const float*)b0, (const float*)w1,
+                                                             (const float*)b1, out, C, E);
+  } else if (weight_dtype == 0) {
+    using bf = __nv_bfloat16;
+    pnm::edm_conditioning_kernel<bf><<<B, 512, smem, st>>>(noise, freqs, extra, (const bf*)w0, (const bf*)b0, (const bf*)w1, (const bf*)b1,
+                                                          out, C, E);
+  } else {
+    return -1;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

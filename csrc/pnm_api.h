@@ -169,6 +169,11 @@ int pnm_conv2d_nhwc_halo(const void* x, const void* weight, void* y, int n, int 
 int pnm_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int BH, int Sq, int Skv, int D,
                        int ldv, float scale, int causal, int v_transposed, void* stream);
 
+// EDM noise conditioning: out[B,E] (fp32) = silu(W1 silu(W0 (emb + extra) + b0) + b1) with emb[b] = [sin(noise[b] f), cos(noise[b] f)],
+// f = freqs[C/2]; extra [B,C] fp32 optional; weights row-major [E,C] and [E,E], biases optional; weight_dtype 0 = bf16, 1 = fp32.
+int pnm_edm_conditioning(const float* noise, const float* freqs, const float* extra, const void* w0, const void* b0, const void* w1,
+                         const void* b1, float* out, int B, int C, int E, int weight_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

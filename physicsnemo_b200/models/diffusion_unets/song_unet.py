@@ -185,19 +185,40 @@ class SongUNet(Module):
         """Noise / class / augmentation conditioning vector (B, emb_channels)."""
         if self.embedding_type == "zero":
             return self.zero_emb.repeat(noise_labels.shape[0], 1)
-        emb = self.map_noise(noise_labels)
-        shape = emb.shape
-        emb = emb.reshape(shape[0], 2, -1)  # swap the sin / cos halves
-        emb = torch.concat([emb[:, 1:], emb[:, :1]], dim=1).reshape(*shape)
+        extra = None
         if self.map_label is not None:
             tmp = class_labels
             if self.training and self.label_dropout:
                 tmp = tmp * (torch.rand([x.shape[0], 1], device=x.device) >= self.label_dropout).to(tmp.dtype)
-            emb = emb + self.map_label(tmp * np.sqrt(self.map_label.in_features))
+            extra = self.map_label(tmp * np.sqrt(self.map_label.in_features))
         if self.map_augment is not None and augment_labels is not None:
-            emb = emb + self.map_augment(augment_labels)
+            aug = self.map_augment(augment_labels)
+            extra = aug if extra is None else extra + aug
+        if self._fused_conditioning_ok(noise_labels):
+            # one launch: [sin, cos] embedding (+ extra) -> Linear + SiLU -> Linear + SiLU
+            from ...ops import conditioning as _cond
+
+            out = _cond.edm_conditioning(noise_labels, self.map_noise.freqs, self.map_layer0.weight, self.map_layer0.bias,
+                                         self.map_layer1.weight, self.map_layer1.bias, extra)
+            return out.to(x.dtype) if self.map_layer0.amp_mode or x.dtype != torch.float32 else out
+        emb = self.map_noise(noise_labels)
+        shape = emb.shape
+        emb = emb.reshape(shape[0], 2, -1)  # swap the sin / cos halves
+        emb = torch.concat([emb[:, 1:], emb[:, :1]], dim=1).reshape(*shape)
+        if extra is not None:
+            emb = emb + extra
         emb = silu(self.map_layer0(emb))
         return silu(self.map_layer1(emb))
+
+    def _fused_conditioning_ok(self, noise_labels) -> bool:
+        mn = self.map_noise
+        if not noise_labels.is_cuda or noise_labels.dim() != 1 or not isinstance(mn, PositionalEmbedding):
+            return False
+        if mn.learnable or mn.embed_fn != "cos_sin" or not hasattr(self.map_layer0, "weight"):
+            return False
+        from ...ops import conditioning as _cond
+
+        return _cond.supported(noise_labels, mn.freqs, self.map_layer0.weight, self.map_layer1.weight)
 
     @staticmethod
     def _extent(x):

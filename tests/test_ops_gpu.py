@@ -172,3 +172,49 @@ def test_ring_attention_blocks_merge_with_flash_kernel():
         got = o / l
     ref, _ = _sdpa_fp32(q, k, v, False, scale)
     assert (got - ref).abs().max().item() < 2e-2
+
+
+# ---- EDM conditioning --------------------------------------------------------------------------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_edm_conditioning_kernel(dtype):
+    from physicsnemo_b200.ops import conditioning as C
+
+    torch.manual_seed(0)
+    B, Cn, E = 8, 128, 512
+    noise = (torch.randn(B, device="cuda") * 1.2 - 1.2).exp()
+    freqs = (1 / 10000) ** (torch.arange(Cn // 2, device="cuda") / (Cn // 2 - 1))
+    w0 = (torch.randn(E, Cn, device="cuda") / Cn ** 0.5).to(dtype).requires_grad_(True)
+    b0 = (0.1 * torch.randn(E, device="cuda")).to(dtype).requires_grad_(True)
+    w1 = (torch.randn(E, E, device="cuda") / E ** 0.5).to(dtype).requires_grad_(True)
+    b1 = (0.1 * torch.randn(E, device="cuda")).to(dtype).requires_grad_(True)
+    extra = (0.3 * torch.randn(B, Cn, device="cuda")).requires_grad_(True)
+    assert C.supported(noise, freqs, w0, w1)
+    out = C.edm_conditioning(noise, freqs, w0, b0, w1, b1, extra)
+    ref = C.reference(noise, freqs, w0, b0, w1, b1, extra)
+    assert out.dtype == torch.float32 and (out - ref).abs().max().item() < (2e-5 if dtype == torch.float32 else 2e-3)
+    g = torch.randn_like(out)
+    got = torch.autograd.grad(out, (w0, b0, w1, b1, extra), g)
+    want = torch.autograd.grad(ref, (w0, b0, w1, b1, extra), g)
+    for a, b in zip(got, want):
+        assert torch.allclose(a.float(), b.float(), atol=1e-4, rtol=1e-3)
+
+
+@pytest.mark.gpu
+def test_song_unet_uses_fused_conditioning():
+    from physicsnemo_b200.models.diffusion_unets import SongUNet
+    from physicsnemo_b200.ops import conditioning as C
+
+    torch.manual_seed(0)
+    net = SongUNet(img_resolution=16, in_channels=2, out_channels=2, label_dim=3, augment_dim=2, model_channels=32, channel_mult=[1, 2],
+                   num_blocks=1, attn_resolutions=[8]).cuda().eval()
+    x, sigma = torch.randn(4, 2, 16, 16, device="cuda"), torch.rand(4, device="cuda") + 0.1
+    labels, aug = torch.randn(4, 3, device="cuda"), torch.randn(4, 2, device="cuda")
+    assert net._fused_conditioning_ok(sigma)
+    with torch.no_grad():
+        fused = net.conditioning_embedding(x, sigma, labels, aug)
+        emb = net.map_noise(sigma)
+        emb = torch.cat([emb[:, emb.shape[1] // 2:], emb[:, :emb.shape[1] // 2]], dim=1)
+        emb = emb + net.map_label(labels * 3 ** 0.5) + net.map_augment(aug)
+        plain = torch.nn.functional.silu(net.map_layer1(torch.nn.functional.silu(net.map_layer0(emb))))
+    assert torch.allclose(fused, plain, atol=1e-4)
