@@ -93,3 +93,40 @@ def test_exposed_interval_arithmetic():
     assert _uncovered([(0, 10)], [(2, 4), (3, 6)]) == pytest.approx(6.0)
     assert _uncovered([(0, 5), (7, 9)], [(4, 8)]) == pytest.approx(5.0)
     assert _uncovered([(1, 2)], []) == pytest.approx(1.0)
+
+
+# ---- solar geometry ------------------------------------------------------------------------------------------------------
+def test_zenith_angle_and_insolation():
+    import datetime
+
+    import numpy as np
+
+    from physicsnemo_b200.utils.insolation import insolation
+    from physicsnemo_b200.utils.zenith_angle import (cos_zenith_angle, cos_zenith_angle_from_timestamp, irradiance,
+                                                     toa_incident_solar_radiation_accumulated, zenith_azimuth_angles)
+
+    noon = datetime.datetime(2021, 6, 21, 12, 0)                       # June solstice, noon UTC: Sun overhead near (23.44 N, 0 E)
+    assert float(cos_zenith_angle(noon, np.array(0.0), np.array(23.44))) > 0.999
+    assert float(cos_zenith_angle(noon, np.array(180.0), np.array(-23.44))) < -0.999   # antipode: midnight
+    lat, lon = np.linspace(-80, 80, 9)[:, None] * np.ones((1, 8)), np.linspace(0, 315, 8)[None, :] * np.ones((9, 1))
+    cz = cos_zenith_angle(noon, lon, lat)
+    assert cz.shape == (9, 8) and cz.dtype == np.float32
+    ts = noon.replace(tzinfo=datetime.timezone.utc).timestamp()
+    t_lat, t_lon = torch.tensor(lat, dtype=torch.float32), torch.tensor(lon, dtype=torch.float32)
+    assert torch.allclose(cos_zenith_angle_from_timestamp(torch.tensor(ts, dtype=torch.float64), t_lon, t_lat), torch.tensor(cz), atol=1e-6)
+    sz, cz2, sa, ca = zenith_azimuth_angles(noon, lon, lat)
+    assert np.allclose(sz ** 2 + cz2 ** 2, 1, atol=1e-5) and np.allclose(sa ** 2 + ca ** 2, 1, atol=2e-2)
+    assert 1310 < float(irradiance(np.array(ts))) < 1330              # aphelion side of the year
+    jan = datetime.datetime(2021, 1, 4, tzinfo=datetime.timezone.utc).timestamp()
+    assert float(irradiance(np.array(jan))) > 1400                     # perihelion
+    # accumulated TOA radiation over an hour equals the time integral of S max(cos z, 0)
+    acc = toa_incident_solar_radiation_accumulated(np.array(ts), lat, lon, interval=3600)
+    steps = np.linspace(ts - 3600, ts, 121)
+    quad = np.trapezoid(np.stack([np.maximum(cos_zenith_angle_from_timestamp(np.array(s), lon, lat), 0) * float(irradiance(np.array(s))) for s in steps]), steps, axis=0)
+    assert np.allclose(acc, quad, rtol=2e-3, atol=50.0)
+    dates = np.array(["2020-01-01T06", "2020-07-01T18"], dtype="datetime64[h]")
+    sol = insolation(dates, lat, lon)
+    assert sol.shape == (2, 9, 8) and sol.min() >= 0 and sol.dtype == np.float32
+    assert sol[1, -1].mean() > sol[0, -1].mean()                       # the Arctic is lit in July, dark in January
+    with pytest.raises(ValueError):
+        insolation(dates, lat, lon[0])
