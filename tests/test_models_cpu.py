@@ -435,3 +435,34 @@ def test_figconv_factor_grid_helpers():
     assert segment_reduce(vals, seg, 3, "mean").flatten().tolist() == [2.0, 0.0, 3.5]
     assert segment_reduce(vals, seg, 3, "max").flatten().tolist() == [3.0, 0.0, 5.0]
     assert segment_reduce(vals, seg, 3, "var").flatten().tolist() == [1.0, 0.0, 2.25]
+
+
+# ---- point transformer attention -------------------------------------------------------------------------------------
+def test_local_point_transformer_blocks():
+    from physicsnemo_b200.nn.module.point_transformer_attention import (AdaLNResidualMLP, LocalPointTransformerBlock,
+                                                                         LocalTokenCrossAttentionBlock)
+
+    torch.manual_seed(0)
+    blk = LocalPointTransformerBlock(dim=16, num_heads=4, neighbor_k=6, dilation=2, mlp_ratio=2, dropout=0.0, conditioning_dim=5)
+    f, c, cond = torch.randn(40, 16), torch.rand(40, 3), torch.randn(5)
+    for p in blk.parameters():
+        torch.nn.init.normal_(p, std=0.2)
+    ids = torch.arange(40) // 20
+    out = blk(f, c, cond=cond, batch_ids=ids)
+    assert out.shape == (40, 16)
+    f2 = f.clone()
+    f2[20:] = torch.randn(20, 16)                                  # other batch element changes ...
+    assert torch.allclose(blk(f2, c, cond=cond, batch_ids=ids)[:20], out[:20], atol=1e-5)   # ... this one does not see it
+    perm = torch.randperm(40)
+    assert torch.allclose(blk(f[perm], c[perm], cond=cond, batch_ids=ids[perm]), out[perm], atol=1e-5)
+    out.sum().backward()
+    assert all(p.grad is not None for p in blk.parameters())
+    cross = LocalTokenCrossAttentionBlock(dim=16, num_heads=4, neighbor_k=5, mlp_ratio=2, dropout=0.0)
+    q = cross(torch.randn(30, 16), torch.rand(30, 3), torch.randn(12, 16), torch.rand(12, 3))
+    assert q.shape == (30, 16)
+    assert cross(torch.randn(0, 16), torch.rand(0, 3), torch.randn(12, 16), torch.rand(12, 3)).shape == (0, 16)
+    mlp = AdaLNResidualMLP(16, 2, 0.0, conditioning_dim=5)
+    x = torch.randn(7, 16)
+    assert torch.allclose(mlp(x, torch.randn(5)), x + mlp.net(mlp.norm(x)), atol=1e-6)      # zero-initialised modulation
+    with pytest.raises(ValueError):
+        mlp(x)
