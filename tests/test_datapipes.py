@@ -229,3 +229,49 @@ def test_mesh_graph_time_series_dataset(tmp_path):
     assert moved.tolist() == [True, True, False, False, True, False]  # only normal nodes are perturbed
     with pytest.raises(ValueError):
         VortexSheddingDataset([traj], split="test")
+
+
+def test_mesh_transforms_and_dataset(tmp_path):
+    import math
+
+    from physicsnemo_b200.datapipes.mesh_dataset import MeshDataset, MeshReader, save_mesh_npz
+    from physicsnemo_b200.datapipes.transforms.mesh import (CenterMesh, ComputeCellCentroids, ComputeSurfaceNormals, DropMeshFields,
+                                                           MeshToTensorDict, NormalizeMeshFields, RandomRotateMesh, RandomScaleMesh,
+                                                           RenameMeshFields, RestructureTensorDict, RotateMesh, ScaleMesh, SetGlobalField,
+                                                           SubsampleMesh, TranslateMesh)
+    from physicsnemo_b200.mesh import Mesh, primitives
+
+    torch.manual_seed(0)
+    base = primitives.icosphere(2)
+    mesh = Mesh(base.points.float() + torch.tensor([1.0, 2.0, 3.0]), base.cells, point_data={"p": torch.randn(base.points.shape[0], 1), "u": torch.randn(base.points.shape[0], 3)})
+    centred = CenterMesh()(mesh.clone())
+    assert centred.points.mean(0).abs().max() < 1e-2
+    rot = RotateMesh(math.pi / 2, axis="z", transform_point_data=True)(centred.clone())
+    assert torch.allclose(rot.points[:, 0], -centred.points[:, 1], atol=1e-6) and torch.allclose(rot.point_data["u"][:, 1], centred.point_data["u"][:, 0], atol=1e-6)
+    assert torch.allclose(rot.point_data["p"], centred.point_data["p"])                  # scalars do not rotate
+    moved = TranslateMesh([1.0, 0, 0])(ScaleMesh(2.0)(centred.clone()))
+    assert torch.allclose(moved.points, centred.points * 2 + torch.tensor([1.0, 0, 0]), atol=1e-6)
+    sub = SubsampleMesh(n_cells=40)(centred.clone())
+    assert sub.n_cells == 40 and int(sub.cells.max()) == sub.n_points - 1 and sub.point_data["p"].shape[0] == sub.n_points
+    out = ComputeCellCentroids()(ComputeSurfaceNormals()(centred.clone()))
+    assert (out.cell_data["normals"] * out.cell_data["centroids"]).sum(-1).min() > 0      # outward on a sphere
+    norm = NormalizeMeshFields("point_data", {"p": {"mean": [0.5], "std": [2.0]}})
+    scaled = norm(centred.clone())
+    assert torch.allclose(norm.inverse(scaled).point_data["p"], centred.point_data["p"], atol=1e-5)
+    tidy = SetGlobalField({"mach": [0.3]})(RenameMeshFields(point_data={"u": "velocity"})(DropMeshFields(point_data=["p"])(centred.clone())))
+    assert set(tidy.point_data) == {"velocity"} and float(tidy.global_data["mach"]) == pytest.approx(0.3)
+    td = RestructureTensorDict({"inputs": {"pos": "points"}, "targets": {"vel": "point_data.velocity"}})(MeshToTensorDict()(tidy))
+    assert td["inputs"]["pos"].shape == (tidy.n_points, 3) and td["targets"]["vel"].shape == (tidy.n_points, 3)
+    r = RandomRotateMesh(seed=3)
+    a, b = r(centred.clone()), r(centred.clone())
+    assert not torch.allclose(a.points, b.points) and torch.allclose(a.points.norm(dim=-1), centred.points.norm(dim=-1), atol=1e-5)
+    for i in range(3):
+        save_mesh_npz(mesh, tmp_path / f"m{i}.npz")
+    ds = MeshDataset(MeshReader(tmp_path, subsample_n_cells=100), transforms=[CenterMesh(), RandomScaleMesh(seed=1)])
+    assert len(ds) == 3 and ds[0].n_cells == 100 and "p" in ds[0].point_data
+    ds.set_epoch(0)
+    first = ds[1].points.clone()
+    ds.set_epoch(0)
+    assert torch.equal(ds[1].points, first)                                               # same epoch, same augmentation
+    ds.set_epoch(1)
+    assert not torch.equal(ds[1].points, first)
