@@ -109,7 +109,7 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
 // dx = rstd * (g*dy - mean_c(g*dy) - xhat * mean_c(g*dy*xhat)) (+ dres) ; partial dgamma/dbeta
 // rows go to scratch[blockIdx.x][2][C].
 template <int VEC>
-__global__ void __launch_bounds__(kLnWarps * 32)
+__global__ void __launch_bounds__(kLnWarps * 32, VEC == 1 ? 3 : 1)
 layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                      const float* __restrict__ gamma, const float* __restrict__ mean_in,
                      const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
@@ -131,7 +131,13 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   for (long long row = warp_global; row < M; row += nwarps) {
     const float mean = mean_in[row], rstd = rstd_in[row];
     float xh[VEC][8], gy[VEC][8];
+    uint4 ur[VEC];   // residual gradient, requested together with x and dy so that three loads per lane are in flight
     float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const int c = (v * 32 + lane) * 8;
+      ur[v] = (dres && c < C) ? *reinterpret_cast<const uint4*>(dres + row * C + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
       const int c = (v * 32 + lane) * 8;
@@ -169,8 +175,7 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = rstd * (gy[v][j] - m1 - xh[v][j] * m2);
         if (dres) {
-          uint4 ur = *reinterpret_cast<const uint4*>(dres + row * C + c);
-          const uint32_t wr[4] = {ur.x, ur.y, ur.z, ur.w};
+          const uint32_t wr[4] = {ur[v].x, ur[v].y, ur[v].z, ur[v].w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) { float2 f = unpack_bf16x2(wr[j]); o[2 * j] += f.x; o[2 * j + 1] += f.y; }
         }
@@ -233,7 +238,8 @@ inline int launch_layernorm_fwd(const void* x, const void* r, const float* gamma
 // Number of CTAs the backward uses (= rows of scratch needed: grid * 2 * C floats).
 inline int layernorm_bwd_grid(long long M, int num_sms) {
   long long want = (M + kLnWarps - 1) / kLnWarps;
-  int grid = (int)(want < (long long)num_sms * 2 ? want : (long long)num_sms * 2);
+  // three resident CTAs per SM (C <= 256): one row per warp is in flight at a time, so the bytes in flight come from the warp count
+  int grid = (int)(want < (long long)num_sms * 3 ? want : (long long)num_sms * 3);
   return grid < 1 ? 1 : grid;
 }
 

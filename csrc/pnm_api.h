@@ -165,9 +165,10 @@ int pnm_conv2d_nhwc_halo(const void* x, const void* weight, void* y, int n, int 
 
 // out[BH,Sq,D] = softmax(scale * q k^T (+ causal mask, top-left aligned)) v for contiguous bf16 q [BH,Sq,D], k [BH,Skv,D] and
 // v [BH,Skv,D] (v_transposed = 0) or v^T [BH,D,ldv] with ldv >= Skv, ldv % 8 == 0 (v_transposed = 1); D in {64, 128};
-// lse [BH,Sq] (fp32, optional) receives the natural-log sum of exponentials of every row.  See flash_attn.cuh.
+// lse [BH,Sq] (fp32, optional) receives the natural-log sum of exponentials of every row; p_in_tmem = 1 keeps the probability
+// tile in tensor memory as the A operand of the second MMA instead of staging it in shared memory.  See flash_attn.cuh.
 int pnm_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int BH, int Sq, int Skv, int D,
-                       int ldv, float scale, int causal, int v_transposed, void* stream);
+                       int ldv, float scale, int causal, int v_transposed, int p_in_tmem, void* stream);
 
 // EDM noise conditioning: out[B,E] (fp32) = silu(W1 silu(W0 (emb + extra) + b0) + b1) with emb[b] = [sin(noise[b] f), cos(noise[b] f)],
 // f = freqs[C/2]; extra [B,C] fp32 optional; weights row-major [E,C] and [E,E], biases optional; weight_dtype 0 = bf16, 1 = fp32.

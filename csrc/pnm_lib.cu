@@ -230,15 +230,24 @@ int pnm_peer_wait_probe(const void* flag, unsigned int expect, double budget_s, 
 }
 
 int pnm_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int BH, int Sq, int Skv, int D,
-                       int ldv, float scale, int causal, int v_transposed, void* stream) {
+                       int ldv, float scale, int causal, int v_transposed, int p_in_tmem, void* stream) {
   if (ensure_init()) return -1;
   if (!q || !k || !v || !out || BH <= 0 || Sq <= 0 || Skv <= 0 || !(scale > 0.f)) return -1;
   if (v_transposed && (ldv < Skv || (ldv & 7))) return -1;
   pnm::FlashCall c{q, k, v, out, lse, BH, Sq, Skv, ldv, scale, causal};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (D == 64) return v_transposed ? pnm::launch_flash_fwd<64, true>(c, g_err_ptr, st) : pnm::launch_flash_fwd<64, false>(c, g_err_ptr, st);
-  if (D == 128) return v_transposed ? pnm::launch_flash_fwd<128, true>(c, g_err_ptr, st) : pnm::launch_flash_fwd<128, false>(c, g_err_ptr, st);
-  return -1;
+  const int variant = (D == 128 ? 4 : 0) | (v_transposed ? 2 : 0) | (p_in_tmem ? 1 : 0);
+  if (D != 64 && D != 128) return -1;
+  switch (variant) {
+    case 0: return pnm::launch_flash_fwd<64, false, false>(c, g_err_ptr, st);
+    case 1: return pnm::launch_flash_fwd<64, false, true>(c, g_err_ptr, st);
+    case 2: return pnm::launch_flash_fwd<64, true, false>(c, g_err_ptr, st);
+    case 3: return pnm::launch_flash_fwd<64, true, true>(c, g_err_ptr, st);
+    case 4: return pnm::launch_flash_fwd<128, false, false>(c, g_err_ptr, st);
+    case 5: return pnm::launch_flash_fwd<128, false, true>(c, g_err_ptr, st);
+    case 6: return pnm::launch_flash_fwd<128, true, false>(c, g_err_ptr, st);
+    default: return pnm::launch_flash_fwd<128, true, true>(c, g_err_ptr, st);
+  }
 }
 
 }  // extern "C"

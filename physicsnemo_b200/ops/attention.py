@@ -21,6 +21,7 @@ from . import _lib
 from . import gemm as _g
 
 V_LAYOUT = "natural"
+P_IN_TMEM = False
 
 
 def _lib_fa():
@@ -28,7 +29,7 @@ def _lib_fa():
     if not getattr(lib, "_fa_declared", False):
         c = ctypes
         vp, i, f = c.c_void_p, c.c_int, c.c_float
-        lib.pnm_flash_attn_fwd.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, f, i, i, vp]
+        lib.pnm_flash_attn_fwd.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, f, i, i, i, vp]
         lib.pnm_flash_attn_fwd.restype = i
         lib._fa_declared = True
     return lib
@@ -44,7 +45,7 @@ def supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
     return math.prod(q.shape[:-2]) * ((q.shape[-2] + 127) // 128) < 2 ** 31
 
 
-def flash_forward(q, k, v, is_causal: bool = False, scale: float | None = None, v_layout: str | None = None):
+def flash_forward(q, k, v, is_causal: bool = False, scale: float | None = None, v_layout: str | None = None, p_in_tmem: bool | None = None):
     if not supported(q, k, v):
         raise ValueError("flash_forward needs CUDA bf16 tensors [..., S, D] with D in (64, 128) and matching batch dimensions")
     lead, Sq, D = q.shape[:-2], q.shape[-2], q.shape[-1]
@@ -67,7 +68,8 @@ def flash_forward(q, k, v, is_causal: bool = False, scale: float | None = None, 
     out = torch.empty(BH, Sq, D, dtype=q.dtype, device=q.device)
     lse = torch.empty(BH, Sq, dtype=torch.float32, device=q.device)
     err = _lib_fa().pnm_flash_attn_fwd(q3.data_ptr(), k3.data_ptr(), v3.data_ptr(), out.data_ptr(), lse.data_ptr(), BH, Sq, Skv, D,
-                                       ldv, scale, int(bool(is_causal)), vt, torch.cuda.current_stream().cuda_stream)
+                                       ldv, scale, int(bool(is_causal)), vt, int(P_IN_TMEM if p_in_tmem is None else p_in_tmem),
+                                       torch.cuda.current_stream().cuda_stream)
     if err:
         raise RuntimeError(f"pnm_flash_attn_fwd failed ({err})")
     _g.launch_count += 1

@@ -129,7 +129,8 @@ def attention_cases(small: bool = False):
         q, k, v = (_r(b, h, s, d) for _ in range(3))
         flops = 4.0 * b * h * s * s * d * (0.5 if causal else 1.0)
         nbytes = 4 * b * h * s * d * 2
-        out[f"flash_{name}"] = (lambda q=q, k=k, v=v, c=causal: A.flash_forward(q, k, v, c), flops, nbytes)
+        out[f"flash_{name}"] = (lambda q=q, k=k, v=v, c=causal: A.flash_forward(q, k, v, c, p_in_tmem=False), flops, nbytes)
+        out[f"flash_ptmem_{name}"] = (lambda q=q, k=k, v=v, c=causal: A.flash_forward(q, k, v, c, p_in_tmem=True), flops, nbytes)
         out[f"torch_sdpa_{name}"] = (lambda q=q, k=k, v=v, c=causal: F.scaled_dot_product_attention(q, k, v, is_causal=c), flops, nbytes)
     return out
 

@@ -88,11 +88,12 @@ def _sdpa_fp32(q, k, v, causal, scale):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("p_tmem", [False, True])
 @pytest.mark.parametrize("layout", ["natural", "transposed"])
 @pytest.mark.parametrize("shape", [(2, 3, 256, 256, 64, False), (1, 2, 384, 384, 128, False), (2, 2, 200, 333, 64, False),
                                    (1, 2, 130, 77, 128, False), (1, 3, 512, 512, 128, True), (2, 1, 300, 300, 64, True),
                                    (1, 1, 1024, 2048, 128, False)])
-def test_flash_attention_forward(shape, layout):
+def test_flash_attention_forward(shape, layout, p_tmem):
     from physicsnemo_b200.ops import attention as A
     from physicsnemo_b200.ops import device_error
 
@@ -102,7 +103,7 @@ def test_flash_attention_forward(shape, layout):
     k = torch.randn(b, h, skv, d, device="cuda", dtype=torch.bfloat16)
     v = torch.randn(b, h, skv, d, device="cuda", dtype=torch.bfloat16)
     scale = 0.7 / d ** 0.5
-    out, lse = A.flash_forward(q, k, v, causal, scale, v_layout=layout)
+    out, lse = A.flash_forward(q, k, v, causal, scale, v_layout=layout, p_in_tmem=p_tmem)
     torch.cuda.synchronize()
     assert device_error() == 0
     ref, ref_lse = _sdpa_fp32(q, k, v, causal, scale)
@@ -131,8 +132,9 @@ def test_flash_attention_autograd_and_fallback():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("p_tmem", [False, True])
 @pytest.mark.parametrize("d", [64, 128])
-def test_flash_attention_growing_scores_rescale_the_accumulator(d):
+def test_flash_attention_growing_scores_rescale_the_accumulator(d, p_tmem):
     """Later key tiles carry much larger scores, so the running reference must move (by more than 2^8 and, for the last
     tile, by more than 2^64) and the TMEM accumulator is corrected in place."""
     from physicsnemo_b200.ops import attention as A
@@ -145,7 +147,7 @@ def test_flash_attention_growing_scores_rescale_the_accumulator(d):
     ramp = torch.tensor([0.2, 1.0, 3.0, 3.0, 30.0], device="cuda").repeat_interleave(128)     # per key tile
     k = (k.float() * ramp[None, None, :, None]).to(torch.bfloat16)
     scale = 1.0 / d ** 0.5
-    out, lse = A.flash_forward(q, k, v, False, scale)
+    out, lse = A.flash_forward(q, k, v, False, scale, p_in_tmem=p_tmem)
     torch.cuda.synchronize()
     assert device_error() == 0
     ref, ref_lse = _sdpa_fp32(q, k, v, False, scale)
