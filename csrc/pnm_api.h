@@ -175,6 +175,12 @@ int pnm_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, f
 int pnm_edm_conditioning(const float* noise, const float* freqs, const float* extra, const void* w0, const void* b0, const void* w1,
                          const void* b1, float* out, int B, int C, int E, int weight_dtype, void* stream);
 
+// out[p,q,m] (+)= sum_r A[p,r,m] * B[r,q,m] over complex64 tensors; m = block of nd <= 4 mode dimensions (extents `shape`, complex-element
+// strides sa / sb / so per tensor); chan_strides = {A_p, A_r, B_r, B_q, out_p, out_q}.  See spectral.cu.
+int pnm_spectral_contract(const void* A, const void* B, void* out, int nd, const int* shape, const long long* sa, const long long* sb,
+                          const long long* so, const long long* chan_strides, int P, int Q, int R, int conj_a, int conj_b,
+                          int accumulate, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

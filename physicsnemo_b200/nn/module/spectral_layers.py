@@ -61,6 +61,17 @@ class _SpectralConvNd(nn.Module):
         x_ft = torch.fft.rfftn(x.float() if x.dtype in (torch.bfloat16, torch.float16) else x, dim=dims)
         out_ft = torch.zeros(x.shape[0], self.out_channels, *x_ft.shape[2:], dtype=x_ft.dtype, device=x.device)
         last = slice(0, self.modes[-1])
+        if x_ft.is_cuda:
+            from ...ops import spectral as _sp
+
+            w1 = self.weights1
+            if _sp.supported(x_ft, w1) and all(m <= n for m, n in zip(self.modes, x_ft.shape[2:])):
+                # one kernel per corner: reads the corner of x_ft in place, contracts, accumulates into the corner of out_ft
+                for k, signs in enumerate(_CORNERS[nd]):
+                    starts = [x_ft.shape[2 + d] - self.modes[d] if hi else 0 for d, hi in enumerate(signs)] + [0]
+                    out_ft = _sp.corner_contract(x_ft, getattr(self, f"weights{k + 1}"), starts, out_ft)
+                y = torch.fft.irfftn(out_ft, s=spatial, dim=dims)
+                return y.to(x.dtype) if y.dtype != x.dtype and x.dtype in (torch.bfloat16, torch.float16) else y
         parts = []
         for k, signs in enumerate(_CORNERS[nd]):
             idx = [slice(None), slice(None)]

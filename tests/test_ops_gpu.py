@@ -220,3 +220,32 @@ def test_song_unet_uses_fused_conditioning():
         emb = emb + net.map_label(labels * 3 ** 0.5) + net.map_augment(aug)
         plain = torch.nn.functional.silu(net.map_layer1(torch.nn.functional.silu(net.map_layer0(emb))))
     assert torch.allclose(fused, plain, atol=1e-4)
+
+
+# ---- spectral mode contraction -------------------------------------------------------------------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("nd", [1, 2, 3])
+def test_spectral_conv_fused_corner_contraction(nd):
+    from physicsnemo_b200.nn.module import spectral_layers as SL
+
+    torch.manual_seed(0)
+    cls = {1: SL.SpectralConv1d, 2: SL.SpectralConv2d, 3: SL.SpectralConv3d}[nd]
+    modes = {1: (5,), 2: (4, 3), 3: (3, 2, 3)}[nd]
+    shape = {1: (24,), 2: (16, 12), 3: (8, 6, 10)}[nd]
+    layer = cls(6, 5, *modes)
+    x = torch.randn(3, 6, *shape)
+    ref_layer, xr = layer, x.clone().requires_grad_(True)                    # CPU: einsum path
+    y_ref = ref_layer(xr)
+    g = torch.randn_like(y_ref)
+    y_ref.backward(g)
+    ref_grads = [p.grad.clone() for p in ref_layer.parameters()]
+    for p in ref_layer.parameters():
+        p.grad = None
+    gpu = layer.cuda()
+    xg = x.cuda().requires_grad_(True)
+    y = gpu(xg)                                                              # CUDA: fused corner kernel
+    y.backward(g.cuda())
+    assert torch.allclose(y.cpu(), y_ref, atol=2e-5, rtol=1e-4)
+    assert torch.allclose(xg.grad.cpu(), xr.grad, atol=2e-5, rtol=1e-4)
+    for p, r in zip(gpu.parameters(), ref_grads):
+        assert torch.allclose(p.grad.cpu(), r, atol=2e-4, rtol=1e-3)
