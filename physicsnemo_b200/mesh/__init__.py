@@ -7,3 +7,5 @@ from .mesh import MESH_FIELD_ASSOCIATIONS, Adjacency, Mesh, MeshFieldAssociation
 __all__ = ["Mesh", "DomainMesh", "Adjacency", "MeshFieldAssociation", "MESH_FIELD_ASSOCIATIONS", "RankSpecDict",
            "flatten_rank_spec", "rank_counts", "ranks_from_tensordict", "validate_data_contains_ranks", "primitives",
            "operations", "spatial", "io"]
+from . import generate, repair, tessellation  # noqa: E402,F401
+from .generate import marching_cubes  # noqa: E402,F401

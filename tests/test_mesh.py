@@ -137,3 +137,66 @@ def test_bvh_kernels_match_all_pairs():
     out = ray_mesh_intersect(m.points, m.cells, o, d, return_bvh=True)
     again = ray_mesh_intersect(m.points, m.cells, o, d, bvh=out[-1])
     assert torch.equal(out[3], again[3])
+
+
+# ---- generation, repair, tessellation ------------------------------------------------------------------------------------
+def test_marching_cubes_sphere_is_watertight_and_outward():
+    import math
+
+    from physicsnemo_b200.mesh.generate import marching_cubes, project_to_zero_set, sdf_box, sdf_difference, sdf_sphere
+
+    ax = torch.linspace(-1, 1, 33)
+    grid = torch.stack(torch.meshgrid(ax, ax, ax, indexing="ij"), -1)
+    phi = sdf_sphere([0.1, 0.0, -0.1], 0.6)
+    m = marching_cubes(phi(grid), 0.0, (ax, ax, ax))
+    e = torch.cat([m.cells[:, [0, 1]], m.cells[:, [1, 2]], m.cells[:, [2, 0]]])
+    _, cnt = torch.unique(e.sort(1).values, dim=0, return_counts=True)
+    assert cnt.unique().tolist() == [2] and torch.unique(e, dim=0).shape[0] == e.shape[0]      # closed, consistently oriented
+    assert m.n_points - cnt.shape[0] + m.n_cells == 2                                             # sphere topology
+    assert (phi(m.points).abs().max()) < 5e-3
+    p = m.points - torch.tensor([0.1, 0.0, -0.1])
+    vol = float((p[m.cells[:, 0]] * torch.linalg.cross(p[m.cells[:, 1]], p[m.cells[:, 2]])).sum() / 6)
+    assert vol == pytest.approx(4 / 3 * math.pi * 0.6 ** 3, rel=0.02)                             # positive: normals point outward
+    on = project_to_zero_set(phi, m.points + 0.05 * torch.randn_like(m.points))
+    assert phi(on).abs().max() < 1e-5
+    shell = sdf_difference(sdf_box([-0.5] * 3, [0.5] * 3), sdf_sphere([0, 0, 0], 0.3))
+    assert float(shell(torch.zeros(1, 3))) > 0 and float(shell(torch.tensor([[0.4, 0.4, 0.4]]))) < 0
+    idx = marching_cubes(phi(grid))                                                               # index space without coords
+    assert float(idx.points.max()) <= 32
+    assert marching_cubes(torch.ones(4, 4, 4)).n_cells == 0
+
+
+def test_fill_holes_and_degenerate_removal():
+    from physicsnemo_b200.mesh import primitives
+    from physicsnemo_b200.mesh.repair import fill_holes, remove_degenerate_cells
+
+    s = primitives.icosphere(2)
+    keep = torch.ones(s.n_cells, dtype=torch.bool)
+    keep[[3, 100]] = False                                        # two separate triangular holes
+    holed = s.slice_cells(keep.nonzero().squeeze(1))
+    filled, stats = fill_holes(holed)
+    assert stats["n_holes_detected"] == 2 and stats["n_holes_filled"] == 2 and stats["n_faces_added"] == 6
+    e = torch.cat([filled.cells[:, [0, 1]], filled.cells[:, [1, 2]], filled.cells[:, [2, 0]]])
+    assert torch.unique(e.sort(1).values, dim=0, return_counts=True)[1].unique().tolist() == [2]
+    assert torch.unique(e, dim=0).shape[0] == e.shape[0]          # orientation of the patches matches the surface
+    _, skipped = fill_holes(holed, max_hole_edges=2)
+    assert skipped["n_holes_skipped"] == 2
+    bad = torch.cat([s.cells, torch.tensor([[0, 0, 1]])])
+    cleaned, info = remove_degenerate_cells(type(s)(s.points, bad))
+    assert info["n_cells_removed"] == 1 and cleaned.n_cells == s.n_cells
+
+
+def test_tessellation_polygons_and_delaunay():
+    from physicsnemo_b200.mesh.tessellation import delaunay_mesh_2d, ear_clip, fill_interior, triangulate
+
+    L = torch.tensor([[0.0, 0], [2, 0], [2, 1], [1, 1], [1, 2], [0, 2]])          # non-convex L shape, area 3
+    tris = ear_clip(L.numpy())
+    area = sum(0.5 * abs(float((L[b] - L[a])[0] * (L[c] - L[a])[1] - (L[b] - L[a])[1] * (L[c] - L[a])[0])) for a, b, c in tris)
+    assert len(tris) == 4 and area == pytest.approx(3.0)
+    m = triangulate(torch.cat([L, torch.zeros(6, 1)], 1), [[0, 1, 2, 3, 4, 5]])
+    assert m.n_cells == 4 and float(m.cell_areas.sum()) == pytest.approx(3.0)
+    torch.manual_seed(0)
+    d = delaunay_mesh_2d(torch.rand(40, 2))
+    assert d.n_cells > 40 and float(d.cell_areas.min()) > 0
+    filled = fill_interior(L, [[0, 1, 2, 3, 4, 5]], spacing=0.25)
+    assert float(filled.cell_areas.sum()) == pytest.approx(3.0, rel=1e-6) and filled.n_points > 20
