@@ -183,3 +183,21 @@ def test_cached_dataset_and_prefetch(tmp_path):
     assert list(prefetch_map(range(5), lambda v: v * v)) == [0, 1, 4, 9, 16] and len(prefetch_map(range(5), abs)) == 5
     with pytest.raises(FileNotFoundError):
         DS([tmp_path / "missing.txt"])
+
+
+def test_tedm_preconditioner_and_loss():
+    from physicsnemo_b200.experimental.models import tEDMPrecondSuperRes, tEDMResidualLoss
+
+    torch.manual_seed(0)
+    net = tEDMPrecondSuperRes(img_resolution=16, img_in_channels=2, img_out_channels=3, model_type="SongUNet", nu=5, model_channels=32,
+                              channel_mult=[1, 2], num_blocks=1, attn_resolutions=[8])
+    x, lr, sigma = torch.randn(2, 3, 16, 16), torch.randn(2, 2, 16, 16), torch.tensor([0.5, 2.0])
+    out = net(x, lr, sigma.clone())
+    assert out.shape == x.shape and torch.allclose(sigma, torch.tensor([0.5, 2.0]))          # the caller's sigma is not modified
+    loss = tEDMResidualLoss(regression_net=lambda *a, **k: torch.zeros(2, 3, 16, 16), nu=5)
+    n, s, w = loss.get_noise_params(torch.zeros(4000, 1, 1, 1))
+    assert n.shape == (4000, 1, 1, 1) and float(w.min()) > 0
+    ratio = (n / s).flatten()
+    assert float(ratio.abs().max()) > 4.5                                                      # heavy tails: beyond what 4000 Gaussians reach
+    with pytest.raises(ValueError):
+        tEDMResidualLoss(regression_net=None, nu=2)
