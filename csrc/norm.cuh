@@ -13,7 +13,7 @@ constexpr int kLnMaxVec = 4;  // supports C up to 32 lanes * 8 elems * 4 = 1024
 // y = (x - mean) * rstd * gamma + beta (+ post); optional second input r: normalises (x + r)
 // and writes the sum to `sum_out` (fused residual add before the normalisation).
 template <int VEC>
-__global__ void __launch_bounds__(kLnWarps * 32)
+__global__ void __launch_bounds__(kLnWarps * 32, VEC == 1 ? 4 : 2)
 layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ r,
                      const float* __restrict__ gamma, const float* __restrict__ beta, __nv_bfloat16* __restrict__ y,
                      __nv_bfloat16* __restrict__ sum_out, float* __restrict__ mean_out, float* __restrict__ rstd_out,
@@ -31,18 +31,34 @@ layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
       bet[v][j] = (c + j < C && beta) ? beta[c + j] : 0.f;
     }
   }
+  // the loads of the next row are issued before this row is processed: two rows per warp are in flight
+  uint4 nx[VEC], nr[VEC];
+  auto fetch = [&](long long row) {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const int c = (v * 32 + lane) * 8;
+      const bool live = row < M && c < C;
+      nx[v] = live ? *reinterpret_cast<const uint4*>(x + row * C + c) : make_uint4(0u, 0u, 0u, 0u);
+      nr[v] = (live && r) ? *reinterpret_cast<const uint4*>(r + row * C + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  fetch(warp_global);
   for (long long row = warp_global; row < M; row += nwarps) {
     float val[VEC][8];
     float s = 0.f;
+    uint4 cx[VEC], cr[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) { cx[v] = nx[v]; cr[v] = nr[v]; }
+    fetch(row + nwarps);
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
       const int c = (v * 32 + lane) * 8;
       if (c < C) {
-        uint4 u = *reinterpret_cast<const uint4*>(x + row * C + c);
+        const uint4 u = cx[v];
         const uint32_t w[4] = {u.x, u.y, u.z, u.w};
         uint32_t rw[4] = {0, 0, 0, 0};
         if (r) {
-          uint4 ur = *reinterpret_cast<const uint4*>(r + row * C + c);
+          const uint4 ur = cr[v];
           rw[0] = ur.x; rw[1] = ur.y; rw[2] = ur.z; rw[3] = ur.w;
         }
 #pragma unroll
@@ -128,22 +144,37 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
       dg[v][j] = 0.f; db[v][j] = 0.f;
     }
   }
-  for (long long row = warp_global; row < M; row += nwarps) {
-    const float mean = mean_in[row], rstd = rstd_in[row];
-    float xh[VEC][8], gy[VEC][8];
-    uint4 ur[VEC];   // residual gradient, requested together with x and dy so that three loads per lane are in flight
-    float s1 = 0.f, s2 = 0.f;
+  // x, dy and the residual gradient of the next row are requested before this row is processed
+  uint4 nx[VEC], nd[VEC], nr[VEC];
+  float nmean = 0.f, nrstd = 0.f;
+  auto fetch = [&](long long row) {
+    const bool in = row < M;
+    nmean = in ? mean_in[row] : 0.f;
+    nrstd = in ? rstd_in[row] : 0.f;
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
       const int c = (v * 32 + lane) * 8;
-      ur[v] = (dres && c < C) ? *reinterpret_cast<const uint4*>(dres + row * C + c) : make_uint4(0u, 0u, 0u, 0u);
+      const bool live = in && c < C;
+      nx[v] = live ? *reinterpret_cast<const uint4*>(x + row * C + c) : make_uint4(0u, 0u, 0u, 0u);
+      nd[v] = live ? *reinterpret_cast<const uint4*>(dy + row * C + c) : make_uint4(0u, 0u, 0u, 0u);
+      nr[v] = (live && dres) ? *reinterpret_cast<const uint4*>(dres + row * C + c) : make_uint4(0u, 0u, 0u, 0u);
     }
+  };
+  fetch(warp_global);
+  for (long long row = warp_global; row < M; row += nwarps) {
+    const float mean = nmean, rstd = nrstd;
+    float xh[VEC][8], gy[VEC][8];
+    uint4 ur[VEC], cx[VEC], cd[VEC];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) { ur[v] = nr[v]; cx[v] = nx[v]; cd[v] = nd[v]; }
+    fetch(row + nwarps);
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
       const int c = (v * 32 + lane) * 8;
       if (c < C) {
-        uint4 ux = *reinterpret_cast<const uint4*>(x + row * C + c);
-        uint4 ud = *reinterpret_cast<const uint4*>(dy + row * C + c);
+        const uint4 ux = cx[v];
+        const uint4 ud = cd[v];
         const uint32_t wx[4] = {ux.x, ux.y, ux.z, ux.w}, wd[4] = {ud.x, ud.y, ud.z, ud.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {

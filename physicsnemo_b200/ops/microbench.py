@@ -69,6 +69,15 @@ def cases(M):
     out["gemm_nt"] = (lambda: G.gemm_nt(p512, a256, colsum=True), 2.0 * M * 512 * 256, M * (512 + 256) * 2)
     g, b = torch.ones(256, device="cuda"), torch.zeros(256, device="cuda")
     out["layernorm"] = (lambda: layer_norm(a256, g, b), 0.0, M * 256 * 2 * 2)
+    gp, bp = g.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    xr = a256.detach().requires_grad_(True)
+    y_keep = layer_norm(xr, gp, bp)
+    dy = _r(M, 256)
+
+    def ln_bwd():                                   # backward only: dy, x read, dx written (+ small dgamma / dbeta)
+        torch.autograd.grad(y_keep, (xr, gp, bp), dy, retain_graph=True)
+
+    out["layernorm_bwd"] = (ln_bwd, 0.0, M * 256 * 2 * 3)
     return out
 
 

@@ -275,3 +275,40 @@ def test_mesh_transforms_and_dataset(tmp_path):
     assert torch.equal(ds[1].points, first)                                               # same epoch, same augmentation
     ds.set_epoch(1)
     assert not torch.equal(ds[1].points, first)
+
+
+def test_transolver_datapipe_feeds_the_model():
+    from physicsnemo_b200.datapipes.cae import TransolverDataPipe
+    from physicsnemo_b200.mesh import primitives
+    from physicsnemo_b200.models.transolver import Transolver
+
+    torch.manual_seed(0)
+    s = primitives.icosphere(3)
+    V, F = s.points.float() * 0.5 + torch.tensor([2.0, 0, 0]), s.cells
+    tri = V[F]
+    n = torch.linalg.cross(tri[:, 1] - tri[:, 0], tri[:, 2] - tri[:, 0])
+    centers, areas = tri.mean(1), 0.5 * n.norm(dim=-1)
+    sample = dict(stl_coordinates=V, stl_faces=F.reshape(-1), stl_centers=centers, surface_mesh_centers=centers, surface_normals=n,
+                  surface_areas=areas, surface_fields=torch.randn(centers.shape[0], 4) * 2 + 5, air_density=torch.tensor(1.2),
+                  stream_velocity=torch.tensor(30.0), volume_mesh_centers=torch.rand(5000, 3) * 4, volume_fields=torch.randn(5000, 5))
+    factors = {"mean": sample["surface_fields"].mean(0), "std": sample["surface_fields"].std(0)}
+    pipe = TransolverDataPipe(model_type="surface", dataset=[sample], resolution=400, scaling_type="mean_std_scaling", surface_factors=factors,
+                              translational_invariance=True, include_geometry=True, geometry_sampling=100)
+    out = pipe[0]
+    assert out["embeddings"].shape == (1, 400, 6) and out["fx"].shape == (1, 400, 2) and out["fields"].shape == (1, 400, 4)
+    assert out["geometry"].shape == (1, 100, 3) and out["surface_areas_sub"].shape == (1, 400)
+    assert torch.allclose(out["embeddings"][0, :, 3:].norm(dim=-1), torch.ones(400), atol=1e-5)          # unit normals
+    assert out["embeddings"][0, :, :3].norm(dim=-1).max() < 0.51                                         # centred on the body
+    back = pipe.unscale_model_targets(out["fields"][0])
+    assert float(back.mean()) == pytest.approx(5.0, abs=0.5)
+    model = Transolver(functional_dim=2, out_dim=4, embedding_dim=6, n_layers=2, n_hidden=32, n_head=4, slice_num=8, use_te=False)
+    pred = model(out["fx"], out["embeddings"])
+    assert pred.shape == out["fields"].shape
+    vol = TransolverDataPipe(model_type="volume", dataset=[sample], resolution=300, include_sdf=True)[0]
+    assert vol["embeddings"].shape == (1, 300, 7)                                                        # xyz, sdf, direction to the surface
+    r = (vol["embeddings"][0, :, :3] - torch.tensor([2.0, 0, 0])).norm(dim=-1)
+    assert (vol["embeddings"][0, :, 3] - (r - 0.5)).abs().max() < 5e-3
+    both = TransolverDataPipe(model_type="combined", dataset=[sample], resolution=200)[0]
+    assert [e.shape[1] for e in both["embeddings"]] == [200, 200]
+    with pytest.raises(ValueError):
+        TransolverDataPipe(model_type="surface").process_data({"stl_centers": centers})
