@@ -130,3 +130,19 @@ def test_zenith_angle_and_insolation():
     assert sol[1, -1].mean() > sol[0, -1].mean()                       # the Arctic is lit in July, dark in January
     with pytest.raises(ValueError):
         insolation(dates, lat, lon[0])
+
+
+def test_sdf_to_stl_and_memory_module(tmp_path):
+    from physicsnemo_b200.mesh.io import read_stl
+    from physicsnemo_b200.utils import memory
+    from physicsnemo_b200.utils.mesh import sdf_to_stl
+
+    ax = torch.linspace(-1, 1, 17)
+    g = torch.stack(torch.meshgrid(ax, ax, ax, indexing="ij"), -1)
+    sdf_to_stl((g.norm(dim=-1) - 0.5).numpy(), filename=str(tmp_path / "s.stl"))
+    m = read_stl(tmp_path / "s.stl")
+    assert m.n_cells > 100
+    assert memory.unified_gpu_memory is None or memory.unified_gpu_memory is True      # no rmm here: a no-op
+    assert memory.srt2bool("Yes") and not memory.srt2bool("0")
+    with pytest.raises(AttributeError):
+        memory.nothing_here
