@@ -235,6 +235,18 @@ __device__ __forceinline__ float ex2_fast(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x on the FMA / ALU pipes (no special-function unit): round-to-nearest split x = n + f, f in [-0.5, 0.5], cubic for 2^f
+// (relative error 1e-4, below bf16 resolution), then n is added to the exponent field.  Inputs below -126 give 0.
+__device__ __forceinline__ float ex2_poly(float x) {
+  const float xc = fmaxf(x, -126.f);
+  const float t = xc + 12582912.f;   // 1.5 * 2^23: the integer part lands in the low mantissa bits
+  const float f = xc - (t - 12582912.f);
+  float p = fmaf(f, 0.05592204f, 0.24264008f);
+  p = fmaf(p, f, 0.69312103f);
+  p = fmaf(p, f, 0.99992448f);
+  const float r = __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+  return x < -126.f ? 0.f : r;
+}
 // GELU in its tanh form (|gelu_tanh - gelu_erf| < 1e-3, below bf16 resolution for O(1) values).
 __device__ __forceinline__ float gelu_f(float x) {
   float u = x * (0.7978845608f + 0.0356774081f * x * x);

@@ -48,6 +48,7 @@ struct FlashArgs {
 };
 
 constexpr int kFaThreads = 320;
+constexpr int kFaPolyMask = 0xAA;   // which of every eight exponentials go to the FMA-pipe polynomial
 constexpr int kFaBarBytes = 256 + 1024;   // barriers, then the 1 KB exchange area of the row halves
 
 template <int D>
@@ -275,7 +276,12 @@ __global__ void __launch_bounds__(kFaThreads, 1) flash_fwd_kernel(const __grid_c
       for (int q = 0; q < 8; ++q) {
         float e[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) e[i] = ex2_fast(fmaf(v[q * 8 + i], c, -use));
+        for (int i = 0; i < 8; ++i) {
+          // the special-function unit (16 results per clock and SM) is the busiest pipe of the softmax: every other
+          // exponential is evaluated by a cubic on the FMA pipe instead
+          const float a = fmaf(v[q * 8 + i], c, -use);
+          e[i] = ((kFaPolyMask >> i) & 1) ? ex2_poly(a) : ex2_fast(a);
+        }
         rs0 += e[0] + e[4];
         rs1 += e[1] + e[5];
         rs2 += e[2] + e[6];

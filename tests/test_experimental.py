@@ -201,3 +201,59 @@ def test_tedm_preconditioner_and_loss():
     assert float(ratio.abs().max()) > 4.5                                                      # heavy tails: beyond what 4000 Gaussians reach
     with pytest.raises(ValueError):
         tEDMResidualLoss(regression_net=None, nu=2)
+
+
+# ------------------------------------------------------------------------------------------------ 3-D diffusion U-Net
+def test_conv3d_box_resampling_matches_filtered_convolution():
+    """The pooled / replicated fast path of the default box filter equals the depthwise (transposed) convolution."""
+    from physicsnemo_b200.experimental.nn import Conv3D
+    import torch.nn.functional as F
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 4, 6, 8)
+    f = torch.ones(1, 1, 2, 2, 2) / 8
+    down = Conv3D(3, 3, kernel=0, down=True)
+    assert torch.allclose(down(x), F.conv3d(x, f.tile(3, 1, 1, 1, 1), groups=3, stride=2), atol=1e-6)
+    up = Conv3D(3, 3, kernel=0, up=True)
+    assert torch.allclose(up(x), F.conv_transpose3d(x, (4 * f).tile(3, 1, 1, 1, 1), groups=3, stride=2), atol=1e-6)
+    # resampling fused with a 3x3x3 convolution keeps the expected shapes
+    assert Conv3D(3, 5, kernel=3, down=True)(x).shape == (2, 5, 2, 3, 4)
+    assert Conv3D(3, 5, kernel=3, up=True, resample_filter=[1, 3, 3, 1])(x).shape == (2, 5, 8, 12, 16)
+
+
+def test_groupnorm3d_eval_uses_unbiased_variance():
+    from physicsnemo_b200.experimental.nn import GroupNorm3D
+
+    torch.manual_seed(0)
+    gn = GroupNorm3D(8, num_groups=2).eval()
+    with torch.no_grad():
+        gn.weight.uniform_(0.5, 1.5); gn.bias.normal_()
+    x = torch.randn(2, 8, 2, 3, 4)
+    g = x.view(2, 2, -1)
+    ref = ((g - g.mean(-1, keepdim=True)) * (g.var(-1, keepdim=True) + gn.eps).rsqrt()).view_as(x)
+    ref = ref * gn.weight.view(1, -1, 1, 1, 1) + gn.bias.view(1, -1, 1, 1, 1)
+    assert torch.allclose(gn(x), ref, atol=1e-5)
+
+
+@pytest.mark.parametrize("enc,dec,emb", [("standard", "standard", "positional"), ("skip", "skip", "fourier"),
+                                         ("residual", "standard", "zero")])
+def test_diffusion_unet_3d(enc, dec, emb):
+    from physicsnemo_b200.experimental.models import DiffusionUNet3D
+
+    torch.manual_seed(0)
+    vec = 0 if emb == "zero" else 3
+    net = DiffusionUNet3D(x_channels=2, vol_cond_channels=1, vec_cond_dim=vec, num_levels=2, model_channels=8, channel_mult=[1, 2],
+                          num_blocks=1, attention_levels=[1], encoder_type=enc, decoder_type=dec, embedding_type=emb, dropout=0.0,
+                          checkpoint_level=1)
+    x, t = torch.randn(2, 2, 4, 8, 8, requires_grad=True), torch.rand(2)
+    cond = {"volume": torch.randn(2, 1, 4, 8, 8)}
+    if vec:
+        cond["vector"] = torch.randn(2, vec)
+    y = net(x, t, cond)
+    assert y.shape == x.shape
+    y.square().sum().backward()
+    assert x.grad is not None and all(p.grad is not None for p in net.parameters())
+    with pytest.raises(ValueError):
+        net(torch.randn(2, 2, 4, 8, 7), t, None)            # 7 is neither a power of two nor a multiple of 2
+    with pytest.raises(ValueError):
+        net(x, t, {"volume": cond["volume"], "other": t})
