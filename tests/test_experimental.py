@@ -257,3 +257,79 @@ def test_diffusion_unet_3d(enc, dec, emb):
         net(torch.randn(2, 2, 4, 8, 7), t, None)            # 7 is neither a power of two nor a multiple of 2
     with pytest.raises(ValueError):
         net(x, t, {"volume": cond["volume"], "other": t})
+
+
+# ------------------------------------------------------------------------------------------------------- xDeepONet
+def test_xdeeponet_padding_helpers():
+    from physicsnemo_b200.experimental.models.xdeeponet._padding import (compute_right_pad_to_multiple, pad_right_nd,
+                                                                          pad_spatial_right)
+    import torch.nn.functional as F
+
+    assert compute_right_pad_to_multiple((5, 8, 16), multiple=8) == (3, 0, 0)
+    assert compute_right_pad_to_multiple((5, 8, 13), multiple=8, min_right_pad=4) == (11, 8, 11)
+    x = torch.randn(2, 3, 5, 4, 2)
+    y = pad_spatial_right(x, spatial_ndim=2, right_pad=(2, 3))
+    ref = F.pad(x.reshape(2, 3, 5, 8).permute(0, 3, 1, 2), (0, 3, 0, 2), mode="replicate").permute(0, 2, 3, 1).reshape(2, 5, 8, 4, 2)
+    assert torch.equal(y, ref)
+    z = pad_right_nd(x, dims=[1, -1], right_pad=[1, 2], mode="constant", constant_value=7.0)
+    assert z.shape == (2, 4, 5, 4, 4) and torch.equal(z[:, :3, :, :, :2], x) and bool((z[:, 3] == 7).all()) and bool((z[..., 2:] == 7).all())
+    with pytest.raises(ValueError):
+        pad_spatial_right(x, spatial_ndim=2, right_pad=(1,))
+
+
+def _mlp(i, w):
+    from physicsnemo_b200.models.mlp import FullyConnected
+    return FullyConnected(i, w, w, 2, "tanh")
+
+
+@pytest.mark.parametrize("decoder", ["mlp", "conv", "temporal_projection"])
+def test_xdeeponet_trunked_variants(decoder):
+    from physicsnemo_b200.experimental.models import DeepONet, SpatialBranch
+
+    torch.manual_seed(0)
+    W = 8
+    net = DeepONet(SpatialBranch(2, width=W, num_fourier_layers=1, num_conv_layers=1, modes1=3, modes2=3, coord_features=True),
+                   trunk=_mlp(1, W), branch2=_mlp(4, W), width=W, out_channels=2, decoder_type=decoder, decoder_width=16,
+                   output_window=3 if decoder == "temporal_projection" else None)
+    u, t, v = torch.randn(2, 8, 12, 3), torch.rand(5), torch.randn(2, 4)
+    y = net(u, t, v)
+    assert y.shape == (2, 8, 12, 3 if decoder == "temporal_projection" else 5, 2)
+    assert torch.allclose(y, net(u, t, x_branch2=v))
+    y.square().sum().backward()
+    assert all(p.grad is not None for p in net.parameters())
+    if decoder != "temporal_projection":
+        # the operator is separable in time: evaluating one query time alone gives the same slice
+        with torch.no_grad():
+            net.eval()
+            assert torch.allclose(net(u, t, v)[..., 2:3, :], net(u, t[2:3], v), atol=1e-6)
+    with pytest.raises(TypeError):
+        net(u)
+    with pytest.raises(TypeError):
+        net(u, t, v, x_branch2=v)
+
+
+def test_xdeeponet_packed_and_trunkless_modes():
+    from physicsnemo_b200.experimental.models import DeepONet, FNO4DWrapper, SpatialBranch
+
+    torch.manual_seed(0)
+    W = 8
+    packed = DeepONet(SpatialBranch(2, width=W, num_fourier_layers=1, modes1=3, modes2=3), trunk=_mlp(3, W), width=W,
+                      auto_pad=True, padding=5, trunk_input="grid")
+    assert packed.padding == 8
+    x = torch.randn(2, 10, 12, 4, 6)
+    assert packed(x).shape == (2, 10, 12, 4, 1)
+    assert packed(x, target_times=torch.rand(7)).shape == (2, 10, 12, 7, 1)
+
+    xfno = DeepONet(SpatialBranch(3, width=W, num_fourier_layers=1, modes1=2, modes2=2, modes3=2), dimension=3, width=W,
+                    auto_pad=True, time_modes=2, decoder_type="conv", decoder_layers=1)
+    vol = torch.randn(1, 4, 4, 5, 3)
+    assert xfno(vol).shape == (1, 4, 4, 5, 1)
+    assert xfno(vol, target_times=torch.rand(2)).shape == (1, 4, 4, 2, 1)
+    with pytest.raises(ValueError):
+        DeepONet(_mlp(3, W), trunk=_mlp(1, W), width=W, decoder_type="conv")
+    with pytest.raises(ValueError):
+        DeepONet(SpatialBranch(2, width=W, num_conv_layers=1), width=W, time_modes=2)
+
+    f4 = FNO4DWrapper(3, 1, latent_channels=4, num_fno_layers=1, num_fno_modes=2, padding=1)
+    x6 = torch.randn(1, 4, 4, 4, 3, 3)
+    assert f4(x6).shape == (1, 4, 4, 4, 3) and f4(x6, torch.rand(2)).shape == (1, 4, 4, 4, 2)
