@@ -181,6 +181,16 @@ int pnm_spectral_contract(const void* A, const void* B, void* out, int nd, const
                           const long long* so, const long long* chan_strides, int P, int Q, int R, int conj_a, int conj_b,
                           int accumulate, void* stream);
 
+// Equivariant normalisation of spherical-harmonic grids x[B, L, M, 2, C] (see sh_norm.cu): degree groups `group[L]`, statistic weights
+// wstat[L, M], affine a[L, C], optional bias[C] on the (0, 0, 0) row, mask[L, M, 2].  dtype 0 = fp32, 1 = bf16, 2 = fp16.
+int pnm_sh_norm_fits(int L, int M, int C, int which);
+int pnm_sh_norm_bwd_grid(long long B, int L, int M, int C);
+int pnm_sh_norm_fwd(const void* x, void* y, const float* aw, const float* bias, const float* wstat, const float* mask, const int* group,
+                    long long B, int L, int M, int C, float eps, int subtract_mean, int dtype, void* stream);
+int pnm_sh_norm_bwd(const void* x, const void* dy, void* dx, const float* aw, const float* wstat, const float* mask, const int* group,
+                    float* daw_part, float* dbias_part, long long B, int L, int M, int C, float eps, int subtract_mean, int dtype,
+                    int grid, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

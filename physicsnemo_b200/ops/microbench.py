@@ -144,6 +144,34 @@ def attention_cases(small: bool = False):
     return out
 
 
+def sh_norm_cases(small=False):
+    """Equivariant norms on spherical-harmonic grids [B, 7, 3, 2, 128] (lmax 6, mmax 2): own kernel against the same
+    operator written with tensor operations.  Bytes: valid rows read, all rows written (forward); x and dy read, dx
+    written (backward)."""
+    from ..experimental.nn.symmetry import EquivariantLayerNorm, EquivariantLayerNormTied, EquivariantRMSNorm
+    from . import sh_norm as S
+
+    B, L, M, C = (8192 if small else 65536), 7, 3, 128
+    out = {}
+    for name, cls in (("rms", EquivariantRMSNorm), ("ln", EquivariantLayerNorm), ("tied", EquivariantLayerNormTied)):
+        for dt in (torch.float32, torch.bfloat16):
+            mod = cls(L - 1, M - 1, C).cuda()
+            x = torch.randn(B, L, M, 2, C, device="cuda").to(dt).requires_grad_(True)
+            valid = int(mod.grid_mask_3d.sum())
+            esz = x.element_size()
+            tag = f"sh_{name}_{'f32' if dt == torch.float32 else 'bf16'}"
+            out[tag + "_fwd"] = (lambda mod=mod, x=x: mod(x.detach()), 0.0, B * C * esz * (valid + L * M * 2))
+            y = mod(x)
+            dy = torch.randn_like(y)
+            out[tag + "_bwd"] = (lambda y=y, x=x, dy=dy, mod=mod: torch.autograd.grad(y, [x] + list(mod.parameters()), dy,
+                                                                                      retain_graph=True),
+                                 0.0, B * C * esz * (2 * valid + L * M * 2))
+            if name == "rms":
+                args = (mod.affine_weight, mod.affine_bias, mod._wstat, mod.grid_mask_3d, mod._group, mod.eps, True)
+                out[tag + "_fwd_torch_ops"] = (lambda x=x, args=args: S.reference(x.detach(), *args), 0.0,
+                                               B * C * esz * (valid + L * M * 2))
+    return out
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel")
@@ -157,6 +185,9 @@ def main():
         names = list(table)
     elif args.kernel == "groupnorm":
         table = groupnorm_cases()
+        names = list(table)
+    elif args.kernel in ("sh_norm", "sh_norm_small"):
+        table = sh_norm_cases(small=args.kernel == "sh_norm_small")
         names = list(table)
     elif args.kernel in ("attention", "attention_small"):
         table = attention_cases(small=args.kernel == "attention_small")

@@ -333,3 +333,188 @@ def test_xdeeponet_packed_and_trunkless_modes():
     f4 = FNO4DWrapper(3, 1, latent_channels=4, num_fno_layers=1, num_fno_modes=2, padding=1)
     x6 = torch.randn(1, 4, 4, 4, 3, 3)
     assert f4(x6).shape == (1, 4, 4, 4, 3) and f4(x6, torch.rand(2)).shape == (1, 4, 4, 4, 2)
+
+
+# --------------------------------------------------------------------------------------------- symmetry: norms
+def _sh_input(B, lmax, mmax, C):
+    return torch.randn(B, lmax + 1, mmax + 1, 2, C, dtype=torch.float64)
+
+
+def test_equivariant_rms_norm_formula():
+    """Direct restatement: masked input, centred scalar row, one balanced RMS, per-degree weight, bias on the scalar row."""
+    from physicsnemo_b200.experimental.nn.symmetry import (EquivariantRMSNorm, make_degree_balance_weight, make_grid_mask,
+                                                          make_m0_imag_mask)
+
+    torch.manual_seed(0)
+    lmax, mmax, C = 3, 2, 6
+    mod = EquivariantRMSNorm(lmax, mmax, C).double()
+    with torch.no_grad():
+        mod.affine_weight.uniform_(0.5, 1.5); mod.affine_bias.normal_()
+    x = _sh_input(4, lmax, mmax, C)
+    mask = make_grid_mask(lmax, mmax).double()[None, :, :, None, None] * make_m0_imag_mask(mmax).double()
+    xm = x * mask
+    xm[:, 0, 0, 0] -= xm[:, 0, 0, 0].mean(-1, keepdim=True)
+    w = make_degree_balance_weight(lmax, mmax).double()
+    ms = torch.einsum("blmrc,lm->b", xm ** 2, w) / (2 * C)
+    want = xm * (ms + mod.eps).rsqrt()[:, None, None, None, None] * mod.affine_weight[None, :, None, None, :]
+    want[:, 0, 0, 0] += mod.affine_bias
+    want = want * mask
+    assert torch.allclose(mod(x), want, atol=1e-12)
+    assert float(w.sum()) == pytest.approx(1.0)           # every degree carries 1 / (lmax + 1)
+
+
+def test_equivariant_norms_are_rotation_equivariant_about_z():
+    """A rotation about z multiplies order m by exp(i m phi): the norms commute with it and ignore invalid entries."""
+    from physicsnemo_b200.experimental.nn.symmetry import (EquivariantLayerNorm, EquivariantLayerNormTied, EquivariantRMSNorm,
+                                                          FusedEquivariantRMSNorm)
+
+    torch.manual_seed(0)
+    lmax, mmax, C = 4, 3, 5
+    x = _sh_input(3, lmax, mmax, C)
+    phi = 0.7
+    m = torch.arange(mmax + 1, dtype=torch.float64)
+    cos, sin = torch.cos(m * phi)[None, None, :, None], torch.sin(m * phi)[None, None, :, None]
+
+    def rotate(t):
+        re, im = t[..., 0, :], t[..., 1, :]
+        return torch.stack([cos * re - sin * im, sin * re + cos * im], dim=-2)
+
+    for cls in (EquivariantRMSNorm, EquivariantLayerNorm, EquivariantLayerNormTied, FusedEquivariantRMSNorm):
+        mod = cls(lmax, mmax, C).double()
+        with torch.no_grad():
+            for p in mod.parameters():
+                p.add_(0.2 * torch.randn_like(p))
+        y = mod(x)
+        valid = mod.grid_mask_3d[None, :, :, :, None].double()
+        assert torch.allclose(mod(rotate(x * valid)), rotate(y), atol=1e-10), cls.__name__
+        junk = x + (1 - valid) * 100.0
+        assert torch.allclose(mod(junk), y, atol=1e-12) and bool((y * (1 - valid) == 0).all())
+    with pytest.raises(ValueError):
+        EquivariantLayerNormTied(0, 0, 4)
+    with pytest.raises(ValueError):
+        EquivariantRMSNorm(2, 3, 4)
+    with pytest.raises(ValueError):
+        EquivariantRMSNorm(2, 1, 4)(torch.randn(2, 3, 2, 2, 5))
+
+
+def test_equivariant_layer_norm_tied_scalar_row_is_layer_norm():
+    from physicsnemo_b200.experimental.nn.symmetry import EquivariantLayerNormTied
+
+    torch.manual_seed(0)
+    mod = EquivariantLayerNormTied(3, 2, 8).double()
+    with torch.no_grad():
+        mod.norm_l0.weight.uniform_(0.5, 1.5); mod.norm_l0.bias.normal_()
+    x = _sh_input(5, 3, 2, 8).requires_grad_(True)
+    y = mod(x)
+    assert torch.allclose(y[:, 0, 0, 0], mod.norm_l0(x[:, 0, 0, 0]), atol=1e-12)
+    y.square().sum().backward()
+    assert mod.norm_l0.weight.grad is not None and mod.affine_weight.grad is not None and x.grad is not None
+    # scaling the l > 0 part leaves its normalised output unchanged (up to eps)
+    x2 = x.detach().clone(); x2[:, 1:] *= 7.0
+    assert torch.allclose(mod(x2)[:, 1:], y[:, 1:].detach(), atol=1e-4)
+
+
+# ------------------------------------------------------------------------ symmetry: linear maps, gates, rotations
+def _random_rotation_angles(B):
+    return tuple(torch.rand(B, dtype=torch.float64) * 6.0 - 3.0 for _ in range(3))
+
+
+def test_wigner_matrices_form_a_representation():
+    """D is orthogonal, D(identity) = 1, D(R1) D(R2) = D(R1 R2) for rotations about one axis, and l = 1 rotates vectors."""
+    from physicsnemo_b200.experimental.nn.symmetry import compute_wigner_d_matrices
+
+    torch.manual_seed(0)
+    a, b, g = _random_rotation_angles(5)
+    D = compute_wigner_d_matrices(a, b, g, 4)
+    eye = torch.eye(25, dtype=torch.float64)
+    assert D.shape == (5, 25, 25) and torch.allclose(D @ D.transpose(1, 2), eye.expand(5, -1, -1), atol=1e-10)
+    zero = torch.zeros(5, dtype=torch.float64)
+    assert torch.allclose(compute_wigner_d_matrices(zero, zero, zero, 4), eye.expand(5, -1, -1), atol=1e-12)
+    D1 = compute_wigner_d_matrices(a, zero, zero, 3)
+    D2 = compute_wigner_d_matrices(b, zero, zero, 3)
+    assert torch.allclose(D1 @ D2, compute_wigner_d_matrices(a + b, zero, zero, 3), atol=1e-10)
+    # block structure: nothing couples different degrees
+    off = D.clone()
+    for l in range(5):
+        off[:, l * l:(l + 1) ** 2, l * l:(l + 1) ** 2] = 0
+    assert float(off.abs().max()) == 0.0
+    # the l = 1 block is a proper rotation (determinant +1)
+    assert torch.allclose(torch.linalg.det(D[:, 1:4, 1:4]), torch.ones(5, dtype=torch.float64), atol=1e-10)
+
+
+def test_edge_rotation_aligns_and_inverts():
+    from physicsnemo_b200.experimental.nn.symmetry import EdgeRotation, edge_vectors_to_euler_angles
+
+    torch.manual_seed(0)
+    rot = EdgeRotation(3, 2).double()
+    ev = torch.randn(4, 5, 3, dtype=torch.float64)
+    mask = torch.rand(4, 5) > 0.3
+    with pytest.raises(RuntimeError):
+        rot(torch.randn(4, 5, 16, 2, dtype=torch.float64))
+    W = rot.get_wigner_matrices(ev, mask)
+    assert W.shape == (4, 5, rot._reduced_dim, 16) and rot._reduced_dim == 1 + 3 + 5 + 5
+    x = torch.randn(4, 5, 16, 6, dtype=torch.float64)
+    y = rot(x)
+    assert torch.allclose(y, W @ x, atol=1e-12)                            # block application = dense matrix
+    assert torch.allclose(rot(y, inverse=True), W.transpose(-1, -2) @ y, atol=1e-12)
+    # rows of an orthogonal matrix: W W^T = 1 on the reduced space; masked edges carry the selection matrix
+    assert torch.allclose(W @ W.transpose(-1, -2), torch.eye(rot._reduced_dim, dtype=torch.float64).expand(4, 5, -1, -1), atol=1e-6)   # J is stored in fp32
+    sel = W[~mask]
+    assert bool(((sel == 0) | (sel == 1)).all()) and bool((sel.sum(-1) == 1).all())
+    # with mmax = lmax the round trip is exact
+    full = EdgeRotation(3).double()
+    full.get_wigner_matrices(ev)
+    assert torch.allclose(full(full(x), inverse=True), x, atol=1e-6)
+    # the pole direction has finite gradients
+    pole = torch.tensor([[[0.0, 1.0, 0.0]]], dtype=torch.float64, requires_grad=True)
+    a, b, _ = edge_vectors_to_euler_angles(pole)
+    (a.sum() + b.sum()).backward()
+    assert bool(torch.isfinite(pole.grad).all())
+    rot.clear_cache()
+    assert rot._cached_wigner is None
+
+
+def test_so3_layers_commute_with_rotations():
+    """Per-degree linear maps and the gated block commute with any rotation of the grid.  (The grid norms weight the
+    stored orders m >= 0 once each, so they commute with rotations about the polar axis only; see the test above.)"""
+    from physicsnemo_b200.experimental.nn.symmetry import SO3ConvolutionBlock, SO3LinearGrid, rotate_grid_coefficients
+
+    torch.manual_seed(0)
+    lmax, C = 3, 4
+    x = torch.randn(2, lmax + 1, lmax + 1, 2, C, dtype=torch.float64)
+    x = rotate_grid_coefficients(x, (0.0, 0.0, 0.0))                     # project on the valid coefficients
+    rot = _random_rotation_angles(2)
+    for layer in (SO3LinearGrid(C, 5, lmax, lmax), SO3ConvolutionBlock(C, 6, lmax, lmax)):
+        layer = layer.double()
+        a = layer(rotate_grid_coefficients(x, rot))
+        b = rotate_grid_coefficients(layer(x), rot)
+        assert torch.allclose(a, b, atol=1e-9), type(layer).__name__
+
+
+def test_so2_convolution_is_complex_linear_per_order():
+    from physicsnemo_b200.experimental.nn.symmetry import GateActivation, SO2Convolution, rotate_grid_coefficients
+
+    torch.manual_seed(0)
+    lmax, mmax, C, O = 3, 2, 4, 5
+    conv = SO2Convolution(C, O, lmax, mmax, edge_channels=3, produce_gates=True).double()
+    x = torch.randn(6, lmax + 1, mmax + 1, 2, C, dtype=torch.float64)
+    e = torch.randn(6, 3, dtype=torch.float64)
+    y = conv(x, e)
+    assert y.shape == (6, lmax + 1, mmax + 1, 2, O + lmax * O)
+    # gate channels live on the scalar row only
+    assert float(y[:, 1:, :, :, O:].abs().max()) == 0.0 and float(y[:, 0, 1:, :, O:].abs().max()) == 0.0
+    # complex arithmetic of order m = 1 at degree l = 2
+    xm = x * conv.rad_func(e).view(6, lmax + 1, mmax + 1, 2, C)
+    z = torch.complex(xm[:, 2, 1, 0], xm[:, 2, 1, 1]) @ torch.complex(conv.W_r[1], conv.W_i[1])
+    assert torch.allclose(y[:, 2, 1, 0, :O], z.real[:, :O], atol=1e-12) and torch.allclose(y[:, 2, 1, 1, :O], z.imag[:, :O], atol=1e-12)
+    # equivariance about the edge axis (rotation by gamma only multiplies order m by a phase)
+    plain = SO2Convolution(C, O, lmax, mmax).double()
+    xs = rotate_grid_coefficients(torch.randn(6, lmax + 1, lmax + 1, 2, C, dtype=torch.float64), (0.0, 0.0, 0.0))[:, :, :mmax + 1]
+    m = torch.arange(mmax + 1, dtype=torch.float64)
+    c, s = torch.cos(0.9 * m)[None, None, :, None], torch.sin(0.9 * m)[None, None, :, None]
+    spin = lambda t: torch.stack([c * t[..., 0, :] - s * t[..., 1, :], s * t[..., 0, :] + c * t[..., 1, :]], dim=-2)  # noqa: E731
+    assert torch.allclose(plain(spin(xs)), spin(plain(xs)), atol=1e-10)
+    gate = GateActivation(lmax, mmax, O).double()
+    assert gate(y).shape == (6, lmax + 1, mmax + 1, 2, O)
+    with pytest.raises(ValueError):
+        conv(x)

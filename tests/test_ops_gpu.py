@@ -249,3 +249,47 @@ def test_spectral_conv_fused_corner_contraction(nd):
     assert torch.allclose(xg.grad.cpu(), xr.grad, atol=2e-5, rtol=1e-4)
     for p, r in zip(gpu.parameters(), ref_grads):
         assert torch.allclose(p.grad.cpu(), r, atol=2e-4, rtol=1e-3)
+
+
+# ------------------------------------------------------------------------------------- spherical-harmonic norms
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind", ["rms", "rms_plain", "ln", "tied"])
+@pytest.mark.parametrize("lmc", [(6, 2, 128), (3, 3, 20), (1, 1, 7)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sh_norm_kernel_matches_tensor_ops(kind, lmc, dtype):
+    """Forward and backward of the grouped spherical-harmonic norm kernel against the same operator in fp32 tensor ops."""
+    from physicsnemo_b200.experimental.nn.symmetry import EquivariantLayerNorm, EquivariantLayerNormTied, EquivariantRMSNorm
+    from physicsnemo_b200.ops import device_error
+    from physicsnemo_b200.ops import gemm as G
+    from physicsnemo_b200.ops import sh_norm as S
+
+    lmax, mmax, C = lmc
+    torch.manual_seed(0)
+    mod = {"rms": lambda: EquivariantRMSNorm(lmax, mmax, C), "rms_plain": lambda: EquivariantRMSNorm(lmax, mmax, C, subtract_mean=False,
+                                                                                                    std_balance_degrees=False),
+           "ln": lambda: EquivariantLayerNorm(lmax, mmax, C), "tied": lambda: EquivariantLayerNormTied(lmax, mmax, C)}[kind]().cuda()
+    with torch.no_grad():
+        for p in mod.parameters():
+            p.add_(0.3 * torch.randn_like(p))
+    B = 777
+    x = (torch.randn(B, lmax + 1, mmax + 1, 2, C, device="cuda") * 2 + 0.5).to(dtype)
+    assert S.supported(x)
+    xa, xb = x.clone().requires_grad_(True), x.float().clone().requires_grad_(True)
+    before = G.launch_count
+    y = mod(xa)
+    assert G.launch_count == before + 1 and y.dtype == dtype
+    if kind == "tied":
+        aff, bias = torch.cat([mod.norm_l0.weight[None], mod.affine_weight], 0), mod.norm_l0.bias
+    else:
+        aff, bias = mod.affine_weight, mod.affine_bias
+    ref = S.reference(xb, aff, bias, mod._wstat, mod.grid_mask_3d, mod._group, mod.eps, mod._centre)
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    assert (y.float() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+    dy = torch.randn_like(ref)
+    params = list(mod.parameters())
+    got = torch.autograd.grad(y, [xa] + params, dy.to(dtype))
+    want = torch.autograd.grad(ref, [xb] + params, dy.to(dtype).float())
+    for g, w in zip(got, want):
+        scale = max(1.0, w.abs().max().item())
+        assert (g.float() - w).abs().max().item() <= (2e-4 if dtype == torch.float32 else 4e-2) * scale, (kind, g.shape)
+    assert device_error() == 0
