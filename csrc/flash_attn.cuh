@@ -48,7 +48,7 @@ struct FlashArgs {
 };
 
 constexpr int kFaThreads = 320;
-constexpr int kFaPolyMask = 0xAA;   // which of every eight exponentials go to the FMA-pipe polynomial
+constexpr int kFaPolyMask = 0;   // bit i set: exponential i of every eight goes to the FMA-pipe polynomial (measured slower: the FMA pipe is the busier one)
 constexpr int kFaBarBytes = 256 + 1024;   // barriers, then the 1 KB exchange area of the row halves
 
 template <int D>

@@ -234,6 +234,261 @@ sh_norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __restr
   for (int i = threadIdx.x; i < C; i += blockDim.x) dbias_part[size_t(blockIdx.x) * C + i] = dbias_s[i];
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Register-resident variants for C = 32 * CPL (CPL = 1, 2, 4) and at most R rows per warp: a warp always owns the same rows
+// (p = warp + k * warps), a lane always owns the same CPL consecutive channels, so the sample lives in registers, all
+// loads of a sample are issued before the first use, and the affine-weight / bias gradients accumulate in registers over
+// all the samples a CTA visits (one shared-memory reduction per CTA at the end instead of one atomic per element).
+constexpr int kShRows = 6;
+
+template <typename T, int CPL>
+__device__ __forceinline__ void load_chunk(const T* __restrict__ src, float (&dst)[CPL]) {
+  const Pack<T, CPL> p = *reinterpret_cast<const Pack<T, CPL>*>(src);
+#pragma unroll
+  for (int i = 0; i < CPL; ++i) dst[i] = to_f(p.v[i]);
+}
+
+template <typename T, int CPL>
+__device__ __forceinline__ void store_chunk(T* __restrict__ dst, const float (&src)[CPL]) {
+  Pack<T, CPL> p;
+#pragma unroll
+  for (int i = 0; i < CPL; ++i) p.v[i] = from_f<T>(src[i]);
+  *reinterpret_cast<Pack<T, CPL>*>(dst) = p;
+}
+
+template <typename T, int CPL>
+__global__ void __launch_bounds__(512)
+sh_norm_fwd_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restrict__ aw, const float* __restrict__ bias,
+                       const float* __restrict__ wstat, const float* __restrict__ mask, const int* __restrict__ group, long long B,
+                       int L, int M, float eps, int subtract_mean) {
+  constexpr int C = 32 * CPL;
+  extern __shared__ float sm[];
+  const int P = L * M * 2;
+  float* pos_sum = sm;
+  float* inv = pos_sum + P;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int c0 = lane * CPL;
+  bool valid[kShRows];
+#pragma unroll
+  for (int k = 0; k < kShRows; ++k) valid[k] = warp + k * nw < P && mask[warp + k * nw] != 0.f;
+  float bv[CPL];
+#pragma unroll
+  for (int i = 0; i < CPL; ++i) bv[i] = (bias != nullptr && warp == 0) ? bias[c0 + i] : 0.f;
+  for (long long b = blockIdx.x; b < B; b += gridDim.x) {
+    const T* xb = x + size_t(b) * P * C + c0;
+    T* yb = y + size_t(b) * P * C + c0;
+    float xr[kShRows][CPL];
+#pragma unroll
+    for (int k = 0; k < kShRows; ++k)
+      if (valid[k]) load_chunk<T, CPL>(xb + size_t(warp + k * nw) * C, xr[k]);
+#pragma unroll
+    for (int k = 0; k < kShRows; ++k) {
+      const int p = warp + k * nw;
+      if (p >= P) continue;
+      float q = 0.f;
+      if (valid[k]) {
+        if (p == 0 && subtract_mean) {
+          float s = 0.f;
+#pragma unroll
+          for (int i = 0; i < CPL; ++i) s += xr[k][i];
+          const float mean = warp_sum(s) / float(C);
+#pragma unroll
+          for (int i = 0; i < CPL; ++i) xr[k][i] -= mean;
+        }
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) q = fmaf(xr[k][i], xr[k][i], q);
+        q = warp_sum(q);
+      }
+      if (lane == 0) pos_sum[p] = q;
+    }
+    __syncthreads();
+    group_inverse(pos_sum, inv, wstat, group, L, M, C, eps);
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kShRows; ++k) {
+      const int p = warp + k * nw;
+      if (p >= P) continue;
+      float o[CPL];
+      if (valid[k]) {
+        const int l = p / (2 * M);
+        const float s = inv[group[l]];
+        float a[CPL];
+        load_chunk<float, CPL>(aw + l * C + c0, a);
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) o[i] = xr[k][i] * s * a[i] + (p == 0 ? bv[i] : 0.f);
+      } else {
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) o[i] = 0.f;
+      }
+      store_chunk<T, CPL>(yb + size_t(p) * C, o);
+    }
+    __syncthreads();   // pos_sum / inv are rewritten by the next sample
+  }
+}
+
+template <typename T, int CPL>
+__global__ void __launch_bounds__(512)
+sh_norm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __restrict__ dx, const float* __restrict__ aw,
+                       const float* __restrict__ wstat, const float* __restrict__ mask, const int* __restrict__ group,
+                       float* __restrict__ daw_part, float* __restrict__ dbias_part, long long B, int L, int M, float eps,
+                       int subtract_mean) {
+  constexpr int C = 32 * CPL;
+  extern __shared__ float sm[];
+  const int P = L * M * 2;
+  float* daw_s = sm;                       // [L, C] then [C] for the bias
+  float* pos_sum = daw_s + size_t(L + 1) * C;
+  float* pos_dot = pos_sum + P;
+  float* inv = pos_dot + P;
+  float* dotg = inv + L;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int c0 = lane * CPL;
+  for (int i = threadIdx.x; i < (L + 1) * C; i += blockDim.x) daw_s[i] = 0.f;
+  bool valid[kShRows];
+  float a[kShRows][CPL], dacc[kShRows][CPL], bacc[CPL];
+#pragma unroll
+  for (int k = 0; k < kShRows; ++k) {
+    const int p = warp + k * nw;
+    valid[k] = p < P && mask[p] != 0.f;
+    const int l = p < P ? p / (2 * M) : 0;
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) {
+      a[k][i] = aw[l * C + c0 + i];
+      dacc[k][i] = 0.f;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < CPL; ++i) bacc[i] = 0.f;
+  __syncthreads();
+  for (long long b = blockIdx.x; b < B; b += gridDim.x) {
+    const size_t off = size_t(b) * P * C + c0;
+    float xr[kShRows][CPL], gr[kShRows][CPL];
+#pragma unroll
+    for (int k = 0; k < kShRows; ++k)
+      if (valid[k]) {
+        load_chunk<T, CPL>(x + off + size_t(warp + k * nw) * C, xr[k]);
+        load_chunk<T, CPL>(dy + off + size_t(warp + k * nw) * C, gr[k]);
+      }
+#pragma unroll
+    for (int k = 0; k < kShRows; ++k) {
+      const int p = warp + k * nw;
+      if (p >= P) continue;
+      float q = 0.f;
+      if (valid[k]) {
+        if (p == 0 && subtract_mean) {
+          float s = 0.f;
+#pragma unroll
+          for (int i = 0; i < CPL; ++i) s += xr[k][i];
+          const float mean = warp_sum(s) / float(C);
+#pragma unroll
+          for (int i = 0; i < CPL; ++i) xr[k][i] -= mean;
+        }
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) q = fmaf(xr[k][i], xr[k][i], q);
+        q = warp_sum(q);
+      }
+      if (lane == 0) pos_sum[p] = q;
+    }
+    __syncthreads();
+    group_inverse(pos_sum, inv, wstat, group, L, M, C, eps);
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kShRows; ++k) {
+      const int p = warp + k * nw;
+      if (p >= P) continue;
+      float dot = 0.f;
+      if (valid[k]) {
+        const float s = inv[group[p / (2 * M)]];
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+          const float d = gr[k][i], v = xr[k][i];
+          dacc[k][i] = fmaf(d * v, s, dacc[k][i]);
+          if (p == 0) bacc[i] += d;
+          const float g = d * a[k][i];
+          gr[k][i] = g;
+          dot = fmaf(g, v, dot);
+        }
+        dot = warp_sum(dot);
+      }
+      if (lane == 0) pos_dot[p] = dot;
+    }
+    __syncthreads();
+    if (threadIdx.x < L) {
+      const int g = threadIdx.x;
+      float D = 0.f;
+      for (int l = 0; l < L; ++l)
+        if (group[l] == g)
+          for (int q = l * M * 2; q < (l + 1) * M * 2; ++q) D += pos_dot[q];
+      dotg[g] = D;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kShRows; ++k) {
+      const int p = warp + k * nw;
+      if (p >= P) continue;
+      float o[CPL];
+      if (valid[k]) {
+        const int l = p / (2 * M), m = (p / 2) % M;
+        const int g = group[l];
+        const float s = inv[g];
+        const float kc = wstat[l * M + m] * s * s * s * dotg[g] / float(C);
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) {
+          o[i] = s * gr[k][i] - kc * xr[k][i];
+          sum += o[i];
+        }
+        if (p == 0 && subtract_mean) {
+          const float mean = warp_sum(sum) / float(C);
+#pragma unroll
+          for (int i = 0; i < CPL; ++i) o[i] -= mean;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) o[i] = 0.f;
+      }
+      store_chunk<T, CPL>(dx + off + size_t(p) * C, o);
+    }
+    // pos_sum is next written after two more barriers of the following iteration at the earliest for inv / dotg readers,
+    // but pos_sum / pos_dot themselves are rewritten right away: separate the samples
+    __syncthreads();
+  }
+#pragma unroll
+  for (int k = 0; k < kShRows; ++k) {
+    const int p = warp + k * nw;
+    if (p < P && valid[k]) {
+      const int l = p / (2 * M);
+#pragma unroll
+      for (int i = 0; i < CPL; ++i) atomicAdd(&daw_s[l * C + c0 + i], dacc[k][i]);
+    }
+  }
+  if (warp == 0) {
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) daw_s[L * C + c0 + i] = bacc[i];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < L * C; i += blockDim.x) daw_part[size_t(blockIdx.x) * L * C + i] = daw_s[i];
+  for (int i = threadIdx.x; i < C; i += blockDim.x) dbias_part[size_t(blockIdx.x) * C + i] = daw_s[L * C + i];
+}
+
+// threads of the register-resident variants (0: not applicable)
+int reg_threads(int L, int M, int C) {
+  const int P = L * M * 2;
+  if (C != 32 && C != 64 && C != 128) return 0;
+  if (P <= 8 * kShRows) return 256;
+  if (P <= 16 * kShRows) return 512;
+  return 0;
+}
+size_t reg_fwd_smem(int L, int M) { return (size_t(L) * M * 2 + L) * sizeof(float); }
+size_t reg_bwd_smem(int L, int M, int C) { return (size_t(L + 1) * C + size_t(L) * M * 2 * 2 + 2 * L) * sizeof(float); }
+
+int reg_grid(int threads, int ctas_per_sm, long long B) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long g = (long long)sms * ctas_per_sm;
+  return int(g < B ? g : B);
+}
+
 size_t fwd_smem(int L, int M, int C) { return (size_t(L) * M * 2 * C + size_t(L) * M * 2 + L) * sizeof(float); }
 size_t bwd_smem(int L, int M, int C) {
   return (size_t(L) * M * 2 * C * 2 + size_t(L + 1) * C + size_t(L) * M * 2 * 2 + 2 * L) * sizeof(float);
@@ -253,6 +508,14 @@ int grid_for(size_t smem, long long B) {
 template <typename T>
 int launch_fwd(const void* x, void* y, const float* aw, const float* bias, const float* wstat, const float* mask, const int* group,
                long long B, int L, int M, int C, float eps, int sub, cudaStream_t st) {
+  if (const int threads = reg_threads(L, M, C)) {
+    const size_t smem = reg_fwd_smem(L, M);
+    auto kern = C == 128 ? sh_norm_fwd_reg_kernel<T, 4> : (C == 64 ? sh_norm_fwd_reg_kernel<T, 2> : sh_norm_fwd_reg_kernel<T, 1>);
+    int per_sm = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+    kern<<<reg_grid(threads, per_sm, B), threads, smem, st>>>((const T*)x, (T*)y, aw, bias, wstat, mask, group, B, L, M, eps, sub);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
   const size_t smem = fwd_smem(L, M, C);
   const int grid = grid_for(smem, B);
   auto k4 = sh_norm_fwd_kernel<T, 4>;
@@ -266,6 +529,19 @@ int launch_fwd(const void* x, void* y, const float* aw, const float* bias, const
 template <typename T>
 int launch_bwd(const void* x, const void* dy, void* dx, const float* aw, const float* wstat, const float* mask, const int* group,
                float* daw_part, float* dbias_part, long long B, int L, int M, int C, float eps, int sub, int grid, cudaStream_t st) {
+  if (const int threads = reg_threads(L, M, C)) {
+    const size_t smem = reg_bwd_smem(L, M, C);
+    if (C == 128)
+      sh_norm_bwd_reg_kernel<T, 4><<<grid, threads, smem, st>>>((const T*)x, (const T*)dy, (T*)dx, aw, wstat, mask, group, daw_part,
+                                                                 dbias_part, B, L, M, eps, sub);
+    else if (C == 64)
+      sh_norm_bwd_reg_kernel<T, 2><<<grid, threads, smem, st>>>((const T*)x, (const T*)dy, (T*)dx, aw, wstat, mask, group, daw_part,
+                                                                 dbias_part, B, L, M, eps, sub);
+    else
+      sh_norm_bwd_reg_kernel<T, 1><<<grid, threads, smem, st>>>((const T*)x, (const T*)dy, (T*)dx, aw, wstat, mask, group, daw_part,
+                                                                 dbias_part, B, L, M, eps, sub);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
   const size_t smem = bwd_smem(L, M, C);
   auto k4 = sh_norm_bwd_kernel<T, 4>;
   auto k1 = sh_norm_bwd_kernel<T, 1>;
@@ -288,6 +564,7 @@ extern "C" int pnm_sh_norm_fits(int L, int M, int C, int which) {
 // number of CTAs of the backward launch = leading extent of the two partial-gradient buffers
 extern "C" int pnm_sh_norm_bwd_grid(long long B, int L, int M, int C) {
   if (!pnm_sh_norm_fits(L, M, C, 1) || B <= 0) return 0;
+  if (const int threads = pnm::reg_threads(L, M, C)) return pnm::reg_grid(threads, threads == 256 ? 2 : 1, B);
   return pnm::grid_for(pnm::bwd_smem(L, M, C), B);
 }
 

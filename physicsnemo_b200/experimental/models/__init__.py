@@ -1,5 +1,6 @@
 from .diffusion_unets import DiffusionUNet3D
 from .xdeeponet import DeepONet, FNO4DWrapper, SpatialBranch
+from .strata import Strata, StrataTransformer3D
 from .tedm import tEDMPrecondSuperRes, tEDMResidualLoss
 
-__all__ = ["DeepONet", "FNO4DWrapper", "SpatialBranch", "DiffusionUNet3D", "tEDMPrecondSuperRes", "tEDMResidualLoss"]
+__all__ = ["Strata", "StrataTransformer3D", "DeepONet", "FNO4DWrapper", "SpatialBranch", "DiffusionUNet3D", "tEDMPrecondSuperRes", "tEDMResidualLoss"]

@@ -518,3 +518,104 @@ def test_so2_convolution_is_complex_linear_per_order():
     assert gate(y).shape == (6, lmax + 1, mmax + 1, 2, O)
     with pytest.raises(ValueError):
         conv(x)
+
+
+# ------------------------------------------------------------------------------------------------------ Strata
+def _latlon(B, H, W):
+    lat = torch.linspace(30, 40, H)[None, :, None].expand(B, H, W)
+    lon = torch.linspace(10, 25, W)[None, None, :].expand(B, H, W)
+    return torch.stack([lat, lon], 1)
+
+
+def test_strata_patch_embed_equals_strided_convolution():
+    from physicsnemo_b200.experimental.models.strata.layers import PatchEmbed3D
+
+    torch.manual_seed(0)
+    pe = PatchEmbed3D(4, 8, 6, patch_size=(2, 4, 3), in_chans=3, embed_dim=10)
+    x = torch.randn(2, 3, 4, 8, 6)
+    ref = torch.nn.functional.conv3d(x, pe.proj.weight, pe.proj.bias, stride=(2, 4, 3))
+    assert torch.allclose(pe(x), ref, atol=1e-5)
+    tok, dhw = pe.tokens(x)
+    assert dhw == (2, 2, 2) and torch.allclose(tok, ref.flatten(2).transpose(1, 2), atol=1e-5)
+    with pytest.raises(ValueError):
+        PatchEmbed3D(4, 8, 6, patch_size=(3, 4, 3))
+
+
+@pytest.mark.parametrize("kw", [dict(attn_kernel=-1), dict(attn_kernel=(1, 3, 3), do_interleaved_dilation=True, na_dilation=1),
+                                dict(attn_kernel=3, do_alt_depthwise_attn=True, gated_attention=True, qk_norm=True, rope_mode="axial"),
+                                dict(attn_kernel=-1, rope_mode="stereographic", activation_checkpointing=0.5)])
+def test_strata_transformer_3d(kw):
+    from physicsnemo_b200.experimental.models import StrataTransformer3D
+
+    torch.manual_seed(0)
+    net = StrataTransformer3D(in_channels=3, out_channels=2, input_shape=(4, 8, 8), patch_size=(1, 2, 2), embed_dim=32, num_heads=4,
+                              num_layers=3, **kw)
+    x = torch.randn(2, 3, 4, 8, 8)
+    pos = _latlon(2, 8, 8) if kw.get("rope_mode") == "stereographic" else None
+    assert float(net(x, pos).abs().max()) == 0.0               # the head starts at zero
+    with torch.no_grad():
+        net.final_layer.linear.weight.normal_(std=0.1)
+    y = net(x, pos)
+    assert y.shape == (2, 2, 4, 8, 8)
+    y.square().sum().backward()
+    assert all(p.grad is not None for p in net.parameters())
+    tok, dhw = net.forward_tokens(x, pos)
+    assert tok.shape == (2, 4 * 4 * 4, 32) and dhw == (4, 4, 4)
+    with pytest.raises(ValueError):
+        net(torch.randn(2, 3, 4, 8, 6), pos)
+    if kw.get("rope_mode") == "stereographic":
+        with pytest.raises(ValueError):
+            net(x)
+
+
+def test_strata_neighbourhood_attention_is_local():
+    """With a 3x3x3 window and one layer, a perturbation only reaches tokens within one patch step."""
+    from physicsnemo_b200.experimental.models import StrataTransformer3D
+
+    torch.manual_seed(0)
+    net = StrataTransformer3D(in_channels=2, input_shape=(8, 8, 8), patch_size=1, embed_dim=16, num_heads=2, num_layers=1,
+                              attn_kernel=3, include_head=False).eval()
+    x = torch.randn(1, 2, 8, 8, 8)
+    x2 = x.clone()
+    x2[0, :, 3, 4, 4] += 1.0
+    with torch.no_grad():
+        diff = (net(x2) - net(x)).abs().sum(-1).reshape(8, 8, 8)
+    touched = diff > 1e-7
+    assert bool(touched[3, 4, 4]) and not bool(touched[0].any()) and not bool(touched[:, 0].any()) and not bool(touched[:, :, 7].any())
+    assert int(touched.sum()) <= 27
+
+
+@pytest.mark.parametrize("mode", ["pixel_proj", "bilinear_dw"])
+def test_strata_two_stage(mode):
+    from physicsnemo_b200.experimental.models import Strata
+    from physicsnemo_b200.experimental.models.strata.layers import StrataPixel3DBlock, StrataTransformer3DBlock
+
+    torch.manual_seed(0)
+    backbone = dict(in_channels=3, out_channels=2, input_shape=(4, 8, 8), patch_size=(2, 2, 2), embed_dim=32, num_heads=4, num_layers=1,
+                    attn_kernel=-1)
+    net = Strata(backbone_config=backbone, embed_dim_pixel=16, num_layers_pixel=2, num_heads_pixel=2, attn_kernel_pixel=(1, 3, 3),
+                 adaln_mode=mode, first_block_only_adaln=True, rope_mode_pixel="stereographic", activation_checkpointing_pixel=True)
+    assert isinstance(net.pixel_blocks[0], StrataPixel3DBlock) and isinstance(net.pixel_blocks[1], StrataTransformer3DBlock)
+    assert net.backbone.final_layer is None
+    with torch.no_grad():
+        for p in net.parameters():
+            p.add_(0.05 * torch.randn_like(p))
+    x, pos = torch.randn(2, 3, 4, 8, 8), _latlon(2, 8, 8)
+    y = net(x, pos)
+    assert y.shape == (2, 2, 4, 8, 8)
+    y.square().sum().backward()
+    assert all(p.grad is not None for p in net.parameters())
+    with pytest.raises(ValueError):
+        net(x)                                                  # stereographic rotary needs lat / lon
+
+
+def test_strata_chunked_depthwise_conv_matches_plain():
+    from physicsnemo_b200.experimental.models.strata.layers import DepthwiseConv
+
+    torch.manual_seed(0)
+    conv = DepthwiseConv(6, kernel_size=(5, 5), padding=(2, 2), bias=True, padding_mode="replicate", chunk_size=2)
+    x = torch.randn(5, 6, 7, 9)
+    ref = torch.nn.functional.conv2d(torch.nn.functional.pad(x, (2, 2, 2, 2), mode="replicate"), conv.weight, conv.bias, groups=6)
+    assert torch.allclose(conv(x), ref, atol=1e-6)
+    with pytest.raises(ValueError):
+        DepthwiseConv(6, kernel_size=3, groups=2)

@@ -254,7 +254,7 @@ def test_spectral_conv_fused_corner_contraction(nd):
 # ------------------------------------------------------------------------------------- spherical-harmonic norms
 @pytest.mark.gpu
 @pytest.mark.parametrize("kind", ["rms", "rms_plain", "ln", "tied"])
-@pytest.mark.parametrize("lmc", [(6, 2, 128), (3, 3, 20), (1, 1, 7)])
+@pytest.mark.parametrize("lmc", [(6, 2, 128), (5, 5, 64), (2, 2, 32), (3, 3, 20), (1, 1, 7)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_sh_norm_kernel_matches_tensor_ops(kind, lmc, dtype):
     """Forward and backward of the grouped spherical-harmonic norm kernel against the same operator in fp32 tensor ops."""
