@@ -191,6 +191,13 @@ int pnm_sh_norm_bwd(const void* x, const void* dy, void* dx, const float* aw, co
                     float* daw_part, float* dbias_part, long long B, int L, int M, int C, float eps, int subtract_mean, int dtype,
                     int grid, void* stream);
 
+// Pixel / observation cross attention in token space and the counting sort that packs observations by pixel (see pixel_attn.cu).
+int pnm_pixel_attn_fwd(const void* qk, const void* tok, const int* cu, void* ctx, float* lse, int P, int H, int Dt, int dtype, void* stream);
+int pnm_pixel_attn_bwd(const void* qk, const void* tok, const int* cu, const void* dctx, const float* lse, const float* delta, float* dqk,
+                       float* dtok, int P, int H, int Dt, int dtype, void* stream);
+int pnm_counting_histogram(const int* idx, int* counts, long long n, int bins, int* bad, void* stream);
+int pnm_counting_scatter(const int* idx, const int* offsets, int* cursor, int* order, long long n, int bins, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -256,6 +256,21 @@ __device__ __forceinline__ void store_chunk(T* __restrict__ dst, const float (&s
   *reinterpret_cast<Pack<T, CPL>*>(dst) = p;
 }
 
+// sum over the positions of each group of wpos[p] * val[p], evaluated redundantly by every warp (no broadcast barrier);
+// the result for the group of row k of this warp is returned in out[k]
+template <int R>
+__device__ __forceinline__ void group_sums(const float* val, const float* wpos, const int* gid, int P, int G, int lane,
+                                           const int (&gk)[R], float (&out)[R]) {
+  for (int g = 0; g < G; ++g) {
+    float sacc = 0.f;
+    for (int p = lane; p < P; p += 32) sacc += gid[p] == g ? wpos[p] * val[p] : 0.f;
+    sacc = warp_sum(sacc);
+#pragma unroll
+    for (int k = 0; k < R; ++k)
+      if (gk[k] == g) out[k] = sacc;
+  }
+}
+
 template <typename T, int CPL>
 __global__ void __launch_bounds__(512)
 sh_norm_fwd_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restrict__ aw, const float* __restrict__ bias,
@@ -264,19 +279,34 @@ sh_norm_fwd_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* 
   constexpr int C = 32 * CPL;
   extern __shared__ float sm[];
   const int P = L * M * 2;
-  float* pos_sum = sm;
-  float* inv = pos_sum + P;
+  float* pos_sum = sm;                       // [2][P], ping-pong over samples
+  float* wpos = pos_sum + 2 * P;             // [P] statistic weight of the position
+  int* gid = reinterpret_cast<int*>(wpos + P);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int c0 = lane * CPL;
+  int G = 0;
+  for (int l = 0; l < L; ++l) G = max(G, group[l] + 1);
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    wpos[p] = wstat[p / 2];
+    gid[p] = group[p / (2 * M)];
+  }
   bool valid[kShRows];
+  int gk[kShRows];
 #pragma unroll
-  for (int k = 0; k < kShRows; ++k) valid[k] = warp + k * nw < P && mask[warp + k * nw] != 0.f;
+  for (int k = 0; k < kShRows; ++k) {
+    const int p = warp + k * nw;
+    valid[k] = p < P && mask[p] != 0.f;
+    gk[k] = p < P ? group[p / (2 * M)] : -1;
+  }
   float bv[CPL];
 #pragma unroll
   for (int i = 0; i < CPL; ++i) bv[i] = (bias != nullptr && warp == 0) ? bias[c0 + i] : 0.f;
-  for (long long b = blockIdx.x; b < B; b += gridDim.x) {
+  __syncthreads();
+  int par = 0;
+  for (long long b = blockIdx.x; b < B; b += gridDim.x, par ^= 1) {
     const T* xb = x + size_t(b) * P * C + c0;
     T* yb = y + size_t(b) * P * C + c0;
+    float* ps = pos_sum + par * P;
     float xr[kShRows][CPL];
 #pragma unroll
     for (int k = 0; k < kShRows; ++k)
@@ -299,30 +329,31 @@ sh_norm_fwd_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* 
         for (int i = 0; i < CPL; ++i) q = fmaf(xr[k][i], xr[k][i], q);
         q = warp_sum(q);
       }
-      if (lane == 0) pos_sum[p] = q;
+      if (lane == 0) ps[p] = q;
     }
+    // one barrier per sample: the other half of pos_sum is only rewritten after the next barrier
     __syncthreads();
-    group_inverse(pos_sum, inv, wstat, group, L, M, C, eps);
-    __syncthreads();
+    float S[kShRows];
+#pragma unroll
+    for (int k = 0; k < kShRows; ++k) S[k] = 0.f;
+    group_sums<kShRows>(ps, wpos, gid, P, G, lane, gk, S);
 #pragma unroll
     for (int k = 0; k < kShRows; ++k) {
       const int p = warp + k * nw;
       if (p >= P) continue;
       float o[CPL];
       if (valid[k]) {
-        const int l = p / (2 * M);
-        const float s = inv[group[l]];
+        const float sc = rsqrtf(S[k] / float(C) + eps);
         float a[CPL];
-        load_chunk<float, CPL>(aw + l * C + c0, a);
+        load_chunk<float, CPL>(aw + (p / (2 * M)) * C + c0, a);
 #pragma unroll
-        for (int i = 0; i < CPL; ++i) o[i] = xr[k][i] * s * a[i] + (p == 0 ? bv[i] : 0.f);
+        for (int i = 0; i < CPL; ++i) o[i] = xr[k][i] * sc * a[i] + (p == 0 ? bv[i] : 0.f);
       } else {
 #pragma unroll
         for (int i = 0; i < CPL; ++i) o[i] = 0.f;
       }
       store_chunk<T, CPL>(yb + size_t(p) * C, o);
     }
-    __syncthreads();   // pos_sum / inv are rewritten by the next sample
   }
 }
 
@@ -336,20 +367,30 @@ sh_norm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __r
   extern __shared__ float sm[];
   const int P = L * M * 2;
   float* daw_s = sm;                       // [L, C] then [C] for the bias
-  float* pos_sum = daw_s + size_t(L + 1) * C;
-  float* pos_dot = pos_sum + P;
-  float* inv = pos_dot + P;
-  float* dotg = inv + L;
+  float* pos_sum = daw_s + size_t(L + 1) * C;   // [2][P]
+  float* pos_dot = pos_sum + 2 * P;             // [2][P]
+  float* wpos = pos_dot + 2 * P;                // [P]
+  float* ones = wpos + P;                       // [P]
+  int* gid = reinterpret_cast<int*>(ones + P);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int c0 = lane * CPL;
   for (int i = threadIdx.x; i < (L + 1) * C; i += blockDim.x) daw_s[i] = 0.f;
+  int G = 0;
+  for (int l = 0; l < L; ++l) G = max(G, group[l] + 1);
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    wpos[p] = wstat[p / 2];
+    ones[p] = 1.f;
+    gid[p] = group[p / (2 * M)];
+  }
   bool valid[kShRows];
+  int gk[kShRows];
   float a[kShRows][CPL], dacc[kShRows][CPL], bacc[CPL];
 #pragma unroll
   for (int k = 0; k < kShRows; ++k) {
     const int p = warp + k * nw;
     valid[k] = p < P && mask[p] != 0.f;
     const int l = p < P ? p / (2 * M) : 0;
+    gk[k] = p < P ? group[l] : -1;
 #pragma unroll
     for (int i = 0; i < CPL; ++i) {
       a[k][i] = aw[l * C + c0 + i];
@@ -359,8 +400,11 @@ sh_norm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __r
 #pragma unroll
   for (int i = 0; i < CPL; ++i) bacc[i] = 0.f;
   __syncthreads();
-  for (long long b = blockIdx.x; b < B; b += gridDim.x) {
+  int par = 0;
+  for (long long b = blockIdx.x; b < B; b += gridDim.x, par ^= 1) {
     const size_t off = size_t(b) * P * C + c0;
+    float* ps = pos_sum + par * P;
+    float* pd = pos_dot + par * P;
     float xr[kShRows][CPL], gr[kShRows][CPL];
 #pragma unroll
     for (int k = 0; k < kShRows; ++k)
@@ -386,22 +430,25 @@ sh_norm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __r
         for (int i = 0; i < CPL; ++i) q = fmaf(xr[k][i], xr[k][i], q);
         q = warp_sum(q);
       }
-      if (lane == 0) pos_sum[p] = q;
+      if (lane == 0) ps[p] = q;
     }
     __syncthreads();
-    group_inverse(pos_sum, inv, wstat, group, L, M, C, eps);
-    __syncthreads();
+    float S[kShRows], D[kShRows];
+#pragma unroll
+    for (int k = 0; k < kShRows; ++k) S[k] = D[k] = 0.f;
+    group_sums<kShRows>(ps, wpos, gid, P, G, lane, gk, S);
 #pragma unroll
     for (int k = 0; k < kShRows; ++k) {
       const int p = warp + k * nw;
       if (p >= P) continue;
       float dot = 0.f;
       if (valid[k]) {
-        const float s = inv[group[p / (2 * M)]];
+        const float sc = rsqrtf(S[k] / float(C) + eps);
+        S[k] = sc;
 #pragma unroll
         for (int i = 0; i < CPL; ++i) {
           const float d = gr[k][i], v = xr[k][i];
-          dacc[k][i] = fmaf(d * v, s, dacc[k][i]);
+          dacc[k][i] = fmaf(d * v, sc, dacc[k][i]);
           if (p == 0) bacc[i] += d;
           const float g = d * a[k][i];
           gr[k][i] = g;
@@ -409,32 +456,22 @@ sh_norm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __r
         }
         dot = warp_sum(dot);
       }
-      if (lane == 0) pos_dot[p] = dot;
+      if (lane == 0) pd[p] = dot;
     }
     __syncthreads();
-    if (threadIdx.x < L) {
-      const int g = threadIdx.x;
-      float D = 0.f;
-      for (int l = 0; l < L; ++l)
-        if (group[l] == g)
-          for (int q = l * M * 2; q < (l + 1) * M * 2; ++q) D += pos_dot[q];
-      dotg[g] = D;
-    }
-    __syncthreads();
+    group_sums<kShRows>(pd, ones, gid, P, G, lane, gk, D);
 #pragma unroll
     for (int k = 0; k < kShRows; ++k) {
       const int p = warp + k * nw;
       if (p >= P) continue;
       float o[CPL];
       if (valid[k]) {
-        const int l = p / (2 * M), m = (p / 2) % M;
-        const int g = group[l];
-        const float s = inv[g];
-        const float kc = wstat[l * M + m] * s * s * s * dotg[g] / float(C);
+        const float sc = S[k];
+        const float kc = wpos[p] * sc * sc * sc * D[k] / float(C);
         float sum = 0.f;
 #pragma unroll
         for (int i = 0; i < CPL; ++i) {
-          o[i] = s * gr[k][i] - kc * xr[k][i];
+          o[i] = sc * gr[k][i] - kc * xr[k][i];
           sum += o[i];
         }
         if (p == 0 && subtract_mean) {
@@ -448,10 +485,8 @@ sh_norm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __r
       }
       store_chunk<T, CPL>(dx + off + size_t(p) * C, o);
     }
-    // pos_sum is next written after two more barriers of the following iteration at the earliest for inv / dotg readers,
-    // but pos_sum / pos_dot themselves are rewritten right away: separate the samples
-    __syncthreads();
   }
+  __syncthreads();
 #pragma unroll
   for (int k = 0; k < kShRows; ++k) {
     const int p = warp + k * nw;
@@ -478,8 +513,8 @@ int reg_threads(int L, int M, int C) {
   if (P <= 16 * kShRows) return 512;
   return 0;
 }
-size_t reg_fwd_smem(int L, int M) { return (size_t(L) * M * 2 + L) * sizeof(float); }
-size_t reg_bwd_smem(int L, int M, int C) { return (size_t(L + 1) * C + size_t(L) * M * 2 * 2 + 2 * L) * sizeof(float); }
+size_t reg_fwd_smem(int L, int M) { return size_t(L) * M * 2 * 4 * sizeof(float); }
+size_t reg_bwd_smem(int L, int M, int C) { return (size_t(L + 1) * C + size_t(L) * M * 2 * 7) * sizeof(float); }
 
 int reg_grid(int threads, int ctas_per_sm, long long B) {
   int dev = 0, sms = 148;

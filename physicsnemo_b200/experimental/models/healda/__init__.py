@@ -1,0 +1,8 @@
+"""HealDA building blocks: packed observation context and the temporal / pixel-observation attention layers."""
+
+from .attention_layers import CrossAttentionModuleBase, PixelCrossAttention, TemporalAttention, mask_causal
+from .obs_context import (ObsContext, PixelGroupMap, build_pixel_group_map, counts_to_cu_seqlens, prepare_obs_context,
+                          sort_and_pack)
+
+__all__ = ["CrossAttentionModuleBase", "ObsContext", "PixelCrossAttention", "PixelGroupMap", "TemporalAttention",
+           "build_pixel_group_map", "counts_to_cu_seqlens", "mask_causal", "prepare_obs_context", "sort_and_pack"]

@@ -172,6 +172,34 @@ def sh_norm_cases(small=False):
                                                B * C * esz * (valid + L * M * 2))
     return out
 
+def pixel_attention_cases(small=False):
+    """Variable-length token-space attention of 49 152 pixels (HEALPix nside 64) over ~20 observation tokens each, 32 heads,
+    token width 64: own kernel against the same operator on dense-padded tensors.  Bytes: tokens once per block of 16 heads,
+    qk read, ctx written (forward); plus dctx read, dqk and fp32 dtok written (backward)."""
+    from . import pixel_attention as PA
+
+    P, H, Dt = (8192 if small else 49152), 32, 64
+    torch.manual_seed(0)
+    counts = torch.randint(0, 41, (P,), device="cuda")
+    cu = torch.zeros(P + 1, dtype=torch.int32, device="cuda")
+    cu[1:] = counts.cumsum(0)
+    N = int(cu[-1])
+    out = {}
+    for dt, tag in ((torch.bfloat16, "bf16"), (torch.float32, "f32")):
+        qk = (torch.randn(P, H, Dt, device="cuda") * 0.3).to(dt).requires_grad_(True)
+        tok = torch.randn(N, Dt, device="cuda").to(dt).requires_grad_(True)
+        esz = qk.element_size()
+        flops = 4.0 * N * H * Dt
+        fwd_bytes = N * Dt * esz * (H // 16) + 2 * P * H * Dt * esz
+        out[f"pixattn_{tag}_fwd"] = (lambda qk=qk, tok=tok: PA.token_attention(qk.detach(), tok.detach(), cu), flops, fwd_bytes)
+        y = PA.token_attention(qk, tok, cu)
+        dy = torch.randn_like(y)
+        out[f"pixattn_{tag}_bwd"] = (lambda y=y, qk=qk, tok=tok, dy=dy: torch.autograd.grad(y, [qk, tok], dy, retain_graph=True), 2.5 * flops,
+                                     fwd_bytes + P * H * Dt * (esz + 4) + N * Dt * 4)
+        out[f"pixattn_{tag}_fwd_dense_padded_torch"] = (lambda qk=qk, tok=tok: PA.token_attention_reference(qk.detach(), tok.detach(), cu),
+                                                        flops, fwd_bytes)
+    return out
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel")
@@ -185,6 +213,9 @@ def main():
         names = list(table)
     elif args.kernel == "groupnorm":
         table = groupnorm_cases()
+        names = list(table)
+    elif args.kernel in ("pixel_attention", "pixel_attention_small"):
+        table = pixel_attention_cases(small=args.kernel == "pixel_attention_small")
         names = list(table)
     elif args.kernel in ("sh_norm", "sh_norm_small"):
         table = sh_norm_cases(small=args.kernel == "sh_norm_small")

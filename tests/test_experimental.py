@@ -619,3 +619,106 @@ def test_strata_chunked_depthwise_conv_matches_plain():
     assert torch.allclose(conv(x), ref, atol=1e-6)
     with pytest.raises(ValueError):
         DepthwiseConv(6, kernel_size=3, groups=2)
+
+
+# ------------------------------------------------------------------------------------------- HealDA attention
+def _naive_pixel_attention(Q, tokens, W_k, W_v, cu, n_kv, scale, B_v=None):
+    P, Hq, dh = Q.shape
+    out = torch.zeros_like(Q)
+    for p in range(P):
+        s, e = int(cu[p]), int(cu[p + 1])
+        if s == e:
+            continue
+        K = (tokens[s:e] @ W_k.t()).view(-1, n_kv, dh)
+        V = tokens[s:e] @ W_v.t()
+        V = (V + B_v if B_v is not None else V).view(-1, n_kv, dh)
+        for h in range(Hq):
+            kv = h // (Hq // n_kv)
+            out[p, h] = torch.softmax(K[:, kv] @ Q[p, h] * scale, 0) @ V[:, kv]
+    return out
+
+
+def test_pixel_attention_matches_per_pixel_softmax():
+    from physicsnemo_b200.ops.pixel_attention import pixel_attention
+
+    torch.manual_seed(0)
+    P, n_kv, g, dh, Dt = 9, 2, 3, 8, 12
+    counts = torch.tensor([3, 0, 5, 1, 0, 2, 4, 0, 7])
+    cu = torch.zeros(P + 1, dtype=torch.int32)
+    cu[1:] = counts.cumsum(0)
+    Q = torch.randn(P, n_kv * g, dh, dtype=torch.float64, requires_grad=True)
+    tok = torch.randn(int(cu[-1]), Dt, dtype=torch.float64, requires_grad=True)
+    Wk, Wv = (torch.randn(n_kv * dh, Dt, dtype=torch.float64, requires_grad=True) for _ in range(2))
+    Bv = torch.randn(n_kv * dh, dtype=torch.float64, requires_grad=True)
+    out = pixel_attention(Q, tok, Wk, Wv, cu, 7, n_kv_heads=n_kv, scale=0.3, B_v=Bv, B_k=torch.randn(n_kv * dh, dtype=torch.float64))
+    ref = _naive_pixel_attention(Q, tok, Wk, Wv, cu, n_kv, 0.3, Bv)
+    assert torch.allclose(out, ref, atol=1e-10)
+    assert float(out[1].abs().max()) == 0.0 and float(out[4].abs().max()) == 0.0          # pixels without observations
+    w = torch.randn_like(out)
+    got = torch.autograd.grad((out * w).sum(), [Q, tok, Wk, Wv, Bv])
+    want = torch.autograd.grad((ref * w).sum(), [Q, tok, Wk, Wv, Bv])
+    for a, b in zip(got, want):
+        assert torch.allclose(a, b, atol=1e-9)
+    # no observation at all
+    none = pixel_attention(Q, tok[:0], Wk, Wv, torch.zeros(P + 1, dtype=torch.int32), 0, n_kv_heads=n_kv, scale=0.3, B_v=Bv)
+    assert none.shape == Q.shape and float(none.abs().max()) == 0.0
+
+
+def test_obs_context_packs_by_pixel():
+    from physicsnemo_b200.experimental.models.healda import build_pixel_group_map, prepare_obs_context
+
+    torch.manual_seed(0)
+    nobs, P = 50, 12
+    flat = torch.randint(0, P, (nobs,))
+    flat[flat == 5] = 6                                             # one empty pixel
+    obs, meta = torch.randn(nobs), torch.randn(nobs, 4)
+    typ, ch, plat = (torch.randint(0, 5, (nobs,)) for _ in range(3))
+    ctx = prepare_obs_context(obs, meta, typ, ch, plat, flat, P)
+    counts = torch.bincount(flat, minlength=P)
+    assert torch.equal(ctx.cu_seqlens_k[1:].long(), counts.cumsum(0)) and ctx.max_seqlen_k == int(counts.max())
+    for p in range(P):
+        s, e = int(ctx.cu_seqlens_k[p]), int(ctx.cu_seqlens_k[p + 1])
+        assert sorted(ctx.obs[s:e].tolist()) == sorted(obs[flat == p].tolist())
+    gm = build_pixel_group_map(ctx.cu_seqlens_k)
+    assert sorted(gm.program_pixels.tolist()) == torch.nonzero(counts > 0).flatten().tolist()
+    assert int(gm.program_ptr[-1]) == gm.program_pixels.numel()
+    empty = prepare_obs_context(obs[:0], meta[:0], typ[:0], ch[:0], plat[:0], flat[:0], P)
+    assert empty.max_seqlen_k == 0 and int(empty.cu_seqlens_k[-1]) == 0 and empty.group_map.program_pixels.numel() == 0
+    assert ctx.to(torch.float64).float_metadata.dtype == torch.float64 and ctx.to(torch.float64).channel.dtype == ch.dtype
+    with pytest.raises(ValueError):
+        prepare_obs_context(obs, meta[:3], typ, ch, plat, flat, P)
+
+
+def test_healda_attention_layers():
+    from physicsnemo_b200.experimental.models.healda import PixelCrossAttention, TemporalAttention, prepare_obs_context
+
+    torch.manual_seed(0)
+    b, t, x, hid, Dt = 2, 2, 3, 16, 8
+    P = b * t * x
+    flat = torch.randint(0, P, (40,))
+    z = torch.zeros(40, dtype=torch.long)
+    ctx = prepare_obs_context(torch.randn(40), torch.randn(40, 2), z, z, z, flat, P)
+    attn = PixelCrossAttention(hid, Dt, n_q_heads=16, n_kv_heads=1, d_head=4, use_proj_bias=True)
+    h = torch.randn(b, t, x, hid, requires_grad=True)
+    tok = torch.randn(40, Dt, requires_grad=True)
+    y = attn(h, tok, ctx.cu_seqlens_k, ctx.max_seqlen_k, group_map=ctx.group_map)
+    assert y.shape == h.shape
+    y.square().sum().backward()
+    assert h.grad is not None and tok.grad is not None and all(p.grad is not None for p in attn.parameters())
+    with pytest.raises(ValueError):
+        attn(h, tok, ctx.cu_seqlens_k[:-1], ctx.max_seqlen_k)
+    with pytest.raises(ValueError):
+        PixelCrossAttention(hid, Dt, n_q_heads=15, n_kv_heads=3, d_head=4)
+
+    # causal softmax attention over time: the output at step q ignores later steps
+    ta = TemporalAttention(hidden_size=hid, num_heads=4, use_rope=False, is_causal=True, linear_attention=False)
+    x1 = torch.randn(1, 4, 3, hid)
+    x2 = x1.clone()
+    x2[:, 3] += 1.0
+    with torch.no_grad():
+        d = (ta(x1) - ta(x2)).abs().amax(dim=(0, 2, 3))
+    assert float(d[:3].max()) < 1e-6 and float(d[3]) > 1e-4
+    with pytest.raises(ValueError):
+        TemporalAttention(hidden_size=hid, num_heads=4)(x1)        # rope tables missing
+    with pytest.raises(ValueError):
+        TemporalAttention(hidden_size=hid, num_heads=4, causal_window=2)

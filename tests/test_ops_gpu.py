@@ -293,3 +293,68 @@ def test_sh_norm_kernel_matches_tensor_ops(kind, lmc, dtype):
         scale = max(1.0, w.abs().max().item())
         assert (g.float() - w).abs().max().item() <= (2e-4 if dtype == torch.float32 else 4e-2) * scale, (kind, g.shape)
     assert device_error() == 0
+
+
+# ---------------------------------------------------------------------------------- pixel / observation attention
+@pytest.mark.gpu
+@pytest.mark.parametrize("cfg", [(300, 16, 64, 40), (257, 40, 32, 100), (64, 32, 128, 9), (50, 16, 96, 0)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_token_attention_kernel(cfg, dtype):
+    """Forward and backward of the variable-length token-space attention kernel against dense-padded fp32 tensor ops."""
+    from physicsnemo_b200.ops import device_error
+    from physicsnemo_b200.ops import pixel_attention as PA
+
+    P, H, Dt, nmax = cfg
+    torch.manual_seed(0)
+    counts = torch.randint(0, nmax + 1, (P,), device="cuda")
+    counts[::7] = 0
+    if nmax:
+        counts[1] = nmax
+    cu = torch.zeros(P + 1, dtype=torch.int32, device="cuda")
+    cu[1:] = counts.cumsum(0)
+    N = max(int(cu[-1]), 1)
+    qk = (torch.randn(P, H, Dt, device="cuda") * 0.4).to(dtype)
+    tok = torch.randn(N, Dt, device="cuda").to(dtype)
+    assert PA.token_attention_supported(qk, tok)
+    qa, ta = qk.clone().requires_grad_(True), tok.clone().requires_grad_(True)
+    qb, tb = qk.float().clone().requires_grad_(True), tok.float().clone().requires_grad_(True)
+    out = PA.token_attention(qa, ta, cu)
+    ref, _ = PA.token_attention_reference(qb, tb, cu)
+    tol = 2e-4 if dtype == torch.float32 else 3e-2
+    assert (out.float() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+    empty = counts == 0
+    assert float(out[empty].float().abs().max()) == 0.0
+    g = torch.randn_like(ref)
+    got = torch.autograd.grad(out, [qa, ta], g.to(dtype))
+    want = torch.autograd.grad(ref, [qb, tb], g.to(dtype).float())
+    for a, b in zip(got, want):
+        assert (a.float() - b).abs().max().item() <= (5e-4 if dtype == torch.float32 else 6e-2) * max(1.0, b.abs().max().item())
+    assert device_error() == 0
+
+
+@pytest.mark.gpu
+def test_pixel_cross_attention_module_on_gpu_matches_cpu():
+    from physicsnemo_b200.experimental.models.healda import PixelCrossAttention, prepare_obs_context
+
+    torch.manual_seed(0)
+    b, t, x, hid, Dt = 2, 2, 50, 64, 32
+    P = b * t * x
+    nobs = 3000
+    flat = torch.randint(0, P, (nobs,))
+    flat[flat % 11 == 0] = 1
+    z = torch.zeros(nobs, dtype=torch.long)
+    cpu = prepare_obs_context(torch.randn(nobs), torch.randn(nobs, 2), z, z, z, flat, P)
+    gpu = prepare_obs_context(torch.randn(nobs).cuda(), torch.randn(nobs, 2).cuda(), z.cuda(), z.cuda(), z.cuda(), flat.cuda(), P)
+    assert torch.equal(cpu.cu_seqlens_k, gpu.cu_seqlens_k.cpu()) and cpu.max_seqlen_k == gpu.max_seqlen_k
+    # the packed order inside a pixel may differ: build the tokens from the pixel index so that both orders agree
+    attn = PixelCrossAttention(hid, Dt, n_q_heads=32, n_kv_heads=2, d_head=16, use_proj_bias=True)
+    h = torch.randn(b, t, x, hid)
+    tok = torch.randn(nobs, Dt)
+    order_cpu = torch.argsort(flat, stable=True)
+    from physicsnemo_b200.ops.pixel_attention import counting_sort_and_pack
+    order_gpu, counts = counting_sort_and_pack(flat.cuda(), P)
+    assert torch.equal(flat.cuda()[order_gpu.long()], flat[order_cpu].cuda()) and torch.equal(counts.cpu(), torch.bincount(flat, minlength=P))
+    y_cpu = attn(h, tok[order_cpu], cpu.cu_seqlens_k, cpu.max_seqlen_k)
+    attn = attn.cuda()
+    y_gpu = attn(h.cuda(), tok.cuda()[order_gpu.long()], gpu.cu_seqlens_k, gpu.max_seqlen_k)
+    assert (y_gpu.cpu() - y_cpu).abs().max().item() < 2e-4
