@@ -722,3 +722,48 @@ def test_healda_attention_layers():
         TemporalAttention(hidden_size=hid, num_heads=4)(x1)        # rope tables missing
     with pytest.raises(ValueError):
         TemporalAttention(hidden_size=hid, num_heads=4, causal_window=2)
+
+
+def test_healda_film_tokenizer_reassociated_first_layer():
+    """Projected-table gathers give the same tokens and gradients as the concatenate-then-multiply form."""
+    from physicsnemo_b200.experimental.models.healda import ObsTokenizerFiLM
+
+    torch.manual_seed(0)
+    tok = ObsTokenizerFiLM(3, 8, platform_embed_dim=2, channel_embed_dim=5).double()
+    n = 64
+    obs, meta = torch.randn(n, dtype=torch.float64), torch.randn(n, 3, dtype=torch.float64)
+    ids = [torch.randint(0, 1024, (n,)) for _ in range(3)]
+    a = tok(obs, meta, *ids)
+    ga = torch.autograd.grad(a.square().sum(), list(tok.parameters()))
+    tok.use_fused_mlp = False
+    b = tok(obs, meta, *ids)
+    gb = torch.autograd.grad(b.square().sum(), list(tok.parameters()))
+    assert a.shape == (n, 8) and torch.allclose(a, b, atol=1e-12)
+    assert all(torch.allclose(u, v, atol=1e-10) for u, v in zip(ga, gb))
+    with pytest.raises(ValueError):
+        tok(obs, meta, ids[0], ids[1])                              # platform ids missing
+    with pytest.raises(ValueError):
+        tok(obs, meta[:, :2], *ids)
+
+
+def test_healda_scatter_aggregator():
+    from physicsnemo_b200.experimental.models.healda import ScatterAggregator, scatter_mean
+
+    torch.manual_seed(0)
+    x = torch.randn(30, 4)
+    bi, px, bk = torch.randint(0, 2, (30,)), torch.randint(0, 5, (30,)), torch.randint(0, 3, (30,))
+    mean, present = scatter_mean(x, torch.stack([bi, px, bk], -1), (2, 5, 3))
+    for b in range(2):
+        for p in range(5):
+            for k in range(3):
+                sel = (bi == b) & (px == p) & (bk == k)
+                assert bool(present[b, p, k]) == bool(sel.any())
+                if sel.any():
+                    assert torch.allclose(mean[b, p, k], x[sel].mean(0), atol=1e-6)
+                else:
+                    assert bool(torch.isnan(mean[b, p, k]).all())
+    agg = ScatterAggregator(4, 6, 3)
+    y = agg(x.requires_grad_(True), bi, px, bk, 2, 5)
+    assert y.shape == (2, 5, 6)
+    y.sum().backward()
+    assert x.grad is not None
