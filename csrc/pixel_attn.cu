@@ -143,11 +143,11 @@ pixel_attn_fwd_kernel(const T* __restrict__ qk, const T* __restrict__ tok, const
   }
 }
 
-template <typename T, int CPL>
+template <typename T, int CPL, bool ATOMIC>
 __global__ void __launch_bounds__(kPaWarps * 32)
 pixel_attn_bwd_kernel(const T* __restrict__ qk, const T* __restrict__ tok, const int* __restrict__ cu, const T* __restrict__ dctx,
                       const float* __restrict__ lse, const float* __restrict__ delta, float* __restrict__ dqk,
-                      float* __restrict__ dtok, int P, int H) {
+                      float* __restrict__ dtok, int P, int H, long long N) {
   constexpr int Dt = 32 * CPL;
   extern __shared__ unsigned char raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -216,7 +216,11 @@ pixel_attn_bwd_kernel(const T* __restrict__ qk, const T* __restrict__ tok, const
           }
         }
 #pragma unroll
-        for (int j = 0; j < CPL; ++j) atomicAdd(&dtok[size_t(start + t0 + t) * Dt + lane + 32 * j], g[j]);
+        for (int j = 0; j < CPL; ++j) {
+          const size_t at = size_t(start + t0 + t) * Dt + lane + 32 * j;
+          if (ATOMIC) atomicAdd(&dtok[at], g[j]);
+          else dtok[size_t(h0 / kPaHeads) * size_t(N) * Dt + at] = g[j];     // one buffer per block of heads
+        }
       }
     }
 #pragma unroll
@@ -267,12 +271,12 @@ int launch_pa_fwd(const void* qk, const void* tok, const int* cu, void* ctx, flo
 
 template <typename T, int CPL>
 int launch_pa_bwd(const void* qk, const void* tok, const int* cu, const void* dctx, const float* lse, const float* delta, float* dqk,
-                  float* dtok, int P, int H, cudaStream_t st) {
+                  float* dtok, int P, int H, long long N, int atomic, cudaStream_t st) {
   const size_t smem = sizeof(PaSmemBwd<CPL>) * kPaWarps;
-  auto k = pixel_attn_bwd_kernel<T, CPL>;
+  auto k = atomic ? pixel_attn_bwd_kernel<T, CPL, true> : pixel_attn_bwd_kernel<T, CPL, false>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return -3;
   k<<<pa_grid((long long)P * ((H + kPaHeads - 1) / kPaHeads)), kPaWarps * 32, smem, st>>>((const T*)qk, (const T*)tok, cu, (const T*)dctx, lse,
-                                                                                          delta, dqk, dtok, P, H);
+                                                                                          delta, dqk, dtok, P, H, N);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -304,12 +308,13 @@ extern "C" int pnm_pixel_attn_fwd(const void* qk, const void* tok, const int* cu
   PNM_PA_DISPATCH(launch_pa_fwd, qk, tok, cu, ctx, lse, P, H, st);
 }
 
-// dqk[P, H, Dt] (fp32, overwritten) and dtok[N, Dt] (fp32, must be zero on entry: accumulated); delta[p, h] = sum_c dctx * ctx.
+// dqk[P, H, Dt] (fp32, overwritten); delta[p, h] = sum_c dctx * ctx.  atomic = 1: dtok[N, Dt] fp32, zero on entry, accumulated with
+// atomics; atomic = 0: dtok[ceil(H / 16), N, Dt] fp32, one slab per block of 16 heads, every element written once (the caller sums).
 extern "C" int pnm_pixel_attn_bwd(const void* qk, const void* tok, const int* cu, const void* dctx, const float* lse, const float* delta,
-                                  float* dqk, float* dtok, int P, int H, int Dt, int dtype, void* stream) {
+                                  float* dqk, float* dtok, int P, int H, int Dt, long long N, int atomic, int dtype, void* stream) {
   if (!qk || !cu || !dctx || !lse || !delta || !dqk || !dtok || P <= 0 || H <= 0) return -1;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  PNM_PA_DISPATCH(launch_pa_bwd, qk, tok, cu, dctx, lse, delta, dqk, dtok, P, H, st);
+  PNM_PA_DISPATCH(launch_pa_bwd, qk, tok, cu, dctx, lse, delta, dqk, dtok, P, H, N, atomic, st);
 }
 
 // counts[bins] += histogram of idx[n] (int32); *bad is set to 1 when an index is outside [0, bins)

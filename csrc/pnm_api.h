@@ -194,7 +194,7 @@ int pnm_sh_norm_bwd(const void* x, const void* dy, void* dx, const float* aw, co
 // Pixel / observation cross attention in token space and the counting sort that packs observations by pixel (see pixel_attn.cu).
 int pnm_pixel_attn_fwd(const void* qk, const void* tok, const int* cu, void* ctx, float* lse, int P, int H, int Dt, int dtype, void* stream);
 int pnm_pixel_attn_bwd(const void* qk, const void* tok, const int* cu, const void* dctx, const float* lse, const float* delta, float* dqk,
-                       float* dtok, int P, int H, int Dt, int dtype, void* stream);
+                       float* dtok, int P, int H, int Dt, long long N, int atomic, int dtype, void* stream);
 int pnm_counting_histogram(const int* idx, int* counts, long long n, int bins, int* bad, void* stream);
 int pnm_counting_scatter(const int* idx, const int* offsets, int* cursor, int* order, long long n, int bins, void* stream);
 

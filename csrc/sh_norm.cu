@@ -256,19 +256,26 @@ __device__ __forceinline__ void store_chunk(T* __restrict__ dst, const float (&s
   *reinterpret_cast<Pack<T, CPL>*>(dst) = p;
 }
 
-// sum over the positions of each group of wpos[p] * val[p], evaluated redundantly by every warp (no broadcast barrier);
-// the result for the group of row k of this warp is returned in out[k]
+// sum over the positions of each group of wpos[p] * val[p], evaluated redundantly by every warp (no broadcast barrier):
+// lane l first sums the 2 M positions of degree l (L <= 32), then the degrees of one group are combined by a warp
+// reduction per row of this warp (a single reduction when there is one group).  out[k] = sum for the group of row k.
 template <int R>
-__device__ __forceinline__ void group_sums(const float* val, const float* wpos, const int* gid, int P, int G, int lane,
+__device__ __forceinline__ void group_sums(const float* val, const float* wpos, const int* gid, int L, int M, int G, int lane,
                                            const int (&gk)[R], float (&out)[R]) {
-  for (int g = 0; g < G; ++g) {
-    float sacc = 0.f;
-    for (int p = lane; p < P; p += 32) sacc += gid[p] == g ? wpos[p] * val[p] : 0.f;
-    sacc = warp_sum(sacc);
-#pragma unroll
-    for (int k = 0; k < R; ++k)
-      if (gk[k] == g) out[k] = sacc;
+  float sl = 0.f;
+  int gl = -2;
+  if (lane < L) {
+    gl = gid[lane * 2 * M];
+    for (int q = lane * 2 * M; q < (lane + 1) * 2 * M; ++q) sl = fmaf(wpos[q], val[q], sl);
   }
+  if (G == 1) {
+    const float tot = warp_sum(sl);
+#pragma unroll
+    for (int k = 0; k < R; ++k) out[k] = tot;
+    return;
+  }
+#pragma unroll
+  for (int k = 0; k < R; ++k) out[k] = warp_sum(gl == gk[k] ? sl : 0.f);
 }
 
 template <typename T, int CPL>
@@ -336,7 +343,7 @@ sh_norm_fwd_reg_kernel(const T* __restrict__ x, T* __restrict__ y, const float* 
     float S[kShRows];
 #pragma unroll
     for (int k = 0; k < kShRows; ++k) S[k] = 0.f;
-    group_sums<kShRows>(ps, wpos, gid, P, G, lane, gk, S);
+    group_sums<kShRows>(ps, wpos, gid, L, M, G, lane, gk, S);
 #pragma unroll
     for (int k = 0; k < kShRows; ++k) {
       const int p = warp + k * nw;
@@ -436,7 +443,7 @@ sh_norm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __r
     float S[kShRows], D[kShRows];
 #pragma unroll
     for (int k = 0; k < kShRows; ++k) S[k] = D[k] = 0.f;
-    group_sums<kShRows>(ps, wpos, gid, P, G, lane, gk, S);
+    group_sums<kShRows>(ps, wpos, gid, L, M, G, lane, gk, S);
 #pragma unroll
     for (int k = 0; k < kShRows; ++k) {
       const int p = warp + k * nw;
@@ -459,7 +466,7 @@ sh_norm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __r
       if (lane == 0) pd[p] = dot;
     }
     __syncthreads();
-    group_sums<kShRows>(pd, ones, gid, P, G, lane, gk, D);
+    group_sums<kShRows>(pd, ones, gid, L, M, G, lane, gk, D);
 #pragma unroll
     for (int k = 0; k < kShRows; ++k) {
       const int p = warp + k * nw;
@@ -508,7 +515,7 @@ sh_norm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __r
 // threads of the register-resident variants (0: not applicable)
 int reg_threads(int L, int M, int C) {
   const int P = L * M * 2;
-  if (C != 32 && C != 64 && C != 128) return 0;
+  if ((C != 32 && C != 64 && C != 128) || L > 32) return 0;
   if (P <= 8 * kShRows) return 256;
   if (P <= 16 * kShRows) return 512;
   return 0;

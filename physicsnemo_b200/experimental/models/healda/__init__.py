@@ -1,10 +1,11 @@
 """HealDA building blocks: packed observation context and the temporal / pixel-observation attention layers."""
 
+from .adaln import AdaLNModulation, gated_residual, modulate
 from .attention_layers import CrossAttentionModuleBase, PixelCrossAttention, TemporalAttention, mask_causal
 from .obs_tokenizer import ObsTokenizerFiLM
 from .scatter_aggregator import ScatterAggregator, scatter_mean
 from .obs_context import (ObsContext, PixelGroupMap, build_pixel_group_map, counts_to_cu_seqlens, prepare_obs_context,
                           sort_and_pack)
 
-__all__ = ["CrossAttentionModuleBase", "ObsContext", "ObsTokenizerFiLM", "ScatterAggregator", "scatter_mean", "PixelCrossAttention", "PixelGroupMap", "TemporalAttention",
+__all__ = ["AdaLNModulation", "gated_residual", "modulate", "CrossAttentionModuleBase", "ObsContext", "ObsTokenizerFiLM", "ScatterAggregator", "scatter_mean", "PixelCrossAttention", "PixelGroupMap", "TemporalAttention",
            "build_pixel_group_map", "counts_to_cu_seqlens", "mask_causal", "prepare_obs_context", "sort_and_pack"]

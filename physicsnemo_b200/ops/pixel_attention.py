@@ -32,7 +32,7 @@ def _lib_pa():
     if not getattr(lib, "_pa_declared", False):
         vp, i, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         lib.pnm_pixel_attn_fwd.argtypes = [vp] * 5 + [i, i, i, i, vp]
-        lib.pnm_pixel_attn_bwd.argtypes = [vp] * 8 + [i, i, i, i, vp]
+        lib.pnm_pixel_attn_bwd.argtypes = [vp] * 8 + [i, i, i, i64, i, i, vp]
         lib.pnm_counting_histogram.argtypes = [vp, vp, i64, i, vp, vp]
         lib.pnm_counting_scatter.argtypes = [vp, vp, vp, vp, i64, i, vp]
         for f in (lib.pnm_pixel_attn_fwd, lib.pnm_pixel_attn_bwd, lib.pnm_counting_histogram, lib.pnm_counting_scatter):
@@ -89,14 +89,23 @@ class _TokenAttention(torch.autograd.Function):
         dout = dout.contiguous().to(qk.dtype)
         delta = (dout.float() * out.float()).sum(-1).contiguous()
         dqk = torch.empty(P, H, Dt, dtype=torch.float32, device=qk.device)
-        dtok = torch.zeros(tokens.shape[0], Dt, dtype=torch.float32, device=qk.device)
+        N, blocks = tokens.shape[0], (H + 15) // 16
+        # every block of 16 heads writes its own slab of token gradients (summed below) unless the slabs would be large
+        atomic = blocks > 1 and blocks * N * Dt * 4 > (2 << 30)
+        dtok = (torch.zeros(N, Dt, dtype=torch.float32, device=qk.device) if atomic
+                else torch.empty(blocks, N, Dt, dtype=torch.float32, device=qk.device))
         err = _lib_pa().pnm_pixel_attn_bwd(qk.data_ptr(), tokens.data_ptr(), cu32.data_ptr(), dout.data_ptr(), lse.data_ptr(),
-                                           delta.data_ptr(), dqk.data_ptr(), dtok.data_ptr(), P, H, Dt, _DT[qk.dtype],
+                                           delta.data_ptr(), dqk.data_ptr(), dtok.data_ptr(), P, H, Dt, N, int(atomic), _DT[qk.dtype],
                                            torch.cuda.current_stream().cuda_stream)
         if err:
             raise RuntimeError(f"pnm_pixel_attn_bwd failed ({err})")
         _g.launch_count += 1
         empty = (cu32[1:] == cu32[:-1])[:, None, None]
+        if not atomic:
+            # rows cu[P]..N (tokens that belong to no pixel) are never written: mask them
+            dtok = dtok[0] if blocks == 1 else dtok.sum(0)
+            if int(cu32[-1]) < N:
+                dtok[int(cu32[-1]):] = 0
         return dqk.masked_fill(empty, 0.0).to(qk.dtype), dtok.to(tokens.dtype), None
 
 

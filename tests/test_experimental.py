@@ -767,3 +767,18 @@ def test_healda_scatter_aggregator():
     assert y.shape == (2, 5, 6)
     y.sum().backward()
     assert x.grad is not None
+
+
+def test_healda_adaln_helpers():
+    from physicsnemo_b200.experimental.models.healda import AdaLNModulation, gated_residual, modulate
+
+    torch.manual_seed(0)
+    x, c = torch.randn(2, 3, 5, 8), torch.randn(2, 6)
+    mod = AdaLNModulation(8, 6, n_blocks=2)
+    parts = mod(c)
+    assert len(parts) == 6 and all(p.shape == (2, 8) and float(p.abs().max()) == 0.0 for p in parts)
+    assert torch.equal(modulate(x, parts[0], parts[1]), x) and torch.equal(gated_residual(x, x, parts[2]), x)
+    shift, scale, gate = torch.randn(2, 8), torch.randn(2, 8), torch.randn(2, 8)
+    assert torch.allclose(modulate(x, shift, scale), x * (1 + scale[:, None, None]) + shift[:, None, None], atol=1e-6)
+    assert torch.allclose(gated_residual(x, 2 * x, gate), x + gate[:, None, None] * 2 * x, atol=1e-6)
+    assert float(AdaLNModulation(8, 6, zero_init=False)(c)[0].abs().max()) > 0
