@@ -41,17 +41,17 @@ template <> __device__ __forceinline__ float pa_t<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 pa_t<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
 
 // per-warp shared memory: token tile [32][Dt + 1], head vectors [16][Dt] (x2 in the backward), weights [32][17] (x2)
-template <int CPL> struct PaSmemFwd {
+template <int CPL> struct alignas(16) PaSmemFwd {
   float tile[kPaTile][32 * CPL + 1];
-  float qk[kPaHeads][32 * CPL];
-  float w[kPaTile][kPaHeads + 1];
+  alignas(16) float qk[kPaHeads][32 * CPL];
+  alignas(16) float w[kPaTile][kPaHeads + 4];
 };
-template <int CPL> struct PaSmemBwd {
+template <int CPL> struct alignas(16) PaSmemBwd {
   float tile[kPaTile][32 * CPL + 1];
-  float qk[kPaHeads][32 * CPL];
-  float dc[kPaHeads][32 * CPL];
-  float w[kPaTile][kPaHeads + 1];
-  float ds[kPaTile][kPaHeads + 1];
+  alignas(16) float qk[kPaHeads][32 * CPL];
+  alignas(16) float dc[kPaHeads][32 * CPL];
+  alignas(16) float w[kPaTile][kPaHeads + 4];
+  alignas(16) float ds[kPaTile][kPaHeads + 4];
 };
 
 template <typename T, int CPL>
@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(kPaWarps * 32)
 pixel_attn_fwd_kernel(const T* __restrict__ qk, const T* __restrict__ tok, const int* __restrict__ cu, T* __restrict__ ctx,
                       float* __restrict__ lse, int P, int H) {
   constexpr int Dt = 32 * CPL;
-  extern __shared__ unsigned char raw[];
+  extern __shared__ __align__(16) unsigned char raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   PaSmemFwd<CPL>& s = reinterpret_cast<PaSmemFwd<CPL>*>(raw)[warp];
   const int blocks = (H + kPaHeads - 1) / kPaHeads;
@@ -98,10 +98,13 @@ pixel_attn_fwd_kernel(const T* __restrict__ qk, const T* __restrict__ tok, const
 #pragma unroll
       for (int h = 0; h < kPaHeads; ++h) sc[h] = 0.f;
       if (lane < nt) {
-        for (int c = 0; c < Dt; ++c) {
-          const float v = s.tile[lane][c];
+        for (int c = 0; c < Dt; c += 4) {
+          const float v0 = s.tile[lane][c], v1 = s.tile[lane][c + 1], v2 = s.tile[lane][c + 2], v3 = s.tile[lane][c + 3];
 #pragma unroll
-          for (int h = 0; h < kPaHeads; ++h) sc[h] = fmaf(v, s.qk[h][c], sc[h]);
+          for (int h = 0; h < kPaHeads; ++h) {
+            const float4 q = *reinterpret_cast<const float4*>(&s.qk[h][c]);
+            sc[h] = fmaf(v0, q.x, fmaf(v1, q.y, fmaf(v2, q.z, fmaf(v3, q.w, sc[h]))));
+          }
         }
       }
 #pragma unroll
@@ -123,10 +126,15 @@ pixel_attn_fwd_kernel(const T* __restrict__ qk, const T* __restrict__ tok, const
 #pragma unroll
         for (int j = 0; j < CPL; ++j) v[j] = s.tile[t][lane + 32 * j];
 #pragma unroll
-        for (int h = 0; h < kPaHeads; ++h) {
-          const float w = s.w[t][h];
+        for (int h4 = 0; h4 < kPaHeads; h4 += 4) {
+          const float4 w = *reinterpret_cast<const float4*>(&s.w[t][h4]);
 #pragma unroll
-          for (int j = 0; j < CPL; ++j) acc[h][j] = fmaf(w, v[j], acc[h][j]);
+          for (int j = 0; j < CPL; ++j) {
+            acc[h4][j] = fmaf(w.x, v[j], acc[h4][j]);
+            acc[h4 + 1][j] = fmaf(w.y, v[j], acc[h4 + 1][j]);
+            acc[h4 + 2][j] = fmaf(w.z, v[j], acc[h4 + 2][j]);
+            acc[h4 + 3][j] = fmaf(w.w, v[j], acc[h4 + 3][j]);
+          }
         }
       }
     }
@@ -149,7 +157,7 @@ pixel_attn_bwd_kernel(const T* __restrict__ qk, const T* __restrict__ tok, const
                       const float* __restrict__ lse, const float* __restrict__ delta, float* __restrict__ dqk,
                       float* __restrict__ dtok, int P, int H, long long N) {
   constexpr int Dt = 32 * CPL;
-  extern __shared__ unsigned char raw[];
+  extern __shared__ __align__(16) unsigned char raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   PaSmemBwd<CPL>& s = reinterpret_cast<PaSmemBwd<CPL>*>(raw)[warp];
   const int blocks = (H + kPaHeads - 1) / kPaHeads;
@@ -183,12 +191,14 @@ pixel_attn_bwd_kernel(const T* __restrict__ qk, const T* __restrict__ tok, const
 #pragma unroll
       for (int h = 0; h < kPaHeads; ++h) sc[h] = dw[h] = 0.f;
       if (lane < nt) {
-        for (int c = 0; c < Dt; ++c) {
-          const float v = s.tile[lane][c];
+        for (int c = 0; c < Dt; c += 4) {
+          const float v0 = s.tile[lane][c], v1 = s.tile[lane][c + 1], v2 = s.tile[lane][c + 2], v3 = s.tile[lane][c + 3];
 #pragma unroll
           for (int h = 0; h < kPaHeads; ++h) {
-            sc[h] = fmaf(v, s.qk[h][c], sc[h]);
-            dw[h] = fmaf(v, s.dc[h][c], dw[h]);
+            const float4 q = *reinterpret_cast<const float4*>(&s.qk[h][c]);
+            const float4 d = *reinterpret_cast<const float4*>(&s.dc[h][c]);
+            sc[h] = fmaf(v0, q.x, fmaf(v1, q.y, fmaf(v2, q.z, fmaf(v3, q.w, sc[h]))));
+            dw[h] = fmaf(v0, d.x, fmaf(v1, d.y, fmaf(v2, d.z, fmaf(v3, d.w, dw[h]))));
           }
         }
       }
@@ -207,13 +217,17 @@ pixel_attn_bwd_kernel(const T* __restrict__ qk, const T* __restrict__ tok, const
           g[j] = 0.f;
         }
 #pragma unroll
-        for (int h = 0; h < kPaHeads; ++h) {
-          const float w = s.w[t][h], d = s.ds[t][h];
+        for (int h4 = 0; h4 < kPaHeads; h4 += 4) {
+          const float4 w4 = *reinterpret_cast<const float4*>(&s.w[t][h4]);
+          const float4 d4 = *reinterpret_cast<const float4*>(&s.ds[t][h4]);
+          const float wv[4] = {w4.x, w4.y, w4.z, w4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
-          for (int j = 0; j < CPL; ++j) {
-            acc[h][j] = fmaf(d, v[j], acc[h][j]);
-            g[j] = fmaf(w, s.dc[h][lane + 32 * j], fmaf(d, s.qk[h][lane + 32 * j], g[j]));
-          }
+          for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) {
+              acc[h4 + u][j] = fmaf(dv[u], v[j], acc[h4 + u][j]);
+              g[j] = fmaf(wv[u], s.dc[h4 + u][lane + 32 * j], fmaf(dv[u], s.qk[h4 + u][lane + 32 * j], g[j]));
+            }
         }
 #pragma unroll
         for (int j = 0; j < CPL; ++j) {

@@ -160,3 +160,26 @@ def _dist_graph(rank, world):
 
 def test_distributed_graph_two_ranks():
     run_ranks(_dist_graph, world=2)
+
+
+def _healda_resharding(rank, world):
+    import torch
+    import torch.distributed as dist
+
+    from physicsnemo_b200.experimental.models.healda.sharding import shard_t, shard_x
+
+    B, T, X, C = 2, 2 * world, 3 * world, 4
+    full = torch.arange(B * T * X * C, dtype=torch.float32).view(B, T, X, C)
+    t_local = full[:, rank * (T // world):(rank + 1) * (T // world)].clone().requires_grad_(True)
+    x_local = shard_x(t_local, dist.group.WORLD)
+    assert torch.equal(x_local, full[:, :, rank * (X // world):(rank + 1) * (X // world)])
+    back = shard_t(x_local, dist.group.WORLD)
+    assert torch.equal(back, t_local)
+    # the all-to-all is differentiable: the gradient of sum(w * round_trip) is w itself
+    w = torch.randn_like(back)
+    (back * w).sum().backward()
+    assert torch.allclose(t_local.grad, w)
+
+
+def test_healda_time_space_resharding():
+    run_ranks(_healda_resharding, world=2)
