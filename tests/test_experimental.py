@@ -782,3 +782,32 @@ def test_healda_adaln_helpers():
     assert torch.allclose(modulate(x, shift, scale), x * (1 + scale[:, None, None]) + shift[:, None, None], atol=1e-6)
     assert torch.allclose(gated_residual(x, 2 * x, gate), x + gate[:, None, None] * 2 * x, atol=1e-6)
     assert float(AdaLNModulation(8, 6, zero_init=False)(c)[0].abs().max()) > 0
+
+
+def test_healda_multi_sensor_embedder():
+    from physicsnemo_b200.experimental.models.healda import MultiSensorObsEmbedder
+
+    torch.manual_seed(0)
+    emb = MultiSensorObsEmbedder(nchannel_per_sensor=[2, 3], nplatform_per_sensor=[1, 2], sensor_names=["amsu", "iasi"], embed_dim=8,
+                                 meta_dim=3, fusion_dim=12, gradient_checkpointing=True)
+    B, T, npix = 2, 2, 6
+    counts = torch.randint(1, 6, (2, B, T))
+    offsets = counts.flatten().cumsum(0).view(2, B, T)
+    n = int(offsets[-1, -1, -1])
+    obs, meta = torch.randn(n, requires_grad=True), torch.randn(n, 3)
+    pix, lc, lp, ty = torch.randint(0, npix, (n,)), torch.randint(0, 2, (n,)), torch.zeros(n, dtype=torch.long), torch.randint(0, 9, (n,))
+    out = emb(obs, meta, pix, lc, lp, ty, offsets, npix)
+    assert out.shape == (B, 12, T, npix)
+    out.square().sum().backward()
+    assert obs.grad is not None and all(p.grad is not None for p in emb.parameters())
+    # an observation only influences its own (batch, time, pixel) site
+    obs2 = obs.detach().clone()
+    obs2[0] += 1.0
+    with torch.no_grad():
+        d = (emb(obs2, meta, pix, lc, lp, ty, offsets, npix) - emb(obs.detach(), meta, pix, lc, lp, ty, offsets, npix)).abs().sum(1)
+    hit = torch.nonzero(d > 1e-7)
+    assert hit.shape[0] == 1 and hit[0].tolist() == [0, 0, int(pix[0])]
+    with pytest.raises(ValueError):
+        emb(obs, meta, pix, lc, lp, ty, offsets[:1], npix)
+    with pytest.raises(ValueError):
+        MultiSensorObsEmbedder([1, 2], [1])
