@@ -466,3 +466,62 @@ def test_local_point_transformer_blocks():
     assert torch.allclose(mlp(x, torch.randn(5)), x + mlp.net(mlp.norm(x)), atol=1e-6)      # zero-initialised modulation
     with pytest.raises(ValueError):
         mlp(x)
+
+
+def test_healpix_pixel_centres_and_patch_tokenizer():
+    """Own HEALPix geometry (equal-area centres, face-local origin at the northern corner) and the GEMM-form patch
+    tokenizer / detokenizer against their strided-convolution definitions."""
+    import math
+
+    from physicsnemo_b200.nn.module.hpx import HEALPixPatchDetokenizer, HEALPixPatchTokenizer, healpix_xy_lonlat
+
+    lon, lat = healpix_xy_lonlat(3)
+    npix = 12 * 4 ** 3
+    assert lon.shape == (npix,) and len({(round(float(a), 6), round(float(b), 6)) for a, b in zip(lon, lat)}) == npix
+    v = torch.stack([torch.cos(torch.deg2rad(lat)) * torch.cos(torch.deg2rad(lon)),
+                     torch.cos(torch.deg2rad(lat)) * torch.sin(torch.deg2rad(lon)), torch.sin(torch.deg2rad(lat))], -1)
+    assert float(v.mean(0).abs().max()) < 1e-12                       # equal-area centres balance
+    z = torch.sin(torch.deg2rad(lat))
+    assert abs(float((z ** 2).mean()) - 1.0 / 3.0) < 2e-3             # <z^2> of a uniform sphere
+    per_face = lat.view(12, -1)
+    assert all(int(per_face[f].argmax()) == 0 for f in range(12))      # pixel 0 of a face is its northern corner
+    assert float(per_face[:4].min()) > 0 and float(per_face[8:].max()) < 0
+    # nearest-neighbour spacing is close to the pixel size everywhere
+    d = torch.cdist(v, v) + 10 * torch.eye(npix, dtype=v.dtype)
+    assert 0.5 < float(d.min(1).values.min()) / math.sqrt(4 * math.pi / npix) < 1.2
+
+    torch.manual_seed(0)
+    tk = HEALPixPatchTokenizer(in_channels=3, hidden_size=16, level_fine=2, level_coarse=1, separate_time_axis=True)
+    x = torch.randn(2, 3, 2, 12 * 16)
+    sod, doy = torch.rand(2, 2) * 86400, torch.rand(2, 2) * 365
+    faces = x.view(2, 3, 2, 12, 4, 4).permute(0, 2, 3, 1, 4, 5).reshape(48, 3, 4, 4)
+    conv = tk.conv(faces).view(2, 2, 12, 16, 2, 2).permute(0, 1, 2, 4, 5, 3).reshape(2, 2, 48, 16)
+    cal = tk.calendar_embed(second_of_day=sod, day_of_year=doy).permute(0, 2, 3, 1)
+    assert torch.allclose(tk(x, sod, doy), conv + cal + tk.pos_embed, atol=1e-5)
+    dt = HEALPixPatchDetokenizer(hidden_size=16, out_channels=5, level_coarse=1, level_fine=2, time_length=2, condition_dim=7)
+    dt.initialize_weights()
+    tok, c = torch.randn(2, 2 * 48, 16), torch.randn(2, 7)
+    normed = dt.norm_out(tok.view(2, 2, 48, 16))
+    ref = dt.conv_t(normed.view(2, 2, 12, 2, 2, 16).permute(0, 1, 2, 5, 3, 4).reshape(48, 16, 2, 2)).view(2, 2, 12, 5, 4, 4)
+    assert torch.allclose(dt(tok, c), ref.permute(0, 3, 1, 2, 4, 5).reshape(2, 5, 2, 192), atol=1e-5)
+
+
+def test_healda_v1_forward_backward():
+    import warnings
+
+    from physicsnemo_b200.experimental.models.healda import HealDA
+
+    torch.manual_seed(0)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        net = HealDA(in_channels=3, out_channels=2, nchannel_per_sensor=[2, 1], nplatform_per_sensor=[1, 1], hidden_size=32, num_layers=2,
+                     num_heads=4, level_in=2, level_model=1, time_length=1, embed_dim=8, meta_dim=3, fusion_dim=8)
+    B, T, npix = 2, 1, 12 * 16
+    offsets = torch.randint(1, 9, (2, B, T)).flatten().cumsum(0).view(2, B, T)
+    n = int(offsets[-1, -1, -1])
+    y = net(torch.randn(B, 3, T, npix), torch.rand(B), torch.randn(n), torch.randn(n, 3), torch.randint(0, npix, (n,)),
+            torch.zeros(n, dtype=torch.long), torch.zeros(n, dtype=torch.long), torch.randint(0, 5, (n,)), offsets,
+            torch.rand(B, T) * 86400, torch.rand(B, T) * 365)
+    assert y.shape == (B, 2, T, npix)
+    y.square().sum().backward()
+    assert sum(p.grad is not None for p in net.parameters()) > 10
