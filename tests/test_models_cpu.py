@@ -525,3 +525,43 @@ def test_healda_v1_forward_backward():
     assert y.shape == (B, 2, T, npix)
     y.square().sum().backward()
     assert sum(p.grad is not None for p in net.parameters()) > 10
+
+
+def test_video_healda_is_causal_in_time_and_reads_observations():
+    from physicsnemo_b200.experimental.models import VideoHealDA
+    from physicsnemo_b200.experimental.models.healda import prepare_obs_context
+
+    torch.manual_seed(0)
+    net = VideoHealDA(in_channels=2, out_channels=3, hidden_size=32, num_layers=2, num_heads=4, level_in=2, level_model=1, time_length=3,
+                      condition_embed_dim=16, noise_channels=16, obs_token_dim=8, obs_meta_dim=5, obs_film_hidden_dim=16,
+                      pixel_attn_n_q_heads=16, pixel_attn_n_kv_heads=1, pixel_attn_head_dim=8, drop_path=0.0).eval()
+    with torch.no_grad():
+        for p in net.parameters():
+            p.add_(0.05 * torch.randn_like(p))                      # leave the zero-initialised gates
+    B, T, npix_c = 2, 3, 48
+    P, n = B * T * npix_c, 400
+    ids = torch.randint(0, 5, (n,))
+    flat = torch.randint(0, P, (n,))
+    obs, meta = torch.randn(n), torch.randn(n, 5)
+    ctx = prepare_obs_context(obs, meta, ids, ids, ids, flat, P)
+    x, t = torch.randn(B, 2, T, 192), torch.rand(B)
+    sod, doy = torch.rand(B, T) * 86400, torch.rand(B, T) * 365
+    with torch.no_grad():
+        y = net(x, t, sod, doy, ctx)
+        assert y.shape == (B, 3, T, 192)
+        x2 = x.clone()
+        x2[:, :, 2] += 1.0                                            # perturb the last frame only
+        d = (net(x2, t, sod, doy, ctx) - y).abs().amax(dim=(0, 1, 3))
+        assert float(d[:2].max()) < 1e-5 and float(d[2]) > 1e-4
+        # observations matter, and only through the site they belong to and later frames of the same sample
+        obs2 = obs.clone()
+        target = int(flat[0])
+        obs2[flat == target] += 3.0
+        ctx2 = prepare_obs_context(obs2, meta, ids, ids, ids, flat, P)
+        dy = (net(x, t, sod, doy, ctx2) - y).abs().amax(dim=(1, 3))    # [B, T]
+        b0, t0 = target // (T * npix_c), (target // npix_c) % T
+        assert float(dy[b0, t0]) > 1e-5 and float(dy[1 - b0].max()) < 1e-6 and float(dy[b0, :t0].max() if t0 else 0.0) < 1e-6
+    with pytest.raises(ValueError):
+        net(x[:, :, :2], t, sod[:, :2], doy[:, :2], ctx)
+    with pytest.raises(ValueError):
+        net(x, t, sod, doy, ctx, class_labels=torch.zeros(B, 2))
