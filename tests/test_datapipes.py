@@ -312,3 +312,72 @@ def test_transolver_datapipe_feeds_the_model():
     assert [e.shape[1] for e in both["embeddings"]] == [200, 200]
     with pytest.raises(ValueError):
         TransolverDataPipe(model_type="surface").process_data({"stl_centers": centers})
+
+
+# -------------------------------------------------------------------------------------------------- CAE dataset
+def _write_cae_samples(root, layout, n=4, nvol=200, nsurf=50):
+    import numpy as np
+
+    rng = np.random.default_rng(0)
+    samples = []
+    for i in range(n):
+        s = {"volume_mesh_centers": rng.normal(size=(nvol, 3)).astype(np.float32), "volume_fields": rng.normal(size=(nvol, 2)).astype(np.float32) + i,
+             "surface_fields": rng.normal(size=(nsurf, 4)).astype(np.float32), "stl_faces": rng.integers(0, 10, size=(30,)).astype(np.int64)}
+        samples.append(s)
+        if layout == "npy":
+            np.save(root / f"s{i}.npy", s, allow_pickle=True)
+        elif layout == "npz":
+            np.savez(root / f"s{i}.npz", **s)
+        else:
+            d = root / f"s{i}"
+            d.mkdir()
+            for k, v in s.items():
+                np.save(d / f"{k}.npy", v)
+    return samples
+
+
+@pytest.mark.parametrize("layout", ["npy", "npz", "npydir"])
+def test_cae_dataset_layouts_and_readahead(tmp_path, layout):
+    import numpy as np
+
+    from physicsnemo_b200.datapipes.cae import CAEDataset, compute_mean_std_min_max
+
+    samples = _write_cae_samples(tmp_path, layout)
+    keys = ["volume_mesh_centers", "volume_fields", "surface_fields", "stl_faces"]
+    ds = CAEDataset(tmp_path, keys, {"air_density": torch.tensor([1.2])}, torch.device("cpu"), preload_depth=2)
+    assert len(ds) == 4
+    got = list(ds)                                            # iteration with read-ahead
+    assert len(got) == 4
+    for g, s in zip(got, samples):
+        assert torch.equal(g["volume_fields"], torch.from_numpy(s["volume_fields"])) and g["stl_faces"].dtype == torch.int32
+        assert torch.equal(g["air_density"], torch.tensor([1.2]))
+    ds.set_indices([3, 1])
+    assert [float(d["volume_fields"][0, 0]) for d in ds] == [float(samples[3]["volume_fields"][0, 0]), float(samples[1]["volume_fields"][0, 0])]
+    ds.preload(2)
+    assert torch.equal(ds[2]["surface_fields"], torch.from_numpy(samples[2]["surface_fields"]))
+    with pytest.raises(IndexError):
+        ds[7]
+    if layout == "npy":
+        with pytest.raises(NotImplementedError):
+            ds.set_volume_sampling_size(10)
+    else:
+        np.random.seed(0)
+        ds.set_volume_sampling_size(64)
+        sub = ds[0]
+        assert sub["volume_fields"].shape == (64, 2) and sub["volume_mesh_centers"].shape == (64, 3) and sub["surface_fields"].shape == (50, 4)
+        # the same rows of all volume arrays, as one cyclic block of the file
+        full_f, full_c = samples[0]["volume_fields"], samples[0]["volume_mesh_centers"]
+        start = int(np.where((full_f == sub["volume_fields"][0].numpy()).all(1))[0][0])
+        rows = (start + np.arange(64)) % 200
+        assert np.array_equal(sub["volume_fields"].numpy(), full_f[rows]) and np.array_equal(sub["volume_mesh_centers"].numpy(), full_c[rows])
+        ds.set_volume_sampling_size(None)
+    ds2 = CAEDataset(tmp_path, ["volume_fields"], None, torch.device("cpu"))
+    mean, std, lo, hi = compute_mean_std_min_max(ds2, ["volume_fields"], max_samples=4)
+    allv = np.concatenate([s["volume_fields"] for s in samples]).astype(np.float64)
+    assert np.allclose(mean["volume_fields"].numpy(), allv.mean(0), atol=1e-6) and np.allclose(std["volume_fields"].numpy(), allv.std(0, ddof=1), atol=1e-6)
+    assert np.allclose(lo["volume_fields"].numpy(), allv.min(0), atol=1e-6) and np.allclose(hi["volume_fields"].numpy(), allv.max(0), atol=1e-6)
+    ds.close(); ds2.close()
+    with pytest.raises(ValueError):
+        CAEDataset(tmp_path, ["not_there"], None, torch.device("cpu"))[0]
+    with pytest.raises(FileNotFoundError):
+        CAEDataset(tmp_path / "missing", keys, None, torch.device("cpu"))
