@@ -1,4 +1,5 @@
+from .geotransolver_guard import GuardedGeoTransolver, attach_ood_guard
 from .gmm import TorchGMM
 from .ood_guard import OODGuard, OODGuardConfig
 
-__all__ = ["OODGuard", "OODGuardConfig", "TorchGMM"]
+__all__ = ["GuardedGeoTransolver", "OODGuard", "OODGuardConfig", "TorchGMM", "attach_ood_guard"]

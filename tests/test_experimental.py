@@ -811,3 +811,31 @@ def test_healda_multi_sensor_embedder():
         emb(obs, meta, pix, lc, lp, ty, offsets[:1], npix)
     with pytest.raises(ValueError):
         MultiSensorObsEmbedder([1, 2], [1])
+
+
+def test_guarded_geotransolver_collects_in_training_and_checks_in_eval():
+    import warnings
+
+    from physicsnemo_b200.experimental.guardrails import GuardedGeoTransolver, OODGuardConfig, attach_ood_guard
+    from physicsnemo_b200.models.geotransolver import GeoTransolver
+
+    torch.manual_seed(0)
+    model = GeoTransolver(functional_dim=3, out_dim=2, geometry_dim=3, global_dim=4, n_layers=1, n_hidden=32, n_head=4, slice_num=8)
+    guard = attach_ood_guard(model, OODGuardConfig(buffer_size=64, knn_k=3, sensitivity=1.5))
+    assert isinstance(guard, GuardedGeoTransolver) and guard.ood_guard.global_min.shape == (4,)
+    x, geo = torch.randn(2, 50, 3), torch.randn(2, 50, 3)
+    glob = torch.rand(2, 1, 4)
+    guard.train()
+    for _ in range(4):
+        y = guard(x, global_embedding=torch.rand(2, 1, 4), geometry=torch.randn(2, 50, 3))
+    assert y.shape == (2, 50, 2) and bool(torch.isfinite(guard.ood_guard.global_min).all())
+    guard.eval()
+    out = guard(x, global_embedding=glob * 0.5 + 0.25, geometry=geo)          # inside the training range
+    assert not bool(guard.ood_guard.last_flags["global"].any())
+    guard(x, global_embedding=glob + 50.0, geometry=geo)                      # far outside: flagged (and logged)
+    assert bool(guard.ood_guard.last_flags["global"].all()) and guard.ood_guard.last_flags["geometry"] is not None
+    assert torch.equal(out, model(x, global_embedding=glob * 0.5 + 0.25, geometry=geo))
+    with pytest.raises(ValueError):
+        guard(x, global_embedding=torch.rand(2, 1, 5), geometry=geo)
+    guard.close()
+    assert guard._geo_hook_handle is None
