@@ -839,3 +839,48 @@ def test_guarded_geotransolver_collects_in_training_and_checks_in_eval():
         guard(x, global_embedding=torch.rand(2, 1, 5), geometry=geo)
     guard.close()
     assert guard._geo_hook_handle is None
+
+
+# ------------------------------------------------------------------------------------------- geometry guardrail
+def _ellipsoid(scale, shift=(0.0, 0.0, 0.0)):
+    from physicsnemo_b200.mesh import Mesh
+    from physicsnemo_b200.mesh.primitives import icosphere
+
+    m = icosphere(subdivisions=2)
+    pts = m.points * torch.tensor(scale, dtype=m.points.dtype) + torch.tensor(shift, dtype=m.points.dtype)
+    return Mesh(points=pts, cells=m.cells)
+
+
+@pytest.mark.parametrize("method", ["gmm", "pce"])
+def test_geometry_guardrail_flags_unusual_shapes(tmp_path, method):
+    from physicsnemo_b200.datapipes.mesh_dataset import save_mesh_npz
+    from physicsnemo_b200.experimental.guardrails.geometry import FeatureSchema, GeometryGuardrail, extract_features
+
+    torch.manual_seed(0)
+    train = [_ellipsoid((1.0 + 0.1 * float(a), 0.6 + 0.05 * float(b), 0.4 + 0.05 * float(c)), (0.02 * float(d), 0.0, 0.0))
+             for a, b, c, d in torch.randn(60, 4)]
+    f = extract_features(train[0])
+    assert f.shape == (FeatureSchema.dim,) == (22,) and abs(f[18] - float(train[0].cell_areas.sum())) < 1e-5
+    assert f[12] > f[13] > f[14] > 0 and f[9] >= f[10] >= f[11] > 0           # extents and principal variances of an ellipsoid
+    guard = GeometryGuardrail(method=method, warn_pct=95.0, reject_pct=99.5, pce_components=3)
+    guard.fit(train)
+    inside = guard.query([_ellipsoid((1.02, 0.61, 0.41))])[0]
+    far = guard.query([_ellipsoid((4.0, 0.2, 3.0), (5.0, 0.0, 0.0))])[0]
+    assert inside["status"] == "OK" and far["status"] == "REJECT" and far["percentile"] == 100.0
+    path = tmp_path / "guard.npz"
+    guard.save(path)
+    again = GeometryGuardrail.load(path)
+    probe = [_ellipsoid((1.3, 0.7, 0.5)), _ellipsoid((1.0, 0.6, 0.4))]
+    assert [r["percentile"] for r in again.query(probe)] == pytest.approx([r["percentile"] for r in guard.query(probe)])
+    d = tmp_path / "meshes"
+    d.mkdir()
+    for i, m in enumerate(probe):
+        save_mesh_npz(m, d / f"m{i}.npz")
+    named = again.query_from_dir(d)
+    assert [r["name"] for r in named] == ["m0", "m1"] and {"percentile", "status"} <= set(named[0])
+    with pytest.raises(ValueError):
+        guard.query([])
+    with pytest.raises(RuntimeError):
+        GeometryGuardrail(method=method).save(tmp_path / "x.npz")
+    with pytest.raises(ValueError):
+        GeometryGuardrail(method="kde")
