@@ -27,7 +27,6 @@ __all__ = ["DiffusionUNet3D"]
 
 @dataclass
 class MetaData(ModelMetaData):
-    name: str = "DiffusionUNet3D"
     amp_gpu: bool = True
     bf16: bool = True
 

@@ -24,7 +24,6 @@ __all__ = ["HealDA"]
 
 @dataclass
 class HealDAMetaData(ModelMetaData):
-    name: str = "HealDA"
     amp_gpu: bool = True
     bf16: bool = True
 

@@ -32,7 +32,6 @@ __all__ = ["VideoDiTBlock", "VideoDiT"]
 
 @dataclass
 class MetaData(ModelMetaData):
-    name: str = "VideoDiT"
     amp_gpu: bool = True
     bf16: bool = True
 

@@ -26,7 +26,6 @@ __all__ = ["VideoHealDA"]
 
 @dataclass
 class VideoHealDAMetaData(ModelMetaData):
-    name: str = "VideoHealDA"
     amp_gpu: bool = True
     bf16: bool = True
 

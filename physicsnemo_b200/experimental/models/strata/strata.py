@@ -27,7 +27,6 @@ __all__ = ["Strata"]
 
 @dataclass
 class StrataMetaData(ModelMetaData):
-    name: str = "Strata"
     amp_gpu: bool = True
     bf16: bool = True
 

@@ -26,7 +26,6 @@ __all__ = ["StrataTransformer3D"]
 
 @dataclass
 class StrataTransformer3DMetaData(ModelMetaData):
-    name: str = "StrataTransformer3D"
     amp_gpu: bool = True
     bf16: bool = True
 

@@ -53,7 +53,7 @@ class _UNetOnGrid(nn.Module):
 
 @dataclass
 class _MetaData(ModelMetaData):
-    name: str = "SpatialBranch"
+    pass
 
 
 class SpatialBranch(Module):

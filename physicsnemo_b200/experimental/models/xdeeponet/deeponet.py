@@ -40,7 +40,7 @@ _DECODERS = ("mlp", "conv", "temporal_projection")
 
 @dataclass
 class _MetaData(ModelMetaData):
-    name: str = "DeepONet"
+    pass
 
 
 class DeepONet(Module):

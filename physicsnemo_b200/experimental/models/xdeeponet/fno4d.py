@@ -21,7 +21,7 @@ __all__ = ["FNO4DWrapper"]
 
 @dataclass
 class _MetaData(ModelMetaData):
-    name: str = "FNO4DWrapper"
+    pass
 
 
 class FNO4DWrapper(Module):

@@ -361,3 +361,62 @@ def test_pixel_cross_attention_module_on_gpu_matches_cpu():
     attn = attn.cuda()
     y_gpu = attn(h.cuda(), tok.cuda()[order_gpu.long()], gpu.cu_seqlens_k, gpu.max_seqlen_k)
     assert (y_gpu.cpu() - y_cpu).abs().max().item() < 2e-4
+
+
+# ------------------------------------------------------------------ experimental models on their own GPU kernels
+@pytest.mark.gpu
+def test_strata_runs_on_neighbourhood_attention_kernels():
+    """Strata with 3-D windows: the CUDA neighbourhood-attention kernels against the tensor-operation path of the same model."""
+    from physicsnemo_b200.experimental.models import Strata
+    from physicsnemo_b200.ops import device_error
+    from physicsnemo_b200.ops import gemm as G
+
+    torch.manual_seed(0)
+    backbone = dict(in_channels=3, out_channels=2, input_shape=(4, 16, 16), patch_size=(2, 2, 2), embed_dim=64, num_heads=4, num_layers=2,
+                    attn_kernel=(1, 3, 3))
+    net = Strata(backbone_config=backbone, embed_dim_pixel=32, num_layers_pixel=2, num_heads_pixel=2, attn_kernel_pixel=3)
+    with torch.no_grad():
+        for p in net.parameters():
+            p.add_(0.05 * torch.randn_like(p))
+    x = torch.randn(2, 3, 4, 16, 16)
+    ref = net(x)
+    net, xg = net.cuda(), x.cuda().requires_grad_(True)
+    before = G.launch_count
+    y = net(xg)
+    assert G.launch_count > before                                   # the window attention ran on the library kernels
+    assert (y.cpu() - ref).abs().max().item() < 2e-3 * max(1.0, ref.abs().max().item())
+    y.square().sum().backward()
+    assert xg.grad is not None and bool(torch.isfinite(xg.grad).all()) and all(p.grad is not None for p in net.parameters())
+    assert device_error() == 0
+
+
+@pytest.mark.gpu
+def test_video_healda_on_gpu_matches_cpu():
+    from physicsnemo_b200.experimental.models import VideoHealDA
+    from physicsnemo_b200.experimental.models.healda import prepare_obs_context
+    from physicsnemo_b200.ops import gemm as G
+
+    torch.manual_seed(0)
+    net = VideoHealDA(in_channels=2, out_channels=3, hidden_size=64, num_layers=2, num_heads=4, level_in=3, level_model=2, time_length=2,
+                      condition_embed_dim=32, noise_channels=32, obs_token_dim=32, obs_meta_dim=5, obs_film_hidden_dim=32,
+                      pixel_attn_n_q_heads=32, pixel_attn_n_kv_heads=2, pixel_attn_head_dim=16, drop_path=0.0).eval()
+    with torch.no_grad():
+        for p in net.parameters():
+            p.add_(0.05 * torch.randn_like(p))
+    B, T, npix_c, npix = 2, 2, 12 * 16, 12 * 64
+    P, n = B * T * npix_c, 5000
+    ids, flat = torch.randint(0, 5, (n,)), torch.randint(0, P, (n,))
+    obs, meta = torch.randn(n), torch.randn(n, 5)
+    x, t = torch.randn(B, 2, T, npix), torch.rand(B)
+    sod, doy = torch.rand(B, T) * 86400, torch.rand(B, T) * 365
+    with torch.no_grad():
+        ref = net(x, t, sod, doy, prepare_obs_context(obs, meta, ids, ids, ids, flat, P))
+    net = net.cuda()
+    ctx = prepare_obs_context(obs.cuda(), meta.cuda(), ids.cuda(), ids.cuda(), ids.cuda(), flat.cuda(), P)
+    before = G.launch_count
+    xg = x.cuda().requires_grad_(True)
+    y = net(xg, t.cuda(), sod.cuda(), doy.cuda(), ctx)
+    assert G.launch_count >= before + 2                              # one pixel-attention launch per block
+    assert (y.detach().cpu() - ref).abs().max().item() < 2e-3 * max(1.0, ref.abs().max().item())
+    y.square().sum().backward()
+    assert bool(torch.isfinite(xg.grad).all()) and all(p.grad is not None for p in net.parameters())
