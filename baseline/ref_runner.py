@@ -54,6 +54,11 @@ class _StubFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
         return mod
 
     def exec_module(self, module):
+        if module.__name__ == "tensordict":
+            # the reference tests ``isinstance(x, TensorDict)`` on plain tensors: the names must be real classes
+            for n in ("TensorDict", "TensorDictBase", "TensorClass", "LazyStackedTensorDict"):
+                setattr(module, n, type(n, (dict,), {}))
+            module.tensorclass = lambda *a, **k: (a[0] if a and isinstance(a[0], type) else (lambda cls: cls))
         if module.__name__ == "jaxtyping":
             # type-annotation helpers used as ``Float[torch.Tensor, "..."]``
             class _Sub:

@@ -1,303 +1,45 @@
-"""Headline benchmark: Transolver training throughput on B200 (samples / s).
+"""Training-throughput benchmark on B200 (samples / s, device-timed, max over ranks).
 
-Config (the reference's "Transolver 3-D point-cloud surrogate"): batch 1 of 1,000,000 surface
-points of a seeded random tri-axial ellipsoid, 6 input channels (xyz + unit normal), 8 blocks,
-hidden 256, 8 heads, 64 slices, MLP ratio 4, 4 output channels, bf16 autocast, Adam.
-With N GPUs the points are sharded N-way (strong scaling: the sample stays 1 M points).
+``python bench.py --gpus N --steps K --warmup W [--config NAME] [--impl reference] [--no-extras]``; for N > 1 launch
+with ``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...``.  Rank 0 prints ONE JSON line.
 
-``python bench.py --gpus N --steps K --warmup W [--impl reference]``; for N > 1 launch with
-``python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...``.
-Rank 0 prints one JSON line.  ``value`` is device-timed (CUDA events, max over ranks) with the
-inputs resident on the GPU; ``e2e.value`` times the same step through the public API including
-the host→device copy of that step's inputs from pinned memory and the device→host read of
-the loss.
+The headline line is the Transolver configuration (1 M points, points sharded over the GPUs).  The other headline
+configurations — ``songunet`` (EDM SongUNet 1024², height-sharded through ShardTensor), ``mgn`` (MeshGraphNet 2 M
+nodes, partitioned graph), ``afno`` (AFNO 720×1440, distributed spectral filter), ``fno`` (FNO-2D on the CPU) — run
+with ``--config NAME``; without ``--config`` they are measured after the headline with a few steps each and reported
+in ``extra_configs`` of the same JSON line (``--no-extras`` skips them).
+
+``value`` is device-timed (CUDA events, max over ranks) with the inputs resident on the GPU; ``e2e.value`` times
+the same step through the public API including the host→device copy of that step's inputs from pinned memory and
+the device→host read of the loss; ``exposed_comm_ms`` is the step time minus the time of the same step with all
+peer traffic switched off.
 """
 from __future__ import annotations
 
 import argparse
+import copy
 import json
 import os
-import statistics
-import subprocess
 import sys
-import threading
 import time
+import traceback
 
 import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-N_POINTS = 1_000_000
-CFG = dict(functional_dim=3, out_dim=4, embedding_dim=3, n_layers=8, n_hidden=256, n_head=8, slice_num=64,
-           mlp_ratio=4, use_te=False)
+EXTRA_ORDER = ("songunet", "afno", "mgn", "fno")
+EXTRA_STEPS = {"songunet": 3, "afno": 4, "mgn": 4, "fno": 100}
 
 
-# ----------------------------------------------------------------------------- data
-def make_ellipsoid_cloud(n: int, seed: int = 0):
-    """Seeded synthetic sample: xyz on a random tri-axial ellipsoid, unit normals, N(0,1) targets."""
-    g = torch.Generator().manual_seed(seed)
-    axes = torch.rand(3, generator=g) * 2.0 + 0.5
-    u = torch.randn(n, 3, generator=g)
-    u = u / u.norm(dim=1, keepdim=True)
-    xyz = u * axes
-    nrm = u / axes
-    nrm = nrm / nrm.norm(dim=1, keepdim=True)
-    tgt = torch.randn(n, 4, generator=g)
-    return xyz.float(), nrm.float(), tgt.float()
+def _run_config(name: str, impl: str, args, rank: int, world: int, dev):
+    import importlib
 
+    if impl == "reference":
+        from baseline import ref_bench
 
-# --------------------------------------------------------------------------- clocks
-class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
-
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int):
-        self.index = index
-        self.proc = None
-        self.lines = []
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._pump, daemon=True)
-            self.thread.start()
-        except Exception:
-            self.proc = None
-
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            pass
-        sm, smax, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 8:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                smax.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[4:8]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
-
-
-# ------------------------------------------------------------------------ timed loop
-def timed_loop(step_fn, steps: int, warmup: int, world: int, dev, e2e: bool, flush_buf=None):
-    import torch.distributed as dist
-
-    for _ in range(warmup):
-        step_fn()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    t0 = time.perf_counter()
-    for i in range(steps):
-        if flush_buf is not None:
-            flush_buf.add_(1.0)  # evict L2 between timed iterations (outside the event pair)
-        ev[i][0].record()
-        step_fn()
-        ev[i][1].record()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
-    ms = sum(a.elapsed_time(b) for a, b in ev)
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return t.item() / steps, wall
-
-
-# ------------------------------------------------------------------------------ ours
-def run_ours(args, rank, world, dev):
-    sys.path.insert(0, ROOT)
-    import physicsnemo_b200  # noqa: F401
-    from physicsnemo_b200 import ops
-    from physicsnemo_b200.models.transolver import Transolver
-    from physicsnemo_b200.optim import FusedAdam
-    from physicsnemo_b200.parallel.point_parallel import PointParallel
-
-    torch.manual_seed(1234)
-    model = Transolver(**CFG).to(dev)
-    pp = PointParallel(model) if world > 1 else None
-    use_graph = not args.no_graph
-    opt = FusedAdam(model.parameters(), lr=1e-3, capturable=use_graph)
-    n_local = N_POINTS // world
-    xyz, nrm, tgt = make_ellipsoid_cloud(N_POINTS, seed=0)
-    sl = slice(rank * n_local, (rank + 1) * n_local if rank < world - 1 else N_POINTS)
-    host = [t[sl].unsqueeze(0).contiguous().pin_memory() for t in (xyz, nrm, tgt)]
-    dev_in = [t.to(dev, non_blocking=True) for t in host]
-    torch.cuda.synchronize()
-    denom = float(N_POINTS * CFG["out_dim"])
-    loss_host = torch.zeros(1, pin_memory=True)
-    state = {"loss": None}
-
-    def train_step(emb, fx, target):
-        opt.zero_grad(set_to_none=True)
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            out = model(fx, embedding=emb)
-        loss = ((out.float() - target) ** 2).sum() / denom
-        loss.backward()
-        if pp is not None:
-            pp.reduce_gradients()
-        opt.step()
-        state["loss"] = loss.detach()
-        return state["loss"]
-
-    flush = torch.empty(256 * 1024 * 1024 // 4, device=dev)  # 256 MB > 126 MB L2
-    sampler = ClockSampler(dev.index or 0)
-    train_step(*dev_in)  # build caches / lazy init before counting launches
-    torch.cuda.synchronize()
-    before = ops.kernel_launches()
-    train_step(*dev_in)
-    torch.cuda.synchronize()
-    launches_per_step = ops.kernel_launches() - before
-
-    if use_graph:
-        # the whole step (forward, backward, peer gradient reduction, Adam) is captured once and replayed: the step's
-        # ~600 kernels then cost one launch on the host, which matters once the per-rank shard is small
-        from physicsnemo_b200.utils.capture import GraphedStep
-
-        graphed = GraphedStep(train_step, dev_in, warmup=1)
-
-        def step_resident():
-            graphed()
-
-        def step_e2e():
-            loss = graphed(*host)                       # H2D of the step's inputs into the captured input tensors
-            loss_host.copy_(loss.reshape(1), non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-    else:
-        def step_resident():
-            train_step(*dev_in)
-
-        def step_e2e():
-            emb, fx, target = (t.to(dev, non_blocking=True) for t in host)
-            train_step(emb, fx, target)
-            loss_host.copy_(state["loss"].reshape(1), non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-    if rank == 0:
-        sampler.start()
-    ms, wall = timed_loop(step_resident, args.steps, max(args.warmup - 2, 0), world, dev, False, flush)
-    clocks = sampler.stop() if rank == 0 else None
-    ms_e2e, _ = timed_loop(step_e2e, args.steps, 1, world, dev, True, flush)
-    err = ops.device_error()
-    h2d = sum(t.numel() * t.element_size() for t in host)
-    if world > 1:                                   # every rank holds the squared error of its shard: sum for the report
-        import torch.distributed as dist
-
-        total = loss_host.to(dev)
-        dist.all_reduce(total)
-        loss_host.copy_(total)
-    if rank == 0:
-        value = 1000.0 / ms
-        print(json.dumps({
-            "metric": "train samples/sec (device-timed, max over ranks)", "value": value, "unit": "samples/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic (seeded ellipsoid point cloud, random-init weights)",
-            "config": {"model": "Transolver 8 blocks / hidden 256 / 8 heads / 64 slices / mlp_ratio 4",
-                       "global_batch": 1, "seq_len": N_POINTS, "parallelism": f"points sharded x{world}",
-                       "optimizer": "Adam (fused)", "cuda_graph": use_graph, "l2": "256 MB buffer rewritten between timed steps; "
-                       "per-step working set is tens of GB (>> 126 MB L2)"},
-            "clocks": clocks,
-            "e2e": {"value": 1000.0 / ms_e2e, "unit": "samples/s", "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
-            "gpu_launches": launches_per_step * args.steps, "gpu_launches_per_step": launches_per_step,
-            "device_error_word": err, "loss": float(loss_host.item()), "impl": "physicsnemo_b200",
-            "wall_s_timed_region": wall,
-        }))
-
-
-# ------------------------------------------------------------------------- reference
-def run_reference(args, rank, world, dev):
-    try:
-        from baseline.ref_runner import import_reference
-
-        pn = import_reference(os.path.join(ROOT, "baseline", "_ref"))
-        from physicsnemo.models.transolver import Transolver as RefTransolver  # type: ignore
-    except Exception as exc:  # noqa: BLE001
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": f"reference import failed: {type(exc).__name__}: {exc}"[:300]}))
-        return
-    if world > 1:
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable":
-                              "reference ShardTensor path needs its optional native deps (warp, tensordict) which "
-                              "are not installed; only the 1-GPU reference arm runs"}))
-        return
-    torch.manual_seed(1234)
-    model = RefTransolver(**CFG).to(dev)
-    opt = torch.optim.Adam(model.parameters(), lr=1e-3, fused=True)
-    xyz, nrm, tgt = make_ellipsoid_cloud(N_POINTS, seed=0)
-    host = [t.unsqueeze(0).contiguous().pin_memory() for t in (xyz, nrm, tgt)]
-    dev_in = [t.to(dev, non_blocking=True) for t in host]
-    denom = float(N_POINTS * CFG["out_dim"])
-    loss_host = torch.zeros(1, pin_memory=True)
-    state = {}
-
-    def train_step(emb, fx, target):
-        opt.zero_grad(set_to_none=True)
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            out = model(fx, embedding=emb)
-        loss = ((out.float() - target) ** 2).sum() / denom
-        loss.backward()
-        opt.step()
-        state["loss"] = loss.detach()
-
-    def step_resident():
-        train_step(*dev_in)
-
-    def step_e2e():
-        emb, fx, target = (t.to(dev, non_blocking=True) for t in host)
-        train_step(emb, fx, target)
-        loss_host.copy_(state["loss"].reshape(1), non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    flush = torch.empty(256 * 1024 * 1024 // 4, device=dev)
-    sampler = ClockSampler(dev.index or 0)
-    try:
-        step_resident()
-        torch.cuda.synchronize()
-        sampler.start()
-        ms, wall = timed_loop(step_resident, args.steps, max(args.warmup - 1, 0), world, dev, False, flush)
-        clocks = sampler.stop()
-        ms_e2e, _ = timed_loop(step_e2e, args.steps, 1, world, dev, True, flush)
-    except Exception as exc:  # noqa: BLE001
-        sampler.stop()
-        print(json.dumps({"impl": "reference", "unavailable": f"reference run failed: {type(exc).__name__}: {exc}"[:300]}))
-        return
-    h2d = sum(t.numel() * t.element_size() for t in host)
-    print(json.dumps({
-        "metric": "train samples/sec (device-timed, max over ranks)", "value": 1000.0 / ms, "unit": "samples/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic (seeded ellipsoid point cloud, random-init weights)",
-        "config": {"model": "Transolver 8 blocks / hidden 256 / 8 heads / 64 slices / mlp_ratio 4 (use_te=False)",
-                   "global_batch": 1, "seq_len": N_POINTS, "parallelism": "single GPU", "optimizer": "Adam (fused)"},
-        "clocks": clocks,
-        "e2e": {"value": 1000.0 / ms_e2e, "unit": "samples/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": 4},
-        "impl": "reference", "loss": float(loss_host.item()), "wall_s_timed_region": wall,
-    }))
+        return ref_bench.run(name, args, rank, world, dev, ROOT)
+    mod = importlib.import_module(f"physicsnemo_b200.benchmarks.{name}")
+    return mod.run(args, rank, world, dev)
 
 
 def main():
@@ -306,6 +48,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default=None, choices=["transolver", "songunet", "mgn", "afno", "fno"])
+    ap.add_argument("--no-extras", action="store_true", help="only the headline configuration")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -313,6 +57,12 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    sys.path.insert(0, ROOT)
+    name = args.config or "transolver"
+    if name == "fno":                                     # the CPU plumbing configuration needs no device
+        if rank == 0:
+            print(json.dumps(_run_config("fno", args.impl, args, 0, 1, torch.device("cpu"))))
+        return
     if not torch.cuda.is_available():
         if rank == 0:
             print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device"}))
@@ -324,16 +74,39 @@ def main():
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+    t_start = time.time()
     try:
-        if args.impl == "reference":
-            run_reference(args, rank, world, dev)
-        else:
-            run_ours(args, rank, world, dev)
+        line = _run_config(name, args.impl, args, rank, world, dev)
+        extras = {}
+        if args.config is None and not args.no_extras and isinstance(line, dict) and "unavailable" not in line:
+            budget_s = float(os.environ.get("PNM_BENCH_EXTRAS_SECONDS", "420"))
+            for extra in EXTRA_ORDER:
+                if time.time() - t_start > budget_s:
+                    extras[extra] = {"skipped": "time budget of the extra configurations used up"}
+                    continue
+                eargs = copy.copy(args)
+                eargs.steps = EXTRA_STEPS[extra]
+                try:
+                    torch.cuda.empty_cache()
+                    if extra == "fno":
+                        res = _run_config("fno", args.impl, eargs, 0, 1, torch.device("cpu")) if rank == 0 else None
+                    else:
+                        res = _run_config(extra, args.impl, eargs, rank, world, dev)
+                    extras[extra] = res
+                except Exception as exc:  # noqa: BLE001  (an extra configuration must never take the headline down)
+                    extras[extra] = {"error": f"{type(exc).__name__}: {exc}"[:400],
+                                     "where": traceback.format_exc().strip().splitlines()[-3:]}
+            line["extra_configs"] = extras
+        if rank == 0:
+            print(json.dumps(line))
     finally:
         if world > 1:
             import torch.distributed as dist
 
-            dist.destroy_process_group()
+            try:
+                dist.destroy_process_group()
+            except Exception:  # noqa: BLE001
+                pass
 
 
 if __name__ == "__main__":

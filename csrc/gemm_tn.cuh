@@ -17,6 +17,7 @@
 #pragma once
 #include "common.cuh"
 #include "tmap.cuh"
+#include "pnm_internal.h"
 
 namespace pnm {
 
@@ -44,6 +45,7 @@ struct GemmArgs {
   const uint32_t* flag_up;
   const uint32_t* flag_down;
   uint32_t halo_epoch;
+  unsigned long long halo_budget_ns;  // budget of the waits on the neighbours' flags
 };
 
 constexpr int kConvTileH = 8;
@@ -68,18 +70,22 @@ __device__ __forceinline__ void conv_tile_origin(const GemmArgs& g, int mt, int&
 }
 
 // Bounded wait (one thread) until a flag written by another GPU reaches `epoch`.
-__device__ __forceinline__ bool wait_remote_flag(const uint32_t* flag, uint32_t epoch, volatile int* abort_flag, int* err_word) {
+// The rows that the flag announces were written by another GPU with generic-proxy stores and are read here by TMA
+// (async proxy): after the acquire succeeds a proxy fence orders the two before the first bulk copy is issued.
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+__device__ __forceinline__ bool wait_remote_flag(const uint32_t* flag, uint32_t epoch, volatile int* abort_flag, int* err_word,
+                                                 unsigned long long budget_ns) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-  if (int32_t(v - epoch) >= 0) return true;
+  if (int32_t(v - epoch) >= 0) { fence_proxy_async_global(); return true; }
   const unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-    if (int32_t(v - epoch) >= 0) return true;
+    if (int32_t(v - epoch) >= 0) { fence_proxy_async_global(); return true; }
     if ((++spins & 0xffu) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+      if (globaltimer_ns() - t0 > budget_ns) {
         atomicCAS(err_word, 0, ERR_WAIT_PEER);
         *abort_flag = 1;
         __threadfence_block();
@@ -193,7 +199,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (g.halo && ys < 0 && g.has_up) {
               // box rows -1 .. 6: row -1 is the upper neighbour's bottom row, rows 0 .. 6 are local
               if (!up_ready) {
-                if (!wait_remote_flag(g.flag_up, g.halo_epoch, abort_flag, g.err)) { ok = false; break; }
+                if (!wait_remote_flag(g.flag_up, g.halo_epoch, abort_flag, g.err, g.halo_budget_ns)) { ok = false; break; }
                 up_ready = true;
               }
               tma_load_4d(sa, &tmA3, &full[s], c0, xs, 0, n);
@@ -201,7 +207,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             } else if (g.halo && ys + kConvTileH > g.img_h && g.has_down) {
               // box rows H-7 .. H: rows H-7 .. H-1 are local, row H is the lower neighbour's top row
               if (!down_ready) {
-                if (!wait_remote_flag(g.flag_down, g.halo_epoch, abort_flag, g.err)) { ok = false; break; }
+                if (!wait_remote_flag(g.flag_down, g.halo_epoch, abort_flag, g.err, g.halo_budget_ns)) { ok = false; break; }
                 down_ready = true;
               }
               tma_load_4d(sa, &tmA2, &full[s], c0, xs, ys, n);
@@ -458,6 +464,7 @@ struct GemmCall {
   const void* up_rows = nullptr; const void* down_rows = nullptr;
   const uint32_t* flag_up = nullptr; const uint32_t* flag_down = nullptr;
   uint32_t halo_epoch = 0;
+  double halo_budget_s = 0.0;   // 0 = the library default
 };
 
 template <int BN, int MODE>
@@ -496,18 +503,18 @@ inline int launch_gemm_tn(const GemmCall& c, int num_sms, int* err_word, cudaStr
   g.tiles_x = g.tiles_y = 0;
   g.halo = c.conv ? c.halo : 0; g.has_up = c.up_rows != nullptr; g.has_down = c.down_rows != nullptr; g.img_n = c.img_n;
   g.flag_up = c.flag_up; g.flag_down = c.flag_down; g.halo_epoch = c.halo_epoch;
+  g.halo_budget_ns = c.halo_budget_s > 0.0 ? (unsigned long long)(c.halo_budget_s * 1e9) : kWaitBudgetNs;
   if (c.conv) {
     g.tiles_x = (c.img_w + kConvTileW - 1) / kConvTileW;
     g.tiles_y = (c.img_h + kConvTileH - 1) / kConvTileH;
     g.num_m_tiles = c.img_n * g.tiles_x * g.tiles_y;
     g.M = g.num_m_tiles * kBM;            // every row of a tile is "in range"; the copy engine clips at image edges
   }
-  static bool attr_set = false;
-  if (!attr_set) {
+  static unsigned long long attr_mask = 0;   // one bit per device: the attribute belongs to the device's context
+  if (first_use_on_device(attr_mask)) {
     if (cudaFuncSetAttribute(gemm_tn_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
         cudaSuccess)
       return -16;
-    attr_set = true;
   }
   int tiles = g.num_m_tiles * g.num_n_tiles;
   int cap = c.max_ctas > 0 ? c.max_ctas : num_sms;

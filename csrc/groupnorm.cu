@@ -8,6 +8,12 @@
 //             2) per-batch channel sums, per-group sums A = sum gamma dz, B = sum gamma dz xhat, dgamma / dbeta
 //             3) dx = rstd * (gamma dz - A/n - xhat B/n)
 //
+// Row-sharded images (channels-last only): the "_sh" entry points take the moments over the whole image.  The
+// statistics kernel's last block folds this rank's partials into (B, G) sums, leaves them in the rank's symmetric
+// buffer and raises one flag per peer; the normalising kernel waits (bounded) for every rank's flag in its prologue
+// and adds the P short vectors with direct peer loads, so no collective call sits between the two passes.  The
+// backward does the same with the two per-group sums of the input gradient.
+//
 // Every access is a 16-byte vector of 8 (bf16) or 4 (fp32) elements.  In the channels-last kernels a thread owns a
 // fixed vector of channels and walks down the pixels, so gamma / beta / scale / shift live in registers.
 #include <cuda_bf16.h>
@@ -15,6 +21,7 @@
 #include <stdint.h>
 
 #include "pnm_api.h"
+#include "pnm_internal.h"
 
 namespace pnm {
 
@@ -46,8 +53,8 @@ template <> struct Vec<float> {
   }
 };
 
-__device__ __forceinline__ float silu_f(float z) { return z / (1.f + __expf(-z)); }
-__device__ __forceinline__ float silu_grad(float z) {
+__device__ __forceinline__ float gn_silu(float z) { return z / (1.f + __expf(-z)); }
+__device__ __forceinline__ float gn_silu_grad(float z) {
   const float s = 1.f / (1.f + __expf(-z));
   return s * (1.f + z * (1.f - s));
 }
@@ -118,7 +125,7 @@ __global__ void __launch_bounds__(256) gn_apply_cf(const T* __restrict__ x, cons
   for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
     Vec<T>::load(xi + v * V, f);
 #pragma unroll
-    for (int i = 0; i < V; ++i) { const float z = f[i] * scale + shift; f[i] = kSilu ? silu_f(z) : z; }
+    for (int i = 0; i < V; ++i) { const float z = f[i] * scale + shift; f[i] = kSilu ? gn_silu(z) : z; }
     Vec<T>::store(yo + v * V, f);
   }
 }
@@ -142,7 +149,7 @@ __global__ void __launch_bounds__(256) gn_bwd_stats_cf(const T* __restrict__ x, 
 #pragma unroll
     for (int i = 0; i < V; ++i) {
       const float xh = (f[i] - mu) * rs;
-      const float dz = kSilu ? e[i] * silu_grad(xh * ga + be) : e[i];
+      const float dz = kSilu ? e[i] * gn_silu_grad(xh * ga + be) : e[i];
       a += dz * xh; d += dz;
     }
   }
@@ -172,7 +179,7 @@ __global__ void __launch_bounds__(256) gn_bwd_apply_cf(const T* __restrict__ x, 
 #pragma unroll
     for (int i = 0; i < V; ++i) {
       const float xh = (f[i] - mu) * rs;
-      const float dz = kSilu ? e[i] * silu_grad(xh * ga + be) : e[i];
+      const float dz = kSilu ? e[i] * gn_silu_grad(xh * ga + be) : e[i];
       f[i] = rs * (ga * dz - A - xh * Bq);
     }
     Vec<T>::store(o + v * V, f);
@@ -240,6 +247,135 @@ __device__ __forceinline__ void all_group_moments(const float2* __restrict__ par
   __syncthreads();
 }
 
+// ---- sharded statistics ---------------------------------------------------------------------------------------------
+// grid (B): sums[b][g] = (sum x, sum x^2) of this rank's rows, written to stage A of the symmetric buffer at float
+// offset 2 * (b * G + g); the block that finishes last raises the flags.
+__global__ void __launch_bounds__(256) gn_publish_moments(const float2* __restrict__ partial, GNShape sh, PeerArgs peer,
+                                                           unsigned int* counter) {
+  const uint32_t epoch = peer_epoch(peer);
+  float2* dst = reinterpret_cast<float2*>(peer_data(peer, peer.rank, epoch & 1, 0));
+  const int b = blockIdx.x;
+  for (int g = threadIdx.x; g < sh.G; g += blockDim.x) {
+    float a = 0.f, q = 0.f;
+    for (int s = 0; s < sh.S; ++s)
+      for (int k = 0; k < sh.cpg; ++k) {
+        const float2 p = partial[((long long)b * sh.S + s) * sh.C + g * sh.cpg + k];
+        a += p.x; q += p.y;
+      }
+    dst[b * sh.G + g] = make_float2(a, q);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(counter, 1u) == gridDim.x - 1) {
+    *counter = 0;
+    peer_small_publish(peer, epoch);
+  }
+}
+
+// grid (B): like gn_bwd_reduce, then publishes group_ab[b][g] = (sum gamma dz, sum gamma dz xhat) of this rank's rows
+__global__ void __launch_bounds__(256) gn_publish_ab(const float2* __restrict__ group_ab, GNShape sh, PeerArgs peer,
+                                                      unsigned int* counter) {
+  const uint32_t epoch = peer_epoch(peer);
+  float2* dst = reinterpret_cast<float2*>(peer_data(peer, peer.rank, epoch & 1, 0));
+  const int b = blockIdx.x;
+  for (int g = threadIdx.x; g < sh.G; g += blockDim.x) dst[b * sh.G + g] = group_ab[b * sh.G + g];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(counter, 1u) == gridDim.x - 1) {
+    *counter = 0;
+    peer_small_publish(peer, epoch);
+  }
+}
+
+template <typename T, bool kSilu>
+__global__ void __launch_bounds__(256) gn_apply_cl_sh(const T* __restrict__ x, const float* __restrict__ gamma,
+                                                       const float* __restrict__ beta, T* __restrict__ y,
+                                                       float* __restrict__ mean_out, float* __restrict__ rstd_out, GNShape sh,
+                                                       float eps, float count_global, PeerArgs peer, int* err) {
+  constexpr int V = Vec<T>::N;
+  extern __shared__ float smem[];
+  float2* mom = reinterpret_cast<float2*>(smem);         // [G]
+  __shared__ int sh_ok;
+  const int s = blockIdx.x, b = blockIdx.y;
+  const uint32_t epoch = peer_epoch(peer);
+  const bool ok = peer_small_wait(peer, epoch, err, &sh_ok);
+  for (int g = threadIdx.x; g < sh.G; g += blockDim.x) {
+    float a = __int_as_float(0x7fc00000), q = a;         // a time-out shows as NaN in the output
+    if (ok) {
+      a = peer_small_sum(peer, epoch, 2 * (b * sh.G + g));
+      q = peer_small_sum(peer, epoch, 2 * (b * sh.G + g) + 1);
+    }
+    const float mean = a / count_global;
+    mom[g] = make_float2(mean, rsqrtf(fmaxf(q / count_global - mean * mean, 0.f) + eps));
+  }
+  __syncthreads();
+  if (s == 0)
+    for (int g = threadIdx.x; g < sh.G; g += blockDim.x) { mean_out[b * sh.G + g] = mom[g].x; rstd_out[b * sh.G + g] = mom[g].y; }
+  const CLThread t = cl_thread<V>(sh, s);
+  if (!t.active) return;
+  float scale[V], shift[V], f[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    const int c = t.c0 + i;
+    const float2 m = mom[c / sh.cpg];
+    scale[i] = m.y * gamma[c];
+    shift[i] = beta[c] - m.x * scale[i];
+  }
+  const long long off = (long long)b * sh.HW * sh.C + t.c0;
+  for (long long p = t.p0 + t.lane_pix; p < t.p1; p += t.ppi) {
+    Vec<T>::load(x + off + p * sh.C, f);
+#pragma unroll
+    for (int i = 0; i < V; ++i) { const float z = f[i] * scale[i] + shift[i]; f[i] = kSilu ? gn_silu(z) : z; }
+    Vec<T>::store(y + off + p * sh.C, f);
+  }
+}
+
+template <typename T, bool kSilu>
+__global__ void __launch_bounds__(256) gn_bwd_apply_cl_sh(const T* __restrict__ x, const T* __restrict__ dy,
+                                                           const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                           const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                           T* __restrict__ dx, GNShape sh, float count_global, PeerArgs peer,
+                                                           int* err) {
+  constexpr int V = Vec<T>::N;
+  extern __shared__ float smem[];
+  float2* gab = reinterpret_cast<float2*>(smem);         // [G]
+  __shared__ int sh_ok;
+  const int s = blockIdx.x, b = blockIdx.y;
+  const uint32_t epoch = peer_epoch(peer);
+  const bool ok = peer_small_wait(peer, epoch, err, &sh_ok);
+  for (int g = threadIdx.x; g < sh.G; g += blockDim.x) {
+    float a = __int_as_float(0x7fc00000), q = a;
+    if (ok) {
+      a = peer_small_sum(peer, epoch, 2 * (b * sh.G + g));
+      q = peer_small_sum(peer, epoch, 2 * (b * sh.G + g) + 1);
+    }
+    gab[g] = make_float2(a, q);
+  }
+  __syncthreads();
+  const CLThread t = cl_thread<V>(sh, s);
+  if (!t.active) return;
+  const float inv_n = 1.f / count_global;
+  float mu[V], rs[V], ga[V], be[V], A[V], Bq[V], f[V], e[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    const int c = t.c0 + i, g = c / sh.cpg;
+    mu[i] = mean[b * sh.G + g]; rs[i] = rstd[b * sh.G + g]; ga[i] = gamma[c]; be[i] = beta[c];
+    A[i] = gab[g].x * inv_n; Bq[i] = gab[g].y * inv_n;
+  }
+  const long long off = (long long)b * sh.HW * sh.C + t.c0;
+  for (long long p = t.p0 + t.lane_pix; p < t.p1; p += t.ppi) {
+    Vec<T>::load(x + off + p * sh.C, f);
+    Vec<T>::load(dy + off + p * sh.C, e);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const float xh = (f[i] - mu[i]) * rs[i];
+      const float dz = kSilu ? e[i] * gn_silu_grad(xh * ga[i] + be[i]) : e[i];
+      f[i] = rs[i] * (ga[i] * dz - A[i] - xh * Bq[i]);
+    }
+    Vec<T>::store(dx + off + p * sh.C, f);
+  }
+}
+
 template <typename T, bool kSilu>
 __global__ void __launch_bounds__(256) gn_apply_cl(const T* __restrict__ x, const float2* __restrict__ partial,
                                                     const float* __restrict__ gamma, const float* __restrict__ beta,
@@ -266,7 +402,7 @@ __global__ void __launch_bounds__(256) gn_apply_cl(const T* __restrict__ x, cons
   for (long long p = t.p0 + t.lane_pix; p < t.p1; p += t.ppi) {
     Vec<T>::load(x + off + p * sh.C, f);
 #pragma unroll
-    for (int i = 0; i < V; ++i) { const float z = f[i] * scale[i] + shift[i]; f[i] = kSilu ? silu_f(z) : z; }
+    for (int i = 0; i < V; ++i) { const float z = f[i] * scale[i] + shift[i]; f[i] = kSilu ? gn_silu(z) : z; }
     Vec<T>::store(y + off + p * sh.C, f);
   }
 }
@@ -297,7 +433,7 @@ __global__ void __launch_bounds__(256) gn_bwd_stats_cl(const T* __restrict__ x, 
 #pragma unroll
       for (int i = 0; i < V; ++i) {
         const float xh = (f[i] - mu[i]) * rs[i];
-        const float dz = kSilu ? e[i] * silu_grad(xh * ga[i] + be[i]) : e[i];
+        const float dz = kSilu ? e[i] * gn_silu_grad(xh * ga[i] + be[i]) : e[i];
         a[i] += dz * xh; d[i] += dz;
       }
     }
@@ -334,7 +470,7 @@ __global__ void __launch_bounds__(256) gn_bwd_apply_cl(const T* __restrict__ x, 
 #pragma unroll
     for (int i = 0; i < V; ++i) {
       const float xh = (f[i] - mu[i]) * rs[i];
-      const float dz = kSilu ? e[i] * silu_grad(xh * ga[i] + be[i]) : e[i];
+      const float dz = kSilu ? e[i] * gn_silu_grad(xh * ga[i] + be[i]) : e[i];
       f[i] = rs[i] * (ga[i] * dz - A[i] - xh * Bq[i]);
     }
     Vec<T>::store(dx + off + p * sh.C, f);
@@ -411,6 +547,41 @@ int gn_backward(const void* x, const void* dy, const float* gamma, const float* 
   return (int)cudaGetLastError();
 }
 
+template <typename T>
+int gn_forward_sh(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd, float* scratch,
+                  GNShape sh, int act, float eps, float count_global, const PeerArgs& peer, unsigned int* counter, int* err,
+                  cudaStream_t st) {
+  float2* partial = reinterpret_cast<float2*>(scratch);
+  const T* xi = static_cast<const T*>(x);
+  T* yo = static_cast<T*>(y);
+  const dim3 grid(sh.S, sh.B);
+  gn_stats_cl<T><<<grid, 256, 2 * sh.C * sizeof(float), st>>>(xi, partial, sh);
+  gn_publish_moments<<<sh.B, 256, 0, st>>>(partial, sh, peer, counter);
+  if (act) gn_apply_cl_sh<T, true><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, gamma, beta, yo, mean, rstd, sh, eps, count_global, peer, err);
+  else gn_apply_cl_sh<T, false><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, gamma, beta, yo, mean, rstd, sh, eps, count_global, peer, err);
+  return (int)cudaGetLastError();
+}
+
+template <typename T>
+int gn_backward_sh(const void* x, const void* dy, const float* gamma, const float* beta, const float* mean, const float* rstd,
+                   void* dx, float* dgamma, float* dbeta, float* scratch, GNShape sh, int act, float count_global,
+                   const PeerArgs& peer, unsigned int* counter, int* err, cudaStream_t st) {
+  float2* pc = reinterpret_cast<float2*>(scratch);
+  float2* ab = pc + (long long)sh.B * sh.S * sh.C;
+  const T* xi = static_cast<const T*>(x);
+  const T* di = static_cast<const T*>(dy);
+  T* o = static_cast<T*>(dx);
+  const dim3 grid(sh.S, sh.B);
+  const size_t sm = 2 * sh.C * sizeof(float);
+  if (act) gn_bwd_stats_cl<T, true><<<grid, 256, sm, st>>>(xi, di, gamma, beta, mean, rstd, pc, sh);
+  else gn_bwd_stats_cl<T, false><<<grid, 256, sm, st>>>(xi, di, gamma, beta, mean, rstd, pc, sh);
+  gn_bwd_reduce<<<sh.B, 256, 2 * sh.G * sizeof(float), st>>>(pc, gamma, ab, dgamma, dbeta, sh);
+  gn_publish_ab<<<sh.B, 256, 0, st>>>(ab, sh, peer, counter);
+  if (act) gn_bwd_apply_cl_sh<T, true><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, di, gamma, beta, mean, rstd, o, sh, count_global, peer, err);
+  else gn_bwd_apply_cl_sh<T, false><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, di, gamma, beta, mean, rstd, o, sh, count_global, peer, err);
+  return (int)cudaGetLastError();
+}
+
 static bool gn_supported(const GNShape& sh, int layout, int dtype) {
   const int V = dtype == 0 ? 8 : 4;
   if (sh.B <= 0 || sh.C <= 0 || sh.G <= 0 || sh.C % sh.G || sh.S <= 0 || sh.HW <= 0) return false;
@@ -444,6 +615,40 @@ int pnm_groupnorm_bwd(const void* x, const void* dy, const float* gamma, const f
   cudaStream_t st = (cudaStream_t)stream;
   return dtype == 0 ? pnm::gn_backward<__nv_bfloat16>(x, dy, gamma, beta, mean, rstd, dx, dgamma, dbeta, scratch, sh, layout, act, st)
                     : pnm::gn_backward<float>(x, dy, gamma, beta, mean, rstd, dx, dgamma, dbeta, scratch, sh, layout, act, st);
+}
+
+// Row-sharded variants (channels-last, layout 1): the moments span all ranks' rows.  hw_global = pixels per image over the
+// whole (unsharded) extent; `counter` is one device uint32 that is zero before the first call (the kernels reset it).  2 * B * G floats must fit into one stage of the symmetric buffer.  Peer arguments as in
+// pnm_peer_allreduce.
+int pnm_groupnorm_fwd_sharded(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
+                              float* scratch, int B, int C, long long HW, long long hw_global, int G, int S, int dtype, int act,
+                              float eps, const void* const* bases, int rank, int world, unsigned int epoch,
+                              long long capacity_floats, double budget_s, const void* epoch_base, void* counter, void* stream) {
+  pnm::GNShape sh{B, C, G, G > 0 ? C / G : 0, S, HW};
+  if (!pnm::gn_supported(sh, 1, dtype) || world < 1 || world > pnm::kPeerMaxRanks || 2LL * B * G > capacity_floats || !counter) return -1;
+  int* err = pnm::error_word_ptr();
+  if (!err) return -2;
+  const pnm::PeerArgs p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, budget_s, epoch_base);
+  const float cnt = (float)sh.cpg * (float)hw_global;
+  cudaStream_t st = (cudaStream_t)stream;
+  return dtype == 0 ? pnm::gn_forward_sh<__nv_bfloat16>(x, gamma, beta, y, mean, rstd, scratch, sh, act, eps, cnt, p, (unsigned int*)counter, err, st)
+                    : pnm::gn_forward_sh<float>(x, gamma, beta, y, mean, rstd, scratch, sh, act, eps, cnt, p, (unsigned int*)counter, err, st);
+}
+
+int pnm_groupnorm_bwd_sharded(const void* x, const void* dy, const float* gamma, const float* beta, const float* mean,
+                              const float* rstd, void* dx, float* dgamma, float* dbeta, float* scratch, int B, int C,
+                              long long HW, long long hw_global, int G, int S, int dtype, int act, const void* const* bases,
+                              int rank, int world, unsigned int epoch, long long capacity_floats, double budget_s,
+                              const void* epoch_base, void* counter, void* stream) {
+  pnm::GNShape sh{B, C, G, G > 0 ? C / G : 0, S, HW};
+  if (!pnm::gn_supported(sh, 1, dtype) || world < 1 || world > pnm::kPeerMaxRanks || 2LL * B * G > capacity_floats || !counter) return -1;
+  int* err = pnm::error_word_ptr();
+  if (!err) return -2;
+  const pnm::PeerArgs p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, budget_s, epoch_base);
+  const float cnt = (float)sh.cpg * (float)hw_global;
+  cudaStream_t st = (cudaStream_t)stream;
+  return dtype == 0 ? pnm::gn_backward_sh<__nv_bfloat16>(x, dy, gamma, beta, mean, rstd, dx, dgamma, dbeta, scratch, sh, act, cnt, p, (unsigned int*)counter, err, st)
+                    : pnm::gn_backward_sh<float>(x, dy, gamma, beta, mean, rstd, dx, dgamma, dbeta, scratch, sh, act, cnt, p, (unsigned int*)counter, err, st);
 }
 
 }  // extern "C"

@@ -38,9 +38,29 @@ int pnm_segment_sum(const void* in, int ldi, const int* perm, const int* offsets
                     int C, int accumulate, int mode, void* stream);
 
 // In-kernel all-reduce (sum, fp32) over peer-mapped symmetric buffers; see peer.cuh for the layout.
+// bases: host array of `world` peer-mapped base pointers; epoch_base: optional device uint32 added to epoch (lets a
+// captured CUDA graph advance the call numbers on replay); max_ctas: 0 = default.  On a time-out the outputs are NaN.
 int pnm_peer_allreduce(const float* in, float* out, long long n, float scale, int two_shot, const void* const* bases,
                        int rank, int world, unsigned int epoch, long long capacity_floats, double budget_s,
-                       void* stream, const void* epoch_base);  // epoch_base: optional device uint32 added to epoch
+                       void* stream, const void* epoch_base, int max_ctas);
+// Gradient-bucket all-reduce, bf16 on the wire: io[i] <- sum over ranks of bf16(scale * io[i]) (fp32 accumulation), in place;
+// cast, reduce-scatter and all-gather are one kernel.  n % 8 == 0, io 32-byte aligned, n <= 2 * capacity_floats.
+int pnm_peer_allreduce_bf16(float* io, long long n, float scale, const void* const* bases, int rank, int world,
+                            unsigned int epoch, long long capacity_floats, double budget_s, void* stream,
+                            const void* epoch_base, int max_ctas);
+// Building blocks of staged transfers.  pnm_peer_signal raises this rank's flag of call `epoch` on every peer (data written
+// before it on the stream is then readable); pnm_peer_pull copies `bytes` from a peer-mapped address into local memory after
+// rank flag_from's flag arrived (flag_from < 0: no wait); pnm_peer_pull_reduce sums block [rank * block, (rank + 1) * block) of
+// every rank's stage A into dst after all flags arrived (reduce-scatter in the pull model).
+int pnm_peer_signal(const void* const* bases, int rank, int world, unsigned int epoch, long long capacity_floats,
+                    void* stream, const void* epoch_base);
+int pnm_peer_pull(const void* src, void* dst, long long bytes, int flag_from, const void* const* bases, int rank, int world,
+                  unsigned int epoch, long long capacity_floats, double budget_s, void* stream, const void* epoch_base,
+                  int max_ctas);
+int pnm_peer_pull_reduce(float* dst, long long block, const void* const* bases, int rank, int world, unsigned int epoch,
+                         long long capacity_floats, double budget_s, void* stream, const void* epoch_base, int max_ctas);
+// Enqueue a copy of the device error word into pinned host memory (non-blocking poll of the bounded waits).
+int pnm_error_copy_async(int* pinned_host, void* stream);
 int pnm_peer_flag_bytes();
 int pnm_peer_wait_probe(const void* flag, unsigned int expect, double budget_s, int* status_out, void* stream);
 
@@ -136,6 +156,18 @@ int pnm_groupnorm_bwd(const void* x, const void* dy, const float* gamma, const f
                       const float* rstd, void* dx, float* dgamma, float* dbeta, float* scratch, int B, int C, long long HW,
                       int G, int S, int layout, int dtype, int act, void* stream);
 
+// GroupNorm over a row-sharded channels-last image: moments over all ranks' rows, summed inside the normalising kernel by
+// peer loads (see groupnorm.cu).  hw_global = pixels per image of the whole image; counter = zeroed device uint32.
+int pnm_groupnorm_fwd_sharded(const void* x, const float* gamma, const float* beta, void* y, float* mean, float* rstd,
+                              float* scratch, int B, int C, long long HW, long long hw_global, int G, int S, int dtype, int act,
+                              float eps, const void* const* bases, int rank, int world, unsigned int epoch,
+                              long long capacity_floats, double budget_s, const void* epoch_base, void* counter, void* stream);
+int pnm_groupnorm_bwd_sharded(const void* x, const void* dy, const float* gamma, const float* beta, const float* mean,
+                              const float* rstd, void* dx, float* dgamma, float* dbeta, float* scratch, int B, int C,
+                              long long HW, long long hw_global, int G, int S, int dtype, int act, const void* const* bases,
+                              int rank, int world, unsigned int epoch, long long capacity_floats, double budget_s,
+                              const void* epoch_base, void* counter, void* stream);
+
 // out = silu^(order)(x) * g (g may be null), order 0..4; dtype 0 bf16, 1 fp32; pointers 16-byte aligned (-2 otherwise).
 int pnm_silu_derivative(const void* x, const void* g, void* out, long long n, int order, int dtype, void* stream);
 
@@ -161,7 +193,14 @@ int pnm_halo_publish(const void* x, void* top, void* bottom, int n, int h, int w
                      unsigned int epoch, void* counter, void* stream);
 int pnm_conv2d_nhwc_halo(const void* x, const void* weight, void* y, int n, int h, int w, int cin, int cout, const float* bias,
                          int act, const void* up_rows, const void* down_rows, const void* flag_up, const void* flag_down,
-                         unsigned int epoch, int bn, int max_ctas, void* stream);
+                         unsigned int epoch, int bn, int max_ctas, void* stream, double budget_s);  // budget_s 0 = default (2 s)
+// Weight (and bias) gradient of the 3 x 3 stride-1 "same" convolution as a split reduction over pixel patches on the tensor
+// cores (gemm_nt.cuh, conv mode): out [cout, 9 * cin] fp32 tap-major and colsum [cout] are ACCUMULATED into.  up_rows /
+// down_rows: input rows just above / below a height slab (local copies or peer-mapped); with flag_up / flag_down the kernel
+// waits until they carry `epoch`.  cin % 64 == 0, cout % 8 == 0, cout >= 64; with halo rows h % 4 == 0.
+int pnm_conv2d_wgrad_nhwc(const void* dy, const void* x, float* out, float* colsum, int n, int h, int w, int cin, int cout,
+                          const void* up_rows, const void* down_rows, const void* flag_up, const void* flag_down,
+                          unsigned int epoch, double budget_s, int max_ctas, void* stream);
 
 // out[BH,Sq,D] = softmax(scale * q k^T (+ causal mask, top-left aligned)) v for contiguous bf16 q [BH,Sq,D], k [BH,Skv,D] and
 // v [BH,Skv,D] (v_transposed = 0) or v^T [BH,D,ldv] with ldv >= Skv, ldv % 8 == 0 (v_transposed = 1); D in {64, 128};

@@ -12,21 +12,50 @@
 #include "flash_attn.cuh"
 #include "pnm_api.h"
 
+#include "pnm_internal.h"
+
 __device__ int pnm_error_word = 0;
 
 namespace {
-int g_num_sms = 0;
-int* g_err_ptr = nullptr;
+// Per-device state: a process may drive more than one GPU, and both the SM count and the address of the error word
+// belong to the device that is current when a function is called.
+struct DevState { int num_sms = 0; int* err_ptr = nullptr; };
+DevState g_dev[pnm::kMaxDevices];
+thread_local int g_num_sms = 0;
+thread_local int* g_err_ptr = nullptr;
 
 int ensure_init() {
-  if (g_num_sms > 0 && g_err_ptr) return 0;
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
-  if (cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
-  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&g_err_ptr), pnm_error_word) != cudaSuccess) return -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= pnm::kMaxDevices) return -1;
+  DevState& d = g_dev[dev];
+  if (d.num_sms <= 0 || !d.err_ptr) {
+    if (cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&d.err_ptr), pnm_error_word) != cudaSuccess) return -1;
+  }
+  g_num_sms = d.num_sms;
+  g_err_ptr = d.err_ptr;
   return 0;
 }
 }  // namespace
+
+namespace pnm {
+int current_device() {
+  int dev = 0;
+  return cudaGetDevice(&dev) == cudaSuccess ? dev : 0;
+}
+int* error_word_ptr() { return ensure_init() ? nullptr : g_err_ptr; }
+int num_sms() { return ensure_init() ? 0 : g_num_sms; }
+PeerArgs make_peer_args(const void* const* bases, int rank, int world, unsigned int epoch, long long capacity_floats,
+                        double budget_s, const void* epoch_base) {
+  PeerArgs p;
+  for (int r = 0; r < kPeerMaxRanks; ++r)
+    p.base[r] = r < world ? reinterpret_cast<uint8_t*>(const_cast<void*>(bases[r])) : nullptr;
+  p.rank = rank; p.world = world; p.epoch = epoch; p.capacity = capacity_floats;
+  p.epoch_base = reinterpret_cast<const uint32_t*>(epoch_base);
+  p.budget_ns = (unsigned long long)(budget_s * 1e9);
+  return p;
+}
+}  // namespace pnm
 
 extern "C" {
 
@@ -142,7 +171,7 @@ int pnm_halo_publish(const void* x, void* top, void* bottom, int n, int h, int w
 // peer-mapped, null at the outer edges) once flag_up / flag_down (local memory) carry `epoch`.  3 x 3 only, h % 8 == 0.
 int pnm_conv2d_nhwc_halo(const void* x, const void* weight, void* y, int n, int h, int w, int cin, int cout, const float* bias,
                          int act, const void* up_rows, const void* down_rows, const void* flag_up, const void* flag_down,
-                         unsigned int epoch, int bn, int max_ctas, void* stream) {
+                         unsigned int epoch, int bn, int max_ctas, void* stream, double budget_s) {
   if (ensure_init()) return -1;
   if (n <= 0 || h <= 0 || w <= 0 || (cin % 64) || (cout % 8) || (h % 8)) return -3;
   pnm::GemmCall c{};
@@ -152,7 +181,7 @@ int pnm_conv2d_nhwc_halo(const void* x, const void* weight, void* y, int n, int 
   c.conv = 1; c.img_n = n; c.img_h = h; c.img_w = w; c.cin = cin; c.ksize = 3;
   c.halo = 1; c.up_rows = up_rows; c.down_rows = down_rows;
   c.flag_up = reinterpret_cast<const uint32_t*>(flag_up); c.flag_down = reinterpret_cast<const uint32_t*>(flag_down);
-  c.halo_epoch = epoch;
+  c.halo_epoch = epoch; c.halo_budget_s = budget_s;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (bn == 0) bn = (cout > 128) ? 256 : 128;
   if (bn == 256) return pnm::launch_gemm_tn<256, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
@@ -169,6 +198,28 @@ int pnm_gemm_nt(const void* A, int lda, const void* B, int ldb, float* out, int 
   c.M = M; c.Na = Na; c.Nb = Nb; c.max_ctas = max_ctas;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (Nb > 128) return pnm::launch_gemm_nt<256>(c, g_num_sms, g_err_ptr, st);
+  return pnm::launch_gemm_nt<128>(c, g_num_sms, g_err_ptr, st);
+}
+
+// dW[cout, 9 * cin] (fp32, tap-major, accumulated into `out`) = sum over pixels of dy[pixel, :]^T x[pixel + tap, :] for a 3 x 3
+// stride-1 "same" convolution of channels-last bf16 tensors; colsum (optional) accumulates the bias gradient.
+// up_rows / down_rows (optional, [n, 1, w, cin]): the input rows just above / below a height slab; when flag_up /
+// flag_down are given the kernel first waits (bounded) until they carry `epoch`.  cin % 64 == 0, cout >= 64, cout % 8 == 0.
+int pnm_conv2d_wgrad_nhwc(const void* dy, const void* x, float* out, float* colsum, int n, int h, int w, int cin, int cout,
+                          const void* up_rows, const void* down_rows, const void* flag_up, const void* flag_down,
+                          unsigned int epoch, double budget_s, int max_ctas, void* stream) {
+  if (ensure_init()) return -1;
+  if (n <= 0 || h <= 0 || w <= 0 || (cin % 64) || (cout % 8) || cout < 64) return -3;
+  pnm::NtCall c{};
+  c.A = dy; c.lda = cout; c.B = x; c.ldb = cin; c.out = out; c.ldo = 9 * cin; c.colsum = colsum;
+  c.M = 0; c.Na = cout; c.Nb = 9 * cin; c.max_ctas = max_ctas;
+  c.conv = 1; c.img_n = n; c.img_h = h; c.img_w = w; c.cin = cin;
+  c.halo = (up_rows || down_rows) ? 1 : 0;
+  c.up_rows = up_rows; c.down_rows = down_rows;
+  c.flag_up = reinterpret_cast<const uint32_t*>(flag_up); c.flag_down = reinterpret_cast<const uint32_t*>(flag_down);
+  c.halo_epoch = epoch; c.halo_budget_s = budget_s;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if ((9 * cin) % 256 == 0) return pnm::launch_gemm_nt<256>(c, g_num_sms, g_err_ptr, st);
   return pnm::launch_gemm_nt<128>(c, g_num_sms, g_err_ptr, st);
 }
 
@@ -208,15 +259,65 @@ int pnm_segment_sum(const void* in, int ldi, const int* perm, const int* offsets
 // bases: host array of `world` peer-mapped pointers to the symmetric buffers (this rank's own included).
 int pnm_peer_allreduce(const float* in, float* out, long long n, float scale, int two_shot, const void* const* bases,
                        int rank, int world, unsigned int epoch, long long capacity_floats, double budget_s,
-                       void* stream, const void* epoch_base) {
+                       void* stream, const void* epoch_base, int max_ctas) {
   if (ensure_init()) return -1;
-  pnm::PeerArgs p;
-  if (world > pnm::kPeerMaxRanks) return -50;
-  for (int r = 0; r < world; ++r) p.base[r] = reinterpret_cast<uint8_t*>(const_cast<void*>(bases[r]));
-  p.rank = rank; p.world = world; p.epoch = epoch; p.capacity = capacity_floats;
-  p.epoch_base = reinterpret_cast<const uint32_t*>(epoch_base);
-  p.budget_ns = (unsigned long long)(budget_s * 1e9);
-  return pnm::launch_peer_allreduce(in, out, n, scale, two_shot, p, g_err_ptr, reinterpret_cast<cudaStream_t>(stream));
+  if (world > pnm::kPeerMaxRanks || world < 1) return -50;
+  const pnm::PeerArgs p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, budget_s, epoch_base);
+  return pnm::launch_peer_allreduce(in, out, n, scale, two_shot, p, max_ctas, g_err_ptr, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int pnm_peer_allreduce_bf16(float* io, long long n, float scale, const void* const* bases, int rank, int world,
+                            unsigned int epoch, long long capacity_floats, double budget_s, void* stream,
+                            const void* epoch_base, int max_ctas) {
+  if (ensure_init()) return -1;
+  if (world > pnm::kPeerMaxRanks || world < 1) return -50;
+  const pnm::PeerArgs p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, budget_s, epoch_base);
+  return pnm::launch_peer_allreduce_bf16(io, n, scale, p, max_ctas, g_err_ptr, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int pnm_peer_signal(const void* const* bases, int rank, int world, unsigned int epoch, long long capacity_floats,
+                    void* stream, const void* epoch_base) {
+  if (ensure_init()) return -1;
+  if (world > pnm::kPeerMaxRanks || world < 1) return -50;
+  const pnm::PeerArgs p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, 1.0, epoch_base);
+  pnm::peer_signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -51;
+}
+
+int pnm_peer_pull(const void* src, void* dst, long long bytes, int flag_from, const void* const* bases, int rank, int world,
+                  unsigned int epoch, long long capacity_floats, double budget_s, void* stream, const void* epoch_base,
+                  int max_ctas) {
+  if (ensure_init()) return -1;
+  if (world > pnm::kPeerMaxRanks || world < 1) return -50;
+  if (bytes <= 0) return 0;
+  if ((bytes & 15) || ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)) return -53;
+  const pnm::PeerArgs p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, budget_s, epoch_base);
+  const long long nvec = bytes / 16;
+  int grid = (int)std::min<long long>((nvec + 2047) / 2048, max_ctas > 0 ? max_ctas : 64);
+  if (grid < 1) grid = 1;
+  pnm::peer_pull_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), nvec, p, flag_from, g_err_ptr);
+  return cudaGetLastError() == cudaSuccess ? 0 : -51;
+}
+
+int pnm_peer_pull_reduce(float* dst, long long block, const void* const* bases, int rank, int world, unsigned int epoch,
+                         long long capacity_floats, double budget_s, void* stream, const void* epoch_base, int max_ctas) {
+  if (ensure_init()) return -1;
+  if (world > pnm::kPeerMaxRanks || world < 1) return -50;
+  if (block <= 0) return 0;
+  if ((block & 3) || block * world > capacity_floats || (reinterpret_cast<uintptr_t>(dst) & 15)) return -53;
+  const pnm::PeerArgs p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, budget_s, epoch_base);
+  int grid = (int)std::min<long long>((block / 4 + 511) / 512, max_ctas > 0 ? max_ctas : 96);
+  if (grid < 1) grid = 1;
+  pnm::peer_pull_reduce_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(dst, block, p, g_err_ptr);
+  return cudaGetLastError() == cudaSuccess ? 0 : -51;
+}
+
+// Non-blocking read of the error word: enqueues a copy into pinned host memory on `stream`.
+int pnm_error_copy_async(int* pinned_host, void* stream) {
+  if (ensure_init()) return -1;
+  return cudaMemcpyAsync(pinned_host, g_err_ptr, sizeof(int), cudaMemcpyDeviceToHost, reinterpret_cast<cudaStream_t>(stream)) ==
+                 cudaSuccess ? 0 : -1;
 }
 
 int pnm_peer_flag_bytes() { return pnm::kFlagBytes; }

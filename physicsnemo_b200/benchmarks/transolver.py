@@ -1,0 +1,138 @@
+"""Transolver on a 1 M-point cloud, bf16, points sharded across the GPUs (headline configuration 3).
+
+Config: batch 1 of 1,000,000 surface points of a seeded random tri-axial ellipsoid, 6 input channels (xyz + unit
+normal), 8 blocks, hidden 256, 8 heads, 64 slices, MLP ratio 4, 4 output channels, bf16 autocast, Adam.  With N GPUs
+the points are sharded N-way (strong scaling: the sample stays 1 M points).  The whole step (forward, backward, the
+peer-memory reductions, Adam) is captured into one CUDA graph and replayed.
+"""
+from __future__ import annotations
+
+import torch
+
+from .common import ClockSampler, base_line, flush_buffer, timed_loop
+
+N_POINTS = 1_000_000
+CFG = dict(functional_dim=3, out_dim=4, embedding_dim=3, n_layers=8, n_hidden=256, n_head=8, slice_num=64,
+           mlp_ratio=4, use_te=False)
+DESC = "Transolver 8 blocks / hidden 256 / 8 heads / 64 slices / mlp_ratio 4"
+
+
+def make_ellipsoid_cloud(n: int, seed: int = 0):
+    """Seeded synthetic sample: xyz on a random tri-axial ellipsoid, unit normals, N(0,1) targets."""
+    g = torch.Generator().manual_seed(seed)
+    axes = torch.rand(3, generator=g) * 2.0 + 0.5
+    u = torch.randn(n, 3, generator=g)
+    u = u / u.norm(dim=1, keepdim=True)
+    xyz = u * axes
+    nrm = u / axes
+    nrm = nrm / nrm.norm(dim=1, keepdim=True)
+    tgt = torch.randn(n, 4, generator=g)
+    return xyz.float(), nrm.float(), tgt.float()
+
+
+def run(args, rank: int, world: int, dev) -> dict:
+    import torch.distributed as dist
+
+    from .. import ops
+    from ..models.transolver import Transolver
+    from ..optim import FusedAdam
+    from ..parallel.peer import set_loopback
+    from ..parallel.point_parallel import PointParallel
+    from ..utils.capture import GraphedStep
+
+    torch.manual_seed(1234)
+    model = Transolver(**CFG).to(dev)
+    pp = PointParallel(model) if world > 1 else None
+    use_graph = not getattr(args, "no_graph", False)
+    opt = FusedAdam(model.parameters(), lr=1e-3, capturable=use_graph)
+    n_local = N_POINTS // world
+    xyz, nrm, tgt = make_ellipsoid_cloud(N_POINTS, seed=0)
+    sl = slice(rank * n_local, (rank + 1) * n_local if rank < world - 1 else N_POINTS)
+    host = [t[sl].unsqueeze(0).contiguous().pin_memory() for t in (xyz, nrm, tgt)]
+    dev_in = [t.to(dev, non_blocking=True) for t in host]
+    torch.cuda.synchronize()
+    denom = float(N_POINTS * CFG["out_dim"])
+    loss_host = torch.zeros(1, pin_memory=True)
+    state = {"loss": None}
+
+    def train_step(emb, fx, target):
+        if pp is not None:
+            pp.zero_grad()
+        else:
+            opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            out = model(fx, embedding=emb)
+        loss = ((out.float() - target) ** 2).sum() / denom
+        loss.backward()
+        if pp is not None:
+            pp.reduce_gradients()
+        opt.step()
+        state["loss"] = loss.detach()
+        return state["loss"]
+
+    flush = flush_buffer(dev)
+    sampler = ClockSampler(dev.index or 0)
+    train_step(*dev_in)  # build caches / lazy init before counting launches
+    torch.cuda.synchronize()
+    before = ops.kernel_launches()
+    train_step(*dev_in)
+    torch.cuda.synchronize()
+    launches_per_step = ops.kernel_launches() - before
+
+    def make_steps():
+        if use_graph:
+            # the whole step (forward, backward, peer gradient reduction, Adam) is captured once and replayed: the step's
+            # kernels then cost one launch on the host, which matters once the per-rank shard is small
+            graphed = GraphedStep(train_step, dev_in, warmup=1)
+
+            def resident():
+                graphed()
+
+            def e2e():
+                loss = graphed(*host)                       # H2D of the step's inputs into the captured input tensors
+                loss_host.copy_(loss.reshape(1), non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+            return resident, e2e
+
+        def resident():
+            train_step(*dev_in)
+
+        def e2e():
+            emb, fx, target = (t.to(dev, non_blocking=True) for t in host)
+            train_step(emb, fx, target)
+            loss_host.copy_(state["loss"].reshape(1), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        return resident, e2e
+
+    step_resident, step_e2e = make_steps()
+    if rank == 0:
+        sampler.start()
+    ms, wall = timed_loop(step_resident, args.steps, max(args.warmup - 2, 1), world, dev, flush)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e, _ = timed_loop(step_e2e, args.steps, 1, world, dev, flush)
+    loss_val = loss_host.clone()
+    exposed = None
+    if world > 1:
+        # the same step with every peer transfer switched off: what is left of the difference is communication that
+        # the step does not hide
+        set_loopback(True)
+        loop_resident, _ = make_steps()
+        ms_loop, _ = timed_loop(loop_resident, max(3, args.steps // 2), 2, world, dev, flush)
+        set_loopback(False)
+        exposed = max(0.0, ms - ms_loop)
+    err = ops.device_error()
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    if world > 1:                                   # every rank holds the squared error of its shard: sum for the report
+        total = loss_val.to(dev)
+        dist.all_reduce(total)
+        loss_val.copy_(total)
+    return base_line(
+        1000.0 / ms, ms, world, args, "strong", "synthetic (seeded ellipsoid point cloud, random-init weights)",
+        {"model": DESC, "global_batch": 1, "seq_len": N_POINTS, "parallelism": f"points sharded x{world}",
+         "optimizer": "Adam (fused)", "cuda_graph": use_graph,
+         "l2": "256 MB buffer rewritten between timed steps; per-step working set is tens of GB (>> 126 MB L2)"},
+        clocks,
+        {"value": 1000.0 / ms_e2e, "unit": "samples/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+        launches_per_step,
+        {"exposed_comm_ms": exposed, "device_error_word": err, "loss": float(loss_val.item()), "wall_s_timed_region": wall,
+         "exposed_comm_how": "step time minus the time of the same step with all peer traffic switched off (loopback)"})

@@ -25,9 +25,10 @@ from .utils.weight_init import _weight_init
 
 
 def _tensor_core_conv_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Use the library's implicit-GEMM convolution: CUDA, channels-last, bf16 (or bf16 autocast), shapes it covers."""
-    if not (x.is_cuda and x.dim() == 4 and x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous()):
-        return False
+    """Use the library's implicit-GEMM convolution: CUDA, bf16 (or bf16 autocast), shapes it covers (any memory format:
+    channels-last input is consumed in place, other layouts are converted once)."""
+    if type(x) is not torch.Tensor or not (x.is_cuda and x.dim() == 4):
+        return False      # tensor subclasses (ShardTensor) reach the kernels through their own handlers
     bf16 = x.dtype == torch.bfloat16 or (torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16)
     return bf16 and _conv.supported(x, w)
 
@@ -51,6 +52,10 @@ class Conv2d(nn.Module):
         self.weight = nn.Parameter(_weight_init([out_channels, in_channels, kernel, kernel], **kw) * init_weight) if kernel else None
         self.bias = nn.Parameter(_weight_init([out_channels], **kw) * init_bias) if kernel and bias else None
         f = torch.as_tensor(resample_filter, dtype=torch.float32)
+        # the box filter [1, 1]: down-sampling is a 2x2 mean, up-sampling a 2x2 replication -- both are done as such
+        # (one memory-bound pass) instead of depth-wise (transposed) convolutions with a constant filter
+        rf = list(resample_filter)
+        self._box_filter = bool((up or down) and len(rf) == 2 and rf[0] == rf[1])
         f = f.ger(f).unsqueeze(0).unsqueeze(1) / f.sum().square()
         self.register_buffer("resample_filter", f if up or down else None)
 
@@ -78,10 +83,16 @@ class Conv2d(nn.Module):
             x = F.conv2d(x, f.tile([self.out_channels, 1, 1, 1]), groups=self.out_channels, stride=2, bias=fb)
         else:
             if self.up:
-                x = F.conv_transpose2d(x, f.mul(4).tile([self.in_channels, 1, 1, 1]), groups=self.in_channels,
-                                       stride=2, padding=f_pad)
+                if self._box_filter:
+                    x = F.interpolate(x, scale_factor=2, mode="nearest")
+                else:
+                    x = F.conv_transpose2d(x, f.mul(4).tile([self.in_channels, 1, 1, 1]), groups=self.in_channels,
+                                           stride=2, padding=f_pad)
             if self.down:
-                x = F.conv2d(x, f.tile([self.in_channels, 1, 1, 1]), groups=self.in_channels, stride=2, padding=f_pad)
+                if self._box_filter:
+                    x = F.avg_pool2d(x, 2)
+                else:
+                    x = F.conv2d(x, f.tile([self.in_channels, 1, 1, 1]), groups=self.in_channels, stride=2, padding=f_pad)
             if w is not None:
                 if _tensor_core_conv_ok(x, w):
                     # channels-last bf16 on a GPU: implicit-GEMM kernel, bias added in its epilogue

@@ -36,6 +36,9 @@ def _src_dst(nfeat):
 def gather_src_dst(nfeat: Union[Tensor, Tuple[Tensor, Tensor]], graph) -> Tuple[Tensor, Tensor]:
     """``(src_feat[src], dst_feat[dst])`` for every edge."""
     src_feat, dst_feat = _src_dst(nfeat)
+    if hasattr(graph, "gather_src"):
+        # partitioned graph: sources may live on another rank; the gather reads them from their owners
+        return graph.gather_src(src_feat), ops.gather_rows(dst_feat, segments(graph, "dst", dst_feat.shape[0]))
     return (ops.gather_rows(src_feat, segments(graph, "src", src_feat.shape[0])),
             ops.gather_rows(dst_feat, segments(graph, "dst", dst_feat.shape[0])))
 

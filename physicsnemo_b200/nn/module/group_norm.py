@@ -65,7 +65,14 @@ class GroupNorm(torch.nn.Module):
                 weight = weight.to(x.dtype)
             if bias.dtype != x.dtype:
                 bias = bias.to(x.dtype)
-        if x.is_cuda and _gn.supported(x, self.num_groups):
+        if type(x) is not torch.Tensor:
+            from ...parallel.shard_tensor import ShardTensor
+
+            if isinstance(x, ShardTensor):   # moments over all shards, fused with the activation where the kernels cover it
+                from ...parallel.patches.norm import group_norm_act
+
+                return group_norm_act(x, self.num_groups, self.weight, self.bias, self.eps, self.act)
+        if type(x) is torch.Tensor and x.is_cuda and _gn.supported(x, self.num_groups):
             # one kernel pair for norm + affine (+ SiLU); same arithmetic in training and evaluation
             fuse = self.act == "silu"
             x = _gn.group_norm(x, self.num_groups, self.weight, self.bias, self.eps, silu=fuse)

@@ -121,7 +121,7 @@ class PhysicsAttentionBase(nn.Module, ABC):
         if self._fusable(x):
             from ...ops.physics_attention import physics_attention_irregular
 
-            return physics_attention_irregular(self, x, residual, reduce_fn=getattr(self, "_reduce_fn", None))
+            return physics_attention_irregular(self, x, residual, exchange=getattr(self, "_exchange", None))
         projected = self.project_input_onto_slices(x)
         if self.plus:
             x_mid = projected
@@ -133,6 +133,12 @@ class PhysicsAttentionBase(nn.Module, ABC):
         out_slice_token = self._compute_slice_attention_sdpa(slice_tokens)
         out = self._project_attention_outputs(out_slice_token, slice_weights)
         return out if residual is None else out + residual
+
+
+def _fused_params_ok(mod) -> bool:
+    from ...ops.physics_attention import fused_supported
+
+    return fused_supported(mod)
 
 
 class PhysicsAttentionIrregularMesh(PhysicsAttentionBase):
@@ -158,6 +164,7 @@ class PhysicsAttentionIrregularMesh(PhysicsAttentionBase):
             and self.dim % 8 == 0
             and (self.dropout.p == 0.0 or not self.training)
             and ops.fused_path_enabled(x)
+            and _fused_params_ok(self)
         )
 
 

@@ -1,7 +1,7 @@
 """Fused Transolver physics attention for irregular meshes (sm_100a).
 
 Mathematics of ``physicsnemo/nn/module/physics_attention.py:501-558`` restated so that
-every pass over the N points is a tcgen05 GEMM:
+every pass over the N points is a tcgen05 GEMM and everything else is four small kernels:
 
 1. ``in_project_x`` followed by ``in_project_slice`` is one affine map (no nonlinearity in
    between): ``logits = xn @ Wc.T + bc`` with ``Wc = blockdiag_H(Ws) @ Wx``; the temperature
@@ -10,14 +10,19 @@ every pass over the N points is a tcgen05 GEMM:
    intermediate.
 2. slice tokens ``Σ_n w[n,h,s] fx[n,h,:]`` and norms ``Σ_n w[n,h,s]`` come from one
    reduction GEMM ``w.T @ fx`` (+ column sums of ``w`` from an extra ones-column MMA); the
-   per-head blocks are its diagonal blocks.  Under point sharding these H*S*(D+1) partial
-   sums are what crosses ranks (one all-reduce).
-3. attention among the 64 tokens per head is tiny and stays in PyTorch (fp32, autograd).
+   per-head blocks are its diagonal blocks.  Under point sharding these partial sums are what
+   crosses ranks: the GEMM writes them into a region of the rank's symmetric buffer, a flag is
+   raised, and the token kernel of every rank adds the P copies with direct peer loads in its
+   prologue — no stand-alone collective.
+3. attention among the 64 tokens per head, the normalisation before it and the combined
+   de-slicing matrix after it are one kernel (``pnm_pa_tokens_fwd``), one CTA per head.
 4. de-slicing followed by ``out_linear`` is again one affine map:
    ``out = w @ Wcomb.T + bo (+ residual)`` with ``Wcomb = Wo @ blockdiag(out_tokens).T``.
 
-The backward mirrors this with the softmax Jacobian, GELU-free, in GEMM epilogues; the
-small matrices (``Wc``, ``Wcomb``, tokens) are differentiated by autograd on a side graph.
+The backward mirrors this: softmax Jacobian in GEMM epilogues, the token-sized backward
+(attention, normalisation, ``dWo``, ``dWqkv`` and the operands of the point-sized GEMMs) in
+``pnm_pa_tokens_bwd`` — which again sums the one quantity that crosses ranks (``dWcomb``) in its
+prologue — and the gradients of ``Wx, bx, Ws, bs, T`` in ``pnm_pa_prepare_bwd``.
 """
 from __future__ import annotations
 
@@ -25,114 +30,99 @@ import torch
 import torch.nn.functional as F
 
 from . import gemm as G
+from . import pa_small as P
 
 
-def _blockdiag(blocks: torch.Tensor) -> torch.Tensor:
-    """(H, a, b) -> (H*a, H*b) block-diagonal matrix (differentiable)."""
-    return torch.block_diag(*blocks.unbind(0))
+class LocalExchange:
+    """Stand-in of ``parallel.peer.PeerRegions`` for an unsharded model: ordinary local buffers, no flags."""
+
+    world = 1
+
+    def region(self, floats: int, device) -> tuple:
+        buf = torch.empty(floats, dtype=torch.float32, device=device)
+        return buf, [buf.data_ptr()]
+
+    def publish(self):
+        return None
 
 
-def _diag_blocks(m: torch.Tensor, H: int) -> torch.Tensor:
-    """(H*a, H*b) -> (H, a, b): the diagonal blocks."""
-    a, b = m.shape[0] // H, m.shape[1] // H
-    return torch.stack([m[h * a:(h + 1) * a, h * b:(h + 1) * b] for h in range(H)])
+_LOCAL = LocalExchange()
 
 
 class _PhysAttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, xn, res, H, D, S, reduce_fn, Wx, bx, Wfx, bfx, Ws, bs, temp, Wqkv, Wo, bo):
-        M = xn.shape[0]
-        params = [Wx, bx, Wfx, bfx, Ws, bs, temp, Wqkv, Wo, bo]
-        with torch.enable_grad():
-            p = [t.detach().float().requires_grad_(True) for t in params]
-            pWx, pbx, pWfx, pbfx, pWs, pbs, ptemp, pWqkv, pWo, pbo = p
-            bd_ws = _blockdiag(pWs.unsqueeze(0).expand(H, S, D))            # (H*S, H*D)
-            Wc = bd_ws @ pWx                                                  # (H*S, C)
-            bc = bd_ws @ pbx + pbs.repeat(H)                                  # (H*S,)
-            inv_t = (1.0 / torch.clamp(ptemp.reshape(H), min=0.5, max=5.0)).repeat_interleave(S)
-        fx = G.gemm_tn(xn, G._bf16_weight(Wfx), bias=pbfx.detach())
-        w = G.gemm_tn(xn, Wc.detach().to(torch.bfloat16), bias=bc.detach(), scale=inv_t.detach().contiguous(),
-                      act=G.ACT_SOFTMAX64)
-        tok_full, norm_full = G.gemm_nt(w, fx, colsum=True)                   # (H*S, H*D) fp32, (H*S,)
-        tok_raw = _diag_blocks(tok_full, H)                                    # (H, S, D)
-        norm_raw = norm_full.reshape(H, S)
-        if reduce_fn is not None:  # point-sharded: partial sums -> global sums
-            packed = torch.cat([tok_raw.reshape(-1), norm_raw.reshape(-1)])
-            packed = reduce_fn(packed)
-            tok_raw = packed[: H * S * D].reshape(H, S, D)
-            norm_raw = packed[H * S * D:].reshape(H, S)
-        with torch.enable_grad():
-            tok_leaf = tok_raw.detach().requires_grad_(True)
-            norm_leaf = norm_raw.detach().requires_grad_(True)
-            token = tok_leaf / (norm_leaf + 1e-2).unsqueeze(-1)              # (H, S, D)
-            qkv = token @ pWqkv.t()                                           # (H, S, 3D)
-            q, k, v = qkv.reshape(H, S, 3, D).unbind(2)
-            out_tok = F.scaled_dot_product_attention(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0)).squeeze(0)
-            Wcomb = pWo @ _blockdiag(out_tok).t()                             # (C, H*D) @ (H*D, H*S) -> (C, H*S)
-        out = G.gemm_tn(w, Wcomb.detach().to(torch.bfloat16), bias=pbo.detach(), aux=res,
-                        aux_mode=G.AUX_ADD if res is not None else G.AUX_NONE)
-        ctx.save_for_backward(xn, fx, w)
-        ctx.graph = (p, Wc, bc, inv_t, tok_leaf, norm_leaf, Wcomb)
+    def forward(ctx, xn, res, H, D, S, exchange, Wx, bx, Wfx, bfx, Ws, bs, temp, Wqkv, Wo, bo):
+        ex = exchange if exchange is not None else _LOCAL
+        HS, inner = H * S, H * D
+        dev = xn.device
+        Wc, bc, inv_t, Wfx16, Wback = P.prepare_fwd(Wx.detach(), bx.detach(), Wfx.detach(), Ws.detach(), bs.detach(),
+                                                    temp.detach().reshape(-1), H, D)
+        fx = G.gemm_tn(xn, Wfx16, bias=bfx.detach().float())
+        w = G.gemm_tn(xn, Wc, bias=bc, scale=inv_t, act=G.ACT_SOFTMAX64)
+        # token sums [H*S, inner] followed by the slice norms [H*S]: partial sums of this rank's points
+        buf, srcs = ex.region(HS * inner + HS, dev)
+        buf.zero_()
+        G.gemm_nt(w, fx, out=buf[: HS * inner].view(HS, inner), colsum_out=buf[HS * inner:])
+        peer = ex.publish()
+        Wcomb16, saved = P.tokens_fwd(srcs, HS * inner, inner, Wqkv.detach(), Wo.detach(), H, D, peer)
+        out = G.gemm_tn(w, Wcomb16, bias=bo.detach().float(), aux=res, aux_mode=G.AUX_ADD if res is not None else G.AUX_NONE)
+        ctx.save_for_backward(xn, fx, w, Wx, bx, Ws, temp, Wqkv, Wo, inv_t, Wback, *saved)
         ctx.dims = (H, D, S)
-        ctx.reduce_fn = reduce_fn
+        ctx.exchange = ex
         ctx.has_res = res is not None
-        ctx.param_dtypes = [t.dtype for t in params]
+        ctx.param_dtypes = [t.dtype for t in (Wx, bx, Wfx, bfx, Ws, bs, temp, Wqkv, Wo, bo)]
+        ctx.temp_shape = temp.shape
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        xn, fx, w = ctx.saved_tensors
-        p, Wc, bc, inv_t, tok_leaf, norm_leaf, Wcomb = ctx.graph
+        xn, fx, w, Wx, bx, Ws, temp, Wqkv, Wo, inv_t, Wback, *saved = ctx.saved_tensors
         H, D, S = ctx.dims
+        ex = ctx.exchange
+        HS, inner = H * S, H * D
+        Cout = Wo.shape[0]
         dout = dout.contiguous()
         dev = xn.device
-        # out = w @ Wcomb.T + bo (+res)
-        dWcomb, dbo = G.gemm_nt(dout, w, colsum=True)                         # (C, H*S), (C,)
-        share = 1.0
-        if ctx.reduce_fn is not None:
-            # the slice tokens are global quantities: their gradient needs the global dWcomb.
-            packed = ctx.reduce_fn(torch.cat([dWcomb.reshape(-1), dbo]))
-            dWcomb, dbo = packed[: dWcomb.numel()].reshape(dWcomb.shape), packed[dWcomb.numel():]
-            # parameter gradients derived from reduced quantities are already global and equal on
-            # every rank; they are handed out as 1/world shares so that the model-wide gradient
-            # sum over the shards restores them.
-            share = 1.0 / float(getattr(ctx.reduce_fn, "world", None) or getattr(getattr(ctx.reduce_fn, "__self__", None), "world", 1))
-        pWo, pWqkv = p[8], p[7]
-        d_tok, d_norm, dWo, dWqkv = torch.autograd.grad(Wcomb, [tok_leaf, norm_leaf, pWo, pWqkv], dWcomb,
-                                                         retain_graph=False)
+        # out = w @ Wcomb.T + bo (+res): dWcomb [Cout, H*S] is a partial sum over this rank's points; dbo stays local
+        buf, srcs = ex.region(Cout * HS, dev)
+        buf.zero_()
+        dbo = torch.zeros(Cout, dtype=torch.float32, device=dev)
+        G.gemm_nt(dout, w, out=buf.view(Cout, HS), colsum_out=dbo)
+        peer = ex.publish()
+        # parameter gradients derived from the reduced dWcomb are global and equal on every rank; they are handed out as
+        # 1/world shares so that the model-wide gradient sum over the shards restores them
+        share = 1.0 / float(ex.world)
+        dWo, dWqkv, d_norm, Bcat, BdT = P.tokens_bwd(srcs, Wqkv.detach(), Wo.detach(), saved, H, D, share, peer)
         # dw = [dout | fx] @ [Wcomb.T | blockdiag(d_tok)].T + d_norm ; softmax backward in the epilogue
-        bd_dtok = _blockdiag(d_tok)                                           # (H*S, H*D)
-        Bcat = torch.cat([Wcomb.detach().t(), bd_dtok], dim=1).to(torch.bfloat16).contiguous()  # (H*S, C + H*D)
         grp = torch.zeros(H, dtype=torch.float32, device=dev)
-        dlogit = G.gemm_tn(dout, Bcat, a2=fx, bias=d_norm.reshape(-1).contiguous(), aux=w, aux_mode=G.AUX_DSOFTMAX,
-                           scale=inv_t.detach().contiguous(), scale_post=True, group_out=grp)
-        # d fx = w @ blockdiag(d_tok)
-        dfx = G.gemm_tn(w, bd_dtok.t().to(torch.bfloat16).contiguous())
+        dlogit = G.gemm_tn(dout, Bcat, a2=fx, bias=d_norm, aux=w, aux_mode=G.AUX_DSOFTMAX, scale=inv_t, scale_post=True,
+                           group_out=grp)
+        dfx = G.gemm_tn(w, BdT)                                                # d fx = w @ blockdiag(d_tok)
         dWc, dbc = G.gemm_nt(dlogit, xn, colsum=True)                         # (H*S, C), (H*S,)
         dWfx, dbfx = G.gemm_nt(dfx, xn, colsum=True)                          # (H*D, C), (H*D,)
-        d_inv_t = (grp / inv_t.detach().reshape(H, S)[:, 0]).repeat_interleave(S) / S
-        pWx, pbx, pWs, pbs, ptemp = p[0], p[1], p[4], p[5], p[6]
-        dWx, dbx, dWs, dbs, dtemp = torch.autograd.grad([Wc, bc, inv_t], [pWx, pbx, pWs, pbs, ptemp],
-                                                        [dWc, dbc, d_inv_t], allow_unused=True)
-        # d xn = [dlogit | dfx] @ [Wc ; Wfx]
-        Wback = torch.cat([Wc.detach().t(), p[2].detach().t()], dim=1).to(torch.bfloat16).contiguous()  # (C, H*S + H*D)
-        dxn = G.gemm_tn(dlogit, Wback, a2=dfx)
+        dWx, dbx, dWs, dbs, dtemp = P.prepare_bwd(dWc, dbc, grp, Wx.detach(), bx.detach(), Ws.detach(),
+                                                  temp.detach().reshape(-1), H, D)
+        dxn = G.gemm_tn(dlogit, Wback, a2=dfx)                                # [dlogit | dfx] @ [Wc ; Wfx]
         dres = dout if ctx.has_res else None
-        if share != 1.0:
-            dWqkv, dWo, dbo = dWqkv * share, dWo * share, dbo * share
-        grads = [dWx, dbx, dWfx, dbfx, dWs, dbs, dtemp, dWqkv, dWo, dbo]
-        grads = [None if g is None else g.to(dt) for g, dt in zip(grads, ctx.param_dtypes)]
-        ctx.graph = None
+        grads = [dWx, dbx, dWfx, dbfx, dWs, dbs, dtemp.reshape(ctx.temp_shape), dWqkv, dWo, dbo]
+        grads = [g if g.dtype == dt else g.to(dt) for g, dt in zip(grads, ctx.param_dtypes)]
         return (dxn, dres, None, None, None, None, *grads)
 
 
-def physics_attention_irregular(mod, x: torch.Tensor, residual: torch.Tensor | None = None, reduce_fn=None):
+def fused_supported(mod) -> bool:
+    """The kernels cover fp32 parameters, 64 slices and head widths that divide 256."""
+    params = [mod.in_project_x.weight, mod.in_project_x.bias, mod.in_project_fx.weight, mod.in_project_fx.bias,
+              mod.in_project_slice.weight, mod.in_project_slice.bias, mod.temperature, mod.qkv_project.weight,
+              mod.out_linear.weight, mod.out_linear.bias]
+    return P.supported(mod.heads, mod.dim_head, mod.slice_num, mod.in_project_x.weight.shape[1], params)
+
+
+def physics_attention_irregular(mod, x: torch.Tensor, residual: torch.Tensor | None = None, exchange=None):
     """Fused forward of ``PhysicsAttentionIrregularMesh`` ``mod`` on ``x`` (B, N, C), B folded.
 
-    ``reduce_fn`` (optional) maps a flat fp32 tensor of partial sums to the sum over all point
-    shards (an all-reduce); it is applied once forward (slice tokens and norms) and once
-    backward (the gradient of the combined de-slicing matrix, from which the token gradients
-    follow).  All other parameter gradients stay per-shard partial sums.
+    ``exchange`` (optional, ``parallel.peer.PeerRegions``): where the partial sums that cross point shards live —
+    once forward (slice tokens and norms) and once backward (the gradient of the combined de-slicing matrix, from
+    which the token gradients follow).  All other parameter gradients stay per-shard partial sums.
     """
     B, N, C = x.shape
     outs = []
@@ -148,7 +138,7 @@ def physics_attention_irregular(mod, x: torch.Tensor, residual: torch.Tensor | N
                 rb = rb.to(torch.bfloat16)
             rb = rb.contiguous()
         out = _PhysAttnFn.apply(
-            xb.contiguous(), rb, mod.heads, mod.dim_head, mod.slice_num, reduce_fn,
+            xb.contiguous(), rb, mod.heads, mod.dim_head, mod.slice_num, exchange,
             mod.in_project_x.weight, mod.in_project_x.bias, mod.in_project_fx.weight, mod.in_project_fx.bias,
             mod.in_project_slice.weight, mod.in_project_slice.bias, mod.temperature, mod.qkv_project.weight,
             mod.out_linear.weight, mod.out_linear.bias,

@@ -24,6 +24,41 @@ def _tup(v, n):
     return tuple(v) if isinstance(v, (tuple, list)) else (v,) * n
 
 
+def _bf16_mode(t: torch.Tensor) -> bool:
+    if t.dtype == torch.bfloat16:
+        return True
+    return t.is_cuda and torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16
+
+
+def _fused_halo_conv(loc, w, b, spec, stride, padding, dilation, groups):
+    """The halo-fused tcgen05 path (``parallel/halo_conv.py``) when it covers this call, else ``None``.
+
+    Conditions: CUDA + NCCL, bf16 compute, 2-D 3×3 / stride 1 / padding 1 / no dilation / one group, input sharded on
+    the height only (tensor dim 2) over a 1-D mesh dimension, every shard a multiple of 8 rows.
+    """
+    if loc.dim() != 4 or not loc.is_cuda or not _bf16_mode(loc) or groups != 1:
+        return None
+    if tuple(w.shape[2:]) != (3, 3) or stride != (1, 1) or dilation != (1, 1) or tuple(padding) != (1, 1):
+        return None
+    shards = [(md, p) for md, p in enumerate(spec.placements) if isinstance(p, Shard)]
+    if len(shards) != 1 or shards[0][1].dim != 2:
+        return None
+    md = shards[0][0]
+    sizes = spec.sharding_sizes[md]
+    if any(v % 8 or v == 0 for v in sizes):
+        return None
+    from ..halo_conv import get_halo_runtime, halo_conv2d_3x3, halo_conv_supported
+    from ..peer import peer_available
+
+    if not peer_available(loc):
+        return None
+    rt = get_halo_runtime(spec.mesh.get_group(md))
+    if not halo_conv_supported(loc, w, rt):
+        return None
+    with NO_TF():
+        return halo_conv2d_3x3(loc, w, b, rt)
+
+
 def _conv(func, types, args, kwargs):
     names = ["input", "weight", "bias", "stride", "padding", "dilation", "groups"]
     a = dict(zip(names, args))
@@ -53,6 +88,10 @@ def _conv(func, types, args, kwargs):
     padding = list(_tup(padding, nsp))
     loc = local(x)
     placements = list(spec.placements)
+    if nsp == 2 and not isinstance(padding, str):
+        fused = _fused_halo_conv(loc, w, b, spec, stride, _tup(padding, nsp), dilation, groups)
+        if fused is not None:
+            return wrap(fused, spec.mesh, placements, dict(spec.sharding_sizes))
     sizes = {}
     for md, p in enumerate(spec.placements):
         if not isinstance(p, Shard):
@@ -93,7 +132,13 @@ def _conv(func, types, args, kwargs):
             sizes[md] = tuple(-(-v // s) for v in in_sizes)
         padding[i] = 0
     with NO_TF():
-        out = func(loc, w, b, stride, tuple(padding), dilation, groups)
+        from ...ops import conv as _oc
+
+        if (nsp == 2 and loc.is_cuda and _bf16_mode(loc) and all(pd == ksize[i] // 2 for i, pd in enumerate(padding))
+                and _oc.supported(loc, w, stride, tuple(padding), dilation, groups)):
+            out = _oc.conv2d_same(loc, w, b)        # no halo left to fetch (1×1, or the padded copy already holds it)
+        else:
+            out = func(loc, w, b, stride, tuple(padding), dilation, groups)
     for md, p in enumerate(spec.placements):
         if isinstance(p, Shard) and p.dim >= 2:
             want = sizes[md][spec.mesh.get_local_rank(md)]

@@ -19,6 +19,48 @@ from .. import collectives as C
 from ._common import MissingShardPatch, NO_TF, ShardTensor, is_st, local, param, register, resolved, wrap
 
 
+def _fused_sharded_gn(x: ShardTensor, G: int, w, b, eps: float, silu: bool):
+    """GroupNorm(+SiLU) on the peer-memory kernels when they cover this tensor, else ``None``.
+
+    Conditions: CUDA + NCCL, 4-D bf16 / fp32 input sharded on one spatial dim over a 1-D mesh dimension, affine
+    parameters present.  The statistics cross the ranks inside the normalising kernel (``ops/group_norm.py``).
+    """
+    spec = x._spec
+    loc = local(x)
+    if w is None or b is None or loc.dim() != 4 or not loc.is_cuda:
+        return None
+    shards = [(md, p) for md, p in enumerate(spec.placements) if isinstance(p, Shard)]
+    if len(shards) != 1 or shards[0][1].dim < 2:
+        return None
+    from ...ops import group_norm as _gn
+    from ..peer import get_runtime, peer_available
+
+    if not peer_available(loc):
+        return None
+    md = shards[0][0]
+    rt = get_runtime(spec.mesh.get_group(md), "compute")
+    if loc.dtype not in (torch.bfloat16, torch.float32) or not _gn.sharded_supported(loc, G, rt):
+        return None
+    with NO_TF():
+        out = _gn.group_norm_sharded(loc, G, w, b, eps, silu, rt, math.prod(x.shape[2:]))
+    return wrap(out, spec.mesh, spec.placements, spec.sharding_sizes)
+
+
+def group_norm_act(x: ShardTensor, num_groups: int, weight, bias, eps: float, act: str | None):
+    """``act(group_norm(x))`` for a ShardTensor: one fused kernel pair when ``act`` is SiLU (or absent), else the
+    composition.  Entry point of ``nn.GroupNorm`` for sharded inputs."""
+    x = resolved(x)
+    if act in (None, "silu"):
+        w, b = param(weight, x._spec.mesh), param(bias, x._spec.mesh)
+        out = _fused_sharded_gn(x, num_groups, w, b, eps, act == "silu")
+        if out is not None:
+            return out
+    y = F.group_norm(x, num_groups, weight, bias, eps)
+    if act is None:
+        return y
+    return getattr(F, act)(y) if hasattr(F, act) else getattr(torch, act)(y)
+
+
 @register(F.group_norm)
 def _group_norm(func, types, args, kwargs):
     names = ["input", "num_groups", "weight", "bias", "eps"]
@@ -29,6 +71,9 @@ def _group_norm(func, types, args, kwargs):
     G = a["num_groups"]
     w, b = param(a.get("weight"), spec.mesh), param(a.get("bias"), spec.mesh)
     eps = a.get("eps", 1e-5)
+    fused = _fused_sharded_gn(x, G, w, b, eps, False)
+    if fused is not None:
+        return fused
     sharded = {p.dim: md for md, p in enumerate(spec.placements) if isinstance(p, Shard)}
     if 1 in sharded:
         raise MissingShardPatch("group_norm over a channel-sharded input")

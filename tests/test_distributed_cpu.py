@@ -1,4 +1,5 @@
 """Distributed primitives on CPU (gloo) ranks against single-process oracles."""
+import pytest
 import torch
 import torch.distributed as dist
 
@@ -183,3 +184,82 @@ def _healda_resharding(rank, world):
 
 def test_healda_time_space_resharding():
     run_ranks(_healda_resharding, world=2)
+
+
+def _rank_that_raises(rank, world):
+    import datetime
+
+    import torch
+    import torch.distributed as dist
+
+    if rank == 1:
+        raise RuntimeError("injected failure before the collective")      # this rank never joins
+    # the surviving rank must get a host-side error within the process-group timeout, not hang
+    t = torch.ones(4)
+    try:
+        work = dist.all_reduce(t, async_op=True)
+        ok = work.wait(timeout=datetime.timedelta(seconds=3))
+        raise AssertionError(f"collective completed although a rank never joined (ok={ok})")
+    except AssertionError:
+        raise
+    except Exception as exc:  # noqa: BLE001  (timeout / connection error raised on the host)
+        print(f"survivor saw: {type(exc).__name__}")
+
+
+def test_failed_rank_gives_host_side_error_not_a_hang():
+    """One rank raises before a collective; the other's wait ends with an error on the host inside the time limit."""
+    import time
+
+    from tests.dist_utils import run_ranks
+
+    t0 = time.time()
+    with pytest.raises(RuntimeError) as err:
+        run_ranks(_rank_that_raises, world=2, timeout=60)
+    assert "injected failure" in str(err.value)
+    assert time.time() - t0 < 60
+
+
+def _partitioned_mgn(rank, world):
+    """MeshGraphNet on a destination-owned graph partition == MeshGraphNet on the whole graph (forward + gradients)."""
+    import numpy as np
+
+    from physicsnemo_b200.models.meshgraphnet import MeshGraphNet
+    from physicsnemo_b200.nn.module.gnn_layers.graph_types import Graph
+    from physicsnemo_b200.parallel.graph_partition import PartitionedGraph, plan_partition, spatial_order
+
+    rng = np.random.default_rng(0)
+    n = 300
+    pts = rng.random((n, 2))
+    src = rng.integers(0, n, 1500)
+    dst = rng.integers(0, n, 1500)
+    keep = src != dst
+    src, dst = src[keep], dst[keep]
+    order = spatial_order(pts)
+    inv = np.empty(n, dtype=np.int64)
+    inv[order] = np.arange(n)
+    src, dst = inv[src], inv[dst]                       # spatially sorted numbering
+    torch.manual_seed(0)
+    nfeat = torch.randn(n, 6, dtype=torch.float64)
+    efeat = torch.randn(len(src), 3, dtype=torch.float64)
+    target = torch.randn(n, 3, dtype=torch.float64)
+    model = MeshGraphNet(6, 3, 3, processor_size=3, hidden_dim_processor=16, hidden_dim_node_encoder=16,
+                         hidden_dim_edge_encoder=16, hidden_dim_node_decoder=16, mlp_activation_fn="silu").double()
+    full = model(nfeat, efeat, Graph(torch.from_numpy(np.stack([src, dst])), num_nodes=n))
+    ((full - target) ** 2).sum().backward()
+    ref = {k: p.grad.clone() for k, p in model.named_parameters()}
+    model.zero_grad()
+    plan = plan_partition(np.stack([src, dst]), n, world, rank)
+    pg = PartitionedGraph(plan, "cpu", group=None)
+    lo, hi = plan.node_range
+    out = model(nfeat[lo:hi], efeat[torch.from_numpy(plan.edge_ids)], pg)
+    assert torch.allclose(out, full[lo:hi], atol=1e-9), float((out - full[lo:hi]).abs().max())
+    ((out - target[lo:hi]) ** 2).sum().backward()
+    for k, p in model.named_parameters():
+        g = p.grad.clone()
+        dist.all_reduce(g)
+        assert torch.allclose(g, ref[k], atol=1e-8, rtol=1e-7), (k, float((g - ref[k]).abs().max()))
+    assert plan.n_halo > 0 and len(plan.send_idx) > 0
+
+
+def test_partitioned_meshgraphnet_three_ranks():
+    run_ranks(_partitioned_mgn, world=3, timeout=240)

@@ -420,3 +420,93 @@ def test_video_healda_on_gpu_matches_cpu():
     assert (y.detach().cpu() - ref).abs().max().item() < 2e-3 * max(1.0, ref.abs().max().item())
     y.square().sum().backward()
     assert bool(torch.isfinite(xg.grad).all()) and all(p.grad is not None for p in net.parameters())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(2, 64, 128, 24, 40), (1, 16, 64, 16, 32), (2, 128, 4, 20, 48), (1, 192, 64, 9, 17)])
+def test_conv3x3_forward_dgrad_wgrad_kernels(shape):
+    """Implicit-GEMM convolution incl. the split-reduction weight-gradient kernel (and channel padding) vs fp32 conv2d."""
+    from physicsnemo_b200 import ops
+    from physicsnemo_b200.ops import conv as C
+
+    n, cin, cout, h, w = shape
+    torch.manual_seed(0)
+    x = torch.randn(n, cin, h, w, device="cuda")
+    wt = torch.randn(cout, cin, 3, 3, device="cuda") / (9 * cin) ** 0.5
+    b = torch.randn(cout, device="cuda")
+    dy = torch.randn(n, cout, h, w, device="cuda")
+    xr, wr, br = x.clone().requires_grad_(True), wt.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    ref = torch.nn.functional.conv2d(xr, wr, br, padding=1)
+    ref.backward(dy)
+    xk, wk, bk = x.clone().requires_grad_(True), wt.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    assert C.supported(xk, wk)
+    before = ops.kernel_launches()
+    out = C.conv2d_same(xk, wk, bk)
+    out.backward(dy.to(out.dtype))
+    assert ops.kernel_launches() - before >= 3          # forward, input gradient, weight gradient: all library kernels
+
+    def rel(a, r):
+        return float((a.float() - r).abs().max()) / float(r.abs().max())
+
+    assert rel(out, ref) < 2e-2
+    assert rel(xk.grad, xr.grad) < 2e-2
+    assert rel(wk.grad, wr.grad) < 2e-2
+    assert rel(bk.grad, br.grad) < 2e-2
+    assert ops.device_error() == 0
+
+
+@pytest.mark.gpu
+def test_conv1x1_kernels_and_box_resampling():
+    from physicsnemo_b200.nn.module.conv_layers import Conv2d
+
+    torch.manual_seed(0)
+    for kw in (dict(kernel=1), dict(kernel=3, down=True), dict(kernel=3, up=True), dict(kernel=0, down=True)):
+        m = Conv2d(64, 64 if kw["kernel"] == 0 else 128, amp_mode=True, **kw).cuda()
+        x = torch.randn(2, 64, 16, 24, device="cuda")
+        xr = x.clone().requires_grad_(True)
+        w = m.weight
+        # oracle: the definition with depth-wise (transposed) convolutions in fp32
+        f = m.resample_filter
+        y = xr
+        if m.up:
+            y = torch.nn.functional.conv_transpose2d(y, f.mul(4).tile([64, 1, 1, 1]), groups=64, stride=2)
+        if m.down:
+            y = torch.nn.functional.conv2d(y, f.tile([64, 1, 1, 1]), groups=64, stride=2)
+        if w is not None:
+            y = torch.nn.functional.conv2d(y, w, m.bias, padding=w.shape[-1] // 2)
+        xk = x.clone().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            out = m(xk)
+        assert out.shape == y.shape
+        assert float((out.float() - y).abs().max()) < 3e-2 * max(1.0, float(y.abs().max()))
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        out.backward(dy.to(out.dtype))
+        assert float((xk.grad - xr.grad).abs().max()) < 3e-2 * float(xr.grad.abs().max())
+
+
+@pytest.mark.gpu
+def test_bounded_wait_gives_up_and_context_survives():
+    """A wait on a flag that nothing sets returns status 0 after its budget, sets error word 6 and leaves the device usable."""
+    import ctypes
+
+    from physicsnemo_b200.ops import _lib
+
+    lib = _lib.load(required=True)
+    lib.pnm_peer_wait_probe.argtypes = [ctypes.c_void_p, ctypes.c_uint, ctypes.c_double, ctypes.c_void_p, ctypes.c_void_p]
+    lib.pnm_peer_wait_probe.restype = ctypes.c_int
+    assert lib.pnm_reset_error() == 0
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.full((1,), 7, dtype=torch.int32, device="cuda")
+    rc = lib.pnm_peer_wait_probe(flag.data_ptr(), 1, 0.005, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0                      # gave up
+    assert lib.pnm_get_error() == 6                     # ERR_WAIT_PEER
+    assert lib.pnm_reset_error() == 0 and lib.pnm_get_error() == 0
+    flag.fill_(1)                                       # a satisfied wait returns status 1 and raises nothing
+    rc = lib.pnm_peer_wait_probe(flag.data_ptr(), 1, 0.005, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0 and int(status.item()) == 1 and lib.pnm_get_error() == 0
+    a = torch.randn(64, 64, device="cuda")
+    assert torch.isfinite(a @ a).all()                  # the context is intact

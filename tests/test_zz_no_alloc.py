@@ -25,8 +25,9 @@ def _bind(lib):
     return fn
 
 
-@pytest.mark.parametrize("M,C", [(4099, 256), (777, 768)])
-def test_noalloc_matches_regular_entry_point_twice(M, C):
+@pytest.mark.parametrize("M,C,with_dres", [(4099, 256, False), (777, 768, False), (1531, 8, False), (613, 1024, True),
+                                            (2050, 256, True)])
+def test_noalloc_matches_regular_entry_point_twice(M, C, with_dres):
     lib = _lib.load(required=True)
     noalloc = _bind(lib)
     dev = torch.device("cuda")
@@ -36,6 +37,8 @@ def test_noalloc_matches_regular_entry_point_twice(M, C):
         torch.manual_seed(100 + trial)
         x = torch.randn(M, C, device=dev).to(torch.bfloat16)
         dy = torch.randn(M, C, device=dev).to(torch.bfloat16)
+        dres = torch.randn(M, C, device=dev).to(torch.bfloat16) if with_dres else None
+        dres_ptr = None if dres is None else dres.data_ptr()
         xf = x.float()
         mean = xf.mean(1).contiguous()
         rstd = torch.rsqrt(xf.var(1, unbiased=False) + 1e-5).contiguous()
@@ -45,14 +48,14 @@ def test_noalloc_matches_regular_entry_point_twice(M, C):
         db_ref = torch.empty(C, device=dev)
         scratch = torch.empty(lib.pnm_layernorm_bwd_scratch_floats(M, C), device=dev)
         rc = lib.pnm_layernorm_bwd(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
-                                   None, dx_ref.data_ptr(), dg_ref.data_ptr(), db_ref.data_ptr(), scratch.data_ptr(),
+                                   dres_ptr, dx_ref.data_ptr(), dg_ref.data_ptr(), db_ref.data_ptr(), scratch.data_ptr(),
                                    M, C, stream)
         assert rc == 0
         # allocation-free entry point: outputs are pre-allocated here, nothing is allocated inside
         dx = torch.empty_like(x)
         dg = torch.empty(C, device=dev)
         db = torch.empty(C, device=dev)
-        rc = noalloc(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), None,
+        rc = noalloc(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dres_ptr,
                      dx.data_ptr(), dg.data_ptr(), db.data_ptr(), M, C, stream)
         assert rc == 0
         torch.cuda.synchronize()
