@@ -287,21 +287,26 @@ peer_allreduce_bf16_kernel(float* __restrict__ io, long long n, float scale, Pee
   }
 }
 
-// Copy `bytes` (multiple of 16) from a peer-mapped source into local memory after that peer's "small" flag of call
-// `epoch` has arrived (flag_from < 0: no wait).  The building block of the staged K / V all-gather of the sharded
-// attention: the copy of the next owner's block runs on a side stream while the tensor cores work on the current one.
+// Copy `bytes` (multiple of 16) from a (peer-mapped) source into local memory after the "small" flag of call `epoch` has
+// arrived from rank flag_from (flag_from >= 0), from every rank (flag_from == -2), or at once (flag_from == -1).  The
+// building block of staged transfers: the copy of the next owner's block can run on a side stream while the tensor
+// cores work on the current one.  On a time-out the destination is filled with NaN patterns.
 static __global__ void __launch_bounds__(512)
 peer_pull_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long nvec, PeerArgs p, int flag_from, int* err) {
   __shared__ int sh_ok;
+  bool ok = true;
   if (flag_from >= 0) {
     const uint32_t epoch = peer_epoch(p);
     if (threadIdx.x == 0)
       sh_ok = peer_wait_flag(peer_flag(p, p.rank, epoch & 1, 0, kPeerSmallCta, flag_from), epoch, p.budget_ns, err) ? 1 : 0;
     __syncthreads();
-    if (!sh_ok) return;
+    ok = sh_ok != 0;
+  } else if (flag_from == -2) {
+    ok = peer_small_wait(p, peer_epoch(p), err, &sh_ok);
   }
+  const uint4 nan4 = make_uint4(0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x)
-    dst[i] = __ldcg(src + i);
+    dst[i] = ok ? __ldcg(src + i) : nan4;
 }
 
 // Raise this rank's "small" flag of call `epoch` on every peer: data written earlier on the stream is then readable.

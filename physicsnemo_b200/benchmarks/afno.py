@@ -1,0 +1,232 @@
+"""AFNO (FourCastNet-style) on a 720 × 1440 grid, bf16, spectral filter distributed over the GPUs (configuration 5).
+
+Input: 73 channels on a 720 × 1440 lat-lon grid, each channel a seeded spherical-harmonic random field with spectrum
+∝ ℓ⁻², normalised to N(0, 1); target: a second such field (next-step MSE).  Model: patch 8 × 8, embedding 768, depth 12,
+8 AFNO blocks, soft-shrink threshold 0.01, batch 2; Adam.
+
+On N ranks the 2 × 90 × 180 tokens are sharded over the ranks for everything but the spectral filter, where a rank owns
+8 / N channel blocks of all tokens; the two reshardings are the load stage of the forward row transform (peer loads)
+and the store stage of the inverse one (peer stores) of the library's own Fourier kernels (``ops/afno_spectral.py``,
+``parallel/afno_sharded.py``) — no library FFT, no all-to-all call.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .common import ClockSampler, base_line, flush_buffer, rel_err, timed_loop
+
+CFG = dict(inp_shape=[720, 1440], in_channels=73, out_channels=73, patch_size=[8, 8], embed_dim=768, depth=12, num_blocks=8,
+           sparsity_threshold=0.01)
+BATCH = 2
+DESC = "AFNO 720x1440: patch 8x8, embed 768, depth 12, 8 blocks, mlp ratio 4, soft-shrink 0.01"
+
+
+def sh_random_fields(n_fields: int, nlat: int, nlon: int, lmax: int = 64, seed: int = 0) -> torch.Tensor:
+    """``[n_fields, nlat, nlon]`` band-limited spherical-harmonic random fields with power ∝ ℓ⁻², each N(0, 1)-normalised."""
+    g = torch.Generator().manual_seed(seed)
+    theta = (torch.arange(nlat, dtype=torch.float64) + 0.5) * math.pi / nlat
+    x, s = torch.cos(theta), torch.sin(theta)
+    spec = torch.zeros(n_fields, nlat, nlon // 2 + 1, dtype=torch.complex128)
+    pmm = torch.full((nlat,), math.sqrt(1.0 / (4 * math.pi)), dtype=torch.float64)      # orthonormal P_0^0
+    for m in range(lmax + 1):
+        if m > 0:
+            pmm = -math.sqrt((2 * m + 1) / (2 * m)) * s * pmm
+        p_prev2, p_prev1 = None, pmm
+        for l in range(m, lmax + 1):
+            if l == m:
+                p = pmm
+            elif l == m + 1:
+                p = math.sqrt(2 * m + 3) * x * pmm
+            else:
+                a = math.sqrt((4 * l * l - 1) / (l * l - m * m))
+                b = math.sqrt(((l - 1) ** 2 - m * m) / (4 * (l - 1) ** 2 - 1))
+                p = a * (x * p_prev1 - b * p_prev2)
+            p_prev2, p_prev1 = p_prev1, p
+            if l == 0:
+                continue
+            amp = 1.0 / l
+            re = torch.randn(n_fields, generator=g, dtype=torch.float64)
+            im = torch.randn(n_fields, generator=g, dtype=torch.float64) if m > 0 else torch.zeros(n_fields, dtype=torch.float64)
+            coef = torch.complex(re, im) * amp
+            spec[:, :, m] += coef[:, None] * p[None, :]
+    f = torch.fft.irfft(spec, n=nlon, dim=-1)
+    f = f - f.mean(dim=(1, 2), keepdim=True)
+    f = f / f.std(dim=(1, 2), keepdim=True)
+    return f.float()
+
+
+def make_batch(batch: int, seed: int = 0):
+    C, H, W = CFG["in_channels"], CFG["inp_shape"][0], CFG["inp_shape"][1]
+    f = sh_random_fields(2 * batch * C, H, W, seed=seed).reshape(2, batch, C, H, W)
+    return f[0].contiguous(), f[1].contiguous()
+
+
+def build_model(dev, depth=None):
+    from ..models.afno import AFNO
+
+    torch.manual_seed(1234)
+    cfg = dict(CFG) if depth is None else dict(CFG, depth=depth)
+    return AFNO(**cfg).to(dev)
+
+
+def _rank_tokens(runner, x, y, dev):
+    """This rank's input tokens (feature order (c, p0, p1)) and target tokens ((p0, p1, c)) as pinned host tensors."""
+    from ..parallel.afno_sharded import patch_tokens
+
+    p = tuple(CFG["patch_size"])
+    xs, ys = [], []
+    for b, r0, r1, off, n in runner.token_rows():
+        xs.append(patch_tokens(x[b][:, r0 * p[0]: r1 * p[0]], p)[off: off + n])
+        ys.append(patch_tokens(y[b][:, r0 * p[0]: r1 * p[0]], p, channels_last_features=True)[off: off + n])
+    return torch.cat(xs).contiguous().pin_memory(), torch.cat(ys).contiguous().pin_memory()
+
+
+def _correctness(rank, world, dev, group, x, y):
+    """Sharded forward + parameter gradients (depth 2) against the stock single-GPU ``AFNO.forward`` on rank 0."""
+    import torch.distributed as dist
+
+    from ..parallel.afno_sharded import TokenShardedAFNO
+
+    model = build_model(dev, depth=2)
+    runner = TokenShardedAFNO(model, BATCH, group)
+    tin, tgt = (t.to(dev) for t in _rank_tokens(runner, x, y, dev))
+    out = runner(tin)
+    (((out.float() - tgt) ** 2).sum() / (BATCH * x[0].numel())).backward()
+    runner.step_done()
+    grads = {}
+    for k, p in model.named_parameters():
+        g = p.grad.detach().clone() if p.grad is not None else torch.zeros_like(p)
+        dist.all_reduce(g, group=group)
+        grads[k] = g
+    gathered = [torch.empty_like(out) for _ in range(world)]
+    dist.all_gather(gathered, out.contiguous(), group=group)
+    model.zero_grad(set_to_none=True)
+    fwd = worst = 0.0
+    name = ""
+    if rank == 0:
+        xb, yb = x.to(dev), y.to(dev)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            ref = model(xb)
+        ((ref.float() - yb) ** 2).sum().div(yb.numel()).backward()
+        p0, p1 = CFG["patch_size"]
+        B, C, H, W = ref.shape
+        ref_tok = ref.reshape(B, C, H // p0, p0, W // p1, p1).permute(0, 2, 4, 3, 5, 1).reshape(-1, p0 * p1 * C)
+        fwd = rel_err(torch.cat(gathered).float(), ref_tok.float())
+        for k, p in model.named_parameters():
+            if p.grad is None:
+                continue
+            e = rel_err(grads[k], p.grad)
+            if e > worst:
+                worst, name = e, k
+    t = torch.tensor([fwd, worst], device=dev, dtype=torch.float64)
+    dist.broadcast(t, src=0, group=group)
+    del model
+    torch.cuda.empty_cache()
+    return {"forward": float(t[0]), "worst_param_grad": float(t[1]), "worst_param": name,
+            "at": "full grid, batch 2, depth 2, vs the stock single-GPU forward on rank 0"}
+
+
+def run(args, rank: int, world: int, dev) -> dict:
+    import torch.distributed as dist
+
+    from .. import ops
+    from ..optim import FusedAdam
+    from ..parallel.afno_sharded import TokenShardedAFNO
+    from ..parallel.grad_reducer import GradBucketReducer
+    from ..parallel.peer import set_loopback
+
+    group = dist.group.WORLD if world > 1 else None
+    x, y = make_batch(BATCH, seed=0)
+    check = _correctness(rank, world, dev, group, x, y) if world > 1 else None
+    model = build_model(dev)
+    params = [p for p in model.parameters() if p.requires_grad]
+    reducer = GradBucketReducer(params, group=group, scale=1.0, wire="bf16") if world > 1 else None
+    opt = FusedAdam(params, lr=5e-4)
+    denom = float(BATCH * x[0].numel())
+    loss_host = torch.zeros(1, pin_memory=True)
+    state = {}
+    if world > 1:
+        runner = TokenShardedAFNO(model, BATCH, group)
+        host = list(_rank_tokens(runner, x, y, dev))
+
+        def fwd_loss(tin, tgt):
+            out = runner(tin)
+            return ((out.float() - tgt) ** 2).sum() / denom
+    else:
+        runner = None
+        host = [x.pin_memory(), y.pin_memory()]
+
+        def fwd_loss(xb, yb):
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                out = model(xb)
+            return ((out.float() - yb) ** 2).sum() / denom
+    del x, y
+    dev_in = [t.to(dev, non_blocking=True) for t in host]
+    torch.cuda.synchronize()
+
+    def train_step(a, b):
+        if reducer is not None:
+            reducer.zero_grad()
+        else:
+            opt.zero_grad(set_to_none=True)
+        loss = fwd_loss(a, b)
+        loss.backward()
+        if reducer is not None:
+            reducer.finish()
+        if runner is not None:
+            runner.step_done()
+        opt.step()
+        state["loss"] = loss.detach()
+
+    def step_resident():
+        train_step(*dev_in)
+
+    def step_e2e():
+        a, b = (t.to(dev, non_blocking=True) for t in host)
+        train_step(a, b)
+        loss_host.copy_(state["loss"].reshape(1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    flush = flush_buffer(dev)
+    step_resident()
+    torch.cuda.synchronize()
+    before = ops.kernel_launches()
+    step_resident()
+    torch.cuda.synchronize()
+    launches = ops.kernel_launches() - before
+    sampler = ClockSampler(dev.index or 0)
+    if rank == 0:
+        sampler.start()
+    ms, wall = timed_loop(step_resident, args.steps, max(args.warmup - 2, 1), world, dev, flush)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e, _ = timed_loop(step_e2e, max(2, args.steps // 2), 1, world, dev, flush)
+    exposed = None
+    if world > 1:
+        set_loopback(True)
+        ms_loop, _ = timed_loop(step_resident, max(2, args.steps // 2), 1, world, dev, flush)
+        set_loopback(False)
+        exposed = max(0.0, ms - ms_loop)
+        step_resident()
+    err = ops.device_error()
+    if world > 1:
+        total = loss_host.to(dev)
+        dist.all_reduce(total)
+        loss_host.copy_(total)
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    return base_line(
+        BATCH * 1000.0 / ms, ms, world, args, "strong",
+        "synthetic (seeded spherical-harmonic random fields, spectrum l^-2, N(0,1)-normalised; random-init weights)",
+        {"model": DESC, "global_batch": BATCH, "seq_len": 90 * 180,
+         "parallelism": f"tokens sharded x{world}; filter: {8 // world} channel block(s) per rank, resharding fused into the "
+                        "Fourier kernels" if world > 1 else "single GPU",
+         "optimizer": "Adam (fused)", "cuda_graph": False,
+         "l2": "256 MB buffer rewritten between timed steps"},
+        clocks,
+        {"value": BATCH * 1000.0 / ms_e2e, "unit": "samples/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
+         "d2h_bytes_per_step": 4},
+        launches,
+        {"exposed_comm_ms": exposed, "sharded_vs_single_rel_err": check, "device_error_word": err,
+         "loss": float(loss_host.item()), "wall_s_timed_region": wall,
+         "exposed_comm_how": "step time minus the time of the same step with all peer traffic switched off (loopback)"})

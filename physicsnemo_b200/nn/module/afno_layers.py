@@ -81,8 +81,19 @@ class AFNO2DLayer(nn.Module):
                 raise ValueError(f"Expected 4D input (B, H, W, C), got {x.ndim}D tensor with shape {tuple(x.shape)}")
         bias = x
         dtype = x.dtype
-        x = x.float()
         B, H, W, C = x.shape
+        if type(x) is torch.Tensor and ops.fused_path_enabled(x) and self.hard_thresholding_fraction == 1 \
+                and self.hidden_size_factor == 1 and self.w1.dtype == torch.float32:
+            # CUDA, bf16 compute: the library's own Fourier kernels (pruned row DFTs, two-level column DFT, complex block
+            # MLP and soft-shrink in one kernel); no library FFT, no complex einsums
+            from ...ops import afno_spectral as _af
+
+            geo = _af.FilterGeometry(B, H, W, C, self.num_blocks, H // 2 + 1)
+            if geo.supported():
+                y = _af.afno_filter(x.reshape(-1, C).to(torch.bfloat16), self.w1, self.b1, self.w2, self.b2, geo,
+                                    self.sparsity_threshold)
+                return y.reshape(B, H, W, C).to(dtype) + bias
+        x = x.float()
         xf = fft.rfft2(x, dim=(1, 2), norm="ortho")
         Wf = W // 2 + 1
         total_modes = H // 2 + 1
@@ -118,6 +129,12 @@ class AFNOPatchEmbed(nn.Module):
             c, h, w = self.proj.in_channels, self.inp_shape[0], self.inp_shape[1]
             if x.ndim != 4 or x.shape[1] != c or x.shape[2] != h or x.shape[3] != w:
                 raise ValueError(f"Expected input shape (B, {c}, {h}, {w}), got {tuple(x.shape)}")
+        if type(x) is torch.Tensor and ops.fused_path_enabled(x):
+            # stride == kernel: the convolution is a GEMM over non-overlapping patches
+            B, C, H, W = x.shape
+            p0, p1 = self.patch_size
+            t = x.reshape(B, C, H // p0, p0, W // p1, p1).permute(0, 2, 4, 1, 3, 5).reshape(B, -1, C * p0 * p1)
+            return ops.linear(t.to(torch.bfloat16), self.proj.weight.reshape(self.proj.weight.shape[0], -1), self.proj.bias)
         return self.proj(x).flatten(2).transpose(1, 2)
 
 

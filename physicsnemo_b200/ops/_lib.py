@@ -53,13 +53,17 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         return _LIB_PATH
     _LIB_DIR.mkdir(parents=True, exist_ok=True)
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc, *NVCC_FLAGS, "-o", str(_LIB_PATH), *[str(p) for p in sorted(_SRC_DIR.glob("*.cu"))]]
+    tmp_out = _LIB_DIR / f".libpnm_b200.{os.getpid()}.so.tmp"     # built aside, then moved into place in one step
+    cmd = [nvcc, *NVCC_FLAGS, "-o", str(tmp_out), *[str(p) for p in sorted(_SRC_DIR.glob("*.cu"))]]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
+        if tmp_out.exists():
+            tmp_out.unlink()
         raise RuntimeError(f"nvcc failed:\n{proc.stdout}\n{proc.stderr}")
+    os.replace(tmp_out, _LIB_PATH)
     if verbose:
         print(proc.stderr)
     return _LIB_PATH

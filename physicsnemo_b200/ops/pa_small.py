@@ -14,7 +14,7 @@ S = 64  # slices per head covered by the kernels
 
 def _lib_pa():
     lib = _lib.load(required=True)
-    if not getattr(lib, "_pa_declared", False):
+    if not getattr(lib, "_pasmall_declared", False):
         c = ctypes
         vp, i, u, ll, f, d = c.c_void_p, c.c_int, c.c_uint, c.c_longlong, c.c_float, c.c_double
         lib.pnm_pa_prepare_fwd.argtypes = [vp] * 11 + [i, i, i, vp]
@@ -23,7 +23,7 @@ def _lib_pa():
         lib.pnm_pa_prepare_bwd.argtypes = [vp] * 12 + [i, i, i, vp]
         for n in ("pnm_pa_prepare_fwd", "pnm_pa_tokens_fwd", "pnm_pa_tokens_bwd", "pnm_pa_prepare_bwd"):
             getattr(lib, n).restype = i
-        lib._pa_declared = True
+        lib._pasmall_declared = True
     return lib
 
 

@@ -510,3 +510,39 @@ def test_bounded_wait_gives_up_and_context_survives():
     assert rc == 0 and int(status.item()) == 1 and lib.pnm_get_error() == 0
     a = torch.randn(64, 64, device="cuda")
     assert torch.isfinite(a @ a).all()                  # the context is intact
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(2, 90, 180, 768, 8), (1, 12, 20, 64, 2), (2, 15, 36, 96, 1)])
+def test_afno_spectral_filter_kernels(shape):
+    """Own Fourier kernels (pruned row DFTs, two-level column DFT, complex block MLP, soft-shrink) vs torch.fft in fp32."""
+    from physicsnemo_b200.nn.module.afno_layers import AFNO2DLayer
+    from physicsnemo_b200.ops import afno_spectral as A
+
+    B, H, W, C, nb = shape
+    torch.manual_seed(0)
+    layer = AFNO2DLayer(C, num_blocks=nb, sparsity_threshold=0.01).cuda()
+    with torch.no_grad():
+        for p in layer.parameters():
+            p.mul_(5.0)                                    # well away from the shrink threshold
+    x = torch.randn(B, H, W, C, device="cuda").to(torch.bfloat16)
+    xr = x.float().requires_grad_(True)
+    ref = layer(xr) - xr                                   # the filter without its residual
+    dy = torch.randn_like(ref)
+    ref.backward(dy)
+    gref = [p.grad.clone() for p in layer.parameters()]
+    layer.zero_grad()
+    kept = int((H // 2 + 1) * layer.hard_thresholding_fraction)
+    geo = A.FilterGeometry(B, H, W, C, nb, kept)
+    assert geo.supported()
+    tok = x.reshape(-1, C).clone().requires_grad_(True)
+    out = A.afno_filter(tok, layer.w1, layer.b1, layer.w2, layer.b2, geo, layer.sparsity_threshold)
+    out.backward(dy.reshape(-1, C).to(out.dtype))
+
+    def rel(a, r):
+        return float((a.float() - r.float()).abs().max()) / max(float(r.float().abs().max()), 1e-12)
+
+    assert rel(out.reshape(B, H, W, C), ref) < 2e-2
+    assert rel(tok.grad.reshape(B, H, W, C), xr.grad) < 2e-2
+    for p, g in zip(layer.parameters(), gref):
+        assert rel(p.grad, g) < 2e-2
