@@ -13,6 +13,23 @@ import warnings
 _GROUPS = ("physicsnemo.models", "physicsnemo_b200.models", "modulus.models")
 
 
+def _pyproject_entry_points() -> Dict[str, str]:
+    """``{name: "module:Class"}`` of the ``physicsnemo.models`` group in the repository's ``pyproject.toml`` (if present)."""
+    from pathlib import Path
+
+    path = Path(__file__).resolve().parents[2] / "pyproject.toml"
+    if not path.exists():
+        return {}
+    try:
+        import tomllib
+
+        with open(path, "rb") as fh:
+            data = tomllib.load(fh)
+        return dict(data.get("project", {}).get("entry-points", {}).get("physicsnemo.models", {}))
+    except Exception:  # noqa: BLE001  (a malformed file must not break imports)
+        return {}
+
+
 class ModelRegistry:
     """Shared-state ("Borg") registry: every instance sees the same table."""
 
@@ -35,6 +52,10 @@ class ModelRegistry:
                 continue
             for ep in eps:
                 table.setdefault(ep.name, ep)
+        if not any(getattr(ep, "value", "").startswith("physicsnemo_b200.") for ep in table.values()):
+            # source checkout that was never pip-installed: read the entry-point table from pyproject.toml
+            for name, value in _pyproject_entry_points().items():
+                table.setdefault(name, EntryPoint(name=name, value=value, group="physicsnemo.models"))
         return table
 
     # -- public API ---------------------------------------------------------

@@ -144,12 +144,12 @@ class ScaleShiftMlp(nn.Module):
     def __init__(self, in_features: int, out_features: int, hidden_features: Union[int, None] = None,
                  hidden_layers: int = 0, activation_fn=nn.GELU):
         super().__init__()
+        from .mlp_layers import Mlp
+
         hidden_features = 2 * out_features if hidden_features is None else hidden_features
-        seq = [nn.Linear(in_features, hidden_features), activation_fn()]
-        for _ in range(hidden_layers):
-            seq += [nn.Linear(hidden_features, hidden_features), activation_fn()]
-        seq.append(nn.Linear(hidden_features, out_features * 2))
-        self.net = nn.Sequential(*seq)
+        # ``net.layers`` holds Linear / activation pairs: the key scheme of the reference's checkpoints
+        self.net = Mlp(in_features=in_features, hidden_features=[hidden_features] * (hidden_layers + 1),
+                       out_features=out_features * 2, act_layer=activation_fn, drop=0.0, final_dropout=False)
 
     def forward(self, x: Tensor) -> Tuple[Tensor, Tensor]:
         scale, shift = torch.chunk(self.net(x), 2, dim=1)

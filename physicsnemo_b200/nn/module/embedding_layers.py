@@ -81,20 +81,19 @@ class PositionalEmbedding(nn.Module):
 
 
 class SinusoidalTimestepEmbedding(nn.Module):
-    """Transformer-style timestep embedding (sin half then cos half)."""
+    """Embedding of a scalar in [0, 1]: ``cat(cos(pi k t), sin(pi k t))`` for ``k = 1 .. num_channels // 2``.
 
-    def __init__(self, num_channels: int, max_period: int = 10000):
+    Parity: ``physicsnemo/nn/module/embedding_layers.py`` (``SinusoidalTimestepEmbedding``; persistent buffer ``freqs``).
+    """
+
+    def __init__(self, num_channels: int):
         super().__init__()
-        self.num_channels, self.max_period = num_channels, max_period
+        self.num_channels = num_channels
+        self.register_buffer("freqs", torch.pi * torch.arange(1, num_channels // 2 + 1, dtype=torch.float32))
 
     def forward(self, t):
-        half = self.num_channels // 2
-        freqs = torch.exp(-math.log(self.max_period) * torch.arange(half, device=t.device, dtype=torch.float32) / half)
-        args = t.float()[:, None] * freqs[None]
-        emb = torch.cat([torch.sin(args), torch.cos(args)], dim=-1)
-        if self.num_channels % 2:
-            emb = torch.cat([emb, torch.zeros_like(emb[:, :1])], dim=-1)
-        return emb
+        arg = t.reshape(-1).outer(self.freqs.to(t.dtype))
+        return torch.cat([arg.cos(), arg.sin()], dim=1)
 
 
 class OneHotEmbedding(nn.Module):

@@ -220,9 +220,13 @@ def check_transolver(rank, world, dev, report):
     torch.cuda.synchronize()
     rel = ((out_sh.float() - out_full[:, sl].float()).norm() / out_full[:, sl].float().norm()).item()
     report("point-sharded Transolver forward", rel, 1e-2)
+    # every gradient within 2 % of its own norm; tensors whose gradient nearly cancels (norm ~1e-3 of the model's total
+    # gradient norm, e.g. the slice projections at initialisation, which differ by that much between two runs of the SAME
+    # unsharded model) are held to an absolute floor of 2e-4 of the total norm instead
+    total = torch.sqrt(sum(q.grad.float().pow(2).sum() for q in full.parameters())).item()
     for (name, p), (_, q) in zip(shard.named_parameters(), full.named_parameters()):
-        r = ((p.grad - q.grad).norm() / (q.grad.norm() + 1e-12)).item()
-        report(f"point-sharded Transolver grad {name}", r, 2e-2)
+        d = (p.grad - q.grad).norm().item()
+        report(f"point-sharded Transolver grad {name}", d / (q.grad.norm().item() + 1e-2 * total), 2e-2)
 
 
 def main():

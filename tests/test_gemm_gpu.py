@@ -13,10 +13,13 @@ def _rand(*shape, scale=1.0):
 
 
 def _close(out, ref, tol=2e-2):
+    """Element-wise: |out - ref| <= tol/2 * |ref| + tol/2 * rms(ref) (bf16 rounding is 0.4 % of the element; the floor
+    covers entries that are small because their terms cancel, whose error scales with the typical size instead)."""
     out, ref = out.float(), ref.float()
-    err = (out - ref).abs().max().item()
-    denom = ref.abs().max().item() + 1e-6
-    assert err <= tol * max(1.0, denom), f"max abs err {err} (ref max {denom})"
+    rms = ref.pow(2).mean().sqrt().item() + 1e-6
+    excess = (out - ref).abs() - (0.5 * tol * ref.abs() + 0.5 * tol * rms)
+    worst = excess.max().item()
+    assert worst <= 0, f"worst excess over the element-wise bound {worst} (rms of the reference {rms})"
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (300, 256, 256), (1000, 64, 128), (257, 264, 72), (20000, 512, 256)])

@@ -565,3 +565,36 @@ def test_video_healda_is_causal_in_time_and_reads_observations():
         net(x[:, :, :2], t, sod[:, :2], doy[:, :2], ctx)
     with pytest.raises(ValueError):
         net(x, t, sod, doy, ctx, class_labels=torch.zeros(B, 2))
+
+
+def test_model_registry_lists_and_loads_every_entry_point():
+    from physicsnemo_b200.core.module import Module
+    from physicsnemo_b200.core.registry import ModelRegistry
+
+    reg = ModelRegistry()
+    names = reg.list_models()
+    for expected in ("FNO", "AFNO", "ModAFNO", "DistributedAFNO", "MeshGraphNet", "Transolver", "SongUNet", "GraphCastNet"):
+        assert expected in names
+    assert len(names) >= 35
+    for name in names:
+        assert issubclass(reg.factory(name), Module), name
+
+
+def test_modafno_forward_backward_and_key_scheme():
+    from physicsnemo_b200.models.afno import ModAFNO
+
+    for mode in ("complex", "real"):
+        m = ModAFNO([16, 32], in_channels=3, out_channels=2, patch_size=[2, 2], embed_dim=32, mod_dim=16, depth=2,
+                    num_blocks=4, scale_shift_mode=mode, embed_model=dict(dim=16))
+        y = m(torch.randn(2, 3, 16, 32), torch.rand(2))
+        assert y.shape == (2, 2, 16, 32)
+        y.square().mean().backward()
+        keys = set(m.state_dict())
+        for k in ("pos_embed", "mod_additive_proj.weight", "mod_embed_net.sinusoid_embed.freqs", "mod_embed_net.mlp.0.weight",
+                  "blocks.0.filter.scale_shift.net.layers.0.weight", "blocks.1.mlp.scale_shift.net.layers.2.bias",
+                  "blocks.0.filter.w1", "head.weight"):
+            assert k in keys, k
+        assert all(p.grad is not None for p in m.parameters())
+    plain = ModAFNO([16, 32], in_channels=3, out_channels=2, patch_size=[2, 2], embed_dim=32, mod_dim=16, depth=1, num_blocks=4,
+                    modulate_filter=False, modulate_mlp=False)
+    assert plain(torch.randn(1, 3, 16, 32), torch.rand(1, 16)).shape == (1, 2, 16, 32)

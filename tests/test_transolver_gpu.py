@@ -38,11 +38,16 @@ def test_fused_block_matches_fp32_reference():
     loss_ref.backward()
     assert ops.device_error() == 0
     assert _rel(out, out_ref) < 3e-2, _rel(out, out_ref)
+    # every gradient within 2 % of its own norm plus 1 % of the model's total gradient norm (the floor covers tensors
+    # whose gradient nearly cancels at this point, e.g. the slice projections: they move by a few % of their own tiny
+    # norm between two runs of the same bf16 model)
+    total = torch.sqrt(sum(q.grad.float().pow(2).sum() for q in ref.parameters())).item()
     bad = []
     for (name, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
         assert p.grad is not None, name
-        r = _rel(p.grad, q.grad)
-        if r > 0.2:
+        d = (p.grad.float() - q.grad.float()).norm().item()
+        r = d / (q.grad.float().norm().item() + 1e-2 * total)
+        if r > 2e-2:
             bad.append((name, r))
     assert not bad, bad
 
