@@ -338,7 +338,127 @@ def _fno_step(model, opt, x, y):
     return loss.item()
 
 
-_RUNNERS = {"transolver": _transolver, "songunet": _songunet, "fno": _fno}
+# -------------------------------------------------------------------------------------------------------- AFNO
+def _afno(args, rank, world, dev):
+    """Stock ``AFNO`` on one GPU; ``DistributedAFNO`` (channel parallel over the group "model_parallel") on several."""
+    import math
+
+    batch = 2
+    cfg = dict(inp_shape=[720, 1440], in_channels=73, out_channels=73, patch_size=[8, 8], embed_dim=768, depth=12, num_blocks=8,
+               sparsity_threshold=0.01)
+    x, y = _sh_fields(batch, 73, 720, 1440, seed=0)
+    torch.manual_seed(1234)
+    if world == 1:
+        from physicsnemo.models.afno import AFNO  # type: ignore
+
+        model = AFNO(**cfg).to(dev)
+        para = "single GPU"
+    else:
+        from physicsnemo.distributed import DistributedManager  # type: ignore
+        from physicsnemo.models.afno import DistributedAFNO  # type: ignore
+
+        if not DistributedManager.is_initialized():
+            DistributedManager.initialize()
+        dm = DistributedManager()
+        if "model_parallel" not in dm.group_names:
+            DistributedManager.create_process_subgroup("model_parallel", world, verbose=False)
+        model = DistributedAFNO(inp_shape=(720, 1440), in_channels=73, out_channels=73, patch_size=8, embed_dim=768, depth=12,
+                                num_blocks=8, channel_parallel_inputs=False, channel_parallel_outputs=False).to(dev)
+        para = f"channel parallel x{world} (the reference's DistributedAFNO)"
+    opt = torch.optim.Adam(model.parameters(), lr=5e-4, fused=True)
+    host = [x.pin_memory(), y.pin_memory()]
+    dev_in = [t.to(dev, non_blocking=True) for t in host]
+    denom = float(y.numel())
+    loss_host = torch.zeros(1, pin_memory=True)
+    state = {}
+
+    def train_step(xb, yb):
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            out = model(xb)
+        loss = ((out.float() - yb) ** 2).sum() / denom
+        loss.backward()
+        opt.step()
+        state["loss"] = loss.detach()
+
+    def resident():
+        train_step(*dev_in)
+
+    def e2e():
+        a, b = (t.to(dev, non_blocking=True) for t in host)
+        train_step(a, b)
+        loss_host.copy_(state["loss"].reshape(1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    flush = torch.empty(256 * 1024 * 1024 // 4, device=dev)
+    sampler = _Clocks(dev.index or 0)
+    resident()
+    torch.cuda.synchronize()
+    if rank == 0:
+        sampler.start()
+    ms, wall = _timed(resident, args.steps, max(args.warmup - 2, 1), world, dev, flush)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e, _ = _timed(e2e, max(2, args.steps // 2), 1, world, dev, flush)
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    return _line(batch * 1000.0 / ms, ms, ms_e2e, batch * 1000.0 / ms_e2e, world, args,
+                 {"model": "AFNO 720x1440: patch 8x8, embed 768, depth 12, 8 blocks, mlp ratio 4, soft-shrink 0.01",
+                  "global_batch": batch, "seq_len": 90 * 180, "parallelism": para, "optimizer": "Adam (fused)", "cuda_graph": False,
+                  "_data": "synthetic (seeded spherical-harmonic random fields, spectrum l^-2, N(0,1)-normalised; random-init weights)"},
+                 clocks, h2d, float(loss_host.item()), wall)
+
+
+def _sh_fields(batch, channels, nlat, nlon, lmax=64, seed=0):
+    """Two ``[batch, channels, nlat, nlon]`` tensors of band-limited spherical-harmonic random fields, power ~ l^-2."""
+    import math
+
+    n_fields = 2 * batch * channels
+    g = torch.Generator().manual_seed(seed)
+    theta = (torch.arange(nlat, dtype=torch.float64) + 0.5) * math.pi / nlat
+    x, s = torch.cos(theta), torch.sin(theta)
+    spec = torch.zeros(n_fields, nlat, nlon // 2 + 1, dtype=torch.complex128)
+    pmm = torch.full((nlat,), math.sqrt(1.0 / (4 * math.pi)), dtype=torch.float64)
+    for m in range(lmax + 1):
+        if m > 0:
+            pmm = -math.sqrt((2 * m + 1) / (2 * m)) * s * pmm
+        p2, p1 = None, pmm
+        for l in range(m, lmax + 1):
+            if l == m:
+                p = pmm
+            elif l == m + 1:
+                p = math.sqrt(2 * m + 3) * x * pmm
+            else:
+                a = math.sqrt((4 * l * l - 1) / (l * l - m * m))
+                b = math.sqrt(((l - 1) ** 2 - m * m) / (4 * (l - 1) ** 2 - 1))
+                p = a * (x * p1 - b * p2)
+            p2, p1 = p1, p
+            if l == 0:
+                continue
+            re = torch.randn(n_fields, generator=g, dtype=torch.float64)
+            im = torch.randn(n_fields, generator=g, dtype=torch.float64) if m > 0 else torch.zeros(n_fields, dtype=torch.float64)
+            spec[:, :, m] += (torch.complex(re, im) / l)[:, None] * p[None, :]
+    f = torch.fft.irfft(spec, n=nlon, dim=-1)
+    f = f - f.mean(dim=(1, 2), keepdim=True)
+    f = (f / f.std(dim=(1, 2), keepdim=True)).float().reshape(2, batch, channels, nlat, nlon)
+    return f[0].contiguous(), f[1].contiguous()
+
+
+# ------------------------------------------------------------------------------------------------- MeshGraphNet
+def _mgn(args, rank, world, dev):
+    if world > 1:
+        return _unavailable("the reference cannot run MeshGraphNet on a partitioned graph: its distributed graph is not wired into "
+                            "MeshGraphNet.forward and graph partitioning raises NotImplementedError with its PyG backend "
+                            "(models/graphcast/graph_cast_net.py:288-296)")
+    import importlib
+
+    for name in ("torch_geometric", "torch_scatter"):
+        spec = importlib.util.find_spec(name)
+        if spec is None or getattr(spec.loader, "__class__", type(None)).__name__ == "_StubFinder":
+            return _unavailable(f"the reference MeshGraphNet needs {name} (gnn_layers/utils.py:83-84, torch_scatter.scatter at :276), "
+                                "which is neither installed in this image nor in the offline wheelhouse")
+    return _unavailable("reference MeshGraphNet arm not reached")
+
+
+_RUNNERS = {"transolver": _transolver, "songunet": _songunet, "fno": _fno, "afno": _afno, "mgn": _mgn}
 
 
 def run(name, args, rank, world, dev, root):

@@ -45,6 +45,14 @@ __device__ __forceinline__ const __nv_bfloat16* token_addr(const TokenPtrs& tp, 
   return tp.p[owner] + (t - owner * g.Tp) * g.C + c;
 }
 
+__device__ __forceinline__ void sm_unpack8(const uint4& u, float* f) {
+  float2 a;
+  a = unpack_bf16x2(u.x); f[0] = a.x; f[1] = a.y;
+  a = unpack_bf16x2(u.y); f[2] = a.x; f[3] = a.y;
+  a = unpack_bf16x2(u.z); f[4] = a.x; f[5] = a.y;
+  a = unpack_bf16x2(u.w); f[6] = a.x; f[7] = a.y;
+}
+
 // ---------------------------------------------------------------------------------------------------- rows: r2c
 // Y[(row * KX + kx) * (nblk * Cb) + j * Cb + c] = kweight(kx) / sqrt(W) * sum_w x[row, w, blk c] e^{-2 pi i kx w / W}
 // kweight: 0 -> 1 for every kx (forward);  1 -> 1 for kx = 0 and 2 otherwise (adjoint of the weighted c2r)
@@ -139,6 +147,194 @@ afno_rows_c2r_kernel(const float2* __restrict__ X, TokenPtrs tok, AfGeom g, int 
         if (idx >= g.W) idx -= g.W;
       }
       ys[w * g.Cb + c] = __float2bfloat16(acc * inv);
+    }
+  }
+  __syncthreads();
+  const int c0 = (g.blk0 + j) * g.Cb;
+  const int vec = g.Cb >> 3;
+  for (int i = tid; i < g.W * vec; i += nt) {
+    const int w = i / vec, v = i % vec;
+    const uint4 u = *reinterpret_cast<const uint4*>(ys + w * g.Cb + v * 8);
+    *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(token_addr(tok, g, (long long)row * g.W + w, c0 + v * 8))) = u;
+  }
+  if (signal) {
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0 && atomicAdd(counter, 1u) == gridDim.x * gridDim.y - 1) {
+      *counter = 0;
+      peer_small_publish(peer, peer_epoch(peer));
+    }
+  }
+}
+
+
+// ------------------------------------------------------------------------- rows, register-blocked form (W even)
+// The same two transforms at several times the arithmetic rate of the kernels above, which issue two shared loads and
+// an index update for every multiply-add pair.  Three changes:
+//   * real-input symmetry: with e[w] = x[w] + x[W-w] and o[w] = x[w] - x[W-w] (w = 1 .. W/2-1),
+//       Re X[k] = x[0] + (-1)^k x[W/2] + sum_w e[w] cos(2 pi k w / W),   Im X[k] = - sum_w o[w] sin(2 pi k w / W),
+//     and in the other direction y[w] = A[w] - B[w], y[W-w] = A[w] + B[w] from the cosine / sine sums: half the work;
+//   * a thread owns TWO adjacent channels and kRowNK modes (positions), so a twiddle fetched from shared memory
+//     (a [w][k] table with the product index already reduced mod W, read as 16-byte vectors) feeds eight
+//     multiply-adds and the x / X operands are reused kRowNK times from registers;
+//   * 4 kRowNK independent accumulators per thread hide the multiply-add latency without more warps.
+constexpr int kRowNK = 6;
+
+struct RowPlan { int groups, passes, pad, threads; };
+
+static RowPlan row_plan(int n_items, int cb) {
+  const int cp = cb / 2;
+  const int blocks = (n_items + kRowNK - 1) / kRowNK;
+  const int max_groups = 512 / cp > 0 ? 512 / cp : 1;
+  RowPlan p;
+  p.passes = (blocks + max_groups - 1) / max_groups;
+  p.groups = (blocks + p.passes - 1) / p.passes;
+  p.pad = p.passes * p.groups * kRowNK;
+  p.threads = ((cp * p.groups + 31) / 32) * 32;
+  if (p.threads < 128) p.threads = 128;
+  return p;
+}
+
+__global__ void __launch_bounds__(512)
+afno_rows_r2c_v2_kernel(TokenPtrs tok, float2* __restrict__ Y, AfGeom g, int kweight, PeerArgs peer, int wait, int* err, int groups,
+                        int passes) {
+  extern __shared__ float sm[];
+  __shared__ int sh_ok;
+  const int Wh = g.W >> 1, nfold = Wh - 1, CP = g.Cb >> 1;
+  const int pad = passes * groups * kRowNK;
+  float* xe = sm;                                    // [nfold][Cb]
+  float* xo = xe + (size_t)nfold * g.Cb;             // [nfold][Cb]
+  float* x0 = xo + (size_t)nfold * g.Cb;             // [Cb]   sample w = 0
+  float* xh = x0 + g.Cb;                             // [Cb]   sample w = W/2
+  float2* tw2 = reinterpret_cast<float2*>(xh + g.Cb);   // [nfold][pad]: (cos, sin)(2 pi ((k w) mod W) / W), w = row + 1
+  const int row = blockIdx.x, j = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
+  bool ok = true;
+  if (wait) ok = peer_small_wait(peer, peer_epoch(peer), err, &sh_ok);
+  for (int i = tid; i < nfold * pad; i += nt) {
+    const int w = i / pad + 1, k = i % pad;
+    float sn, cs;
+    sincospif(2.f * ((k * w) % g.W) / g.W, &sn, &cs);
+    tw2[i] = make_float2(cs, sn);
+  }
+  const int c0 = (g.blk0 + j) * g.Cb;
+  const int vec = g.Cb >> 3;
+  const float nanv = __int_as_float(0x7fc00000);
+  for (int i = tid; i < (Wh + 1) * vec; i += nt) {
+    const int w = i / vec, v = i % vec;
+    float f[8], h[8];
+    const bool pair = w > 0 && w < Wh;
+    if (ok) {
+      sm_unpack8(__ldcg(reinterpret_cast<const uint4*>(token_addr(tok, g, (long long)row * g.W + w, c0 + v * 8))), f);
+      if (pair) sm_unpack8(__ldcg(reinterpret_cast<const uint4*>(token_addr(tok, g, (long long)row * g.W + g.W - w, c0 + v * 8))), h);
+    } else {
+      for (int q = 0; q < 8; ++q) f[q] = h[q] = nanv;
+    }
+    if (pair) {
+      for (int q = 0; q < 8; ++q) {
+        xe[(w - 1) * g.Cb + v * 8 + q] = f[q] + h[q];
+        xo[(w - 1) * g.Cb + v * 8 + q] = f[q] - h[q];
+      }
+    } else {
+      float* dst = w == 0 ? x0 : xh;
+      for (int q = 0; q < 8; ++q) dst[v * 8 + q] = f[q];
+    }
+  }
+  __syncthreads();
+  const int cp = tid % CP, kg = tid / CP;
+  if (kg >= groups) return;
+  const float inv = rsqrtf((float)g.W);
+  const int ldy = g.nblk * g.Cb;
+  const float2* xe2 = reinterpret_cast<const float2*>(xe);
+  const float2* xo2 = reinterpret_cast<const float2*>(xo);
+  const float2 a0 = reinterpret_cast<const float2*>(x0)[cp], ah = reinterpret_cast<const float2*>(xh)[cp];
+  for (int pass = 0; pass < passes; ++pass) {
+    const int k0 = (pass * groups + kg) * kRowNK;
+    if (k0 >= g.KX) break;
+    float re0[kRowNK], re1[kRowNK], im0[kRowNK], im1[kRowNK];
+#pragma unroll
+    for (int q = 0; q < kRowNK; ++q) re0[q] = re1[q] = im0[q] = im1[q] = 0.f;
+    for (int wi = 0; wi < nfold; ++wi) {
+      const float2 e = xe2[wi * CP + cp], o = xo2[wi * CP + cp];
+      const float4* t4 = reinterpret_cast<const float4*>(tw2 + (size_t)wi * pad + k0);
+#pragma unroll
+      for (int q = 0; q < kRowNK / 2; ++q) {
+        const float4 t = t4[q];
+        re0[2 * q] += e.x * t.x;      re1[2 * q] += e.y * t.x;
+        im0[2 * q] -= o.x * t.y;      im1[2 * q] -= o.y * t.y;
+        re0[2 * q + 1] += e.x * t.z;  re1[2 * q + 1] += e.y * t.z;
+        im0[2 * q + 1] -= o.x * t.w;  im1[2 * q + 1] -= o.y * t.w;
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < kRowNK; ++q) {
+      const int kx = k0 + q;
+      if (kx < g.KX) {
+        const float sg = (kx & 1) ? -1.f : 1.f;
+        const float s = inv * ((kweight && kx > 0) ? 2.f : 1.f);
+        float4 out;
+        out.x = (re0[q] + a0.x + sg * ah.x) * s;  out.y = im0[q] * s;
+        out.z = (re1[q] + a0.y + sg * ah.y) * s;  out.w = im1[q] * s;
+        *reinterpret_cast<float4*>(Y + ((size_t)row * g.KX + kx) * ldy + j * g.Cb + 2 * cp) = out;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(512)
+afno_rows_c2r_v2_kernel(const float2* __restrict__ X, TokenPtrs tok, AfGeom g, int kweight, PeerArgs peer, int signal,
+                        unsigned int* counter, int groups, int passes) {
+  extern __shared__ float sm[];
+  const int Wh = g.W >> 1, CP = g.Cb >> 1;
+  const int pad = passes * groups * kRowNK;                       // >= W/2 + 1 positions w = 0 .. W/2
+  float2* xs = reinterpret_cast<float2*>(sm);                     // [KX][Cb] spectrum, weighted
+  float2* twT = xs + (size_t)g.KX * g.Cb;                         // [KX][pad]
+  __nv_bfloat16* ys = reinterpret_cast<__nv_bfloat16*>(twT + (size_t)g.KX * pad);   // [W][Cb]
+  const int row = blockIdx.x, j = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
+  const int ldx = g.nblk * g.Cb;
+  for (int i = tid; i < g.KX * pad; i += nt) {
+    const int kx = i / pad, w = i % pad;
+    float sn, cs;
+    sincospif(2.f * ((kx * w) % g.W) / g.W, &sn, &cs);
+    twT[i] = make_float2(cs, sn);
+  }
+  for (int i = tid; i < g.KX * g.Cb; i += nt) {
+    const int kx = i / g.Cb, c = i % g.Cb;
+    const float2 v = X[((size_t)row * g.KX + kx) * ldx + j * g.Cb + c];
+    const float s = (kweight && kx > 0) ? 2.f : 1.f;
+    xs[i] = make_float2(v.x * s, v.y * s);
+  }
+  __syncthreads();
+  const int cp = tid % CP, wg = tid / CP;
+  if (wg < groups) {
+    const float inv = rsqrtf((float)g.W);
+    const float4* xs4 = reinterpret_cast<const float4*>(xs);
+    for (int pass = 0; pass < passes; ++pass) {
+      const int w0 = (pass * groups + wg) * kRowNK;
+      if (w0 > Wh) break;
+      float A0[kRowNK], A1[kRowNK], B0[kRowNK], B1[kRowNK];
+#pragma unroll
+      for (int q = 0; q < kRowNK; ++q) A0[q] = A1[q] = B0[q] = B1[q] = 0.f;
+      for (int kx = 0; kx < g.KX; ++kx) {
+        const float4 xv = xs4[kx * CP + cp];                      // (re, im) of the two channels
+        const float4* t4 = reinterpret_cast<const float4*>(twT + (size_t)kx * pad + w0);
+#pragma unroll
+        for (int q = 0; q < kRowNK / 2; ++q) {
+          const float4 t = t4[q];
+          A0[2 * q] += xv.x * t.x;      B0[2 * q] += xv.y * t.y;
+          A1[2 * q] += xv.z * t.x;      B1[2 * q] += xv.w * t.y;
+          A0[2 * q + 1] += xv.x * t.z;  B0[2 * q + 1] += xv.y * t.w;
+          A1[2 * q + 1] += xv.z * t.z;  B1[2 * q + 1] += xv.w * t.w;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < kRowNK; ++q) {
+        const int w = w0 + q;
+        if (w <= Wh) {
+          *reinterpret_cast<uint32_t*>(ys + w * g.Cb + 2 * cp) = pack_bf16x2((A0[q] - B0[q]) * inv, (A1[q] - B1[q]) * inv);
+          if (w > 0 && w < Wh)
+            *reinterpret_cast<uint32_t*>(ys + (g.W - w) * g.Cb + 2 * cp) = pack_bf16x2((A0[q] + B0[q]) * inv, (A1[q] + B1[q]) * inv);
+        }
+      }
     }
   }
   __syncthreads();
@@ -396,6 +592,176 @@ afno_cols_bwd_kernel(const float2* __restrict__ dYout, float2* __restrict__ dY, 
   }
 }
 
+// ---------------------------------------------------------------------- columns, split form (MLP on the tensor cores)
+// The two-layer complex MLP is two real GEMMs on the [real | imag] expansion of the spectrum, so under bf16 compute it
+// belongs on the tcgen05 GEMM kernel (the reference's einsums run in bf16 under autocast as well).  The two kernels below
+// are the Fourier halves around those GEMMs.  E: bf16 [nblk][Mp][2 Cb] with row (b*KX + kx)*H + ky of a block's Mp
+// (>= B*KX*H, the GEMM's padding) rows, columns [real | imag].
+//   cols_dft : E = DFT_H(Y) (sign -1), optionally masked: entries whose counterpart in `mask` (same layout, the pre-shrink
+//              MLP output of the forward) has magnitude <= lambda are zeroed (backward of the soft-shrink)
+//   cols_idft: Yout = IDFT_H(softshrink_lambda(E)) (sign +1; lambda = 0 leaves E unchanged)
+// ------------------------------------------------- columns, register-blocked form of the split (tensor-core MLP) stage
+// [H][CH] complex data of a chunk of CH channels in shared memory (two buffers), H = H1 * H2.  A work item is a channel
+// PAIR, one inner index and a block of kColNB outputs, so that a data vector read once (16 bytes: two complex values)
+// meets kColNB twiddles (warp-uniform addresses) in 8 kColNB multiply-adds with 4 kColNB independent accumulators.
+// Tables (sign folded in): w1[k1][n1] = e^{s 2 pi i n1 k1 / H1}, wm[k1][n2] = e^{s 2 pi i n2 k1 / H}, w2[k2][n2] = e^{s 2 pi i n2 k2 / H2}.
+constexpr int kColNB = 5;
+
+__device__ __forceinline__ void col_tables(float2* w1, float2* wm, float2* w2, int H1, int H2, float sign) {
+  const int H = H1 * H2;
+  for (int i = threadIdx.x; i < H1 * H1 + H + H2 * H2; i += blockDim.x) {
+    float sn, cs;
+    if (i < H1 * H1) {
+      sincospif(2.f * (((i / H1) * (i % H1)) % H1) / H1, &sn, &cs);
+      w1[i] = make_float2(cs, sign * sn);
+    } else if (i < H1 * H1 + H) {
+      const int t = i - H1 * H1;                                   // t = k1 * H2 + n2
+      sincospif(2.f * (((t / H2) * (t % H2)) % H) / H, &sn, &cs);
+      wm[t] = make_float2(cs, sign * sn);
+    } else {
+      const int t = i - H1 * H1 - H;
+      sincospif(2.f * (((t / H2) * (t % H2)) % H2) / H2, &sn, &cs);
+      w2[t] = make_float2(cs, sign * sn);
+    }
+  }
+}
+
+// a -> b -> a;  the caller synchronises before (a and the tables complete); a is complete on return
+__device__ void col_dft_v2(float2* a, float2* b, const float2* w1, const float2* wm, const float2* w2, int H1, int H2, int CH) {
+  const int CP = CH >> 1, tid = threadIdx.x, nt = blockDim.x;
+  const float4* a4 = reinterpret_cast<const float4*>(a);
+  float4* b4 = reinterpret_cast<float4*>(b);
+  const int nb1 = (H1 + kColNB - 1) / kColNB;
+  for (int item = tid; item < nb1 * H2 * CP; item += nt) {
+    const int cp = item % CP, r = item / CP, n2 = r % H2, k10 = (r / H2) * kColNB;
+    float2 p[kColNB], q[kColNB];
+#pragma unroll
+    for (int u = 0; u < kColNB; ++u) p[u] = q[u] = make_float2(0.f, 0.f);
+    for (int n1 = 0; n1 < H1; ++n1) {
+      const float4 v = a4[(H2 * n1 + n2) * CP + cp];
+#pragma unroll
+      for (int u = 0; u < kColNB; ++u) {
+        const float2 t = w1[min(k10 + u, H1 - 1) * H1 + n1];
+        p[u].x += v.x * t.x - v.y * t.y;  p[u].y += v.x * t.y + v.y * t.x;
+        q[u].x += v.z * t.x - v.w * t.y;  q[u].y += v.z * t.y + v.w * t.x;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kColNB; ++u) {
+      const int k1 = k10 + u;
+      if (k1 < H1) {
+        const float2 t = wm[k1 * H2 + n2];
+        const float2 x = cmul(p[u], t), y = cmul(q[u], t);
+        b4[(k1 * H2 + n2) * CP + cp] = make_float4(x.x, x.y, y.x, y.y);
+      }
+    }
+  }
+  __syncthreads();
+  const float inv = rsqrtf((float)(H1 * H2));
+  const float4* bb4 = reinterpret_cast<const float4*>(b);
+  float4* o4 = reinterpret_cast<float4*>(a);
+  const int nb2 = (H2 + kColNB - 1) / kColNB;
+  for (int item = tid; item < nb2 * H1 * CP; item += nt) {
+    const int cp = item % CP, r = item / CP, k1 = r % H1, k20 = (r / H1) * kColNB;
+    float2 p[kColNB], q[kColNB];
+#pragma unroll
+    for (int u = 0; u < kColNB; ++u) p[u] = q[u] = make_float2(0.f, 0.f);
+    for (int n2 = 0; n2 < H2; ++n2) {
+      const float4 v = bb4[(k1 * H2 + n2) * CP + cp];
+#pragma unroll
+      for (int u = 0; u < kColNB; ++u) {
+        const float2 t = w2[min(k20 + u, H2 - 1) * H2 + n2];
+        p[u].x += v.x * t.x - v.y * t.y;  p[u].y += v.x * t.y + v.y * t.x;
+        q[u].x += v.z * t.x - v.w * t.y;  q[u].y += v.z * t.y + v.w * t.x;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kColNB; ++u) {
+      const int k2 = k20 + u;
+      if (k2 < H2) o4[(k1 + H1 * k2) * CP + cp] = make_float4(p[u].x * inv, p[u].y * inv, q[u].x * inv, q[u].y * inv);
+    }
+  }
+  __syncthreads();
+}
+
+struct ColSmem { float2 *a, *b, *w1, *wm, *w2; };
+__device__ __forceinline__ ColSmem col_smem(float* sm, int H, int H1, int H2, int CH) {
+  ColSmem c;
+  c.a = reinterpret_cast<float2*>(sm);
+  c.b = c.a + (size_t)H * CH;
+  c.w1 = c.b + (size_t)H * CH;
+  c.wm = c.w1 + H1 * H1;
+  c.w2 = c.wm + H;
+  return c;
+}
+
+// blockIdx.y = owned block * chunks + chunk;  CH = Cb / chunks channels per CTA
+__global__ void __launch_bounds__(256)
+afno_cols_dft_v2_kernel(const float2* __restrict__ Y, __nv_bfloat16* __restrict__ E, const __nv_bfloat16* __restrict__ mask, AfGeom g,
+                        float lambda, int chunks, int Mp) {
+  extern __shared__ float sm[];
+  const int CH = g.Cb / chunks;
+  const ColSmem s = col_smem(sm, g.H, g.H1, g.H2, CH);
+  const int bk = blockIdx.x, j = blockIdx.y / chunks, coff = (blockIdx.y % chunks) * CH, tid = threadIdx.x, nt = blockDim.x;
+  const int bb = bk / g.KX, kx = bk % g.KX;
+  const int ld = g.nblk * g.Cb;
+  col_tables(s.w1, s.wm, s.w2, g.H1, g.H2, -1.f);
+  for (int i = tid; i < g.H * CH; i += nt) {
+    const int h = i / CH, c = i % CH;
+    s.a[i] = Y[((size_t)(bb * g.H + h) * g.KX + kx) * ld + j * g.Cb + coff + c];
+  }
+  __syncthreads();
+  col_dft_v2(s.a, s.b, s.w1, s.wm, s.w2, g.H1, g.H2, CH);
+  const size_t base = ((size_t)j * Mp + (size_t)bk * g.H) * (2 * g.Cb) + coff;
+  const int CP = CH >> 1;
+  for (int i = tid; i < g.H * CP; i += nt) {
+    const int ky = i / CP, cp = i % CP;
+    float4 v = reinterpret_cast<const float4*>(s.a)[i];           // (re, im) of channels 2 cp, 2 cp + 1
+    const size_t o = base + (size_t)ky * 2 * g.Cb + 2 * cp;
+    if (mask) {
+      const float2 mr = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(mask + o));
+      const float2 mi = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(mask + o + g.Cb));
+      if (fabsf(mr.x) <= lambda) v.x = 0.f;
+      if (fabsf(mi.x) <= lambda) v.y = 0.f;
+      if (fabsf(mr.y) <= lambda) v.z = 0.f;
+      if (fabsf(mi.y) <= lambda) v.w = 0.f;
+    }
+    *reinterpret_cast<uint32_t*>(E + o) = pack_bf16x2(v.x, v.z);
+    *reinterpret_cast<uint32_t*>(E + o + g.Cb) = pack_bf16x2(v.y, v.w);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+afno_cols_idft_v2_kernel(const __nv_bfloat16* __restrict__ E, float2* __restrict__ Yout, AfGeom g, float lambda, int chunks,
+                         int Mp) {
+  extern __shared__ float sm[];
+  const int CH = g.Cb / chunks;
+  const ColSmem s = col_smem(sm, g.H, g.H1, g.H2, CH);
+  const int bk = blockIdx.x, j = blockIdx.y / chunks, coff = (blockIdx.y % chunks) * CH, tid = threadIdx.x, nt = blockDim.x;
+  const int bb = bk / g.KX, kx = bk % g.KX;
+  const int ld = g.nblk * g.Cb;
+  col_tables(s.w1, s.wm, s.w2, g.H1, g.H2, +1.f);
+  const size_t base = ((size_t)j * Mp + (size_t)bk * g.H) * (2 * g.Cb) + coff;
+  const int CP = CH >> 1;
+  for (int i = tid; i < g.H * CP; i += nt) {
+    const int ky = i / CP, cp = i % CP;
+    const size_t o = base + (size_t)ky * 2 * g.Cb + 2 * cp;
+    float2 re = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(E + o));
+    float2 im = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(E + o + g.Cb));
+    if (lambda > 0.f) {
+      re.x = softshrink_f(re.x, lambda); re.y = softshrink_f(re.y, lambda);
+      im.x = softshrink_f(im.x, lambda); im.y = softshrink_f(im.y, lambda);
+    }
+    reinterpret_cast<float4*>(s.a)[i] = make_float4(re.x, im.x, re.y, im.y);
+  }
+  __syncthreads();
+  col_dft_v2(s.a, s.b, s.w1, s.wm, s.w2, g.H1, g.H2, CH);
+  for (int i = tid; i < g.H * CH; i += nt) {
+    const int h = i / CH, c = i % CH;
+    Yout[((size_t)(bb * g.H + h) * g.KX + kx) * ld + j * g.Cb + coff + c] = s.a[i];
+  }
+}
+
 static TokenPtrs make_tok(const void* const* ptrs) {
   TokenPtrs t;
   for (int r = 0; r < kPeerMaxRanks; ++r) t.p[r] = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(ptrs[r]));
@@ -430,11 +796,22 @@ int pnm_afno_rows_r2c(const void* const* tokens, void* Y, const int* geom, long 
   if (pnm::af_check(g)) return -2;
   int* err = pnm::error_word_ptr();
   if (!err) return -1;
+  pnm::PeerArgs p{};
+  if (wait) p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, budget_s, epoch_base);
+  if (g.W % 2 == 0 && g.W >= 4) {
+    const pnm::RowPlan rp = pnm::row_plan(g.KX, g.Cb);
+    const size_t smem2 = sizeof(float) * (2 * (size_t)(g.W / 2) * g.Cb + 2 * (size_t)(g.W / 2 - 1) * rp.pad);
+    if (smem2 <= 220 * 1024) {
+      static unsigned long long mask2 = 0;
+      if (int rc = pnm::af_smem_attr(pnm::afno_rows_r2c_v2_kernel, smem2, mask2)) return rc;
+      pnm::afno_rows_r2c_v2_kernel<<<dim3(g.B * g.H, g.nblk), rp.threads, smem2, (cudaStream_t)stream>>>(
+          pnm::make_tok(tokens), (float2*)Y, g, kweight, p, wait, err, rp.groups, rp.passes);
+      return cudaGetLastError() == cudaSuccess ? 0 : -3;
+    }
+  }
   const size_t smem = sizeof(float) * ((size_t)g.W * g.Cb + 2 * g.W);
   static unsigned long long mask = 0;
   if (int rc = pnm::af_smem_attr(pnm::afno_rows_r2c_kernel, smem, mask)) return rc;
-  pnm::PeerArgs p{};
-  if (wait) p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, budget_s, epoch_base);
   pnm::afno_rows_r2c_kernel<<<dim3(g.B * g.H, g.nblk), 2 * g.Cb, smem, (cudaStream_t)stream>>>(pnm::make_tok(tokens), (float2*)Y, g,
                                                                                               kweight, p, wait, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
@@ -446,11 +823,22 @@ int pnm_afno_rows_c2r(const void* X, const void* const* tokens, const int* geom,
                       const void* epoch_base, void* counter, void* stream) {
   pnm::AfGeom g{geom[0], geom[1], geom[2], geom[3], geom[4], geom[5], geom[6], geom[7], Tp, geom[8], geom[9]};
   if (pnm::af_check(g) || (signal && !counter)) return -2;
+  pnm::PeerArgs p{};
+  if (signal) p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, 1.0, epoch_base);
+  if (g.W % 2 == 0 && g.W >= 4) {
+    const pnm::RowPlan rp = pnm::row_plan(g.W / 2 + 1, g.Cb);
+    const size_t smem2 = sizeof(float2) * ((size_t)g.KX * g.Cb + (size_t)g.KX * rp.pad) + sizeof(__nv_bfloat16) * (size_t)g.W * g.Cb;
+    if (smem2 <= 220 * 1024) {
+      static unsigned long long mask2 = 0;
+      if (int rc = pnm::af_smem_attr(pnm::afno_rows_c2r_v2_kernel, smem2, mask2)) return rc;
+      pnm::afno_rows_c2r_v2_kernel<<<dim3(g.B * g.H, g.nblk), rp.threads, smem2, (cudaStream_t)stream>>>(
+          (const float2*)X, pnm::make_tok(tokens), g, kweight, p, signal, (unsigned int*)counter, rp.groups, rp.passes);
+      return cudaGetLastError() == cudaSuccess ? 0 : -3;
+    }
+  }
   const size_t smem = sizeof(float2) * ((size_t)g.KX * g.Cb + g.W) + sizeof(__nv_bfloat16) * (size_t)g.W * g.Cb;
   static unsigned long long mask = 0;
   if (int rc = pnm::af_smem_attr(pnm::afno_rows_c2r_kernel, smem, mask)) return rc;
-  pnm::PeerArgs p{};
-  if (signal) p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, 1.0, epoch_base);
   pnm::afno_rows_c2r_kernel<<<dim3(g.B * g.H, g.nblk), 2 * g.Cb, smem, (cudaStream_t)stream>>>((const float2*)X, pnm::make_tok(tokens),
                                                                                               g, kweight, p, signal,
                                                                                               (unsigned int*)counter);
@@ -484,6 +872,31 @@ int pnm_afno_cols_bwd(const void* dYout, void* dY, const void* Zs, const void* O
   pnm::AfGrads gd{dw1, db1, dw2, db2};
   pnm::afno_cols_bwd_kernel<<<dim3(g.B * g.KX, g.nblk), 2 * g.Cb, smem, (cudaStream_t)stream>>>(
       (const float2*)dYout, (float2*)dY, (const float2*)Zs, (const float2*)O1s, (const float2*)O2s, wt, gd, g);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Split form of the column stage (see afno_cols_dft_v2_kernel): E bf16 [nblk, Mp, 2*Cb]; mask optional (same layout).
+int pnm_afno_cols_dft(const void* Y, void* E, const void* mask, const int* geom, int Mp, float lambda, void* stream) {
+  pnm::AfGeom g{geom[0], geom[1], geom[2], geom[3], geom[4], geom[5], geom[6], geom[7], 1, geom[8], geom[9]};
+  if (pnm::af_check(g) || Mp < g.B * g.KX * g.H) return -2;
+  const int chunks = (g.Cb % 16 == 0 && g.Cb >= 64) ? 2 : 1;
+  const size_t smem = sizeof(float2) * (2 * (size_t)g.H * (g.Cb / chunks) + g.H1 * g.H1 + g.H + g.H2 * g.H2);
+  static unsigned long long mask_bits = 0;
+  if (int rc = pnm::af_smem_attr(pnm::afno_cols_dft_v2_kernel, smem, mask_bits)) return rc;
+  pnm::afno_cols_dft_v2_kernel<<<dim3(g.B * g.KX, g.nblk * chunks), 256, smem, (cudaStream_t)stream>>>(
+      (const float2*)Y, (__nv_bfloat16*)E, (const __nv_bfloat16*)mask, g, lambda, chunks, Mp);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int pnm_afno_cols_idft(const void* E, void* Yout, const int* geom, int Mp, float lambda, void* stream) {
+  pnm::AfGeom g{geom[0], geom[1], geom[2], geom[3], geom[4], geom[5], geom[6], geom[7], 1, geom[8], geom[9]};
+  if (pnm::af_check(g) || Mp < g.B * g.KX * g.H) return -2;
+  const int chunks = (g.Cb % 16 == 0 && g.Cb >= 64) ? 2 : 1;
+  const size_t smem = sizeof(float2) * (2 * (size_t)g.H * (g.Cb / chunks) + g.H1 * g.H1 + g.H + g.H2 * g.H2);
+  static unsigned long long mask_bits = 0;
+  if (int rc = pnm::af_smem_attr(pnm::afno_cols_idft_v2_kernel, smem, mask_bits)) return rc;
+  pnm::afno_cols_idft_v2_kernel<<<dim3(g.B * g.KX, g.nblk * chunks), 256, smem, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)E, (float2*)Yout, g, lambda, chunks, Mp);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

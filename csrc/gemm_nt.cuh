@@ -45,6 +45,10 @@ struct NtArgs {
   float* out; int ldo;
   float* colsum;       // [Na] or null
   int* err;
+  // stacked batch (batch > 1): `batch` problems of batch_rows reduction rows one after the other in A and B; problem b adds
+  // into out + b * out_stride and colsum + b * Na.  Grid = tiles x splits x batch.
+  int batch, batch_rows, splits;
+  long long out_stride;
   // convolution weight gradient
   int conv, img_n, img_h, img_w, cin, tiles_x, tiles_y;
   int halo, has_up, has_down;
@@ -76,11 +80,14 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x % (g.tiles_a * g.tiles_b);
-  const int split = blockIdx.x / (g.tiles_a * g.tiles_b);
+  const int split_all = blockIdx.x / (g.tiles_a * g.tiles_b);
+  const int prob = g.batch > 1 ? split_all / g.splits : 0;
+  const int split = g.batch > 1 ? split_all % g.splits : split_all;
   const int ta = tile / g.tiles_b, tb = tile % g.tiles_b;
-  const int m_begin = split * g.rows_per_split;
+  const int m_lo = prob * g.batch_rows, m_hi = g.batch > 1 ? m_lo + g.batch_rows : g.M;
+  const int m_begin = m_lo + split * g.rows_per_split;
   int m_end = m_begin + g.rows_per_split;
-  if (m_end > g.M) m_end = g.M;
+  if (m_end > m_hi) m_end = m_hi;
   const int num_kb = m_end > m_begin ? (m_end - m_begin + kNtBK - 1) / kNtBK : 0;
 
   if (threadIdx.x == 0) {
@@ -191,7 +198,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tmem_ld_wait();
         const int col0 = tb * BNB + c;
         if (row < g.Na) {
-          float* dst = g.out + size_t(row) * g.ldo + col0;
+          float* dst = g.out + prob * g.out_stride + size_t(row) * g.ldo + col0;
           if (col0 + 32 <= g.Nb && (g.ldo & 3) == 0) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
@@ -208,7 +215,7 @@ gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         float v[32];
         tmem_ld32(tmem_base + BNB + (uint32_t(q * 32) << 16), v);
         tmem_ld_wait();
-        if (row < g.Na) atomicAdd(g.colsum + row, v[0]);
+        if (row < g.Na) atomicAdd(g.colsum + prob * g.Na + row, v[0]);
       }
     }
   }
@@ -227,6 +234,7 @@ struct NtCall {
   float* colsum;
   int M, Na, Nb;
   int max_ctas;
+  int batch = 1; long long out_stride = 0;   // stacked problems: M is the total row count (M / batch % 64 == 0)
   // convolution weight gradient: A = dY [img_n, img_h, img_w, Na], B = X [img_n, img_h, img_w, cin]; Nb = 9 * cin
   int conv = 0, img_n = 0, img_h = 0, img_w = 0, cin = 0;
   int halo = 0;
@@ -270,21 +278,24 @@ inline int launch_gemm_nt(const NtCall& c, int num_sms, int* err_word, cudaStrea
   g.tiles_a = (c.Na + 127) / 128;
   g.tiles_b = (c.Nb + BNB - 1) / BNB;
   const int tiles = g.tiles_a * g.tiles_b;
+  const int nprob = c.batch > 1 ? c.batch : 1;
+  if (nprob > 1 && (c.conv || M % (nprob * kNtBK))) return -25;
   const int cap = c.max_ctas > 0 ? c.max_ctas : num_sms;
-  int splits = cap / tiles;
+  int splits = cap / (tiles * nprob);
   if (splits < 1) splits = 1;
-  const int kblocks = (M + kNtBK - 1) / kNtBK;
+  const int kblocks = (M / nprob + kNtBK - 1) / kNtBK;
   if (splits > kblocks) splits = kblocks;
   int per = (kblocks + splits - 1) / splits;
   g.rows_per_split = per * kNtBK;
   splits = (kblocks + per - 1) / per;
   g.out = c.out; g.ldo = c.ldo; g.colsum = c.colsum; g.err = err_word;
+  g.batch = nprob; g.batch_rows = M / nprob; g.splits = splits; g.out_stride = c.out_stride;
   static unsigned long long attr_mask = 0;
   if (first_use_on_device(attr_mask)) {
     if (cudaFuncSetAttribute(gemm_nt_kernel<BNB>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
       return -22;
   }
-  gemm_nt_kernel<BNB><<<tiles * splits, kNtThreads, Cfg::SMEM, stream>>>(tA, tB, tB3, tUp, tDown, g);
+  gemm_nt_kernel<BNB><<<tiles * splits * nprob, kNtThreads, Cfg::SMEM, stream>>>(tA, tB, tB3, tUp, tDown, g);
   return cudaGetLastError() == cudaSuccess ? 0 : -23;
 }
 

@@ -35,6 +35,9 @@ struct GemmArgs {
   int scale_post;
   int num_m_tiles, num_n_tiles;
   int* err;
+  // stacked batch (batch_m_tiles != 0): A / C hold `batch` problems of batch_m_tiles * 128 rows one after the other, B holds
+  // their [N, K] matrices one after the other, bias / scale their [N] vectors: M tile mt belongs to problem mt / batch_m_tiles
+  int batch_m_tiles;
   // implicit-GEMM convolution (conv != 0): rows of A are output pixels of an NHWC image, tiled 8 x 16 per M tile;
   // K runs over (tap, input channel); the A tile of k-block (tap, c0) is the input window shifted by the tap
   int conv, tiles_x, tiles_y, cin, ksize, pad, img_h;
@@ -218,7 +221,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           } else if (k < g.K1) tma_load_2d(sa, &tmA, &full[s], k, mt * kBM);
           else if (k < g.K2) tma_load_2d(sa, &tmA2, &full[s], k - g.K1, mt * kBM);
           else tma_load_2d(sa, &tmA3, &full[s], k - g.K2, mt * kBM);
-          tma_load_2d(sb, &tmB, &full[s], k, nt * BN);
+          tma_load_2d(sb, &tmB, &full[s], k, nt * BN + (g.batch_m_tiles ? (mt / g.batch_m_tiles) * g.N : 0));
         }
       }
       if (!ok) {
@@ -307,22 +310,23 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         const bool store_ok = (r0 < g.M) && (c0 < g.N);
         const bool full_cols = (c0 + 64 <= g.N);
+        const int vo = g.batch_m_tiles ? (r0 / (kBM * g.batch_m_tiles)) * g.N : 0;   // offset of the problem's bias / scale
         // ---- x = (acc + bias) * scale
         if (g.bias) {
-          if (full_cols) {
+          if (full_cols && !(vo & 3)) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + c0) + j);
+              float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + vo + c0) + j);
               v[4 * j] += b.x; v[4 * j + 1] += b.y; v[4 * j + 2] += b.z; v[4 * j + 3] += b.w;
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 64; ++j) if (c0 + j < g.N) v[j] += __ldg(g.bias + c0 + j);
+            for (int j = 0; j < 64; ++j) if (c0 + j < g.N) v[j] += __ldg(g.bias + vo + c0 + j);
           }
         }
         if (g.scale && !g.scale_post) {
 #pragma unroll
-          for (int j = 0; j < 64; ++j) if (c0 + j < g.N) v[j] *= __ldg(g.scale + c0 + j);
+          for (int j = 0; j < 64; ++j) if (c0 + j < g.N) v[j] *= __ldg(g.scale + vo + c0 + j);
         }
         // ---- second output: pre-activation
         if (MODE == MODE_Z) {
@@ -414,7 +418,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         if (g.scale && g.scale_post) {
 #pragma unroll
-          for (int j = 0; j < 64; ++j) if (c0 + j < g.N) v[j] *= __ldg(g.scale + c0 + j);
+          for (int j = 0; j < 64; ++j) if (c0 + j < g.N) v[j] *= __ldg(g.scale + vo + c0 + j);
         }
         stage_write_row(stg + b * kChunkBytes, lane, v);
         fence_async_smem();
@@ -457,6 +461,7 @@ struct GemmCall {
   const float* bias; const float* scale; float* group_out;
   int act, aux_mode, scale_post;
   int max_ctas;  // 0 = number of SMs
+  int batch = 1; // > 1: `batch` stacked problems (see GemmArgs::batch_m_tiles); M is the total row count, M / batch % 128 == 0
   // convolution: A is an NHWC image [img_n, img_h, img_w, cin], B holds [N, ksize*ksize*cin] (tap-major), C is NHWC
   int conv = 0, img_n = 0, img_h = 0, img_w = 0, cin = 0, ksize = 0;
   // halo exchange fused into the convolution (see GemmArgs): boundary rows published by the neighbours [img_n, 1, img_w, cin]
@@ -486,7 +491,8 @@ inline int launch_gemm_tn(const GemmCall& c, int num_sms, int* err_word, cudaStr
   else if (!halo) tA2 = tA;
   if (c.K > c.K2) { if (make_tmap_2d_b16(&tA3, c.A3, c.M, c.K - c.K2, c.lda3, kBM, kBK)) return -18; }
   else if (!(halo && c.up_rows)) tA3 = tA;
-  if (make_tmap_2d_b16(&tB, c.B, c.N, c.K, c.ldb, BN, kBK)) return -12;
+  if (c.batch > 1 && (c.conv || c.M % (c.batch * kBM) || c.group_out)) return -21;
+  if (make_tmap_2d_b16(&tB, c.B, c.N * (c.batch > 1 ? c.batch : 1), c.K, c.ldb, BN, kBK)) return -12;
   if (c.conv) { if (make_tmap_nhwc_b16(&tC, c.C, c.img_n, c.img_h, c.img_w, c.N, 2, kConvTileW)) return -13; }
   else if (make_tmap_2d_b16(&tC, c.C, c.M, c.N, c.ldc, 32, 64)) return -13;
   if (MODE == MODE_Z) { if (make_tmap_2d_b16(&tX, c.Z, c.M, c.N, c.ldz, 32, 64)) return -14; }
@@ -499,6 +505,7 @@ inline int launch_gemm_tn(const GemmCall& c, int num_sms, int* err_word, cudaStr
   g.num_m_tiles = (c.M + kBM - 1) / kBM;
   g.num_n_tiles = (c.N + BN - 1) / BN;
   g.err = err_word;
+  g.batch_m_tiles = c.batch > 1 ? c.M / c.batch / kBM : 0;
   g.conv = c.conv; g.cin = c.cin; g.ksize = c.ksize; g.pad = c.ksize / 2; g.img_h = c.img_h;
   g.tiles_x = g.tiles_y = 0;
   g.halo = c.conv ? c.halo : 0; g.has_up = c.up_rows != nullptr; g.has_down = c.down_rows != nullptr; g.img_n = c.img_n;

@@ -334,6 +334,27 @@ peer_pull_reduce_kernel(float* __restrict__ dst, long long block, PeerArgs p, in
   }
 }
 
+// dst[i] = sum over ranks r of srcs.p[r][i], i < n: every rank has left a partial result in symmetric memory before raising
+// its flag of call `epoch`; the caller passes, per rank, the address of the block that belongs to THIS rank.  The same
+// reduce-scatter in the pull model as above, with explicit addresses instead of the slot layout.
+struct PeerSrcs { const float* p[kPeerMaxRanks]; };
+static __global__ void __launch_bounds__(512)
+peer_sum_blocks_kernel(float* __restrict__ dst, PeerSrcs srcs, long long n, int wait, PeerArgs p, int* err) {
+  __shared__ int sh_ok;
+  bool ok = true;
+  if (wait) ok = peer_small_wait(p, peer_epoch(p), err, &sh_ok);
+  const float nanv = __int_as_float(0x7fc00000);
+  for (long long i = 4 * (blockIdx.x * (long long)blockDim.x + threadIdx.x); i < n; i += 4 * (long long)gridDim.x * blockDim.x) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ok) {
+      for (int r = 0; r < p.world; ++r) { const float4 v = ldcg4(srcs.p[r] + i); s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w; }
+    } else {
+      s = make_float4(nanv, nanv, nanv, nanv);
+    }
+    *reinterpret_cast<float4*>(dst + i) = s;
+  }
+}
+
 // A wait that nothing satisfies: used by the failure-detection test to check that a bounded
 // wait gives up, reports ERR_WAIT_PEER and leaves the context usable.
 static __global__ void peer_wait_probe_kernel(const uint32_t* flag, uint32_t expect, unsigned long long budget_ns,

@@ -21,6 +21,11 @@ int pnm_gemm_tn(const void* A, int lda, const void* A2, int lda2, const void* A3
 // out[Na,Nb] (fp32) += A[M,Na]^T * B[M,Nb];  colsum[Na] += column sums of A (optional).
 int pnm_gemm_nt(const void* A, int lda, const void* B, int ldb, float* out, int ldo, float* colsum, int M, int Na,
                 int Nb, int max_ctas, void* stream);
+// Stacked batches of equal problems in one launch (rows of a problem padded to Mp; see pnm_lib.cu)
+int pnm_gemm_tn_stacked(const void* A, int lda, const void* B, int ldb, void* C, int ldc, const void* AUX, int ldaux, int Mp, int N,
+                        int K, int batch, const float* bias, int act, int aux_mode, int max_ctas, void* stream);
+int pnm_gemm_nt_stacked(const void* A, int lda, const void* B, int ldb, float* out, float* colsum, int Mp, int Na, int Nb, int batch,
+                        int max_ctas, void* stream);
 
 // y = LN(x [+ r]) [+ post]; bf16 rows of C channels (C % 8 == 0, C <= 1024), fp32 gamma / beta / statistics.
 int pnm_layernorm_fwd(const void* x, const void* r, const float* gamma, const float* beta, void* y, void* sum_out,
@@ -59,6 +64,12 @@ int pnm_peer_pull(const void* src, void* dst, long long bytes, int flag_from, co
                   int max_ctas);
 int pnm_peer_pull_reduce(float* dst, long long block, const void* const* bases, int rank, int world, unsigned int epoch,
                          long long capacity_floats, double budget_s, void* stream, const void* epoch_base, int max_ctas);
+int pnm_peer_sum_blocks(float* dst, const void* const* srcs, long long n, int wait, const void* const* bases, int rank, int world,
+                        unsigned int epoch, long long capacity_floats, double budget_s, const void* epoch_base, void* stream,
+                        int max_ctas);
+// Row softmax over bf16 rows (softmax_rows.cu): forward in place with optional log-sum-exp, backward over dP in place.
+int pnm_softmax_rows_fwd(void* S, long long ld, long long rows, int L, float scale, float* lse, void* stream);
+int pnm_softmax_rows_bwd(const void* P, long long ldp, void* dP, long long ldd, long long rows, int L, float scale, void* stream);
 // Enqueue a copy of the device error word into pinned host memory (non-blocking poll of the bounded waits).
 int pnm_error_copy_async(int* pinned_host, void* stream);
 int pnm_peer_flag_bytes();

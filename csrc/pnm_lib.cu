@@ -104,6 +104,29 @@ int pnm_gemm_tn(const void* A, int lda, const void* A2, int lda2, const void* A3
 }
 
 
+// `batch` problems of the same shape in one launch: A [batch * Mp, K] (Mp % 128 == 0, problem b in rows b Mp ..), B [batch * N, K],
+// C / AUX [batch * Mp, N], bias [batch * N] or null; C_b = epilogue(A_b @ B_b^T).  Rows that pad a problem to Mp are computed
+// like any other (their inputs should be finite).
+int pnm_gemm_tn_stacked(const void* A, int lda, const void* B, int ldb, void* C, int ldc, const void* AUX, int ldaux, int Mp, int N,
+                        int K, int batch, const float* bias, int act, int aux_mode, int max_ctas, void* stream) {
+  if (ensure_init()) return -1;
+  if (Mp <= 0 || N <= 0 || K <= 0 || batch <= 0 || (Mp % 128)) return -2;
+  if ((N % 8) || (K % 8) || (lda % 8) || (ldb % 8) || (ldc % 8)) return -3;
+  if ((aux_mode != 0) != (AUX != nullptr)) return -6;
+  if (act == pnm::ACT_SOFTMAX64) return -7;
+  pnm::GemmCall c;
+  c.A = A; c.lda = lda; c.A2 = nullptr; c.lda2 = 0; c.A3 = nullptr; c.lda3 = 0; c.B = B; c.ldb = ldb; c.C = C; c.ldc = ldc;
+  c.Z = nullptr; c.ldz = 0; c.AUX = AUX; c.ldaux = ldaux;
+  c.M = Mp * batch; c.N = N; c.K = K; c.K1 = K; c.K2 = K;
+  c.bias = bias; c.scale = nullptr; c.group_out = nullptr;
+  c.act = act; c.aux_mode = aux_mode; c.scale_post = 0; c.max_ctas = max_ctas;
+  c.batch = batch;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (AUX) return pnm::launch_gemm_tn<128, pnm::MODE_AUX>(c, g_num_sms, g_err_ptr, st);
+  if (N > 128) return pnm::launch_gemm_tn<256, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+  return pnm::launch_gemm_tn<128, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+}
+
 // y[n, h, w, :] = act(sum over taps and input channels of x[n, h + dy, w + dx, :] W[:, tap, :] + bias): stride-1 "same"
 // convolution of a channels-last bf16 image on the tensor cores.  weight: [cout, ksize*ksize*cin] bf16, tap-major
 // (tap = ky * ksize + kx).  Requires cin % 64 == 0, cout % 8 == 0, odd ksize.
@@ -196,6 +219,22 @@ int pnm_gemm_nt(const void* A, int lda, const void* B, int ldb, float* out, int 
   pnm::NtCall c;
   c.A = A; c.lda = lda; c.B = B; c.ldb = ldb; c.out = out; c.ldo = ldo; c.colsum = colsum;
   c.M = M; c.Na = Na; c.Nb = Nb; c.max_ctas = max_ctas;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (Nb > 128) return pnm::launch_gemm_nt<256>(c, g_num_sms, g_err_ptr, st);
+  return pnm::launch_gemm_nt<128>(c, g_num_sms, g_err_ptr, st);
+}
+
+// `batch` weight-gradient problems in one launch: A [batch * Mp, Na], B [batch * Mp, Nb] (Mp % 64 == 0; rows that pad a problem
+// must be zero in A or B), out [batch, Na, Nb] fp32 (accumulated into), colsum [batch, Na] or null.
+int pnm_gemm_nt_stacked(const void* A, int lda, const void* B, int ldb, float* out, float* colsum, int Mp, int Na, int Nb, int batch,
+                        int max_ctas, void* stream) {
+  if (ensure_init()) return -1;
+  if (Mp <= 0 || Na <= 0 || Nb <= 0 || batch <= 0 || (Mp % 64)) return -2;
+  if ((Na % 8) || (Nb % 8) || (lda % 8) || (ldb % 8)) return -3;
+  pnm::NtCall c;
+  c.A = A; c.lda = lda; c.B = B; c.ldb = ldb; c.out = out; c.ldo = Nb; c.colsum = colsum;
+  c.M = Mp * batch; c.Na = Na; c.Nb = Nb; c.max_ctas = max_ctas;
+  c.batch = batch; c.out_stride = (long long)Na * Nb;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (Nb > 128) return pnm::launch_gemm_nt<256>(c, g_num_sms, g_err_ptr, st);
   return pnm::launch_gemm_nt<128>(c, g_num_sms, g_err_ptr, st);
@@ -310,6 +349,26 @@ int pnm_peer_pull_reduce(float* dst, long long block, const void* const* bases, 
   int grid = (int)std::min<long long>((block / 4 + 511) / 512, max_ctas > 0 ? max_ctas : 96);
   if (grid < 1) grid = 1;
   pnm::peer_pull_reduce_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(dst, block, p, g_err_ptr);
+  return cudaGetLastError() == cudaSuccess ? 0 : -51;
+}
+
+// dst[i] = sum_r srcs[r][i] (srcs: host array of 8 peer-mapped addresses, unused entries repeating a valid one), n % 4 == 0.
+int pnm_peer_sum_blocks(float* dst, const void* const* srcs, long long n, int wait, const void* const* bases, int rank, int world,
+                        unsigned int epoch, long long capacity_floats, double budget_s, const void* epoch_base, void* stream,
+                        int max_ctas) {
+  if (ensure_init()) return -1;
+  if (world > pnm::kPeerMaxRanks || world < 1) return -50;
+  if (n <= 0) return 0;
+  if ((n & 3) || (reinterpret_cast<uintptr_t>(dst) & 15)) return -53;
+  pnm::PeerSrcs ps;
+  for (int r = 0; r < pnm::kPeerMaxRanks; ++r) {
+    if (reinterpret_cast<uintptr_t>(srcs[r]) & 15) return -53;
+    ps.p[r] = reinterpret_cast<const float*>(srcs[r]);
+  }
+  const pnm::PeerArgs p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, budget_s, epoch_base);
+  int grid = (int)std::min<long long>((n / 4 + 511) / 512, max_ctas > 0 ? max_ctas : 2 * g_num_sms);
+  if (grid < 1) grid = 1;
+  pnm::peer_sum_blocks_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(dst, ps, n, wait, p, g_err_ptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -51;
 }
 

@@ -60,6 +60,10 @@ def _correctness(rank, world, dev, mesh):
 
     res = 512
     model = build_model(dev, res)
+    with torch.no_grad():                      # the zero-initialised output convolutions would hide forward errors
+        gen = torch.Generator(device=dev).manual_seed(99)
+        for p in model.parameters():
+            p.add_(torch.randn(p.shape, generator=gen, device=dev) * 0.02)
     cond, x0 = make_batch(1, res, seed=7)
     sigma = torch.tensor([0.7])
     noise = torch.randn(1, 4, res, res, generator=torch.Generator().manual_seed(11))

@@ -39,6 +39,18 @@ class AttentionOp(torch.autograd.Function):
         return dq, dk
 
 
+def _wide_head_gemm_attention(q: torch.Tensor) -> bool:
+    """Plain CUDA 16-bit tensors with a head wider than the flash kernels take (the 512-wide single head of the
+    SongUNet bottleneck): attention as two tcgen05 GEMMs around the library's row softmax (``ops/gemm_attention.py``)."""
+    if type(q) is not torch.Tensor or not q.is_cuda or q.dtype not in (torch.bfloat16, torch.float16):
+        return False
+    if q.shape[-1] <= 128 or q.shape[-1] % 8 or q.shape[-2] % 8 or q.shape[0] * q.shape[1] > 16:
+        return False
+    from ...ops import _lib
+
+    return _lib.available()
+
+
 class UNetAttention(torch.nn.Module):
     """Self-attention over the pixels of a feature map (keys ``norm``, ``qkv``, ``proj``)."""
 
@@ -65,7 +77,12 @@ class UNetAttention(torch.nn.Module):
         x1 = self.qkv(self.norm(x))
         qkv = x1.reshape(x.shape[0], self.num_heads, x.shape[1] // self.num_heads, 3, -1).permute(0, 1, 4, 3, 2)
         q, k, v = (qkv[..., i, :] for i in range(3))
-        attn = torch.nn.functional.scaled_dot_product_attention(q, k, v, scale=1 / math.sqrt(k.shape[-1]))
+        if _wide_head_gemm_attention(q):
+            from ...ops.gemm_attention import gemm_attention
+
+            attn = gemm_attention(q, k, v, 1 / math.sqrt(k.shape[-1]))
+        else:
+            attn = torch.nn.functional.scaled_dot_product_attention(q, k, v, scale=1 / math.sqrt(k.shape[-1]))
         attn = attn.transpose(-1, -2)
         return self.proj(attn.reshape(*x.shape)) + x
 

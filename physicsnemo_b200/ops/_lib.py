@@ -80,6 +80,8 @@ def _declare(lib):
         "pnm_gemm_tn": ([vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp,
                          i32, i32, i32, i32, i32, vp], i32),
         "pnm_gemm_nt": ([vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, vp], i32),
+        "pnm_gemm_tn_stacked": ([vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, vp, i32, i32, i32, vp], i32),
+        "pnm_gemm_nt_stacked": ([vp, i32, vp, i32, vp, vp, i32, i32, i32, i32, i32, vp], i32),
         "pnm_layernorm_fwd": ([vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, f32, vp], i32),
         "pnm_gather_rows": ([vp, i32, vp, vp, vp, i32, i64, i32, vp], i32),
         "pnm_segment_sum": ([vp, i32, vp, vp, vp, i32, i64, i32, i32, i32, vp], i32),

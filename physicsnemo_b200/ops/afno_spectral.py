@@ -29,7 +29,10 @@ def _lib_af():
         lib.pnm_afno_rows_c2r.argtypes = [vp, vp, vp, ll, i, i, vp, i, i, u, ll, vp, vp, vp]
         lib.pnm_afno_cols_fwd.argtypes = [vp] * 9 + [i, vp, f, vp]
         lib.pnm_afno_cols_bwd.argtypes = [vp] * 11 + [i, vp, vp]
-        for n in ("pnm_afno_rows_r2c", "pnm_afno_rows_c2r", "pnm_afno_cols_fwd", "pnm_afno_cols_bwd"):
+        lib.pnm_afno_cols_dft.argtypes = [vp, vp, vp, vp, i, f, vp]
+        lib.pnm_afno_cols_idft.argtypes = [vp, vp, vp, i, f, vp]
+        for n in ("pnm_afno_rows_r2c", "pnm_afno_rows_c2r", "pnm_afno_cols_fwd", "pnm_afno_cols_bwd", "pnm_afno_cols_dft",
+                  "pnm_afno_cols_idft"):
             getattr(lib, n).restype = i
         lib._afno_declared = True
     return lib
@@ -60,6 +63,8 @@ class FilterGeometry:
         self.H1, self.H2 = _factor(H)
         self.rank, self.world = rank, world
         self.arr = (ctypes.c_int * 10)(B, H, W, C, self.Cb, self.KX, self.blk0, self.nblk, self.H1, self.H2)
+        self.Mb = B * self.KX * H                       # spectral rows (b, kx, ky) of one channel block
+        self.Mp = -(-self.Mb // 128) * 128              # ... padded to the GEMM's M tile
 
     def supported(self) -> bool:
         return self.Cb % 8 == 0 and self.Cb <= 128 and 2 * self.KX <= self.W and self.H * self.Cb * 8 * 3 + self.H * 8 <= 220 * 1024
@@ -71,8 +76,124 @@ def _ptrs8(ptrs):
     return (ctypes.c_void_p * 8)(*ptrs)
 
 
+def _expand_weight(w: torch.Tensor) -> torch.Tensor:
+    """Complex block weights ``w[2, nb, Cb_in, Cb_out]`` as the real matrices ``[nb, 2 Cb (out), 2 Cb (in)]`` (bf16) that
+    act on ``[real | imag]`` rows: ``[xr | xi] @ [[wr, wi], [-wi, wr]]``, stored output-major for ``gemm_tn``."""
+    wr, wi = w[0].transpose(1, 2), w[1].transpose(1, 2)
+    top = torch.cat([wr, -wi], dim=2)
+    bottom = torch.cat([wi, wr], dim=2)
+    return torch.cat([top, bottom], dim=1).to(torch.bfloat16).contiguous()
+
+
+def _fold_weight_grad(dwe: torch.Tensor, cb: int) -> torch.Tensor:
+    """Inverse of ``_expand_weight`` for gradients: ``[nb, 2 Cb, 2 Cb]`` fp32 -> ``[2, nb, Cb_in, Cb_out]``."""
+    a, b, c, d = dwe[:, :cb, :cb], dwe[:, :cb, cb:], dwe[:, cb:, :cb], dwe[:, cb:, cb:]
+    return torch.stack([(a + d).transpose(1, 2), (c - b).transpose(1, 2)])
+
+
+class _AfnoFilterTcFn(torch.autograd.Function):
+    """The filter with its block MLP on the tensor cores: Fourier kernels write / read the ``[real | imag]`` bf16
+    expansion of the spectrum, the two complex layers are ``gemm_tn`` calls with bias / ReLU epilogues, their backward
+    ``gemm_nt`` (weight and bias gradients in one pass) and ``gemm_tn`` with the ReLU mask in the epilogue."""
+
+    @staticmethod
+    def forward(ctx, tokens, w1, b1, w2, b2, geo: FilterGeometry, lam: float, exchange):
+        lib = _lib_af()
+        dev = tokens.device
+        st = torch.cuda.current_stream().cuda_stream
+        g = geo
+        rows, ld, cb2 = g.B * g.H, g.nblk * g.Cb, 2 * g.Cb
+        own = slice(g.blk0, g.blk0 + g.nblk)
+        Y = torch.empty(rows, g.KX, ld, 2, dtype=torch.float32, device=dev)
+        Y2 = torch.empty_like(Y)
+        Z = torch.empty(g.nblk, g.Mp, cb2, dtype=torch.bfloat16, device=dev)
+        if g.Mp > g.Mb:
+            Z[:, g.Mb:].zero_()                                   # rows that pad a block to the GEMM's M tile
+        O1, O2 = torch.empty_like(Z), torch.empty_like(Z)
+        w1e, w2e = _expand_weight(w1.detach()[:, own]), _expand_weight(w2.detach()[:, own])
+        b1e = torch.cat([b1.detach()[0, own], b1.detach()[1, own]], dim=1).float().contiguous()
+        b2e = torch.cat([b2.detach()[0, own], b2.detach()[1, own]], dim=1).float().contiguous()
+
+        def cols():
+            _g._check(lib.pnm_afno_cols_dft(Y.data_ptr(), Z.data_ptr(), None, g.arr, g.Mp, 0.0, st), "pnm_afno_cols_dft")
+            _g.gemm_tn_stacked(Z, w1e, bias=b1e, act=_g.ACT_RELU, out=O1)            # all blocks in one launch
+            _g.gemm_tn_stacked(O1, w2e, bias=b2e, out=O2)
+            _g._check(lib.pnm_afno_cols_idft(O2.data_ptr(), Y2.data_ptr(), g.arr, g.Mp, float(lam), st), "pnm_afno_cols_idft")
+
+        if exchange is None:
+            src = tokens.contiguous()
+            out = torch.empty_like(src)
+            rc = lib.pnm_afno_rows_r2c(_ptrs8([src.data_ptr()]), Y.data_ptr(), g.arr, g.Tp, 0, 0, None, 0, 1, 0, 0, 1.0, None, st)
+            _g._check(rc, "pnm_afno_rows_r2c")
+            cols()
+            rc = lib.pnm_afno_rows_c2r(Y2.data_ptr(), _ptrs8([out.data_ptr()]), g.arr, g.Tp, 1, 0, None, 0, 1, 0, 0, None, None, st)
+            _g._check(rc, "pnm_afno_rows_c2r")
+        else:
+            out = exchange.transform(lib, tokens, Y, Y2, cols, g, kw_in=0, kw_out=1)
+        _g.launch_count += 4
+        ctx.save_for_backward(w1e, w2e, Z, O1, O2)
+        ctx.geo, ctx.exchange, ctx.lam = geo, exchange, float(lam)
+        ctx.dtypes = (w1.dtype, b1.dtype, w2.dtype, b2.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        lib = _lib_af()
+        w1e, w2e, Z, O1, O2 = ctx.saved_tensors
+        g, exchange, lam = ctx.geo, ctx.exchange, ctx.lam
+        dev = dout.device
+        st = torch.cuda.current_stream().cuda_stream
+        rows, ld, cb2 = g.B * g.H, g.nblk * g.Cb, 2 * g.Cb
+        dY2 = torch.empty(rows, g.KX, ld, 2, dtype=torch.float32, device=dev)
+        dY = torch.empty_like(dY2)
+        G2 = torch.empty_like(Z)
+        if g.Mp > g.Mb:
+            G2[:, g.Mb:].zero_()          # zero padding rows: they then contribute nothing to the weight gradients
+        G1, dZ = torch.empty_like(Z), torch.empty_like(Z)
+        dw1e = torch.zeros(g.nblk, cb2, cb2, dtype=torch.float32, device=dev)
+        dw2e = torch.zeros_like(dw1e)
+        db1e = torch.zeros(g.nblk, cb2, dtype=torch.float32, device=dev)
+        db2e = torch.zeros_like(db1e)
+        w1t, w2t = w1e.transpose(1, 2).contiguous(), w2e.transpose(1, 2).contiguous()
+
+        def cols():
+            # adjoint of the inverse transform is the forward one; the soft-shrink mask comes from the saved O2
+            _g._check(lib.pnm_afno_cols_dft(dY2.data_ptr(), G2.data_ptr(), O2.data_ptr(), g.arr, g.Mp, lam, st), "pnm_afno_cols_dft")
+            _g.gemm_nt_stacked(G2, O1, dw2e, db2e)
+            _g.gemm_tn_stacked(G2, w2t, aux=O1, aux_mode=_g.AUX_DRELU, out=G1)
+            _g.gemm_nt_stacked(G1, Z, dw1e, db1e)
+            _g.gemm_tn_stacked(G1, w1t, out=dZ)
+            _g._check(lib.pnm_afno_cols_idft(dZ.data_ptr(), dY.data_ptr(), g.arr, g.Mp, 0.0, st), "pnm_afno_cols_idft")
+
+        d = dout.to(torch.bfloat16).contiguous()
+        if exchange is None:
+            dx = torch.empty_like(d)
+            rc = lib.pnm_afno_rows_r2c(_ptrs8([d.data_ptr()]), dY2.data_ptr(), g.arr, g.Tp, 1, 0, None, 0, 1, 0, 0, 1.0, None, st)
+            _g._check(rc, "pnm_afno_rows_r2c")
+            cols()
+            rc = lib.pnm_afno_rows_c2r(dY.data_ptr(), _ptrs8([dx.data_ptr()]), g.arr, g.Tp, 0, 0, None, 0, 1, 0, 0, None, None, st)
+            _g._check(rc, "pnm_afno_rows_c2r")
+        else:
+            dx = exchange.transform(lib, d, dY2, dY, cols, g, kw_in=1, kw_out=0)
+        _g.launch_count += 4
+        dt = ctx.dtypes
+        own = slice(g.blk0, g.blk0 + g.nblk)
+
+        def scatter(part, shape, dtype):
+            full = torch.zeros(shape, dtype=torch.float32, device=dev)
+            full[:, own] = part
+            return full.to(dtype)
+
+        dw1 = scatter(_fold_weight_grad(dw1e, g.Cb), (2, g.nb, g.Cb, g.Cb), dt[0])
+        dw2 = scatter(_fold_weight_grad(dw2e, g.Cb), (2, g.nb, g.Cb, g.Cb), dt[2])
+        db1 = scatter(torch.stack([db1e[:, :g.Cb], db1e[:, g.Cb:]]), (2, g.nb, g.Cb), dt[1])
+        db2 = scatter(torch.stack([db2e[:, :g.Cb], db2e[:, g.Cb:]]), (2, g.nb, g.Cb), dt[3])
+        return dx, dw1, db1, dw2, db2, None, None, None
+
+
 class _AfnoFilterFn(torch.autograd.Function):
-    """tokens [Tp, C] bf16 (this rank's tokens, all channels) -> filtered tokens [Tp, C] bf16."""
+    """tokens [Tp, C] bf16 (this rank's tokens, all channels) -> filtered tokens [Tp, C] bf16; block MLP in fp32 inside
+    the column kernel (the path for fp32-exact filters)."""
 
     @staticmethod
     def forward(ctx, tokens, w1, b1, w2, b2, geo: FilterGeometry, lam: float, exchange):
@@ -190,6 +311,10 @@ class TokenChannelExchange:
 
 
 def afno_filter(tokens: torch.Tensor, w1, b1, w2, b2, geo: FilterGeometry, sparsity_threshold: float,
-                exchange: Optional[TokenChannelExchange] = None) -> torch.Tensor:
-    """Filtered tokens (without the layer's residual): ``tokens`` is this rank's ``[Tp, C]`` bf16 slice of the token tensor."""
-    return _AfnoFilterFn.apply(tokens, w1, b1, w2, b2, geo, float(sparsity_threshold), exchange)
+                exchange: Optional[TokenChannelExchange] = None, mlp: str = "bf16") -> torch.Tensor:
+    """Filtered tokens (without the layer's residual): ``tokens`` is this rank's ``[Tp, C]`` bf16 slice of the token tensor.
+
+    ``mlp="bf16"`` runs the block MLP as tcgen05 GEMMs on the bf16 ``[real | imag]`` spectrum (what the reference's
+    einsums do under bf16 autocast); ``mlp="fp32"`` keeps it in fp32 inside the column kernel."""
+    fn = _AfnoFilterTcFn if (mlp == "bf16" and geo.Cb % 4 == 0) else _AfnoFilterFn
+    return fn.apply(tokens, w1, b1, w2, b2, geo, float(sparsity_threshold), exchange)

@@ -139,6 +139,47 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, *, colsum: bool = False, out: Opti
 
 
 # ------------------------------------------------------------------ oracles
+def gemm_tn_stacked(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None, act: int = ACT_NONE,
+                    aux: Optional[torch.Tensor] = None, aux_mode: int = AUX_NONE, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[p] = epilogue(a[p] @ b[p].T)`` for ``a: [P, Mp, K]``, ``b: [P, N, K]`` (contiguous bf16, ``Mp % 128 == 0``),
+    ``bias: [P, N]`` fp32, ``aux: [P, Mp, N]`` — all problems in ONE launch of the tcgen05 kernel."""
+    global launch_count
+    lib = _lib.load(required=True)
+    P, Mp, K = a.shape
+    N = b.shape[1]
+    assert a.is_contiguous() and b.is_contiguous() and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert b.shape == (P, N, K) and Mp % 128 == 0
+    if out is None:
+        out = torch.empty((P, Mp, N), dtype=torch.bfloat16, device=a.device)
+    assert out.is_contiguous() and out.shape == (P, Mp, N)
+    if aux is not None:
+        assert aux.is_contiguous() and aux.shape == (P, Mp, N) and aux.dtype == torch.bfloat16
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.is_contiguous() and bias.shape == (P, N)
+    code = lib.pnm_gemm_tn_stacked(_ptr(a), K, _ptr(b), K, _ptr(out), N, _ptr(aux), N if aux is not None else 0, Mp, N, K, P,
+                                   _ptr(bias), act, aux_mode, 0, _stream())
+    _check(code, "pnm_gemm_tn_stacked")
+    launch_count += 1
+    return out
+
+
+def gemm_nt_stacked(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, colsum: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[p] += a[p].T @ b[p]`` (and ``colsum[p] += a[p].sum(0)``) for ``a: [P, Mp, Na]``, ``b: [P, Mp, Nb]`` contiguous
+    bf16 with ``Mp % 64 == 0``; ``out: [P, Na, Nb]`` / ``colsum: [P, Na]`` fp32, accumulated into.  One launch."""
+    global launch_count
+    lib = _lib.load(required=True)
+    P, Mp, Na = a.shape
+    Nb = b.shape[2]
+    assert a.is_contiguous() and b.is_contiguous() and b.shape[:2] == (P, Mp) and Mp % 64 == 0
+    assert out.is_contiguous() and out.shape == (P, Na, Nb) and out.dtype == torch.float32
+    if colsum is not None:
+        assert colsum.is_contiguous() and colsum.shape == (P, Na) and colsum.dtype == torch.float32
+    code = lib.pnm_gemm_nt_stacked(_ptr(a), Na, _ptr(b), Nb, _ptr(out), _ptr(colsum), Mp, Na, Nb, P, 0, _stream())
+    _check(code, "pnm_gemm_nt_stacked")
+    launch_count += 1
+    return out
+
+
 def act_torch(x: torch.Tensor, act: int) -> torch.Tensor:
     if act == ACT_GELU:
         return F.gelu(x)

@@ -32,6 +32,21 @@ def _flash_block_ok(q, k, v) -> bool:
     return _fa.supported(q, k, v)
 
 
+def _peer_attention_ok(q, k, v, k_sizes, q_sizes, group) -> bool:
+    """Sequence-sharded attention on the library's GEMM / softmax kernels with K / V staged over peer memory: CUDA,
+    16-bit tensors, every rank holding the same number of keys (and of queries), peer memory available."""
+    if not (q.is_cuda and q.dtype in (torch.bfloat16, torch.float16)):
+        return False
+    if len({tuple(s) if isinstance(s, (tuple, list, torch.Size)) else s for s in k_sizes}) != 1:
+        return False
+    if len({tuple(s) if isinstance(s, (tuple, list, torch.Size)) else s for s in q_sizes}) != 1:
+        return False
+    from ...ops import gemm_attention as _ga
+    from ..peer import peer_available
+
+    return _ga.supported(q, k, v) and peer_available(q)
+
+
 def _block(q, k, v, scale, mask=None):
     """Un-normalised attention of one K/V block: (max, sumexp, weighted values), fp32."""
     acc = torch.float32 if q.dtype in (torch.bfloat16, torch.float16) else q.dtype
@@ -112,6 +127,12 @@ def _sdpa(func, types, args, kwargs):
             return wrap(out, mesh, placements, spec.sharding_sizes if spec else {})
         if mq != md:
             raise MissingShardPatch("queries and keys are sharded over different mesh dimensions")
+        if _peer_attention_ok(lq, lk, lv, k_sizes, q._spec.sharding_sizes[md], group):
+            # equal shards on CUDA: K / V blocks pulled over peer memory under the first block's GEMMs, softmax once
+            from ...ops import gemm_attention as _ga
+
+            out = _ga.sharded_attention(lq, lk, lv, group, scale)
+            return wrap(out, mesh, q._spec.placements, q._spec.sharding_sizes)
         acc = None
         kb, vb = lk, lv
         for step in range(n):

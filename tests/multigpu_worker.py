@@ -229,6 +229,41 @@ def check_transolver(rank, world, dev, report):
         report(f"point-sharded Transolver grad {name}", d / (q.grad.norm().item() + 1e-2 * total), 2e-2)
 
 
+def check_sharded_attention(rank, world, dev, report):
+    """F.scaled_dot_product_attention on sequence-sharded ShardTensors (peer-staged K / V, GEMM + softmax kernels) vs
+    fp32 attention over the gathered sequence, forward and the gradients of q, k, v."""
+    import math
+
+    from physicsnemo_b200 import ops
+    from physicsnemo_b200.distributed import DistributedManager
+    from physicsnemo_b200.parallel import Shard, ShardTensor
+
+    mesh = DistributedManager().global_mesh
+    torch.manual_seed(3)
+    for (b, hh, sl, d) in [(1, 1, 1024, 512), (2, 2, 264, 64)]:
+        s = sl * world
+        full = [torch.randn(b, hh, s, d, device=dev).to(torch.bfloat16) for _ in range(3)]
+        do = torch.randn(b, hh, s, d, device=dev).to(torch.bfloat16)
+        for t in full + [do]:
+            dist.broadcast(t, src=0)
+        sel = slice(rank * sl, (rank + 1) * sl)
+        for it in range(2):
+            loc = [t[:, :, sel].clone().requires_grad_(True) for t in full]
+            st = [ShardTensor.from_local(t, mesh, [Shard(2)], sharding_shapes="chunk", global_shape=full[0].shape) for t in loc]
+            before = ops.kernel_launches()
+            out = torch.nn.functional.scaled_dot_product_attention(*st)
+            assert ops.kernel_launches() > before, "the peer-staged attention path was not taken"
+            out.to_local().backward(do[:, :, sel])
+            ref_in = [t.float().requires_grad_(True) for t in full]
+            sc = (ref_in[0] @ ref_in[1].transpose(-1, -2)) / math.sqrt(d)
+            ref = torch.softmax(sc, dim=-1) @ ref_in[2]
+            ref.backward(do.float())
+            tag = f"sharded attention S={s} D={d} it{it}"
+            report(tag + " fwd", _rel(out.to_local(), ref[:, :, sel]), 1.5e-2)
+            for name, a, r in zip("qkv", loc, ref_in):
+                report(tag + f" d{name}", _rel(a.grad, r.grad[:, :, sel]), 2.5e-2)
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
@@ -244,9 +279,9 @@ def main():
         if not (err <= tol):
             failures.append(f"[rank {rank}] {what}: {err:.3e} > {tol:.1e}")
 
-    which = sys.argv[1:] or ["allreduce", "timeout", "conv_gn", "reducer", "transolver"]
+    which = sys.argv[1:] or ["allreduce", "timeout", "conv_gn", "reducer", "attention", "transolver"]
     table = {"allreduce": check_allreduce, "timeout": check_timeout_and_recovery, "conv_gn": check_sharded_conv_gn,
-             "reducer": check_grad_reducer, "transolver": check_transolver}
+             "reducer": check_grad_reducer, "attention": check_sharded_attention, "transolver": check_transolver}
     for name in which:
         t0 = time.time()
         table[name](rank, world, dev, report)

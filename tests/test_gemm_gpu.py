@@ -87,6 +87,30 @@ def test_gemm_nt(M, Na, Nb):
     assert ops.device_error() == 0
 
 
+@pytest.mark.parametrize("P,Mp,N,K", [(8, 8320, 192, 192), (3, 256, 64, 64), (2, 384, 264, 136)])
+def test_gemm_stacked_batches(P, Mp, N, K):
+    """`P` equal problems in one launch: forward with bias + ReLU, data gradient with the ReLU mask, weight gradient
+    with column sums — each against the per-problem fp32 statement."""
+    a, w = _rand(P, Mp, K), _rand(P, N, K, scale=0.1)
+    bias = torch.randn(P, N, device="cuda")
+    out = G.gemm_tn_stacked(a, w, bias=bias, act=G.ACT_RELU)
+    ref = torch.relu(torch.einsum("pmk,pnk->pmn", a.float(), w.float()) + bias[:, None])
+    _close(out, ref)
+    gy = _rand(P, Mp, N)
+    wt = w.transpose(1, 2).contiguous()
+    # the mask has the product's shape: dx = (gy @ w) where aux > 0
+    dref = torch.einsum("pmn,pnk->pmk", gy.float(), w.float())
+    aux = _rand(P, Mp, K)
+    dx = G.gemm_tn_stacked(gy, wt, aux=aux, aux_mode=G.AUX_DRELU)
+    _close(dx, dref * (aux.float() > 0))
+    dw = torch.zeros(P, N, K, device="cuda")
+    db = torch.zeros(P, N, device="cuda")
+    G.gemm_nt_stacked(gy, a, dw, db)
+    _close(dw, torch.einsum("pmn,pmk->pnk", gy.float(), a.float()), tol=1e-2)
+    _close(db, gy.float().sum(1), tol=1e-2)
+    assert ops.device_error() == 0
+
+
 @pytest.mark.parametrize("C", [128, 256, 768])
 def test_layernorm(C):
     M = 3001
