@@ -204,8 +204,41 @@ __device__ __forceinline__ CLThread cl_thread(const GNShape& sh, int s) {
   return t;
 }
 
+// One counter per batch item (zero between launches: the CTA that folds resets it).  Forward and backward keep apart.
+__device__ unsigned int g_gn_fwd_counter[65536];
+__device__ unsigned int g_gn_bwd_counter[65536];
+
+// Called by every CTA of the (S, B) grid after it wrote its group partials part[b][s][0..G): the CTA that arrives last at
+// the batch item's counter sums part[b][0..S)[g] in a fixed order (one warp per group, lanes over slices, shuffle tree)
+// into out[b][g].  The channels-last kernels use hundreds of slices so that a batch of one still fills the machine; this
+// keeps the fold off every consumer CTA's prologue and out of a launch of its own.
+__device__ __forceinline__ void cl_fold_slices(const float2* part, float2* out, unsigned int* counter, const GNShape& sh, int b) {
+  __shared__ int last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last = atomicAdd(counter + b, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int g = warp; g < sh.G; g += nw) {
+    float a = 0.f, q = 0.f;
+#pragma unroll 4
+    for (int sl = lane; sl < sh.S; sl += 32) {
+      const float2 v = __ldcg(part + ((long long)b * sh.S + sl) * sh.G + g);
+      a += v.x; q += v.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); q += __shfl_xor_sync(0xffffffffu, q, o); }
+    if (lane == 0) out[b * sh.G + g] = make_float2(a, q);
+  }
+  if (threadIdx.x == 0) counter[b] = 0;
+}
+
+// part[b][s][g] = (sum x, sum x^2) of slice s; gsum[b][g] = their sum over the slices (written by the last CTA of item b)
 template <typename T>
-__global__ void __launch_bounds__(256) gn_stats_cl(const T* __restrict__ x, float2* __restrict__ partial, GNShape sh) {
+__global__ void __launch_bounds__(256) gn_stats_cl(const T* __restrict__ x, float2* __restrict__ part, float2* __restrict__ gsum,
+                                                    GNShape sh) {
   constexpr int V = Vec<T>::N;
   extern __shared__ float smem[];                        // [C][2]
   const int s = blockIdx.x, b = blockIdx.y;
@@ -217,6 +250,7 @@ __global__ void __launch_bounds__(256) gn_stats_cl(const T* __restrict__ x, floa
   for (int i = 0; i < V; ++i) a[i] = q[i] = 0.f;
   if (t.active) {
     const T* base = x + (long long)b * sh.HW * sh.C + t.c0;
+#pragma unroll 4
     for (long long p = t.p0 + t.lane_pix; p < t.p1; p += t.ppi) {
       Vec<T>::load(base + p * sh.C, f);
 #pragma unroll
@@ -226,44 +260,35 @@ __global__ void __launch_bounds__(256) gn_stats_cl(const T* __restrict__ x, floa
     for (int i = 0; i < V; ++i) { atomicAdd(&smem[2 * (t.c0 + i)], a[i]); atomicAdd(&smem[2 * (t.c0 + i) + 1], q[i]); }
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < sh.C; c += blockDim.x)
-    partial[((long long)b * sh.S + s) * sh.C + c] = make_float2(smem[2 * c], smem[2 * c + 1]);
+  for (int g = threadIdx.x; g < sh.G; g += blockDim.x) {
+    float a2 = 0.f, q2 = 0.f;
+    for (int k = 0; k < sh.cpg; ++k) { a2 += smem[2 * (g * sh.cpg + k)]; q2 += smem[2 * (g * sh.cpg + k) + 1]; }
+    part[((long long)b * sh.S + s) * sh.G + g] = make_float2(a2, q2);
+  }
+  cl_fold_slices(part, gsum, g_gn_fwd_counter, sh, b);
 }
 
-// fills smem mom[g] = (mean, rstd) for all groups of batch b
-__device__ __forceinline__ void all_group_moments(const float2* __restrict__ partial, const GNShape& sh, int b, float eps,
+// fills smem mom[g] = (mean, rstd) for all groups of batch item b from the folded sums
+__device__ __forceinline__ void all_group_moments(const float2* __restrict__ gsum, const GNShape& sh, int b, float eps,
                                                   float2* mom) {
+  const float cnt = (float)sh.cpg * (float)sh.HW;
   for (int g = threadIdx.x; g < sh.G; g += blockDim.x) {
-    float a = 0.f, q = 0.f;
-    for (int s = 0; s < sh.S; ++s)
-      for (int k = 0; k < sh.cpg; ++k) {
-        const float2 p = partial[((long long)b * sh.S + s) * sh.C + g * sh.cpg + k];
-        a += p.x; q += p.y;
-      }
-    const float cnt = (float)sh.cpg * (float)sh.HW;
-    const float mean = a / cnt;
-    mom[g] = make_float2(mean, rsqrtf(fmaxf(q / cnt - mean * mean, 0.f) + eps));
+    const float2 v = gsum[b * sh.G + g];
+    const float mean = v.x / cnt;
+    mom[g] = make_float2(mean, rsqrtf(fmaxf(v.y / cnt - mean * mean, 0.f) + eps));
   }
   __syncthreads();
 }
 
 // ---- sharded statistics ---------------------------------------------------------------------------------------------
-// grid (B): sums[b][g] = (sum x, sum x^2) of this rank's rows, written to stage A of the symmetric buffer at float
+// grid (B): the folded sums[b][g] = (sum x, sum x^2) of this rank's rows go to stage A of the symmetric buffer at float
 // offset 2 * (b * G + g); the block that finishes last raises the flags.
-__global__ void __launch_bounds__(256) gn_publish_moments(const float2* __restrict__ partial, GNShape sh, PeerArgs peer,
+__global__ void __launch_bounds__(256) gn_publish_moments(const float2* __restrict__ gsum, GNShape sh, PeerArgs peer,
                                                            unsigned int* counter) {
   const uint32_t epoch = peer_epoch(peer);
   float2* dst = reinterpret_cast<float2*>(peer_data(peer, peer.rank, epoch & 1, 0));
   const int b = blockIdx.x;
-  for (int g = threadIdx.x; g < sh.G; g += blockDim.x) {
-    float a = 0.f, q = 0.f;
-    for (int s = 0; s < sh.S; ++s)
-      for (int k = 0; k < sh.cpg; ++k) {
-        const float2 p = partial[((long long)b * sh.S + s) * sh.C + g * sh.cpg + k];
-        a += p.x; q += p.y;
-      }
-    dst[b * sh.G + g] = make_float2(a, q);
-  }
+  for (int g = threadIdx.x; g < sh.G; g += blockDim.x) dst[b * sh.G + g] = gsum[b * sh.G + g];
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0 && atomicAdd(counter, 1u) == gridDim.x - 1) {
@@ -322,6 +347,7 @@ __global__ void __launch_bounds__(256) gn_apply_cl_sh(const T* __restrict__ x, c
     shift[i] = beta[c] - m.x * scale[i];
   }
   const long long off = (long long)b * sh.HW * sh.C + t.c0;
+#pragma unroll 4
   for (long long p = t.p0 + t.lane_pix; p < t.p1; p += t.ppi) {
     Vec<T>::load(x + off + p * sh.C, f);
 #pragma unroll
@@ -363,6 +389,7 @@ __global__ void __launch_bounds__(256) gn_bwd_apply_cl_sh(const T* __restrict__ 
     A[i] = gab[g].x * inv_n; Bq[i] = gab[g].y * inv_n;
   }
   const long long off = (long long)b * sh.HW * sh.C + t.c0;
+#pragma unroll 2
   for (long long p = t.p0 + t.lane_pix; p < t.p1; p += t.ppi) {
     Vec<T>::load(x + off + p * sh.C, f);
     Vec<T>::load(dy + off + p * sh.C, e);
@@ -399,6 +426,7 @@ __global__ void __launch_bounds__(256) gn_apply_cl(const T* __restrict__ x, cons
     shift[i] = beta[c] - m.x * scale[i];
   }
   const long long off = (long long)b * sh.HW * sh.C + t.c0;
+#pragma unroll 4
   for (long long p = t.p0 + t.lane_pix; p < t.p1; p += t.ppi) {
     Vec<T>::load(x + off + p * sh.C, f);
 #pragma unroll
@@ -411,7 +439,8 @@ template <typename T, bool kSilu>
 __global__ void __launch_bounds__(256) gn_bwd_stats_cl(const T* __restrict__ x, const T* __restrict__ dy,
                                                         const float* __restrict__ gamma, const float* __restrict__ beta,
                                                         const float* __restrict__ mean, const float* __restrict__ rstd,
-                                                        float2* __restrict__ pc, GNShape sh) {
+                                                        float2* __restrict__ part, float2* __restrict__ group_ab,
+                                                        float* __restrict__ dgamma, float* __restrict__ dbeta, GNShape sh) {
   constexpr int V = Vec<T>::N;
   extern __shared__ float smem[];                        // [C][2]
   const int s = blockIdx.x, b = blockIdx.y;
@@ -427,6 +456,7 @@ __global__ void __launch_bounds__(256) gn_bwd_stats_cl(const T* __restrict__ x, 
       a[i] = d[i] = 0.f;
     }
     const long long off = (long long)b * sh.HW * sh.C + t.c0;
+#pragma unroll 2
     for (long long p = t.p0 + t.lane_pix; p < t.p1; p += t.ppi) {
       Vec<T>::load(x + off + p * sh.C, f);
       Vec<T>::load(dy + off + p * sh.C, e);
@@ -441,8 +471,22 @@ __global__ void __launch_bounds__(256) gn_bwd_stats_cl(const T* __restrict__ x, 
     for (int i = 0; i < V; ++i) { atomicAdd(&smem[2 * (t.c0 + i)], a[i]); atomicAdd(&smem[2 * (t.c0 + i) + 1], d[i]); }
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < sh.C; c += blockDim.x)
-    pc[((long long)b * sh.S + s) * sh.C + c] = make_float2(smem[2 * c], smem[2 * c + 1]);
+  // parameter gradients: every slice adds its channel sums (dgamma / dbeta are zeroed by the caller)
+  for (int c = threadIdx.x; c < sh.C; c += blockDim.x) {
+    atomicAdd(&dgamma[c], smem[2 * c]);
+    atomicAdd(&dbeta[c], smem[2 * c + 1]);
+  }
+  // group sums for dx: A = sum gamma * (sum dz), B = sum gamma * (sum dz xhat), folded over the slices by the last CTA
+  for (int g = threadIdx.x; g < sh.G; g += blockDim.x) {
+    float A = 0.f, Bq = 0.f;
+    for (int k = 0; k < sh.cpg; ++k) {
+      const int c = g * sh.cpg + k;
+      A += gamma[c] * smem[2 * c + 1];
+      Bq += gamma[c] * smem[2 * c];
+    }
+    part[((long long)b * sh.S + s) * sh.G + g] = make_float2(A, Bq);
+  }
+  cl_fold_slices(part, group_ab, g_gn_bwd_counter, sh, b);
 }
 
 template <typename T, bool kSilu>
@@ -464,6 +508,7 @@ __global__ void __launch_bounds__(256) gn_bwd_apply_cl(const T* __restrict__ x, 
     A[i] = ab.x * inv_n; Bq[i] = ab.y * inv_n;
   }
   const long long off = (long long)b * sh.HW * sh.C + t.c0;
+#pragma unroll 2
   for (long long p = t.p0 + t.lane_pix; p < t.p1; p += t.ppi) {
     Vec<T>::load(x + off + p * sh.C, f);
     Vec<T>::load(dy + off + p * sh.C, e);
@@ -512,9 +557,10 @@ int gn_forward(const void* x, const float* gamma, const float* beta, void* y, fl
     else gn_apply_cf<T, false><<<grid, 256, 0, st>>>(xi, partial, gamma, beta, yo, mean, rstd, sh, eps);
   } else {
     const dim3 grid(sh.S, sh.B);
-    gn_stats_cl<T><<<grid, 256, 2 * sh.C * sizeof(float), st>>>(xi, partial, sh);
-    if (act) gn_apply_cl<T, true><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, partial, gamma, beta, yo, mean, rstd, sh, eps);
-    else gn_apply_cl<T, false><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, partial, gamma, beta, yo, mean, rstd, sh, eps);
+    float2* gsum = partial + (long long)sh.B * sh.S * sh.G;
+    gn_stats_cl<T><<<grid, 256, 2 * sh.C * sizeof(float), st>>>(xi, partial, gsum, sh);
+    if (act) gn_apply_cl<T, true><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, gsum, gamma, beta, yo, mean, rstd, sh, eps);
+    else gn_apply_cl<T, false><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, gsum, gamma, beta, yo, mean, rstd, sh, eps);
   }
   return (int)cudaGetLastError();
 }
@@ -523,7 +569,7 @@ template <typename T>
 int gn_backward(const void* x, const void* dy, const float* gamma, const float* beta, const float* mean, const float* rstd,
                 void* dx, float* dgamma, float* dbeta, float* scratch, GNShape sh, int layout, int act, cudaStream_t st) {
   float2* pc = reinterpret_cast<float2*>(scratch);
-  float2* ab = pc + (long long)sh.B * sh.S * sh.C;
+  float2* ab = pc + (long long)sh.B * sh.S * (layout == 0 ? sh.C : sh.G);
   const T* xi = static_cast<const T*>(x);
   const T* di = static_cast<const T*>(dy);
   T* o = static_cast<T*>(dx);
@@ -532,11 +578,11 @@ int gn_backward(const void* x, const void* dy, const float* gamma, const float* 
   if (layout == 0) {
     if (act) gn_bwd_stats_cf<T, true><<<grid, 256, 0, st>>>(xi, di, gamma, beta, mean, rstd, pc, sh);
     else gn_bwd_stats_cf<T, false><<<grid, 256, 0, st>>>(xi, di, gamma, beta, mean, rstd, pc, sh);
+    gn_bwd_reduce<<<sh.B, 256, 2 * sh.G * sizeof(float), st>>>(pc, gamma, ab, dgamma, dbeta, sh);
   } else {
-    if (act) gn_bwd_stats_cl<T, true><<<grid, 256, sm, st>>>(xi, di, gamma, beta, mean, rstd, pc, sh);
-    else gn_bwd_stats_cl<T, false><<<grid, 256, sm, st>>>(xi, di, gamma, beta, mean, rstd, pc, sh);
+    if (act) gn_bwd_stats_cl<T, true><<<grid, 256, sm, st>>>(xi, di, gamma, beta, mean, rstd, pc, ab, dgamma, dbeta, sh);
+    else gn_bwd_stats_cl<T, false><<<grid, 256, sm, st>>>(xi, di, gamma, beta, mean, rstd, pc, ab, dgamma, dbeta, sh);
   }
-  gn_bwd_reduce<<<sh.B, 256, 2 * sh.G * sizeof(float), st>>>(pc, gamma, ab, dgamma, dbeta, sh);
   if (layout == 0) {
     if (act) gn_bwd_apply_cf<T, true><<<grid, 256, 0, st>>>(xi, di, gamma, beta, mean, rstd, ab, o, sh);
     else gn_bwd_apply_cf<T, false><<<grid, 256, 0, st>>>(xi, di, gamma, beta, mean, rstd, ab, o, sh);
@@ -555,8 +601,9 @@ int gn_forward_sh(const void* x, const float* gamma, const float* beta, void* y,
   const T* xi = static_cast<const T*>(x);
   T* yo = static_cast<T*>(y);
   const dim3 grid(sh.S, sh.B);
-  gn_stats_cl<T><<<grid, 256, 2 * sh.C * sizeof(float), st>>>(xi, partial, sh);
-  gn_publish_moments<<<sh.B, 256, 0, st>>>(partial, sh, peer, counter);
+  float2* gsum = partial + (long long)sh.B * sh.S * sh.G;
+  gn_stats_cl<T><<<grid, 256, 2 * sh.C * sizeof(float), st>>>(xi, partial, gsum, sh);
+  gn_publish_moments<<<sh.B, 256, 0, st>>>(gsum, sh, peer, counter);
   if (act) gn_apply_cl_sh<T, true><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, gamma, beta, yo, mean, rstd, sh, eps, count_global, peer, err);
   else gn_apply_cl_sh<T, false><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, gamma, beta, yo, mean, rstd, sh, eps, count_global, peer, err);
   return (int)cudaGetLastError();
@@ -567,15 +614,14 @@ int gn_backward_sh(const void* x, const void* dy, const float* gamma, const floa
                    void* dx, float* dgamma, float* dbeta, float* scratch, GNShape sh, int act, float count_global,
                    const PeerArgs& peer, unsigned int* counter, int* err, cudaStream_t st) {
   float2* pc = reinterpret_cast<float2*>(scratch);
-  float2* ab = pc + (long long)sh.B * sh.S * sh.C;
+  float2* ab = pc + (long long)sh.B * sh.S * sh.G;
   const T* xi = static_cast<const T*>(x);
   const T* di = static_cast<const T*>(dy);
   T* o = static_cast<T*>(dx);
   const dim3 grid(sh.S, sh.B);
   const size_t sm = 2 * sh.C * sizeof(float);
-  if (act) gn_bwd_stats_cl<T, true><<<grid, 256, sm, st>>>(xi, di, gamma, beta, mean, rstd, pc, sh);
-  else gn_bwd_stats_cl<T, false><<<grid, 256, sm, st>>>(xi, di, gamma, beta, mean, rstd, pc, sh);
-  gn_bwd_reduce<<<sh.B, 256, 2 * sh.G * sizeof(float), st>>>(pc, gamma, ab, dgamma, dbeta, sh);
+  if (act) gn_bwd_stats_cl<T, true><<<grid, 256, sm, st>>>(xi, di, gamma, beta, mean, rstd, pc, ab, dgamma, dbeta, sh);
+  else gn_bwd_stats_cl<T, false><<<grid, 256, sm, st>>>(xi, di, gamma, beta, mean, rstd, pc, ab, dgamma, dbeta, sh);
   gn_publish_ab<<<sh.B, 256, 0, st>>>(ab, sh, peer, counter);
   if (act) gn_bwd_apply_cl_sh<T, true><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, di, gamma, beta, mean, rstd, o, sh, count_global, peer, err);
   else gn_bwd_apply_cl_sh<T, false><<<grid, 256, sh.G * sizeof(float2), st>>>(xi, di, gamma, beta, mean, rstd, o, sh, count_global, peer, err);

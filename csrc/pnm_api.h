@@ -248,6 +248,10 @@ int pnm_pixel_attn_bwd(const void* qk, const void* tok, const int* cu, const voi
 int pnm_counting_histogram(const int* idx, int* counts, long long n, int bins, int* bad, void* stream);
 int pnm_counting_scatter(const int* idx, const int* offsets, int* cursor, int* order, long long n, int bins, void* stream);
 
+// 2 x 2 box resampling of a channels-last bf16 image (mode 0: down, sum of the four pixels times scale; mode 1: up,
+// replication times scale); c % 8 == 0
+int pnm_resample2x_nhwc(const void* x, void* y, int n, int h, int w, int c, int mode, float scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

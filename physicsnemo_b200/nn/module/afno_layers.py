@@ -133,8 +133,10 @@ class AFNOPatchEmbed(nn.Module):
             # stride == kernel: the convolution is a GEMM over non-overlapping patches
             B, C, H, W = x.shape
             p0, p1 = self.patch_size
-            t = x.reshape(B, C, H // p0, p0, W // p1, p1).permute(0, 2, 4, 1, 3, 5).reshape(B, -1, C * p0 * p1)
-            return ops.linear(t.to(torch.bfloat16), self.proj.weight.reshape(self.proj.weight.shape[0], -1), self.proj.bias)
+            # one pass: the cast to bf16 writes the patch-major layout directly
+            t = x.reshape(B, C, H // p0, p0, W // p1, p1).permute(0, 2, 4, 1, 3, 5)
+            t = t.to(torch.bfloat16, memory_format=torch.contiguous_format).reshape(B, -1, C * p0 * p1)
+            return ops.linear(t, self.proj.weight.reshape(self.proj.weight.shape[0], -1), self.proj.bias)
         return self.proj(x).flatten(2).transpose(1, 2)
 
 

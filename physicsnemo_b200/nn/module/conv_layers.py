@@ -17,6 +17,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ...ops import conv as _conv
+from ...ops import resample as _resample
 
 from .activations import get_activation
 from .utils.utils import _validate_amp
@@ -84,13 +85,13 @@ class Conv2d(nn.Module):
         else:
             if self.up:
                 if self._box_filter:
-                    x = F.interpolate(x, scale_factor=2, mode="nearest")
+                    x = _resample.up2x(x)
                 else:
                     x = F.conv_transpose2d(x, f.mul(4).tile([self.in_channels, 1, 1, 1]), groups=self.in_channels,
                                            stride=2, padding=f_pad)
             if self.down:
                 if self._box_filter:
-                    x = F.avg_pool2d(x, 2)
+                    x = _resample.down2x(x)
                 else:
                     x = F.conv2d(x, f.tile([self.in_channels, 1, 1, 1]), groups=self.in_channels, stride=2, padding=f_pad)
             if w is not None:

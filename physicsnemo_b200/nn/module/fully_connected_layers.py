@@ -201,5 +201,7 @@ class Linear(nn.Module):
                 bias = bias.to(x.dtype)
         x = x @ weight.t()
         if bias is not None:
-            x = x.add_(bias) if not x.requires_grad else x + bias
+            # the result keeps the product's dtype (an in-place add in the reference): under autocast a bf16 product
+            # plus an fp32 bias must not promote the whole activation path to fp32
+            x = x.add_(bias) if not x.requires_grad else x + bias.to(x.dtype)
         return x

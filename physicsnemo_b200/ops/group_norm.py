@@ -64,10 +64,12 @@ def _slices(B: int, C: int, hw: int, layout: int, v: int) -> int:
     target = 4 * 148
     if layout == 0:
         base, most = B * C, max(1, (hw // v) // 256)
-    else:
-        ppi = max(1, 256 // (C // v))
-        base, most = B, max(1, hw // (4 * ppi))
-    return int(max(1, min(128, most, -(-target // base))))
+        return int(max(1, min(128, most, -(-target // base))))
+    # channels-last: the grid is (S, B), so a batch of one needs hundreds of slices to fill 148 SMs with 4 CTAs each; the
+    # slices' partials are folded by the last CTA of the statistics kernels, not by their consumers
+    ppi = max(1, 256 // (C // v))
+    most = max(1, hw // (8 * ppi))
+    return int(max(1, min(2048, most, -(-target // B))))
 
 
 class _GroupNormFn(torch.autograd.Function):

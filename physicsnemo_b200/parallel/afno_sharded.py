@@ -82,10 +82,14 @@ class TokenShardedAFNO:
 
     def forward(self, tokens_in: torch.Tensor) -> torch.Tensor:
         """``tokens_in``: ``[Tp, C_in * p0 * p1]`` patch tokens of this rank (feature order ``(c, p0, p1)``)."""
+        with torch.autocast("cuda", dtype=torch.bfloat16, enabled=tokens_in.is_cuda):
+            return self._forward(tokens_in)
+
+    def _forward(self, tokens_in: torch.Tensor) -> torch.Tensor:
         m = self.model
         pe = m.patch_embed.proj
         x = ops.linear(tokens_in.to(torch.bfloat16), pe.weight.reshape(pe.weight.shape[0], -1), pe.bias)
-        x = x + m.pos_embed[0, self.pos_index].to(x.dtype)
+        x = x + m.pos_embed[0, self.pos_index]          # fp32 like the stock forward: the first block's skip stays fp32
         for blk in m.blocks:
             f = blk.filter
             xn = ops.layer_norm(x, blk.norm1.weight, blk.norm1.bias, blk.norm1.eps)

@@ -660,3 +660,25 @@ def test_softmax_rows_kernels():
         dref = 0.3 * pr * (dp.float() - (dp.float() * pr).sum(-1, keepdim=True))
         ds = GA.softmax_rows_bwd_(p, dp.clone(), 0.3)
         assert float((ds.float() - dref).abs().max()) < 1e-2 * float(dref.abs().max()) + 1e-7
+
+
+@pytest.mark.gpu
+def test_box_resample_kernels():
+    """2 x 2 mean / replication on channels-last bf16 images, with their backward passes, vs avg_pool2d / interpolate."""
+    from physicsnemo_b200.ops import resample as R
+
+    torch.manual_seed(0)
+    for (n, c, h, w) in [(2, 64, 24, 40), (1, 8, 6, 2), (3, 136, 10, 14)]:
+        x = torch.randn(n, c, h, w, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        assert R.supported(x)
+        for fn, ref in ((R.down2x, lambda t: torch.nn.functional.avg_pool2d(t, 2)),
+                        (R.up2x, lambda t: torch.nn.functional.interpolate(t, scale_factor=2, mode="nearest"))):
+            a = x.clone().requires_grad_(True)
+            b = x.float().clone().requires_grad_(True)
+            ya, yb = fn(a), ref(b)
+            assert ya.shape == yb.shape and ya.is_contiguous(memory_format=torch.channels_last)
+            assert float((ya.float() - yb).abs().max()) <= 8e-3 * float(yb.abs().max())
+            g = torch.randn_like(yb)
+            ya.backward(g.to(torch.bfloat16))
+            yb.backward(g.to(torch.bfloat16).float())
+            assert float((a.grad.float() - b.grad).abs().max()) <= 1e-2 * float(b.grad.abs().max())
