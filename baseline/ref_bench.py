@@ -147,7 +147,10 @@ def _transolver(args, rank, world, dev):
         from physicsnemo.domain_parallel import ShardTensor  # type: ignore
 
         mesh = _ref_mesh(world)
-        wrap = lambda t: ShardTensor.from_local(t, mesh, (Shard(1),), sharding_shapes="chunk")  # noqa: E731
+        def wrap(t):        # equal point shards: the global shape follows from the local one
+            shape = list(t.shape)
+            shape[1] *= world
+            return ShardTensor.from_local(t, mesh, (Shard(1),), sharding_shapes="chunk", global_shape=tuple(shape))
 
     def train_step(emb, fx, target):
         opt.zero_grad(set_to_none=True)
@@ -222,7 +225,10 @@ def _songunet(args, rank, world, dev):
         mesh = _ref_mesh(world)
         sched = DomainParallelNoiseScheduler(sched, mesh, shard_dim=2) if _takes(DomainParallelNoiseScheduler, "shard_dim") \
             else DomainParallelNoiseScheduler(sched, mesh)
-        wrap = lambda t: ShardTensor.from_local(t, mesh, (Shard(2),), sharding_shapes="chunk")  # noqa: E731
+        def wrap(t):        # equal height slabs
+            shape = list(t.shape)
+            shape[2] *= world
+            return ShardTensor.from_local(t, mesh, (Shard(2),), sharding_shapes="chunk", global_shape=tuple(shape))
     loss_fn = MSEDSMLoss(model, sched)
     g = torch.Generator().manual_seed(0)
     cond = torch.randn(batch, 12, res, res, generator=g)

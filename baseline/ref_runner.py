@@ -10,6 +10,7 @@ reference itself is patched and none of this repository's code runs on that path
 from __future__ import annotations
 
 import importlib
+import os
 import importlib.abc
 import importlib.machinery
 import importlib.util
@@ -83,6 +84,9 @@ def import_reference(ref_dir: str):
         sys.meta_path.append(_StubFinder(missing))
     if ref_dir not in sys.path:
         sys.path.insert(0, ref_dir)
+    loaded = sys.modules.get("physicsnemo")
+    if loaded is not None and str(getattr(loaded, "__file__", "")).startswith(os.path.abspath(ref_dir)):
+        return loaded          # already the reference: keep its state (its DistributedManager holds the process group)
     for key in [k for k in sys.modules if k == "physicsnemo" or k.startswith("physicsnemo.")]:
         del sys.modules[key]
     return importlib.import_module("physicsnemo")

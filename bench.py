@@ -42,6 +42,23 @@ def _run_config(name: str, impl: str, args, rank: int, world: int, dev):
     return mod.run(args, rank, world, dev)
 
 
+def _arm_watchdog(line: dict, extras: dict, rank: int, seconds: float) -> None:
+    """The headline number must reach stdout even if an extra configuration stalls: after ``seconds`` every rank leaves,
+    rank 0 first printing the headline line with the extras finished so far."""
+    import threading
+
+    def fire():
+        if rank == 0:
+            out = dict(line)
+            out["extra_configs"] = dict(extras, watchdog=f"extra configurations still running after {seconds:.0f} s; cut off")
+            print(json.dumps(out), flush=True)
+        os._exit(0)
+
+    t = threading.Timer(seconds + (0.0 if rank == 0 else 5.0), fire)
+    t.daemon = True
+    t.start()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -73,13 +90,15 @@ def main():
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        if args.impl != "reference":          # the reference's own DistributedManager brings up the group of its arm
+            dist.init_process_group("nccl", device_id=dev)
     t_start = time.time()
     try:
         line = _run_config(name, args.impl, args, rank, world, dev)
         extras = {}
         if args.config is None and not args.no_extras and isinstance(line, dict) and "unavailable" not in line:
             budget_s = float(os.environ.get("PNM_BENCH_EXTRAS_SECONDS", "420"))
+            _arm_watchdog(line, extras, rank, budget_s + 240.0)
             for extra in EXTRA_ORDER:
                 if time.time() - t_start > budget_s:
                     extras[extra] = {"skipped": "time budget of the extra configurations used up"}
@@ -104,7 +123,8 @@ def main():
             import torch.distributed as dist
 
             try:
-                dist.destroy_process_group()
+                if dist.is_initialized():
+                    dist.destroy_process_group()
             except Exception:  # noqa: BLE001
                 pass
 

@@ -3,21 +3,29 @@
 worker scheduling."""
 from __future__ import annotations
 
+from typing import List, Union
+
 import numpy as np
 import torch
 
 
 def derive_seed(base_seed: int, *coords: int) -> int:
-    seq = np.random.SeedSequence([int(base_seed), *(int(c) for c in coords)])
-    return int(seq.generate_state(1, dtype=np.uint64)[0])
+    """64-bit seed hashed (NumPy ``SeedSequence``) from the base seed followed by the coordinates."""
+    entropy = [int(base_seed)]
+    entropy.extend(int(c) for c in coords)
+    words = np.random.SeedSequence(entropy).generate_state(1, dtype=np.uint64)
+    return int(words[0])
 
 
-def spawn_generator(base_seed: int, *coords: int, device: torch.device | str = "cpu") -> torch.Generator:
-    g = torch.Generator(device=device)
-    g.manual_seed(derive_seed(base_seed, *coords))
-    return g
+def spawn_generator(base_seed: int, *coords: int, device: Union[torch.device, str] = "cpu") -> torch.Generator:
+    """A fresh generator on ``device`` seeded for the given coordinates."""
+    return torch.Generator(device=device).manual_seed(derive_seed(base_seed, *coords))   # manual_seed returns the generator
 
 
-def fork_generator(parent: torch.Generator, n: int) -> list[torch.Generator]:
-    base = parent.initial_seed()
-    return [spawn_generator(base, i, device=parent.device) for i in range(n)]
+def fork_generator(parent: torch.Generator, n: int) -> List[torch.Generator]:
+    """``n`` independent children of ``parent``: child ``i`` is addressed by (``parent``'s initial seed, ``i``)."""
+    root, where = parent.initial_seed(), parent.device
+    children: List[torch.Generator] = []
+    for child in range(n):
+        children.append(spawn_generator(root, child, device=where))
+    return children

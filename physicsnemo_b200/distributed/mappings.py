@@ -1,77 +1,71 @@
 """Tensor-parallel region mappings (Megatron style), groups looked up by name.
 
-Parity: ``physicsnemo/distributed/mappings.py:27-138``.
+Parity: ``physicsnemo/distributed/mappings.py:27-138`` (four autograd functions ``copy_to`` / ``reduce_from`` /
+``scatter_to`` / ``gather_from`` a parallel region).  Here the four are ONE autograd function that is handed the name
+of its forward operation and of its backward operation out of {keep, sum, local chunk, gather}: every mapping is a pair
+of mutually adjoint operations on the region's process group.
 """
+from typing import Optional, Sequence
+
 import torch
 
+from . import utils as _u
 from .manager import DistributedManager
-from .utils import _reduce, _split, all_gather_v_wrapper, compute_split_shapes
 
 
-class _CopyToParallelRegion(torch.autograd.Function):
-    """Identity forward, all-reduce backward."""
+class _Region:
+    """The process group behind a region name and the tensor operations the mappings are made of."""
 
-    @staticmethod
-    def forward(ctx, input_, group_):
-        ctx.group = group_
-        return input_
+    def __init__(self, name: str):
+        manager = DistributedManager()
+        self.group = manager.group(name)
+        self.size = manager.group_size(name)
 
-    @staticmethod
-    def backward(ctx, grad_output):
-        return _reduce(grad_output, group=DistributedManager().group(ctx.group)), None
+    def keep(self, t: torch.Tensor, dim, shapes) -> torch.Tensor:
+        return t
 
+    def total(self, t: torch.Tensor, dim, shapes) -> torch.Tensor:
+        return _u._reduce(t, group=self.group)
 
-class _ReduceFromParallelRegion(torch.autograd.Function):
-    """All-reduce forward, identity backward."""
+    def local_chunk(self, t: torch.Tensor, dim, shapes) -> torch.Tensor:
+        return _u._split(t, dim, group=self.group)
 
-    @staticmethod
-    def forward(ctx, input_, group_):
-        return _reduce(input_, group=DistributedManager().group(group_))
-
-    @staticmethod
-    def backward(ctx, grad_output):
-        return grad_output, None
+    def gathered(self, t: torch.Tensor, dim, shapes) -> torch.Tensor:
+        return _u.all_gather_v_wrapper(t, shapes, dim, group=self.group)
 
 
-class _ScatterToParallelRegion(torch.autograd.Function):
-    """Keep the local chunk forward, all-gather backward."""
+class _RegionMap(torch.autograd.Function):
+    """``forward`` applies operation ``fwd`` of the region, ``backward`` applies ``bwd`` to the incoming gradient."""
 
     @staticmethod
-    def forward(ctx, input_, dim_, group_):
-        ctx.dim, ctx.group = dim_, group_
-        ctx.split_shapes = compute_split_shapes(input_.shape[dim_], DistributedManager().group_size(group_))
-        return _split(input_, dim_, group=DistributedManager().group(group_))
+    def forward(ctx, tensor, fwd: str, bwd: str, region: str, dim: Optional[int], shapes: Optional[Sequence[int]]):
+        where = _Region(region)
+        if dim is not None and shapes is None:            # chunk sizes along ``dim`` of the tensor that gets split
+            shapes = _u.compute_split_shapes(tensor.shape[dim], where.size)
+        ctx.plan = (bwd, region, dim, shapes)
+        return getattr(where, fwd)(tensor, dim, shapes)
 
     @staticmethod
-    def backward(ctx, grad_output):
-        return (all_gather_v_wrapper(grad_output, ctx.split_shapes, ctx.dim, group=DistributedManager().group(ctx.group)),
-                None, None)
-
-
-class _GatherFromParallelRegion(torch.autograd.Function):
-    """All-gather forward, keep the local chunk backward."""
-
-    @staticmethod
-    def forward(ctx, input_, dim_, shapes_, group_):
-        ctx.dim, ctx.group = dim_, group_
-        return all_gather_v_wrapper(input_, shapes_, dim_, group=DistributedManager().group(group_))
-
-    @staticmethod
-    def backward(ctx, grad_output):
-        return _split(grad_output, ctx.dim, group=DistributedManager().group(ctx.group)), None, None, None
+    def backward(ctx, grad):
+        op, region, dim, shapes = ctx.plan
+        return (getattr(_Region(region), op)(grad, dim, shapes),) + (None,) * 5
 
 
 def copy_to_parallel_region(input, group):
-    return _CopyToParallelRegion.apply(input, group)
+    """Identity into the region; the gradients of the region's ranks are summed on the way back."""
+    return _RegionMap.apply(input, "keep", "total", group, None, None)
 
 
 def reduce_from_parallel_region(input, group):
-    return _ReduceFromParallelRegion.apply(input, group)
+    """Sum over the region's ranks; the gradient passes unchanged."""
+    return _RegionMap.apply(input, "total", "keep", group, None, None)
 
 
 def scatter_to_parallel_region(input, dim, group):
-    return _ScatterToParallelRegion.apply(input, dim, group)
+    """This rank's chunk of ``input`` along ``dim``; the gradient chunks are gathered back."""
+    return _RegionMap.apply(input, "local_chunk", "gathered", group, dim, None)
 
 
 def gather_from_parallel_region(input, dim, shapes, group):
-    return _GatherFromParallelRegion.apply(input, dim, shapes, group)
+    """All ranks' chunks (sizes ``shapes`` along ``dim``) concatenated; the gradient keeps this rank's chunk."""
+    return _RegionMap.apply(input, "gathered", "local_chunk", group, dim, shapes)

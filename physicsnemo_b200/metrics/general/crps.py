@@ -1,4 +1,10 @@
-"""Continuous ranked probability score (parity: ``physicsnemo/metrics/general/crps.py``)."""
+"""Continuous ranked probability score (parity: ``physicsnemo/metrics/general/crps.py``).
+
+Three estimators: the kernel form ``E|X − y| − ½ E|X − X'|`` on a sorted ensemble (exact, O(m log m)), the closed form
+for a Gaussian forecast, and the integral of the squared difference between an empirical CDF on bins and the step
+function at the observation.
+"""
+import math
 from typing import Union
 
 import numpy as np
@@ -7,64 +13,69 @@ from torch import Tensor
 
 from .histogram import cdf as cdf_function
 
+_METHODS = ("kernel", "sort", "histogram")
+
+
+def _as_tensor_like(obs, like: Tensor) -> Tensor:
+    return torch.from_numpy(obs).to(like.device) if isinstance(obs, np.ndarray) else obs
+
 
 def _kernel_crps_implementation(pred: Tensor, obs: Tensor, biased: bool) -> Tensor:
-    """``E|X − y| − ½ E|X − X'|`` with the spread term evaluated on the sorted ensemble in O(m log m)."""
-    skill = torch.abs(pred - obs[..., None]).mean(-1)
-    pred, _ = torch.sort(pred)
-    m = pred.size(-1)
-    i = torch.arange(1, m + 1, device=pred.device, dtype=pred.dtype)
-    denom = m * m if biased else m * (m - 1)
-    spread = torch.sum((2 * i - m - 1) / denom * pred, dim=-1)
-    return skill - spread
+    """Ensemble members along the LAST axis.  The pair term ``½ E|X − X'|`` of a sorted sample is the weighted sum
+    ``Σ_i (2i − m − 1) x_(i) / norm`` with ``norm = m²`` (biased) or ``m (m − 1)`` (fair)."""
+    members = pred.shape[-1]
+    distance_to_obs = (pred - obs.unsqueeze(-1)).abs().mean(dim=-1)
+    ordered = pred.sort(dim=-1).values
+    rank = torch.arange(members, device=pred.device, dtype=pred.dtype)
+    weight = (2.0 * rank - (members - 1)) / float(members * members if biased else members * (members - 1))
+    return distance_to_obs - (ordered * weight).sum(dim=-1)
 
 
 def kcrps(pred: Tensor, obs: Tensor, dim: int = 0, biased: bool = True):
-    """Kernel CRPS of an ensemble along ``dim``."""
-    return _kernel_crps_implementation(torch.movedim(pred, dim, -1), obs, biased=biased)
+    """Kernel CRPS of an ensemble whose members run along ``dim``."""
+    return _kernel_crps_implementation(pred.movedim(dim, -1), obs, biased)
 
 
 def _crps_gaussian(mean: Tensor, std: Tensor, obs) -> Tensor:
-    if isinstance(obs, np.ndarray):
-        obs = torch.from_numpy(obs).to(mean.device)
-    if mean.shape != std.shape:
-        raise ValueError(f"Mean and standard deviation must have compatible shapes but found {mean.shape} and {std.shape}.")
-    if mean.shape != obs.shape:
-        raise ValueError(f"Mean and obs must have compatible shapes but found {mean.shape} and {obs.shape}.")
-    d = (obs - mean) / std
-    phi = torch.exp(-0.5 * d ** 2) / (2 * torch.pi) ** 0.5
-    Phi = torch.erf(d / 2 ** 0.5)
-    return std * (2 * phi + d * Phi - 1.0 / torch.pi ** 0.5)
+    """``σ [ z (2Φ(z) − 1) + 2φ(z) − 1/√π ]`` with ``z = (y − μ)/σ``."""
+    obs = _as_tensor_like(obs, mean)
+    for name, other in (("standard deviation", std), ("observation", obs)):
+        if other.shape != mean.shape:
+            raise ValueError(f"the {name} has shape {tuple(other.shape)} but the mean has shape {tuple(mean.shape)}")
+    z = (obs - mean) / std
+    density = torch.exp(-0.5 * z * z) / math.sqrt(2.0 * math.pi)
+    two_cdf_minus_one = torch.erf(z / math.sqrt(2.0))
+    return std * (z * two_cdf_minus_one + 2.0 * density - 1.0 / math.sqrt(math.pi))
 
 
 def _crps_from_cdf(bin_edges: Tensor, cdf: Tensor, obs) -> Tensor:
-    if isinstance(obs, np.ndarray):
-        obs = torch.from_numpy(obs).to(cdf.device)
-    if bin_edges.shape[1:] != cdf.shape[1:]:
-        raise ValueError(f"Expected bins and cdf to have compatible non-zeroth dimensions but have shapes {bin_edges.shape[1:]} and {cdf.shape[1:]}.")
-    if bin_edges.shape[1:] != obs.shape:
-        raise ValueError(f"Expected bins and observations to have compatible broadcasting dimensions but have shapes {bin_edges.shape[1:]} and {obs.shape}.")
-    if bin_edges.shape[0] != cdf.shape[0] + 1:
-        raise ValueError(f"Expected zeroth dimension of cdf to be equal to the zeroth dimension of bins + 1 but have shapes {bin_edges.shape[0]} and {cdf.shape[0]}+1.")
-    dbins = bin_edges[1] - bin_edges[0]
-    mids = 0.5 * (bin_edges[1:] + bin_edges[:-1])
-    heaviside = torch.ge(mids, obs).int()
-    return torch.sum(torch.abs(cdf - heaviside) ** 2 * dbins, dim=0)
+    """``∫ (F(x) − 1[x ≥ y])² dx`` on equally spaced bins: ``bin_edges`` ``[B + 1, ...]``, ``cdf`` ``[B, ...]``."""
+    obs = _as_tensor_like(obs, cdf)
+    trailing = bin_edges.shape[1:]
+    if cdf.shape[1:] != trailing:
+        raise ValueError(f"bins {tuple(bin_edges.shape)} and cdf {tuple(cdf.shape)} differ beyond their first dimension")
+    if obs.shape != trailing:
+        raise ValueError(f"observations {tuple(obs.shape)} do not match the bins' trailing shape {tuple(trailing)}")
+    if bin_edges.shape[0] - 1 != cdf.shape[0]:
+        raise ValueError(f"{bin_edges.shape[0]} bin edges need {bin_edges.shape[0] - 1} cdf values, got {cdf.shape[0]}")
+    width = bin_edges[1] - bin_edges[0]
+    centres = (bin_edges[:-1] + bin_edges[1:]) / 2
+    step = (centres >= obs).to(torch.int32)
+    return ((cdf - step).abs().square() * width).sum(dim=0)
 
 
 def _crps_from_counts(bin_edges: Tensor, counts: Tensor, obs) -> Tensor:
-    cdf_hat = torch.cumsum(counts / torch.sum(counts, dim=0), dim=0)
-    return _crps_from_cdf(bin_edges, cdf_hat, obs)
+    empirical = (counts / counts.sum(dim=0)).cumsum(dim=0)
+    return _crps_from_cdf(bin_edges, empirical, obs)
 
 
 def crps(pred: Tensor, obs, dim: int = 0, method: str = "kernel") -> Tensor:
-    """CRPS of an ensemble forecast: ``method`` in {"kernel", "sort", "histogram"}."""
-    if method not in ["kernel", "sort", "histogram"]:
-        raise ValueError("Method must either be 'kernel', 'sort' or 'histogram'.")
-    n = pred.shape[dim]
+    """CRPS of an ensemble forecast; ``method`` is one of "kernel" / "sort" (exact) or "histogram" (binned CDF)."""
+    if method not in _METHODS:
+        raise ValueError(f"unknown CRPS method {method!r}; choose from {', '.join(_METHODS)}")
     obs = torch.as_tensor(obs, device=pred.device, dtype=pred.dtype)
-    if method in ["kernel", "sort"]:
+    if method != "histogram":
         return kcrps(pred, obs, dim=dim)
-    pred = torch.movedim(pred, dim, 0)
-    bin_edges, c = cdf_function(pred, bins=max(int(np.sqrt(n)), 100))
-    return _crps_from_cdf(bin_edges, c, obs)
+    members = pred.shape[dim]
+    edges, values = cdf_function(pred.movedim(dim, 0), bins=max(int(np.sqrt(members)), 100))
+    return _crps_from_cdf(edges, values, obs)

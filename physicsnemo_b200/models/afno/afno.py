@@ -23,26 +23,28 @@ from ...nn.module.layer_norm import LayerNorm
 
 
 class Block(nn.Module):
-    """AFNO transformer block on (B, H, W, C) tokens."""
+    """AFNO transformer block on (B, H, W, C) tokens: spectral token mixing, then a channel MLP, both pre-normed.
+
+    With ``double_skip`` the block has two residual connections (around the filter and around the MLP); without it a
+    single one spans both.  The MLP adds its residual inside its last GEMM."""
 
     def __init__(self, embed_dim: int, num_blocks: int = 8, mlp_ratio: float = 4.0, drop: float = 0.0,
                  activation_fn: nn.Module = nn.GELU(), norm_layer=LayerNorm, double_skip: bool = True,
                  sparsity_threshold: float = 0.01, hard_thresholding_fraction: float = 1.0):
         super().__init__()
-        self.norm1 = norm_layer(embed_dim)
-        self.filter = AFNO2DLayer(embed_dim, num_blocks, sparsity_threshold, hard_thresholding_fraction)
-        self.norm2 = norm_layer(embed_dim)
-        self.mlp = AFNOMlp(in_features=embed_dim, latent_features=int(embed_dim * mlp_ratio), out_features=embed_dim,
-                           activation_fn=activation_fn, drop=drop)
+        hidden = int(mlp_ratio * embed_dim)
         self.double_skip = double_skip
+        self.norm1, self.norm2 = norm_layer(embed_dim), norm_layer(embed_dim)
+        self.filter = AFNO2DLayer(embed_dim, num_blocks=num_blocks, sparsity_threshold=sparsity_threshold,
+                                  hard_thresholding_fraction=hard_thresholding_fraction)
+        self.mlp = AFNOMlp(embed_dim, hidden, embed_dim, activation_fn=activation_fn, drop=drop)
 
     def forward(self, x: Tensor) -> Tensor:
-        residual = x
-        x = self.filter(self.norm1(x))
+        mixed = self.filter(self.norm1(x))
+        skip = x
         if self.double_skip:
-            x = x + residual
-            residual = x
-        return self.mlp(self.norm2(x), residual=residual)
+            mixed = skip = mixed + x
+        return self.mlp(self.norm2(mixed), residual=skip)
 
 
 @dataclass
@@ -66,58 +68,53 @@ class AFNO(Module):
                  num_blocks: int = 16, sparsity_threshold: float = 0.01,
                  hard_thresholding_fraction: float = 1.0) -> None:
         super().__init__(meta=MetaData())
-        if len(inp_shape) != 2:
-            raise ValueError("inp_shape should be a list of length 2")
-        if len(patch_size) != 2:
-            raise ValueError("patch_size should be a list of length 2")
-        if not (inp_shape[0] % patch_size[0] == 0 and inp_shape[1] % patch_size[1] == 0):
-            raise ValueError(f"input shape {inp_shape} should be divisible by patch_size {patch_size}")
-        self.in_chans, self.out_chans = in_channels, out_channels
+        for name, pair in (("inp_shape", inp_shape), ("patch_size", patch_size)):
+            if len(pair) != 2:
+                raise ValueError(f"{name} must give (height, width); got {list(pair)}")
+        if any(n % p for n, p in zip(inp_shape, patch_size)):
+            raise ValueError(f"a {list(inp_shape)} grid cannot be cut into {list(patch_size)} patches without remainder")
         self.inp_shape, self.patch_size = inp_shape, patch_size
-        self.num_features = self.embed_dim = embed_dim
+        self.in_chans, self.out_chans = in_channels, out_channels
+        self.embed_dim = self.num_features = embed_dim
         self.num_blocks = num_blocks
-        norm_layer = partial(LayerNorm, eps=1e-6)
+        self.h, self.w = (n // p for n, p in zip(inp_shape, patch_size))        # token grid
         self.patch_embed = AFNOPatchEmbed(inp_shape=inp_shape, in_channels=in_channels, patch_size=patch_size,
                                           embed_dim=embed_dim)
         self.pos_embed = nn.Parameter(torch.zeros(1, self.patch_embed.num_patches, embed_dim))
         self.pos_drop = nn.Dropout(p=drop_rate)
-        self.h = inp_shape[0] // patch_size[0]
-        self.w = inp_shape[1] // patch_size[1]
-        self.blocks = nn.ModuleList([
-            Block(embed_dim=embed_dim, num_blocks=num_blocks, mlp_ratio=mlp_ratio, drop=drop_rate,
-                  norm_layer=norm_layer, sparsity_threshold=sparsity_threshold,
-                  hard_thresholding_fraction=hard_thresholding_fraction)
-            for _ in range(depth)
-        ])
-        self.head = nn.Linear(embed_dim, out_channels * patch_size[0] * patch_size[1], bias=False)
-        torch.nn.init.trunc_normal_(self.pos_embed, std=0.02)
+        block_args = dict(num_blocks=num_blocks, mlp_ratio=mlp_ratio, drop=drop_rate, norm_layer=partial(LayerNorm, eps=1e-6),
+                          sparsity_threshold=sparsity_threshold, hard_thresholding_fraction=hard_thresholding_fraction)
+        self.blocks = nn.ModuleList(Block(embed_dim, **block_args) for _ in range(depth))
+        self.head = nn.Linear(embed_dim, patch_size[0] * patch_size[1] * out_channels, bias=False)
+        nn.init.trunc_normal_(self.pos_embed, std=0.02)
         self.apply(self._init_weights)
 
-    def _init_weights(self, m: nn.Module) -> None:
-        if isinstance(m, nn.Linear):
-            torch.nn.init.trunc_normal_(m.weight, std=0.02)
+    @staticmethod
+    def _init_weights(m: nn.Module) -> None:
+        """Linear layers: truncated normal weights (std 0.02), zero bias; LayerNorm: unit scale, zero shift."""
+        if isinstance(m, nn.LayerNorm):
+            nn.init.ones_(m.weight)
+            nn.init.zeros_(m.bias)
+        elif isinstance(m, nn.Linear):
+            nn.init.trunc_normal_(m.weight, std=0.02)
             if m.bias is not None:
-                nn.init.constant_(m.bias, 0)
-        elif isinstance(m, nn.LayerNorm):
-            nn.init.constant_(m.bias, 0)
-            nn.init.constant_(m.weight, 1.0)
+                nn.init.zeros_(m.bias)
 
     def _forward_features(self, x: Tensor) -> Tensor:
-        B = x.shape[0]
-        x = self.patch_embed(x)
-        x = self.pos_drop(x + self.pos_embed)
-        x = x.reshape(B, self.h, self.w, self.embed_dim)
+        tokens = self.pos_drop(self.patch_embed(x) + self.pos_embed)
+        tokens = tokens.reshape(x.shape[0], self.h, self.w, self.embed_dim)
         for blk in self.blocks:
-            x = blk(x)
-        return x
+            tokens = blk(tokens)
+        return tokens
 
     def forward(self, x: Tensor) -> Tensor:
         if not torch.compiler.is_compiling():
-            expected = (self.in_chans, self.inp_shape[0], self.inp_shape[1])
-            if x.ndim != 4 or tuple(x.shape[1:]) != expected:
-                raise ValueError(f"Expected input shape (B, {expected[0]}, {expected[1]}, {expected[2]}), got {tuple(x.shape)}")
-        x = self._forward_features(x)
-        x = ops.linear(x, self.head.weight, None)
-        out = x.view(list(x.shape[:-1]) + [self.patch_size[0], self.patch_size[1], -1])
-        out = torch.permute(out, (0, 5, 1, 3, 2, 4))
-        return out.reshape(list(out.shape[:2]) + [self.inp_shape[0], self.inp_shape[1]])
+            wanted = (self.in_chans, *self.inp_shape)
+            if x.ndim != 4 or tuple(x.shape[1:]) != wanted:
+                raise ValueError(f"AFNO was built for inputs [B, {wanted[0]}, {wanted[1]}, {wanted[2]}]; got {tuple(x.shape)}")
+        tokens = ops.linear(self._forward_features(x), self.head.weight, None)           # [B, h, w, p0 * p1 * C_out]
+        p0, p1 = self.patch_size
+        B = tokens.shape[0]
+        # un-patchify: the head's features are ordered (p0, p1, channel)
+        image = tokens.reshape(B, self.h, self.w, p0, p1, self.out_chans).permute(0, 5, 1, 3, 2, 4)
+        return image.reshape(B, self.out_chans, self.h * p0, self.w * p1)

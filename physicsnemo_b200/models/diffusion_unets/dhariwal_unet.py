@@ -20,6 +20,7 @@ from ...nn.module.fully_connected_layers import Linear
 from ...nn.module.group_norm import get_group_norm
 from ...nn.module.unet_layers import UNetBlock
 from ...nn.module.utils.utils import _recursive_property
+from ._adm_layout import Stage, unet_layout
 
 
 @dataclass
@@ -36,83 +37,80 @@ class MetaData(ModelMetaData):
 
 
 class DhariwalUNet(Module):
+    """``forward(x, noise_labels, class_labels=None, augment_labels=None)`` → ``[B, out_channels, H, W]``."""
+
     def __init__(self, img_resolution: int, in_channels: int, out_channels: int, label_dim: int = 0, augment_dim: int = 0,
                  model_channels: int = 192, channel_mult: List[int] = [1, 2, 3, 4], channel_mult_emb: int = 4,
                  num_blocks: int = 3, attn_resolutions: List[int] = [32, 16, 8], dropout: float = 0.10,
                  label_dropout: float = 0.0):
         super().__init__(meta=MetaData())
         self.label_dim, self.augment_dim, self.label_dropout = label_dim, augment_dim, label_dropout
-        emb_channels = model_channels * channel_mult_emb
-        init = dict(init_mode="kaiming_uniform", init_weight=np.sqrt(1 / 3), init_bias=np.sqrt(1 / 3))
-        init_zero = dict(init_mode="kaiming_uniform", init_weight=0, init_bias=0)
-        blk = dict(emb_channels=emb_channels, channels_per_head=64, dropout=dropout, init=init, init_zero=init_zero)
+        width_emb = channel_mult_emb * model_channels
+        third = float(np.sqrt(1 / 3))
+        uniform = {"init_mode": "kaiming_uniform", "init_weight": third, "init_bias": third}
+        zeros = {"init_mode": "kaiming_uniform", "init_weight": 0, "init_bias": 0}
+        # embedding path (all names are checkpoint keys): noise features (+ augmentation map) -> 2-layer MLP (+ label map)
         self.map_noise = PositionalEmbedding(num_channels=model_channels)
-        self.map_augment = Linear(in_features=augment_dim, out_features=model_channels, bias=False, **init_zero) if augment_dim else None
-        self.map_layer0 = Linear(in_features=model_channels, out_features=emb_channels, **init)
-        self.map_layer1 = Linear(in_features=emb_channels, out_features=emb_channels, **init)
-        self.map_label = Linear(in_features=label_dim, out_features=emb_channels, bias=False, init_mode="kaiming_normal",
-                                init_weight=np.sqrt(label_dim)) if label_dim else None
-        self.enc = torch.nn.ModuleDict()
-        cout = in_channels
-        for level, mult in enumerate(channel_mult):
-            res = img_resolution >> level
-            if level == 0:
-                cin, cout = cout, model_channels * mult
-                self.enc[f"{res}x{res}_conv"] = Conv2d(in_channels=cin, out_channels=cout, kernel=3, **init)
-            else:
-                self.enc[f"{res}x{res}_down"] = UNetBlock(in_channels=cout, out_channels=cout, down=True, **blk)
-            for idx in range(num_blocks):
-                cin, cout = cout, model_channels * mult
-                self.enc[f"{res}x{res}_block{idx}"] = UNetBlock(in_channels=cin, out_channels=cout,
-                                                                attention=(res in attn_resolutions), **blk)
-        skips = [b.out_channels for b in self.enc.values()]
-        self.dec = torch.nn.ModuleDict()
-        for level, mult in reversed(list(enumerate(channel_mult))):
-            res = img_resolution >> level
-            if level == len(channel_mult) - 1:
-                self.dec[f"{res}x{res}_in0"] = UNetBlock(in_channels=cout, out_channels=cout, attention=True, **blk)
-                self.dec[f"{res}x{res}_in1"] = UNetBlock(in_channels=cout, out_channels=cout, **blk)
-            else:
-                self.dec[f"{res}x{res}_up"] = UNetBlock(in_channels=cout, out_channels=cout, up=True, **blk)
-            for idx in range(num_blocks + 1):
-                cin, cout = cout + skips.pop(), model_channels * mult
-                self.dec[f"{res}x{res}_block{idx}"] = UNetBlock(in_channels=cin, out_channels=cout,
-                                                                attention=(res in attn_resolutions), **blk)
-        self.out_norm = get_group_norm(num_channels=cout)
-        self.out_conv = Conv2d(in_channels=cout, out_channels=out_channels, kernel=3, **init_zero)
+        self.map_augment = Linear(augment_dim, model_channels, bias=False, **zeros) if augment_dim else None
+        self.map_layer0 = Linear(model_channels, width_emb, **uniform)
+        self.map_layer1 = Linear(width_emb, width_emb, **uniform)
+        self.map_label = None
+        if label_dim:
+            self.map_label = Linear(label_dim, width_emb, bias=False, init_mode="kaiming_normal", init_weight=np.sqrt(label_dim))
+        encoder, decoder, width_last = unet_layout(img_resolution, in_channels, model_channels, channel_mult, num_blocks,
+                                                   attn_resolutions)
+
+        def build(stage: Stage) -> torch.nn.Module:
+            if stage.kind == "conv":
+                return Conv2d(in_channels=stage.width_in, out_channels=stage.width_out, kernel=3, **uniform)
+            return UNetBlock(in_channels=stage.width_in, out_channels=stage.width_out, emb_channels=width_emb, dropout=dropout,
+                             channels_per_head=64, init=uniform, init_zero=zeros, **dict(stage.options))
+
+        self.enc = torch.nn.ModuleDict({stage.key: build(stage) for stage in encoder})
+        self.dec = torch.nn.ModuleDict({stage.key: build(stage) for stage in decoder})
+        self.out_norm = get_group_norm(num_channels=width_last)
+        self.out_conv = Conv2d(in_channels=width_last, out_channels=out_channels, kernel=3, **zeros)
         self.profile_mode = False
         self.amp_mode = False
 
     profile_mode = _recursive_property("profile_mode", bool, "Should be set to ``True`` to enable profiling.")
     amp_mode = _recursive_property("amp_mode", bool, "Should be set to ``True`` to enable automatic mixed precision.")
 
-    def forward(self, x, noise_labels, class_labels=None, augment_labels=None):
-        if not torch.compiler.is_compiling():
-            B = x.shape[0]
-            if x.ndim != 4:
-                raise ValueError(f"Expected 'x' to be a 4D tensor (B, C_in, H, W), got {x.ndim}D tensor with shape {tuple(x.shape)}")
-            if noise_labels.ndim != 1 or noise_labels.shape[0] not in (B, 1):
-                raise ValueError(f"Expected 'noise_labels' shape ({B},) or (1,), got {tuple(noise_labels.shape)}")
-            if self.label_dim > 0 and class_labels is not None and tuple(class_labels.shape) != (B, self.label_dim):
-                raise ValueError(f"Expected 'class_labels' shape ({B}, {self.label_dim}), got {tuple(class_labels.shape)}")
-            if self.augment_dim > 0 and augment_labels is not None and tuple(augment_labels.shape) != (B, self.augment_dim):
-                raise ValueError(f"Expected 'augment_labels' shape ({B}, {self.augment_dim}), got {tuple(augment_labels.shape)}")
+    def _check_inputs(self, x, noise_labels, class_labels, augment_labels) -> None:
+        if x.ndim != 4:
+            raise ValueError(f"'x' must be a batch of images [B, C_in, H, W]; got shape {tuple(x.shape)}")
+        batch = x.shape[0]
+        if noise_labels.ndim != 1 or noise_labels.shape[0] not in (1, batch):
+            raise ValueError(f"'noise_labels' must hold one level per sample ([{batch}]) or a single level ([1]); "
+                             f"got shape {tuple(noise_labels.shape)}")
+        for name, labels, width in (("class_labels", class_labels, self.label_dim),
+                                    ("augment_labels", augment_labels, self.augment_dim)):
+            if width > 0 and labels is not None and tuple(labels.shape) != (batch, width):
+                raise ValueError(f"'{name}' must have shape ({batch}, {width}); got {tuple(labels.shape)}")
+
+    def _embedding(self, batch, device, noise_labels, class_labels, augment_labels):
         emb = self.map_noise(noise_labels)
-        if self.map_augment is not None and augment_labels is not None:
+        if augment_labels is not None and self.map_augment is not None:
             emb = emb + self.map_augment(augment_labels)
         emb = self.map_layer1(silu(self.map_layer0(emb)))
         if self.map_label is not None:
-            lab = class_labels
-            if self.training and self.label_dropout:
-                lab = lab * (torch.rand([x.shape[0], 1], device=x.device) >= self.label_dropout).to(lab.dtype)
-            emb = emb + self.map_label(lab)
-        emb = silu(emb)
-        skips = []
-        for block in self.enc.values():
-            x = block(x, emb) if isinstance(block, UNetBlock) else block(x)
-            skips.append(x)
-        for block in self.dec.values():
-            if x.shape[1] != block.in_channels:
-                x = torch.cat([x, skips.pop()], dim=1)
-            x = block(x, emb)
-        return self.out_conv(silu(self.out_norm(x)))
+            labels = class_labels
+            if self.label_dropout and self.training:       # drop whole label vectors (classifier-free guidance)
+                dropped = torch.rand([batch, 1], device=device) < self.label_dropout
+                labels = labels.masked_fill(dropped, 0)
+            emb = emb + self.map_label(labels)
+        return silu(emb)
+
+    def forward(self, x, noise_labels, class_labels=None, augment_labels=None):
+        if not torch.compiler.is_compiling():
+            self._check_inputs(x, noise_labels, class_labels, augment_labels)
+        emb = self._embedding(x.shape[0], x.device, noise_labels, class_labels, augment_labels)
+        h, stack = x, []
+        for stage in self.enc.values():
+            h = stage(h, emb) if isinstance(stage, UNetBlock) else stage(h)
+            stack.append(h)
+        for stage in self.dec.values():
+            if stage.in_channels != h.shape[1]:            # this block takes a skip connection
+                h = torch.cat((h, stack.pop()), dim=1)
+            h = stage(h, emb)
+        return self.out_conv(silu(self.out_norm(h)))

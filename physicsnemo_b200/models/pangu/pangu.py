@@ -35,6 +35,27 @@ def _expect(cond, msg):
         raise ValueError(msg)
 
 
+def _check_field(name: str, tensor, wanted: tuple) -> None:
+    """``tensor`` must have exactly the shape ``wanted`` (batch first where there is one); the message names the first
+    axis that differs: sample, channel, pressure level or grid."""
+    got = tuple(tensor.shape)
+    if got == tuple(wanted):
+        return
+    if len(got) != len(wanted):
+        raise ValueError(f"'{name}' should have {len(wanted)} dimensions {tuple(wanted)}, but its shape is {got}")
+    axis = next(i for i, (g, w) in enumerate(zip(got, wanted)) if g != w)
+    from_end = len(wanted) - axis
+    if from_end <= 2:
+        what = "grid size"
+    elif axis == 0 and len(wanted) >= 4:
+        what = "batch size"
+    elif len(wanted) == 5 and axis == 2:
+        what = "number of pressure levels"
+    else:
+        what = "channel count"
+    raise ValueError(f"'{name}' has the wrong {what}: expected shape {tuple(wanted)}, got {got}")
+
+
 class Pangu(Module):
     def __init__(self, img_size: tuple[int, int] = (721, 1440), patch_size: tuple[int, int, int] = (2, 4, 4),
                  embed_dim: int = 192, num_heads: tuple[int, int, int, int] = (6, 12, 12, 6),
@@ -67,29 +88,20 @@ class Pangu(Module):
     def prepare_input(self, surface, surface_mask, upper_air):
         """Concatenate ``surface [B,4,H,W]``, ``surface_mask [3,H,W]`` (or batched) and ``upper_air [B,5,13,H,W]``."""
         if not torch.compiler.is_compiling():
-            hw = self.img_size
-            _expect(surface.ndim == 4, f"Expected 'surface' to be a 4D tensor, got {surface.ndim}D tensor with shape {tuple(surface.shape)}")
-            _expect(surface.shape[1] == self.surface_channels, f"Expected 'surface' to have {self.surface_channels} channels, got tensor with shape {tuple(surface.shape)}")
-            _expect(tuple(surface.shape[2:]) == hw, f"Expected 'surface' spatial shape {hw}, got tensor with shape {tuple(surface.shape)}")
-            _expect(surface_mask.ndim in (3, 4), f"Expected 'surface_mask' to be a 3D or 4D tensor, got {surface_mask.ndim}D tensor with shape {tuple(surface_mask.shape)}")
-            if surface_mask.ndim == 4:
-                _expect(surface_mask.shape[0] == surface.shape[0], f"Expected 'surface_mask' batch size {surface.shape[0]}, got tensor with shape {tuple(surface_mask.shape)}")
-            _expect(surface_mask.shape[-3] == self.surface_mask_channels, f"Expected 'surface_mask' to have {self.surface_mask_channels} channels, got tensor with shape {tuple(surface_mask.shape)}")
-            _expect(tuple(surface_mask.shape[-2:]) == hw, f"Expected 'surface_mask' spatial shape {hw}, got tensor with shape {tuple(surface_mask.shape)}")
-            _expect(upper_air.ndim == 5, f"Expected 'upper_air' to be a 5D tensor, got {upper_air.ndim}D tensor with shape {tuple(upper_air.shape)}")
-            _expect(upper_air.shape[0] == surface.shape[0], f"Expected 'upper_air' batch size {surface.shape[0]}, got tensor with shape {tuple(upper_air.shape)}")
-            _expect(upper_air.shape[1] == self.upper_air_channels, f"Expected 'upper_air' to have {self.upper_air_channels} channels, got tensor with shape {tuple(upper_air.shape)}")
-            _expect(upper_air.shape[2] == self.upper_air_levels, f"Expected 'upper_air' to have {self.upper_air_levels} pressure levels, got tensor with shape {tuple(upper_air.shape)}")
-            _expect(tuple(upper_air.shape[3:]) == hw, f"Expected 'upper_air' spatial shape {hw}, got tensor with shape {tuple(upper_air.shape)}")
+            batch = surface.shape[0]
+            _check_field("surface", surface, (batch, self.surface_channels, *self.img_size))
+            _expect(surface_mask.ndim in (3, 4), f"'surface_mask' is either one [C, H, W] mask for all samples or a batch "
+                                                  f"[B, C, H, W] of masks; its shape is {tuple(surface_mask.shape)}")
+            lead = (batch,) if surface_mask.ndim == 4 else ()
+            _check_field("surface_mask", surface_mask, (*lead, self.surface_mask_channels, *self.img_size))
+            _check_field("upper_air", upper_air, (batch, self.upper_air_channels, self.upper_air_levels, *self.img_size))
         if surface_mask.ndim == 3:
             surface_mask = surface_mask.unsqueeze(0).repeat(surface.shape[0], 1, 1, 1)
         return torch.cat([surface, surface_mask, upper_air.flatten(1, 2)], dim=1)
 
     def forward(self, x):
         if not torch.compiler.is_compiling():
-            _expect(x.ndim == 4, f"Expected 'x' to be a 4D tensor, got {x.ndim}D tensor with shape {tuple(x.shape)}")
-            _expect(x.shape[1] == self.in_channels, f"Expected 'x' to have {self.in_channels} channels, got tensor with shape {tuple(x.shape)}")
-            _expect(tuple(x.shape[2:]) == self.img_size, f"Expected 'x' spatial shape {self.img_size}, got tensor with shape {tuple(x.shape)}")
+            _check_field("x", x, (x.shape[0], self.in_channels, *self.img_size))
         n_s = self.surface_input_channels
         surface = self.patchembed2d(x[:, :n_s])
         upper = self.patchembed3d(x[:, n_s:].reshape(x.shape[0], self.upper_air_channels, self.upper_air_levels, *x.shape[2:]))

@@ -18,103 +18,90 @@ class Identity(nn.Module):
         return x
 
 
+class Sin(nn.Module):
+    """Sine activation."""
+
+    def forward(self, x: Tensor) -> Tensor:
+        return x.sin()
+
+
 class Stan(nn.Module):
-    """Self-scalable tanh: ``tanh(x) * (1 + beta * x)`` with learnable ``beta``."""
+    """Self-scalable tanh: ``tanh(x) * (1 + beta * x)`` with one learnable ``beta`` per feature."""
 
     def __init__(self, out_features: int = 1):
         super().__init__()
         self.beta = nn.Parameter(torch.ones(out_features))
 
     def forward(self, x: Tensor) -> Tensor:
-        if x.shape[-1] != self.beta.shape[-1]:
-            raise ValueError(
-                f"The last dimension of the input must be equal to the dimension of Stan parameters. Got inputs: {x.shape}, params: {self.beta.shape}"
-            )
-        return torch.tanh(x) * (1.0 + self.beta * x)
+        width = self.beta.numel()
+        if x.size(-1) != width:
+            raise ValueError(f"Stan holds {width} slopes, so the input's last dimension must be {width}; got {tuple(x.shape)}")
+        squashed = torch.tanh(x)
+        return torch.addcmul(squashed, squashed, self.beta * x)
 
 
 class SquarePlus(nn.Module):
-    """``0.5 * (x + sqrt(x^2 + b))`` with ``b = 4``."""
+    """``0.5 * (x + sqrt(x^2 + b))`` with ``b = 4``: a smooth ReLU without exponentials."""
 
     def __init__(self):
         super().__init__()
         self.b = 4
 
     def forward(self, x: Tensor) -> Tensor:
-        return 0.5 * (x + torch.sqrt(x * x + self.b))
+        return (x + (x.square() + self.b).sqrt()) / 2
 
 
-class CappedLeakyReLU(nn.Module):
+class _Capped(nn.Module):
+    """``min(inner(x), cap)``; the inner activation is registered under ``slot`` (a state-dict key of checkpoints)."""
+
+    slot: str = ""
+    inner_type: type = nn.Identity
+
+    def __init__(self, cap_value=1.0, **kwargs):
+        super().__init__()
+        setattr(self, self.slot, self.inner_type(**kwargs))
+        self.register_buffer("cap", torch.tensor(cap_value, dtype=torch.float32))
+
+    def forward(self, inputs):
+        return torch.minimum(getattr(self, self.slot)(inputs), self.cap.to(inputs.dtype))
+
+
+class CappedLeakyReLU(_Capped):
     """Leaky ReLU clamped from above at ``cap_value``."""
 
-    def __init__(self, cap_value=1.0, **kwargs):
-        super().__init__()
-        self.add_module("leaky_relu", nn.LeakyReLU(**kwargs))
-        self.register_buffer("cap", torch.tensor(cap_value, dtype=torch.float32))
-
-    def forward(self, inputs):
-        return torch.clamp(self.leaky_relu(inputs), max=self.cap)
+    slot, inner_type = "leaky_relu", nn.LeakyReLU
 
 
-class CappedGELU(nn.Module):
+class CappedGELU(_Capped):
     """GELU clamped from above at ``cap_value``."""
 
-    def __init__(self, cap_value=1.0, **kwargs):
-        super().__init__()
-        self.add_module("gelu", nn.GELU(**kwargs))
-        self.register_buffer("cap", torch.tensor(cap_value, dtype=torch.float32))
-
-    def forward(self, inputs):
-        return torch.clamp(self.gelu(inputs), max=self.cap)
+    slot, inner_type = "gelu", nn.GELU
 
 
-class Sin(nn.Module):
-    """Sine activation."""
-
-    def forward(self, x: Tensor) -> Tensor:
-        return torch.sin(x)
-
-
-ACT2FN = {
-    "relu": nn.ReLU,
-    "leaky_relu": (nn.LeakyReLU, {"negative_slope": 0.1}),
-    "prelu": nn.PReLU,
-    "relu6": nn.ReLU6,
-    "elu": nn.ELU,
+# name -> class, or (class, constructor arguments) where the reference fixes arguments
+_TORCH_BY_NAME = {name.lower(): getattr(nn, name) for name in (
+    "ELU", "GELU", "Hardtanh", "LogSigmoid", "PReLU", "ReLU", "ReLU6", "SELU", "SiLU", "Sigmoid", "Softplus", "Softshrink",
+    "Softsign", "Tanh", "Tanhshrink")}
+_WITH_ARGUMENTS = {
     "celu": (nn.CELU, {"alpha": 1.0}),
-    "selu": nn.SELU,
-    "silu": nn.SiLU,
-    "gelu": nn.GELU,
-    "sin": Sin,
-    "sigmoid": nn.Sigmoid,
-    "logsigmoid": nn.LogSigmoid,
-    "softplus": nn.Softplus,
-    "softshrink": nn.Softshrink,
-    "softsign": nn.Softsign,
-    "tanh": nn.Tanh,
-    "tanhshrink": nn.Tanhshrink,
+    "leaky_relu": (nn.LeakyReLU, {"negative_slope": 0.1}),
     "threshold": (nn.Threshold, {"threshold": 1.0, "value": 1.0}),
-    "hardtanh": nn.Hardtanh,
-    "identity": Identity,
-    "stan": Stan,
-    "squareplus": SquarePlus,
-    "cappek_leaky_relu": CappedLeakyReLU,
-    "capped_leaky_relu": CappedLeakyReLU,
-    "capped_gelu": CappedGELU,
 }
+_OWN = {"identity": Identity, "sin": Sin, "stan": Stan, "squareplus": SquarePlus, "capped_gelu": CappedGELU,
+        "capped_leaky_relu": CappedLeakyReLU, "cappek_leaky_relu": CappedLeakyReLU}   # the misspelt key is a published alias
+ACT2FN = {**_TORCH_BY_NAME, **_WITH_ARGUMENTS, **_OWN}
 
 
 def get_activation(activation: str) -> nn.Module:
-    """Instantiate the activation registered under ``activation``."""
-    try:
-        entry = ACT2FN[activation.lower()]
-    except KeyError:
-        raise KeyError(
-            f"Activation function {activation} not found. Available options are: {list(ACT2FN.keys())}"
-        )
-    if isinstance(entry, tuple):
-        return entry[0](**entry[1])
-    return entry()
+    """A new instance of the activation registered under ``activation`` (case-insensitive)."""
+    entry = ACT2FN.get(activation.lower())
+    if entry is None:
+        raise KeyError(f"no activation is registered as {activation!r}; known names: {sorted(ACT2FN)}")
+    cls, kwargs = entry if isinstance(entry, tuple) else (entry, {})
+    return cls(**kwargs)
+
+
+_EPILOGUE_CODES = ((nn.SiLU, 2), (nn.ReLU, 3))
 
 
 def activation_code(act) -> int | None:
@@ -124,10 +111,9 @@ def activation_code(act) -> int | None:
     """
     if act is None or isinstance(act, (Identity, nn.Identity)):
         return 0
-    if isinstance(act, nn.GELU) and getattr(act, "approximate", "none") == "none":
-        return 1
-    if isinstance(act, nn.SiLU):
-        return 2
-    if isinstance(act, nn.ReLU):
-        return 3
+    if isinstance(act, nn.GELU):
+        return 1 if getattr(act, "approximate", "none") == "none" else None
+    for kind, code in _EPILOGUE_CODES:
+        if isinstance(act, kind):
+            return code
     return None

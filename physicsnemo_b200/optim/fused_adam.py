@@ -34,36 +34,77 @@ def _declare(lib):
 
 
 class _Tables:
-    """Pinned host + device copies of the entry / block tables of one parameter group."""
+    """Device copy of the entry / block tables of one parameter group, fed from a ring of pinned host buffers.
 
-    def __init__(self, n_entries: int, n_blocks: int, device):
-        self.host = torch.empty(n_entries * _ENTRY_WORDS + n_blocks, dtype=torch.int64).pin_memory()
-        self.dev = torch.empty_like(self.host, device=device)
+    The upload is an asynchronous copy, and a GPU-bound training loop runs the host several steps ahead of the device:
+    a host buffer is therefore rewritten only after the copy that last read it has executed (one event per ring slot),
+    and not at all while the pointers are the ones already on the device.  Under stream capture the copy becomes a node
+    that re-reads its host buffer at every replay, so captured uploads get a buffer of their own that is never reused.
+    """
+
+    RING = 3
+
+    def __init__(self, n_entries: int, n_blocks: int, device, blocks: torch.Tensor):
+        words = n_entries * _ENTRY_WORDS + n_blocks
         self.n_entries, self.n_blocks = n_entries, n_blocks
+        self.blocks = blocks
+        self.hosts = [self._new_host(words) for _ in range(self.RING)]
+        self.events = [None] * self.RING
+        self.slot = 0
+        self.dev = torch.empty(words, dtype=torch.int64, device=device)
+        self.rows_on_device = None
+        self.captured_hosts = []
+        self.spare = self._new_host(words)       # pinned memory cannot be allocated while a stream is capturing
 
-    def upload(self):
-        self.dev.copy_(self.host, non_blocking=True)
+    def _new_host(self, words: int) -> torch.Tensor:
+        h = torch.empty(words, dtype=torch.int64).pin_memory()
+        h[self.n_entries * _ENTRY_WORDS:] = self.blocks
+        return h
+
+    def upload(self, rows):
+        """Make the device table hold ``rows`` (a flat list of ints); returns the entry and block table addresses."""
+        capturing = torch.cuda.is_current_stream_capturing()
+        if capturing or rows != self.rows_on_device:
+            if capturing:
+                host, self.spare = self.spare, None
+                if host is None:
+                    raise RuntimeError("FusedAdam: run one eager step between two captures of step() (staging buffers "
+                                       "for a captured step are set aside outside of capture)")
+                self.captured_hosts.append(host)
+            else:
+                if self.spare is None:
+                    self.spare = self._new_host(self.dev.numel())
+                self.slot = (self.slot + 1) % self.RING
+                ev = self.events[self.slot]
+                if ev is not None:
+                    ev.synchronize()                      # the copy that last read this buffer has run
+                host = self.hosts[self.slot]
+            host[: len(rows)] = torch.tensor(rows, dtype=torch.int64)
+            self.dev.copy_(host, non_blocking=True)
+            if not capturing:
+                ev = self.events[self.slot] or torch.cuda.Event()
+                ev.record()
+                self.events[self.slot] = ev
+            # a captured upload is replayed later with these rows; an eager step in between must upload again
+            self.rows_on_device = None if capturing else list(rows)
         base = self.dev.data_ptr()
         return base, base + self.n_entries * _ENTRY_WORDS * 8
 
 
 def build_tables(params, grads, ms, vs, chunk: int, cache: dict):
-    """Fill (and cache by shape signature) the tables for the given tensors."""
+    """The (cached by shape signature) tables for the given tensors and the rows that describe them."""
     key = tuple(p.numel() for p in params)
-    n_blocks = sum((n + chunk - 1) // chunk for n in key)
     t = cache.get(key)
     if t is None:
-        t = cache[key] = _Tables(len(params), n_blocks, params[0].device)
         blocks = []
         for i, n in enumerate(key):
             blocks += [i | (j << 32) for j in range((n + chunk - 1) // chunk)]  # int2 {entry, chunk} little-endian
-        t.host[len(params) * _ENTRY_WORDS:] = torch.tensor(blocks, dtype=torch.int64)
+        t = cache[key] = _Tables(len(params), len(blocks), params[0].device, torch.tensor(blocks, dtype=torch.int64))
     rows = []
     for p, g, m, v in zip(params, grads, ms, vs):
         rows += [p.data_ptr(), g.data_ptr(), m.data_ptr() if m is not None else 0, v.data_ptr() if v is not None else 0,
                  p.numel(), 1 if g.dtype == torch.bfloat16 else 0]
-    t.host[: len(rows)] = torch.tensor(rows, dtype=torch.int64)
-    return t
+    return t, rows
 
 
 class FusedAdam(Optimizer):
@@ -94,7 +135,8 @@ class FusedAdam(Optimizer):
     def _hyper_of(self, gi: int, group, device) -> torch.Tensor:
         h = self._hyper.get(gi)
         if h is None:
-            h = self._hyper[gi] = torch.tensor([float(group["lr"]), 0.0], dtype=torch.float32, device=device)
+            done = max((int(self.state[p]["step"]) for p in group["params"] if p in self.state and self.state[p]), default=1) - 1
+            h = self._hyper[gi] = torch.tensor([float(group["lr"]), float(max(done, 0))], dtype=torch.float32, device=device)
         return h
 
     def set_lr(self, lr: float, group: Optional[int] = None) -> None:
@@ -104,6 +146,41 @@ class FusedAdam(Optimizer):
                 g["lr"] = lr
                 if gi in self._hyper:
                     self._hyper[gi][0] = float(lr)
+
+    def _sync_host_from_device(self) -> None:
+        """Capturable mode keeps {lr, step} on the device and graph replays advance them without running ``step()``:
+        bring the host copies (``param_groups[i]["lr"]``, ``state[p]["step"]``) up to date."""
+        for gi, group in enumerate(self.param_groups):
+            h = self._hyper.get(gi)
+            if h is None:
+                continue
+            lr, t = (float(v) for v in h.tolist())
+            group["lr"] = lr
+            for p in group["params"]:
+                if p in self.state and self.state[p]:
+                    self.state[p]["step"] = int(round(t))
+
+    def state_dict(self):
+        if self.capturable:
+            self._sync_host_from_device()
+        return super().state_dict()
+
+    def load_state_dict(self, state_dict) -> None:
+        super().load_state_dict(state_dict)
+        for gi, group in enumerate(self.param_groups):
+            steps = [int(self.state[p]["step"]) for p in group["params"] if p in self.state and "step" in self.state[p]]
+            for p in group["params"]:
+                if p in self.state and "step" in self.state[p]:
+                    self.state[p]["step"] = int(self.state[p]["step"])
+            if self.capturable and steps:
+                dev = next((p.device for p in group["params"] if p.is_cuda), None)
+                if dev is None:
+                    continue
+                vals = torch.tensor([float(group["lr"]), float(steps[0])], dtype=torch.float32, device=dev)
+                if gi in self._hyper:
+                    self._hyper[gi].copy_(vals)          # in place: a captured graph keeps reading this tensor
+                else:
+                    self._hyper[gi] = vals
 
     @torch.no_grad()
     def step(self, closure: Optional[Callable] = None):
@@ -146,9 +223,9 @@ class FusedAdam(Optimizer):
                 t = sts[0]["step"]
                 if any(st["step"] != t for st in sts):
                     raise RuntimeError("parameters of one group must share the step count")
-                tab = build_tables(fused, [p.grad for p in fused], [s["exp_avg"] for s in sts],
-                                   [s["exp_avg_sq"] for s in sts], lib.pnm_opt_chunk(), self._tables.setdefault(gi, {}))
-                e_ptr, b_ptr = tab.upload()
+                tab, rows = build_tables(fused, [p.grad for p in fused], [s["exp_avg"] for s in sts],
+                                         [s["exp_avg_sq"] for s in sts], lib.pnm_opt_chunk(), self._tables.setdefault(gi, {}))
+                e_ptr, b_ptr = tab.upload(rows)
                 hyper = None
                 if self.capturable:
                     hyper = self._hyper_of(gi, group, fused[0].device)
@@ -177,8 +254,8 @@ def grad_global_norm(params: Iterable[torch.Tensor]) -> torch.Tensor:
         lib = _lib.load(required=True)
         _declare(lib)
         cache = grad_global_norm.__dict__.setdefault("_cache", {})
-        tab = build_tables(ps, [p.grad for p in ps], [None] * len(ps), [None] * len(ps), lib.pnm_opt_chunk(), cache)
-        e_ptr, b_ptr = tab.upload()
+        tab, rows = build_tables(ps, [p.grad for p in ps], [None] * len(ps), [None] * len(ps), lib.pnm_opt_chunk(), cache)
+        e_ptr, b_ptr = tab.upload(rows)
         out = torch.zeros(1, device=ps[0].device, dtype=torch.float32)
         err = lib.pnm_grad_sqnorm_multi(e_ptr, b_ptr, tab.n_blocks, out.data_ptr(), torch.cuda.current_stream().cuda_stream)
         if err:

@@ -10,8 +10,10 @@ and ``checkpoint.{mp_rank}.{epoch}.pt`` with "next free / latest" index discover
 Models whose parameters are sharded (FSDP / DTensor / ShardTensor) are gathered to full
 tensors collectively and written by rank 0 as a topology-agnostic file; on load rank 0
 reads and the state is broadcast and re-sharded by ``load_state_dict`` of each rank.
+The optimizer's per-parameter state (Adam moments, ...) of sharded parameters is gathered
+the same way and re-distributed with the layout of the loading run's parameters.
 A training-state file that cannot be read (truncated write) makes ``load_checkpoint``
-fall back to the previous index.
+fall back to the previous index, and the model files of that same index are loaded.
 """
 from __future__ import annotations
 
@@ -133,6 +135,62 @@ def _full_state_dict(model: torch.nn.Module) -> dict:
     return out
 
 
+def _is_sharded_tensor(v) -> bool:
+    return isinstance(v, torch.Tensor) and hasattr(v, "full_tensor") and hasattr(v, "placements")
+
+
+def _optimizer_is_sharded(optimizer) -> bool:
+    if optimizer is None:
+        return False
+    return any(_is_sharded_tensor(p) for g in optimizer.param_groups for p in g["params"])
+
+
+def _full_optimizer_state(optimizer) -> dict:
+    """``optimizer.state_dict()`` with every sharded state tensor (the moments of DTensor / ShardTensor parameters)
+    gathered to a full CPU tensor — collective; the result does not depend on how the parameters were sharded
+    (reference: ``get_optimizer_state_dict(..., StateDictOptions(full_state_dict=True))``)."""
+    sd = optimizer.state_dict()
+    out_state = {}
+    for idx in sorted(sd["state"]):                       # same order on every rank: the gathers are collectives
+        out_state[idx] = {}
+        for k, v in sd["state"][idx].items():
+            if _is_sharded_tensor(v):
+                v = v.full_tensor()
+            out_state[idx][k] = v.detach().cpu() if isinstance(v, torch.Tensor) else v
+    return {"state": out_state, "param_groups": sd["param_groups"]}
+
+
+def _reshard_optimizer_state(optimizer, full: dict) -> dict:
+    """A full optimizer state dict laid out for THIS run's parameters: state tensors that have the global shape of a
+    sharded parameter are distributed with that parameter's mesh and placements (``set_optimizer_state_dict`` with
+    ``full_state_dict`` in the reference)."""
+    params = [p for g in optimizer.param_groups for p in g["params"]]
+    saved_ids = [i for g in full["param_groups"] for i in g["params"]]
+    state = {}
+    for pos, idx in enumerate(saved_ids):
+        if idx not in full["state"]:
+            continue
+        p = params[pos] if pos < len(params) else None
+        entry = {}
+        for k, v in full["state"][idx].items():
+            if p is not None and _is_sharded_tensor(p) and isinstance(v, torch.Tensor) and tuple(v.shape) == tuple(p.shape):
+                v = _distribute_like(v, p)
+            entry[k] = v
+        state[idx] = entry
+    return {"state": state, "param_groups": full["param_groups"]}
+
+
+def _distribute_like(full: torch.Tensor, like) -> torch.Tensor:
+    local_dev = like.to_local().device
+    if hasattr(like, "copy_full_"):                       # ShardTensor: same layout as the parameter
+        out = torch.zeros_like(like)
+        out.copy_full_(full.to(local_dev))
+        return out
+    from torch.distributed.tensor import distribute_tensor
+
+    return distribute_tensor(full.to(local_dev), like.device_mesh, like.placements)
+
+
 def save_checkpoint(path: Union[Path, str], models=None, optimizer=None, scheduler=None, scaler=None,
                     epoch: Optional[int] = None, metadata: Optional[Dict[str, Any]] = None,
                     optimizer_model: Optional[torch.nn.Module] = None) -> None:
@@ -144,7 +202,8 @@ def save_checkpoint(path: Union[Path, str], models=None, optimizer=None, schedul
     m = _manager()
     model_list = [] if models is None else (models if isinstance(models, list) else [models])
     named = _unique_model_names(model_list)
-    any_dist = any(_is_distributed_model(mod) for mod in named.values())
+    any_dist = any(_is_distributed_model(mod) for mod in named.values()) or _optimizer_is_sharded(optimizer) or (
+        optimizer_model is not None and _is_distributed_model(_unwrap(optimizer_model)))
     for name, model in named.items():
         is_pn = isinstance(model, Module)
         model_type = "mdlus" if is_pn else "pt"
@@ -167,7 +226,8 @@ def save_checkpoint(path: Union[Path, str], models=None, optimizer=None, schedul
         checkpoint_logging.info(f"Saved model state dictionary: {file_name}")
     state: Dict[str, Any] = {}
     if optimizer is not None:
-        state["optimizer_state_dict"] = optimizer.state_dict()
+        # sharded parameters: gather the moments (collective, every rank) so that rank 0's file holds all of them
+        state["optimizer_state_dict"] = _full_optimizer_state(optimizer) if any_dist else optimizer.state_dict()
     if scheduler is not None:
         state["scheduler_state_dict"] = scheduler.state_dict()
     if scaler is not None:
@@ -260,37 +320,43 @@ def load_checkpoint(path: Union[Path, str], models=None, optimizer=None, schedul
         return 0
     model_list = [] if models is None else (models if isinstance(models, list) else [models])
     named = _unique_model_names(model_list, loading=True)
-    any_dist = any(_is_distributed_model(mod) for mod in named.values())
-    for name, model in named.items():
-        model_type = "mdlus" if isinstance(model, Module) else "pt"
-        file_name = _get_checkpoint_filename(path, name, index=epoch, model_type=model_type,
-                                             distributed=_is_distributed_model(model))
-        if not fs.exists(file_name):
-            checkpoint_logging.error(f"Could not find valid model file {file_name}, skipping load")
-            continue
-        load_model_weights(model, file_name, device)
-        checkpoint_logging.info(f"Loaded model state dictionary {file_name} to device {device}")
-    # training state: newest readable index (falls back when the newest file is damaged)
+    any_dist = any(_is_distributed_model(mod) for mod in named.values()) or _optimizer_is_sharded(optimizer) or (
+        optimizer_model is not None and _is_distributed_model(_unwrap(optimizer_model)))
+    # training state first: newest readable index (falls back when the newest file is damaged); the model files are then
+    # taken from the SAME index, so that weights and optimizer state always belong to one step
     m = _manager()
     mp_rank = 0 if any_dist else (m.group_rank("model_parallel") if "model_parallel" in m.group_names else 0)
     resolved = str(Path(path).resolve()) if "://" not in path else path
     candidates = [epoch] if epoch is not None else list(reversed(_indices(resolved, "checkpoint", mp_rank, ".pt")))
-    state = None
+    state, used = None, epoch
     for idx in candidates:
         file_name = _get_checkpoint_filename(path, index=idx, model_type="pt", distributed=any_dist)
         if not fs.exists(file_name):
             continue
         try:
             state = _load_plain(file_name, device)
+            used = idx
             checkpoint_logging.info(f"Loaded checkpoint file {file_name} to device {device}")
             break
         except Exception as exc:  # noqa: BLE001 - damaged / partial file: try the previous index
             checkpoint_logging.warning(f"Checkpoint file {file_name} is unreadable ({exc}); trying an older one")
+    for name, model in named.items():
+        model_type = "mdlus" if isinstance(model, Module) else "pt"
+        file_name = _get_checkpoint_filename(path, name, index=used if state is not None else epoch, model_type=model_type,
+                                             distributed=_is_distributed_model(model))
+        if not fs.exists(file_name):
+            checkpoint_logging.error(f"Could not find valid model file {file_name}, skipping load")
+            continue
+        load_model_weights(model, file_name, device)
+        checkpoint_logging.info(f"Loaded model state dictionary {file_name} to device {device}")
     if state is None:
         checkpoint_logging.warning("Could not find valid checkpoint file, skipping load")
         return 0
     if optimizer is not None and "optimizer_state_dict" in state:
-        optimizer.load_state_dict(state["optimizer_state_dict"])
+        osd = state["optimizer_state_dict"]
+        if _optimizer_is_sharded(optimizer):
+            osd = _reshard_optimizer_state(optimizer, osd)
+        optimizer.load_state_dict(osd)
     if scheduler is not None and "scheduler_state_dict" in state:
         scheduler.load_state_dict(state["scheduler_state_dict"])
     if scaler is not None and "scaler_state_dict" in state:

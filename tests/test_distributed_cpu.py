@@ -263,3 +263,63 @@ def _partitioned_mgn(rank, world):
 
 def test_partitioned_meshgraphnet_three_ranks():
     run_ranks(_partitioned_mgn, world=3, timeout=240)
+
+
+def _sharded_optimizer_checkpoint(rank, world, tmp):
+    """Adam on DTensor-sharded parameters: save on two ranks (Shard(0)), reload with another layout (Shard(1)) and compare
+    the moments; the file is also read back by a single process afterwards."""
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+
+    from physicsnemo_b200.utils.checkpoint import load_checkpoint, save_checkpoint
+
+    mesh = init_device_mesh("cpu", (world,))
+
+    def build(dim):
+        torch.manual_seed(0)
+        lin = torch.nn.Linear(6, 4)
+        lin.weight = torch.nn.Parameter(distribute_tensor(lin.weight.detach(), mesh, [Shard(dim)]))
+        return lin
+
+    model = build(0)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-2)
+    torch.manual_seed(1)
+    for _ in range(3):
+        x = torch.randn(5, 6)
+        y = torch.nn.functional.linear(x, model.weight.full_tensor(), model.bias)
+        opt.zero_grad()
+        y.square().sum().backward()
+        opt.step()
+    want = {k: opt.state[model.weight][k].full_tensor().clone() for k in ("exp_avg", "exp_avg_sq")}
+    want_w = model.weight.full_tensor().clone()
+    save_checkpoint(tmp, models=model, optimizer=opt, epoch=3)
+    if rank == 0:
+        torch.save({"w": want_w, **want, "bias_avg": opt.state[model.bias]["exp_avg"].clone()}, tmp + "/expected.pt")
+    # other layout, same job
+    model2 = build(1)
+    with torch.no_grad():
+        model2.weight.mul_(0.0)
+    opt2 = torch.optim.Adam(model2.parameters(), lr=1e-2)
+    assert load_checkpoint(tmp, models=model2, optimizer=opt2) == 3
+    st = opt2.state[model2.weight]
+    assert st["exp_avg"].placements == model2.weight.placements          # re-sharded like the new parameter
+    for k in ("exp_avg", "exp_avg_sq"):
+        assert torch.allclose(st[k].full_tensor(), want[k])
+    assert torch.allclose(model2.weight.full_tensor(), want_w)
+    assert int(st["step"]) == 3
+
+
+def test_sharded_optimizer_state_checkpoint(tmp_path):
+    from physicsnemo_b200.utils.checkpoint import load_checkpoint
+
+    run_ranks(_sharded_optimizer_checkpoint, world=2, args=(str(tmp_path),))
+    # a single process (no sharding at all) resumes from the same files
+    exp = torch.load(str(tmp_path / "expected.pt"))
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(6, 4)
+    opt = torch.optim.Adam(lin.parameters(), lr=1e-2)
+    assert load_checkpoint(str(tmp_path), models=lin, optimizer=opt) == 3
+    assert torch.allclose(lin.weight, exp["w"])
+    assert torch.allclose(opt.state[lin.weight]["exp_avg"], exp["exp_avg"])
+    assert torch.allclose(opt.state[lin.weight]["exp_avg_sq"], exp["exp_avg_sq"])
+    assert torch.allclose(opt.state[lin.bias]["exp_avg"], exp["bias_avg"])

@@ -48,6 +48,31 @@ def test_checkpoint_round_trip(tmp_path, legacy):
     assert torch.equal(model(x), other(x))
 
 
+def test_checkpoint_fallback_keeps_model_and_state_on_one_index(tmp_path):
+    """A damaged newest training-state file makes load_checkpoint fall back one index; the model weights must then be
+    the ones of that same index, not the newest model file."""
+    import glob
+
+    from physicsnemo_b200.utils.checkpoint import load_checkpoint, save_checkpoint
+
+    lin = torch.nn.Linear(3, 2)
+    opt = torch.optim.SGD(lin.parameters(), lr=0.1, momentum=0.9)
+    weights = {}
+    for epoch in (1, 2):
+        lin(torch.randn(4, 3)).sum().backward()
+        opt.step()
+        weights[epoch] = lin.weight.detach().clone()
+        save_checkpoint(str(tmp_path), models=lin, optimizer=opt, epoch=epoch)
+    newest = glob.glob(str(tmp_path / "checkpoint.0.2.pt"))
+    assert len(newest) == 1
+    with open(newest[0], "wb") as f:
+        f.write(b"truncated")
+    other = torch.nn.Linear(3, 2)
+    opt2 = torch.optim.SGD(other.parameters(), lr=0.1, momentum=0.9)
+    assert load_checkpoint(str(tmp_path), models=other, optimizer=opt2) == 1
+    assert torch.equal(other.weight, weights[1])
+
+
 def test_nested_modules_and_overrides(tmp_path):
     class Inner(pn.Module):
         _overridable_args = {"scale"}
@@ -598,3 +623,30 @@ def test_modafno_forward_backward_and_key_scheme():
     plain = ModAFNO([16, 32], in_channels=3, out_channels=2, patch_size=[2, 2], embed_dim=32, mod_dim=16, depth=1, num_blocks=4,
                     modulate_filter=False, modulate_mlp=False)
     assert plain(torch.randn(1, 3, 16, 32), torch.rand(1, 16)).shape == (1, 2, 16, 32)
+
+
+def test_topodiff_layout_and_forward():
+    """Key scheme of the constraint-conditioned U-Net and of its encoder head; forward shapes; input checks."""
+    from physicsnemo_b200.models.topodiff import TopoDiff, UNetEncoder
+
+    torch.manual_seed(0)
+    net = TopoDiff(img_resolution=16, in_channels=4, out_channels=1, model_channels=32, channel_mult=[1, 2, 2], num_blocks=1,
+                   attn_resolutions=[8])
+    assert list(net.enc.keys()) == ["16x16_conv", "16x16_block0", "8x8_down", "8x8_block0", "4x4_down", "4x4_block0"]
+    assert list(net.dec.keys()) == ["4x4_in0", "4x4_in1", "4x4_block0", "4x4_block1", "8x8_up", "8x8_block0", "8x8_block1",
+                                    "16x16_up", "16x16_block0", "16x16_block1"]
+    assert net.dec["8x8_block0"].in_channels == 64 + 64 and net.dec["16x16_block1"].in_channels == 32 + 32
+    with torch.no_grad():
+        net.out_conv.weight.normal_(std=0.1)
+    x, cons, t = torch.randn(2, 1, 16, 16), torch.randn(2, 3, 16, 16), torch.tensor([1.0, 5.0])
+    y = net(x, cons, t)
+    assert y.shape == (2, 1, 16, 16) and torch.isfinite(y).all() and float(y.abs().max()) > 0
+    with pytest.raises(ValueError):
+        net(x, cons[:1], t)
+    with pytest.raises(ValueError):
+        net(x, cons, t[:1])
+    enc = UNetEncoder(in_channels=3, out_channels=2, model_channels=32, num_res_blocks=2, channel_mult=(1, 2),
+                      attention_resolutions=(2,), output_prob=True)
+    assert len(enc.encoder) == 4 and isinstance(enc.out[-1], torch.nn.Sigmoid)
+    p = enc(torch.randn(2, 3, 16, 16), t)
+    assert p.shape == (2, 2) and float(p.min()) >= 0 and float(p.max()) <= 1

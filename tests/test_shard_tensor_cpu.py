@@ -164,3 +164,40 @@ def _redistribute_and_scatter(rank, world):
 
 def test_redistribute_scatter_sync_three_ranks():
     run_ranks(_redistribute_and_scatter, world=3)
+
+
+def _sharded_preconditioner(rank, world):
+    """EDM preconditioner on a height-sharded activation: the per-sample coefficients are plain tensors, also when the
+    noise level arrives as a replicated ShardTensor, and the result matches the unsharded call."""
+    from physicsnemo_b200.core.module import Module
+    from physicsnemo_b200.diffusion.preconditioners import EDMPreconditioner
+    from physicsnemo_b200.distributed import DistributedManager
+    from physicsnemo_b200.parallel import Replicate, Shard, ShardTensor
+
+    mesh = DistributedManager().initialize_mesh((world,), ("domain",))
+
+    class Net(Module):
+        def __init__(self):
+            super().__init__()
+            self.conv = torch.nn.Conv2d(2, 2, 3, padding=1)
+
+        def forward(self, x, noise_labels):
+            return self.conv(x) * noise_labels.reshape(-1, 1, 1, 1).to(x.dtype)
+
+    torch.manual_seed(0)
+    net = EDMPreconditioner(Net(), sigma_data=[0.5, 0.8])
+    x = torch.randn(3, 2, 8, 6)
+    t = torch.tensor([0.3, 1.0, 4.0])
+    want = net(x, t)
+    rows = x.tensor_split(world, dim=2)[rank].clone()
+    xs = ShardTensor.from_local(rows, mesh, [Shard(2)])
+    for level in (t, ShardTensor.from_local(t.clone(), mesh, [Replicate()])):
+        got = net(xs, level)
+        assert isinstance(got, ShardTensor)
+        _check("preconditioned output", got.full_tensor(), want)
+    c = net._coefficients_for(xs, ShardTensor.from_local(t.clone(), mesh, [Replicate()]))
+    assert all(type(v) is torch.Tensor for v in c)
+
+
+def test_preconditioner_on_shard_tensor_two_ranks():
+    run_ranks(_sharded_preconditioner, world=2)
