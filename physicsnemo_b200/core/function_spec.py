@@ -145,6 +145,19 @@ class FunctionSpec:
         """Build the public function (adds a keyword-only ``implementation``)."""
 
         def _function(*args, **kwargs):
+            # sharded inputs: these functions are not torch functions, so ``__torch_function__`` never sees them; the
+            # domain-parallel layer registers its rules by name instead (``ShardTensor.register_named_function_handler``)
+            sharded = next((a for a in (*args, *kwargs.values()) if type(a).__name__ == "ShardTensor"), None)
+            if sharded is not None:
+                from ..parallel import patches  # noqa: F401  (registers the rules on first use)
+
+                registry = type(sharded)._named_function_registry
+                handler = registry.get(f"{cls.__module__}.{_function.__name__}") or registry.get(_function.__name__)
+                if handler is None:
+                    from ..parallel.shard_tensor import MissingShardPatch
+
+                    raise MissingShardPatch(f"no ShardTensor rule is registered for '{_function.__name__}'")
+                return handler(_function, (type(sharded),), args, kwargs)
             return cls.dispatch(*args, **kwargs)
 
         impls = cls._get_impls()

@@ -6,25 +6,25 @@ source, grid destination), aggregation onto the grid nodes, residual ``node_mlp`
 import torch.nn as nn
 from torch import Tensor
 
-from .mesh_graph_mlp import MeshGraphEdgeMLPConcat, MeshGraphEdgeMLPSum, MeshGraphMLP
-from .utils import aggregate
+from ._bipartite import BipartiteMessagePassing
 
 
-class MeshGraphDecoder(nn.Module):
+class MeshGraphDecoder(BipartiteMessagePassing):
+    """``grid ← grid + node_mlp(cat(Σ_edges edge_mlp(e, mesh_src, grid_dst), grid))``."""
+
     def __init__(self, aggregation: str = "sum", input_dim_src_nodes: int = 512, input_dim_dst_nodes: int = 512,
                  input_dim_edges: int = 512, output_dim_dst_nodes: int = 512, output_dim_edges: int = 512,
                  hidden_dim: int = 512, hidden_layers: int = 1, activation_fn: nn.Module = nn.SiLU(),
                  norm_type: str = "LayerNorm", do_concat_trick: bool = False, recompute_activation: bool = False):
         super().__init__()
         self.aggregation = aggregation
-        edge_cls = MeshGraphEdgeMLPSum if do_concat_trick else MeshGraphEdgeMLPConcat
-        kw = dict(hidden_dim=hidden_dim, hidden_layers=hidden_layers, activation_fn=activation_fn, norm_type=norm_type,
-                  recompute_activation=recompute_activation)
-        self.edge_mlp = edge_cls(efeat_dim=input_dim_edges, src_dim=input_dim_src_nodes, dst_dim=input_dim_dst_nodes,
-                                 output_dim=output_dim_edges, **kw)
-        self.node_mlp = MeshGraphMLP(input_dim=input_dim_dst_nodes + output_dim_edges, output_dim=output_dim_dst_nodes, **kw)
+        shared = {"norm_type": norm_type, "activation_fn": activation_fn, "hidden_layers": hidden_layers, "hidden_dim": hidden_dim,
+                  "recompute_activation": recompute_activation}
+        self._make_mlps(src_width=input_dim_src_nodes, dst_width=input_dim_dst_nodes, edge_width=input_dim_edges,
+                        edge_out=output_dim_edges, concat_trick=do_concat_trick, shared=shared)
+        self.node_mlp = self.node_mlp_for(output_dim_edges + input_dim_dst_nodes, output_dim_dst_nodes, shared)
 
     def forward(self, m2g_efeat: Tensor, grid_nfeat: Tensor, mesh_nfeat: Tensor, graph) -> Tensor:
-        efeat = self.edge_mlp(m2g_efeat, (mesh_nfeat, grid_nfeat), graph)
-        agg = aggregate(efeat, grid_nfeat.shape[0], graph, self.aggregation)
-        return self.node_mlp((agg, grid_nfeat), post=grid_nfeat)
+        incoming = self.messages_to_dst(m2g_efeat, mesh_nfeat, grid_nfeat, graph)
+        # two column blocks, no materialised concatenation; the residual is added by the MLP's last kernel
+        return self.node_mlp((incoming, grid_nfeat), post=grid_nfeat)

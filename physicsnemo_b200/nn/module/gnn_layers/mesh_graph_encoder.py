@@ -9,11 +9,13 @@ from typing import Tuple
 import torch.nn as nn
 from torch import Tensor
 
-from .mesh_graph_mlp import MeshGraphEdgeMLPConcat, MeshGraphEdgeMLPSum, MeshGraphMLP
-from .utils import aggregate
+from ._bipartite import BipartiteMessagePassing
 
 
-class MeshGraphEncoder(nn.Module):
+class MeshGraphEncoder(BipartiteMessagePassing):
+    """Returns ``(grid, mesh)``: the mesh nodes receive the aggregated grid → mesh messages, the grid nodes get their own
+    residual MLP."""
+
     def __init__(self, aggregation: str = "sum", input_dim_src_nodes: int = 512, input_dim_dst_nodes: int = 512,
                  input_dim_edges: int = 512, output_dim_src_nodes: int = 512, output_dim_dst_nodes: int = 512,
                  output_dim_edges: int = 512, hidden_dim: int = 512, hidden_layers: int = 1,
@@ -21,18 +23,15 @@ class MeshGraphEncoder(nn.Module):
                  recompute_activation: bool = False):
         super().__init__()
         self.aggregation = aggregation
-        edge_cls = MeshGraphEdgeMLPSum if do_concat_trick else MeshGraphEdgeMLPConcat
-        kw = dict(hidden_dim=hidden_dim, hidden_layers=hidden_layers, activation_fn=activation_fn, norm_type=norm_type,
-                  recompute_activation=recompute_activation)
-        self.edge_mlp = edge_cls(efeat_dim=input_dim_edges, src_dim=input_dim_src_nodes, dst_dim=input_dim_dst_nodes,
-                                 output_dim=output_dim_edges, **kw)
-        self.src_node_mlp = MeshGraphMLP(input_dim=input_dim_src_nodes, output_dim=output_dim_src_nodes, **kw)
-        self.dst_node_mlp = MeshGraphMLP(input_dim=input_dim_dst_nodes + output_dim_edges, output_dim=output_dim_dst_nodes, **kw)
+        shared = {"norm_type": norm_type, "activation_fn": activation_fn, "hidden_layers": hidden_layers, "hidden_dim": hidden_dim,
+                  "recompute_activation": recompute_activation}
+        self._make_mlps(src_width=input_dim_src_nodes, dst_width=input_dim_dst_nodes, edge_width=input_dim_edges,
+                        edge_out=output_dim_edges, concat_trick=do_concat_trick, shared=shared)
+        self.src_node_mlp = self.node_mlp_for(input_dim_src_nodes, output_dim_src_nodes, shared)
+        self.dst_node_mlp = self.node_mlp_for(output_dim_edges + input_dim_dst_nodes, output_dim_dst_nodes, shared)
 
     def forward(self, g2m_efeat: Tensor, grid_nfeat: Tensor, mesh_nfeat: Tensor, graph) -> Tuple[Tensor, Tensor]:
-        efeat = self.edge_mlp(g2m_efeat, (grid_nfeat, mesh_nfeat), graph)
-        agg = aggregate(efeat, mesh_nfeat.shape[0], graph, self.aggregation)
-        # the MLP takes the two column blocks without materialising their concatenation; residual added in its epilogue
-        mesh_out = self.dst_node_mlp((agg, mesh_nfeat), post=mesh_nfeat)
-        grid_out = self.src_node_mlp(grid_nfeat, post=grid_nfeat)
-        return grid_out, mesh_out
+        incoming = self.messages_to_dst(g2m_efeat, grid_nfeat, mesh_nfeat, graph)
+        mesh_new = self.dst_node_mlp((incoming, mesh_nfeat), post=mesh_nfeat)
+        grid_new = self.src_node_mlp(grid_nfeat, post=grid_nfeat)
+        return grid_new, mesh_new

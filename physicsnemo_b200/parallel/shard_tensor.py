@@ -52,7 +52,6 @@ _NO_TF = torch._C.DisableTorchFunctionSubclass
 
 
 class ShardTensor(torch.Tensor):
-    _local_tensor: torch.Tensor
     _spec: ShardTensorSpec
 
     _function_registry: Dict[Callable, Callable] = {}
@@ -68,9 +67,35 @@ class ShardTensor(torch.Tensor):
             r = torch.Tensor._make_wrapper_subclass(
                 cls, spec.global_shape, dtype=local_tensor.dtype, device=local_tensor.device,
                 layout=local_tensor.layout, requires_grad=False)
-        r._local_tensor = local_tensor
+        r._lt = local_tensor
+        r._pending = None        # CUDA event of a redistribution issued with async_op=True on a side stream
         r._spec = spec
         return r
+
+    @property
+    def _local_tensor(self) -> torch.Tensor:
+        """This rank's shard.  The first access after an asynchronous redistribution makes the current stream wait for
+        the side stream that produced it."""
+        ev = self._pending
+        if ev is not None:
+            torch.cuda.current_stream(self._lt.device).wait_event(ev)
+            self._lt.record_stream(torch.cuda.current_stream(self._lt.device))
+            self._pending = None
+        return self._lt
+
+    @_local_tensor.setter
+    def _local_tensor(self, value: torch.Tensor) -> None:
+        self._lt = value
+        self._pending = None
+
+    # -------------------------------------------------------- traceable wrapper-subclass protocol
+    def __tensor_flatten__(self):
+        """Inner tensors and the rest of the state (``torch.compile`` / AOT autograd wrapper-subclass protocol)."""
+        return ["_local_tensor"], (self._spec,)
+
+    @staticmethod
+    def __tensor_unflatten__(inner_tensors, meta, outer_size=None, outer_stride=None):
+        return ShardTensor(inner_tensors["_local_tensor"], meta[0])
 
     def __init__(self, *args, **kwargs):
         pass
@@ -175,8 +200,50 @@ class ShardTensor(torch.Tensor):
         spec = infer_spec_from_local(local_tensor, device_mesh, placements, sharding_shapes, global_shape)
         return ShardTensor(local_tensor, spec)
 
+    @staticmethod
+    def from_dtensor(dtensor) -> "ShardTensor":
+        """A ``torch.distributed.tensor.DTensor`` as a ShardTensor (no copy, no communication): DTensor shards are the
+        ``torch.chunk`` pieces of the global tensor, which is the ``"chunk"`` rule of ``from_local``.  ``Partial``
+        placements carry over.  Reference: ``ShardTensor.from_dtensor`` (``domain_parallel/shard_tensor.py:957-1005``)."""
+        local = dtensor.to_local()
+        return ShardTensor.from_local(local, dtensor.device_mesh, tuple(dtensor.placements), sharding_shapes="chunk",
+                                      global_shape=tuple(dtensor.shape))
+
+    def to_dtensor(self):
+        """The same data as a DTensor; only for shardings a DTensor can express (``torch.chunk`` pieces)."""
+        from torch.distributed.tensor import DTensor
+
+        mesh, spec = self._spec.mesh, self._spec
+        for md, p in enumerate(spec.placements):
+            if isinstance(p, Shard):
+                n = mesh.size(md)
+                full = spec.global_shape[p.dim]
+                even = [len(c) for c in torch.arange(full).chunk(n)] + [0] * n
+                have = [int(v) for v in spec.sharding_sizes[md]]
+                if have != even[:n]:
+                    raise ValueError("uneven shards that are not torch.chunk pieces have no DTensor equivalent; redistribute first")
+        return DTensor.from_local(self._local_tensor, mesh, tuple(spec.placements), run_check=False,
+                                  shape=torch.Size(spec.global_shape), stride=torch.empty(spec.global_shape, device="meta").stride())
+
     def to_local(self, grad_placements=None) -> torch.Tensor:
-        return self._local_tensor
+        """This rank's shard (it carries the autograd graph itself).  ``grad_placements`` states how the gradient that
+        later flows into the returned tensor is laid out over the mesh: ``Partial`` on a mesh dimension where this tensor
+        is replicated means every rank will hold only a share of the gradient, so the shares are summed over that mesh
+        dimension on the way back (reference: ``to_local(grad_placements=...)``, ``shard_tensor.py:1331``)."""
+        local = self._local_tensor
+        if grad_placements is None:
+            return local
+        from . import collectives as C
+
+        grad_placements = tuple(grad_placements)
+        if len(grad_placements) != self._spec.mesh.ndim:
+            raise ValueError(f"grad_placements needs one entry per mesh dimension ({self._spec.mesh.ndim})")
+        for md, (own, g) in enumerate(zip(self._spec.placements, grad_placements)):
+            if isinstance(g, Partial) and isinstance(own, Replicate):
+                local = C.GradAllReduce.apply(local, self._spec.mesh.get_group(md))
+            elif type(g) is not type(own) or (isinstance(g, Shard) and g.dim != own.dim):
+                raise NotImplementedError(f"gradient layout {g} for a tensor placed as {own} on mesh dimension {md}")
+        return local
 
     def full_tensor(self, grad_placements=None) -> torch.Tensor:
         """The global tensor on every rank (resolves Partial, gathers shards)."""
@@ -190,7 +257,21 @@ class ShardTensor(torch.Tensor):
             raise NotImplementedError("redistribution across different meshes is not supported")
         if placements is None:
             raise ValueError("placements are required")
-        return redistribute_shard_tensor(self, tuple(placements))
+        local = self._local_tensor
+        if not (async_op and local.is_cuda):
+            return redistribute_shard_tensor(self, tuple(placements))
+        # asynchronous: the collectives run on a side stream; the result waits for them at its first use
+        cur = torch.cuda.current_stream(local.device)
+        side = _side_stream(local.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            out = redistribute_shard_tensor(self, tuple(placements))
+            ev = torch.cuda.Event()
+            ev.record(side)
+        local.record_stream(side)
+        if out is not self:
+            out._pending = ev
+        return out
 
     def backward(self, gradient=None, retain_graph=None, create_graph=False, inputs=None):
         """Backward from this tensor.  A Partial tensor stands for the sum of the ranks' values,
@@ -241,6 +322,17 @@ class ShardTensor(torch.Tensor):
             f"aten op {func} reached ShardTensor dispatch without a handler; the calling torch function "
             "needs a ShardTensor rule (register one with ShardTensor.register_function_handler)"
         )
+
+
+_side_streams: Dict[int, "torch.cuda.Stream"] = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    st = _side_streams.get(key)
+    if st is None:
+        st = _side_streams[key] = torch.cuda.Stream(device=device)
+    return st
 
 
 def scatter_tensor(tensor: Optional[torch.Tensor], global_src: int, mesh: DeviceMesh, placements: Sequence,

@@ -1,0 +1,114 @@
+"""Child process of the checkpoint cross-load test: the reference package (with its optional third-party imports stubbed)
+and this package build the same five models, exchange ``.mdlus`` files in both directions and compare outputs."""
+import os
+import sys
+import tempfile
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+
+def _cases(ref, mine):
+    torch.manual_seed(0)
+    yield ("FNO", ref.models.fno.FNO, mine.models.fno.FNO,
+           dict(in_channels=2, out_channels=1, dimension=2, latent_channels=8, num_fno_layers=2, num_fno_modes=3, padding=2,
+                decoder_layer_size=8),
+           lambda: (torch.randn(2, 2, 12, 12),), {})
+    yield ("AFNO", ref.models.afno.AFNO, mine.models.afno.AFNO,
+           dict(inp_shape=[16, 24], in_channels=3, out_channels=2, patch_size=[4, 4], embed_dim=32, depth=2, num_blocks=4),
+           lambda: (torch.randn(2, 3, 16, 24),), {})
+    yield ("Transolver", ref.models.transolver.Transolver, mine.models.transolver.Transolver,
+           dict(functional_dim=3, out_dim=2, embedding_dim=3, n_layers=2, n_hidden=32, n_head=4, slice_num=8, mlp_ratio=2,
+                unified_pos=False, structured_shape=None, use_te=False, time_input=False),
+           lambda: (torch.randn(1, 50, 3),), {"embedding": lambda: torch.randn(1, 50, 3)})
+    yield ("SongUNet", ref.models.diffusion_unets.SongUNet, mine.models.diffusion_unets.SongUNet,
+           dict(img_resolution=16, in_channels=3, out_channels=2, model_channels=16, channel_mult=[1, 2], num_blocks=1,
+                attn_resolutions=[8]),
+           lambda: (torch.randn(2, 3, 16, 16), torch.tensor([0.5, 2.0]), None), {})
+
+
+def main() -> int:
+    from baseline.ref_runner import import_reference
+
+    ref = import_reference(os.path.join(ROOT, "baseline", "_ref"))
+    import importlib
+
+    for sub in ("models.fno", "models.afno", "models.transolver", "models.diffusion_unets"):
+        importlib.import_module("physicsnemo." + sub)
+    import physicsnemo_b200 as mine
+    import physicsnemo_b200.models.afno, physicsnemo_b200.models.diffusion_unets, physicsnemo_b200.models.fno  # noqa: E401,F401
+    import physicsnemo_b200.models.transolver  # noqa: F401
+
+    failures = []
+    with tempfile.TemporaryDirectory() as tmp:
+        for name, ref_cls, my_cls, cfg, make_args, make_kwargs in _cases(ref, mine):
+            torch.manual_seed(1)
+            a = ref_cls(**cfg).eval()
+            torch.manual_seed(2)
+            b = my_cls(**cfg).eval()
+            with torch.no_grad():                       # zero-initialised output layers would hide differences
+                for p in a.parameters():
+                    if float(p.abs().max()) == 0:
+                        p.normal_(std=0.05)
+            keys_a, keys_b = list(a.state_dict().keys()), list(b.state_dict().keys())
+            if sorted(keys_a) != sorted(keys_b):
+                failures.append(f"{name}: state-dict keys differ: {sorted(set(keys_a) ^ set(keys_b))[:6]}")
+                continue
+            args = make_args()
+            kwargs = {k: v() for k, v in make_kwargs.items()}
+            # reference -> this package
+            fa = os.path.join(tmp, f"{name}_ref.mdlus")
+            a.save(fa)
+            b.load(fa)
+            with torch.no_grad():
+                ya, yb = a(*args, **kwargs), b(*args, **kwargs)
+            err = float((ya - yb).abs().max()) / max(float(ya.abs().max()), 1e-12)
+            if not err < 2e-5:
+                failures.append(f"{name}: outputs differ after loading the reference's file here: {err:.2e}")
+            # this package -> reference
+            with torch.no_grad():
+                for p in b.parameters():
+                    p.add_(torch.randn_like(p) * 0.01)
+            fb = os.path.join(tmp, f"{name}_own.mdlus")
+            b.save(fb)
+            a.load(fb)
+            with torch.no_grad():
+                ya, yb = a(*args, **kwargs), b(*args, **kwargs)
+            err = float((ya - yb).abs().max()) / max(float(yb.abs().max()), 1e-12)
+            if not err < 2e-5:
+                failures.append(f"{name}: outputs differ after loading this package's file in the reference: {err:.2e}")
+            print(f"{name}: ok ({len(keys_a)} tensors)", flush=True)
+        # MeshGraphNet: the reference's forward needs torch_geometric (absent here), so the exchange is checked on tensors
+        try:
+            importlib.import_module("physicsnemo.models.meshgraphnet")
+            import physicsnemo_b200.models.meshgraphnet  # noqa: F401
+
+            cfg = dict(input_dim_nodes=4, input_dim_edges=3, output_dim=2, processor_size=2, hidden_dim_processor=16,
+                       hidden_dim_node_encoder=16, hidden_dim_edge_encoder=16, hidden_dim_node_decoder=16)
+            a = ref.models.meshgraphnet.MeshGraphNet(**cfg)
+            b = mine.models.meshgraphnet.MeshGraphNet(**cfg)
+            fa, fb = os.path.join(tmp, "mgn_ref.mdlus"), os.path.join(tmp, "mgn_own.mdlus")
+            a.save(fa)
+            b.load(fa)
+            same = all(torch.equal(v, b.state_dict()[k]) for k, v in a.state_dict().items())
+            with torch.no_grad():
+                for p in b.parameters():
+                    p.add_(0.01)
+            b.save(fb)
+            a.load(fb)
+            same = same and all(torch.equal(v, a.state_dict()[k]) for k, v in b.state_dict().items())
+            if not same or sorted(a.state_dict()) != sorted(b.state_dict()):
+                failures.append("MeshGraphNet: tensors differ after the exchange")
+            else:
+                print(f"MeshGraphNet: ok ({len(a.state_dict())} tensors, state exchange only)", flush=True)
+        except Exception as exc:  # noqa: BLE001
+            failures.append(f"MeshGraphNet: {type(exc).__name__}: {exc}")
+    for f in failures:
+        print("FAIL", f, flush=True)
+    return 1 if failures else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

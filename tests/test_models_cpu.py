@@ -650,3 +650,20 @@ def test_topodiff_layout_and_forward():
     assert len(enc.encoder) == 4 and isinstance(enc.out[-1], torch.nn.Sigmoid)
     p = enc(torch.randn(2, 3, 16, 16), t)
     assert p.shape == (2, 2) and float(p.min()) >= 0 and float(p.max()) <= 1
+
+
+def test_mdlus_files_cross_load_with_the_reference():
+    """FNO, AFNO, Transolver, SongUNet (outputs) and MeshGraphNet (tensors): ``.mdlus`` files written by the reference load
+    here and the other way round.  Runs in a child process; skipped when the reference is not installed beside the repo."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if not os.path.isdir(os.path.join(root, "baseline", "_ref", "physicsnemo")):
+        pytest.skip("the reference package is not installed under baseline/_ref")
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    proc = subprocess.run([sys.executable, os.path.join(root, "tests", "helpers", "crossload_worker.py")], capture_output=True,
+                          text=True, timeout=900, env=env)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert proc.stdout.count(": ok") == 5, proc.stdout

@@ -201,3 +201,146 @@ def _sharded_preconditioner(rank, world):
 
 def test_preconditioner_on_shard_tensor_two_ranks():
     run_ranks(_sharded_preconditioner, world=2)
+
+
+def _shard_tensor_api(rank, world):
+    """DTensor bridge, gradient layouts of ``to_local``, the async flag of ``redistribute`` and the flatten protocol."""
+    from torch.distributed.tensor import DTensor, Partial, Replicate, Shard, distribute_tensor
+
+    from physicsnemo_b200.distributed import DistributedManager
+    from physicsnemo_b200.parallel import ShardTensor
+
+    mesh = DistributedManager().initialize_mesh((world,), ("domain",))
+    torch.manual_seed(0)
+    full = torch.randn(7, 5)
+    # DTensor -> ShardTensor -> DTensor, uneven chunks included (7 rows over the ranks)
+    dt = distribute_tensor(full, mesh, [Shard(0)])
+    st = ShardTensor.from_dtensor(dt)
+    assert isinstance(st, ShardTensor) and tuple(st.shape) == (7, 5)
+    assert torch.equal(st.to_local(), dt.to_local()) and torch.equal(st.full_tensor(), full)
+    back = st.to_dtensor()
+    assert isinstance(back, DTensor) and torch.equal(back.full_tensor(), full)
+    rep = ShardTensor.from_dtensor(distribute_tensor(full, mesh, [Replicate()]))
+    assert rep._spec.is_replicated()
+    # to_local(grad_placements=[Partial()]) on a replicated tensor: the ranks' gradient shares are summed
+    leaf = full.clone().requires_grad_(True)
+    r = ShardTensor.from_local(leaf, mesh, [Replicate()])
+    loc = r.to_local(grad_placements=[Partial()])
+    (loc * float(rank + 1)).sum().backward()
+    want = float(sum(range(1, world + 1)))
+    assert torch.allclose(leaf.grad, torch.full_like(full, want))
+    leaf2 = full.clone().requires_grad_(True)
+    ShardTensor.from_local(leaf2, mesh, [Replicate()]).to_local().sum().backward()          # default: no reduction
+    assert torch.allclose(leaf2.grad, torch.ones_like(full))
+    # redistribute(async_op=True) gives the same values (on CPU it completes synchronously)
+    g = st.redistribute(placements=[Replicate()], async_op=True)
+    assert torch.equal(g.to_local(), full)
+    # wrapper-subclass protocol used by tracing
+    names, meta = st.__tensor_flatten__()
+    again = ShardTensor.__tensor_unflatten__({n: getattr(st, n) for n in names}, meta, tuple(st.shape), None)
+    assert torch.equal(again.to_local(), st.to_local()) and again._spec is st._spec
+
+
+def test_shard_tensor_api_three_ranks():
+    run_ranks(_shard_tensor_api, world=3)
+
+
+def _ring_neighbor_search(rank, world):
+    """kNN and capped radius search with points and queries sharded (uneven shards) against the single-process result."""
+    from physicsnemo_b200.distributed import DistributedManager
+    from physicsnemo_b200.nn.functional.neighbors.knn import knn
+    from physicsnemo_b200.nn.functional.neighbors.radius_search import radius_search
+    from physicsnemo_b200.parallel import Replicate, Shard, ShardTensor
+
+    mesh = DistributedManager().initialize_mesh((world,), ("domain",))
+    torch.manual_seed(0)
+    pts, qry = torch.rand(101, 3), torch.rand(37, 3)
+    p_loc = pts.tensor_split(world)[rank].clone()
+    q_loc = qry.tensor_split(world)[rank].clone().requires_grad_(True)
+    ps = ShardTensor.from_local(p_loc, mesh, [Shard(0)])
+    qs = ShardTensor.from_local(q_loc, mesh, [Shard(0)])
+    want_i, want_d = knn(pts, qry, 5)
+    got_i, got_d = knn(ps, qs, 5)
+    assert isinstance(got_i, ShardTensor) and torch.equal(got_i.full_tensor(), want_i)
+    _check("knn distances", got_d.full_tensor().detach(), want_d)
+    got_d.to_local().sum().backward()                     # distances are differentiable in the queries
+    assert q_loc.grad is not None and torch.isfinite(q_loc.grad).all()
+    # sharded points, replicated queries
+    ri, rd = knn(ps, ShardTensor.from_local(qry.clone(), mesh, [Replicate()]), 4)
+    wi, wd = knn(pts, qry, 4)
+    assert torch.equal(ri.to_local(), wi)
+    # replicated points, sharded queries: purely local
+    li, _ = knn(ShardTensor.from_local(pts.clone(), mesh, [Replicate()]), qs, 3)
+    assert torch.equal(li.full_tensor(), knn(pts, qry, 3)[0])
+    # ball query, at most 6 neighbours per query: same neighbour sets and distances
+    want = radius_search(pts, qry, 0.25, 6, True, True)
+    got = radius_search(ps, qs, 0.25, 6, True, True)
+    gi, gp, gd = (t.full_tensor() for t in got)
+    wd_sorted, _ = torch.sort(torch.where(want[2] > 0, want[2], torch.full_like(want[2], 9.0)), dim=1)
+    gd_sorted, _ = torch.sort(torch.where(gd > 0, gd, torch.full_like(gd, 9.0)), dim=1)
+    _check("ball query distances", gd_sorted.detach(), wd_sorted)
+    found = gd > 0
+    assert torch.allclose(gp[found], pts[gi[found]])
+
+
+def test_ring_knn_and_ball_query_three_ranks():
+    run_ranks(_ring_neighbor_search, world=3)
+
+
+def _sharded_sdf(rank, world):
+    from physicsnemo_b200.distributed import DistributedManager
+    from physicsnemo_b200.nn.functional.geometry.sdf import signed_distance_field
+    from physicsnemo_b200.parallel import Shard, ShardTensor
+
+    mesh = DistributedManager().initialize_mesh((world,), ("domain",))
+    verts = torch.tensor([[0.0, 0, 0], [1, 0, 0], [0, 1, 0], [0, 0, 1]])
+    faces = torch.tensor([[0, 2, 1], [0, 1, 3], [0, 3, 2], [1, 2, 3]], dtype=torch.int32)
+    torch.manual_seed(0)
+    pts = torch.rand(23, 3) * 1.5 - 0.25
+    want = signed_distance_field(verts, faces, pts)
+    loc = pts.tensor_split(world)[rank].clone()
+    got = signed_distance_field(ShardTensor.from_local(verts.tensor_split(world)[rank].clone(), mesh, [Shard(0)]),
+                                ShardTensor.from_local(faces.tensor_split(world)[rank].clone(), mesh, [Shard(0)]),
+                                ShardTensor.from_local(loc, mesh, [Shard(0)]))
+    want = want if isinstance(want, tuple) else (want,)
+    got = got if isinstance(got, tuple) else (got,)
+    for w, g in zip(want, got):
+        assert isinstance(g, ShardTensor)
+        _check("sdf output", g.full_tensor().float(), w.float())
+
+
+def test_sharded_sdf_two_ranks():
+    run_ranks(_sharded_sdf, world=2)
+
+
+def _fsdp2_with_domain_parallel(rank, world):
+    """2-D mesh: FSDP2 (``fully_shard``) shards the parameters over "dp" and splits the batch, ShardTensor splits the
+    image height over "domain".  Forward and parameter gradients match the single-process model on the whole batch."""
+    from torch.distributed.fsdp import fully_shard
+
+    from physicsnemo_b200.distributed import DistributedManager
+    from physicsnemo_b200.parallel import Shard, ShardTensor
+
+    mesh = DistributedManager().initialize_mesh((2, 2), ("dp", "domain"))
+    dp, dom = mesh["dp"], mesh["domain"]
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.GroupNorm(2, 8), torch.nn.SiLU(),
+                              torch.nn.Conv2d(8, 4, 3, padding=1))
+    ref = copy.deepcopy(net)
+    fully_shard(net, mesh=dp)
+    x = torch.randn(4, 3, 8, 6)
+    dp_r, dom_r = dp.get_local_rank(), dom.get_local_rank()
+    rows = x.tensor_split(2, dim=0)[dp_r].tensor_split(2, dim=2)[dom_r].clone()
+    y = net(ShardTensor.from_local(rows, dom, [Shard(2)]))
+    assert isinstance(y, ShardTensor)
+    y.float().square().mean().backward()
+    yr = ref(x)
+    yr.square().mean().backward()
+    _check("forward", y.full_tensor().detach(), yr.tensor_split(2, dim=0)[dp_r].detach(), 1e-5)
+    for (name, p), (_, q) in zip(net.named_parameters(), ref.named_parameters()):
+        assert hasattr(p.grad, "full_tensor"), name                  # FSDP2 keeps parameters and gradients as DTensors
+        _check(f"grad {name}", p.grad.full_tensor(), q.grad, 1e-4)
+
+
+def test_fsdp2_coexists_with_shard_tensor_four_ranks():
+    run_ranks(_fsdp2_with_domain_parallel, world=4)
