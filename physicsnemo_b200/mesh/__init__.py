@@ -9,3 +9,5 @@ __all__ = ["Mesh", "DomainMesh", "Adjacency", "MeshFieldAssociation", "MESH_FIEL
            "operations", "spatial", "io"]
 from . import generate, repair, tessellation  # noqa: E402,F401
 from .generate import marching_cubes  # noqa: E402,F401
+from . import calculus, subdivision  # noqa: E402,F401
+from .subdivision import subdivide_linear, subdivide_loop  # noqa: E402,F401

@@ -381,3 +381,116 @@ def test_cae_dataset_layouts_and_readahead(tmp_path, layout):
         CAEDataset(tmp_path, ["not_there"], None, torch.device("cpu"))[0]
     with pytest.raises(FileNotFoundError):
         CAEDataset(tmp_path / "missing", keys, None, torch.device("cpu"))
+
+
+def _surface_sample(rng, n):
+    import numpy as np
+
+    pos = rng.random((n, 3)).astype(np.float32)
+    cells = np.array([[i, (i + 1) % n, (i + 2) % n] for i in range(n)])
+    return dict(pos=pos, cells=cells, p=rng.random((n, 1)), wallShearStress=rng.random((n, 3)), velocity=30.0 + n,
+                reynolds_number=1e6 + n, length=1000.0 + n, width=300.0, height=280.0 + n, ground_clearance=50.0 + n, slant_angle=25.0 + n,
+                fillet_radius=10.0 + n)
+
+
+def test_static_graph_datasets(tmp_path):
+    import numpy as np
+
+    from physicsnemo_b200.datapipes.gnn import AhmedBodyDataset, DrivAerNetDataset, StokesDataset
+
+    rng = np.random.default_rng(0)
+    train = AhmedBodyDataset(samples=[_surface_sample(rng, 20), _surface_sample(rng, 24)], stats_dir=tmp_path, compute_drag=True)
+    g, case, normals, areas, coeff = train[1]
+    assert g.x.shape == (24, 11) and g.y.shape == (24, 4) and g.edge_attr.shape[1] == 4
+    assert float(g.y.min()) >= -1 - 1e-6 and float(g.y.max()) <= 1 + 1e-6               # min-max bounds
+    assert normals.shape == (24, 3) and areas.shape == (24,) and coeff > 0
+    pred, gt = train.denormalize(g.y, g.y)
+    raw = torch.cat([train._raw_nodes[1]["p"], train._raw_nodes[1]["wallShearStress"]], 1)
+    assert torch.allclose(pred, raw, atol=1e-5)
+    valid = AhmedBodyDataset(samples=[_surface_sample(rng, 20)], split="validation", stats_dir=tmp_path)      # reuses the statistics
+    assert valid[0].x.shape == (20, 11)
+    with pytest.raises(IOError):
+        AhmedBodyDataset(samples=[_surface_sample(rng, 20)], split="test", stats_dir=tmp_path / "nowhere")
+    car = DrivAerNetDataset(samples=[dict(_surface_sample(rng, 16), c_d=0.31)])
+    assert car[0].x.shape == (16, 3) and abs(float(car[0].c_d) - 0.31) < 1e-6
+    flow = StokesDataset(samples=[dict(pos=rng.random((15, 2)), cells=np.array([[i, (i + 1) % 15, (i + 2) % 15] for i in range(15)]),
+                                       marker=rng.integers(0, 5, 15), u=rng.random(15), v=rng.random(15), p=rng.random(15))])
+    assert flow[0].x.shape == (15, 2 + 5) and flow[0].y.shape == (15, 3)
+
+
+def test_lagrangian_and_hydrograph_datasets(tmp_path):
+    import numpy as np
+
+    from physicsnemo_b200.datapipes.gnn import HydroGraphDataset, LagrangianDataset
+
+    rng = np.random.default_rng(1)
+    meta = dict(dim=2, sequence_length=11, dt=0.0025, default_connectivity_radius=0.15, bounds=[[0.1, 0.9], [0.1, 0.9]],
+                vel_mean=[0, 0], vel_std=[0.01, 0.01], acc_mean=[0, 0], acc_std=[0.001, 0.001])
+    traj = [dict(position=(0.5 + 0.3 * rng.random((12, 30, 2))).astype(np.float32), particle_type=np.array([5] * 25 + [3] * 5))
+            for _ in range(2)]
+    ds = LagrangianDataset(trajectories=traj, metadata=meta, num_history=5, split="valid")
+    assert len(ds) == 2 * (12 - 5 - 1)
+    g = ds[3]
+    assert g.x.shape == (30, 2 + 5 * 2 + 4 + 6) and g.y.shape == (30, 6) and g.edge_attr.shape[1] == 3
+    pos, vel, kinds = ds.unpack_inputs(g)
+    assert vel.shape == (5, 30, 2) and torch.equal(kinds.argmax(1), torch.tensor([5] * 25 + [3] * 5))
+    seq = traj[0]["position"]
+    want_v = (torch.as_tensor(seq[8] - seq[7]) - ds.vel_mean) / ds.vel_std               # sample 3: t = 8 is the current step
+    assert torch.allclose(vel[-1], want_v, atol=1e-5) and torch.allclose(pos, torch.as_tensor(seq[8]))
+    assert int(g.mask.sum()) == 25
+    # hydrographs
+    n, T = 40, 16
+    static = dict(xy_coords=rng.random((n, 2)), **{k: rng.random(n) for k in
+                                                   ("area", "elevation", "slope", "aspect", "curvature", "manning", "flow_accum", "infiltration")})
+    events = [dict(water_depth=rng.random((T, n)), volume=rng.random((T, n)), precipitation=rng.random(T), inflow_hydrograph=rng.random(T))
+              for _ in range(3)]
+    tr = HydroGraphDataset(static=static, hydrographs=events, n_time_steps=4, k=3, stats_dir=tmp_path, return_physics=True)
+    assert len(tr) == 3 * (T - 4)
+    g, phys = tr[5]
+    assert g.x.shape == (n, 2 + 8 + 2 + 4 + 4) and g.y.shape == (n, 2) and g.edge_attr.shape[1] == 3
+    assert set(phys) >= {"flow_future", "precip_future", "past_volume", "future_volume"}
+    te = HydroGraphDataset(static=static, hydrographs=events[:1], n_time_steps=4, k=3, stats_dir=tmp_path, split="test", rollout_length=6)
+    g, roll = te[0]
+    assert roll["water_depth"].shape == (6, n) and g.x.shape[0] == n
+
+
+def test_bistride_multilayer_graph(tmp_path):
+    from physicsnemo_b200.datapipes.gnn import BistrideMultiLayerGraph, BistrideMultiLayerGraphDataset, cells_to_edges
+    from physicsnemo_b200.nn.module.gnn_layers.graph_types import Graph
+
+    n = 9
+    xs = torch.linspace(0, 1, n)
+    X, Y = torch.meshgrid(xs, xs, indexing="ij")
+    pos = torch.stack([X.reshape(-1), Y.reshape(-1)], 1)
+    cells = []
+    for i in range(n - 1):
+        for j in range(n - 1):
+            a, b, c, d = i * n + j, (i + 1) * n + j, (i + 1) * n + j + 1, i * n + j + 1
+            cells += [[a, b, c], [a, c, d]]
+    g = Graph(cells_to_edges(torch.tensor(cells)), num_nodes=n * n, pos=pos)
+    ms = BistrideMultiLayerGraph(g, 2)
+    sizes = [n * n] + [ids.numel() for ids in ms.m_ids]
+    assert sizes[1] < 0.7 * sizes[0] and sizes[2] < 0.7 * sizes[1] and sizes[2] >= 4
+    for level, (edges, count) in enumerate(zip(ms.m_flat_es[1:], sizes[1:])):
+        assert int(edges.max()) < count and (edges[0] != edges[1]).all()
+    # every node that was dropped has a surviving neighbour one hop away (the strides alternate)
+    kept = torch.zeros(n * n, dtype=torch.bool)
+    kept[ms.m_ids[0]] = True
+    e0 = ms.m_flat_es[0]
+    covered = kept.clone()
+    covered[e0[0][kept[e0[1]]]] = True
+    assert bool(covered.all())
+
+    class One(torch.utils.data.Dataset):
+        split = "train"
+
+        def __len__(self):
+            return 1
+
+        def __getitem__(self, i):
+            return g
+
+    wrapped = BistrideMultiLayerGraphDataset(One(), 2, cache_dir=tmp_path)
+    first, again = wrapped[0], wrapped[0]
+    assert len(first["ms_edges"]) == 3 and len(first["ms_ids"]) == 2
+    assert all(torch.equal(a, b) for a, b in zip(first["ms_ids"], again["ms_ids"]))

@@ -200,3 +200,61 @@ def test_tessellation_polygons_and_delaunay():
     assert d.n_cells > 40 and float(d.cell_areas.min()) > 0
     filled = fill_interior(L, [[0, 1, 2, 3, 4, 5]], spacing=0.25)
     assert float(filled.cell_areas.sum()) == pytest.approx(3.0, rel=1e-6) and filled.n_points > 20
+
+
+def _grid_mesh(n=6):
+    from physicsnemo_b200.mesh.mesh import Mesh
+
+    xs = torch.linspace(0, 1, n)
+    X, Y = torch.meshgrid(xs, xs, indexing="ij")
+    pts = torch.stack([X.reshape(-1), Y.reshape(-1)], 1)
+    cells = []
+    for i in range(n - 1):
+        for j in range(n - 1):
+            a, b, c, d = i * n + j, (i + 1) * n + j, (i + 1) * n + j + 1, i * n + j + 1
+            cells += [[a, b, c], [a, c, d]]
+    return Mesh(pts, torch.tensor(cells))
+
+
+def test_mesh_calculus_is_exact_for_linear_fields():
+    from physicsnemo_b200.mesh import calculus as K
+
+    m = _grid_mesh()
+    p = m.points
+    g = K.gradient(m, 2 * p[:, 0] + 3 * p[:, 1])
+    assert torch.allclose(g, torch.tensor([2.0, 3.0]).expand_as(g), atol=1e-5)
+    assert torch.allclose(K.divergence(m, p), torch.full((m.n_points,), 2.0), atol=1e-5)
+    assert torch.allclose(K.curl(m, torch.stack([-p[:, 1], p[:, 0]], 1)), torch.full((m.n_points,), 2.0), atol=1e-5)
+    assert abs(float(K.integrate(m, torch.ones(m.n_points))) - 1.0) < 1e-6
+    assert abs(float(K.integrate(m, p[:, 0])) - 0.5) < 1e-5                      # ∫ x over the unit square
+    # a surface in 3-D: the gradient of z on a tilted plane lies in the plane
+    from physicsnemo_b200.mesh.mesh import Mesh
+
+    tilt = torch.stack([p[:, 0], p[:, 1], 0.5 * p[:, 0]], 1)
+    s = Mesh(tilt, m.cells)
+    gz = K.gradient(s, tilt[:, 2], at="cells")
+    normal = torch.tensor([-0.5, 0.0, 1.0]) / (1.25 ** 0.5)
+    assert float((gz @ normal).abs().max()) < 1e-5 and torch.allclose(gz.norm(dim=1), torch.full((s.n_cells,), 0.5 / 1.25 ** 0.5), atol=1e-5)
+
+
+def test_mesh_subdivision_linear_and_loop():
+    from physicsnemo_b200.mesh import subdivide_linear, subdivide_loop
+    from physicsnemo_b200.mesh.mesh import Mesh
+    from physicsnemo_b200.mesh.operations import validate
+
+    m = _grid_mesh(4)
+    m.point_data["f"] = m.points[:, 0].clone()
+    m.cell_data["id"] = torch.arange(m.n_cells)
+    fine = subdivide_linear(m, 2)
+    assert fine.n_cells == 16 * m.n_cells and abs(float(fine.cell_areas.sum()) - 1.0) < 1e-5
+    assert torch.allclose(fine.point_data["f"], fine.points[:, 0], atol=1e-6)      # linear data stays linear
+    assert torch.equal(fine.cell_data["id"][::16], m.cell_data["id"])
+    octa = Mesh(torch.tensor([[1.0, 0, 0], [-1, 0, 0], [0, 1, 0], [0, -1, 0], [0, 0, 1], [0, 0, -1]]),
+                torch.tensor([[0, 2, 4], [2, 1, 4], [1, 3, 4], [3, 0, 4], [2, 0, 5], [1, 2, 5], [3, 1, 5], [0, 3, 5]]))
+    smooth = subdivide_loop(octa, 3)
+    report = validate(smooth)
+    assert report["is_watertight"] and report["is_manifold"] and report["euler_characteristic"] == 2
+    radii = smooth.points.norm(dim=1)
+    assert float(radii.max() - radii.min()) < 0.1                                   # the octahedron rounds to a near-sphere
+    flat = subdivide_loop(_grid_mesh(4), 1)                                         # boundary rule keeps a square a square
+    assert abs(float(flat.cell_areas.sum()) - 1.0) < 0.05 and float(flat.points.min()) >= -1e-6
