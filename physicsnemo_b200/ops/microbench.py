@@ -200,6 +200,69 @@ def pixel_attention_cases(small=False):
                                                         flops, fwd_bytes)
     return out
 
+def afno_filter_cases(small: bool = False):
+    """Stages of the AFNO spectral filter on the FourCastNet grid (2 x 90 x 180 tokens, 768 channels in 8 blocks; the small
+    variant is 1 x 90 x 180 with 4 blocks): pruned row transforms, column transforms, the stacked-batch block MLP."""
+    import ctypes
+
+    from . import afno_spectral as A
+    from . import gemm as G
+
+    B, H, W, nb = (1, 90, 180, 4) if small else (2, 90, 180, 8)
+    C = 96 * nb
+    geo = A.FilterGeometry(B, H, W, C, nb, H // 2 + 1)
+    lib = A._lib_af()
+    st = torch.cuda.current_stream().cuda_stream
+    tok = _r(B * H * W, C)
+    out = torch.empty_like(tok)
+    Y = torch.empty(B * H, geo.KX, C, 2, device="cuda")
+    Z = torch.zeros(nb, geo.Mp, 192, device="cuda", dtype=torch.bfloat16)
+    O = torch.empty_like(Z)
+    w = _r(nb, 192, 192, scale=0.05)
+    bias = torch.randn(nb, 192, device="cuda")
+    dw = torch.zeros(nb, 192, 192, device="cuda")
+    ptr = lambda t: (ctypes.c_void_p * 8)(*([t.data_ptr()] * 8))            # noqa: E731
+    rows_flops = 2.0 * B * H * C * geo.KX * W * 2 / 2                          # folded real-input transform
+    cols_flops = 8.0 * B * geo.KX * C * H * (geo.H1 + geo.H2)
+    spec_bytes = B * H * geo.KX * C * 8
+    return {
+        "afno_rows_r2c": (lambda: lib.pnm_afno_rows_r2c(ptr(tok), Y.data_ptr(), geo.arr, geo.Tp, 0, 0, None, 0, 1, 0, 0, 1.0, None, st),
+                          rows_flops, tok.numel() * 2 + spec_bytes),
+        "afno_rows_c2r": (lambda: lib.pnm_afno_rows_c2r(Y.data_ptr(), ptr(out), geo.arr, geo.Tp, 1, 0, None, 0, 1, 0, 0, None, None, st),
+                          rows_flops, tok.numel() * 2 + spec_bytes),
+        "afno_cols_dft": (lambda: lib.pnm_afno_cols_dft(Y.data_ptr(), Z.data_ptr(), None, geo.arr, geo.Mp, 0.0, st),
+                          cols_flops, spec_bytes + Z.numel() * 2),
+        "afno_cols_idft": (lambda: lib.pnm_afno_cols_idft(Z.data_ptr(), Y.data_ptr(), geo.arr, geo.Mp, 0.01, st),
+                           cols_flops, spec_bytes + Z.numel() * 2),
+        "afno_block_mlp_layer": (lambda: G.gemm_tn_stacked(Z, w, bias=bias, act=G.ACT_RELU, out=O),
+                                 2.0 * nb * geo.Mp * 192 * 192, 2 * Z.numel() * 2),
+        "afno_block_mlp_wgrad": (lambda: G.gemm_nt_stacked(O, Z, dw), 2.0 * nb * geo.Mp * 192 * 192, 2 * Z.numel() * 2),
+    }
+
+
+def gemm_attention_cases(small: bool = False):
+    """The 512-wide single head of the SongUNet bottleneck over 16 384 tokens (4 096 in the small variant): forward and
+    forward + backward of attention as GEMMs around the row softmax."""
+    from . import gemm_attention as GA
+
+    S = 4096 if small else 16384
+    q, k, v = (_r(1, 1, S, 512).requires_grad_(True) for _ in range(3))
+    do = _r(1, 1, S, 512)
+    P = _r(S, S)
+
+    def fwd():
+        with torch.no_grad():
+            GA.gemm_attention(q, k, v)
+
+    def fwd_bwd():
+        GA.gemm_attention(q, k, v).backward(do)
+        q.grad = k.grad = v.grad = None
+
+    fl = 4.0 * S * S * 512
+    return {"gemm_attention_fwd": (fwd, fl, 2 * S * S * 2 * 2), "gemm_attention_fwd_bwd": (fwd_bwd, 3.5 * fl, 8 * S * S * 2),
+            "softmax_rows": (lambda: GA.softmax_rows_(P, 0.044), 5.0 * S * S, 2 * S * S * 2)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel")
@@ -219,6 +282,12 @@ def main():
         names = list(table)
     elif args.kernel in ("sh_norm", "sh_norm_small"):
         table = sh_norm_cases(small=args.kernel == "sh_norm_small")
+        names = list(table)
+    elif args.kernel in ("afno_filter", "afno_filter_small"):
+        table = afno_filter_cases(small=args.kernel == "afno_filter_small")
+        names = list(table)
+    elif args.kernel in ("gemm_attention", "gemm_attention_small"):
+        table = gemm_attention_cases(small=args.kernel == "gemm_attention_small")
         names = list(table)
     elif args.kernel in ("attention", "attention_small"):
         table = attention_cases(small=args.kernel == "attention_small")

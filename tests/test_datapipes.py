@@ -494,3 +494,78 @@ def test_bistride_multilayer_graph(tmp_path):
     first, again = wrapped[0], wrapped[0]
     assert len(first["ms_edges"]) == 3 and len(first["ms_ids"]) == 2
     assert all(torch.equal(a, b) for a, b in zip(first["ms_ids"], again["ms_ids"]))
+
+
+def _healpix_store(T=40, C=3, F=12, H=4):
+    import numpy as np
+
+    rng = np.random.default_rng(0)
+    t0 = np.datetime64("2020-01-01T00:00:00")
+    time = t0 + np.arange(T) * np.timedelta64(3, "h")
+    data = rng.random((T, C, F, H, H)).astype(np.float32)
+    data[:, 0] += np.arange(T, dtype=np.float32)[:, None, None, None]           # channel 0 encodes its time index
+    lat = rng.uniform(-80, 80, (F, H, H)).astype(np.float32)
+    lon = rng.uniform(0, 360, (F, H, H)).astype(np.float32)
+    return dict(inputs=data, targets=data.copy(), time=time, lat=lat, lon=lon, constants=rng.random((2, F, H, H)).astype(np.float32),
+                channel_in=np.array(["z500", "t2m", "sst"]), channel_out=np.array(["z500", "t2m", "sst"]))
+
+
+def test_healpix_timeseries_dataset_shapes_and_indices():
+    import numpy as np
+
+    from physicsnemo_b200.datapipes.healpix import TimeSeriesDataset
+
+    store = _healpix_store()
+    scaling = {k: {"mean": 0.0, "std": 1.0} for k in ("z500", "t2m", "sst")}
+    ds = TimeSeriesDataset(store, scaling, input_time_dim=2, output_time_dim=2, data_time_step="3h", time_step="6h", batch_size=4,
+                           add_insolation=True)
+    window = 2 * 1 + 1 + 2 + 2                                                   # (T_in-1)*2 + 1 + gap 2 + (T_out-1)*2
+    assert ds._window_length == window and len(ds) == int(np.ceil((40 - window + 1) / 4))
+    (x, sol, const), y = ds[1]
+    assert x.shape == (4, 12, 2, 3, 4, 4) and y.shape == (4, 12, 2, 3, 4, 4)
+    assert sol.shape == (4, 12, 4, 1, 4, 4) and const.shape == (12, 2, 4, 4)
+    t_in = np.round(x[:, 0, :, 0, 0, 0] - store["inputs"][0, 0, 0, 0, 0] % 1).astype(int)
+    first = np.floor(x[:, 0, :, 0, 0, 0]).astype(int)
+    assert (first == np.array([[4, 6], [5, 7], [6, 8], [7, 9]])).all()           # batch 1 starts at time index 4, stride 2
+    assert (np.floor(y[:, 0, :, 0, 0, 0]).astype(int) == np.array([[8, 10], [9, 11], [10, 12], [11, 13]])).all()
+    last_inputs, _ = ds[len(ds) - 1]
+    assert 1 <= last_inputs[0].shape[0] <= 4                                     # ragged last batch unless drop_last
+    fc = TimeSeriesDataset(store, scaling, input_time_dim=2, output_time_dim=2, batch_size=4,
+                           forecast_init_times=[store["time"][10], store["time"][20]])
+    assert len(fc) == 2 and fc[0][0].shape == (1, 12, 2, 3, 4, 4)
+    assert np.floor(fc[1][0][0, 0, :, 0, 0, 0]).astype(int).tolist() == [18, 20]  # history ends at the initial time
+    del t_in
+
+
+def test_healpix_coupled_dataset_and_couplers():
+    import numpy as np
+
+    from physicsnemo_b200.datapipes.healpix import ConstantCoupler, CoupledTimeSeriesDataset, TrailingAverageCoupler
+
+    store = _healpix_store()
+    scaling = {k: {"mean": 0.0, "std": 1.0} for k in ("z500", "t2m", "sst")}
+    coupler = TrailingAverageCoupler(store, batch_size=3, variables=["z500"], input_time_dim=2, output_time_dim=2,
+                                     input_times=["6h", "12h"], averaging_window="6h")
+    ds = CoupledTimeSeriesDataset(store, ["t2m", "sst"], ["t2m"], scaling, input_time_dim=2, output_time_dim=2, batch_size=3,
+                                  couplings=[coupler])
+    (x, const, coupled), y = ds[0]
+    assert x.shape == (3, 12, 2, 2, 4, 4) and y.shape == (3, 12, 2, 1, 4, 4)
+    assert coupled.shape == (1, 3, 2, 12, 4, 4)                                  # [integration steps, B, var x lead, F, H, W]
+    # z500 carries its time index: offsets are b + (T_in * i + 1) * interval + lead / dt
+    assert np.floor(coupled[0, :, :, 0, 0, 0]).astype(int).tolist() == [[4, 6], [5, 7], [6, 8]]
+
+    class Ocean:
+        output_variables = ["z500", "other"]
+        time_step = "6h"
+
+    coupler.setup_coupling(Ocean())
+    fields = torch.arange(4.0).reshape(1, 1, 4, 1, 1, 1).expand(1, 12, 4, 2, 4, 4)      # time index as value
+    coupler.set_coupled_fields(fields)
+    preset = coupler.construct_integrated_couplings()
+    assert preset.shape == (1, 1, 2, 12, 4, 4)
+    assert preset[0, 0, :, 0, 0, 0].tolist() == [0.0, 1.0]                        # windows [0:1] and [1:2] of the other model's steps
+    const_c = ConstantCoupler(store, batch_size=3, variables=["sst"], input_time_dim=2, output_time_dim=2, input_times=["6h"])
+    const_c.compute_coupled_indices(2, "3h")
+    got = const_c.construct_integrated_couplings({"time": slice(5, 20)}, 2)
+    assert got.shape == (1, 2, 1, 12, 4, 4)
+    assert np.allclose(got[0, 0, 0], store["inputs"][5 + 2, 2])
