@@ -38,6 +38,11 @@ struct GemmArgs {
   // stacked batch (batch_m_tiles != 0): A / C hold `batch` problems of batch_m_tiles * 128 rows one after the other, B holds
   // their [N, K] matrices one after the other, bias / scale their [N] vectors: M tile mt belongs to problem mt / batch_m_tiles
   int batch_m_tiles;
+  // split_m (BN = 256 instantiation only): a tile is TWO 128-row sub-tiles that share one 128-column B tile, i.e. 256 x 128
+  // outputs.  For N <= 128 this reads B once per 256 rows instead of once per 128 (the 128 x 128 tile is bound by the
+  // L2 -> shared-memory traffic of its operands); stage size, TMEM layout and the epilogue's warp mapping are those of
+  // the 128 x 256 tile with "column half" replaced by "row half".  num_m_tiles counts 256-row tiles.
+  int split_m;
   // implicit-GEMM convolution (conv != 0): rows of A are output pixels of an NHWC image, tiled 8 x 16 per M tile;
   // K runs over (tap, input channel); the A tile of k-block (tap, c0) is the input window shifted by the tap
   int conv, tiles_x, tiles_y, cin, ksize, pad, img_h;
@@ -194,33 +199,42 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint8_t* sb = sa + kBM * kBK * 2;
           mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
           const int k = kb * kBK;
-          if (g.conv) {
-            int n, y0, x0;
-            conv_tile_origin(g, mt, n, y0, x0);
-            const int tap = k / g.cin, c0 = k - tap * g.cin;
-            const int xs = x0 + tap % g.ksize - g.pad, ys = y0 + tap / g.ksize - g.pad;
-            if (g.halo && ys < 0 && g.has_up) {
-              // box rows -1 .. 6: row -1 is the upper neighbour's bottom row, rows 0 .. 6 are local
-              if (!up_ready) {
-                if (!wait_remote_flag(g.flag_up, g.halo_epoch, abort_flag, g.err, g.halo_budget_ns)) { ok = false; break; }
-                up_ready = true;
+          auto load_a = [&](uint8_t* sa, int mt) -> bool {
+            if (g.conv) {
+              int n, y0, x0;
+              conv_tile_origin(g, mt, n, y0, x0);
+              const int tap = k / g.cin, c0 = k - tap * g.cin;
+              const int xs = x0 + tap % g.ksize - g.pad, ys = y0 + tap / g.ksize - g.pad;
+              if (g.halo && ys < 0 && g.has_up) {
+                // box rows -1 .. 6: row -1 is the upper neighbour's bottom row, rows 0 .. 6 are local
+                if (!up_ready) {
+                  if (!wait_remote_flag(g.flag_up, g.halo_epoch, abort_flag, g.err, g.halo_budget_ns)) return false;
+                  up_ready = true;
+                }
+                tma_load_4d(sa, &tmA3, &full[s], c0, xs, 0, n);
+                tma_load_4d(sa + kConvTileW * 128, &tmA2, &full[s], c0, xs, 0, n);
+              } else if (g.halo && ys + kConvTileH > g.img_h && g.has_down) {
+                // box rows H-7 .. H: rows H-7 .. H-1 are local, row H is the lower neighbour's top row
+                if (!down_ready) {
+                  if (!wait_remote_flag(g.flag_down, g.halo_epoch, abort_flag, g.err, g.halo_budget_ns)) return false;
+                  down_ready = true;
+                }
+                tma_load_4d(sa, &tmA2, &full[s], c0, xs, ys, n);
+                tma_load_4d(sa + (kConvTileH - 1) * kConvTileW * 128, &tmX, &full[s], c0, xs, 0, n);
+              } else {
+                tma_load_4d(sa, &tmA, &full[s], c0, xs, ys, n);
               }
-              tma_load_4d(sa, &tmA3, &full[s], c0, xs, 0, n);
-              tma_load_4d(sa + kConvTileW * 128, &tmA2, &full[s], c0, xs, 0, n);
-            } else if (g.halo && ys + kConvTileH > g.img_h && g.has_down) {
-              // box rows H-7 .. H: rows H-7 .. H-1 are local, row H is the lower neighbour's top row
-              if (!down_ready) {
-                if (!wait_remote_flag(g.flag_down, g.halo_epoch, abort_flag, g.err, g.halo_budget_ns)) { ok = false; break; }
-                down_ready = true;
-              }
-              tma_load_4d(sa, &tmA2, &full[s], c0, xs, ys, n);
-              tma_load_4d(sa + (kConvTileH - 1) * kConvTileW * 128, &tmX, &full[s], c0, xs, 0, n);
-            } else {
-              tma_load_4d(sa, &tmA, &full[s], c0, xs, ys, n);
-            }
-          } else if (k < g.K1) tma_load_2d(sa, &tmA, &full[s], k, mt * kBM);
-          else if (k < g.K2) tma_load_2d(sa, &tmA2, &full[s], k - g.K1, mt * kBM);
-          else tma_load_2d(sa, &tmA3, &full[s], k - g.K2, mt * kBM);
+            } else if (k < g.K1) tma_load_2d(sa, &tmA, &full[s], k, mt * kBM);
+            else if (k < g.K2) tma_load_2d(sa, &tmA2, &full[s], k - g.K1, mt * kBM);
+            else tma_load_2d(sa, &tmA3, &full[s], k - g.K2, mt * kBM);
+            return true;
+          };
+          if (BN == 256 && g.split_m) {
+            if (!load_a(sa, 2 * mt) || !load_a(sa + kBM * kBK * 2, 2 * mt + 1)) { ok = false; break; }
+            tma_load_2d(sa + 2 * kBM * kBK * 2, &tmB, &full[s], k, nt * 128);
+            continue;
+          }
+          if (!load_a(sa, mt)) { ok = false; break; }
           tma_load_2d(sb, &tmB, &full[s], k, nt * BN + (g.batch_m_tiles ? (mt / g.batch_m_tiles) * g.N : 0));
         }
       }
@@ -249,6 +263,18 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_fence_after();
           uint8_t* sa = base + s * Cfg::STAGE_BYTES;
           const uint64_t ad = make_smem_desc(smem_u32(sa), 16, 1024, 2);
+          if (BN == 256 && g.split_m) {
+            constexpr uint32_t idesc_half = make_idesc_bf16(kBM, 128, false, false);
+            const uint64_t ad1 = make_smem_desc(smem_u32(sa + kBM * kBK * 2), 16, 1024, 2);
+            const uint64_t bdh = make_smem_desc(smem_u32(sa + 2 * kBM * kBK * 2), 16, 1024, 2);
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k) {
+              umma_f16(d, ad + 2 * k, bdh + 2 * k, idesc_half, (kb | k) != 0 ? 1u : 0u);
+              umma_f16(d + 128, ad1 + 2 * k, bdh + 2 * k, idesc_half, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(&empty[s]);
+            continue;
+          }
           const uint64_t bd = make_smem_desc(smem_u32(sa + kBM * kBK * 2), 16, 1024, 2);
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k)
@@ -271,6 +297,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int tile = blockIdx.x + int(item / CH) * gridDim.x;
       if (tile >= num_tiles) return false;
       const int mt = tile / g.num_n_tiles, nt = tile % g.num_n_tiles;
+      if (BN == 256 && g.split_m) {             // warp half h owns the rows of sub-tile h, all 128 columns
+        r0 = (2 * mt + h) * kBM + q * 32;
+        c0 = nt * 128 + int(item % CH) * 64;
+        return true;
+      }
       r0 = mt * kBM + q * 32;
       c0 = nt * BN + h * (BN / 2) + int(item % CH) * 64;
       return true;
@@ -429,7 +460,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int n, y0, x0;
             conv_tile_origin(g, r0 / kBM, n, y0, x0);
             const int yy = y0 + 2 * q;
-            if (c0 < g.N && yy < g.img_h) tma_store_4d(stg + b * kChunkBytes, &tmC, c0, x0, yy, n);
+            if (r0 < g.M && c0 < g.N && yy < g.img_h) tma_store_4d(stg + b * kChunkBytes, &tmC, c0, x0, yy, n);
           } else if (store_ok) tma_store_2d(stg + b * kChunkBytes, &tmC, c0, r0);
           tma_store_commit();
         }
@@ -461,6 +492,7 @@ struct GemmCall {
   const float* bias; const float* scale; float* group_out;
   int act, aux_mode, scale_post;
   int max_ctas;  // 0 = number of SMs
+  int split_m = 0;  // BN = 256 instantiation as 256-row x 128-column tiles (see GemmArgs::split_m)
   int batch = 1; // > 1: `batch` stacked problems (see GemmArgs::batch_m_tiles); M is the total row count, M / batch % 128 == 0
   // convolution: A is an NHWC image [img_n, img_h, img_w, cin], B holds [N, ksize*ksize*cin] (tap-major), C is NHWC
   int conv = 0, img_n = 0, img_h = 0, img_w = 0, cin = 0, ksize = 0;
@@ -492,7 +524,8 @@ inline int launch_gemm_tn(const GemmCall& c, int num_sms, int* err_word, cudaStr
   if (c.K > c.K2) { if (make_tmap_2d_b16(&tA3, c.A3, c.M, c.K - c.K2, c.lda3, kBM, kBK)) return -18; }
   else if (!(halo && c.up_rows)) tA3 = tA;
   if (c.batch > 1 && (c.conv || c.M % (c.batch * kBM) || c.group_out)) return -21;
-  if (make_tmap_2d_b16(&tB, c.B, c.N * (c.batch > 1 ? c.batch : 1), c.K, c.ldb, BN, kBK)) return -12;
+  const bool split = BN == 256 && MODE == MODE_PLAIN && c.split_m && c.batch <= 1;
+  if (make_tmap_2d_b16(&tB, c.B, c.N * (c.batch > 1 ? c.batch : 1), c.K, c.ldb, split ? 128 : BN, kBK)) return -12;
   if (c.conv) { if (make_tmap_nhwc_b16(&tC, c.C, c.img_n, c.img_h, c.img_w, c.N, 2, kConvTileW)) return -13; }
   else if (make_tmap_2d_b16(&tC, c.C, c.M, c.N, c.ldc, 32, 64)) return -13;
   if (MODE == MODE_Z) { if (make_tmap_2d_b16(&tX, c.Z, c.M, c.N, c.ldz, 32, 64)) return -14; }
@@ -506,6 +539,7 @@ inline int launch_gemm_tn(const GemmCall& c, int num_sms, int* err_word, cudaStr
   g.num_n_tiles = (c.N + BN - 1) / BN;
   g.err = err_word;
   g.batch_m_tiles = c.batch > 1 ? c.M / c.batch / kBM : 0;
+  g.split_m = split ? 1 : 0;
   g.conv = c.conv; g.cin = c.cin; g.ksize = c.ksize; g.pad = c.ksize / 2; g.img_h = c.img_h;
   g.tiles_x = g.tiles_y = 0;
   g.halo = c.conv ? c.halo : 0; g.has_up = c.up_rows != nullptr; g.has_down = c.down_rows != nullptr; g.img_n = c.img_n;
@@ -522,6 +556,10 @@ inline int launch_gemm_tn(const GemmCall& c, int num_sms, int* err_word, cudaStr
     if (cudaFuncSetAttribute(gemm_tn_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) !=
         cudaSuccess)
       return -16;
+  }
+  if (split) {                                // 256-row tiles of 128 columns
+    g.num_m_tiles = (g.num_m_tiles + 1) / 2;
+    g.num_n_tiles = (c.N + 127) / 128;
   }
   int tiles = g.num_m_tiles * g.num_n_tiles;
   int cap = c.max_ctas > 0 ? c.max_ctas : num_sms;

@@ -252,6 +252,22 @@ int pnm_counting_scatter(const int* idx, const int* offsets, int* cursor, int* o
 // replication times scale); c % 8 == 0
 int pnm_resample2x_nhwc(const void* x, void* y, int n, int h, int w, int c, int mode, float scale, void* stream);
 
+// Physics-attention small algebra (csrc/physics_attn_small.cu), partitioned-graph halo exchange (csrc/graph_halo.cu) and the
+// AFNO spectral filter (csrc/afno_spectral.cu); argument conventions are documented above each definition.
+int pnm_pa_prepare_fwd(const float* Wx, const float* bx, const float* Wfx, const float* Ws, const float* bs, const float* temp, void* Wc16, float* bc, float* inv_t, void* Wfx16, void* Wback16, int H, int D, int C, void* stream);
+int pnm_pa_tokens_fwd(const void* const* srcs, int world, int use_flags, long long norm_off, int ld_tok, const float* Wqkv, const float* Wo, void* wcomb16, void* const* saved, int H, int D, int Cout, float scale, const void* const* bases, int rank, unsigned int epoch, long long capacity_floats, double budget_s, const void* epoch_base, void* stream);
+int pnm_pa_tokens_bwd(const void* const* srcs, int world, int use_flags, const float* Wqkv, const float* Wo, void* const* saved, float* dWo, float* dWqkv, float* d_norm, void* Bcat16, void* BdT16, int H, int D, int Cout, float scale, float share, const void* const* bases, int rank, unsigned int epoch, long long capacity_floats, double budget_s, const void* epoch_base, void* stream);
+int pnm_pa_prepare_bwd(const float* dWc, const float* dbc, const float* grp, const float* Wx, const float* bx, const float* Ws, const float* temp, float* dWx, float* dbx, float* dWs, float* dbs, float* dtemp, int H, int D, int C, void* stream);
+int pnm_graph_halo_publish(const void* in, int ldi, const int* send_idx, void* mailbox, long long n_send, int C, const void* const* bases, int rank, int world, unsigned int epoch, long long capacity_floats, const void* epoch_base, void* counter, void* stream);
+int pnm_graph_gather_halo(const void* in, int ldi, const int* idx, int n_local, const int* halo_owner, const int* halo_slot, const void* const* mailboxes, void* out, int ldo, long long E, int C, int wait, const void* const* bases, int rank, int world, unsigned int epoch, long long capacity_floats, double budget_s, const void* epoch_base, void* stream);
+int pnm_graph_halo_pull_add(void* dn, int ldn, const int* bnd_row, const int* bnd_off, const int* ent_peer, const int* ent_slot, const void* const* mailboxes, long long n_bnd, int C, int wait, const void* const* bases, int rank, int world, unsigned int epoch, long long capacity_floats, double budget_s, const void* epoch_base, void* stream);
+int pnm_afno_rows_r2c(const void* const* tokens, void* Y, const int* geom, long long Tp, int kweight, int wait, const void* const* bases, int rank, int world, unsigned int epoch, long long capacity_floats, double budget_s, const void* epoch_base, void* stream);
+int pnm_afno_rows_c2r(const void* X, const void* const* tokens, const int* geom, long long Tp, int kweight, int signal, const void* const* bases, int rank, int world, unsigned int epoch, long long capacity_floats, const void* epoch_base, void* counter, void* stream);
+int pnm_afno_cols_fwd(const void* Y, void* Yout, void* Zs, void* O1s, void* O2s, const float* w1, const float* b1, const float* w2, const float* b2, int nb, const int* geom, float lambda, void* stream);
+int pnm_afno_cols_bwd(const void* dYout, void* dY, const void* Zs, const void* O1s, const void* O2s, const float* w1, const float* w2, float* dw1, float* db1, float* dw2, float* db2, int nb, const int* geom, void* stream);
+int pnm_afno_cols_dft(const void* Y, void* E, const void* mask, const int* geom, int Mp, float lambda, void* stream);
+int pnm_afno_cols_idft(const void* E, void* Yout, const int* geom, int Mp, float lambda, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

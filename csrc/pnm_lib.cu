@@ -98,7 +98,11 @@ int pnm_gemm_tn(const void* A, int lda, const void* A2, int lda2, const void* A3
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (AUX) return pnm::launch_gemm_tn<128, pnm::MODE_AUX>(c, g_num_sms, g_err_ptr, st);
   if (Z) return pnm::launch_gemm_tn<128, pnm::MODE_Z>(c, g_num_sms, g_err_ptr, st);
-  if (bn == 0) bn = (N > 128) ? 256 : 128;
+  if (bn == 0) {
+    bn = (N > 128) ? 256 : 128;
+    // N <= 128 with many row tiles: 256-row x 128-column tiles of the BN = 256 instantiation (B read once per 256 rows)
+    if (bn == 128 && N > 64 && (long long)M >= 256LL * 2 * g_num_sms) { bn = 256; c.split_m = 1; }
+  } else if (bn == -256) { bn = 256; c.split_m = 1; }
   if (bn == 256) return pnm::launch_gemm_tn<256, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
   return pnm::launch_gemm_tn<128, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
 }
@@ -143,7 +147,10 @@ int pnm_conv2d_nhwc(const void* x, const void* weight, void* y, int n, int h, in
   c.max_ctas = max_ctas;
   c.conv = 1; c.img_n = n; c.img_h = h; c.img_w = w; c.cin = cin; c.ksize = ksize;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (bn == 0) bn = (cout > 128) ? 256 : 128;
+  if (bn == 0) {
+    bn = (cout > 128) ? 256 : 128;
+    if (bn == 128 && cout > 64 && (long long)n * h * w >= 256LL * 2 * g_num_sms) { bn = 256; c.split_m = 1; }
+  } else if (bn == -256) { bn = 256; c.split_m = 1; }
   if (bn == 256) return pnm::launch_gemm_tn<256, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
   return pnm::launch_gemm_tn<128, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
 }
@@ -206,7 +213,10 @@ int pnm_conv2d_nhwc_halo(const void* x, const void* weight, void* y, int n, int 
   c.flag_up = reinterpret_cast<const uint32_t*>(flag_up); c.flag_down = reinterpret_cast<const uint32_t*>(flag_down);
   c.halo_epoch = epoch; c.halo_budget_s = budget_s;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (bn == 0) bn = (cout > 128) ? 256 : 128;
+  if (bn == 0) {
+    bn = (cout > 128) ? 256 : 128;
+    if (bn == 128 && cout > 64 && (long long)n * h * w >= 256LL * 2 * g_num_sms) { bn = 256; c.split_m = 1; }
+  } else if (bn == -256) { bn = 256; c.split_m = 1; }
   if (bn == 256) return pnm::launch_gemm_tn<256, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
   return pnm::launch_gemm_tn<128, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
 }

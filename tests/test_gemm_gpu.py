@@ -155,7 +155,21 @@ def test_mlp_chain_matches_torch():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("shape", [(2, 64, 128, 24, 40, 3), (1, 128, 64, 17, 33, 3), (3, 64, 72, 8, 16, 1), (1, 192, 256, 40, 24, 5)])
+@pytest.mark.parametrize("M,N,K", [(1000, 128, 128), (257, 72, 72), (90000, 128, 320), (512, 128, 64)])
+def test_gemm_tn_split_m_tiles(M, N, K):
+    """256-row x 128-column tiles (two row sub-tiles sharing one B tile), forced with bn = -256 and, for the large M,
+    chosen by the launcher itself."""
+    a, b = _rand(M, K), _rand(N, K, scale=0.1)
+    bias = torch.randn(N, device="cuda")
+    ref, _ = ops.gemm_tn_reference(a, b, bias=bias, act=G.ACT_SILU)
+    _close(ops.gemm_tn(a, b, bias=bias, act=G.ACT_SILU, bn=-256), ref)
+    _close(ops.gemm_tn(a, b, bias=bias, act=G.ACT_SILU), ref)
+    assert ops.device_error() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(2, 64, 128, 24, 40, 3), (1, 128, 64, 17, 33, 3), (3, 64, 72, 8, 16, 1), (1, 192, 256, 40, 24, 5),
+                                   (1, 128, 128, 296, 272, 3), (1, 64, 96, 320, 256, 1)])
 def test_conv2d_same_implicit_gemm(shape):
     from physicsnemo_b200.ops import conv as C
 
