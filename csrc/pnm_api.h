@@ -268,6 +268,9 @@ int pnm_afno_cols_bwd(const void* dYout, void* dY, const void* Zs, const void* O
 int pnm_afno_cols_dft(const void* Y, void* E, const void* mask, const int* geom, int Mp, float lambda, void* stream);
 int pnm_afno_cols_idft(const void* E, void* Yout, const int* geom, int Mp, float lambda, void* stream);
 
+// out = (a + b) * scale over n bf16 elements (n % 8 == 0; b may be null)
+int pnm_add_scale_bf16(const void* a, const void* b, void* out, long long n, float scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

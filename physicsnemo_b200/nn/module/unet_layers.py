@@ -10,6 +10,8 @@ from __future__ import annotations
 from typing import Any, Dict, List, Set
 
 import torch
+
+from ...ops import resample as _resample
 from torch.nn.functional import silu
 
 from .attention_layers import UNetAttention as Attention
@@ -70,8 +72,8 @@ class UNetBlock(torch.nn.Module):
         else:
             x = self.norm1(x + params)
         x = self.conv1(torch.nn.functional.dropout(x, p=self.dropout, training=self.training))
-        x = x + (self.skip(orig) if self.skip is not None else orig)
-        x = x * self.skip_scale
+        # residual join and rescaling in one pass (one kernel forward, one shared by both branches backward)
+        x = _resample.add_scale(x, self.skip(orig) if self.skip is not None else orig, self.skip_scale)
         if self.attn:
             x = self.attn(x)
             x = x * self.skip_scale

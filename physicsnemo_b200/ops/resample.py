@@ -72,3 +72,48 @@ def up2x(x: torch.Tensor) -> torch.Tensor:
     if supported(x):
         return _Up2x.apply(x)
     return F.interpolate(x, scale_factor=2, mode="nearest")
+
+
+# ------------------------------------------------------------------------------------------------ residual join
+def _add_scale_fn():
+    lib = _lib.load(required=True)
+    if not getattr(lib, "_add_scale_declared", False):
+        c = ctypes
+        lib.pnm_add_scale_bf16.argtypes = [c.c_void_p, c.c_void_p, c.c_void_p, c.c_longlong, c.c_float, c.c_void_p]
+        lib.pnm_add_scale_bf16.restype = c.c_int
+        lib._add_scale_declared = True
+    return lib.pnm_add_scale_bf16
+
+
+def _same_dense_layout(a: torch.Tensor, b: torch.Tensor) -> bool:
+    return a.shape == b.shape and a.stride() == b.stride() and (a.is_contiguous() or a.is_contiguous(memory_format=torch.channels_last))
+
+
+class _AddScale(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, scale: float):
+        out = torch.empty_like(a)
+        rc = _add_scale_fn()(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), float(scale), torch.cuda.current_stream().cuda_stream)
+        _g._check(rc, "pnm_add_scale_bf16")
+        _g.launch_count += 1
+        ctx.scale = float(scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous(memory_format=torch.channels_last) if g.dim() == 4 and not g.is_contiguous() else g.contiguous() if not (
+            g.is_contiguous() or (g.dim() == 4 and g.is_contiguous(memory_format=torch.channels_last))) else g
+        d = torch.empty_like(g)
+        rc = _add_scale_fn()(g.data_ptr(), None, d.data_ptr(), g.numel(), ctx.scale, torch.cuda.current_stream().cuda_stream)
+        _g._check(rc, "pnm_add_scale_bf16")
+        _g.launch_count += 1
+        return d, d, None                      # both branches receive the same scaled gradient
+
+
+def add_scale(a: torch.Tensor, b: torch.Tensor, scale: float) -> torch.Tensor:
+    """``(a + b) * scale``: one kernel (forward) and one (backward, shared by both inputs) for bf16 CUDA tensors of the
+    same dense layout; the PyTorch expression otherwise."""
+    if (type(a) is torch.Tensor and type(b) is torch.Tensor and a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+            and a.numel() % 8 == 0 and _same_dense_layout(a, b) and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0 and _lib.available()):
+        return _AddScale.apply(a, b, scale)
+    return (a + b) * scale

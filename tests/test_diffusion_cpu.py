@@ -180,6 +180,41 @@ def test_multi_diffusion_model_losses_and_predictor():
     assert starts == list(range(0, patches.shape[0], 4))
 
 
+def test_multi_diffusion_patch_local_dps_guidance():
+    """Chunked, patch-local DPS guidance: for a point-wise x0-predictor the streamed result equals the global formula."""
+    from physicsnemo_b200.diffusion.multi_diffusion import (MultiDiffusionDataConsistencyDPSGuidance, MultiDiffusionDPSGuidance,
+                                                             MultiDiffusionDPSScorePredictor, MultiDiffusionModel2D,
+                                                             MultiDiffusionModelConsistencyDPSGuidance, MultiDiffusionPredictor)
+
+    torch.manual_seed(0)
+    net = _PatchNet()
+    md = MultiDiffusionModel2D(net, (16, 24))
+    pred = MultiDiffusionPredictor(md, chunk_size=4, fuse=False)
+    pred.set_patching(overlap_pix=0, boundary_pix=0, patch_shape=(8, 8))
+    x, t = torch.randn(2, 3, 16, 24), torch.tensor([0.5, 1.5])
+    y = torch.randn(2, 3, 16, 24)
+    mask = (torch.rand(2, 3, 16, 24) > 0.6).float()
+    score_fn = lambda x0, xt, tt: (x0 - xt) / tt.reshape(-1, 1, 1, 1) ** 2                     # noqa: E731
+    data = MultiDiffusionDataConsistencyDPSGuidance(pred, mask, y, std_y=0.3, gamma=0.5, sigma_fn=lambda s: s,
+                                                    retain_graph=True)           # a second guidance differentiates the same chunk
+    model = MultiDiffusionModelConsistencyDPSGuidance(pred, lambda z: 2.0 * z, y, std_y=0.5)
+    assert isinstance(data, MultiDiffusionDPSGuidance) and isinstance(model, MultiDiffusionDPSGuidance)
+    guided = MultiDiffusionDPSScorePredictor(pred, score_fn, [data, model])
+    with torch.no_grad():
+        got = guided(x, t)
+    assert got.shape == x.shape and not got.requires_grad
+    g = float(net.gain)                                              # the network is x0 = gain * x, pixel by pixel
+    x0 = g * x
+    tb = t.reshape(-1, 1, 1, 1)
+    rho_d = 1.0 / (2.0 * (0.3 ** 2 + 0.5 * tb ** 2))
+    want = (x0 - x) / tb ** 2 - rho_d * mask * 2 * (x0 - y) * g - (1.0 / (2 * 0.25)) * 2 * (2 * x0 - y) * 2 * g
+    assert torch.allclose(got, want, atol=1e-4)
+    with pytest.raises(ValueError):
+        MultiDiffusionDPSScorePredictor(MultiDiffusionPredictor(md), score_fn, data)
+    with pytest.raises(ValueError):
+        MultiDiffusionDataConsistencyDPSGuidance(pred, mask, y, std_y=0.3, gamma=0.5)
+
+
 def test_generate_steps_are_seeded():
     from physicsnemo_b200.diffusion.generate import diffusion_step, regression_step
 

@@ -682,3 +682,19 @@ def test_box_resample_kernels():
             ya.backward(g.to(torch.bfloat16))
             yb.backward(g.to(torch.bfloat16).float())
             assert float((a.grad.float() - b.grad).abs().max()) <= 1e-2 * float(b.grad.abs().max())
+
+
+@pytest.mark.gpu
+def test_add_scale_kernel():
+    from physicsnemo_b200.ops.resample import add_scale
+
+    torch.manual_seed(0)
+    for fmt in (torch.contiguous_format, torch.channels_last):
+        a = torch.randn(2, 16, 12, 10, device="cuda").to(torch.bfloat16).contiguous(memory_format=fmt).requires_grad_(True)
+        b = torch.randn(2, 16, 12, 10, device="cuda").to(torch.bfloat16).contiguous(memory_format=fmt).requires_grad_(True)
+        y = add_scale(a, b, 0.70710678)
+        ref = (a.detach().float() + b.detach().float()) * 0.70710678
+        assert y.stride() == a.stride() and float((y.float() - ref).abs().max()) < 2e-2
+        g = torch.randn_like(y)
+        y.backward(g)
+        assert torch.allclose(a.grad.float(), g.float() * 0.70710678, atol=2e-2) and torch.equal(a.grad, b.grad)
