@@ -344,3 +344,31 @@ def _fsdp2_with_domain_parallel(rank, world):
 
 def test_fsdp2_coexists_with_shard_tensor_four_ranks():
     run_ranks(_fsdp2_with_domain_parallel, world=4)
+
+
+def _sharded_natten(rank, world):
+    """2-D neighbourhood attention on a height-sharded token grid vs the whole grid (output and q / k / v gradients)."""
+    from physicsnemo_b200.distributed import DistributedManager
+    from physicsnemo_b200.nn.functional.natten import na2d
+    from physicsnemo_b200.parallel import Shard, ShardTensor
+
+    mesh = DistributedManager().initialize_mesh((world,), ("domain",))
+    torch.manual_seed(0)
+    full = [torch.randn(1, 12, 7, 2, 8) for _ in range(3)]
+    dy = torch.randn(1, 12, 7, 2, 8)
+    for kernel, dilation in ((3, 1), (5, 1), (3, 2)):
+        ref_in = [t.clone().requires_grad_(True) for t in full]
+        ref = na2d(*ref_in, kernel, dilation=dilation)
+        ref.backward(dy)
+        loc = [t.tensor_split(world, dim=1)[rank].clone().requires_grad_(True) for t in full]
+        st = [ShardTensor.from_local(t, mesh, [Shard(1)]) for t in loc]
+        out = na2d(*st, kernel, dilation=dilation)
+        assert isinstance(out, ShardTensor)
+        _check(f"natten k={kernel} d={dilation}", out.full_tensor().detach(), ref.detach(), 1e-5)
+        out.to_local().backward(dy.tensor_split(world, dim=1)[rank])
+        for a, b in zip(loc, ref_in):
+            _check("natten input grad", a.grad, b.grad.tensor_split(world, dim=1)[rank], 1e-4)
+
+
+def test_sharded_neighbourhood_attention_two_ranks():
+    run_ranks(_sharded_natten, world=2)
