@@ -219,6 +219,29 @@ class PeerRuntime:
         if err != 0:
             raise PeerTimeoutError(f"device error word = {err} (6 = wait on a peer flag ran out); call recover() on every rank")
 
+    def audit_flags(self) -> dict:
+        """Collective consistency check of this rank's flag block at a quiescent point (debug aid against stray or
+        reordered signals).  Flags hold the call number of the last signal that peer ``r`` raised for CTA ``c`` in
+        ``[slot][phase]``; after a device synchronisation and a barrier every signal of every finished call has landed,
+        so: no flag may exceed the current call number, the columns of ranks that do not exist must still be zero,
+        and the flags of one (slot, phase, CTA) row that were written may differ between peers by at most the calls
+        still allowed in flight (one per slot).  Returns the per-peer maxima; raises ``RuntimeError`` on a violation."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        words = self.buffer[: self.flag_bytes].view(torch.int32).cpu().view(2, 2, -1, 8)      # [slot][phase][cta][rank]
+        now = int(self.epoch_base.item()) + self.epoch
+        if int(words.max()) > now:
+            raise RuntimeError(f"a flag carries call number {int(words.max())} but only {now} calls were made")
+        if self.world < 8 and int(words[..., self.world:].abs().max()) != 0:
+            raise RuntimeError("a flag column of a rank outside the group was written")
+        live = words[..., : self.world]
+        written = live.max(dim=-1).values > 0
+        spread = (live.max(dim=-1).values - live.min(dim=-1).values)[written]
+        if spread.numel() and int(spread.max()) > 2:
+            raise RuntimeError(f"peers disagree by {int(spread.max())} calls on one flag row (at most 2 may be in flight)")
+        dist.barrier(group=self.group)
+        return {"calls": now, "max_per_peer": [int(live[..., r].max()) for r in range(self.world)]}
+
     def recover(self) -> None:
         """Collective: bring flags, call numbers and the error word back to their initial state after a time-out."""
         torch.cuda.synchronize()

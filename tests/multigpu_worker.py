@@ -68,6 +68,8 @@ def check_allreduce(rank, world, dev, report):
         torch.cuda.synchronize()
         if rank == 0:
             print(f"gradient all_reduce 12 M floats via {name}: {e0.elapsed_time(e1) / 10:.3f} ms", flush=True)
+    audit = rt.audit_flags()          # hundreds of calls of every kind later: no stray, future-dated or diverging flags
+    report("flag audit after the all-reduce traffic", 0.0 if audit["calls"] >= max(audit["max_per_peer"]) > 0 else 1.0, 0.5)
     return rt
 
 
@@ -101,6 +103,8 @@ def check_timeout_and_recovery(rank, world, dev, report):
     out = rt.all_reduce(x)
     report("allreduce after recover()", _rel(out, ref), 1e-6)
     rt.check()
+    audit = rt.audit_flags()                      # no stray, future-dated or diverging flags after the traffic above
+    report("flag audit", 0.0 if len(audit["max_per_peer"]) == world and audit["calls"] >= max(audit["max_per_peer"]) else 1.0, 0.5)
 
 
 def check_sharded_conv_gn(rank, world, dev, report):
