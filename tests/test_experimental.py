@@ -884,3 +884,37 @@ def test_geometry_guardrail_flags_unusual_shapes(tmp_path, method):
         GeometryGuardrail(method=method).save(tmp_path / "x.npz")
     with pytest.raises(ValueError):
         GeometryGuardrail(method="kde")
+
+
+def test_field_variational_gp_head_learns_a_field_and_flags_far_inputs():
+    """Two-channel field of a 1-D feature: the ELBO falls, the mean fits, and the epistemic variance grows away from data."""
+    from physicsnemo_b200.experimental.uq import FieldVariationalGPHead, FieldVariationalGPPrediction
+
+    torch.manual_seed(0)
+    x = torch.rand(2, 150, 1) * 4 - 2
+    y = torch.cat([torch.sin(2 * x), 0.5 * x ** 2], dim=-1) + 0.05 * torch.randn(2, 150, 2)
+    head = FieldVariationalGPHead(1, n_train=300, num_tasks=2, n_inducing=20, lengthscale_range=(0.05, 5.0))
+    head.set_inducing_points(x)
+    opt = torch.optim.Adam(head.parameters(), lr=0.05)
+    first = None
+    for _ in range(150):
+        opt.zero_grad()
+        mean, nelbo = head.forward_and_loss(x, y)
+        first = float(nelbo) if first is None else first
+        nelbo.backward()
+        opt.step()
+    assert mean.shape == (2, 150, 2) and float(nelbo) < first - 0.5
+    pred = head.predict(x)
+    assert isinstance(pred, FieldVariationalGPPrediction) and pred.mean.shape == (2, 150, 2)
+    assert float((pred.mean - y).abs().mean()) < 0.15
+    assert bool((pred.upper > pred.lower).all()) and bool((pred.variance >= pred.epistemic_variance).all())
+    far = head.predict(torch.full((1, 5, 1), 6.0))
+    assert float(far.epistemic_variance.mean()) > 5 * float(pred.epistemic_variance.mean())
+    # heteroscedastic noise MLP and radial feature normalisation: shapes and a finite objective
+    het = FieldVariationalGPHead(3, n_train=100, num_tasks=2, n_inducing=8, mlp_hidden=[6], feature_norm="l2_radial",
+                                 noise_mlp_hidden=[4], use_double=False)
+    assert het.gp_input_dim == 7 and het.heteroscedastic
+    m, l = het.forward_and_loss(torch.randn(4, 9, 3), torch.randn(4, 9, 2))
+    assert m.shape == (4, 9, 2) and torch.isfinite(l)
+    l.backward()
+    assert het.noise_head[-1].weight.grad is not None
