@@ -108,3 +108,44 @@ class OneHotEmbedding(nn.Module):
     def forward(self, t):
         ind = t * (self.num_channels - 1)
         return torch.clamp(1 - torch.abs(ind - self.indices), min=0)
+
+
+class FourierPositionalEmbedding(nn.Module):
+    """Parameter-free per-axis Fourier features of coordinates (the encoding of implicit decoders).
+
+    Every coordinate ``x_a`` becomes ``[sin(f_0 x_a) … sin(f_{F-1} x_a), cos(f_0 x_a) … cos(f_{F-1} x_a)]``
+    with ``f_i = base_freq · freq_scale^i`` (or an explicit ``freqs`` vector); the axes follow one another and
+    the raw coordinates come first when ``include_input``.  Parity:
+    ``physicsnemo/nn/module/embedding_layers.py:263`` (persistent ``freqs`` buffer, ``out_dim`` property).
+    """
+
+    def __init__(self, in_dim: int = 3, num_bands: int = 10, include_input: bool = True, base_freq: float = math.pi,
+                 freq_scale: float = 2.0, freqs: torch.Tensor | None = None):
+        super().__init__()
+        if in_dim < 1:
+            raise ValueError(f"in_dim must be >= 1, got {in_dim}")
+        if freqs is None:
+            if num_bands < 1:
+                raise ValueError(f"num_bands must be >= 1, got {num_bands}")
+            table = base_freq * freq_scale ** torch.arange(num_bands, dtype=torch.float32)
+        else:
+            table = torch.as_tensor(freqs, dtype=torch.float32)
+            if table.ndim != 1 or table.numel() < 1:
+                raise ValueError(f"freqs must be a 1-D tensor of shape (F,) with F >= 1, got shape {tuple(table.shape)}.")
+        self.in_dim, self.include_input = int(in_dim), bool(include_input)
+        self.register_buffer("freqs", table)
+
+    @property
+    def num_bands(self) -> int:
+        return self.freqs.numel()
+
+    @property
+    def out_dim(self) -> int:
+        return self.in_dim * (2 * self.num_bands + int(self.include_input))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.shape[-1] != self.in_dim:
+            raise ValueError(f"Expected tensor with last dim {self.in_dim}, got tensor of shape {tuple(x.shape)}")
+        phase = x[..., None] * self.freqs.to(x.dtype)
+        waves = torch.cat([phase.sin(), phase.cos()], dim=-1).flatten(-2)
+        return torch.cat([x, waves], dim=-1) if self.include_input else waves
