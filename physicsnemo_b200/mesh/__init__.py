@@ -11,3 +11,5 @@ from . import generate, repair, tessellation  # noqa: E402,F401
 from .generate import marching_cubes  # noqa: E402,F401
 from . import calculus, subdivision  # noqa: E402,F401
 from .subdivision import subdivide_linear, subdivide_loop  # noqa: E402,F401
+from . import boundaries, cluster_tree, projections  # noqa: E402,F401
+from .projections import embed, extrude, project  # noqa: E402,F401

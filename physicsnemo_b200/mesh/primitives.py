@@ -286,3 +286,202 @@ def lumpy_sphere(subdivisions: int = 3, amplitude: float = 0.2, n_modes: int = 6
     amp = torch.rand(n_modes, generator=generator) * amplitude
     bump = (amp[None] * torch.cos(3.0 * s.points @ dirs.T)).sum(1)
     return s._with_points(s.points * (1 + bump)[:, None])
+
+
+# ------------------------------------------------- further basic shapes, curves
+def three_points(dim: int = 3) -> Mesh:
+    """Three isolated points (a 0-manifold)."""
+    p = torch.zeros(3, dim)
+    p[1, 0], p[2, min(1, dim - 1)] = 1.0, 1.0
+    return Mesh(p, torch.arange(3)[:, None])
+
+
+def three_edges(dim: int = 3) -> Mesh:
+    """An open chain of three unit-ish segments that bends in the plane."""
+    xy = torch.tensor([[0.0, 0.0], [1.0, 0.0], [1.5, 0.8], [2.5, 1.0]])
+    return polyline(torch.nn.functional.pad(xy, (0, dim - 2)))
+
+
+def line_segments_1d(n_segments: int = 8, x_range=(0.0, 1.0)) -> Mesh:
+    """A partition of an interval: 1-manifold in one spatial dimension."""
+    return polyline(torch.linspace(x_range[0], x_range[1], n_segments + 1)[:, None])
+
+
+def circular_arc(n_segments: int = 32, radius: float = 1.0, start_angle: float = 0.0, end_angle: float = math.pi / 2) -> Mesh:
+    a = torch.linspace(start_angle, end_angle, n_segments + 1)
+    return polyline(radius * torch.stack([a.cos(), a.sin()], 1))
+
+
+def spline(control_points: torch.Tensor | None = None, n_segments: int = 64, closed: bool = False) -> Mesh:
+    """Catmull–Rom curve through the control points (default: a 3-D zig-zag), sampled uniformly in parameter."""
+    if control_points is None:
+        control_points = torch.tensor([[0.0, 0, 0], [1, 1, 0], [2, 0, 1], [3, 1, 1], [4, 0, 0]])
+    c = torch.as_tensor(control_points, dtype=torch.float32)
+    n = c.shape[0]
+    if n < 2:
+        raise ValueError("a spline needs at least two control points")
+    spans = n if closed else n - 1
+    t = torch.linspace(0, spans, n_segments + (0 if closed else 1) + (1 if closed else 0))[: n_segments + (0 if closed else 1)]
+    i = t.floor().clamp(max=spans - 1).long()
+    u = (t - i)[:, None]
+
+    def pick(k):
+        return c[(i + k) % n] if closed else c[(i + k).clamp(0, n - 1)]
+
+    p0, p1, p2, p3 = pick(-1), pick(0), pick(1), pick(2)
+    pts = 0.5 * (2 * p1 + (p2 - p0) * u + (2 * p0 - 5 * p1 + 4 * p2 - p3) * u ** 2 + (3 * p1 - p0 - 3 * p2 + p3) * u ** 3)
+    return polyline(pts, closed=closed)
+
+
+# ------------------------------------------------------ further planar regions
+def annulus(n_radial: int = 4, n_angular: int = 32, inner_radius: float = 0.5, outer_radius: float = 1.0) -> Mesh:
+    return disk(n_radial=n_radial, n_angular=n_angular, radius=outer_radius, inner_radius=inner_radius)
+
+
+def equilateral_triangle(side: float = 1.0, subdivisions: int = 0) -> Mesh:
+    p = torch.tensor([[0.0, 0.0], [side, 0.0], [side / 2, side * math.sqrt(3) / 2]])
+    m = Mesh(p, torch.tensor([[0, 1, 2]]))
+    return m.subdivide(subdivisions) if subdivisions else m
+
+
+def perturbed_grid(nx: int = 10, ny: int = 10, amplitude: float = 0.2, generator=None) -> Mesh:
+    """Structured triangle grid whose interior vertices move by at most ``amplitude`` (< 0.5) cell widths per axis."""
+    g = structured_grid(nx, ny)
+    cell = torch.tensor([1.0 / nx, 1.0 / ny])
+    jitter = (torch.rand(g.points.shape, generator=generator) * 2 - 1) * amplitude * cell
+    jitter[g.get_boundary_mesh(data_source="none").cells.reshape(-1)] = 0
+    return g._with_points(g.points + jitter)
+
+
+# ------------------------------------------------------------ further surfaces
+def _platonic(points, faces, radius: float, subdivisions: int) -> Mesh:
+    p = torch.tensor(points, dtype=torch.float32)
+    m = Mesh(radius * p / p.norm(dim=1, keepdim=True), torch.tensor(faces))
+    return m.subdivide(subdivisions) if subdivisions else m
+
+
+def tetrahedron_surface(radius: float = 1.0, subdivisions: int = 0) -> Mesh:
+    return _platonic([[1, 1, 1], [1, -1, -1], [-1, 1, -1], [-1, -1, 1]], [[0, 1, 2], [0, 3, 1], [0, 2, 3], [1, 3, 2]],
+                     radius, subdivisions)
+
+
+def octahedron_surface(radius: float = 1.0, subdivisions: int = 0) -> Mesh:
+    return _platonic([[1, 0, 0], [-1, 0, 0], [0, 1, 0], [0, -1, 0], [0, 0, 1], [0, 0, -1]],
+                     [[0, 2, 4], [2, 1, 4], [1, 3, 4], [3, 0, 4], [2, 0, 5], [1, 2, 5], [3, 1, 5], [0, 3, 5]], radius, subdivisions)
+
+
+def icosahedron_surface(radius: float = 1.0) -> Mesh:
+    return icosphere(0, radius)
+
+
+def hemisphere(n_lat: int = 8, n_lon: int = 32, radius: float = 1.0) -> Mesh:
+    """Upper half of a latitude / longitude sphere, open at the equator."""
+    th = torch.linspace(0, math.pi / 2, n_lat + 1)[1:]
+    ph = torch.arange(n_lon) * (2 * math.pi / n_lon)
+    T, P = torch.meshgrid(th, ph, indexing="ij")
+    ring = torch.stack([T.sin() * P.cos(), T.sin() * P.sin(), T.cos()], -1).reshape(-1, 3)
+    pts = radius * torch.cat([torch.tensor([[0.0, 0.0, 1.0]]), ring])
+    j = torch.arange(n_lon)
+    jn = (j + 1) % n_lon
+    cells = [torch.stack([torch.zeros_like(j), 1 + j, 1 + jn], 1)]
+    for r in range(n_lat - 1):
+        a, b = 1 + r * n_lon, 1 + (r + 1) * n_lon
+        cells += [torch.stack([a + j, b + j, b + jn], 1), torch.stack([a + j, b + jn, a + jn], 1)]
+    return Mesh(pts, torch.cat(cells))
+
+
+def cone(n_angular: int = 32, n_height: int = 8, radius: float = 1.0, height: float = 2.0, capped: bool = True) -> Mesh:
+    """Lateral surface from the base circle (z = 0) to the apex (z = height), optionally with the base disk."""
+    ph = torch.arange(n_angular) * (2 * math.pi / n_angular)
+    levels = torch.linspace(0, 1, n_height + 1)[:-1]
+    rings = [torch.stack([(1 - s) * radius * ph.cos(), (1 - s) * radius * ph.sin(), torch.full_like(ph, float(s) * height)], 1)
+             for s in levels]
+    pts = torch.cat(rings + [torch.tensor([[0.0, 0.0, height]])])
+    apex = n_height * n_angular
+    j = torch.arange(n_angular)
+    jn = (j + 1) % n_angular
+    cells = []
+    for r in range(n_height - 1):
+        a, b = r * n_angular, (r + 1) * n_angular
+        cells += [torch.stack([a + j, a + jn, b + jn], 1), torch.stack([a + j, b + jn, b + j], 1)]
+    top = (n_height - 1) * n_angular
+    cells.append(torch.stack([top + j, top + jn, torch.full_like(j, apex)], 1))
+    if capped:
+        pts = torch.cat([pts, torch.zeros(1, 3)])
+        cells.append(torch.stack([jn, j, torch.full_like(j, apex + 1)], 1))
+    return Mesh(pts, torch.cat(cells))
+
+
+def cylinder_open(n_angular: int = 32, n_height: int = 8, radius: float = 1.0, height: float = 2.0) -> Mesh:
+    return cylinder(n_angular=n_angular, n_height=n_height, radius=radius, height=height, capped=False)
+
+
+def mobius_strip(n_around: int = 64, n_across: int = 4, radius: float = 1.0, width: float = 0.4) -> Mesh:
+    """One-sided band: the cross-section turns by half a revolution around the loop, and the seam joins flipped."""
+    u = torch.arange(n_around) * (2 * math.pi / n_around)
+    v = torch.linspace(-width / 2, width / 2, n_across + 1)
+    U, V = torch.meshgrid(u, v, indexing="ij")
+    r = radius + V * (U / 2).cos()
+    pts = torch.stack([r * U.cos(), r * U.sin(), V * (U / 2).sin()], -1).reshape(-1, 3)
+    w = n_across + 1
+    cells = []
+    for i in range(n_around):
+        last = i == n_around - 1
+        for k in range(n_across):
+            a, b = i * w + k, i * w + k + 1
+            c, d = ((n_across - k), (n_across - k - 1)) if last else ((i + 1) * w + k, (i + 1) * w + k + 1)
+            cells += [[a, c, d], [a, d, b]]
+    return Mesh(pts, torch.tensor(cells))
+
+
+# ------------------------------------------------------------- further volumes
+def sphere_volume(subdivisions: int = 2, radius: float = 1.0) -> Mesh:
+    return ball_volume(subdivisions, radius)
+
+
+def tetrahedron_volume(subdivisions: int = 0) -> Mesh:
+    m = single_tetrahedron()
+    return m.subdivide(subdivisions) if subdivisions else m
+
+
+def cylinder_volume(n_radial: int = 3, n_angular: int = 16, n_height: int = 4, radius: float = 1.0, height: float = 2.0) -> Mesh:
+    """Tetrahedral solid cylinder: a triangulated disk swept along ``z`` in ``n_height`` layers."""
+    from .projections import extrude
+
+    layer = disk(n_radial=n_radial, n_angular=n_angular, radius=radius)
+    step = height / n_height
+    slabs = []
+    for k in range(n_height):
+        base = Mesh(torch.nn.functional.pad(layer.points, (0, 1), value=k * step), layer.cells)
+        slabs.append(extrude(base, [0.0, 0.0, step]))
+    return Mesh.merge(slabs).clean()
+
+
+# ---------------------------------------------------------- further procedural
+def value_noise(points: torch.Tensor, frequency: float = 2.0, octaves: int = 3, seed: int = 0) -> torch.Tensor:
+    """Smooth pseudo-random scalar field: a sum of randomly oriented, randomly phased cosines per octave."""
+    g = torch.Generator().manual_seed(int(seed))
+    out = torch.zeros(points.shape[0], dtype=points.dtype)
+    for o in range(octaves):
+        k = torch.randn(8, points.shape[1], generator=g)
+        k = k / k.norm(dim=1, keepdim=True) * frequency * 2 ** o
+        phase = torch.rand(8, generator=g) * 2 * math.pi
+        out = out + (torch.cos(points.cpu() @ k.T.to(points.dtype) + phase.to(points.dtype))).mean(1) / 2 ** o
+    return out.to(points.device)
+
+
+def noisy_mesh(mesh: Mesh, amplitude: float = 0.05, frequency: float = 2.0, octaves: int = 3, seed: int = 0) -> Mesh:
+    """Displace a codimension-1 mesh along its point normals (any other mesh: along the first axis) by smooth noise."""
+    field = value_noise(mesh.points, frequency, octaves, seed)
+    if mesh.n_cells and mesh.codimension == 1:
+        direction = mesh.point_normals
+    else:
+        direction = torch.zeros_like(mesh.points)
+        direction[:, 0] = 1.0
+    return mesh._with_points(mesh.points + amplitude * field[:, None] * direction)
+
+
+def lumpy_ball(subdivisions: int = 2, amplitude: float = 0.2, n_modes: int = 6, generator=None) -> Mesh:
+    """Tetrahedral solid bounded by :func:`lumpy_sphere`."""
+    s = lumpy_sphere(subdivisions, amplitude, n_modes, generator)
+    return Mesh(torch.cat([s.points, torch.zeros(1, 3)]), torch.cat([s.cells, torch.full((s.n_cells, 1), s.n_points)], 1))

@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from physicsnemo_b200.mesh import DomainMesh, Mesh, io, operations as O, primitives as P, spatial as S
+from physicsnemo_b200.mesh import primitives
 from physicsnemo_b200.nn.functional.geometry import ray_mesh_intersect, signed_distance_field
 
 
@@ -258,3 +259,105 @@ def test_mesh_subdivision_linear_and_loop():
     assert float(radii.max() - radii.min()) < 0.1                                   # the octahedron rounds to a near-sphere
     flat = subdivide_loop(_grid_mesh(4), 1)                                         # boundary rule keeps a square a square
     assert abs(float(flat.cell_areas.sum()) - 1.0) < 0.05 and float(flat.points.min()) >= -1e-6
+
+
+def test_boundary_detection_and_topology_checks():
+    from physicsnemo_b200.mesh import boundaries as B
+
+    sq = primitives.unit_square(4)
+    assert int(B.get_boundary_vertices(sq).sum()) == 16 and B.get_boundary_edges(sq).shape == (16, 2)
+    assert int(B.get_boundary_cells(sq).sum()) == 14            # two corner triangles own two boundary edges each
+    assert int(B.get_boundary_cells(sq, boundary_codimension=2).sum()) == 2      # the two corners with a single triangle
+    assert not B.is_watertight(sq) and B.is_manifold(sq)
+    sphere = primitives.icosphere(1)
+    assert B.is_watertight(sphere) and B.is_manifold(sphere) and B.get_boundary_edges(sphere).shape == (0, 2)
+    assert not bool(B.get_boundary_vertices(sphere).any())
+    box = primitives.box_volume(2, 2, 2)
+    assert int(B.get_boundary_vertices(box).sum()) == 26 and B.is_manifold(box)
+    edges = B.get_boundary_edges(box)                            # edges of the 48 boundary triangles: V - E + F = 2
+    assert 26 - edges.shape[0] + 48 == 2
+    bow_tie = Mesh(torch.tensor([[0.0, 0], [1, 0], [0, 1], [-1, 0], [0, -1]]), torch.tensor([[0, 1, 2], [0, 3, 4]]))
+    assert B.is_manifold(bow_tie, "facets") and not B.is_manifold(bow_tie)
+    fin = Mesh(torch.tensor([[0.0, 0, 0], [1, 0, 0], [0, 1, 0], [0, -1, 0], [0, 0, 1]]),
+               torch.tensor([[0, 1, 2], [0, 1, 3], [0, 1, 4]]))         # three triangles on one edge
+    assert not B.is_manifold(fin, "facets")
+    with pytest.raises(ValueError):
+        B.get_boundary_cells(sq, boundary_codimension=3)
+
+
+def test_embed_project_extrude():
+    from physicsnemo_b200.mesh import boundaries as B
+    from physicsnemo_b200.mesh.projections import embed, extrude, project
+
+    sq = primitives.unit_square(3).with_data(point_data={"v": torch.rand(16, 2), "s": torch.rand(16)},
+                                             cell_data={"c": torch.arange(18.0)})
+    up = embed(sq, 3)
+    assert up.n_spatial_dims == 3 and float(up.points[:, 2].abs().max()) == 0 and embed(sq, 2) is sq
+    mid = embed(sq, 3, insert_at=1)
+    assert torch.equal(mid.points[:, [0, 2]], sq.points) and float(mid.points[:, 1].abs().max()) == 0
+    back = project(up, 2)
+    assert torch.equal(back.points, sq.points) and project(up, keep_dims=[0, 1, 2]) is up
+    lifted = up.with_data(point_data={"w": torch.rand(16, 3)})
+    flat = project(lifted, keep_dims=[2, 0], transform_point_data=True)
+    assert flat.n_spatial_dims == 2 and torch.equal(flat.point_data["w"], lifted.point_data["w"][:, [2, 0]])
+    with pytest.raises(ValueError):
+        project(up, 1)                                            # below the manifold dimension
+    with pytest.raises(ValueError):
+        embed(up, 2)
+    with pytest.raises(ValueError):
+        project(up, 2, keep_dims=[0, 1])
+    slab = extrude(sq, [0.0, 0.0, 0.5], allow_new_spatial_dims=True)
+    assert slab.n_manifold_dims == 3 and slab.n_cells == 3 * sq.n_cells and slab.n_points == 2 * sq.n_points
+    assert abs(float(slab.cell_areas.sum()) - 0.5) < 1e-6 and B.is_manifold(slab)
+    rel = slab.points[slab.cells[:, 1:]] - slab.points[slab.cells[:, :1]]
+    assert bool((torch.det(rel) > 0).all())
+    assert torch.equal(slab.cell_data["c"], sq.cell_data["c"].repeat(3)) and slab.point_data["s"].shape == (32,)
+    band = extrude(embed(primitives.circle(24), 3))       # closed curve → open tube of height 1
+    assert band.n_manifold_dims == 2 and band.n_spatial_dims == 3 and B.get_boundary_edges(band).shape[0] == 48
+    with pytest.raises(ValueError):
+        extrude(sq)
+    with pytest.raises(NotImplementedError):
+        extrude(sq, capping=True)
+
+
+def test_further_primitives():
+    from physicsnemo_b200.mesh import boundaries as B
+
+    closed = {"tetrahedron_surface": 8 / math.sqrt(3), "octahedron_surface": 4 * math.sqrt(3), "icosahedron_surface": None,
+              "cone": None}
+    for name, area in closed.items():
+        m = getattr(primitives, name)()
+        assert B.is_watertight(m) and B.is_manifold(m), name
+        assert float(m.cell_normals.mul(m.cell_centroids - m.points.mean(0)).sum(1).min()) > 0, name   # outward faces
+        if area is not None:
+            assert abs(float(m.cell_areas.sum()) - area) < 1e-4
+    assert abs(float(primitives.cone(64, 8).cell_areas.sum()) - math.pi * (math.sqrt(5) + 1)) < 0.05
+    assert abs(float(primitives.hemisphere(16, 64).cell_areas.sum()) - 2 * math.pi) < 0.05
+    assert abs(float(primitives.annulus().cell_areas.sum()) - math.pi * 0.75) < 0.03
+    assert abs(float(primitives.circular_arc(64).cell_areas.sum()) - math.pi / 2) < 1e-3
+    assert abs(float(primitives.cylinder_volume(4, 32, 4).cell_areas.sum()) - 2 * math.pi) < 0.1
+    strip = primitives.mobius_strip()
+    assert B.is_manifold(strip) and not B.is_watertight(strip)
+    loops = B.get_boundary_edges(strip)                          # one boundary loop of twice the circumference count
+    assert loops.shape[0] == 2 * 64 and orient_consistently_fails(strip)
+    grid = primitives.perturbed_grid(8, 8, 0.3, generator=torch.Generator().manual_seed(0))
+    assert abs(float(grid.cell_areas.sum()) - 1.0) < 1e-5
+    for name in ("three_points", "three_edges", "line_segments_1d", "spline", "equilateral_triangle", "sphere_volume",
+                 "tetrahedron_volume", "lumpy_ball", "cylinder_open"):
+        m = getattr(primitives, name)()
+        assert m.n_cells > 0 and B.is_manifold(m), name
+    ring = primitives.spline(torch.tensor([[1.0, 0, 0], [0, 1, 0], [-1, 0, 0], [0, -1, 0]]), 40, closed=True)
+    assert ring.n_cells == 40 and not bool(B.get_boundary_vertices(ring).any())
+    bumpy = primitives.noisy_mesh(primitives.icosphere(2), amplitude=0.1)
+    radii = bumpy.points.norm(dim=1)
+    assert float(radii.std()) > 1e-3 and float((radii - 1).abs().max()) <= 0.1 + 1e-6
+
+
+def orient_consistently_fails(mesh) -> bool:
+    """A one-sided surface admits no consistent orientation: some neighbouring pair keeps traversing a shared edge the same way."""
+    from physicsnemo_b200.mesh.operations import orient_consistently
+
+    c = orient_consistently(mesh).cells
+    directed = torch.cat([c[:, [0, 1]], c[:, [1, 2]], c[:, [2, 0]]])
+    key = directed[:, 0] * mesh.n_points + directed[:, 1]
+    return bool((torch.unique(key, return_counts=True)[1] > 1).any())
