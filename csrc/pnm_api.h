@@ -271,6 +271,12 @@ int pnm_afno_cols_idft(const void* E, void* Yout, const int* geom, int Mp, float
 // out = (a + b) * scale over n bf16 elements (n % 8 == 0; b may be null)
 int pnm_add_scale_bf16(const void* a, const void* b, void* out, long long n, float scale, void* stream);
 
+// Metadata features of observations (see obs_features.cu): out [n, 28] (extended = 0) or [n, 30] (extended = 1), fp32.
+// lat is read only in the extended scheme; time_ns / target_s are int64 nanoseconds / seconds since the epoch.
+int pnm_obs_metadata(const float* lat, const float* lon, const long long* time_ns, const long long* target_s, const float* height,
+                     const float* pressure, const float* scan, const float* sat_zen, const float* sol_zen, float* out, long long n,
+                     int extended, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

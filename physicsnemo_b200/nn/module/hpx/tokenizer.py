@@ -21,7 +21,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-__all__ = ["HEALPixPatchTokenizer", "HEALPixPatchDetokenizer", "FrequencyEmbedding", "CalendarEmbedding", "healpix_xy_lonlat"]
+__all__ = ["HEALPixPatchTokenizer", "HEALPixPatchDetokenizer", "FrequencyEmbedding", "CalendarEmbedding", "healpix_xy_lonlat", "healpix_lonlat_to_xy"]
 
 _JRLL = (2, 2, 2, 2, 3, 3, 3, 3, 4, 4, 4, 4)
 _JPLL = (1, 3, 5, 7, 0, 2, 4, 6, 1, 3, 5, 7)
@@ -47,6 +47,38 @@ def healpix_xy_lonlat(level: int) -> Tuple[torch.Tensor, torch.Tensor]:
     jp = torch.where(jp < 1, jp + 4 * nr, jp)
     phi = (jp.double() - (kshift.double() + 1) * 0.5) * (math.pi / 2) / nr.double()
     return torch.rad2deg(phi).reshape(-1), torch.rad2deg(torch.asin(z.expand(12, n, n))).reshape(-1)
+
+
+def healpix_lonlat_to_xy(lon: torch.Tensor, lat: torch.Tensor, level: int) -> torch.Tensor:
+    """Index (in the order of :func:`healpix_xy_lonlat`) of the pixel that contains each point; degrees in, int64 out.
+
+    Standard HEALPix point location: the equatorial belt ``|z| <= 2/3`` uses the two diagonal line
+    counters ``jp``, ``jm`` of the cylindrical projection, the polar caps the Collignon coordinates;
+    both give the face and the in-face ``(ix, iy)``, which map to ``row = n - 1 - ix``, ``col = n - 1 - iy``.
+    """
+    n = 2 ** level
+    z = torch.sin(torch.deg2rad(lat.double()))
+    za = z.abs()
+    tt = torch.remainder(lon.double(), 360.0) / 90.0                       # [0, 4)
+    # equatorial belt
+    t1, t2 = n * (0.5 + tt), n * z * 0.75
+    jp, jm = torch.floor(t1 - t2).long(), torch.floor(t1 + t2).long()
+    ifp, ifm = jp // n, jm // n
+    face_eq = torch.where(ifp == ifm, (ifp % 4) + 4, torch.where(ifp < ifm, ifp % 4, (ifm % 4) + 8))
+    ix_eq, iy_eq = jm % n, n - 1 - (jp % n)
+    # polar caps
+    ntt = tt.floor().clamp(max=3)
+    tp = tt - ntt
+    tmp = n * torch.sqrt(3 * (1 - za))
+    jp_c = torch.floor(tp * tmp).long().clamp(max=n - 1)
+    jm_c = torch.floor((1 - tp) * tmp).long().clamp(max=n - 1)
+    up = z >= 0
+    face_cap = torch.where(up, ntt.long(), ntt.long() + 8)
+    ix_cap, iy_cap = torch.where(up, n - 1 - jm_c, jp_c), torch.where(up, n - 1 - jp_c, jm_c)
+    belt = za <= 2.0 / 3.0
+    face = torch.where(belt, face_eq, face_cap)
+    ix, iy = torch.where(belt, ix_eq, ix_cap), torch.where(belt, iy_eq, iy_cap)
+    return face * (n * n) + (n - 1 - ix) * n + (n - 1 - iy)
 
 
 class FrequencyEmbedding(nn.Module):
