@@ -667,3 +667,40 @@ def test_mdlus_files_cross_load_with_the_reference():
                           text=True, timeout=900, env=env)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert proc.stdout.count(": ok") == 5, proc.stdout
+
+
+def test_domino_utils():
+    import math
+
+    from physicsnemo_b200.mesh import primitives
+    from physicsnemo_b200.models.domino import utils as U
+
+    torch.manual_seed(0)
+    x = torch.randn(50, 3) * 4 + 1
+    n = U.normalize(x)
+    assert torch.allclose(n.amin(0), -torch.ones(3)) and torch.allclose(n.amax(0), torch.ones(3))
+    assert torch.allclose(U.unnormalize(n, x.amax(0, keepdim=True), x.amin(0, keepdim=True)), x, atol=1e-5)
+    s = U.standardize(x)
+    assert torch.allclose(s.mean(0), torch.zeros(3), atol=1e-5) and torch.allclose(U.unstandardize(s, x.mean(0), x.std(0)), x, atol=1e-5)
+    enc = U.calculate_pos_encoding(torch.tensor([0.0, 1.0]), d=4)
+    assert len(enc) == 4 and torch.allclose(enc[1], torch.tensor([1.0, math.cos(1.0)])) and torch.allclose(enc[2][1], torch.sin(torch.tensor(0.01)))
+    assert U.calculate_normal_positional_encoding(x, x + 1, (0.5, 0.5, 0.5)).shape == (50, 12)
+    assert U.pad(x, 60, -1.0).shape == (60, 3) and float(U.pad(x, 60, -1.0)[55, 0]) == -1.0 and U.pad(x, 10) is x
+    assert U.pad_inp(torch.ones(2, 3, 3), 4).shape == (4, 3, 3)
+    grid = U.create_grid(torch.tensor([1.0, 1, 1]), torch.tensor([0.0, 0, 0]), [3, 4, 5])
+    assert grid.shape == (3, 4, 5, 3)
+    field = x[:, :1] * 2
+    assert torch.allclose(U.nd_interpolator(x, field, x, k=1), field)
+    assert U.combine_dict({"a": 1, "b": 2.0}, {"a": 2, "b": 0.5}) == {"a": 3, "b": 2.5}
+    out = U.mean_std_sampling(torch.tensor([[0.0, 0], [10, 0], [0, -9]]), torch.zeros(2), torch.ones(2), 3.0)
+    assert sorted(int(i) for i in out) == [1, 2]
+    moved = U.dict_to_device({"x": x, "filename": "f"}, "cpu")
+    assert list(moved) == ["x"]
+    picked, idx = U.area_weighted_shuffle_array(x, 10, torch.rand(50) + 0.1, 2.0)
+    assert picked.shape == (10, 3) and torch.equal(picked, x[idx]) and len(set(idx.tolist())) == 10
+    assert U.solution_weighted_shuffle_array(x, 80, torch.rand(50) + 0.1)[0].shape[0] == 50
+    sphere = primitives.icosphere(2)
+    pts, face, area, normal = U.sample_points_on_mesh(sphere.points, sphere.cells, 2000)
+    assert pts.shape == (2000, 3) and float((pts.norm(dim=1) - 1).abs().max()) < 0.03          # on the faces of the unit sphere
+    assert torch.allclose(area, sphere.cell_areas[face], atol=1e-6) and float((normal * pts).sum(1).min()) > 0.9
+    assert abs(float(pts.mean(0).norm())) < 0.08                                               # area-uniform
