@@ -13,3 +13,4 @@ from . import calculus, subdivision  # noqa: E402,F401
 from .subdivision import subdivide_linear, subdivide_loop  # noqa: E402,F401
 from . import boundaries, cluster_tree, projections  # noqa: E402,F401
 from .projections import embed, extrude, project  # noqa: E402,F401
+from . import geometry, sampling  # noqa: E402,F401

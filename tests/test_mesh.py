@@ -361,3 +361,93 @@ def orient_consistently_fails(mesh) -> bool:
     directed = torch.cat([c[:, [0, 1]], c[:, [1, 2]], c[:, [2, 0]]])
     key = directed[:, 0] * mesh.n_points + directed[:, 1]
     return bool((torch.unique(key, return_counts=True)[1] > 1).any())
+
+
+def test_angles_dual_volumes_and_cotangent_weights():
+    from physicsnemo_b200.mesh import geometry as G
+
+    a = torch.tensor([[1.0, 0, 0], [1.0, 1e-9, 0], [-1.0, 1e-9, 0]])
+    b = torch.tensor([[0.0, 2, 0], [1.0, 0, 0], [1.0, 0, 0]])
+    ang = G.stable_angle_between_vectors(a.double(), b.double())
+    assert torch.allclose(ang, torch.tensor([math.pi / 2, 1e-9, math.pi - 1e-9], dtype=torch.float64), atol=1e-12)
+    grid = primitives.perturbed_grid(6, 6, 0.3, generator=torch.Generator().manual_seed(1))
+    sums = G.compute_vertex_angle_sums(grid)
+    from physicsnemo_b200.mesh.boundaries import get_boundary_vertices
+    inner = ~get_boundary_vertices(grid)
+    assert torch.allclose(sums[inner], torch.full_like(sums[inner], 2 * math.pi), atol=1e-5)
+    assert abs(float(sums.sum()) - math.pi * grid.n_cells) < 1e-3
+    # dual volumes tile the mesh, with obtuse triangles included
+    sliver = Mesh(torch.tensor([[0.0, 0], [4, 0], [2, 0.3], [2, -3]]), torch.tensor([[0, 1, 2], [0, 3, 1]]))
+    for m in (grid, sliver, primitives.icosphere(2), primitives.box_volume(2, 2, 2), primitives.circle(12)):
+        assert abs(float(G.compute_dual_volumes_0(m).sum() - m.cell_areas.sum())) < 1e-4 * float(m.cell_areas.sum())
+    assert torch.allclose(G.compute_dual_volumes_0(sliver)[2], sliver.cell_areas[0] / 2)       # the obtuse corner
+    right = Mesh(torch.tensor([[0.0, 0], [2, 0], [0, 2]]), torch.tensor([[0, 1, 2]]))
+    assert torch.allclose(G.compute_dual_volumes_0(right), torch.tensor([1.0, 0.5, 0.5]))      # circumcentric shares
+    cc = G.compute_circumcenters(right.points[right.cells])
+    assert torch.allclose(cc, torch.tensor([[1.0, 1.0]]))
+    tet = primitives.single_tetrahedron()
+    centre = G.compute_circumcenters(tet.points[tet.cells])[0]
+    assert float((tet.points - centre).norm(dim=1).std()) < 1e-6
+    flat3d = G.compute_circumcenters(torch.tensor([[[0.0, 0, 1], [2, 0, 1], [0, 2, 1]]]))
+    assert torch.allclose(flat3d, torch.tensor([[1.0, 1.0, 1.0]]))
+    # cotangent weights: equilateral triangles give cot(60°)/2 per incident triangle; curves give 1 / length
+    w, edges = G.compute_cotan_weights_fem(primitives.equilateral_triangle())
+    assert edges.shape == (3, 2) and torch.allclose(w, torch.full((3,), 0.5 / math.sqrt(3)), atol=1e-6)
+    w, _ = G.compute_cotan_weights_fem(primitives.line_segments_1d(4))
+    assert torch.allclose(w, torch.full((4,), 4.0), atol=1e-5)
+    # the weights reproduce the Laplacian of a linear field (zero) and of x² (−2 · dual area) at interior vertices
+    w, edges = G.compute_cotan_weights_fem(grid)
+    x = grid.points[:, 0]
+    lap = torch.zeros(grid.n_points)
+    for f in (x, x ** 2):
+        lap = torch.zeros(grid.n_points).index_add_(0, edges[:, 0], w * (f[edges[:, 1]] - f[edges[:, 0]])) \
+                                         .index_add_(0, edges[:, 1], w * (f[edges[:, 0]] - f[edges[:, 1]]))
+        if f is x:
+            assert float(lap[inner].abs().max()) < 1e-5
+    dual = G.compute_dual_volumes_0(grid)
+    assert abs(float(lap[inner].sum()) - 2 * float(dual[inner].sum())) < 0.35 * float(dual[inner].sum())
+    grads = G.compute_barycentric_gradients(grid)
+    assert float(grads.sum(dim=1).abs().max()) < 1e-5
+    lin = (grid.points[grid.cells] @ torch.tensor([2.0, -1.0]))[:, :, None]
+    assert torch.allclose((grads * lin).sum(dim=1), torch.tensor([2.0, -1.0]).expand(grid.n_cells, 2), atol=1e-4)
+    vol, e1 = G.compute_dual_volumes_1(grid)
+    assert vol.shape[0] == e1.shape[0]
+
+
+def test_point_location_and_data_sampling():
+    from physicsnemo_b200.mesh import sampling as SM
+
+    grid = primitives.perturbed_grid(5, 5, 0.25, generator=torch.Generator().manual_seed(2))
+    grid = grid.with_data(point_data={"lin": grid.points @ torch.tensor([3.0, -2.0]) + 1, "vec": grid.points * 2,
+                                      "id": torch.arange(grid.n_points)},
+                          cell_data={"cid": torch.arange(grid.n_cells), "val": torch.arange(grid.n_cells, dtype=torch.float32)})
+    pts, cell = grid.sample_points(200, generator=torch.Generator().manual_seed(3))
+    found, bary = SM.find_containing_cells(grid, pts)
+    assert torch.equal(found, cell) and torch.allclose(bary.sum(1), torch.ones(200), atol=1e-5) and float(bary.min()) > -1e-6
+    assert torch.allclose((bary[:, :, None] * grid.points[grid.cells[found]]).sum(1), pts, atol=1e-5)
+    outside = torch.tensor([[1.5, 0.5], [-0.1, 0.2]])
+    miss, nb = SM.find_containing_cells(grid, outside)
+    assert miss.tolist() == [-1, -1] and bool(nb.isnan().all())
+    got = SM.sample_data_at_points(grid, torch.cat([pts, outside]), data_source="points")
+    assert torch.allclose(got["lin"][:200], pts @ torch.tensor([3.0, -2.0]) + 1, atol=1e-4) and bool(got["lin"][200:].isnan().all())
+    assert torch.allclose(got["vec"][:200], pts * 2, atol=1e-5) and got["id"].dtype == torch.float64
+    cells = SM.sample_data_at_points(grid, torch.cat([pts, outside]))
+    assert torch.equal(cells["val"][:200], cell.float()) and cells["cid"].dtype == torch.float64 and bool(cells["val"][200:].isnan().all())
+    # a vertex of the grid lies in several cells: mean of their values, or NaN on request
+    v = grid.points[12:13]
+    owners = (grid.cells == 12).any(1).nonzero().squeeze(1)
+    qi, ci, _ = SM.find_all_containing_cells(grid, v)
+    assert sorted(ci.tolist()) == sorted(owners.tolist()) and set(qi.tolist()) == {0}
+    assert torch.allclose(SM.sample_data_at_points(grid, v)["val"], owners.float().mean()[None])
+    assert bool(SM.sample_data_at_points(grid, v, multiple_cells_strategy="nan")["val"].isnan().all())
+    # surfaces: off-manifold queries miss unless projected onto the nearest cell
+    sphere = primitives.icosphere(2).with_data(cell_data={"k": torch.arange(320, dtype=torch.float32)})
+    q = sphere.cell_centroids[:5] * 1.2
+    assert bool(SM.sample_data_at_points(sphere, q)["k"].isnan().all())
+    assert SM.sample_data_at_points(sphere, q, project_onto_nearest_cell=True)["k"].tolist() == [0, 1, 2, 3, 4]
+    assert torch.equal(SM.find_nearest_cells(sphere, q), torch.arange(5))
+    assert SM.match_points(grid.points[[3, 7]] + 1e-8, grid.points).tolist() == [3, 7]
+    assert SM.match_points(torch.tensor([[9.0, 9.0]]), grid.points).tolist() == [-1]
+    assert SM.compute_barycentric_coordinates(pts[:4], grid.points[grid.cells[:6]]).shape == (4, 6, 3)
+    with pytest.raises(ValueError):
+        SM.sample_data_at_points(grid, pts, data_source="edges")
