@@ -65,7 +65,7 @@ def compute_unified_metadata_reference(target_time_sec, *, time, lon, lat=None, 
 
 
 def _lib_obs():
-    from ....ops import _lib
+    from .....ops import _lib
 
     lib = _lib.load(required=True)
     if not getattr(lib, "_obs_declared", False):
