@@ -68,6 +68,8 @@ def main():
     ap.add_argument("--config", default=None, choices=["transolver", "songunet", "mgn", "afno", "fno"])
     ap.add_argument("--no-extras", action="store_true", help="only the headline configuration")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
+    ap.add_argument("--micro-batch", type=int, default=None,
+                    help="images per micro-step of the SongUNet configuration (default: one image-equivalent of rows per GPU)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

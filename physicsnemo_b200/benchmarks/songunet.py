@@ -3,8 +3,10 @@
 Model: ``SongUNet(img_resolution=1024, in_channels=16, out_channels=4, model_channels=128, channel_mult=[1,2,2,4],
 num_blocks=2, attn_resolutions=[64])`` (73.8 M parameters; 12 conditioning + 4 noisy-target input channels) inside
 ``EDMPreconditioner``; loss ``MSEDSMLoss`` with the EDM log-normal noise levels (P_mean −1.2, P_std 1.2); Adam.
-Global batch 8.  On N ranks every image is split into N height slabs; the batch is processed in micro-batches of N
-images (one image-equivalent of activations per GPU whatever N is) with gradient accumulation, one optimizer step.
+Global batch 8.  On N ranks every image is split into N height slabs; the batch is processed in micro-batches of
+``min(8, 4 N)`` images (at most four image-equivalents of activations per GPU; ``--micro-batch`` overrides) with gradient
+accumulation, one optimizer step.  Micro-batches of one image leave the 128² and 256² levels of the U-Net with fewer
+tiles than SMs; four images per micro-step measured 10 % faster at one GPU (1051 → 950 ms per step).
 
 Sharded path: every 3×3 convolution is the halo-fused tcgen05 kernel (boundary rows read from the neighbours'
 mailboxes inside the kernel), its weight gradient the split-reduction kernel on saved halo rows, GroupNorm(+SiLU)
@@ -131,7 +133,11 @@ def run(args, rank: int, world: int, dev) -> dict:
     base = EDMNoiseScheduler(P_mean=-1.2, P_std=1.2) if _accepts_p(EDMNoiseScheduler) else EDMNoiseScheduler()
     sched = DomainParallelNoiseScheduler(base, mesh, shard_dim=2) if world > 1 else base
     loss_fn = MSEDSMLoss(model, sched)
-    micro = world if world > 1 else 1          # images per micro-batch: one image-equivalent of rows per GPU
+    micro = min(BATCH, 4 * world)              # images per micro-batch: four image-equivalents of rows per GPU
+    if getattr(args, "micro_batch", None):
+        micro = int(args.micro_batch)
+        if BATCH % micro:
+            raise ValueError(f"--micro-batch must divide the batch of {BATCH}")
     accum = BATCH // micro
     hl = RES // world
     cond, x0 = make_batch(BATCH, RES, seed=0)
@@ -212,6 +218,7 @@ def run(args, rank: int, world: int, dev) -> dict:
         launches,
         {"exposed_comm_ms": exposed, "sharded_vs_single_rel_err": check, "device_error_word": err,
          "loss": float(loss_host.item()), "wall_s_timed_region": wall,
+         "peak_memory_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1),
          "exposed_comm_how": "step time minus the time of the same step with all peer traffic switched off (loopback)"})
 
 
