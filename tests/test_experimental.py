@@ -1,4 +1,5 @@
 """experimental: LoRA adapters and the variational GP head."""
+import numpy as np
 import pytest
 import torch
 import torch.nn as nn
@@ -918,3 +919,25 @@ def test_field_variational_gp_head_learns_a_field_and_flags_far_inputs():
     assert m.shape == (4, 9, 2) and torch.isfinite(l)
     l.backward()
     assert het.noise_head[-1].weight.grad is not None
+
+
+def test_geometry_features_from_a_directory_of_stl_files(tmp_path):
+    from physicsnemo_b200.experimental.guardrails.geometry import FeatureSchema, extract_features
+    from physicsnemo_b200.experimental.guardrails.geometry.mesh_io import load_features_from_dir
+    from physicsnemo_b200.mesh import io, primitives
+
+    shapes = {"a_sphere": primitives.icosphere(2), "b_torus": primitives.torus(24, 12), "c_cube": primitives.cube_surface(3)}
+    for name, mesh in shapes.items():
+        io.write_stl(mesh, tmp_path / f"{name}.stl")
+    (tmp_path / "d_broken.stl").write_bytes(b"solid x\nfacet normal 0 0 0\nouter loop\nvertex 0 0\n")
+    (tmp_path / "notes.txt").write_text("not a mesh")
+    feats, names = load_features_from_dir(tmp_path, n_workers=1)
+    assert names == ["a_sphere.stl", "b_torus.stl", "c_cube.stl"] and all(f.shape == (FeatureSchema.dim,) for f in feats)
+    direct = extract_features(io.read_stl(tmp_path / "b_torus.stl"), return_tensor=False)
+    assert np.allclose(feats[1], direct)
+    pooled, names2 = load_features_from_dir(tmp_path, n_workers=2)
+    assert names2 == names and all(np.allclose(a, b) for a, b in zip(feats, pooled))
+    empty = tmp_path / "none"
+    empty.mkdir()
+    with pytest.raises(RuntimeError, match="No valid STL"):
+        load_features_from_dir(empty)
