@@ -39,7 +39,8 @@ class CoupledTimeSeriesDataset(TimeSeriesDataset):
         for spec in couplings:
             if isinstance(spec, Mapping):                       # {"coupler": class name, "params": {...}} as in the configs
                 cls = getattr(_couplers, spec["coupler"])
-                spec = cls(store, self.batch_size, **dict(spec.get("params", {}), presteps=presteps, input_time_dim=input_time_dim,
+                params = {k: v for k, v in spec.get("params", {}).items() if k != "batch_size"}     # the dataset's own is used
+                spec = cls(store, self.batch_size, **dict(params, presteps=presteps, input_time_dim=input_time_dim,
                                                           output_time_dim=output_time_dim))
             spec.compute_coupled_indices(self.interval, self.data_time_step)
             if self.scaling:

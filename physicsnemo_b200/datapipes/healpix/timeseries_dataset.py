@@ -50,11 +50,76 @@ class ArrayStore:
         self.constants = np.asarray(raw("constants"), dtype=np.float32) if has("constants") else None
         self.channel_in = [str(c) for c in np.asarray(raw("channel_in"))] if has("channel_in") else None
         self.channel_out = [str(c) for c in np.asarray(raw("channel_out"))] if has("channel_out") else self.channel_in
+        self.channel_c = [str(c) for c in np.asarray(raw("channel_c"))] if has("channel_c") else None
 
     @staticmethod
     def slab(array, start: int, stop: int) -> np.ndarray:
         part = array[start:stop]
         return np.asarray(getattr(part, "values", part), dtype=np.float32)
+
+    def sel(self, channel_in=None, channel_out=None, channel_c=None, time=None) -> "ArrayStore":
+        """Sub-store by names / time range, like ``xarray.Dataset.sel`` on the reference's archives.
+
+        ``channel_in`` / ``channel_out`` list variable names in the wanted order; ``channel_c`` lists
+        constant names (needs ``channel_c`` names in the source) or indices; ``time`` is a
+        ``slice(start, stop)`` of anything ``numpy.datetime64`` accepts, both ends inclusive.  The data
+        stay where they are: the result indexes into the parent lazily.
+        """
+        out = ArrayStore.__new__(ArrayStore)
+        out.__dict__.update(self.__dict__)
+        t0, t1 = 0, len(self.time)
+        if time is not None:
+            if time.start is not None:
+                t0 = int(np.searchsorted(self.time, np.datetime64(time.start).astype("datetime64[s]"), side="left"))
+            if time.stop is not None:
+                t1 = int(np.searchsorted(self.time, np.datetime64(time.stop).astype("datetime64[s]"), side="right"))
+            out.time = self.time[t0:t1]
+
+        def pick(array, names, wanted):
+            if array is None:
+                return None, names
+            cols = None
+            if wanted is not None:
+                if names is None:
+                    raise KeyError("selecting variables by name needs the channel names of the data")
+                missing = [w for w in wanted if w not in names]
+                if missing:
+                    raise KeyError(f"variables {missing} are not in the data (available: {names})")
+                cols = np.asarray([names.index(w) for w in wanted])
+                names = list(wanted)
+            return (_LazyRows(array, t0, t1, cols) if (cols is not None or time is not None) else array), names
+
+        out.inputs, out.channel_in = pick(self.inputs, self.channel_in, channel_in)
+        out.targets, out.channel_out = pick(self.targets, self.channel_out if self.targets is not None else None, channel_out)
+        if self.targets is None:
+            out.channel_out = out.channel_in if channel_out is None else list(channel_out)
+        if channel_c is not None and self.constants is not None:
+            names_c = getattr(self, "channel_c", None)
+            idx = [names_c.index(c) if isinstance(c, str) else int(c) for c in channel_c] if names_c or all(
+                not isinstance(c, str) for c in channel_c) else list(range(len(channel_c)))
+            out.constants = self.constants[idx]
+            out.channel_c = [str(c) for c in channel_c]
+        return out
+
+
+class _LazyRows:
+    """``base[t0:t1][:, cols]`` evaluated per requested time slab (keeps memory-mapped archives on disk)."""
+
+    def __init__(self, base, t0: int, t1: int, cols):
+        self.base, self.t0, self.t1, self.cols = base, t0, t1, cols
+        n_ch = base.shape[1] if cols is None else len(cols)
+        self.shape = (t1 - t0, n_ch) + tuple(base.shape[2:])
+
+    def __len__(self) -> int:
+        return self.shape[0]
+
+    def __getitem__(self, key):
+        if not isinstance(key, slice):
+            raise TypeError("only time slices are supported")
+        start, stop, _ = key.indices(self.shape[0])
+        part = self.base[self.t0 + start:self.t0 + stop]
+        part = np.asarray(getattr(part, "values", part))
+        return part if self.cols is None else part[:, self.cols]
 
 
 class TimeSeriesDataset:

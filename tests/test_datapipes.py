@@ -569,3 +569,63 @@ def test_healpix_coupled_dataset_and_couplers():
     got = const_c.construct_integrated_couplings({"time": slice(5, 20)}, 2)
     assert got.shape == (1, 2, 1, 12, 4, 4)
     assert np.allclose(got[0, 0, 0], store["inputs"][5 + 2, 2])
+
+
+def test_healpix_data_modules(tmp_path):
+    import numpy as np
+
+    from physicsnemo_b200.datapipes.healpix import (ArrayStore, CoupledTimeSeriesDataModule, TimeSeriesDataModule,
+                                                    create_time_series_dataset_classic,
+                                                    open_time_series_dataset_classic_prebuilt)
+
+    src, dst = tmp_path / "src", tmp_path / "dst"
+    src.mkdir()
+    n_t = 60
+    time = np.datetime64("2020-01-01T00") + np.arange(n_t) * np.timedelta64(3, "h")
+    rng = np.random.default_rng(0)
+    fields = {v: (rng.normal(size=(n_t, 12, 4, 4)) + i).astype(np.float32) for i, v in enumerate(("z500", "t2m", "sst"))}
+    for v, a in fields.items():
+        np.save(src / f"era5_{v}.npy", a)
+    np.save(src / "era5_lsm.npy", rng.random((12, 4, 4)).astype(np.float32))
+    np.savez(src / "era5_coords.npz", time=time, lat=rng.random((12, 4, 4)), lon=rng.random((12, 4, 4)))
+    scaling = {v: {"mean": float(i), "std": 2.0} for i, v in enumerate(("z500", "t2m", "sst"))}
+    path = create_time_series_dataset_classic(str(src), str(dst), "ds", ["z500", "t2m", "sst"], ["t2m"], {"lsm": "land_sea_mask"},
+                                              prefix="era5_", scaling=scaling)
+    store = open_time_series_dataset_classic_prebuilt(str(dst), "ds", constants=True)
+    assert store.inputs.shape == (n_t, 3, 12, 4, 4) and store.targets.shape == (n_t, 1, 12, 4, 4) and store.channel_c == ["land_sea_mask"]
+    sub = store.sel(channel_in=["sst", "z500"], time=slice("2020-01-02", "2020-01-03T21"))
+    assert sub.inputs.shape == (16, 2, 12, 4, 4) and sub.time[0] == np.datetime64("2020-01-02T00") and sub.channel_in == ["sst", "z500"]
+    assert np.array_equal(sub.inputs[2:4], np.stack([fields["sst"], fields["z500"]], 1)[10:12])
+    with pytest.raises(KeyError):
+        store.sel(channel_in=["u10"])
+    with pytest.raises(FileNotFoundError):
+        open_time_series_dataset_classic_prebuilt(str(dst), "missing")
+    splits = dict(train_date_start="2020-01-01", train_date_end="2020-01-04T21", val_date_start="2020-01-05",
+                  val_date_end="2020-01-06T21", test_date_start="2020-01-07", test_date_end="2020-01-08T09")
+    dm = TimeSeriesDataModule(str(src), str(dst), "ds", prefix="era5_", batch_size=4, input_variables=["t2m", "z500"],
+                              output_variables=["t2m"], constants={"lsm": "land_sea_mask"}, scaling=scaling, splits=splits,
+                              input_time_dim=2, output_time_dim=2, num_workers=0, shuffle=False)
+    assert os.path.samefile(path, dst / "ds")
+    assert len(dm.train_dataset.ds.time) == 32 and len(dm.val_dataset.ds.time) == 16 and len(dm.test_dataset.ds.time) == 12
+    loader, sampler = dm.train_dataloader()
+    (x, *_), y = next(iter(loader))
+    assert sampler is None and tuple(x.shape[:4]) == (4, 12, 2, 2) and tuple(y.shape[:4]) == (4, 12, 2, 1)
+    want = (fields["t2m"][0] - 1.0) / 2.0                                       # first sample, first input step, scaled
+    assert np.allclose(np.asarray(x)[0, :, 0, 0], want, atol=1e-6)
+    assert dm.get_constants().shape == (12, 1, 4, 4)
+    sharded, s2 = dm.val_dataloader(num_shards=2, shard_id=1)
+    assert s2 is not None and len(list(sharded)) == len(s2)
+    forecast = TimeSeriesDataModule(dataset=store, input_variables=["z500"], output_variables=["t2m"], scaling=scaling, batch_size=2,
+                                    input_time_dim=1, output_time_dim=1, num_workers=0,
+                                    forecast_init_times=[np.datetime64("2020-01-02T00"), np.datetime64("2020-01-03T12")])
+    assert forecast.train_dataset is None and len(forecast.test_dataset) == 2
+    coupled = CoupledTimeSeriesDataModule(dataset=ArrayStore({"inputs": np.stack(list(fields.values()), 1), "time": time,
+                                                              "lat": np.zeros((12, 4, 4)), "lon": np.zeros((12, 4, 4)),
+                                                              "channel_in": np.asarray(["z500", "t2m", "sst"])}),
+                                          input_variables=["t2m"], output_variables=["t2m"], scaling=scaling, splits=splits,
+                                          batch_size=3, input_time_dim=2, output_time_dim=2, num_workers=0,
+                                          couplings=[{"coupler": "ConstantCoupler",
+                                                      "params": {"batch_size": 3, "variables": ["sst"], "input_times": ["6h"]}}])
+    assert coupled._archive_variables() == ["t2m", "sst"] and len(coupled.train_dataset) > 0
+    with pytest.raises(ValueError):
+        TimeSeriesDataModule(dataset=store, data_format="zarr")
