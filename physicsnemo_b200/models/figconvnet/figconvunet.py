@@ -453,6 +453,36 @@ class FIGConvUNet(Module):
             self.vertex_to_point_features = nn.ModuleDict({"mlp": MLP(3 * pos_encode_dim, hidden_channels[0], [])})
             self._vertex_encoding = SinusoidalEncoding(pos_encode_dim, float(aabb_max[0] - aabb_min[0]))
 
+    # ------------------------------------------------------------ checkpoints
+    #: (pattern in the reference's parameter names, replacement here); applied in order to every incoming key
+    _REFERENCE_KEY_RULES = (
+        (r"^point_feature_to_grids\.(\d+)\.0\.", r"point_feature_to_grids.\1."),
+        (r"\.norm(\d)\.feature_transform\.", r".norm\1."),
+        (r"^(down_blocks\.\d+\.\d+\.convs\.\d+\.shortcut)\.conv\.", r"\1."),
+        (r"^grid_pools\.(\d+)\.pools\.", r"grid_pools.\1."),
+        (r"(mlp\.layers\.\d+)\.block\.", r"\1."),
+        (r"^to_point\.conv_list\.(\d+)\.conv\.conv\.", r"to_point.\1.conv."),
+        (r"^projection\.feature_transform\.", "projection."),
+    )
+
+    @classmethod
+    def _from_reference_key(cls, key: str) -> str:
+        import re
+
+        for pattern, repl in cls._REFERENCE_KEY_RULES:
+            key = re.sub(pattern, repl, key)
+        return key
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        """Accept state dicts written by the reference implementation: its parameter names differ from the ones here only
+        by wrapper levels (``.0.``, ``.pools.``, ``.block.``, ``.conv_list.N.conv.``, ``.feature_transform.``), which
+        are renamed before loading.  Keys already in this package's naming pass through unchanged."""
+        for key in [k for k in state_dict if k.startswith(prefix)]:
+            new = prefix + self._from_reference_key(key[len(prefix):])
+            if new != key and new not in state_dict:
+                state_dict[new] = state_dict.pop(key)
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+
     def _grid_forward(self, xyz, feat):
         levels = [[to_grid(xyz, feat) for to_grid in self.point_feature_to_grids]]
         for block in self.down_blocks:

@@ -105,6 +105,28 @@ def main() -> int:
                 print(f"MeshGraphNet: ok ({len(a.state_dict())} tensors, state exchange only)", flush=True)
         except Exception as exc:  # noqa: BLE001
             failures.append(f"MeshGraphNet: {type(exc).__name__}: {exc}")
+        # FIGConvUNet: the reference's forward needs torch_scatter (absent here); its file loads here through the key
+        # renaming of ``FIGConvUNet._load_from_state_dict``, tensor for tensor
+        try:
+            from physicsnemo.models.figconvnet.figconvunet import FIGConvUNet as RefFIG
+
+            from physicsnemo_b200.models.figconvnet import FIGConvUNet as OwnFIG
+
+            cfg = dict(in_channels=8, out_channels=2, kernel_size=3, hidden_channels=[8, 12, 16], num_levels=2, mlp_channels=[32, 32],
+                       resolution_memory_format_pairs=[("b_xc_y_z", (2, 8, 8)), ("b_yc_x_z", (8, 2, 8)), ("b_zc_x_y", (8, 8, 2))])
+            torch.manual_seed(3)
+            a, b = RefFIG(**cfg), OwnFIG(**cfg)
+            fa = os.path.join(tmp, "fig_ref.mdlus")
+            a.save(fa)
+            b.load(fa)
+            mine_sd = b.state_dict()
+            moved = {OwnFIG._from_reference_key(k): v for k, v in a.state_dict().items()}
+            if sorted(moved) != sorted(mine_sd) or not all(torch.equal(v, mine_sd[k]) for k, v in moved.items()):
+                failures.append("FIGConvUNet: tensors differ after loading the reference's file")
+            else:
+                print(f"FIGConvUNet: ok ({len(moved)} tensors, reference file -> this package)", flush=True)
+        except Exception as exc:  # noqa: BLE001
+            failures.append(f"FIGConvUNet: {type(exc).__name__}: {exc}")
     for f in failures:
         print("FAIL", f, flush=True)
     return 1 if failures else 0

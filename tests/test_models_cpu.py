@@ -653,7 +653,7 @@ def test_topodiff_layout_and_forward():
 
 
 def test_mdlus_files_cross_load_with_the_reference():
-    """FNO, AFNO, Transolver, SongUNet (outputs) and MeshGraphNet (tensors): ``.mdlus`` files written by the reference load
+    """FNO, AFNO, Transolver, SongUNet (outputs), MeshGraphNet and FIGConvUNet (tensors): ``.mdlus`` files written by the reference load
     here and the other way round.  Runs in a child process; skipped when the reference is not installed beside the repo."""
     import os
     import subprocess
@@ -666,7 +666,7 @@ def test_mdlus_files_cross_load_with_the_reference():
     proc = subprocess.run([sys.executable, os.path.join(root, "tests", "helpers", "crossload_worker.py")], capture_output=True,
                           text=True, timeout=900, env=env)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
-    assert proc.stdout.count(": ok") == 5, proc.stdout
+    assert proc.stdout.count(": ok") == 6, proc.stdout
 
 
 def test_domino_utils():
