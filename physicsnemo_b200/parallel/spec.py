@@ -99,6 +99,21 @@ class ShardTensorSpec:
         return hash((id(self.mesh), tuple(str(p) for p in self.placements), tuple(self.global_shape), self.dtype,
                      tuple(sorted(self.sharding_sizes.items()))))
 
+    def _stable_hash(self) -> str:
+        """Digest that is equal on every process and in every run for equal layouts (the in-process ``__hash__`` keys on
+        the mesh object's identity).  Covers the mesh's shape, dimension names and device type, the placements, the
+        global shape and dtype, the per-rank shard extents and this rank's local shape, so that an uneven layout and
+        the even chunking of the same global shape do not collide.  Usable as a cache key across processes
+        (reference: ``ShardTensorSpec._stable_hash``, ``_shard_tensor_spec.py:119``)."""
+        import hashlib
+
+        mesh = self.mesh
+        parts = (tuple(mesh.mesh.shape), tuple(mesh.mesh_dim_names or ()), str(mesh.device_type),
+                 tuple(repr(p) for p in self.placements), tuple(int(d) for d in self.global_shape), str(self.dtype),
+                 tuple(sorted((int(k), tuple(int(x) for x in v)) for k, v in self.sharding_sizes.items())),
+                 tuple(int(d) for d in self.local_shape()))
+        return hashlib.sha256(repr(parts).encode()).hexdigest()
+
     def same_layout(self, other: "ShardTensorSpec") -> bool:
         return (self.mesh is other.mesh or self.mesh == other.mesh) and tuple(self.placements) == tuple(other.placements) \
             and self.sharding_sizes == other.sharding_sizes

@@ -372,3 +372,26 @@ def _sharded_natten(rank, world):
 
 def test_sharded_neighbourhood_attention_two_ranks():
     run_ranks(_sharded_natten, world=2)
+
+
+def _spec_hashes(rank, world):
+    from physicsnemo_b200.distributed import DistributedManager
+    from physicsnemo_b200.parallel import Replicate, Shard, ShardTensor
+
+    mesh = DistributedManager().initialize_mesh((world,), ("domain",))
+    even = ShardTensor.from_local(torch.zeros(4, 3), mesh, [Shard(0)])
+    uneven = ShardTensor.from_local(torch.zeros(5 if rank == 0 else 3, 3), mesh, [Shard(0)])
+    again = ShardTensor.from_local(torch.ones(4, 3), mesh, [Shard(0)])
+    repl = ShardTensor.from_local(torch.zeros(8, 3), mesh, [Replicate()])
+    digests = {n: t._spec._stable_hash() for n, t in (("even", even), ("uneven", uneven), ("again", again), ("repl", repl))}
+    assert digests["even"] == digests["again"] and len({digests["even"], digests["uneven"], digests["repl"]}) == 3
+    # equal on every rank for the even layout (same local shape), different for the uneven one (local shapes differ)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, digests)
+    assert gathered[0]["even"] == gathered[1]["even"] and gathered[0]["repl"] == gathered[1]["repl"]
+    assert gathered[0]["uneven"] != gathered[1]["uneven"]
+    assert hash(even._spec) == hash(again._spec)
+
+
+def test_spec_stable_hash_two_ranks():
+    run_ranks(_spec_hashes, world=2)
