@@ -10,7 +10,6 @@ from __future__ import annotations
 
 from contextlib import nullcontext
 from dataclasses import dataclass
-from itertools import chain
 from typing import Callable, Literal, Tuple
 from warnings import warn
 
@@ -40,70 +39,78 @@ class MetaData(ModelMetaData):
     auto_grad: bool = True
 
 
+def _expect_rows(what: str, t: Tensor, width: int) -> None:
+    """``t`` must be a 2-D feature table with ``width`` columns."""
+    if torch.compiler.is_compiling():
+        return
+    if t.ndim != 2 or t.shape[1] != width:
+        raise ValueError(f"Expected tensor of shape (N_{what}, {width}) but got tensor of shape {tuple(t.shape)}")
+
+
 class MeshGraphNetProcessor(nn.Module):
-    """Alternating edge / node blocks with optional activation-checkpoint segments."""
+    """``processor_size`` message-passing steps, each an edge block followed by a node block.
+
+    The ``2 · processor_size`` layers can be cut into equal activation-checkpoint segments
+    (``num_processor_checkpoint_segments``), whose saved tensors may additionally be kept in pinned host memory
+    (``checkpoint_offloading``).
+    """
 
     def __init__(self, processor_size: int = 15, input_dim_node: int = 128, input_dim_edge: int = 128,
                  num_layers_node: int = 2, num_layers_edge: int = 2, aggregation: str = "sum",
                  norm_type: str = "LayerNorm", activation_fn: nn.Module = nn.ReLU(), do_concat_trick: bool = False,
                  num_processor_checkpoint_segments: int = 0, checkpoint_offloading: bool = False):
         super().__init__()
-        self.processor_size = processor_size
+        self.processor_size, self.input_dim_node, self.input_dim_edge = processor_size, input_dim_node, input_dim_edge
         self.num_processor_checkpoint_segments = num_processor_checkpoint_segments
-        self.input_dim_node, self.input_dim_edge = input_dim_node, input_dim_edge
-        self.checkpoint_offloading = checkpoint_offloading if num_processor_checkpoint_segments > 0 else False
-        edge_blocks = [MeshEdgeBlock(input_dim_node, input_dim_edge, input_dim_edge, input_dim_edge, num_layers_edge,
-                                     activation_fn, norm_type, do_concat_trick, False) for _ in range(processor_size)]
-        node_blocks = [MeshNodeBlock(aggregation, input_dim_node, input_dim_edge, input_dim_edge, input_dim_edge,
-                                     num_layers_node, activation_fn, norm_type, False) for _ in range(processor_size)]
-        self.processor_layers = nn.ModuleList(list(chain(*zip(edge_blocks, node_blocks))))
-        self.num_processor_layers = len(self.processor_layers)
+        self.checkpoint_offloading = bool(checkpoint_offloading) and num_processor_checkpoint_segments > 0
+        width = input_dim_edge
+        layers = []
+        for _ in range(processor_size):
+            layers.append(MeshEdgeBlock(input_dim_node, width, width, width, num_layers_edge, activation_fn, norm_type,
+                                        do_concat_trick, False))
+            layers.append(MeshNodeBlock(aggregation, input_dim_node, width, width, width, num_layers_node, activation_fn,
+                                        norm_type, False))
+        self.processor_layers = nn.ModuleList(layers)
+        self.num_processor_layers = 2 * processor_size
         self.set_checkpoint_segments(num_processor_checkpoint_segments)
         self.set_checkpoint_offload_ctx(self.checkpoint_offloading)
 
     def set_checkpoint_offload_ctx(self, enabled: bool) -> None:
+        """Keep the tensors saved inside checkpointed segments on the host (pinned) when ``enabled``."""
         self.checkpoint_offload_ctx = torch.autograd.graph.save_on_cpu(pin_memory=True) if enabled else nullcontext()
 
     def set_checkpoint_segments(self, checkpoint_segments: int) -> None:
-        if checkpoint_segments > 0:
-            if self.num_processor_layers % checkpoint_segments != 0:
-                raise ValueError("Processor layers must be a multiple of checkpoint_segments")
-            size = self.num_processor_layers // checkpoint_segments
-            self.checkpoint_segments = [(i, i + size) for i in range(0, self.num_processor_layers, size)]
-            self.checkpoint_fn = set_checkpoint_fn(True)
-        else:
-            self.checkpoint_fn = set_checkpoint_fn(False)
-            self.checkpoint_segments = [(0, self.num_processor_layers)]
+        """Cut the layer list into ``checkpoint_segments`` equal parts (0: one part, no recomputation)."""
+        n = self.num_processor_layers
+        if checkpoint_segments > 0 and n % checkpoint_segments:
+            raise ValueError("Processor layers must be a multiple of checkpoint_segments")
+        per_part = n // checkpoint_segments if checkpoint_segments > 0 else n
+        self.checkpoint_segments = [(lo, lo + per_part) for lo in range(0, n, max(per_part, 1))] or [(0, 0)]
+        self.checkpoint_fn = set_checkpoint_fn(checkpoint_segments > 0)
 
     _set_checkpoint_segments = set_checkpoint_segments
     _set_checkpoint_offload_ctx = set_checkpoint_offload_ctx
 
     def run_function(self, segment_start: int, segment_end: int) -> Callable:
-        segment = self.processor_layers[segment_start:segment_end]
+        """Callable ``(nodes, edges, graph) → (edges, nodes)`` that applies layers ``[segment_start, segment_end)``."""
+        part = list(self.processor_layers[segment_start:segment_end])
 
-        def custom_forward(node_features: Tensor, edge_features: Tensor, graph) -> Tuple[Tensor, Tensor]:
-            for module in segment:
-                edge_features, node_features = module(edge_features, node_features, graph)
-            return edge_features, node_features
+        def apply(nodes: Tensor, edges: Tensor, graph) -> Tuple[Tensor, Tensor]:
+            for layer in part:
+                edges, nodes = layer(edges, nodes, graph)
+            return edges, nodes
 
-        return custom_forward
+        return apply
 
     def forward(self, node_features: Tensor, edge_features: Tensor, graph) -> Tensor:
-        if not torch.compiler.is_compiling():
-            if node_features.ndim != 2 or node_features.shape[1] != self.input_dim_node:
-                raise ValueError(
-                    f"Expected tensor of shape (N_nodes, {self.input_dim_node}) but got tensor of shape {tuple(node_features.shape)}"
-                )
-            if edge_features.ndim != 2 or edge_features.shape[1] != self.input_dim_edge:
-                raise ValueError(
-                    f"Expected tensor of shape (N_edges, {self.input_dim_edge}) but got tensor of shape {tuple(edge_features.shape)}"
-                )
+        _expect_rows("nodes", node_features, self.input_dim_node)
+        _expect_rows("edges", edge_features, self.input_dim_edge)
+        nodes, edges = node_features, edge_features
         with self.checkpoint_offload_ctx:
-            for start, end in self.checkpoint_segments:
-                edge_features, node_features = self.checkpoint_fn(
-                    self.run_function(start, end), node_features, edge_features, graph,
-                    use_reentrant=False, preserve_rng_state=False)
-        return node_features
+            for lo, hi in self.checkpoint_segments:
+                edges, nodes = self.checkpoint_fn(self.run_function(lo, hi), nodes, edges, graph, use_reentrant=False,
+                                                  preserve_rng_state=False)
+        return nodes
 
 
 class MeshGraphNet(Module):
@@ -119,49 +126,35 @@ class MeshGraphNet(Module):
                  num_processor_checkpoint_segments: int = 0, checkpoint_offloading: bool = False,
                  recompute_activation: bool = False, norm_type: Literal["LayerNorm", "TELayerNorm"] = "LayerNorm"):
         super().__init__(meta=MetaData())
-        self.input_dim_nodes, self.input_dim_edges, self.output_dim = input_dim_nodes, input_dim_edges, output_dim
-        activation_fn = get_activation(mlp_activation_fn)
-        if num_layers_node_encoder is None:
-            raise ValueError("num_layers_node_encoder cannot be None")
-        if num_layers_edge_encoder is None:
-            raise ValueError("num_layers_edge_encoder cannot be None")
-        if num_layers_node_decoder is None:
-            raise ValueError("num_layers_node_decoder cannot be None")
-        if norm_type not in ["LayerNorm", "TELayerNorm"]:
+        depth = {"num_layers_node_encoder": num_layers_node_encoder, "num_layers_edge_encoder": num_layers_edge_encoder,
+                 "num_layers_node_decoder": num_layers_node_decoder}
+        for name, value in depth.items():
+            if value is None:
+                raise ValueError(f"{name} cannot be None")
+        if norm_type not in ("LayerNorm", "TELayerNorm"):
             raise ValueError("Norm type should be either 'LayerNorm' or 'TELayerNorm'")
-        if not torch.cuda.is_available() and norm_type == "TELayerNorm":
+        if norm_type == "TELayerNorm" and not torch.cuda.is_available():
             warn("TELayerNorm is not supported on CPU. Switching to LayerNorm.")
             norm_type = "LayerNorm"
-        self.edge_encoder = MeshGraphMLP(input_dim_edges, output_dim=hidden_dim_processor,
-                                         hidden_dim=hidden_dim_edge_encoder, hidden_layers=num_layers_edge_encoder,
-                                         activation_fn=activation_fn, norm_type=norm_type,
-                                         recompute_activation=recompute_activation)
-        self.node_encoder = MeshGraphMLP(input_dim_nodes, output_dim=hidden_dim_processor,
-                                         hidden_dim=hidden_dim_node_encoder, hidden_layers=num_layers_node_encoder,
-                                         activation_fn=activation_fn, norm_type=norm_type,
-                                         recompute_activation=recompute_activation)
-        self.node_decoder = MeshGraphMLP(hidden_dim_processor, output_dim=output_dim,
-                                         hidden_dim=hidden_dim_node_decoder, hidden_layers=num_layers_node_decoder,
-                                         activation_fn=activation_fn, norm_type=None,
-                                         recompute_activation=recompute_activation)
+        self.input_dim_nodes, self.input_dim_edges, self.output_dim = input_dim_nodes, input_dim_edges, output_dim
+        act = get_activation(mlp_activation_fn)
+        latent = hidden_dim_processor
+
+        def mlp(n_in: int, n_out: int, hidden: int, layers: int, norm) -> MeshGraphMLP:
+            return MeshGraphMLP(n_in, output_dim=n_out, hidden_dim=hidden, hidden_layers=layers, activation_fn=act,
+                                norm_type=norm, recompute_activation=recompute_activation)
+
+        self.edge_encoder = mlp(input_dim_edges, latent, hidden_dim_edge_encoder, num_layers_edge_encoder, norm_type)
+        self.node_encoder = mlp(input_dim_nodes, latent, hidden_dim_node_encoder, num_layers_node_encoder, norm_type)
+        self.node_decoder = mlp(latent, output_dim, hidden_dim_node_decoder, num_layers_node_decoder, None)
         self.processor = MeshGraphNetProcessor(
-            processor_size=processor_size, input_dim_node=hidden_dim_processor, input_dim_edge=hidden_dim_processor,
-            num_layers_node=num_layers_node_processor, num_layers_edge=num_layers_edge_processor,
-            aggregation=aggregation, norm_type=norm_type, activation_fn=activation_fn,
+            processor_size=processor_size, input_dim_node=latent, input_dim_edge=latent, num_layers_node=num_layers_node_processor,
+            num_layers_edge=num_layers_edge_processor, aggregation=aggregation, norm_type=norm_type, activation_fn=act,
             do_concat_trick=do_concat_trick, num_processor_checkpoint_segments=num_processor_checkpoint_segments,
             checkpoint_offloading=checkpoint_offloading)
 
     def forward(self, node_features: Tensor, edge_features: Tensor, graph, **kwargs) -> Tensor:
-        if not torch.compiler.is_compiling():
-            if node_features.ndim != 2 or node_features.shape[1] != self.input_dim_nodes:
-                raise ValueError(
-                    f"Expected tensor of shape (N_nodes, {self.input_dim_nodes}) but got tensor of shape {tuple(node_features.shape)}"
-                )
-            if edge_features.ndim != 2 or edge_features.shape[1] != self.input_dim_edges:
-                raise ValueError(
-                    f"Expected tensor of shape (N_edges, {self.input_dim_edges}) but got tensor of shape {tuple(edge_features.shape)}"
-                )
-        edge_features = self.edge_encoder(edge_features)
-        node_features = self.node_encoder(node_features)
-        x = self.processor(node_features, edge_features, graph)
-        return self.node_decoder(x)
+        _expect_rows("nodes", node_features, self.input_dim_nodes)
+        _expect_rows("edges", edge_features, self.input_dim_edges)
+        latent_nodes = self.processor(self.node_encoder(node_features), self.edge_encoder(edge_features), graph)
+        return self.node_decoder(latent_nodes)
