@@ -21,8 +21,15 @@ from .group_norm import get_group_norm
 from .utils.utils import _validate_amp
 
 
+#: attention parameters of checkpoints written before the attention sub-module existed, and where they live now
+_LEGACY_ATTENTION_KEYS = {f"{old}.{leaf}": f"attn.{new}.{leaf}"
+                          for old, new in (("norm2", "norm"), ("qkv", "qkv"), ("proj", "proj")) for leaf in ("weight", "bias")}
+
+
 class UNetBlock(torch.nn.Module):
-    _reserved_attributes: Set[str] = set(["norm2", "qkv", "proj"])
+    """Residual block conditioned on an embedding, with optional 2× resampling and optional self-attention."""
+
+    _reserved_attributes: Set[str] = {"norm2", "qkv", "proj"}
 
     def __init__(self, in_channels: int, out_channels: int, emb_channels: int, up: bool = False, down: bool = False,
                  attention: bool = False, num_heads: int | None = None, channels_per_head: int = 64,
@@ -32,65 +39,63 @@ class UNetBlock(torch.nn.Module):
                  init_attn: Any = None, use_apex_gn: bool = False, act: str = "silu", fused_conv_bias: bool = False,
                  profile_mode: bool = False, amp_mode: bool = False):
         super().__init__()
-        self.in_channels, self.out_channels, self.emb_channels = in_channels, out_channels, emb_channels
-        self.num_heads = 0 if not attention else (num_heads if num_heads is not None else out_channels // channels_per_head)
-        self.attention, self.dropout, self.skip_scale = attention, dropout, skip_scale
-        self.adaptive_scale, self.profile_mode, self.amp_mode = adaptive_scale, profile_mode, amp_mode
-        self.norm0 = get_group_norm(num_channels=in_channels, eps=eps, use_apex_gn=use_apex_gn, act=act, amp_mode=amp_mode)
-        self.conv0 = Conv2d(in_channels=in_channels, out_channels=out_channels, kernel=3, up=up, down=down,
-                            resample_filter=resample_filter, fused_conv_bias=fused_conv_bias, amp_mode=amp_mode, **init)
-        self.affine = Linear(in_features=emb_channels, out_features=out_channels * (2 if adaptive_scale else 1),
+        for name in ("in_channels", "out_channels", "emb_channels", "attention", "dropout", "skip_scale", "adaptive_scale",
+                     "profile_mode", "amp_mode"):
+            setattr(self, name, locals()[name])
+        heads = num_heads if num_heads is not None else out_channels // channels_per_head
+        self.num_heads = heads if attention else 0
+        norm = dict(eps=eps, use_apex_gn=use_apex_gn, amp_mode=amp_mode)
+        conv = dict(fused_conv_bias=fused_conv_bias, amp_mode=amp_mode)
+        resample = dict(up=up, down=down, resample_filter=resample_filter)
+        # main branch: norm + act, 3×3 (resampling) conv, embedding injection, norm, dropout, zero-initialised 3×3 conv
+        self.norm0 = get_group_norm(num_channels=in_channels, act=act, **norm)
+        self.conv0 = Conv2d(in_channels=in_channels, out_channels=out_channels, kernel=3, **resample, **conv, **init)
+        self.affine = Linear(in_features=emb_channels, out_features=(2 if adaptive_scale else 1) * out_channels,
                              amp_mode=amp_mode, **init)
-        self.norm1 = get_group_norm(num_channels=out_channels, eps=eps, use_apex_gn=use_apex_gn,
-                                    act=None if adaptive_scale else act, amp_mode=amp_mode)
-        self.conv1 = Conv2d(in_channels=out_channels, out_channels=out_channels, kernel=3,
-                            fused_conv_bias=fused_conv_bias, amp_mode=amp_mode, **init_zero)
+        self.norm1 = get_group_norm(num_channels=out_channels, act=act if not adaptive_scale else None, **norm)
+        self.conv1 = Conv2d(in_channels=out_channels, out_channels=out_channels, kernel=3, **conv, **init_zero)
+        # skip branch: identity unless the shape changes; a 1×1 projection when the width changes (or on request)
         self.skip = None
-        if out_channels != in_channels or up or down:
-            kernel = 1 if resample_proj or out_channels != in_channels else 0
-            self.skip = Conv2d(in_channels=in_channels, out_channels=out_channels, kernel=kernel, up=up, down=down,
-                               resample_filter=resample_filter,
-                               fused_conv_bias=fused_conv_bias if kernel != 0 else False, amp_mode=amp_mode, **init)
-        if self.attention:
-            self.attn = Attention(out_channels=out_channels, num_heads=self.num_heads, eps=eps, init_zero=init_zero,
-                                  init_attn=init_attn, init=init, use_apex_gn=use_apex_gn, amp_mode=amp_mode,
-                                  fused_conv_bias=fused_conv_bias)
-        else:
-            self.attn = None
+        if up or down or in_channels != out_channels:
+            project = resample_proj or in_channels != out_channels
+            self.skip = Conv2d(in_channels=in_channels, out_channels=out_channels, kernel=int(project), **resample,
+                               fused_conv_bias=fused_conv_bias and project, amp_mode=amp_mode, **init)
+        self.attn = None
+        if attention:
+            self.attn = Attention(out_channels=out_channels, num_heads=self.num_heads, init=init, init_zero=init_zero,
+                                  init_attn=init_attn, **norm, fused_conv_bias=fused_conv_bias)
         self.register_load_state_dict_pre_hook(self._migrate_attention_module)
 
     def forward(self, x, emb):
-        orig = x
-        x = self.conv0(self.norm0(x))
-        params = self.affine(emb).unsqueeze(2).unsqueeze(3)
+        h = self.conv0(self.norm0(x))
+        cond = self.affine(emb)[:, :, None, None]
         _validate_amp(self.amp_mode)
-        if not self.amp_mode and params.dtype != x.dtype:
-            params = params.to(x.dtype)
+        if cond.dtype != h.dtype and not self.amp_mode:
+            cond = cond.to(h.dtype)
         if self.adaptive_scale:
-            scale, shift = params.chunk(chunks=2, dim=1)
-            x = silu(torch.addcmul(shift, self.norm1(x), scale + 1))
+            scale, shift = cond.chunk(2, dim=1)
+            h = silu(torch.addcmul(shift, self.norm1(h), scale + 1))
         else:
-            x = self.norm1(x + params)
-        x = self.conv1(torch.nn.functional.dropout(x, p=self.dropout, training=self.training))
+            h = self.norm1(h + cond)
+        h = self.conv1(torch.nn.functional.dropout(h, p=self.dropout, training=self.training))
         # residual join and rescaling in one pass (one kernel forward, one shared by both branches backward)
-        x = _resample.add_scale(x, self.skip(orig) if self.skip is not None else orig, self.skip_scale)
-        if self.attn:
-            x = self.attn(x)
-            x = x * self.skip_scale
-        return x
+        h = _resample.add_scale(h, x if self.skip is None else self.skip(x), self.skip_scale)
+        if self.attn is not None:
+            h = self.attn(h) * self.skip_scale
+        return h
 
     def __setattr__(self, name, value):
-        if name in getattr(self.__class__, "_reserved_attributes", set()):
+        if name in type(self)._reserved_attributes:
             raise AttributeError(f"Attribute '{name}' is reserved and cannot be set.")
         super().__setattr__(name, value)
 
     @staticmethod
     def _migrate_attention_module(module, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
                                   error_msgs):
-        for old, new in {"norm2.weight": "attn.norm.weight", "norm2.bias": "attn.norm.bias",
-                         "qkv.weight": "attn.qkv.weight", "qkv.bias": "attn.qkv.bias",
-                         "proj.weight": "attn.proj.weight", "proj.bias": "attn.proj.bias"}.items():
-            if prefix + old in state_dict:
-                if prefix + new in state_dict:
-                    raise ValueError(f"Checkpoint contains both legacy and new keys for {prefix + old}")
-                state_dict[prefix + new] = state_dict.pop(prefix + old)
+        """Move ``norm2 / qkv / proj`` tensors of old checkpoints under ``attn.``; refuse a file that has both."""
+        for old, new in _LEGACY_ATTENTION_KEYS.items():
+            if prefix + old not in state_dict:
+                continue
+            if prefix + new in state_dict:
+                raise ValueError(f"Checkpoint contains both legacy and new keys for {prefix + old}")
+            state_dict[prefix + new] = state_dict.pop(prefix + old)
