@@ -11,7 +11,21 @@ from .._rng import derive_seed
 from ..tensordict import TensorDict
 
 
+def _relocate(value, device: torch.device):
+    """Copy of an attribute on ``device`` when it is device-bound (tensor, dict of tensors, generator); else ``None``."""
+    if isinstance(value, torch.Tensor):
+        return value.to(device)
+    if isinstance(value, torch.Generator):
+        return torch.Generator(device=device).manual_seed(value.initial_seed())
+    if isinstance(value, dict) and value and all(isinstance(v, torch.Tensor) for v in value.values()):
+        return {k: v.to(device) for k, v in value.items()}
+    return None
+
+
 class Transform(ABC):
+    """Base of all sample transforms.  A subclass that draws random numbers keeps its ``torch.Generator`` in
+    ``self._generator`` (``None`` until the pipeline seeds it); that attribute is what marks it as stochastic."""
+
     def __init__(self) -> None:
         self._device: Optional[torch.device] = None
 
@@ -19,47 +33,49 @@ class Transform(ABC):
     def __call__(self, data: TensorDict) -> TensorDict:
         raise NotImplementedError
 
+    # -------------------------------------------------------------- randomness
     @property
     def stochastic(self) -> bool:
-        """Stochastic transforms declare a ``_generator`` attribute (possibly ``None`` until seeded)."""
-        return hasattr(self, "_generator")
+        return "_generator" in self.__dict__ or hasattr(type(self), "_generator")
 
     def set_generator(self, generator: torch.Generator) -> None:
-        if self.stochastic:
-            self._generator = generator
-            self._seed_base = generator.initial_seed()
+        """Adopt the pipeline's generator (no-op for deterministic transforms); its seed anchors the per-epoch reseeding."""
+        if not self.stochastic:
+            return
+        self._generator, self._seed_base = generator, generator.initial_seed()
 
     def set_epoch(self, epoch: int) -> None:
-        if self.stochastic and self._generator is not None:
-            if getattr(self, "_seed_base", None) is None:
-                self._seed_base = self._generator.initial_seed()
-            self._generator.manual_seed(derive_seed(self._seed_base, epoch))
+        """Reseed from ``(base seed, epoch)`` so that an epoch's draws do not depend on how earlier epochs ran."""
+        gen = getattr(self, "_generator", None)
+        if gen is None:
+            return
+        base = getattr(self, "_seed_base", None)
+        if base is None:
+            base = self._seed_base = gen.initial_seed()
+        gen.manual_seed(derive_seed(base, epoch))
 
+    # ------------------------------------------------------------------ device
     def to(self, device: torch.device | str) -> "Transform":
         self._device = torch.device(device)
-        for name, value in list(self.__dict__.items()):
-            if isinstance(value, torch.Tensor):
-                setattr(self, name, value.to(self._device))
-            elif isinstance(value, torch.Generator):
-                g = torch.Generator(device=self._device)
-                g.manual_seed(value.initial_seed())
-                setattr(self, name, g)
-            elif isinstance(value, dict) and value and all(isinstance(v, torch.Tensor) for v in value.values()):
-                setattr(self, name, {k: v.to(self._device) for k, v in value.items()})
+        for name in list(vars(self)):
+            moved = _relocate(getattr(self, name), self._device)
+            if moved is not None:
+                setattr(self, name, moved)
         return self
 
     @property
     def device(self) -> torch.device | None:
         return self._device
 
-    def extra_repr(self) -> str:
-        return ""
-
+    # ------------------------------------------------------------------- state
     def state_dict(self) -> dict[str, Any]:
         return {}
 
     def load_state_dict(self, state_dict: dict[str, Any]) -> None:
         return None
 
+    def extra_repr(self) -> str:
+        return ""
+
     def __repr__(self) -> str:
-        return f"{self.__class__.__name__}({self.extra_repr()})"
+        return f"{type(self).__name__}({self.extra_repr()})"
