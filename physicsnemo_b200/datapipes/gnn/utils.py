@@ -14,7 +14,8 @@ def load_json(file: str | Path) -> dict:
 
 
 def save_json(var: dict, file: str | Path) -> None:
-    """Save a dict of tensors / scalars as JSON."""
+    """Save a dict of tensors / scalars as JSON (the parent directory is created when missing)."""
+    Path(file).parent.mkdir(parents=True, exist_ok=True)
     with open(file, "w") as f:
         json.dump({k: (v.tolist() if hasattr(v, "tolist") else v) for k, v in var.items()}, f)
 
