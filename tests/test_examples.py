@@ -8,7 +8,7 @@ import pytest
 
 ROOT = Path(__file__).resolve().parents[1]
 RECIPES = ["cfd/darcy_fno/train.py", "cfd/transolver_point_cloud/train.py", "generative/edm_songunet/train.py",
-           "cfd/globe_potential_flow/train.py", "cfd/stokes_mgn/train.py"]
+           "cfd/globe_potential_flow/train.py", "cfd/stokes_mgn/train.py", "weather/afno_era5/train.py"]
 
 
 @pytest.mark.parametrize("recipe", RECIPES)
