@@ -66,8 +66,6 @@ extern "C" int pnm_layernorm_bwd_noalloc(const void* dy, const void* x, const fl
   }
   if (rc) return rc;
   // every scratch row [0, grid) was fully written above; the fold reads exactly those rows
-  const int threads = 256;
-  pnm::layernorm_bwd_finalize_kernel<<<(2 * C + threads - 1) / threads, threads, 0, st>>>(scratch, grid, C, dgamma,
-                                                                                         dbeta);
+  pnm::layernorm_bwd_finalize_kernel<<<(2 * C + 31) / 32, 32 * pnm::kLnFoldRows, 0, st>>>(scratch, grid, C, dgamma, dbeta);
   return cudaGetLastError() == cudaSuccess ? 0 : PNM_NOALLOC_E_LAUNCH;
 }

@@ -235,16 +235,29 @@ layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   }
 }
 
-// dgamma[c] = sum_b scratch[b][0][c], dbeta[c] = sum_b scratch[b][1][c]
-static __global__ void layernorm_bwd_finalize_kernel(const float* __restrict__ scratch, int nblocks, int C,
-                                              float* __restrict__ dgamma, float* __restrict__ dbeta) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= 2 * C) return;
-  const int which = i / C, c = i % C;
+// dgamma[c] = sum_b scratch[b][0][c], dbeta[c] = sum_b scratch[b][1][c].  A CTA owns 32 consecutive entries of the
+// 2 C-wide scratch row; its 16 row groups walk the nblocks rows in parallel (coalesced 128-byte reads) and are folded
+// through shared memory, so the dependent chain is nblocks / 16 loads instead of nblocks.
+constexpr int kLnFoldRows = 16;
+static __global__ void __launch_bounds__(32 * kLnFoldRows)
+layernorm_bwd_finalize_kernel(const float* __restrict__ scratch, int nblocks, int C, float* __restrict__ dgamma,
+                              float* __restrict__ dbeta) {
+  __shared__ float part[kLnFoldRows][33];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int i = blockIdx.x * 32 + lane;                       // entry of the [2][C] row
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += scratch[((size_t)b * 2 + which) * C + c];
-  if (which == 0) { if (dgamma) dgamma[c] = s; }
-  else { if (dbeta) dbeta[c] = s; }
+  if (i < 2 * C)
+    for (int b = grp; b < nblocks; b += kLnFoldRows) s += scratch[(size_t)b * 2 * C + i];
+  part[grp][lane] = s;
+  __syncthreads();
+  if (grp == 0 && i < 2 * C) {
+    float t = 0.f;
+#pragma unroll
+    for (int g = 0; g < kLnFoldRows; ++g) t += part[g][lane];
+    const int which = i / C, c = i % C;
+    if (which == 0) { if (dgamma) dgamma[c] = t; }
+    else { if (dbeta) dbeta[c] = t; }
+  }
 }
 
 inline int ln_vec_for(int C) { return (C + 255) / 256; }
@@ -287,8 +300,7 @@ inline int launch_layernorm_bwd(const void* dy, const void* x, const float* gamm
     default: layernorm_bwd_kernel<4><<<grid, kLnWarps * 32, 0, st>>>(DY, X, gamma, mean, rstd, DR, DX, scratch, M, C); break;
   }
   if (cudaGetLastError() != cudaSuccess) return -33;
-  const int threads = 256;
-  layernorm_bwd_finalize_kernel<<<(2 * C + threads - 1) / threads, threads, 0, st>>>(scratch, grid, C, dgamma, dbeta);
+  layernorm_bwd_finalize_kernel<<<(2 * C + 31) / 32, 32 * kLnFoldRows, 0, st>>>(scratch, grid, C, dgamma, dbeta);
   return cudaGetLastError() == cudaSuccess ? 0 : -34;
 }
 

@@ -25,6 +25,7 @@ namespace pnm {
 
 constexpr int kPaS = 64;
 constexpr int kPaMaxD = 64;
+constexpr int kPaTokenThreads = 1024;   // the token kernels are latency-bound chains: 32 warps hide the shared-memory latency
 
 struct PaSrc {
   const float* p[kPeerMaxRanks];  // per rank: base of the partial-sum matrix (peer-mapped for r != rank)
@@ -88,8 +89,9 @@ struct PaSaved {        // per block, fp32, all [H][S][...]
   float* wcomb;         // [Cout][H*S]
 };
 
-// grid H, 256 threads, dynamic shared memory (see pa_tokens_smem_floats)
-__global__ void __launch_bounds__(256)
+// grid H, kPaTokenThreads threads, dynamic shared memory (see pa_fwd_smem).  One CTA per head: the work per head is a
+// chain of dependent 64 x 64 x D products, so the only parallelism to add inside a head is more warps per phase.
+__global__ void __launch_bounds__(kPaTokenThreads)
 pa_tokens_fwd_kernel(PaSrc src, long long norm_off, int ld_tok, const float* __restrict__ Wqkv, const float* __restrict__ Wo,
                      __nv_bfloat16* __restrict__ wcomb16, PaSaved sv, int H, int D, int Cout, float scale, PeerArgs peer, int* err) {
   extern __shared__ float sm[];
@@ -102,11 +104,13 @@ pa_tokens_fwd_kernel(PaSrc src, long long norm_off, int ld_tok, const float* __r
   float* o = v + S * P1;
   float* pr = o + S * P1;          // [S][S+1]
   float* wq = pr + S * (S + 1);    // [3D][D]
+  float* wo_s = wq + 3 * D * D;    // [Cout][D+1]  this head's columns of Wo
   const int h = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
   const int HS = H * S, inner = H * D;
   const bool ok = pa_wait(src, peer, err, &sh_ok);
   const float nanv = __int_as_float(0x7fc00000);
   for (int i = tid; i < 3 * D * D; i += nt) wq[i] = Wqkv[i];
+  for (int i = tid; i < Cout * D; i += nt) wo_s[(i / D) * P1 + (i % D)] = Wo[(size_t)(i / D) * inner + h * D + (i % D)];
   for (int i = tid; i < S * D; i += nt) {
     const int s = i / D, d = i % D;
     const float nrm = ok ? pa_sum(src, norm_off + h * S + s) + 1e-2f : nanv;
@@ -161,16 +165,15 @@ pa_tokens_fwd_kernel(PaSrc src, long long norm_off, int ld_tok, const float* __r
   __syncthreads();
   for (int i = tid; i < Cout * S; i += nt) {
     const int c = i / S, s = i % S;
-    const float* wo = Wo + (size_t)c * inner + h * D;
     float acc = 0.f;
-    for (int d = 0; d < D; ++d) acc += wo[d] * o[s * P1 + d];
+    for (int d = 0; d < D; ++d) acc += wo_s[c * P1 + d] * o[s * P1 + d];
     wcomb16[(size_t)c * HS + h * S + s] = __float2bfloat16(acc);
     sv.wcomb[(size_t)c * HS + h * S + s] = acc;
   }
 }
 
-// grid H, 256 threads, dynamic shared memory
-__global__ void __launch_bounds__(256)
+// grid H, kPaTokenThreads threads, dynamic shared memory
+__global__ void __launch_bounds__(kPaTokenThreads)
 pa_tokens_bwd_kernel(PaSrc src, const float* __restrict__ Wqkv, const float* __restrict__ Wo, PaSaved sv,
                      float* __restrict__ dWo, float* __restrict__ dWqkv, float* __restrict__ d_norm,
                      __nv_bfloat16* __restrict__ Bcat, __nv_bfloat16* __restrict__ BdT, int H, int D, int Cout, float scale,
@@ -191,6 +194,7 @@ pa_tokens_bwd_kernel(PaSrc src, const float* __restrict__ Wqkv, const float* __r
   float* ds = pr + S * SP;         // [S][S+1]
   float* wq = ds + S * SP;         // [3D][D]
   float* rowdot = wq + 3 * D * D;  // [S]
+  float* wo_s = rowdot + S;        // [Cout][D+1]  this head's columns of Wo
   const int h = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
   const int HS = H * S, inner = H * D;
   const bool ok = pa_wait(src, peer, err, &sh_ok);
@@ -200,10 +204,12 @@ pa_tokens_bwd_kernel(PaSrc src, const float* __restrict__ Wqkv, const float* __r
     dwc[c * SP + s] = ok ? pa_sum(src, (long long)c * HS + h * S + s) : nanv;
   }
   for (int i = tid; i < 3 * D * D; i += nt) wq[i] = Wqkv[i];
+  for (int i = tid; i < Cout * D; i += nt) wo_s[(i / D) * P1 + (i % D)] = Wo[(size_t)(i / D) * inner + h * D + (i % D)];
   for (int i = tid; i < S * D; i += nt) {
     const int s = i / D, d = i % D;
     const size_t g = (size_t)(h * S + s) * D + d;
     q[s * P1 + d] = sv.q[g]; k[s * P1 + d] = sv.k[g]; v[s * P1 + d] = sv.v[g]; tok[s * P1 + d] = sv.token[g];
+    dq[s * P1 + d] = sv.out[g];          // dq holds the attention output until the attention backward overwrites it
   }
   for (int i = tid; i < S * S; i += nt) pr[(i / S) * SP + (i % S)] = sv.prob[(size_t)h * S * S + i];
   __syncthreads();
@@ -211,16 +217,18 @@ pa_tokens_bwd_kernel(PaSrc src, const float* __restrict__ Wqkv, const float* __r
   for (int i = tid; i < S * D; i += nt) {
     const int s = i / D, d = i % D;
     float acc = 0.f;
-    for (int c = 0; c < Cout; ++c) acc += dwc[c * SP + s] * Wo[(size_t)c * inner + h * D + d];
+    for (int c = 0; c < Cout; ++c) acc += dwc[c * SP + s] * wo_s[c * P1 + d];
     dout[s * P1 + d] = acc;
   }
   for (int i = tid; i < Cout * D; i += nt) {
     const int c = i / D, d = i % D;
     float acc = 0.f;
-    for (int s = 0; s < S; ++s) acc += dwc[c * SP + s] * sv.out[(size_t)(h * S + s) * D + d];
+    for (int s = 0; s < S; ++s) acc += dwc[c * SP + s] * dq[s * P1 + d];
     dWo[(size_t)c * inner + h * D + d] = acc * share;
   }
   __syncthreads();
+  // dWcomb is consumed: its buffer now stages this head's Wcomb^T tile for the coalesced Bcat rows written at the end
+  for (int i = tid; i < Cout * S; i += nt) dwc[(i / S) * SP + (i % S)] = sv.wcomb[(size_t)(i / S) * HS + h * S + (i % S)];
   // dP = dout v^T ; dv = P^T dout
   for (int i = tid; i < S * S; i += nt) {
     const int s = i / S, t = i % S;
@@ -286,7 +294,7 @@ pa_tokens_bwd_kernel(PaSrc src, const float* __restrict__ Wqkv, const float* __r
   for (int i = tid; i < S * ldc; i += nt) {
     const int s = i / ldc, col = i % ldc;
     float val;
-    if (col < Cout) val = sv.wcomb[(size_t)col * HS + h * S + s];
+    if (col < Cout) val = dwc[col * SP + s];
     else {
       const int jd = col - Cout;
       val = (jd / D == h) ? dout[s * P1 + (jd % D)] * rowdot[s] : 0.f;
@@ -301,13 +309,12 @@ pa_tokens_bwd_kernel(PaSrc src, const float* __restrict__ Wqkv, const float* __r
   }
 }
 
-// grid inner + S + 1, 256 threads
+// grid inner + S * D / 8 + 1, 256 threads
 __global__ void __launch_bounds__(256)
 pa_prepare_bwd_kernel(const float* __restrict__ dWc, const float* __restrict__ dbc, const float* __restrict__ grp,
                       const float* __restrict__ Wx, const float* __restrict__ bx, const float* __restrict__ Ws,
                       const float* __restrict__ temp, float* __restrict__ dWx, float* __restrict__ dbx,
                       float* __restrict__ dWs, float* __restrict__ dbs, float* __restrict__ dtemp, int H, int D, int C) {
-  __shared__ float red[256];
   const int S = kPaS, inner = H * D;
   const int b = blockIdx.x, tid = threadIdx.x;
   if (b < inner) {
@@ -322,31 +329,26 @@ pa_prepare_bwd_kernel(const float* __restrict__ dWc, const float* __restrict__ d
       for (int s = 0; s < S; ++s) acc += Ws[s * D + d] * dbc[h * S + s];
       dbx[b] = acc;
     }
-  } else if (b < inner + S) {
-    const int s = b - inner;
-    // dWs[s][d] = sum_h ( sum_c dWc[h S + s][c] Wx[h D + d][c] + dbc[h S + s] bx[h D + d] ): threads = (part, d)
-    const int parts = blockDim.x / D;
-    const int d = tid % D, part = tid / D;
+  } else if (b < inner + (S * D) / 8) {
+    // dWs[s][d] = sum_h ( sum_c dWc[h S + s][c] Wx[h D + d][c] + dbc[h S + s] bx[h D + d] ): one warp per (s, d), lanes over c
+    const int warp = tid >> 5, lane = tid & 31;
+    const int e = (b - inner) * 8 + warp;
+    const int s = e / D, d = e % D;
     float acc = 0.f;
-    if (part < parts) {
+    for (int h = 0; h < H; ++h) {
+      const float* a = dWc + (size_t)(h * S + s) * C;
+      const float* w = Wx + (size_t)(h * D + d) * C;
+      for (int c = lane; c < C; c += 32) acc += a[c] * w[c];
+    }
+    for (int x = 16; x > 0; x >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, x);
+    if (lane == 0) {
+      float t = acc, bsum = 0.f;
       for (int h = 0; h < H; ++h) {
-        const float* a = dWc + (size_t)(h * S + s) * C;
-        const float* w = Wx + (size_t)(h * D + d) * C;
-        for (int c = part; c < C; c += parts) acc += a[c] * w[c];
+        t += dbc[h * S + s] * bx[h * D + d];
+        bsum += dbc[h * S + s];
       }
-    }
-    red[tid] = acc;
-    __syncthreads();
-    if (tid < D) {
-      float t = 0.f;
-      for (int p = 0; p < parts; ++p) t += red[p * D + tid];
-      for (int h = 0; h < H; ++h) t += dbc[h * S + s] * bx[h * D + tid];
-      dWs[s * D + tid] = t;
-    }
-    if (tid == 0) {
-      float t = 0.f;
-      for (int h = 0; h < H; ++h) t += dbc[h * S + s];
-      dbs[s] = t;
+      dWs[s * D + d] = t;
+      if (d == 0) dbs[s] = bsum;
     }
   } else {
     for (int h = tid; h < H; h += blockDim.x) {
@@ -356,9 +358,12 @@ pa_prepare_bwd_kernel(const float* __restrict__ dWc, const float* __restrict__ d
   }
 }
 
-static size_t pa_fwd_smem(int D) { return sizeof(float) * (5 * kPaS * (D + 1) + kPaS * (kPaS + 1) + 3 * D * D); }
+static size_t pa_fwd_smem(int D, int Cout) {
+  return sizeof(float) * (5 * kPaS * (D + 1) + kPaS * (kPaS + 1) + 3 * D * D + (size_t)Cout * (D + 1));
+}
 static size_t pa_bwd_smem(int D, int Cout) {
-  return sizeof(float) * ((size_t)Cout * (kPaS + 1) + 9 * kPaS * (D + 1) + 2 * kPaS * (kPaS + 1) + 3 * D * D + kPaS);
+  return sizeof(float) * ((size_t)Cout * (kPaS + 1) + 9 * kPaS * (D + 1) + 2 * kPaS * (kPaS + 1) + 3 * D * D + kPaS +
+                          (size_t)Cout * (D + 1));
 }
 
 static PaSrc make_src(const void* const* srcs, int world, int use_flags) {
@@ -398,7 +403,7 @@ int pnm_pa_tokens_fwd(const void* const* srcs, int world, int use_flags, long lo
   if (H <= 0 || D <= 0 || D > pnm::kPaMaxD || Cout <= 0 || world < 1 || world > pnm::kPeerMaxRanks) return -2;
   int* err = pnm::error_word_ptr();
   if (!err) return -1;
-  const size_t smem = pnm::pa_fwd_smem(D);
+  const size_t smem = pnm::pa_fwd_smem(D, Cout);
   static unsigned long long mask = 0;
   if (pnm::first_use_on_device(mask) &&
       cudaFuncSetAttribute(pnm::pa_tokens_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
@@ -406,7 +411,7 @@ int pnm_pa_tokens_fwd(const void* const* srcs, int world, int use_flags, long lo
   if (smem > 160 * 1024) return -2;
   pnm::PeerArgs p{};
   if (use_flags) p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, budget_s, epoch_base);
-  pnm::pa_tokens_fwd_kernel<<<H, 256, smem, (cudaStream_t)stream>>>(pnm::make_src(srcs, world, use_flags), norm_off, ld_tok, Wqkv,
+  pnm::pa_tokens_fwd_kernel<<<H, pnm::kPaTokenThreads, smem, (cudaStream_t)stream>>>(pnm::make_src(srcs, world, use_flags), norm_off, ld_tok, Wqkv,
                                                                    Wo, (__nv_bfloat16*)wcomb16, pnm::make_saved(saved), H, D,
                                                                    Cout, scale, p, err);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
@@ -421,14 +426,14 @@ int pnm_pa_tokens_bwd(const void* const* srcs, int world, int use_flags, const f
   int* err = pnm::error_word_ptr();
   if (!err) return -1;
   const size_t smem = pnm::pa_bwd_smem(D, Cout);
-  if (smem > 200 * 1024) return -2;
+  if (smem > 226 * 1024) return -2;
   static unsigned long long mask = 0;
   if (pnm::first_use_on_device(mask) &&
-      cudaFuncSetAttribute(pnm::pa_tokens_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+      cudaFuncSetAttribute(pnm::pa_tokens_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024) != cudaSuccess)
     return -4;
   pnm::PeerArgs p{};
   if (use_flags) p = pnm::make_peer_args(bases, rank, world, epoch, capacity_floats, budget_s, epoch_base);
-  pnm::pa_tokens_bwd_kernel<<<H, 256, smem, (cudaStream_t)stream>>>(pnm::make_src(srcs, world, use_flags), Wqkv, Wo,
+  pnm::pa_tokens_bwd_kernel<<<H, pnm::kPaTokenThreads, smem, (cudaStream_t)stream>>>(pnm::make_src(srcs, world, use_flags), Wqkv, Wo,
                                                                    pnm::make_saved(saved), dWo, dWqkv, d_norm,
                                                                    (__nv_bfloat16*)Bcat16, (__nv_bfloat16*)BdT16, H, D, Cout,
                                                                    scale, share, p, err);
@@ -438,8 +443,8 @@ int pnm_pa_tokens_bwd(const void* const* srcs, int world, int use_flags, const f
 int pnm_pa_prepare_bwd(const float* dWc, const float* dbc, const float* grp, const float* Wx, const float* bx, const float* Ws,
                        const float* temp, float* dWx, float* dbx, float* dWs, float* dbs, float* dtemp, int H, int D, int C,
                        void* stream) {
-  if (H <= 0 || D <= 0 || D > pnm::kPaMaxD || C <= 0 || 256 % D) return -2;
-  pnm::pa_prepare_bwd_kernel<<<H * D + pnm::kPaS + 1, 256, 0, (cudaStream_t)stream>>>(dWc, dbc, grp, Wx, bx, Ws, temp, dWx, dbx,
+  if (H <= 0 || D <= 0 || D > pnm::kPaMaxD || C <= 0) return -2;
+  pnm::pa_prepare_bwd_kernel<<<H * D + (pnm::kPaS * D) / 8 + 1, 256, 0, (cudaStream_t)stream>>>(dWc, dbc, grp, Wx, bx, Ws, temp, dWx, dbx,
                                                                                       dWs, dbs, dtemp, H, D, C);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
