@@ -103,13 +103,13 @@ pa_tokens_fwd_kernel(PaSrc src, long long norm_off, int ld_tok, const float* __r
   float* v = k + S * P1;
   float* o = v + S * P1;
   float* pr = o + S * P1;          // [S][S+1]
-  float* wq = pr + S * (S + 1);    // [3D][D]
-  float* wo_s = wq + 3 * D * D;    // [Cout][D+1]  this head's columns of Wo
+  float* wq = pr + S * (S + 1);    // [3D][D+1]  padded rows: the q k v product reads one row per lane
+  float* wo_s = wq + 3 * D * P1;   // [Cout][D+1]  this head's columns of Wo
   const int h = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
   const int HS = H * S, inner = H * D;
   const bool ok = pa_wait(src, peer, err, &sh_ok);
   const float nanv = __int_as_float(0x7fc00000);
-  for (int i = tid; i < 3 * D * D; i += nt) wq[i] = Wqkv[i];
+  for (int i = tid; i < 3 * D * D; i += nt) wq[(i / D) * P1 + (i % D)] = Wqkv[i];
   for (int i = tid; i < Cout * D; i += nt) wo_s[(i / D) * P1 + (i % D)] = Wo[(size_t)(i / D) * inner + h * D + (i % D)];
   for (int i = tid; i < S * D; i += nt) {
     const int s = i / D, d = i % D;
@@ -124,7 +124,7 @@ pa_tokens_fwd_kernel(PaSrc src, long long norm_off, int ld_tok, const float* __r
   for (int i = tid; i < S * 3 * D; i += nt) {
     const int s = i / (3 * D), j = i % (3 * D);
     float acc = 0.f;
-    for (int d = 0; d < D; ++d) acc += tok[s * P1 + d] * wq[j * D + d];
+    for (int d = 0; d < D; ++d) acc += tok[s * P1 + d] * wq[j * P1 + d];
     float* dst = j < D ? q : (j < 2 * D ? k : v);
     float* gsv = j < D ? sv.q : (j < 2 * D ? sv.k : sv.v);
     dst[s * P1 + (j % D)] = acc;
@@ -359,7 +359,7 @@ pa_prepare_bwd_kernel(const float* __restrict__ dWc, const float* __restrict__ d
 }
 
 static size_t pa_fwd_smem(int D, int Cout) {
-  return sizeof(float) * (5 * kPaS * (D + 1) + kPaS * (kPaS + 1) + 3 * D * D + (size_t)Cout * (D + 1));
+  return sizeof(float) * (5 * kPaS * (D + 1) + kPaS * (kPaS + 1) + 3 * D * (D + 1) + (size_t)Cout * (D + 1));
 }
 static size_t pa_bwd_smem(int D, int Cout) {
   return sizeof(float) * ((size_t)Cout * (kPaS + 1) + 9 * kPaS * (D + 1) + 2 * kPaS * (kPaS + 1) + 3 * D * D + kPaS +
