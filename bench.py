@@ -68,6 +68,9 @@ def main():
     ap.add_argument("--config", default=None, choices=["transolver", "songunet", "mgn", "afno", "fno"])
     ap.add_argument("--no-extras", action="store_true", help="only the headline configuration")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
+    ap.add_argument("--points", type=int, default=None,
+                    help="Transolver configuration only: number of points (default 1 M, the headline size); smaller values "
+                         "measure the per-GPU work of an N-way shard on one GPU")
     ap.add_argument("--micro-batch", type=int, default=None,
                     help="images per micro-step of the SongUNet configuration (default: one image-equivalent of rows per GPU)")
     args = ap.parse_args()

@@ -40,6 +40,9 @@ def run(args, rank: int, world: int, dev) -> dict:
     from ..parallel.point_parallel import PointParallel
     from ..utils.capture import GraphedStep
 
+    global N_POINTS
+    if getattr(args, "points", None):                  # diagnosis runs only: the headline size is the module default
+        N_POINTS = int(args.points)
     torch.manual_seed(1234)
     model = Transolver(**CFG).to(dev)
     pp = PointParallel(model) if world > 1 else None
