@@ -282,7 +282,8 @@ afno_rows_r2c_v2_kernel(TokenPtrs tok, float2* __restrict__ Y, AfGeom g, int kwe
 
 __global__ void __launch_bounds__(512)
 afno_rows_c2r_v2_kernel(const float2* __restrict__ X, TokenPtrs tok, AfGeom g, int kweight, PeerArgs peer, int signal,
-                        unsigned int* counter, int groups, int passes) {
+                        unsigned int* counter, int groups, int passes, const __nv_bfloat16* __restrict__ add0,
+                        const __nv_bfloat16* __restrict__ add1) {
   extern __shared__ float sm[];
   const int Wh = g.W >> 1, CP = g.Cb >> 1;
   const int pad = passes * groups * kRowNK;                       // >= W/2 + 1 positions w = 0 .. W/2
@@ -342,7 +343,22 @@ afno_rows_c2r_v2_kernel(const float2* __restrict__ X, TokenPtrs tok, AfGeom g, i
   const int vec = g.Cb >> 3;
   for (int i = tid; i < g.W * vec; i += nt) {
     const int w = i / vec, v = i % vec;
-    const uint4 u = *reinterpret_cast<const uint4*>(ys + w * g.Cb + v * 8);
+    uint4 u = *reinterpret_cast<const uint4*>(ys + w * g.Cb + v * 8);
+    if (add0) {
+      // residual terms of the surrounding block (local [T, C] token layout), summed in fp32 and rounded once
+      const long long at = ((long long)row * g.W + w) * g.C + c0 + v * 8;
+      float f[8], a[8];
+      sm_unpack8(u, f);
+      sm_unpack8(*reinterpret_cast<const uint4*>(add0 + at), a);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) f[q] += a[q];
+      if (add1) {
+        sm_unpack8(*reinterpret_cast<const uint4*>(add1 + at), a);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) f[q] += a[q];
+      }
+      u = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+    }
     *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(token_addr(tok, g, (long long)row * g.W + w, c0 + v * 8))) = u;
   }
   if (signal) {
@@ -832,7 +848,8 @@ int pnm_afno_rows_c2r(const void* X, const void* const* tokens, const int* geom,
       static unsigned long long mask2 = 0;
       if (int rc = pnm::af_smem_attr(pnm::afno_rows_c2r_v2_kernel, smem2, mask2)) return rc;
       pnm::afno_rows_c2r_v2_kernel<<<dim3(g.B * g.H, g.nblk), rp.threads, smem2, (cudaStream_t)stream>>>(
-          (const float2*)X, pnm::make_tok(tokens), g, kweight, p, signal, (unsigned int*)counter, rp.groups, rp.passes);
+          (const float2*)X, pnm::make_tok(tokens), g, kweight, p, signal, (unsigned int*)counter, rp.groups, rp.passes, nullptr,
+          nullptr);
       return cudaGetLastError() == cudaSuccess ? 0 : -3;
     }
   }
@@ -842,6 +859,25 @@ int pnm_afno_rows_c2r(const void* X, const void* const* tokens, const int* geom,
   pnm::afno_rows_c2r_kernel<<<dim3(g.B * g.H, g.nblk), 2 * g.Cb, smem, (cudaStream_t)stream>>>((const float2*)X, pnm::make_tok(tokens),
                                                                                               g, kweight, p, signal,
                                                                                               (unsigned int*)counter);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Single-GPU form of pnm_afno_rows_c2r that also adds up to two residual tensors (add0, add1: [T, C] bf16, add1 may be
+// null) to the transformed tokens before the store.  -2 when the shape needs the fallback row kernel (no addends there).
+int pnm_afno_rows_c2r_add(const void* X, void* out, const void* add0, const void* add1, const int* geom, long long Tp, int kweight,
+                          void* stream) {
+  pnm::AfGeom g{geom[0], geom[1], geom[2], geom[3], geom[4], geom[5], geom[6], geom[7], Tp, geom[8], geom[9]};
+  if (pnm::af_check(g) || !out || !add0) return -2;
+  if (g.W % 2 || g.W < 4) return -2;
+  const pnm::RowPlan rp = pnm::row_plan(g.W / 2 + 1, g.Cb);
+  const size_t smem2 = sizeof(float2) * ((size_t)g.KX * g.Cb + (size_t)g.KX * rp.pad) + sizeof(__nv_bfloat16) * (size_t)g.W * g.Cb;
+  if (smem2 > 220 * 1024) return -2;
+  static unsigned long long mask2 = 0;
+  if (int rc = pnm::af_smem_attr(pnm::afno_rows_c2r_v2_kernel, smem2, mask2)) return rc;
+  const void* ptrs[8] = {out, out, out, out, out, out, out, out};
+  pnm::afno_rows_c2r_v2_kernel<<<dim3(g.B * g.H, g.nblk), rp.threads, smem2, (cudaStream_t)stream>>>(
+      (const float2*)X, pnm::make_tok(ptrs), g, kweight, pnm::PeerArgs{}, 0, nullptr, rp.groups, rp.passes,
+      (const __nv_bfloat16*)add0, (const __nv_bfloat16*)add1);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -266,10 +266,24 @@ int pnm_afno_rows_c2r(const void* X, const void* const* tokens, const int* geom,
 int pnm_afno_cols_fwd(const void* Y, void* Yout, void* Zs, void* O1s, void* O2s, const float* w1, const float* b1, const float* w2, const float* b2, int nb, const int* geom, float lambda, void* stream);
 int pnm_afno_cols_bwd(const void* dYout, void* dY, const void* Zs, const void* O1s, const void* O2s, const float* w1, const float* w2, float* dw1, float* db1, float* dw2, float* db2, int nb, const int* geom, void* stream);
 int pnm_afno_cols_dft(const void* Y, void* E, const void* mask, const int* geom, int Mp, float lambda, void* stream);
+int pnm_afno_rows_c2r_add(const void* X, void* out, const void* add0, const void* add1, const int* geom, long long Tp, int kweight,
+                          void* stream);
 int pnm_afno_cols_idft(const void* E, void* Yout, const int* geom, int Mp, float lambda, void* stream);
 
 // out = (a + b) * scale over n bf16 elements (n % 8 == 0; b may be null)
 int pnm_add_scale_bf16(const void* a, const void* b, void* out, long long n, float scale, void* stream);
+
+// Tokens [B, h, w, p0 * p1 * C] (features ordered (i, j, c)) <-> image [B, C, h * p0, w * p1], bf16.  to_image = 1 writes
+// the image from the tokens, 0 writes the tokens from the image.  Returns -2 for shapes the kernel does not cover.
+int pnm_unpatchify_bf16(void* tokens, void* image, int B, int h, int w, int p0, int p1, int C, int to_image, void* stream);
+
+// out[0] = scale * sum((pred - tgt)^2) over n elements; dtype codes 0 = fp32, 1 = bf16; partial holds
+// pnm_sq_err_partials() floats.  pnm_sq_err_grad writes grad = coef * gout[0] * (pred - tgt) in pred's dtype.
+int pnm_sq_err_partials(void);
+int pnm_sq_err_sum(const void* pred, const void* tgt, long long n, int pred_dtype, int tgt_dtype, double scale, float* partial,
+                   float* out, void* stream);
+int pnm_sq_err_grad(const void* pred, const void* tgt, const float* gout, long long n, int pred_dtype, int tgt_dtype, float coef,
+                    void* grad, void* stream);
 
 // Metadata features of observations (see obs_features.cu): out [n, 28] (extended = 0) or [n, 30] (extended = 1), fp32.
 // lat is read only in the extended scheme; time_ns / target_s are int64 nanoseconds / seconds since the epoch.

@@ -161,7 +161,7 @@ def run(args, rank: int, world: int, dev) -> dict:
 
         def fwd_loss(tin, tgt):
             out = runner(tin)
-            return ((out.float() - tgt) ** 2).sum() / denom
+            return ops.squared_error(out, tgt, scale=1.0 / denom)
     else:
         runner = None
         host = [x.pin_memory(), y.pin_memory()]
@@ -169,7 +169,7 @@ def run(args, rank: int, world: int, dev) -> dict:
         def fwd_loss(xb, yb):
             with torch.autocast("cuda", dtype=torch.bfloat16):
                 out = model(xb)
-            return ((out.float() - yb) ** 2).sum() / denom
+            return ops.squared_error(out, yb, scale=1.0 / denom)
     del x, y
     dev_in = [t.to(dev, non_blocking=True) for t in host]
     torch.cuda.synchronize()

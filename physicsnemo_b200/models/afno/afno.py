@@ -40,11 +40,30 @@ class Block(nn.Module):
         self.mlp = AFNOMlp(embed_dim, hidden, embed_dim, activation_fn=activation_fn, drop=drop)
 
     def forward(self, x: Tensor) -> Tensor:
+        if self._fused_residuals(x):
+            return self._forward_fused(x)
         mixed = self.filter(self.norm1(x))
         skip = x
         if self.double_skip:
             mixed = skip = mixed + x
         return self.mlp(self.norm2(mixed), residual=skip)
+
+    def _fused_residuals(self, x: Tensor) -> bool:
+        return (type(x) is torch.Tensor and x.is_cuda and x.dtype == torch.bfloat16 and type(self.norm1) is LayerNorm
+                and type(self.norm2) is LayerNorm and type(self.filter) is AFNO2DLayer and ops.fused_path_enabled(x))
+
+    def _forward_fused(self, x: Tensor) -> Tensor:
+        """Same block with no separate elementwise kernels: each LayerNorm hands its input on as the skip tensor (the
+        LayerNorm backward then sums the two gradient paths), the filter adds its own residual and the skip while it
+        stores its result, the MLP adds its residual in its last GEMM."""
+        n1, x_skip = ops.layer_norm(x, self.norm1.weight, self.norm1.bias, self.norm1.eps, return_residual=True)
+        if self.double_skip:
+            mixed = self.filter(n1, residual=x_skip)
+            n2, skip = ops.layer_norm(mixed, self.norm2.weight, self.norm2.bias, self.norm2.eps, return_residual=True)
+        else:
+            mixed = self.filter(n1)
+            n2, skip = ops.layer_norm(mixed, self.norm2.weight, self.norm2.bias, self.norm2.eps), x_skip
+        return self.mlp(n2, residual=skip)
 
 
 @dataclass
@@ -114,7 +133,5 @@ class AFNO(Module):
                 raise ValueError(f"AFNO was built for inputs [B, {wanted[0]}, {wanted[1]}, {wanted[2]}]; got {tuple(x.shape)}")
         tokens = ops.linear(self._forward_features(x), self.head.weight, None)           # [B, h, w, p0 * p1 * C_out]
         p0, p1 = self.patch_size
-        B = tokens.shape[0]
         # un-patchify: the head's features are ordered (p0, p1, channel)
-        image = tokens.reshape(B, self.h, self.w, p0, p1, self.out_chans).permute(0, 5, 1, 3, 2, 4)
-        return image.reshape(B, self.out_chans, self.h * p0, self.w * p1)
+        return ops.unpatchify(tokens, self.h, self.w, p0, p1, self.out_chans)

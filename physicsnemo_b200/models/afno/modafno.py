@@ -16,6 +16,7 @@ import torch
 import torch.nn as nn
 from torch import Tensor
 
+from ... import ops
 from ...core.meta import ModelMetaData
 from ...core.module import Module
 from ...nn.module.afno_layers import AFNO2DLayer, AFNOMlp, AFNOPatchEmbed, ModAFNO2DLayer, ModAFNOMlp
@@ -137,5 +138,4 @@ class ModAFNO(Module):
                 raise ValueError(f"ModAFNO takes (B, {want[0]}, {want[1]}, {want[2]}) inputs, received {tuple(x.shape)}")
         y = self.head(self._forward_features(x, mod))
         p0, p1 = self.patch_size
-        y = y.view(*y.shape[:-1], p0, p1, -1).permute(0, 5, 1, 3, 2, 4)
-        return y.reshape(y.shape[0], y.shape[1], self.inp_shape[0], self.inp_shape[1])
+        return ops.unpatchify(y, self.h, self.w, p0, p1, y.shape[-1] // (p0 * p1))

@@ -75,10 +75,14 @@ class AFNO2DLayer(nn.Module):
         o1r, o1i = F.relu(o1r), F.relu(o1i)
         return _block_cmul(o1r, o1i, self.w2, self.b2)
 
-    def forward(self, x: Tensor) -> Tensor:
+    def forward(self, x: Tensor, residual: Tensor | None = None) -> Tensor:
+        """``filter(x) + x`` (``+ residual`` when given: the skip connection of the surrounding block)."""
         if not torch.compiler.is_compiling():
             if x.ndim != 4:
                 raise ValueError(f"Expected 4D input (B, H, W, C), got {x.ndim}D tensor with shape {tuple(x.shape)}")
+        if residual is not None and not (type(x) is torch.Tensor and x.is_cuda and x.dtype == torch.bfloat16
+                                         and residual.dtype == torch.bfloat16 and residual.shape == x.shape):
+            return self.forward(x) + residual
         bias = x
         dtype = x.dtype
         B, H, W, C = x.shape
@@ -90,9 +94,16 @@ class AFNO2DLayer(nn.Module):
 
             geo = _af.FilterGeometry(B, H, W, C, self.num_blocks, H // 2 + 1)
             if geo.supported():
+                if dtype == torch.bfloat16:
+                    # the layer's residual (and the block's skip) are added in the store of the inverse transform
+                    y = _af.afno_filter(x.reshape(-1, C), self.w1, self.b1, self.w2, self.b2, geo, self.sparsity_threshold,
+                                        add_input=True, residual=None if residual is None else residual.reshape(-1, C))
+                    return y.reshape(B, H, W, C)
                 y = _af.afno_filter(x.reshape(-1, C).to(torch.bfloat16), self.w1, self.b1, self.w2, self.b2, geo,
                                     self.sparsity_threshold)
                 return y.reshape(B, H, W, C).to(dtype) + bias
+        if residual is not None:
+            return self.forward(x) + residual
         x = x.float()
         xf = fft.rfft2(x, dim=(1, 2), norm="ortho")
         Wf = W // 2 + 1

@@ -7,6 +7,7 @@ from .gemm import (
 )
 from .norm import layer_norm
 from .graph import SegmentIndex, gather_rows, segment_reduce
+from .patch_loss import squared_error, unpatchify
 
 
 def library_available() -> bool:

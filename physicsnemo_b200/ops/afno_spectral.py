@@ -27,11 +27,12 @@ def _lib_af():
         vp, i, u, ll, f, d = c.c_void_p, c.c_int, c.c_uint, c.c_longlong, c.c_float, c.c_double
         lib.pnm_afno_rows_r2c.argtypes = [vp, vp, vp, ll, i, i, vp, i, i, u, ll, d, vp, vp]
         lib.pnm_afno_rows_c2r.argtypes = [vp, vp, vp, ll, i, i, vp, i, i, u, ll, vp, vp, vp]
+        lib.pnm_afno_rows_c2r_add.argtypes = [vp, vp, vp, vp, vp, ll, i, vp]
         lib.pnm_afno_cols_fwd.argtypes = [vp] * 9 + [i, vp, f, vp]
         lib.pnm_afno_cols_bwd.argtypes = [vp] * 11 + [i, vp, vp]
         lib.pnm_afno_cols_dft.argtypes = [vp, vp, vp, vp, i, f, vp]
         lib.pnm_afno_cols_idft.argtypes = [vp, vp, vp, i, f, vp]
-        for n in ("pnm_afno_rows_r2c", "pnm_afno_rows_c2r", "pnm_afno_cols_fwd", "pnm_afno_cols_bwd", "pnm_afno_cols_dft",
+        for n in ("pnm_afno_rows_r2c", "pnm_afno_rows_c2r", "pnm_afno_rows_c2r_add", "pnm_afno_cols_fwd", "pnm_afno_cols_bwd", "pnm_afno_cols_dft",
                   "pnm_afno_cols_idft"):
             getattr(lib, n).restype = i
         lib._afno_declared = True
@@ -97,7 +98,7 @@ class _AfnoFilterTcFn(torch.autograd.Function):
     ``gemm_nt`` (weight and bias gradients in one pass) and ``gemm_tn`` with the ReLU mask in the epilogue."""
 
     @staticmethod
-    def forward(ctx, tokens, w1, b1, w2, b2, geo: FilterGeometry, lam: float, exchange):
+    def forward(ctx, tokens, w1, b1, w2, b2, geo: FilterGeometry, lam: float, exchange, add_input=False, residual=None):
         lib = _lib_af()
         dev = tokens.device
         st = torch.cuda.current_stream().cuda_stream
@@ -126,13 +127,16 @@ class _AfnoFilterTcFn(torch.autograd.Function):
             rc = lib.pnm_afno_rows_r2c(_ptrs8([src.data_ptr()]), Y.data_ptr(), g.arr, g.Tp, 0, 0, None, 0, 1, 0, 0, 1.0, None, st)
             _g._check(rc, "pnm_afno_rows_r2c")
             cols()
-            rc = lib.pnm_afno_rows_c2r(Y2.data_ptr(), _ptrs8([out.data_ptr()]), g.arr, g.Tp, 1, 0, None, 0, 1, 0, 0, None, None, st)
-            _g._check(rc, "pnm_afno_rows_c2r")
+            addends = ([src] if add_input else []) + ([residual.contiguous()] if residual is not None else [])
+            _rows_c2r_local(lib, Y2, out, addends, g, 1, st)
         else:
+            if add_input or residual is not None:
+                raise ValueError("residual terms are fused only on the single-GPU path")
             out = exchange.transform(lib, tokens, Y, Y2, cols, g, kw_in=0, kw_out=1)
         _g.launch_count += 4
         ctx.save_for_backward(w1e, w2e, Z, O1, O2)
         ctx.geo, ctx.exchange, ctx.lam = geo, exchange, float(lam)
+        ctx.add_input, ctx.has_residual = bool(add_input), residual is not None
         ctx.dtypes = (w1.dtype, b1.dtype, w2.dtype, b2.dtype)
         return out
 
@@ -171,8 +175,8 @@ class _AfnoFilterTcFn(torch.autograd.Function):
             rc = lib.pnm_afno_rows_r2c(_ptrs8([d.data_ptr()]), dY2.data_ptr(), g.arr, g.Tp, 1, 0, None, 0, 1, 0, 0, 1.0, None, st)
             _g._check(rc, "pnm_afno_rows_r2c")
             cols()
-            rc = lib.pnm_afno_rows_c2r(dY.data_ptr(), _ptrs8([dx.data_ptr()]), g.arr, g.Tp, 0, 0, None, 0, 1, 0, 0, None, None, st)
-            _g._check(rc, "pnm_afno_rows_c2r")
+            # the input's own residual path: its gradient is the incoming one, added in the same store
+            _rows_c2r_local(lib, dY, dx, [d] if ctx.add_input else [], g, 0, st)
         else:
             dx = exchange.transform(lib, d, dY2, dY, cols, g, kw_in=1, kw_out=0)
         _g.launch_count += 4
@@ -188,7 +192,24 @@ class _AfnoFilterTcFn(torch.autograd.Function):
         dw2 = scatter(_fold_weight_grad(dw2e, g.Cb), (2, g.nb, g.Cb, g.Cb), dt[2])
         db1 = scatter(torch.stack([db1e[:, :g.Cb], db1e[:, g.Cb:]]), (2, g.nb, g.Cb), dt[1])
         db2 = scatter(torch.stack([db2e[:, :g.Cb], db2e[:, g.Cb:]]), (2, g.nb, g.Cb), dt[3])
-        return dx, dw1, db1, dw2, db2, None, None, None
+        return dx, dw1, db1, dw2, db2, None, None, None, None, (d if ctx.has_residual else None)
+
+
+def _rows_c2r_local(lib, Y, out, addends, g, kweight, st):
+    """Inverse row transform on one GPU; up to two ``[T, C]`` bf16 ``addends`` are summed into the stored tokens."""
+    if addends:
+        a0 = addends[0]
+        a1 = addends[1] if len(addends) > 1 else None
+        rc = lib.pnm_afno_rows_c2r_add(Y.data_ptr(), out.data_ptr(), a0.data_ptr(), None if a1 is None else a1.data_ptr(), g.arr,
+                                       g.Tp, kweight, st)
+        if rc == 0:
+            return
+        if rc != -2:
+            _g._check(rc, "pnm_afno_rows_c2r_add")
+    rc = lib.pnm_afno_rows_c2r(Y.data_ptr(), _ptrs8([out.data_ptr()]), g.arr, g.Tp, kweight, 0, None, 0, 1, 0, 0, None, None, st)
+    _g._check(rc, "pnm_afno_rows_c2r")
+    for a in addends:                       # shapes that take the fallback row kernel
+        out.add_(a)
 
 
 class _AfnoFilterFn(torch.autograd.Function):
@@ -311,10 +332,20 @@ class TokenChannelExchange:
 
 
 def afno_filter(tokens: torch.Tensor, w1, b1, w2, b2, geo: FilterGeometry, sparsity_threshold: float,
-                exchange: Optional[TokenChannelExchange] = None, mlp: str = "bf16") -> torch.Tensor:
-    """Filtered tokens (without the layer's residual): ``tokens`` is this rank's ``[Tp, C]`` bf16 slice of the token tensor.
+                exchange: Optional[TokenChannelExchange] = None, mlp: str = "bf16", add_input: bool = False,
+                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Filtered tokens: ``tokens`` is this rank's ``[Tp, C]`` bf16 slice of the token tensor.  ``add_input`` adds the
+    tokens themselves (the layer's residual) and ``residual`` one more ``[Tp, C]`` bf16 tensor (the block's skip) to the
+    result; on one GPU with the tensor-core MLP both sums happen in the store of the inverse row transform.
 
     ``mlp="bf16"`` runs the block MLP as tcgen05 GEMMs on the bf16 ``[real | imag]`` spectrum (what the reference's
     einsums do under bf16 autocast); ``mlp="fp32"`` keeps it in fp32 inside the column kernel."""
     fn = _AfnoFilterTcFn if (mlp == "bf16" and geo.Cb % 4 == 0) else _AfnoFilterFn
-    return fn.apply(tokens, w1, b1, w2, b2, geo, float(sparsity_threshold), exchange)
+    if fn is _AfnoFilterTcFn and exchange is None and (add_input or residual is not None):
+        if residual is not None and (residual.dtype != torch.bfloat16 or residual.shape != tokens.shape):
+            raise ValueError("residual must be a bf16 tensor of the tokens' shape")
+        return fn.apply(tokens, w1, b1, w2, b2, geo, float(sparsity_threshold), None, add_input, residual)
+    out = fn.apply(tokens, w1, b1, w2, b2, geo, float(sparsity_threshold), exchange)
+    if add_input:
+        out = out + tokens
+    return out if residual is None else out + residual

@@ -698,3 +698,134 @@ def test_add_scale_kernel():
         g = torch.randn_like(y)
         y.backward(g)
         assert torch.allclose(a.grad.float(), g.float() * 0.70710678, atol=2e-2) and torch.equal(a.grad, b.grad)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dims", [(2, 6, 45, 8, 8, 73), (1, 3, 5, 4, 16, 3), (2, 4, 7, 2, 3, 5), (1, 2, 40, 8, 8, 20)])
+def test_unpatchify_kernel_matches_permute(dims):
+    """Token -> image rearrangement and its gradient against the plain reshape / permute, bit for bit (a pure copy)."""
+    from physicsnemo_b200.ops import patch_loss as pl
+
+    B, h, w, p0, p1, C = dims
+    g = torch.Generator(device="cuda").manual_seed(3)
+    tokens = torch.randn(B, h, w, p0 * p1 * C, device="cuda", generator=g).to(torch.bfloat16).requires_grad_(True)
+    image = pl.unpatchify(tokens, h, w, p0, p1, C)
+    ref = pl._unpatchify_reference(tokens.detach(), h, w, p0, p1, C)
+    assert image.shape == (B, C, h * p0, w * p1)
+    assert torch.equal(image, ref)
+    dimage = torch.randn(image.shape, device="cuda", generator=g).to(torch.bfloat16)
+    image.backward(dimage)
+    assert torch.equal(tokens.grad, pl._patchify_reference(dimage, h, w, p0, p1, C))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("pd,td,n", [(torch.bfloat16, torch.float32, 1 << 20), (torch.bfloat16, torch.bfloat16, 4099),
+                                     (torch.float32, torch.float32, 77777), (torch.float32, torch.bfloat16, 8)])
+def test_squared_error_kernel(pd, td, n):
+    """Fused sum of squared differences and its gradient against the fp32 expression of the same loss."""
+    from physicsnemo_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    pred = torch.randn(n, device="cuda", generator=g).to(pd).requires_grad_(True)
+    tgt = torch.randn(n, device="cuda", generator=g).to(td)
+    loss = ops.squared_error(pred, tgt, scale=0.37 / n)
+    (3.0 * loss).backward()
+    p32 = pred.detach().float().requires_grad_(True)
+    ref = ((p32 - tgt.float()) ** 2).sum() * (0.37 / n)
+    (3.0 * ref).backward()
+    assert loss.dtype == torch.float32 and loss.ndim == 0
+    assert abs(loss.item() - ref.item()) <= 1e-5 * abs(ref.item())
+    tol = 1e-2 if pd == torch.bfloat16 else 1e-6
+    assert torch.allclose(pred.grad.float(), p32.grad, rtol=tol, atol=tol * p32.grad.abs().max().item())
+
+
+def test_patch_loss_host_paths():
+    """On the host both ops are the plain tensor expressions."""
+    from physicsnemo_b200 import ops
+
+    tokens = torch.randn(2, 3, 4, 2 * 2 * 5)
+    image = ops.unpatchify(tokens, 3, 4, 2, 2, 5)
+    assert image.shape == (2, 5, 6, 8)
+    assert image[1, 3, 2 * 2 + 1, 3 * 2 + 0] == tokens[1, 2, 3, (1 * 2 + 0) * 5 + 3]
+    a, b = torch.randn(10, requires_grad=True), torch.randn(10)
+    loss = ops.squared_error(a, b)
+    assert torch.allclose(loss, torch.nn.functional.mse_loss(a, b))
+    loss.backward()
+    assert torch.allclose(a.grad, 2 * (a.detach() - b) / 10)
+    with pytest.raises(ValueError):
+        ops.squared_error(a, torch.randn(5))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(2, 90, 180, 768, 8), (1, 12, 20, 64, 2)])
+def test_afno_filter_fused_residuals(shape):
+    """``afno_filter(add_input, residual)`` (sums in the store of the inverse row transform) against the same filter
+    followed by the two additions in fp32: output and all gradients."""
+    from physicsnemo_b200.nn.module.afno_layers import AFNO2DLayer
+    from physicsnemo_b200.ops import afno_spectral as A
+
+    B, H, W, C, nb = shape
+    torch.manual_seed(1)
+    layer = AFNO2DLayer(C, num_blocks=nb, sparsity_threshold=0.01).cuda()
+    with torch.no_grad():
+        for p in layer.parameters():
+            p.mul_(5.0)
+    geo = A.FilterGeometry(B, H, W, C, nb, H // 2 + 1)
+    args = (layer.w1, layer.b1, layer.w2, layer.b2, geo, layer.sparsity_threshold)
+    x = torch.randn(B * H * W, C, device="cuda").to(torch.bfloat16)
+    r = torch.randn(B * H * W, C, device="cuda").to(torch.bfloat16)
+    dy = torch.randn(B * H * W, C, device="cuda").to(torch.bfloat16)
+
+    x0, r0 = x.clone().requires_grad_(True), r.clone().requires_grad_(True)
+    ref = A.afno_filter(x0, *args).float() + x0.float() + r0.float()
+    ref.backward(dy.float())
+    gref = [p.grad.clone() for p in layer.parameters()]
+    layer.zero_grad()
+
+    x1, r1 = x.clone().requires_grad_(True), r.clone().requires_grad_(True)
+    out = A.afno_filter(x1, *args, add_input=True, residual=r1)
+    out.backward(dy)
+    assert out.dtype == torch.bfloat16
+    scale = ref.abs().max().item()
+    assert (out.float() - ref).abs().max().item() <= 2 ** -7 * scale           # one bf16 rounding of the sum
+    gscale = x0.grad.abs().max().item()
+    assert (x1.grad.float() - x0.grad.float()).abs().max().item() <= 2 ** -6 * gscale
+    assert torch.equal(r1.grad, dy)
+    for p, g in zip(layer.parameters(), gref):
+        assert torch.allclose(p.grad, g, rtol=1e-5, atol=1e-6 * g.abs().max().item())
+
+
+@pytest.mark.gpu
+def test_afno_block_fused_residuals_match_plain_block():
+    """The AFNO block without separate elementwise kernels against the same block written with tensor additions."""
+    from physicsnemo_b200.models.afno.afno import Block
+
+    torch.manual_seed(2)
+    for double_skip in (True, False):
+        blk = Block(64, num_blocks=2, double_skip=double_skip).cuda()
+        with torch.no_grad():
+            for p in blk.filter.parameters():
+                p.mul_(5.0)
+        x = torch.randn(1, 12, 20, 64, device="cuda").to(torch.bfloat16)
+        dy = torch.randn_like(x)
+        res = []
+        for fused in (True, False):
+            blk.zero_grad()
+            xi = x.clone().requires_grad_(True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                if fused:
+                    assert blk._fused_residuals(xi)
+                    y = blk(xi)
+                else:
+                    mixed = blk.filter(blk.norm1(xi))
+                    skip = xi
+                    if double_skip:
+                        mixed = skip = mixed + xi
+                    y = blk.mlp(blk.norm2(mixed), residual=skip)
+            y.backward(dy)
+            res.append((y.detach().float(), xi.grad.float(), [p.grad.clone() for p in blk.parameters()]))
+        (y1, g1, p1), (y0, g0, p0) = res
+        assert (y1 - y0).abs().max().item() <= 3e-2 * y0.abs().max().item()
+        assert (g1 - g0).norm().item() <= 3e-2 * g0.norm().item()
+        for a, b in zip(p1, p0):
+            assert (a - b).norm().item() <= 5e-2 * b.norm().item() + 1e-6
