@@ -1,0 +1,388 @@
+// C[M,N] = epilogue( A[M,K] * B[N,K]^T ) on CTA PAIRS: one 256 x 256 output tile per cluster of two CTAs, computed by
+// tcgen05.mma.cta_group::2.
+//
+// Why: the single-CTA kernel (gemm_tn.cuh) loads (128 + 256) x 64 operand elements per 128 x 256 x 64 block of products,
+// 85 FLOP per byte brought from L2 into shared memory.  For compute-bound shapes (K >= 512) that traffic, not the tensor
+// pipe, sets the pace: the 128 x 128 and the 128 x 256 tile both stop near the same L2 -> SM bandwidth.  A CTA pair
+// shares its operands through the pair MMA: each CTA loads only ITS 128 rows of A and ITS 128 of the 256 rows of B per
+// k-block (32 KB) and the tensor cores of both SMs read both halves of B, which gives 128 FLOP per loaded byte.
+//
+// Layout of the work (per cluster; both CTAs run the same warp roles):
+//   warp 0      TMA producer: own A half and own B half of every k-block; the byte counts of BOTH CTAs are signalled on
+//               the leader's "full" barrier (cp.async.bulk.tensor with .cta_group::2, no multicast)
+//   warp 1      leader CTA only: tcgen05.mma.cta_group::2 issuer; tcgen05.commit with a CTA mask of 0b11 releases the
+//               stage in both CTAs and publishes the finished accumulator to both epilogues
+//   warps 2..9  epilogue of the CTA's own 128 rows x 256 columns (TMEM -> registers -> fused math -> TMA store); the
+//               epilogue warps of both CTAs arrive on the leader's "accumulator free" barrier
+// Every wait is bounded; a CTA that gives up raises the library's error word and still reaches the two cluster barriers
+// that frame the kernel, so its peer is never left waiting on hardware.
+#pragma once
+#include "gemm_tn.cuh"
+
+namespace pnm {
+
+constexpr int kPairStageBytes = 2 * kBM * kBK * 2;                 // own A half + own B half: 32 KB
+constexpr int kPairTmemCols = 512;                                 // two 256-column accumulators
+// Five stages and two staging buffers per epilogue warp in every mode: a third buffer for the auxiliary operand costs a
+// stage (4 x 32 KB + 96 KB) and measured slower on K = 3072 (132 vs 124 us) and no faster on K = 768.
+template <int MODE>
+struct PairCfg {
+  static constexpr int NBUF = 2;
+  static constexpr int STAGES = 5;
+  static constexpr int STAGING = 8 * NBUF * kChunkBytes;           // 8 epilogue warps x NBUF buffers x 4 KB
+  static constexpr int SMEM = 1024 + STAGES * kPairStageBytes + STAGING + 512;
+  static_assert(SMEM <= 232448, "paired GEMM: shared memory budget");
+};
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory location in the CTA of rank `rank` of this cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 2-D tile load into THIS CTA's shared memory whose bytes are counted on a barrier of the pair's leader CTA.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t leader_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A[both CTAs' 128 rows] * B[both CTAs' column halves]
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in BOTH CTAs once the pair MMAs issued so far have retired.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask)
+               : "memory");
+}
+
+struct PairArgs {
+  int M, N, K;
+  const float* bias;
+  int act, aux_mode;
+  int num_m_tiles, num_n_tiles;      // 256 x 256 tiles
+  int* err;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, const PairArgs g) {
+  using Cfg = PairCfg<MODE>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int NBUF = Cfg::NBUF;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* staging = base + STAGES * kPairStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + Cfg::STAGING);
+  uint64_t* full = bars;                              // leader's copies are the live ones
+  uint64_t* empty = bars + STAGES;                    // per CTA, released by the leader's commits
+  uint64_t* tfull = bars + 2 * STAGES;                // per CTA, published by the leader's commits
+  uint64_t* tempty = tfull + 2;                       // leader's copies are the live ones (16 arrivals)
+  uint64_t* auxbar = tempty + 2;                      // [8 warps][NBUF], per CTA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(auxbar + 8 * NBUF);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const bool leader = rank == 0;
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int num_tiles = g.num_m_tiles * g.num_n_tiles;
+  const int num_kb = (g.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 16); }
+    for (int i = 0; i < 8 * NBUF; ++i) mbar_init(&auxbar[i], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmC);
+  }
+  if (warp == 1) { tmem_alloc_pair(tmem_slot, kPairTmemCols); tmem_relinquish_pair(); }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                 // both CTAs' barriers exist before any remote arrival or copy
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
+        const int mt = tile / g.num_n_tiles, nt = tile % g.num_n_tiles;
+        const int row0 = mt * 256 + int(rank) * kBM;              // own rows of A
+        const int col0 = nt * 256 + int(rank) * 128;              // own rows of B (output columns)
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          uint8_t* sa = base + s * kPairStageBytes;
+          if (leader) mbar_expect_tx(&full[s], 2 * kPairStageBytes);
+          const uint32_t lbar = map_to_cta(smem_u32(&full[s]), 0);
+          tma_load_2d_pair(sa, &tmA, lbar, kb * kBK, row0);
+          tma_load_2d_pair(sa + kBM * kBK * 2, &tmB, lbar, kb * kBK, col0);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer (leader CTA)
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(256, 256, false, false);
+      uint32_t it = 0, tc = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++tc) {
+        const int acc = tc & 1;
+        const uint32_t aph = (tc >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], aph ^ 1, abort_flag, g.err, ERR_WAIT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d = tmem_base + acc * 256;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          uint8_t* sa = base + s * kPairStageBytes;
+          const uint64_t ad = make_smem_desc(smem_u32(sa), 16, 1024, 2);
+          const uint64_t bd = make_smem_desc(smem_u32(sa + kBM * kBK * 2), 16, 1024, 2);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)
+            umma_f16_pair(d, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(&empty[s]);
+        }
+        if (ok) umma_commit_pair(&tfull[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int e = warp - 2, q = warp & 3, h = e >> 2;
+    constexpr int CH = 2;                              // 64-column chunks per warp per tile (128 of the 256 columns)
+    uint8_t* stg = staging + e * NBUF * kChunkBytes;
+    uint64_t* mybar = auxbar + e * NBUF;
+    const uint32_t tempty_leader[2] = {map_to_cta(smem_u32(&tempty[0]), 0), map_to_cta(smem_u32(&tempty[1]), 0)};
+    uint32_t use = 0, tc = 0;
+    bool ok = true;
+
+    auto item_coords = [&](uint32_t item, int& r0, int& c0) -> bool {
+      const int tile = cluster_id + int(item / CH) * num_clusters;
+      if (tile >= num_tiles) return false;
+      const int mt = tile / g.num_n_tiles, nt = tile % g.num_n_tiles;
+      r0 = mt * 256 + int(rank) * kBM + q * 32;
+      c0 = nt * 256 + h * 128 + int(item % CH) * 64;
+      return true;
+    };
+    auto issue_aux = [&](uint32_t item) {
+      int r0, c0;
+      if (!item_coords(item, r0, c0)) return;
+      if (lane == 0) {
+        tma_store_wait_read<NBUF - 2>();               // the buffer's previous result has left
+        const int b = item % NBUF;
+        mbar_expect_tx(&mybar[b], kChunkBytes);
+        tma_load_2d(stg + b * kChunkBytes, &tmX, &mybar[b], c0, r0);
+      }
+    };
+    if (MODE == MODE_AUX) issue_aux(0);
+
+    uint32_t item = 0;
+    for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++tc) {
+      const int acc = tc & 1;
+      const uint32_t aph = (tc >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], aph, abort_flag, g.err, ERR_WAIT_TMEM_FULL)) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int ci = 0; ci < CH; ++ci, ++item) {
+        int r0, c0;
+        item_coords(item, r0, c0);
+        if (MODE == MODE_AUX) issue_aux(item + 1);
+        float v[64];
+        const uint32_t taddr = tmem_base + acc * 256 + h * 128 + ci * 64 + (uint32_t(q * 32) << 16);
+        tmem_ld32(taddr, v);
+        tmem_ld32(taddr + 32, v + 32);
+        tmem_ld_wait();
+        if (ci == CH - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tempty_leader[acc]);
+        }
+        const bool store_ok = (r0 < g.M) && (c0 < g.N);
+        if (g.bias) {
+          if (c0 + 64 <= g.N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + c0) + j);
+              v[4 * j] += b.x; v[4 * j + 1] += b.y; v[4 * j + 2] += b.z; v[4 * j + 3] += b.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) if (c0 + j < g.N) v[j] += __ldg(g.bias + c0 + j);
+          }
+        }
+        if (MODE == MODE_Z) {                          // second output: the pre-activation
+          const int b = use % NBUF;
+          if (lane == 0) tma_store_wait_read<NBUF - 1>();
+          __syncwarp();
+          stage_write_row(stg + b * kChunkBytes, lane, v);
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (store_ok) tma_store_2d(stg + b * kChunkBytes, &tmX, c0, r0);
+            tma_store_commit();
+          }
+          ++use;
+        }
+        switch (g.act) {
+          case ACT_GELU:
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = gelu_f(v[j]);
+            break;
+          case ACT_SILU:
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = silu_f(v[j]);
+            break;
+          case ACT_RELU:
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = fmaxf(v[j], 0.f);
+            break;
+          default: break;
+        }
+        int b = use % NBUF;
+        if (MODE == MODE_AUX) {
+          b = item % NBUF;
+          const uint32_t bph = (item / NBUF) & 1;
+          if (!mbar_wait(&mybar[b], bph, abort_flag, g.err, ERR_WAIT_AUX)) { ok = false; break; }
+          float a[64];
+          stage_read_row(stg + b * kChunkBytes, lane, a);
+          switch (g.aux_mode) {
+            case AUX_ADD:
+#pragma unroll
+              for (int j = 0; j < 64; ++j) v[j] += a[j];
+              break;
+            case AUX_DGELU:
+#pragma unroll
+              for (int j = 0; j < 64; ++j) v[j] *= gelu_grad_f(a[j]);
+              break;
+            case AUX_DSILU:
+#pragma unroll
+              for (int j = 0; j < 64; ++j) v[j] *= silu_grad_f(a[j]);
+              break;
+            case AUX_DRELU:
+#pragma unroll
+              for (int j = 0; j < 64; ++j) v[j] = a[j] > 0.f ? v[j] : 0.f;
+              break;
+            default: break;
+          }
+        } else {
+          if (lane == 0) tma_store_wait_read<NBUF - 1>();
+          __syncwarp();
+        }
+        stage_write_row(stg + b * kChunkBytes, lane, v);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (store_ok) tma_store_2d(stg + b * kChunkBytes, &tmC, c0, r0);
+          tma_store_commit();
+        }
+        ++use;
+      }
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+    __syncwarp();
+  }
+  // ------------------------------------------------------------- teardown
+  if (*abort_flag) {
+    // a wait ran out: copies of this pair may still be in flight towards this CTA's shared memory; give them time to land
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) {}
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                  // the peer has issued its last read of this CTA's operands
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kPairTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------- host
+// Shapes the pair kernel takes over from the single-CTA one: one A source, no column scale, no softmax epilogues, no
+// stacked batch, no convolution, and enough work per dimension for 256 x 256 tiles to pay.
+inline bool pair_gemm_applicable(const GemmCall& c) {
+  if (c.conv || c.batch > 1 || c.split_m || c.scale || c.group_out || c.max_ctas) return false;
+  if (c.K1 != c.K || c.K2 != c.K) return false;
+  if (c.act == ACT_SOFTMAX64 || c.aux_mode == AUX_DSOFTMAX) return false;
+  if (c.Z && c.AUX) return false;
+  return c.K >= 512 && c.N >= 256 && c.M >= 2048;
+}
+
+template <int MODE>
+inline int launch_gemm_tn_pair(const GemmCall& c, int num_sms, int* err_word, cudaStream_t stream) {
+  CUtensorMap tA, tB, tC, tX;
+  if (make_tmap_2d_b16(&tA, c.A, c.M, c.K, c.lda, kBM, kBK)) return -10;
+  if (make_tmap_2d_b16(&tB, c.B, c.N, c.K, c.ldb, 128, kBK)) return -12;
+  if (make_tmap_2d_b16(&tC, c.C, c.M, c.N, c.ldc, 32, 64)) return -13;
+  if (MODE == MODE_Z) { if (make_tmap_2d_b16(&tX, c.Z, c.M, c.N, c.ldz, 32, 64)) return -14; }
+  else if (MODE == MODE_AUX) { if (make_tmap_2d_b16(&tX, c.AUX, c.M, c.N, c.ldaux, 32, 64)) return -15; }
+  else tX = tC;
+  PairArgs g;
+  g.M = c.M; g.N = c.N; g.K = c.K;
+  g.bias = c.bias; g.act = c.act; g.aux_mode = c.aux_mode;
+  g.num_m_tiles = (c.M + 255) / 256;
+  g.num_n_tiles = (c.N + 255) / 256;
+  g.err = err_word;
+  static unsigned long long attr_mask = 0;
+  if (first_use_on_device(attr_mask)) {
+    if (cudaFuncSetAttribute(gemm_tn_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<MODE>::SMEM) != cudaSuccess)
+      return -16;
+  }
+  const int tiles = g.num_m_tiles * g.num_n_tiles;
+  int clusters = num_sms / 2;
+  if (clusters > tiles) clusters = tiles;
+  if (clusters < 1) return -17;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = PairCfg<MODE>::SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemm_tn_pair_kernel<MODE>, tA, tB, tC, tX, g) != cudaSuccess) return -3;
+  return 0;
+}
+
+}  // namespace pnm

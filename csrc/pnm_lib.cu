@@ -2,9 +2,11 @@
 // pointers + a CUDA stream) that the Python layer binds with ctypes; no dependency on the
 // PyTorch headers, so the whole library rebuilds in seconds.
 #include <algorithm>
+#include <cstdlib>
 #include "common.cuh"
 #include "tmap.cuh"
 #include "gemm_tn.cuh"
+#include "gemm_tn_pair.cuh"
 #include "gemm_nt.cuh"
 #include "norm.cuh"
 #include "graph.cuh"
@@ -57,6 +59,16 @@ PeerArgs make_peer_args(const void* const* bases, int rank, int world, unsigned 
 }
 }  // namespace pnm
 
+// PNM_GEMM_PAIR=0 in the environment keeps every GEMM on the single-CTA kernel (for A/B timing).
+static bool pair_gemm_enabled() {
+  static int state = -1;
+  if (state < 0) {
+    const char* e = getenv("PNM_GEMM_PAIR");
+    state = (e && e[0] == '0') ? 0 : 1;
+  }
+  return state == 1;
+}
+
 extern "C" {
 
 int pnm_version() { return 100; }
@@ -96,6 +108,12 @@ int pnm_gemm_tn(const void* A, int lda, const void* A2, int lda2, const void* A3
   c.bias = bias; c.scale = scale; c.group_out = group_out;
   c.act = act; c.aux_mode = aux_mode; c.scale_post = scale_post; c.max_ctas = max_ctas;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 0 && pair_gemm_enabled() && pnm::pair_gemm_applicable(c)) {
+    // compute-bound shapes: 256 x 256 tiles on CTA pairs (tcgen05.mma.cta_group::2)
+    if (AUX) return pnm::launch_gemm_tn_pair<pnm::MODE_AUX>(c, g_num_sms, g_err_ptr, st);
+    if (Z) return pnm::launch_gemm_tn_pair<pnm::MODE_Z>(c, g_num_sms, g_err_ptr, st);
+    return pnm::launch_gemm_tn_pair<pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+  }
   if (AUX) return pnm::launch_gemm_tn<128, pnm::MODE_AUX>(c, g_num_sms, g_err_ptr, st);
   if (Z) return pnm::launch_gemm_tn<128, pnm::MODE_Z>(c, g_num_sms, g_err_ptr, st);
   if (bn == 0) {

@@ -192,3 +192,28 @@ def test_conv2d_same_implicit_gemm(shape):
     assert (b.grad - br.grad).abs().max() < 2e-2 * float(br.grad.abs().max())
     fused = C.conv2d_same(x.detach(), wt.detach(), b.detach(), act="silu")
     assert (fused.float() - torch.nn.functional.silu(ref.detach())).abs().max() < 4e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(2048, 256, 512), (4000, 768, 1024), (32400, 1096, 768), (2304, 520, 584)])
+@pytest.mark.parametrize("mode", ["plain", "gelu_z", "add", "dgelu", "drelu"])
+def test_gemm_tn_cta_pair_tiles(M, N, K, mode):
+    """Compute-bound shapes (K >= 512, N >= 256, M >= 2048) run as 256 x 256 tiles on CTA pairs (cta_group::2): ragged M,
+    N and K edges, every epilogue the pair kernel carries, against the fp32 statement and against the single-CTA kernel."""
+    a, b = _rand(M, K), _rand(N, K, scale=0.05)
+    bias = torch.randn(N, device="cuda")
+    aux = _rand(M, N)
+    kw = {"plain": dict(bias=bias), "gelu_z": dict(bias=bias, act=G.ACT_GELU, z_out=True),
+          "add": dict(bias=bias, aux=aux, aux_mode=G.AUX_ADD), "dgelu": dict(aux=aux, aux_mode=G.AUX_DGELU),
+          "drelu": dict(aux=aux, aux_mode=G.AUX_DRELU)}[mode]
+    out = ops.gemm_tn(a, b, **kw)
+    ref_kw = {k: v for k, v in kw.items() if k != "z_out"}
+    ref, zref = ops.gemm_tn_reference(a, b, **ref_kw)
+    single = ops.gemm_tn(a, b, bn=128 if mode == "plain" else 0, max_ctas=148, **kw)      # max_ctas keeps it off the pair kernel
+    if mode == "gelu_z":
+        (out, z), (single, zs) = out, single
+        _close(z, zref)
+        _close(z, zs, tol=1e-2)
+    _close(out, ref)
+    assert (out.float() - single.float()).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    assert ops.device_error() == 0
