@@ -110,9 +110,9 @@ int pnm_gemm_tn(const void* A, int lda, const void* A2, int lda2, const void* A3
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (bn == 0 && pair_gemm_enabled() && pnm::pair_gemm_applicable(c)) {
     // compute-bound shapes: 256 x 256 tiles on CTA pairs (tcgen05.mma.cta_group::2)
-    if (AUX) return pnm::launch_gemm_tn_pair<pnm::MODE_AUX>(c, g_num_sms, g_err_ptr, st);
-    if (Z) return pnm::launch_gemm_tn_pair<pnm::MODE_Z>(c, g_num_sms, g_err_ptr, st);
-    return pnm::launch_gemm_tn_pair<pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+    if (AUX) return pnm::launch_gemm_tn_pair<256, pnm::MODE_AUX>(c, g_num_sms, g_err_ptr, st);
+    if (Z) return pnm::launch_gemm_tn_pair<256, pnm::MODE_Z>(c, g_num_sms, g_err_ptr, st);
+    return pnm::launch_gemm_tn_pair<256, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
   }
   if (AUX) return pnm::launch_gemm_tn<128, pnm::MODE_AUX>(c, g_num_sms, g_err_ptr, st);
   if (Z) return pnm::launch_gemm_tn<128, pnm::MODE_Z>(c, g_num_sms, g_err_ptr, st);
@@ -165,6 +165,10 @@ int pnm_conv2d_nhwc(const void* x, const void* weight, void* y, int n, int h, in
   c.max_ctas = max_ctas;
   c.conv = 1; c.img_n = n; c.img_h = h; c.img_w = w; c.cin = cin; c.ksize = ksize;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 0 && pair_gemm_enabled() && pnm::pair_gemm_applicable(c)) {
+    if (cout > 128) return pnm::launch_gemm_tn_pair<256, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+    return pnm::launch_gemm_tn_pair<128, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+  }
   if (bn == 0) {
     bn = (cout > 128) ? 256 : 128;
     if (bn == 128 && cout > 64 && (long long)n * h * w >= 256LL * 2 * g_num_sms) { bn = 256; c.split_m = 1; }

@@ -169,7 +169,11 @@ def test_gemm_tn_split_m_tiles(M, N, K):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("shape", [(2, 64, 128, 24, 40, 3), (1, 128, 64, 17, 33, 3), (3, 64, 72, 8, 16, 1), (1, 192, 256, 40, 24, 5),
-                                   (1, 128, 128, 296, 272, 3), (1, 64, 96, 320, 256, 1)])
+                                   (1, 128, 128, 296, 272, 3), (1, 64, 96, 320, 256, 1),
+                                   # >= 8192 pixels and K >= 512: the CTA-pair tiles (256 x 128 and 256 x 256), with ragged image
+                                   # edges, a ragged channel edge, an odd number of pixel tiles and a 1 x 1 window
+                                   (1, 128, 256, 90, 100, 3), (1, 64, 192, 100, 90, 3), (1, 128, 128, 72, 144, 3),
+                                   (1, 512, 128, 96, 96, 1)])
 def test_conv2d_same_implicit_gemm(shape):
     from physicsnemo_b200.ops import conv as C
 
