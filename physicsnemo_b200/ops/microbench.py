@@ -240,6 +240,35 @@ def afno_filter_cases(small: bool = False):
     }
 
 
+def mlp_gemm_cases(M: int = 32400):
+    """The six GEMMs of one AFNO channel MLP (768 -> 3072 -> 768 over ``M`` tokens, forward and backward) and the
+    patch head: compute-bound shapes, which run as 256 x 256 tiles on CTA pairs (``tcgen05.mma.cta_group::2``) unless
+    ``PNM_GEMM_PAIR=0`` keeps them on the single-CTA kernel.  Each has a ``cublas_*`` twin (``torch`` matmul, without
+    the fused epilogue) as the library figure for the same product."""
+    x, h, z, dy, g1 = _r(M, 768), _r(M, 3072), _r(M, 3072), _r(M, 768), _r(M, 3072)
+    res = _r(M, 768)
+    w1, w2 = _r(3072, 768, scale=0.03), _r(768, 3072, scale=0.02)
+    w1t, w2t = w1.t().contiguous(), w2.t().contiguous()
+    b1, b2 = torch.randn(3072, device="cuda"), torch.randn(768, device="cuda")
+    wh, dh = _r(4672, 768, scale=0.03), _r(M, 4672)
+    wht = wh.t().contiguous()
+    fl = 2.0 * M * 768 * 3072
+    flh = 2.0 * M * 768 * 4672
+    out = {}
+    out["fc1_gelu_z"] = (lambda: G.gemm_tn(x, w1, bias=b1, act=G.ACT_GELU, z_out=True), fl, M * (768 + 2 * 3072) * 2)
+    out["cublas_fc1"] = (lambda: x @ w1.t(), fl, M * (768 + 3072) * 2)
+    out["fc2_residual"] = (lambda: G.gemm_tn(h, w2, bias=b2, aux=res, aux_mode=G.AUX_ADD), fl, M * (3072 + 2 * 768) * 2)
+    out["cublas_fc2"] = (lambda: h @ w2.t(), fl, M * (3072 + 768) * 2)
+    out["dgrad2_dgelu"] = (lambda: G.gemm_tn(dy, w2t, aux=z, aux_mode=G.AUX_DGELU), fl, M * (768 + 2 * 3072) * 2)
+    out["dgrad1"] = (lambda: G.gemm_tn(g1, w1t), fl, M * (3072 + 768) * 2)
+    out["wgrad2_colsum"] = (lambda: G.gemm_nt(dy, h, colsum=True), fl, M * (3072 + 768) * 2)
+    out["cublas_wgrad2"] = (lambda: dy.t() @ h, fl, M * (3072 + 768) * 2)
+    out["head"] = (lambda: G.gemm_tn(x, wh), flh, M * (768 + 4672) * 2)
+    out["cublas_head"] = (lambda: x @ wh.t(), flh, M * (768 + 4672) * 2)
+    out["head_dgrad"] = (lambda: G.gemm_tn(dh, wht), flh, M * (768 + 4672) * 2)
+    return out
+
+
 def gemm_attention_cases(small: bool = False):
     """The 512-wide single head of the SongUNet bottleneck over 16 384 tokens (4 096 in the small variant): forward and
     forward + backward of attention as GEMMs around the row softmax."""
@@ -288,6 +317,10 @@ def main():
         names = list(table)
     elif args.kernel in ("gemm_attention", "gemm_attention_small"):
         table = gemm_attention_cases(small=args.kernel == "gemm_attention_small")
+        names = list(table)
+    elif args.kernel in ("mlp_gemm", "mlp_gemm_small"):
+        args.m = 8192 if args.kernel == "mlp_gemm_small" else 32400
+        table = mlp_gemm_cases(args.m)
         names = list(table)
     elif args.kernel in ("attention", "attention_small"):
         table = attention_cases(small=args.kernel == "attention_small")
