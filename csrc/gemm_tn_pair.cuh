@@ -12,7 +12,8 @@
 //
 // Layout of the work (per cluster; both CTAs run the same warp roles):
 //   warp 0      TMA producer: own A half and own B half of every k-block; the byte counts of BOTH CTAs are signalled on
-//               the leader's "full" barrier (cp.async.bulk.tensor with .cta_group::2, no multicast)
+//               the leader's "full" barrier (tensor-map copies with .cta_group::2; every load is a unicast copy into
+//               the issuing CTA's own shared memory)
 //   warp 1      leader CTA only: tcgen05.mma.cta_group::2 issuer; tcgen05.commit with a CTA mask of 0b11 releases the
 //               stage in both CTAs and publishes the finished accumulator to both epilogues
 //   warps 2..9  epilogue of the CTA's own 128 rows x 256 columns (TMEM -> registers -> fused math -> TMA store); the
