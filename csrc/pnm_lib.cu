@@ -8,6 +8,7 @@
 #include "gemm_tn.cuh"
 #include "gemm_tn_pair.cuh"
 #include "gemm_nt.cuh"
+#include "gemm_nt_pair.cuh"
 #include "norm.cuh"
 #include "graph.cuh"
 #include "peer.cuh"
@@ -252,6 +253,10 @@ int pnm_gemm_nt(const void* A, int lda, const void* B, int ldb, float* out, int 
   c.A = A; c.lda = lda; c.B = B; c.ldb = ldb; c.out = out; c.ldo = ldo; c.colsum = colsum;
   c.M = M; c.Na = Na; c.Nb = Nb; c.max_ctas = max_ctas;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (pair_gemm_enabled() && pnm::pair_gemm_nt_applicable(c)) {
+    if (Nb > 128) return pnm::launch_gemm_nt_pair<256>(c, g_num_sms, g_err_ptr, st);
+    return pnm::launch_gemm_nt_pair<128>(c, g_num_sms, g_err_ptr, st);
+  }
   if (Nb > 128) return pnm::launch_gemm_nt<256>(c, g_num_sms, g_err_ptr, st);
   return pnm::launch_gemm_nt<128>(c, g_num_sms, g_err_ptr, st);
 }
@@ -290,6 +295,10 @@ int pnm_conv2d_wgrad_nhwc(const void* dy, const void* x, float* out, float* cols
   c.flag_up = reinterpret_cast<const uint32_t*>(flag_up); c.flag_down = reinterpret_cast<const uint32_t*>(flag_down);
   c.halo_epoch = epoch; c.halo_budget_s = budget_s;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (pair_gemm_enabled() && pnm::pair_gemm_nt_applicable(c)) {
+    if ((9 * cin) % 256 == 0) return pnm::launch_gemm_nt_pair<256>(c, g_num_sms, g_err_ptr, st);
+    return pnm::launch_gemm_nt_pair<128>(c, g_num_sms, g_err_ptr, st);
+  }
   if ((9 * cin) % 256 == 0) return pnm::launch_gemm_nt<256>(c, g_num_sms, g_err_ptr, st);
   return pnm::launch_gemm_nt<128>(c, g_num_sms, g_err_ptr, st);
 }

@@ -77,7 +77,9 @@ def test_gemm_tn_k_concat():
     _close(out, ref)
 
 
-@pytest.mark.parametrize("M,Na,Nb", [(64, 128, 128), (5000, 256, 256), (4097, 512, 256), (1000, 64, 32), (30000, 1024, 256)])
+@pytest.mark.parametrize("M,Na,Nb", [(64, 128, 128), (5000, 256, 256), (4097, 512, 256), (1000, 64, 32), (30000, 1024, 256),
+                                     # >= 8192 rows and >= 256 output rows: the CTA-pair kernel (ragged edges in all three sizes)
+                                     (32400, 768, 3072), (9001, 264, 136), (8192, 256, 128)])
 def test_gemm_nt(M, Na, Nb):
     a, b = _rand(M, Na, scale=0.3), _rand(M, Nb, scale=0.3)
     out, cs = ops.gemm_nt(a, b, colsum=True)
@@ -173,7 +175,7 @@ def test_gemm_tn_split_m_tiles(M, N, K):
                                    # >= 8192 pixels and K >= 512: the CTA-pair tiles (256 x 128 and 256 x 256), with ragged image
                                    # edges, a ragged channel edge, an odd number of pixel tiles and a 1 x 1 window
                                    (1, 128, 256, 90, 100, 3), (1, 64, 192, 100, 90, 3), (1, 128, 128, 72, 144, 3),
-                                   (1, 512, 128, 96, 96, 1)])
+                                   (1, 512, 128, 96, 96, 1), (1, 256, 256, 64, 136, 3)])
 def test_conv2d_same_implicit_gemm(shape):
     from physicsnemo_b200.ops import conv as C
 
