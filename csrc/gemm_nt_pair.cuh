@@ -4,7 +4,8 @@
 // single CTA loads for half as many products); the leader CTA issues the MMAs for both SMs; each CTA adds its 128 output
 // rows to the fp32 result with vector reductions.  Same operand layout as the single-CTA kernel (MN-major boxes of 64
 // columns, 128-byte swizzle), same convolution weight-gradient mode (4 x 16 pixel patches as reduction blocks, shifted
-// 4-D boxes of the input), without the halo variant.  Used when the output has at least 256 rows.
+// 4-D boxes of the input) including the halo variant of a row-sharded image (boundary rows from the neighbours'
+// published buffers after a bounded wait on their flags).  Used when the output has at least 256 rows.
 #pragma once
 #include "gemm_nt.cuh"
 #include "gemm_tn_pair.cuh"
@@ -27,7 +28,9 @@ struct NtPairCfg {
 
 template <int BNB>
 __global__ void __launch_bounds__(kNtThreads, 1)
-gemm_nt_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const NtArgs g) {
+gemm_nt_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmB3 /* conv + halo: 3-row box of X */,
+                    const __grid_constant__ CUtensorMap tmUp, const __grid_constant__ CUtensorMap tmDown, const NtArgs g) {
   using Cfg = NtPairCfg<BNB>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -71,6 +74,7 @@ gemm_nt_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   if (warp == 0) {
     if (lane == 0) {
+      bool up_ready = false, down_ready = false;
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = (kb / STAGES) & 1;
@@ -78,13 +82,30 @@ gemm_nt_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         uint8_t* sa = base + s * Cfg::STAGE_BYTES;
         uint8_t* sb = sa + Cfg::A_BYTES;
         const int m = m_begin + kb * kNtBK;
-        if (leader) mbar_expect_tx(&full[s], 2 * Cfg::STAGE_BYTES);
-        const uint32_t lbar = map_to_cta(smem_u32(&full[s]), 0);
+        int n = 0, y0 = 0, x0 = 0;
         if (g.conv) {
           const int patch = m / kNtBK;
           const int per_img = g.tiles_x * g.tiles_y;
-          const int n = patch / per_img, r = patch - n * per_img;
-          const int y0 = (r / g.tiles_x) * kWgTileH, x0 = (r % g.tiles_x) * kWgTileW;
+          n = patch / per_img;
+          const int r = patch - n * per_img;
+          y0 = (r / g.tiles_x) * kWgTileH; x0 = (r % g.tiles_x) * kWgTileW;
+          // the flags are looked at before the stage is armed, so that a time-out leaves no barrier half expected
+          bool flags_ok = true;
+          if (g.halo) {
+            if (y0 == 0 && g.has_up && g.flag_up && !up_ready) {
+              flags_ok = wait_remote_flag(g.flag_up, g.halo_epoch, abort_flag, g.err, g.halo_budget_ns);
+              up_ready = flags_ok;
+            }
+            if (flags_ok && y0 + kWgTileH >= g.img_h && g.has_down && g.flag_down && !down_ready) {
+              flags_ok = wait_remote_flag(g.flag_down, g.halo_epoch, abort_flag, g.err, g.halo_budget_ns);
+              down_ready = flags_ok;
+            }
+          }
+          if (!flags_ok) break;
+        }
+        if (leader) mbar_expect_tx(&full[s], 2 * Cfg::STAGE_BYTES);
+        const uint32_t lbar = map_to_cta(smem_u32(&full[s]), 0);
+        if (g.conv) {
 #pragma unroll
           for (int i = 0; i < 2; ++i) tma_load_4d_pair(sa + i * 8192, &tmA, lbar, a_col0 + i * 64, x0, y0, n);
 #pragma unroll
@@ -92,7 +113,17 @@ gemm_nt_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int col = b_col0 + i * 64;
             int tap = col / g.cin, c0 = col - tap * g.cin;
             if (tap >= 9) { tap = 4; c0 = g.cin; }           // past the last tap: channel coordinate out of range reads zeros
-            tma_load_4d_pair(sb + i * 8192, &tmB, lbar, c0, x0 + tap % 3 - 1, y0 + tap / 3 - 1, n);
+            const int xs = x0 + tap % 3 - 1, ys = y0 + tap / 3 - 1;
+            uint8_t* dst = sb + i * 8192;
+            if (g.halo && ys < 0 && g.has_up) {
+              tma_load_4d_pair(dst, &tmUp, lbar, c0, xs, 0, n);                          // row -1: upper neighbour's last row
+              tma_load_4d_pair(dst + kWgTileW * 128, &tmB3, lbar, c0, xs, 0, n);         // rows 0 .. 2
+            } else if (g.halo && ys + kWgTileH > g.img_h && g.has_down) {
+              tma_load_4d_pair(dst, &tmB3, lbar, c0, xs, ys, n);                         // rows H-3 .. H-1
+              tma_load_4d_pair(dst + (kWgTileH - 1) * kWgTileW * 128, &tmDown, lbar, c0, xs, 0, n);  // row H
+            } else {
+              tma_load_4d_pair(dst, &tmB, lbar, c0, xs, ys, n);
+            }
           }
         } else {
 #pragma unroll
@@ -172,7 +203,8 @@ gemm_nt_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 }
 
 inline bool pair_gemm_nt_applicable(const NtCall& c) {
-  if (c.batch > 1 || c.halo || c.max_ctas) return false;
+  if (c.batch > 1 || c.max_ctas) return false;
+  if (c.halo && (!c.conv || (c.img_h % kWgTileH))) return false;
   if (c.Na < 256 || c.Nb < 128) return false;
   const long long rows = c.conv ? (long long)c.img_n * c.img_h * c.img_w : c.M;
   return rows >= 8192;
@@ -181,20 +213,30 @@ inline bool pair_gemm_nt_applicable(const NtCall& c) {
 template <int BNB>
 inline int launch_gemm_nt_pair(const NtCall& c, int num_sms, int* err_word, cudaStream_t stream) {
   using Cfg = NtPairCfg<BNB>;
-  CUtensorMap tA, tB;
+  CUtensorMap tA, tB, tB3, tUp, tDown;
   NtArgs g = {};
   g.conv = c.conv; g.img_n = c.img_n; g.img_h = c.img_h; g.img_w = c.img_w; g.cin = c.cin;
+  g.halo = c.conv ? c.halo : 0; g.has_up = c.up_rows != nullptr; g.has_down = c.down_rows != nullptr;
+  g.flag_up = c.flag_up; g.flag_down = c.flag_down; g.halo_epoch = c.halo_epoch;
+  g.halo_budget_ns = c.halo_budget_s > 0.0 ? (unsigned long long)(c.halo_budget_s * 1e9) : kWaitBudgetNs;
   int M = c.M;
   if (c.conv) {
     if (c.cin % 64 || c.Nb != 9 * c.cin || c.Na < 64) return -24;
     if (make_tmap_nhwc_b16(&tA, c.A, c.img_n, c.img_h, c.img_w, c.Na, kWgTileH, kWgTileW)) return -20;
     if (make_tmap_nhwc_b16(&tB, c.B, c.img_n, c.img_h, c.img_w, c.cin, kWgTileH, kWgTileW)) return -21;
+    tB3 = tB; tUp = tB; tDown = tB;
+    if (g.halo) {
+      if (make_tmap_nhwc_b16(&tB3, c.B, c.img_n, c.img_h, c.img_w, c.cin, kWgTileH - 1, kWgTileW)) return -21;
+      if (c.up_rows && make_tmap_nhwc_b16(&tUp, c.up_rows, c.img_n, 1, c.img_w, c.cin, 1, kWgTileW)) return -21;
+      if (c.down_rows && make_tmap_nhwc_b16(&tDown, c.down_rows, c.img_n, 1, c.img_w, c.cin, 1, kWgTileW)) return -21;
+    }
     g.tiles_x = (c.img_w + kWgTileW - 1) / kWgTileW;
     g.tiles_y = (c.img_h + kWgTileH - 1) / kWgTileH;
     M = c.img_n * g.tiles_x * g.tiles_y * kNtBK;       // reduction rows = patches of 64 pixels
   } else {
     if (make_tmap_2d_b16(&tA, c.A, c.M, c.Na, c.lda, kNtBK, 64)) return -20;
     if (make_tmap_2d_b16(&tB, c.B, c.M, c.Nb, c.ldb, kNtBK, 64)) return -21;
+    tB3 = tB; tUp = tB; tDown = tB;
   }
   g.M = M; g.Na = c.Na; g.Nb = c.Nb;
   g.tiles_a = (c.Na + 255) / 256;
@@ -226,7 +268,7 @@ inline int launch_gemm_nt_pair(const NtCall& c, int num_sms, int* err_word, cuda
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, gemm_nt_pair_kernel<BNB>, tA, tB, g) != cudaSuccess) return -23;
+  if (cudaLaunchKernelEx(&cfg, gemm_nt_pair_kernel<BNB>, tA, tB, tB3, tUp, tDown, g) != cudaSuccess) return -23;
   return 0;
 }
 

@@ -105,8 +105,11 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 // 128-pixel tiles x 128 (the last pair may own a single tile) and halo is 0.
 template <int BN, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, const GemmArgs g) {
+gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2 /* halo: 7-row box */,
+                    const __grid_constant__ CUtensorMap tmA3 /* halo: upper neighbour's row */,
+                    const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+                    const __grid_constant__ CUtensorMap tmX /* Z (store), aux (load) or, halo: lower neighbour's row */,
+                    const GemmArgs g) {
   using Cfg = PairCfg<BN, MODE>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int NBUF = Cfg::NBUF;
@@ -148,6 +151,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ------------------------------------------------------------ producer (both CTAs)
     if (lane == 0) {
       uint32_t it = 0;
+      bool up_ready = false, down_ready = false;
       for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
         const int mt = tile / g.num_n_tiles, nt = tile % g.num_n_tiles;
         const int mt1 = 2 * mt + int(rank);                       // own 128-row tile of A
@@ -165,7 +169,26 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const int k = kb * kBK;
           if (g.conv) {
             const int tap = k / g.cin, c0 = k - tap * g.cin;
-            tma_load_4d_pair(sa, &tmA, lbar, c0, cx0 + tap % g.ksize - g.pad, cy0 + tap / g.ksize - g.pad, cn);
+            const int xs = cx0 + tap % g.ksize - g.pad, ys = cy0 + tap / g.ksize - g.pad;
+            if (g.halo && ys < 0 && g.has_up) {
+              // box rows -1 .. 6: row -1 is the upper neighbour's published bottom row (peer memory, plain copy), rows 0 .. 6 local
+              if (!up_ready) {
+                if (!wait_remote_flag(g.flag_up, g.halo_epoch, abort_flag, g.err, g.halo_budget_ns)) { ok = false; break; }
+                up_ready = true;
+              }
+              tma_load_4d_pair(sa, &tmA3, lbar, c0, xs, 0, cn);
+              tma_load_4d_pair(sa + kConvTileW * 128, &tmA2, lbar, c0, xs, 0, cn);
+            } else if (g.halo && ys + kConvTileH > g.img_h && g.has_down) {
+              // box rows H-7 .. H: rows H-7 .. H-1 local, row H is the lower neighbour's published top row
+              if (!down_ready) {
+                if (!wait_remote_flag(g.flag_down, g.halo_epoch, abort_flag, g.err, g.halo_budget_ns)) { ok = false; break; }
+                down_ready = true;
+              }
+              tma_load_4d_pair(sa, &tmA2, lbar, c0, xs, ys, cn);
+              tma_load_4d_pair(sa + (kConvTileH - 1) * kConvTileW * 128, &tmX, lbar, c0, xs, 0, cn);
+            } else {
+              tma_load_4d_pair(sa, &tmA, lbar, c0, xs, ys, cn);
+            }
           } else {
             tma_load_2d_pair(sa, &tmA, lbar, k, mt1 * kBM);
           }
@@ -370,9 +393,11 @@ inline int pair_gemm_min_k() {
 }
 
 // Shapes the pair kernel takes over from the single-CTA one: one A source, no column scale, no softmax epilogues, no
-// stacked batch, no halo exchange, and enough work per dimension for 256-row tiles to pay.
+// stacked batch, and enough work per dimension for 256-row tiles to pay.  The halo-fused 3 x 3 convolution of a row-sharded
+// image is carried too (boundary rows from the neighbours' published buffers after a bounded wait on their flags).
 inline bool pair_gemm_applicable(const GemmCall& c) {
-  if (c.batch > 1 || c.split_m || c.scale || c.group_out || c.max_ctas || c.halo) return false;
+  if (c.batch > 1 || c.split_m || c.scale || c.group_out || c.max_ctas) return false;
+  if (c.halo && (!c.conv || c.ksize != 3 || (c.img_h % kConvTileH))) return false;
   if (c.K1 != c.K || c.K2 != c.K) return false;
   if (c.act == ACT_SOFTMAX64 || c.aux_mode == AUX_DSOFTMAX) return false;
   if (c.Z && c.AUX) return false;
@@ -391,7 +416,7 @@ inline bool pair_gemm_applicable(const GemmCall& c) {
 template <int BN, int MODE>
 inline int launch_gemm_tn_pair(const GemmCall& c, int num_sms, int* err_word, cudaStream_t stream) {
   using Cfg = PairCfg<BN, MODE>;
-  CUtensorMap tA, tB, tC, tX;
+  CUtensorMap tA, tA2, tA3, tB, tC, tX;
   GemmArgs g = {};
   g.M = c.M; g.N = c.N; g.K = c.K; g.K1 = c.K; g.K2 = c.K;
   g.bias = c.bias; g.act = c.act; g.aux_mode = c.aux_mode;
@@ -406,6 +431,14 @@ inline int launch_gemm_tn_pair(const GemmCall& c, int num_sms, int* err_word, cu
     g.tiles_y = (c.img_h + kConvTileH - 1) / kConvTileH;
     tiles128 = c.img_n * g.tiles_x * g.tiles_y;
     g.M = tiles128 * kBM;                  // every row of a valid tile is "in range"; the copy engine clips at image edges
+    tA2 = tA; tA3 = tA;
+    if (c.halo) {
+      if (make_tmap_nhwc_b16(&tA2, c.A, c.img_n, c.img_h, c.img_w, c.cin, kConvTileH - 1, kConvTileW)) return -11;
+      if (c.up_rows && make_tmap_nhwc_b16(&tA3, c.up_rows, c.img_n, 1, c.img_w, c.cin, 1, kConvTileW)) return -18;
+      g.halo = 1; g.has_up = c.up_rows != nullptr; g.has_down = c.down_rows != nullptr;
+      g.flag_up = c.flag_up; g.flag_down = c.flag_down; g.halo_epoch = c.halo_epoch;
+      g.halo_budget_ns = c.halo_budget_s > 0.0 ? (unsigned long long)(c.halo_budget_s * 1e9) : kWaitBudgetNs;
+    }
   } else {
     if (make_tmap_2d_b16(&tA, c.A, c.M, c.K, c.lda, kBM, kBK)) return -10;
     if (make_tmap_2d_b16(&tC, c.C, c.M, c.N, c.ldc, 32, 64)) return -13;
@@ -413,7 +446,9 @@ inline int launch_gemm_tn_pair(const GemmCall& c, int num_sms, int* err_word, cu
   if (make_tmap_2d_b16(&tB, c.B, c.N, c.K, c.ldb, Cfg::B_ROWS, kBK)) return -12;
   if (MODE == MODE_Z) { if (make_tmap_2d_b16(&tX, c.Z, c.M, c.N, c.ldz, 32, 64)) return -14; }
   else if (MODE == MODE_AUX) { if (make_tmap_2d_b16(&tX, c.AUX, c.M, c.N, c.ldaux, 32, 64)) return -15; }
+  else if (c.conv && c.halo && c.down_rows) { if (make_tmap_nhwc_b16(&tX, c.down_rows, c.img_n, 1, c.img_w, c.cin, 1, kConvTileW)) return -15; }
   else tX = tC;
+  if (!c.conv) { tA2 = tA; tA3 = tA; }
   g.num_m_tiles = (tiles128 + 1) / 2;
   g.num_n_tiles = (c.N + BN - 1) / BN;
   static unsigned long long attr_mask = 0;
@@ -437,7 +472,7 @@ inline int launch_gemm_tn_pair(const GemmCall& c, int num_sms, int* err_word, cu
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, gemm_tn_pair_kernel<BN, MODE>, tA, tB, tC, tX, g) != cudaSuccess) return -3;
+  if (cudaLaunchKernelEx(&cfg, gemm_tn_pair_kernel<BN, MODE>, tA, tA2, tA3, tB, tC, tX, g) != cudaSuccess) return -3;
   return 0;
 }
 

@@ -236,6 +236,10 @@ int pnm_conv2d_nhwc_halo(const void* x, const void* weight, void* y, int n, int 
   c.flag_up = reinterpret_cast<const uint32_t*>(flag_up); c.flag_down = reinterpret_cast<const uint32_t*>(flag_down);
   c.halo_epoch = epoch; c.halo_budget_s = budget_s;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 0 && pair_gemm_enabled() && pnm::pair_gemm_applicable(c)) {
+    if (cout > 128) return pnm::launch_gemm_tn_pair<256, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+    return pnm::launch_gemm_tn_pair<128, pnm::MODE_PLAIN>(c, g_num_sms, g_err_ptr, st);
+  }
   if (bn == 0) {
     bn = (cout > 128) ? 256 : 128;
     if (bn == 128 && cout > 64 && (long long)n * h * w >= 256LL * 2 * g_num_sms) { bn = 256; c.split_m = 1; }
