@@ -92,15 +92,24 @@ class TokenShardedAFNO:
         x = x + m.pos_embed[0, self.pos_index]          # fp32 like the stock forward: the first block's skip stays fp32
         for blk in m.blocks:
             f = blk.filter
-            xn = ops.layer_norm(x, blk.norm1.weight, blk.norm1.bias, blk.norm1.eps)
+            # bf16 tokens: each LayerNorm hands its input on as the skip tensor, so the two gradient paths of a skip are
+            # summed inside the LayerNorm backward kernel instead of by a separate add (the first block's tokens are fp32)
+            alias = x.dtype == torch.bfloat16
+            if alias:
+                xn, x = ops.layer_norm(x, blk.norm1.weight, blk.norm1.bias, blk.norm1.eps, return_residual=True)
+            else:
+                xn = ops.layer_norm(x, blk.norm1.weight, blk.norm1.bias, blk.norm1.eps)
             y = A.afno_filter(xn, f.w1, f.b1, f.w2, f.b2, self.geo, f.sparsity_threshold, self.exchange)
             x1 = y + xn                                             # the filter's own residual
             if blk.double_skip:
                 x1 = x1 + x
-                res = x1
+                if x1.dtype == torch.bfloat16:
+                    n2, res = ops.layer_norm(x1, blk.norm2.weight, blk.norm2.bias, blk.norm2.eps, return_residual=True)
+                else:
+                    n2, res = ops.layer_norm(x1, blk.norm2.weight, blk.norm2.bias, blk.norm2.eps), x1
             else:
-                res = x
-            x = blk.mlp(ops.layer_norm(x1, blk.norm2.weight, blk.norm2.bias, blk.norm2.eps), residual=res)
+                n2, res = ops.layer_norm(x1, blk.norm2.weight, blk.norm2.bias, blk.norm2.eps), x
+            x = blk.mlp(n2, residual=res)
         return ops.linear(x, m.head.weight, None)
 
     __call__ = forward
