@@ -154,10 +154,11 @@ class _AfnoFilterTcFn(torch.autograd.Function):
         if g.Mp > g.Mb:
             G2[:, g.Mb:].zero_()          # zero padding rows: they then contribute nothing to the weight gradients
         G1, dZ = torch.empty_like(Z), torch.empty_like(Z)
-        dw1e = torch.zeros(g.nblk, cb2, cb2, dtype=torch.float32, device=dev)
-        dw2e = torch.zeros_like(dw1e)
-        db1e = torch.zeros(g.nblk, cb2, dtype=torch.float32, device=dev)
-        db2e = torch.zeros_like(db1e)
+        # the four accumulators of the weight / bias gradients as views of ONE zero-filled buffer (one fill kernel, not four)
+        nw, nbias = g.nblk * cb2 * cb2, g.nblk * cb2
+        acc = torch.zeros(2 * nw + 2 * nbias, dtype=torch.float32, device=dev)
+        dw1e, dw2e = acc[:nw].view(g.nblk, cb2, cb2), acc[nw:2 * nw].view(g.nblk, cb2, cb2)
+        db1e, db2e = acc[2 * nw:2 * nw + nbias].view(g.nblk, cb2), acc[2 * nw + nbias:].view(g.nblk, cb2)
         w1t, w2t = w1e.transpose(1, 2).contiguous(), w2e.transpose(1, 2).contiguous()
 
         def cols():
@@ -184,6 +185,8 @@ class _AfnoFilterTcFn(torch.autograd.Function):
         own = slice(g.blk0, g.blk0 + g.nblk)
 
         def scatter(part, shape, dtype):
+            if g.nblk == g.nb:                       # this rank owns every block: nothing to embed
+                return part.to(dtype)
             full = torch.zeros(shape, dtype=torch.float32, device=dev)
             full[:, own] = part
             return full.to(dtype)
